@@ -1,0 +1,400 @@
+#!/usr/bin/env python3
+"""Benchmark of the decode linear stack (the hot path) on B200.
+
+A "step" is one decode step of the Qwen3-0.6B-shaped linear stack: the four
+projections (fused QKV, O, fused gate/up, down) of all 28 layers, block-quantised
+weights, each projection with its own seeded activation matrix, executed by the
+grouped persistent launch of libizwi_b200.so.  All inputs are synthetic and
+seeded.  One JSON line is printed by rank 0.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+  python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+`value` is tokens/s with everything resident in HBM; `e2e` is the same metric
+through the C ABI with host activations copied in and host results copied out
+every step; `roofline` is algorithmic bytes per launch over the measured launch
+time against the measured HBM copy bandwidth; `cpu_baseline` / `--impl
+reference` time the CPU restatement of the same stack on the host cores.
+At N > 1 the stack does not shard (0.6B decode): each rank runs a replica.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "decode_linear_stack_tokens_per_s"
+WORKLOADS = {
+    # name: (format, tokens per step)
+    "qwen3-0.6b-q8_0-m1": ("q8_0", 1),
+    "qwen3-0.6b-q8_0-m4": ("q8_0", 4),
+    "qwen3-0.6b-q8_0-m16": ("q8_0", 16),
+    "qwen3-0.6b-q8_0-m64": ("q8_0", 64),
+    "qwen3-0.6b-q4_k-m1": ("q4_k", 1),
+    "qwen3-0.6b-q4_k-m4": ("q4_k", 4),
+    "qwen3-0.6b-q4_k-m16": ("q4_k", 16),
+    "qwen3-0.6b-q4_k-m64": ("q4_k", 64),
+    "qwen3-0.6b-bf16-m1": ("bf16", 1),
+}
+DEFAULT_WORKLOAD = "qwen3-0.6b-q8_0-m1"
+WEIGHT_SEED, ACT_SEED = 0, 2
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the grouped kernel, from the ncu
+# capture summarised under profiles/ (None until a capture exists for that workload).
+NCU_DRAM_BYTES_PER_LAUNCH = {}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock, power and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples = []  # (time, sm_mhz, power_w, reasons bitmask)
+        self.stop_flag = threading.Event()
+        self.max_mhz = None
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                power = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                self.samples.append((time.perf_counter(), mhz, power, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def summary(self, t0: float, t1: float):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml_unavailable"]}
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        where = "timed_region"
+        if len(inside) < 3:  # a very short timed region: fall back to every sample taken under load
+            inside, where = self.samples, "warmup_and_timed_region"
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+                 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+        mask = 0
+        for s in inside:
+            mask |= s[3]
+        return {"sm_mhz": statistics.median(s[1] for s in inside) if inside else None,
+                "sm_max_mhz": self.max_mhz,
+                "power_w_max": max((s[2] for s in inside), default=None),
+                "reasons": [n for b, n in names.items() if mask & b],
+                "samples": len(inside), "sampled_during": where}
+
+
+def dist_setup(n_gpus: int):
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return world, rank, local
+
+
+def barrier(world):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, world: int) -> float:
+    if world == 1:
+        return ms
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps: int, world: int):
+    """Exactly `steps` calls of fn between CUDA events on the launching stream, barrier + sync on both sides."""
+    import torch
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world), t0, t1
+
+
+def oracle_lib():
+    import subprocess
+    so = ROOT / "oracle" / "liboracle_c.so"
+    if not so.exists():
+        subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True, capture_output=True)
+    lib = ctypes.CDLL(str(so))
+    lib.orc_num_threads.restype = ctypes.c_int
+    return lib
+
+
+class CpuStack:
+    """The same stack on the host: raw weight bytes (or fp32 for bf16) + fp32 activations, run by the C port."""
+
+    def __init__(self, stack):
+        import numpy as np
+        import torch
+        self.lib = oracle_lib()
+        self.fmt, self.m = stack.fmt, stack.m
+        self.items = []
+        for wl, al in zip(stack.weights, stack.acts):
+            for (_, n, k), w, x in zip(stack.shape.projections, wl, al):
+                wh = (w.float() if self.fmt == "bf16" else w).cpu().numpy()
+                xh = x.float().cpu().numpy()
+                self.items.append((np.ascontiguousarray(wh), np.ascontiguousarray(xh), np.empty((self.m, n), np.float32), n, k))
+        self.cores = self.lib.orc_num_threads()
+
+    def step(self):
+        vp = ctypes.c_void_p
+        for wh, xh, yh, n, k in self.items:
+            if self.fmt == "bf16":
+                self.lib.orc_linear_f32(xh.ctypes.data_as(vp), wh.ctypes.data_as(vp), None, yh.ctypes.data_as(vp),
+                                        ctypes.c_int64(self.m), ctypes.c_int64(n), ctypes.c_int64(k))
+            else:
+                self.lib.orc_qlinear_f32(0 if self.fmt == "q8_0" else 1, xh.ctypes.data_as(vp), wh.ctypes.data_as(vp),
+                                         yh.ctypes.data_as(vp), ctypes.c_int64(self.m), ctypes.c_int64(n),
+                                         ctypes.c_int64(k))
+
+    def timed(self, budget_s: float, max_steps: int = 400):
+        self.step()  # warm-up (page in, thread pool)
+        t0 = time.perf_counter()
+        self.step()
+        one = time.perf_counter() - t0
+        n = int(max(1, min(max_steps, budget_s / max(one, 1e-6))))
+        t0 = time.perf_counter()
+        for _ in range(n):
+            self.step()
+        dt = time.perf_counter() - t0
+        return n, dt
+
+
+def make_stack(workload: str, device):
+    from izwi_b200 import workloads as wl
+    fmt, m = WORKLOADS[workload]
+    return wl.make_linear_stack(wl.QWEN3_0_6B, fmt, m, device, WEIGHT_SEED, ACT_SEED)
+
+
+def measure_case(workload: str, device, steps: int, warmup: int, peak: float):
+    """Short device-resident measurement of one more configuration (not the headline line)."""
+    import torch
+    from izwi_b200 import workloads as wl
+    stack = make_stack(workload, device)
+    group = wl.stack_group(stack)
+    for _ in range(warmup):
+        group.launch()
+    ms, _, _ = time_steps(group.launch, steps, 1)
+    group.ctx.check()
+    per = ms / steps
+    gbs = stack.algorithmic_bytes / (per * 1e-3) / 1e9
+    out = {"workload": workload, "ms_per_step": round(per, 5), "tokens_per_s": round(stack.m / (per * 1e-3), 1),
+           "hbm_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak, 4),
+           "tflops": round(stack.flops / (per * 1e-3) / 1e12, 2)}
+    del group, stack
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args):
+    import torch
+    from izwi_b200 import workloads as wl
+
+    world, rank, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    peak, peak_kind = load_peaks()
+    fmt, m = WORKLOADS[args.workload]
+
+    stack = make_stack(args.workload, device)
+    group = wl.stack_group(stack)
+    ctx = group.ctx
+
+    for _ in range(max(args.warmup, 3)):
+        group.launch()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = ctx.launch_count
+    ms, t0, t1 = time_steps(group.launch, args.steps, world)
+    launches = ctx.launch_count - launches0
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    ctx.check()  # raises if any bounded device-side wait gave up
+
+    per_ms = ms / args.steps
+    tokens_per_s = world * m / (per_ms * 1e-3)
+    achieved = stack.algorithmic_bytes / (per_ms * 1e-3) / 1e9
+
+    # ---- end to end through the C ABI: host activations in, host results out, every step ----
+    h_in = torch.empty_like(stack.acts_buf, device="cpu").pin_memory()
+    h_in.copy_(stack.acts_buf)
+    h_out = torch.empty_like(stack.outs_buf, device="cpu").pin_memory()
+
+    def e2e_step():
+        stack.acts_buf.copy_(h_in, non_blocking=True)
+        group.launch()
+        h_out.copy_(stack.outs_buf, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result before the next token
+
+    e2e_steps = max(3, min(args.steps, 2000))
+    for _ in range(3):
+        e2e_step()
+    e2e_ms, _, _ = time_steps(e2e_step, e2e_steps, world)
+    e2e_tokens = world * m / (e2e_ms / e2e_steps * 1e-3)
+    ctx.check()
+
+    line = {
+        "metric": METRIC, "value": round(tokens_per_s, 2), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(per_ms, 6),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "weights": fmt, "tokens_per_step": m,
+                   "layers": stack.shape.layers, "projections_per_layer": 4,
+                   "weight_bytes": stack.weight_bytes, "launch": "one grouped persistent launch per step",
+                   "l2": f"inputs larger than L2 ({stack.weight_bytes / 1e6:.0f} MB streamed per step vs 126 MB)",
+                   "multi_gpu": "replicas only (the 0.6B decode stack does not shard)" if world > 1 else "single GPU"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
+                     "frac_of_nominal_8000": round(achieved / 8000.0, 4),
+                     "algorithmic_bytes_per_launch": stack.algorithmic_bytes,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)},
+        "e2e": {"value": round(e2e_tokens, 2), "unit": "tokens/s",
+                "h2d_bytes_per_step": h_in.numel() * 2, "d2h_bytes_per_step": h_out.numel() * 2,
+                "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": sampler.summary(t0, t1),
+    }
+
+    if rank == 0 and world == 1:
+        if not args.no_cpu_baseline:
+            cpu = CpuStack(stack)
+            # parity of the timed path against the checker, on the spot
+            import numpy as np
+            cpu.step()
+            worst_rel, worst_cos = 0.0, 1.0
+            flat_out = [y for ol in stack.outs for y in ol]
+            for (wh, xh, yh, n, k), yd in list(zip(cpu.items, flat_out))[:8]:
+                g = yd.float().cpu().numpy()
+                denom = np.abs(yh).max(axis=1, keepdims=True)
+                worst_rel = max(worst_rel, float((np.abs(g - yh) / np.where(denom == 0, 1, denom)).max()))
+                worst_cos = min(worst_cos, float((g * yh).sum() / (np.linalg.norm(g) * np.linalg.norm(yh))))
+            line["parity"] = {"max_rel_err": round(worst_rel, 6), "min_cosine": round(worst_cos, 7),
+                              "checked": "first 2 layers vs CPU port", "gate": "rel<=2e-2, cos>=0.9999"}
+            n, dt = cpu.timed(args.cpu_seconds)
+            line["cpu_baseline"] = {"value": round(n * m / dt, 3), "unit": "tokens/s", "cores": cpu.cores,
+                                    "kind": "port",
+                                    "sample": f"{n} full decode steps of the same stack (dequantise + fp32 dot, "
+                                              f"OpenMP over weight rows), {dt:.1f} s"}
+            del cpu
+        if not args.no_cases:
+            del group
+            cases = []
+            for wname in WORKLOADS:
+                if wname == args.workload:
+                    continue
+                cases.append(measure_case(wname, device, args.case_steps, 5, peak))
+            line["cases"] = cases
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement of the same stack on the host cores (the reference's
+    own Candle CPU path cannot be built without a Rust toolchain)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    fmt, m = WORKLOADS[args.workload]
+    stack = make_stack(args.workload, dev)
+    cpu = CpuStack(stack)
+    weight_bytes = stack.weight_bytes
+    del stack
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu.step()
+    steps = max(1, min(args.steps, 50))  # each step is a full CPU decode step; bounded so the run ends in minutes
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu.step()
+    dt = time.perf_counter() - t0
+    v = round(steps * m / dt, 3)
+    sample = f"{steps} full decode steps of the stack on the host cores"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": round(dt / steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "weights": fmt, "tokens_per_step": m, "weight_bytes": weight_bytes},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cpu.cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--case-steps", type=int, default=300)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cases", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,126 @@
+/*
+ * izwi_b200 — C ABI of the B200 (sm_100a) matrix-multiplication hot path of
+ * izwi-core: decode/prefill linear layers over dense bf16 and GGML
+ * block-quantised (Q8_0, Q4_K) weights, SwiGLU glue, block dequantisation,
+ * and the top-k mixture-of-experts path.
+ *
+ * Conventions (identical to the reference's Candle `Linear`):
+ *   - row-major; W is [N = out, K = in]; X is [M, K]; Y = X . W^T (+ bias).
+ *   - every pointer is a DEVICE pointer unless the name starts with `host_`.
+ *   - entry points never allocate or free device memory (izb_ctx_create /
+ *     izb_ctx_destroy excepted); the caller owns x / w / y / workspace.
+ *   - every launch goes to the caller's stream; entry points are re-entrant.
+ *   - return value: IZB_OK (0) or a negative izb_status. No exceptions cross
+ *     this boundary and there is no CPU fallback.
+ *
+ * File:line citations name the interface of the reference
+ * (crates/izwi-core/src/...) that the entry point stands behind.
+ */
+#ifndef IZWI_B200_H
+#define IZWI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct izb_ctx izb_ctx;
+typedef void* izb_stream; /* a cudaStream_t / CUstream */
+
+typedef enum izb_status {
+    IZB_OK = 0,
+    IZB_ERR_BAD_ARG = -1,     /* null / misaligned pointer, negative size, shape mismatch */
+    IZB_ERR_UNSUPPORTED = -2, /* shape or dtype outside what the kernels cover */
+    IZB_ERR_LAUNCH = -3,      /* CUDA runtime refused the launch or the copy */
+    IZB_ERR_TIMEOUT = -4,     /* a bounded device-side wait gave up */
+    IZB_ERR_NO_DEVICE = -5    /* no sm_100 device / driver entry point missing */
+} izb_status;
+
+typedef enum izb_dtype { IZB_BF16 = 0, IZB_F32 = 1 } izb_dtype;
+
+/* Weight storage formats: dense bf16 (Candle `Linear` weight) or raw GGML
+ * blocks exactly as they sit in a GGUF file (Candle `QTensor` data). */
+typedef enum izb_wfmt { IZB_W_BF16 = 0, IZB_W_Q8_0 = 1, IZB_W_Q4_K = 2 } izb_wfmt;
+
+int32_t izb_version(void);
+const char* izb_status_string(int32_t status);
+
+/* One context per device and host thread group; owns a small device status
+ * word that kernels use to report a bounded wait that ran out. */
+int32_t izb_ctx_create(int32_t device, izb_ctx** out);
+int32_t izb_ctx_destroy(izb_ctx* ctx);
+/* Synchronises `stream`, then returns IZB_ERR_TIMEOUT if any kernel launched
+ * through this context recorded a wait that gave up (and clears the record). */
+int32_t izb_ctx_check(izb_ctx* ctx, izb_stream stream);
+/* Number of kernels this context has launched so far (diagnostic counter). */
+int64_t izb_ctx_launch_count(const izb_ctx* ctx);
+
+/* Byte size of `rows x cols` values in a block format; fails unless
+ * rows*cols is a multiple of the block size.
+ * Replaces `quantized_storage_bytes` (models/architectures/qwen3/core.rs:891-909). */
+int32_t izb_quantized_storage_bytes(int32_t wfmt, int64_t rows, int64_t cols, size_t* out_bytes);
+
+/* Block dequantisation, bit-exact with GGML: Q8_0 `d*q`; Q4_K
+ * `(d*sc)*q - (dmin*m)` with separately rounded products.  `out_dtype` F32 is
+ * exact; BF16 rounds the fp32 value to nearest-even.
+ * Replaces `QTensor::dequantize` at models/shared/weights/gguf.rs:131 and
+ * qwen3/core.rs:853-858. */
+int32_t izb_dequantize(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void* raw,
+                       int64_t n_elems, int32_t out_dtype, void* out);
+
+/* One linear layer.  Replaces `impl Module for Qwen3Projection::forward`
+ * (qwen3/core.rs:791-832): Dense -> `Linear::forward` (:794), Quantized ->
+ * `QMatMul::forward` (:812) with the dtype casts around it folded away
+ * (activations stay bf16, accumulation is fp32). */
+typedef struct izb_linear_args {
+    int32_t wfmt;      /* izb_wfmt */
+    int32_t y_dtype;   /* izb_dtype of y */
+    const void* x;     /* [M, ldx] bf16 */
+    const void* w;     /* [N, K] in wfmt, rows contiguous */
+    const void* bias;  /* [N] bf16 or NULL */
+    void* y;           /* [M, ldy] */
+    int64_t M, N, K;
+    int64_t ldx, ldy;  /* row strides in elements */
+    void* workspace;   /* NULL unless izb_linear_workspace_bytes() > 0 */
+    size_t workspace_bytes;
+} izb_linear_args;
+
+size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K);
+int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args);
+
+/* Thin typed forms of izb_linear (y is bf16, contiguous strides). */
+int32_t izb_linear_bf16(izb_ctx* ctx, izb_stream stream, const void* x, const void* w,
+                        const void* bias, void* y, int64_t M, int64_t N, int64_t K);
+int32_t izb_linear_q8_0(izb_ctx* ctx, izb_stream stream, const void* x, const void* w,
+                        void* y, int64_t M, int64_t N, int64_t K);
+int32_t izb_linear_q4_k(izb_ctx* ctx, izb_stream stream, const void* x, const void* w,
+                        void* y, int64_t M, int64_t N, int64_t K);
+
+/* A group of independent small-M linear layers executed by ONE persistent
+ * launch that streams all weights back to back (the projections of a decode
+ * step that do not depend on one another, separate q/k/v or gate/up matrices,
+ * the experts one token selects).  All problems share wfmt and y_dtype and
+ * have M <= 64.  The plan is built on the host, copied by the caller to the
+ * device (plain bytes), and can be launched any number of times.
+ * No counterpart in the reference, which issues one Candle op per projection
+ * (qwen3/core.rs:1599,1624,1787,1796). */
+size_t izb_linear_group_plan_bytes(int32_t n_problems);
+int32_t izb_linear_group_plan(izb_ctx* ctx, const izb_linear_args* problems, int32_t n_problems,
+                              void* host_plan, size_t host_plan_bytes);
+int32_t izb_linear_group_launch(izb_ctx* ctx, izb_stream stream, const void* host_plan,
+                                const void* dev_plan);
+
+/* out = silu(gate) * up, fp32 math, bf16 storage; gate/up/out are [rows, cols]
+ * views with their own row strides so the two halves of a fused gate/up
+ * output can be passed in place.
+ * Replaces `try_fused_silu_mul_with_status` (kernels/mod.rs:94-108 ->
+ * kernels/cuda.rs:51-62) as called by `Qwen3Mlp::forward` (qwen3/core.rs:1788). */
+int32_t izb_silu_mul(izb_ctx* ctx, izb_stream stream, const void* gate, const void* up, void* out,
+                     int64_t rows, int64_t cols, int64_t ld_gate, int64_t ld_up, int64_t ld_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IZWI_B200_H */

@@ -1,0 +1,90 @@
+"""ctypes binding of the C ABI declared in include/izwi_b200.h.
+
+There is no fallback: if the shared library is missing the import of any
+compute wrapper raises, so a box without the CUDA build fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libizwi_b200.so"
+
+IZB_OK = 0
+IZB_ERR_BAD_ARG = -1
+IZB_ERR_UNSUPPORTED = -2
+IZB_ERR_LAUNCH = -3
+IZB_ERR_TIMEOUT = -4
+IZB_ERR_NO_DEVICE = -5
+
+IZB_BF16, IZB_F32 = 0, 1
+IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K = 0, 1, 2
+
+
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("wfmt", C.c_int32), ("y_dtype", C.c_int32),
+        ("x", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("y", C.c_void_p),
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
+        ("ldx", C.c_int64), ("ldy", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+_SIGNATURES = {
+    "izb_version": (C.c_int32, []),
+    "izb_status_string": (C.c_char_p, [C.c_int32]),
+    "izb_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(C.c_void_p)]),
+    "izb_ctx_destroy": (C.c_int32, [C.c_void_p]),
+    "izb_ctx_check": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "izb_ctx_launch_count": (C.c_int64, [C.c_void_p]),
+    "izb_quantized_storage_bytes": (C.c_int32, [C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_size_t)]),
+    "izb_dequantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
+    "izb_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
+    "izb_linear": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(LinearArgs)]),
+    "izb_linear_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_int64, C.c_int64, C.c_int64]),
+    "izb_linear_q8_0": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_int64, C.c_int64, C.c_int64]),
+    "izb_linear_q4_k": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_int64, C.c_int64, C.c_int64]),
+    "izb_linear_group_plan_bytes": (C.c_size_t, [C.c_int32]),
+    "izb_linear_group_plan": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_int32, C.c_void_p, C.c_size_t]),
+    "izb_linear_group_launch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
+}
+
+_lib = None
+
+
+def exported_symbols() -> list[str]:
+    return sorted(_SIGNATURES)
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m izwi_b200.build` "
+                "(there is no CPU or PyTorch fallback for these ops)")
+        handle = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+class IzbError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().izb_status_string(status).decode()
+        super().__init__(f"{where}: {msg} ({status})")
+
+
+def check(status: int, where: str) -> None:
+    if status != IZB_OK:
+        raise IzbError(status, where)

@@ -1,0 +1,322 @@
+// C ABI: context, block dequantisation, SwiGLU glue and the linear-layer entry points.
+#include <cstring>
+#include <new>
+
+#include "izb_common.cuh"
+#include "skinny.cuh"
+
+namespace izb {
+
+// ---------------------------------------------------------------------------
+// block dequantisation (bit-exact with GGML)
+// ---------------------------------------------------------------------------
+template <typename OutT>
+__device__ __forceinline__ void store_val(OutT* out, long long i, float v);
+template <>
+__device__ __forceinline__ void store_val<float>(float* out, long long i, float v) {
+    out[i] = v;
+}
+template <>
+__device__ __forceinline__ void store_val<__nv_bfloat16>(__nv_bfloat16* out, long long i, float v) {
+    out[i] = __float2bfloat16_rn(v);
+}
+
+// One thread per (block, 4 consecutive values): value = d * q.
+template <typename OutT>
+__global__ void dequant_q8_0_kernel(const uint8_t* __restrict__ raw, OutT* __restrict__ out, long long n_blocks) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_blocks * 8; i += stride) {
+        const long long b = i >> 3;
+        const int part = static_cast<int>(i & 7);
+        const uint8_t* blk = raw + b * 34;
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(blk[0] | (blk[1] << 8))));
+        const int8_t* q = reinterpret_cast<const int8_t*>(blk + 2 + part * 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) store_val(out, b * 32 + part * 4 + j, __fmul_rn(d, static_cast<float>(q[j])));
+    }
+}
+
+// One thread per (super-block, sub-block, 4-value run): value = (d*sc)*q - (dmin*m), each
+// product and the difference rounded on its own (no fused multiply-add), as GGML does.
+template <typename OutT>
+__global__ void dequant_q4_k_kernel(const uint8_t* __restrict__ raw, OutT* __restrict__ out, long long n_blocks) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_blocks * 64; i += stride) {
+        const long long b = i >> 6;
+        const int sub = static_cast<int>((i >> 3) & 7), part = static_cast<int>(i & 7);
+        const uint8_t* blk = raw + b * 144;
+        const uint16_t* hd = reinterpret_cast<const uint16_t*>(blk);
+        const float d = __half2float(__ushort_as_half(hd[0])), dmin = __half2float(__ushort_as_half(hd[1]));
+        const uint8_t* s = blk + 4;
+        int sc, mn;
+        if (sub < 4) {
+            sc = s[sub] & 63;
+            mn = s[sub + 4] & 63;
+        } else {
+            sc = (s[sub + 4] & 0x0F) | ((s[sub - 4] >> 6) << 4);
+            mn = (s[sub + 4] >> 4) | ((s[sub] >> 6) << 4);
+        }
+        const float dsc = __fmul_rn(d, static_cast<float>(sc));
+        const float dm = __fmul_rn(dmin, static_cast<float>(mn));
+        const uint8_t* qs = blk + 16 + 32 * (sub >> 1) + part * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int q = (sub & 1) ? (qs[j] >> 4) : (qs[j] & 0x0F);
+            store_val(out, b * 256 + sub * 32 + part * 4 + j, __fsub_rn(__fmul_rn(dsc, static_cast<float>(q)), dm));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// out = silu(gate) * up
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float silu_mul_f(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                                __nv_bfloat16* __restrict__ out, long long rows, long long cols, long long ldg,
+                                long long ldu, long long ldo, int vec) {
+    const long long cols_v = vec ? cols / 8 : cols;
+    const long long total = rows * cols_v;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long r = i / cols_v, c = i % cols_v;
+        if (vec) {
+            const uint4 gv = *reinterpret_cast<const uint4*>(gate + r * ldg + c * 8);
+            const uint4 uv = *reinterpret_cast<const uint4*>(up + r * ldu + c * 8);
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                ow[j] = pack_bf16x2(silu_mul_f(bf16_lo_to_f32(gw[j]), bf16_lo_to_f32(uw[j])),
+                                    silu_mul_f(bf16_hi_to_f32(gw[j]), bf16_hi_to_f32(uw[j])));
+            *reinterpret_cast<uint4*>(out + r * ldo + c * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        } else {
+            out[r * ldo + c] = __float2bfloat16_rn(
+                silu_mul_f(__bfloat162float(gate[r * ldg + c]), __bfloat162float(up[r * ldu + c])));
+        }
+    }
+}
+
+static int grid_for(const izb_ctx* ctx, long long work_items, int threads) {
+    const long long want = (work_items + threads - 1) / threads;
+    const long long cap = static_cast<long long>(ctx->sm_count) * 16;
+    return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace izb
+
+using namespace izb;
+
+extern "C" {
+
+int32_t izb_version(void) { return 100; }
+
+const char* izb_status_string(int32_t status) {
+    switch (status) {
+        case IZB_OK: return "ok";
+        case IZB_ERR_BAD_ARG: return "bad argument";
+        case IZB_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+        case IZB_ERR_LAUNCH: return "CUDA launch or copy failed";
+        case IZB_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case IZB_ERR_NO_DEVICE: return "no usable sm_100 device";
+        default: return "unknown status";
+    }
+}
+
+int32_t izb_ctx_create(int32_t device, izb_ctx** out) {
+    if (!out || device < 0) return IZB_ERR_BAD_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device >= count) {
+        (void)cudaGetLastError();
+        return IZB_ERR_NO_DEVICE;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return IZB_ERR_NO_DEVICE;
+    if (prop.major != 10) return IZB_ERR_NO_DEVICE;  // the kernels are sm_100a only
+    int prev = 0;
+    IZB_CUDA_TRY(cudaGetDevice(&prev));
+    IZB_CUDA_TRY(cudaSetDevice(device));
+    izb_ctx* ctx = new (std::nothrow) izb_ctx();
+    if (!ctx) return IZB_ERR_LAUNCH;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+    ctx->launches.store(0);
+    ctx->d_status = nullptr;
+    if (cudaMalloc(&ctx->d_status, IZB_STATUS_WORDS * sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->d_status, 0, IZB_STATUS_WORDS * sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        delete ctx;
+        (void)cudaSetDevice(prev);
+        return IZB_ERR_LAUNCH;
+    }
+    (void)cudaSetDevice(prev);
+    *out = ctx;
+    return IZB_OK;
+}
+
+int32_t izb_ctx_destroy(izb_ctx* ctx) {
+    if (!ctx) return IZB_ERR_BAD_ARG;
+    if (ctx->d_status) (void)cudaFree(ctx->d_status);
+    delete ctx;
+    return IZB_OK;
+}
+
+int32_t izb_ctx_check(izb_ctx* ctx, izb_stream stream) {
+    if (!ctx) return IZB_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host[IZB_STATUS_WORDS] = {0};
+    IZB_CUDA_TRY(cudaMemcpyAsync(host, ctx->d_status, sizeof(host), cudaMemcpyDeviceToHost, s));
+    IZB_CUDA_TRY(cudaStreamSynchronize(s));
+    if (host[0] != 0) {
+        IZB_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(host), s));
+        IZB_CUDA_TRY(cudaStreamSynchronize(s));
+        return IZB_ERR_TIMEOUT;
+    }
+    return IZB_OK;
+}
+
+int64_t izb_ctx_launch_count(const izb_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
+
+int32_t izb_quantized_storage_bytes(int32_t wfmt, int64_t rows, int64_t cols, size_t* out_bytes) {
+    if (!out_bytes || rows < 0 || cols < 0) return IZB_ERR_BAD_ARG;
+    int64_t block, type;
+    switch (wfmt) {
+        case IZB_W_BF16: block = 1; type = 2; break;
+        case IZB_W_Q8_0: block = 32; type = 34; break;
+        case IZB_W_Q4_K: block = 256; type = 144; break;
+        default: return IZB_ERR_BAD_ARG;
+    }
+    if (cols != 0 && rows > INT64_MAX / cols) return IZB_ERR_BAD_ARG;  // element count overflows
+    const int64_t elems = rows * cols;
+    if (elems % block != 0) return IZB_ERR_BAD_ARG;
+    if (elems / block > INT64_MAX / type) return IZB_ERR_BAD_ARG;
+    *out_bytes = static_cast<size_t>(elems / block * type);
+    return IZB_OK;
+}
+
+int32_t izb_dequantize(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void* raw, int64_t n_elems,
+                       int32_t out_dtype, void* out) {
+    if (!ctx || n_elems < 0) return IZB_ERR_BAD_ARG;
+    if (out_dtype != IZB_F32 && out_dtype != IZB_BF16) return IZB_ERR_BAD_ARG;
+    if (wfmt != IZB_W_Q8_0 && wfmt != IZB_W_Q4_K) return IZB_ERR_UNSUPPORTED;
+    const int64_t block = wfmt == IZB_W_Q8_0 ? 32 : 256;
+    if (n_elems % block != 0) return IZB_ERR_BAD_ARG;
+    if (n_elems == 0) return IZB_OK;
+    if (!raw || !out || !izb_aligned(raw, 2) || !izb_aligned(out, out_dtype == IZB_F32 ? 4 : 2)) return IZB_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long nb = n_elems / block;
+    const uint8_t* r = static_cast<const uint8_t*>(raw);
+    const int threads = 256;
+    if (wfmt == IZB_W_Q8_0) {
+        const int grid = grid_for(ctx, nb * 8, threads);
+        if (out_dtype == IZB_F32)
+            dequant_q8_0_kernel<float><<<grid, threads, 0, s>>>(r, static_cast<float*>(out), nb);
+        else
+            dequant_q8_0_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(r, static_cast<__nv_bfloat16*>(out), nb);
+    } else {
+        const int grid = grid_for(ctx, nb * 64, threads);
+        if (out_dtype == IZB_F32)
+            dequant_q4_k_kernel<float><<<grid, threads, 0, s>>>(r, static_cast<float*>(out), nb);
+        else
+            dequant_q4_k_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(r, static_cast<__nv_bfloat16*>(out), nb);
+    }
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_silu_mul(izb_ctx* ctx, izb_stream stream, const void* gate, const void* up, void* out, int64_t rows,
+                     int64_t cols, int64_t ld_gate, int64_t ld_up, int64_t ld_out) {
+    if (!ctx || rows < 0 || cols < 0) return IZB_ERR_BAD_ARG;
+    if (rows == 0 || cols == 0) return IZB_OK;
+    if (!gate || !up || !out) return IZB_ERR_BAD_ARG;
+    if (ld_gate < cols || ld_up < cols || ld_out < cols) return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(gate, 2) || !izb_aligned(up, 2) || !izb_aligned(out, 2)) return IZB_ERR_BAD_ARG;
+    const bool vec = cols % 8 == 0 && ld_gate % 8 == 0 && ld_up % 8 == 0 && ld_out % 8 == 0 && izb_aligned(gate, 16) &&
+                     izb_aligned(up, 16) && izb_aligned(out, 16);
+    const long long items = rows * (vec ? cols / 8 : cols);
+    const int threads = 256;
+    silu_mul_kernel<<<grid_for(ctx, items, threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out),
+        rows, cols, ld_gate, ld_up, ld_out, vec ? 1 : 0);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K) {
+    (void)wfmt; (void)M; (void)N; (void)K;
+    return 0;
+}
+
+int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args) {
+    if (!ctx || !args) return IZB_ERR_BAD_ARG;
+    if (args->M < 0 || args->N < 0 || args->K < 0) return IZB_ERR_BAD_ARG;
+    if (args->M == 0 || args->N == 0) return IZB_OK;
+    if (args->K == 0) return IZB_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Token rows are processed 64 at a time by the weight-streaming kernel.
+    const size_t ybytes = args->y_dtype == IZB_F32 ? 4 : 2;
+    for (int64_t m0 = 0; m0 < args->M; m0 += 64) {
+        izb_linear_args a = *args;
+        a.M = args->M - m0 < 64 ? args->M - m0 : 64;
+        a.x = static_cast<const uint8_t*>(args->x) + static_cast<size_t>(m0) * args->ldx * 2;
+        a.y = static_cast<uint8_t*>(args->y) + static_cast<size_t>(m0) * args->ldy * ybytes;
+        SkinnyPlanHeader hdr;
+        SkinnyProblem prob;
+        int rc = skinny_plan_build(ctx, &a, 1, &hdr, &prob);
+        if (rc != IZB_OK) return rc;
+        rc = skinny_launch(ctx, s, hdr, nullptr, &prob);
+        if (rc != IZB_OK) return rc;
+    }
+    return IZB_OK;
+}
+
+static int32_t linear_typed(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void* x, const void* w,
+                            const void* bias, void* y, int64_t M, int64_t N, int64_t K) {
+    izb_linear_args a;
+    std::memset(&a, 0, sizeof(a));
+    a.wfmt = wfmt;
+    a.y_dtype = IZB_BF16;
+    a.x = x; a.w = w; a.bias = bias; a.y = y;
+    a.M = M; a.N = N; a.K = K; a.ldx = K; a.ldy = N;
+    return izb_linear(ctx, stream, &a);
+}
+
+int32_t izb_linear_bf16(izb_ctx* ctx, izb_stream stream, const void* x, const void* w, const void* bias, void* y,
+                        int64_t M, int64_t N, int64_t K) {
+    return linear_typed(ctx, stream, IZB_W_BF16, x, w, bias, y, M, N, K);
+}
+int32_t izb_linear_q8_0(izb_ctx* ctx, izb_stream stream, const void* x, const void* w, void* y, int64_t M, int64_t N,
+                        int64_t K) {
+    return linear_typed(ctx, stream, IZB_W_Q8_0, x, w, nullptr, y, M, N, K);
+}
+int32_t izb_linear_q4_k(izb_ctx* ctx, izb_stream stream, const void* x, const void* w, void* y, int64_t M, int64_t N,
+                        int64_t K) {
+    return linear_typed(ctx, stream, IZB_W_Q4_K, x, w, nullptr, y, M, N, K);
+}
+
+size_t izb_linear_group_plan_bytes(int32_t n_problems) {
+    if (n_problems <= 0) return 0;
+    return sizeof(SkinnyPlanHeader) + static_cast<size_t>(n_problems) * sizeof(SkinnyProblem);
+}
+
+int32_t izb_linear_group_plan(izb_ctx* ctx, const izb_linear_args* problems, int32_t n_problems, void* host_plan,
+                              size_t host_plan_bytes) {
+    if (!ctx || !problems || !host_plan || n_problems <= 0) return IZB_ERR_BAD_ARG;
+    if (host_plan_bytes < izb_linear_group_plan_bytes(n_problems) || !izb_aligned(host_plan, 16)) return IZB_ERR_BAD_ARG;
+    auto* hdr = static_cast<SkinnyPlanHeader*>(host_plan);
+    auto* probs = reinterpret_cast<SkinnyProblem*>(static_cast<uint8_t*>(host_plan) + sizeof(SkinnyPlanHeader));
+    return skinny_plan_build(ctx, problems, n_problems, hdr, probs);
+}
+
+int32_t izb_linear_group_launch(izb_ctx* ctx, izb_stream stream, const void* host_plan, const void* dev_plan) {
+    if (!ctx || !host_plan || !dev_plan || !izb_aligned(dev_plan, 16)) return IZB_ERR_BAD_ARG;
+    const auto* hdr = static_cast<const SkinnyPlanHeader*>(host_plan);
+    const auto* dev = reinterpret_cast<const SkinnyProblem*>(static_cast<const uint8_t*>(dev_plan) + sizeof(SkinnyPlanHeader));
+    return skinny_launch(ctx, static_cast<cudaStream_t>(stream), *hdr, dev, nullptr);
+}
+
+}  // extern "C"

@@ -1,0 +1,664 @@
+// Small-M linear layers: the persistent weight-streaming kernel and its host planner.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "skinny.cuh"
+
+namespace izb {
+
+// ---------------------------------------------------------------------------
+// per-format constants
+// ---------------------------------------------------------------------------
+template <int FMT>
+struct Fmt;
+template <>
+struct Fmt<IZB_W_BF16> {
+    static constexpr int kUnit = 64;          // k values a consumer warp handles per inner step
+    static constexpr int kAlign = 64;         // K must be a multiple of this
+    static constexpr int kXStrideMod = 64;    // x row stride == this (mod 128) -> conflict-free LDS.128
+    __host__ __device__ static constexpr int bytes(int k) { return k * 2; }
+};
+template <>
+struct Fmt<IZB_W_Q8_0> {
+    static constexpr int kUnit = 64;   // one pair of 34-byte blocks = 17 aligned words
+    static constexpr int kAlign = 256; // 8 blocks = 272 bytes: smallest 16-byte aligned run
+    static constexpr int kXStrideMod = 32;  // LDS.64 activation loads
+    __host__ __device__ static constexpr int bytes(int k) { return k / 32 * 34; }
+};
+template <>
+struct Fmt<IZB_W_Q4_K> {
+    static constexpr int kUnit = 256;  // one 144-byte super-block
+    static constexpr int kAlign = 256;
+    static constexpr int kXStrideMod = 64;
+    __host__ __device__ static constexpr int bytes(int k) { return k / 256 * 144; }
+};
+
+__device__ __forceinline__ float half_bits_to_f32(uint32_t h) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
+}
+
+// Four int8 in a word -> two bf16x2 registers holding the exact integers.
+// byte ^ 0x80 is q+128 as an unsigned byte; placed in the low mantissa bits of
+// 2^23 it reads as 8388608 + q + 128, and one subtraction leaves q.
+__device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t& p01, uint32_t& p23) {
+    const uint32_t u = w ^ 0x80808080u;
+    const float f0 = __uint_as_float(prmt(u, 0x4B000000u, 0x7440)) - 8388736.0f;
+    const float f1 = __uint_as_float(prmt(u, 0x4B000000u, 0x7441)) - 8388736.0f;
+    const float f2 = __uint_as_float(prmt(u, 0x4B000000u, 0x7442)) - 8388736.0f;
+    const float f3 = __uint_as_float(prmt(u, 0x4B000000u, 0x7443)) - 8388736.0f;
+    p01 = pack_bf16x2(f0, f1);
+    p23 = pack_bf16x2(f2, f3);
+}
+
+__device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t bcast_bf16x2(float v) {
+    return pack_bf16x2(v, v);
+}
+
+// ---------------------------------------------------------------------------
+// consumer inner loops: one k-chunk of one stage
+//   wbase/xbase: shared-memory byte addresses of the stage's weight / activation regions
+//   rowbase: first row (inside the tile) of this warp; g = lane/4, t = lane%4
+// ---------------------------------------------------------------------------
+template <int NT, int RT, int KS>
+__device__ __forceinline__ void chunk_bf16(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase, int ws, int xs,
+                                           int kcur, int rowbase, int ks, int g, int t) {
+    const int units = kcur >> 6;
+    for (int u = ks; u < units; u += KS) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t koff = static_cast<uint32_t>((u * 64 + h * 32 + t * 8) * 2);
+            uint4 wa[RT], wb[RT];
+#pragma unroll
+            for (int rt = 0; rt < RT; ++rt) {
+                const uint32_t ra = wbase + static_cast<uint32_t>((rowbase + rt * 16 + g) * ws) + koff;
+                wa[rt] = lds128(ra);
+                wb[rt] = lds128(ra + 8 * ws);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint4 xb = lds128(xbase + static_cast<uint32_t>((nt * 8 + g) * xs) + koff);
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) {
+                    mma_bf16_16816(acc[rt][nt], wa[rt].x, wb[rt].x, wa[rt].y, wb[rt].y, xb.x, xb.y);
+                    mma_bf16_16816(acc[rt][nt], wa[rt].z, wb[rt].z, wa[rt].w, wb[rt].w, xb.z, xb.w);
+                }
+            }
+        }
+    }
+}
+
+// Q8_0.  A pair of blocks is 68 bytes = 17 aligned words:
+//   word 0 = [d0 | q0[0..1]], words 1..7 = q0[2..29], word 8 = [q0[30..31] | d1], words 9..16 = q1[0..31].
+// Block 0's codes sit half a word off, so each logical word is funnelled out of two neighbours.
+// The integer codes go through the tensor core exactly; the block scale is applied in fp32.
+template <int NT, int RT, int KS>
+__device__ __forceinline__ void chunk_q8_0(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase, int ws, int xs,
+                                           int kcur, int rowbase, int ks, int g, int t) {
+    const int units = kcur >> 6;
+    for (int u = ks; u < units; u += KS) {
+        uint32_t a[RT][4][4];  // [tile][step][a0..a3]
+        float d[RT][2][2];     // [tile][block][row a / row b]
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t wr =
+                    wbase + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * ws) + static_cast<uint32_t>(u * 68);
+                const uint32_t w0 = lds32(wr), w8 = lds32(wr + 32);
+                const uint32_t l0 = lds32(wr + 4 * t), l1 = lds32(wr + 4 * t + 4);
+                const uint32_t h0 = lds32(wr + 16 + 4 * t), h1 = lds32(wr + 20 + 4 * t);
+                const uint32_t q2 = lds32(wr + 36 + 4 * t), q3 = lds32(wr + 52 + 4 * t);
+                const uint32_t q0 = prmt(l0, l1, 0x5432), q1 = prmt(h0, h1, 0x5432);
+                d[rt][0][half] = half_bits_to_f32(w0);
+                d[rt][1][half] = half_bits_to_f32(w8 >> 16);
+                s8x4_to_bf16x4(q0, a[rt][0][half], a[rt][0][half + 2]);
+                s8x4_to_bf16x4(q1, a[rt][1][half], a[rt][1][half + 2]);
+                s8x4_to_bf16x4(q2, a[rt][2][half], a[rt][2][half + 2]);
+                s8x4_to_bf16x4(q3, a[rt][3][half], a[rt][3][half + 2]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t xr = xbase + static_cast<uint32_t>((nt * 8 + g) * xs) + static_cast<uint32_t>((u * 64 + 4 * t) * 2);
+            uint2 xv[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) xv[s] = lds64(xr + s * 32);
+#pragma unroll
+            for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_bf16_16816(tmp, a[rt][2 * b][0], a[rt][2 * b][1], a[rt][2 * b][2], a[rt][2 * b][3], xv[2 * b].x,
+                                   xv[2 * b].y);
+                    mma_bf16_16816(tmp, a[rt][2 * b + 1][0], a[rt][2 * b + 1][1], a[rt][2 * b + 1][2],
+                                   a[rt][2 * b + 1][3], xv[2 * b + 1].x, xv[2 * b + 1].y);
+                    acc[rt][nt][0] = fmaf(d[rt][b][0], tmp[0], acc[rt][nt][0]);
+                    acc[rt][nt][1] = fmaf(d[rt][b][0], tmp[1], acc[rt][nt][1]);
+                    acc[rt][nt][2] = fmaf(d[rt][b][1], tmp[2], acc[rt][nt][2]);
+                    acc[rt][nt][3] = fmaf(d[rt][b][1], tmp[3], acc[rt][nt][3]);
+                }
+            }
+        }
+    }
+}
+
+// Q4_K.  Super-block = [d, dmin (fp16) | 12 scale bytes | 4 groups of 32 code bytes]; group j holds
+// sub-block 2j in the low nibbles and 2j+1 in the high nibbles.  A nibble n is lifted to the bf16
+// value 16+n with one shift and one logic op (0x4180 | n<<3), then one bf16x2 fma with the
+// sub-block's (d*sc) and -(16*d*sc + dmin*m) turns it into the dequantised weight.  Lane t of a
+// quad decodes the scales of sub-blocks 2t and 2t+1 and hands them round by shuffle.
+template <int NT, int RT, int KS>
+__device__ __forceinline__ void chunk_q4_k(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase, int ws, int xs,
+                                           int kcur, int rowbase, int ks, int g, int t, int lane) {
+    const int nsb = kcur >> 8;
+    for (int sb = ks; sb < nsb; sb += KS) {
+        uint32_t my_s[RT][2][2], my_c[RT][2][2];  // [tile][row a/b][own sub-block 0/1]
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint4 hd = lds128(wbase + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * ws) +
+                                        static_cast<uint32_t>(sb * 144));
+                const float dd = half_bits_to_f32(hd.x), dmin = half_bits_to_f32(hd.x >> 16);
+                const uint32_t sc_lo = hd.y & 0x3F3F3F3Fu, mn_lo = hd.z & 0x3F3F3F3Fu;
+                const uint32_t sc_hi = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+                const uint32_t mn_hi = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+                const uint32_t scw = (t < 2 ? sc_lo : sc_hi) >> ((t & 1) * 16);
+                const uint32_t mnw = (t < 2 ? mn_lo : mn_hi) >> ((t & 1) * 16);
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    const float dsc = dd * static_cast<float>((scw >> (8 * s)) & 0xFFu);
+                    const float dm = dmin * static_cast<float>((mnw >> (8 * s)) & 0xFFu);
+                    const float dsc_r = __bfloat162float(__float2bfloat16_rn(dsc));
+                    my_s[rt][half][s] = bcast_bf16x2(dsc);
+                    my_c[rt][half][s] = bcast_bf16x2(-(16.0f * dsc_r + dm));
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int src = (lane & ~3) | j;
+            uint32_t a[RT][4][4];  // [tile][step = sub*2 + word][a0..a3]
+#pragma unroll
+            for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t s0 = __shfl_sync(0xFFFFFFFFu, my_s[rt][half][0], src);
+                    const uint32_t s1 = __shfl_sync(0xFFFFFFFFu, my_s[rt][half][1], src);
+                    const uint32_t c0 = __shfl_sync(0xFFFFFFFFu, my_c[rt][half][0], src);
+                    const uint32_t c1 = __shfl_sync(0xFFFFFFFFu, my_c[rt][half][1], src);
+                    const uint2 wv = lds64(wbase + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * ws) +
+                                           static_cast<uint32_t>(sb * 144 + 16 + j * 32 + t * 8));
+#pragma unroll
+                    for (int wd = 0; wd < 2; ++wd) {
+                        const uint32_t w = wd ? wv.y : wv.x;
+                        // low nibbles (sub-block 2j): bytes 0,2 then bytes 1,3
+                        a[rt][wd][half] = hfma2_bf16(lop3<0xEA>(w << 3, 0x00780078u, 0x41804180u), s0, c0);
+                        a[rt][wd][half + 2] = hfma2_bf16(lop3<0xEA>(w >> 5, 0x00780078u, 0x41804180u), s0, c0);
+                        // high nibbles (sub-block 2j+1)
+                        a[rt][2 + wd][half] = hfma2_bf16(lop3<0xEA>(w >> 1, 0x00780078u, 0x41804180u), s1, c1);
+                        a[rt][2 + wd][half + 2] = hfma2_bf16(lop3<0xEA>(w >> 9, 0x00780078u, 0x41804180u), s1, c1);
+                    }
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t xr = xbase + static_cast<uint32_t>((nt * 8 + g) * xs) +
+                                    static_cast<uint32_t>((sb * 256 + j * 64 + t * 8) * 2);
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    const uint4 xq = lds128(xr + sub * 64);
+                    // word 0 covers x[0..3] -> operand pairs (x0,x2),(x1,x3); word 1 covers x[4..7]
+                    const uint32_t b00 = prmt(xq.x, xq.y, 0x5410), b01 = prmt(xq.x, xq.y, 0x7632);
+                    const uint32_t b10 = prmt(xq.z, xq.w, 0x5410), b11 = prmt(xq.z, xq.w, 0x7632);
+#pragma unroll
+                    for (int rt = 0; rt < RT; ++rt) {
+                        mma_bf16_16816(acc[rt][nt], a[rt][sub * 2][0], a[rt][sub * 2][1], a[rt][sub * 2][2],
+                                       a[rt][sub * 2][3], b00, b01);
+                        mma_bf16_16816(acc[rt][nt], a[rt][sub * 2 + 1][0], a[rt][sub * 2 + 1][1], a[rt][sub * 2 + 1][2],
+                                       a[rt][sub * 2 + 1][3], b10, b11);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+struct SkinnyShared {
+    unsigned long long full[SK_MAX_STAGES];
+    unsigned long long empty[SK_MAX_STAGES];
+    int abort_flag;
+};
+
+__device__ __forceinline__ void store_out(void* y, int y_dtype, long long idx, float v) {
+    if (y_dtype == IZB_F32) {
+        static_cast<float*>(y)[idx] = v;
+    } else {
+        static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+    }
+}
+
+template <int FMT, int NT, int RT, int KS>
+__global__ void __launch_bounds__(SK_THREADS)
+    skinny_kernel(const SkinnyProblem* __restrict__ probs, const __grid_constant__ SkinnyProblem single, int n_probs,
+                  int total_tiles, int n_stages, int stage_bytes, int red_bytes, int y_dtype, int* status) {
+    constexpr int RG = SK_CONSUMER_WARPS / KS;
+    constexpr int TILE_ROWS = RG * RT * 16;
+    constexpr int ACC = RT * NT * 4;
+
+    extern __shared__ __align__(128) uint8_t dyn_smem[];
+    __shared__ SkinnyShared sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const SkinnyProblem* plist = probs ? probs : &single;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < n_stages; ++s) {
+            mbar_init(smem_u32(&sh.full[s]), 1);
+            mbar_init(smem_u32(&sh.empty[s]), SK_CONSUMER_WARPS);
+        }
+        sh.abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    volatile int* abort_flag = &sh.abort_flag;
+    const uint32_t stage0 = smem_u32(dyn_smem) + static_cast<uint32_t>(red_bytes);
+
+    if (warp == SK_CONSUMER_WARPS) {
+        // ---------------- producer ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        long long issued = 0;
+        bool ok = true;
+        int p = 0;
+        SkinnyProblem P = plist[0];
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            bool moved = false;
+            while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) {
+                ++p;
+                moved = true;
+            }
+            if (moved) P = plist[p];
+            const int row0 = (tile - P.tile_start) * TILE_ROWS;
+            const int rows = min(TILE_ROWS, P.N - row0);
+            for (int c = 0; c < P.n_chunks; ++c) {
+                const int kcur = min(P.kc, P.K - c * P.kc);
+                const uint32_t wbytes = static_cast<uint32_t>(Fmt<FMT>::bytes(kcur));
+                const uint32_t xbytes = static_cast<uint32_t>(kcur * 2);
+                const uint32_t fbar = smem_u32(&sh.full[stage]);
+                if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (lane == 0) mbar_expect_tx(fbar, static_cast<uint32_t>(rows) * wbytes + static_cast<uint32_t>(P.M) * xbytes);
+                __syncwarp();
+                const uint32_t sbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
+                const uint8_t* wsrc = P.w + static_cast<long long>(row0) * P.row_bytes + static_cast<long long>(c) * P.chunk_bytes;
+                for (int r = lane; r < rows; r += 32)
+                    bulk_g2s(sbase + static_cast<uint32_t>(r * P.w_stride), wsrc + static_cast<long long>(r) * P.row_bytes, wbytes,
+                             fbar);
+                const __nv_bfloat16* xsrc = P.x + static_cast<long long>(c) * P.kc;
+                for (int m = lane; m < P.M; m += 32)
+                    bulk_g2s(sbase + static_cast<uint32_t>(P.x_off + m * P.x_stride), xsrc + static_cast<long long>(m) * P.ldx,
+                             xbytes, fbar);
+                ++issued;
+                if (++stage == n_stages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        if (ok) {
+            // Drain: every stage handed out has been read back by all consumers.
+            for (int s = 0; s < n_stages && ok; ++s) {
+                if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) ok = false;
+                if (++stage == n_stages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        if (!ok) {
+            // A wait gave up: let the copies still in flight land before the CTA's shared memory goes away.
+            const long long first = issued > n_stages ? issued - n_stages : 0;
+            for (long long f = first; f < issued; ++f) {
+                const uint32_t bar = smem_u32(&sh.full[f % n_stages]);
+                const uint32_t par = static_cast<uint32_t>((f / n_stages) & 1);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar, par)) {
+                    if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) break;
+                }
+            }
+            if (lane == 0) atomicExch(status, 1);
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int g = lane >> 2, t = lane & 3;
+    const int rg = warp / KS, ks = warp % KS;
+    const int rowbase = rg * RT * 16;
+    float* red = reinterpret_cast<float*>(dyn_smem);
+
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int p = 0;
+    int tile_parity = 0;
+    SkinnyProblem P = plist[0];
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_parity ^= 1) {
+        bool moved = false;
+        while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) {
+            ++p;
+            moved = true;
+        }
+        if (moved) P = plist[p];
+        const int row0 = (tile - P.tile_start) * TILE_ROWS;
+
+        float acc[RT][NT][4];
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[rt][nt][i] = 0.f;
+
+        for (int c = 0; c < P.n_chunks; ++c) {
+            const int kcur = min(P.kc, P.K - c * P.kc);
+            if (ok && !mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) ok = false;
+            if (ok) {
+                const uint32_t wbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
+                const uint32_t xbase = wbase + static_cast<uint32_t>(P.x_off);
+                if constexpr (FMT == IZB_W_BF16)
+                    chunk_bf16<NT, RT, KS>(acc, wbase, xbase, P.w_stride, P.x_stride, kcur, rowbase, ks, g, t);
+                else if constexpr (FMT == IZB_W_Q8_0)
+                    chunk_q8_0<NT, RT, KS>(acc, wbase, xbase, P.w_stride, P.x_stride, kcur, rowbase, ks, g, t);
+                else
+                    chunk_q4_k<NT, RT, KS>(acc, wbase, xbase, P.w_stride, P.x_stride, kcur, rowbase, ks, g, t, lane);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.empty[stage]));
+            if (++stage == n_stages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+
+        if constexpr (KS > 1) {
+            // k-slices 1..KS-1 park their partial sums in shared memory; slice 0 adds them up.
+            // Two buffers alternate by tile so one barrier per tile is enough.
+            float* buf = red + tile_parity * ((KS - 1) * RG * ACC * 32);
+            if (ks > 0) {
+                float* dst = buf + ((ks - 1) * RG + rg) * ACC * 32 + lane;
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[((rt * NT + nt) * 4 + i) * 32] = acc[rt][nt][i];
+            }
+            named_bar_sync(1, SK_CONSUMER_WARPS * 32);
+            if (ks == 0) {
+#pragma unroll
+                for (int s = 1; s < KS; ++s) {
+                    const float* src = buf + ((s - 1) * RG + rg) * ACC * 32 + lane;
+#pragma unroll
+                    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[rt][nt][i] += src[((rt * NT + nt) * 4 + i) * 32];
+                }
+            }
+        }
+
+        if (ks == 0 && ok) {
+#pragma unroll
+            for (int rt = 0; rt < RT; ++rt) {
+                const int ra = row0 + rowbase + rt * 16 + g;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int row = ra + half * 8;
+                    if (row < P.N) {
+                        const float b = P.bias ? __bfloat162float(P.bias[row]) : 0.f;
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                const int tok = nt * 8 + 2 * t + i;
+                                if (tok < P.M)
+                                    store_out(P.y, y_dtype, static_cast<long long>(tok) * P.ldy + row,
+                                              acc[rt][nt][half * 2 + i] + b);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0) atomicExch(status, 1);
+}
+
+// ---------------------------------------------------------------------------
+// host: planning and launch
+// ---------------------------------------------------------------------------
+namespace {
+
+int env_int(const char* name, int dflt) {
+    const char* v = std::getenv(name);
+    if (!v || !*v) return dflt;
+    return std::atoi(v);
+}
+
+int fmt_bytes(int fmt, int k) {
+    switch (fmt) {
+        case IZB_W_BF16: return Fmt<IZB_W_BF16>::bytes(k);
+        case IZB_W_Q8_0: return Fmt<IZB_W_Q8_0>::bytes(k);
+        default: return Fmt<IZB_W_Q4_K>::bytes(k);
+    }
+}
+int fmt_unit(int fmt) { return fmt == IZB_W_Q4_K ? 256 : 64; }
+int fmt_kalign(int fmt) { return fmt == IZB_W_BF16 ? 64 : 256; }
+int fmt_xmod(int fmt) { return fmt == IZB_W_Q8_0 ? 32 : 64; }
+
+// Padded shared-memory row stride that keeps the consumers' loads free of bank conflicts.
+int w_stride_for(int fmt, int chunk_bytes) {
+    switch (fmt) {
+        case IZB_W_BF16: return chunk_bytes + ((64 - chunk_bytes % 128) + 128) % 128;  // == 64 (mod 128)
+        case IZB_W_Q8_0: return chunk_bytes + ((16 - chunk_bytes % 32) + 32) % 32;     // == 16 (mod 32)
+        default: return chunk_bytes + ((32 - chunk_bytes % 128) + 128) % 128;          // == 32 (mod 128)
+    }
+}
+int x_stride_for(int fmt, int kc) {
+    const int raw = kc * 2, mod = fmt_xmod(fmt);
+    return raw + ((mod - raw % 128) + 128) % 128;
+}
+
+template <int FMT, int NT, int RT, int KS>
+int launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+               const SkinnyProblem& single) {
+    auto kern = skinny_kernel<FMT, NT, RT, KS>;
+    // The opt-in shared-memory ceiling is per function and per device; raise it only when it grows.
+    static std::atomic<int> smem_set[16];
+    const int dev_slot = ctx->device & 15;
+    if (smem_set[dev_slot].load(std::memory_order_relaxed) < h.smem_bytes) {
+        IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));
+        smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);
+    }
+    kern<<<h.grid, SK_THREADS, h.smem_bytes, stream>>>(dev, single, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes,
+                                                       h.red_bytes, h.y_dtype, ctx->d_status);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+template <int FMT, int NT>
+int launch_cfg(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+               const SkinnyProblem& single) {
+    if (h.rt == 2 && h.ks == 1) {
+        if constexpr (NT <= 2) return launch_one<FMT, NT, 2, 1>(ctx, stream, h, dev, single);
+        return IZB_ERR_UNSUPPORTED;
+    }
+    if (h.rt != 1) return IZB_ERR_UNSUPPORTED;
+    switch (h.ks) {
+        case 1: return launch_one<FMT, NT, 1, 1>(ctx, stream, h, dev, single);
+        case 2: return launch_one<FMT, NT, 1, 2>(ctx, stream, h, dev, single);
+        case 4: return launch_one<FMT, NT, 1, 4>(ctx, stream, h, dev, single);
+        default: return IZB_ERR_UNSUPPORTED;
+    }
+}
+
+template <int FMT>
+int launch_fmt(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+               const SkinnyProblem& single) {
+    switch (h.nt) {
+        case 1: return launch_cfg<FMT, 1>(ctx, stream, h, dev, single);
+        case 2: return launch_cfg<FMT, 2>(ctx, stream, h, dev, single);
+        case 4: return launch_cfg<FMT, 4>(ctx, stream, h, dev, single);
+        case 8: return launch_cfg<FMT, 8>(ctx, stream, h, dev, single);
+        default: return IZB_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace
+
+int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, SkinnyPlanHeader* hdr,
+                      SkinnyProblem* out) {
+    if (!ctx || !probs || !hdr || !out || n <= 0) return IZB_ERR_BAD_ARG;
+    const int fmt = probs[0].wfmt, y_dtype = probs[0].y_dtype;
+    if (fmt != IZB_W_BF16 && fmt != IZB_W_Q8_0 && fmt != IZB_W_Q4_K) return IZB_ERR_BAD_ARG;
+    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
+
+    int64_t max_m = 0, total_rows = 0;
+    for (int i = 0; i < n; ++i) {
+        const izb_linear_args& a = probs[i];
+        if (a.wfmt != fmt || a.y_dtype != y_dtype) return IZB_ERR_BAD_ARG;
+        if (!a.x || !a.w || !a.y) return IZB_ERR_BAD_ARG;
+        if (a.M <= 0 || a.N <= 0 || a.K <= 0) return IZB_ERR_BAD_ARG;
+        if (a.M > 64) return IZB_ERR_UNSUPPORTED;
+        if (a.N > (1 << 24) || a.K > (1 << 20)) return IZB_ERR_UNSUPPORTED;
+        if (a.K % fmt_kalign(fmt) != 0) return IZB_ERR_UNSUPPORTED;
+        if (a.ldx < a.K || a.ldy < a.N || a.ldx % 8 != 0) return IZB_ERR_BAD_ARG;
+        if (!izb_aligned(a.x, 16) || !izb_aligned(a.w, 16)) return IZB_ERR_BAD_ARG;
+        if (!izb_aligned(a.y, y_dtype == IZB_F32 ? 4 : 2)) return IZB_ERR_BAD_ARG;
+        if (a.bias && !izb_aligned(a.bias, 2)) return IZB_ERR_BAD_ARG;
+        max_m = std::max<int64_t>(max_m, a.M);
+        total_rows += a.N;
+    }
+    const int nt = max_m <= 8 ? 1 : max_m <= 16 ? 2 : max_m <= 32 ? 4 : 8;
+    const int mp = nt * 8;
+
+    const int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", 2));
+    const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
+    const int max_grid = ctx->sm_count * ctas_per_sm;
+
+    // Largest row tile that still leaves every CTA a few tiles to balance with.
+    struct Cand { int rt, ks, rows; };
+    const Cand cands[4] = {{2, 1, 128}, {1, 1, 64}, {1, 2, 32}, {1, 4, 16}};
+    int pick = 3;
+    const int forced_rows = env_int("IZB_SKINNY_TILE_ROWS", 0);
+    for (int c = 0; c < 4; ++c) {
+        if (cands[c].rt == 2 && nt > 2) continue;
+        if (forced_rows) {
+            if (cands[c].rows == forced_rows) { pick = c; break; }
+            continue;
+        }
+        int64_t tiles = 0;
+        for (int i = 0; i < n; ++i) tiles += (probs[i].N + cands[c].rows - 1) / cands[c].rows;
+        if (tiles >= 4LL * max_grid) { pick = c; break; }
+    }
+    const int rt = cands[pick].rt, ks = cands[pick].ks, tile_rows = cands[pick].rows;
+    const int rg = SK_CONSUMER_WARPS / ks;
+
+    int stage_bytes = 0, tile_cursor = 0;
+    const int unit = fmt_kalign(fmt);
+    for (int i = 0; i < n; ++i) {
+        const izb_linear_args& a = probs[i];
+        SkinnyProblem& q = out[i];
+        std::memset(&q, 0, sizeof(q));
+        const int K = static_cast<int>(a.K);
+        // Largest k-chunk (multiple of the format's aligned unit) whose stage fits the target;
+        // at least enough for every k-slice of the CTA to have one inner unit.
+        int kc = unit;
+        const int kmin = std::min(K, std::max(unit, fmt_unit(fmt) * ks));
+        for (int cand = unit; cand <= K; cand += unit) {
+            const int sz = tile_rows * w_stride_for(fmt, fmt_bytes(fmt, cand)) + mp * x_stride_for(fmt, cand);
+            if (cand <= kmin || sz <= stage_target) kc = cand; else break;
+        }
+        q.w = static_cast<const uint8_t*>(a.w);
+        q.x = static_cast<const __nv_bfloat16*>(a.x);
+        q.y = a.y;
+        q.bias = static_cast<const __nv_bfloat16*>(a.bias);
+        q.row_bytes = fmt_bytes(fmt, K);
+        q.N = static_cast<int>(a.N);
+        q.K = K;
+        q.M = static_cast<int>(a.M);
+        q.ldx = static_cast<int>(a.ldx);
+        q.ldy = static_cast<int>(a.ldy);
+        q.tile_start = tile_cursor;
+        q.kc = kc;
+        q.n_chunks = (K + kc - 1) / kc;
+        q.chunk_bytes = fmt_bytes(fmt, kc);
+        q.w_stride = w_stride_for(fmt, q.chunk_bytes);
+        q.x_stride = x_stride_for(fmt, kc);
+        q.x_off = (tile_rows * q.w_stride + 127) / 128 * 128;
+        stage_bytes = std::max(stage_bytes, (q.x_off + mp * q.x_stride + 127) / 128 * 128);
+        tile_cursor += (q.N + tile_rows - 1) / tile_rows;
+    }
+
+    const int red_bytes = ks > 1 ? 2 * (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
+    const int budget = ctx->max_smem_optin / ctas_per_sm - 1024 - static_cast<int>(sizeof(SkinnyShared));
+    int n_stages = (budget - red_bytes) / stage_bytes;
+    const int forced_stages = env_int("IZB_SKINNY_STAGES", 0);
+    if (forced_stages) n_stages = forced_stages;
+    n_stages = std::min(n_stages, SK_MAX_STAGES);
+    if (n_stages < 2) {
+        // A single stage pair must still fit one CTA per SM.
+        n_stages = 2;
+        if (red_bytes + 2 * stage_bytes > ctx->max_smem_optin - 1024) return IZB_ERR_UNSUPPORTED;
+    }
+
+    std::memset(hdr, 0, sizeof(*hdr));
+    hdr->magic = SK_PLAN_MAGIC;
+    hdr->fmt = fmt;
+    hdr->nt = nt;
+    hdr->rt = rt;
+    hdr->ks = ks;
+    hdr->n_probs = n;
+    hdr->total_tiles = tile_cursor;
+    hdr->n_stages = n_stages;
+    hdr->stage_bytes = stage_bytes;
+    hdr->red_bytes = red_bytes;
+    hdr->smem_bytes = red_bytes + n_stages * stage_bytes;
+    hdr->grid = std::min(tile_cursor, max_grid);
+    hdr->y_dtype = y_dtype;
+    return IZB_OK;
+}
+
+int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev_probs,
+                  const SkinnyProblem* single) {
+    if (h.magic != SK_PLAN_MAGIC) return IZB_ERR_BAD_ARG;
+    SkinnyProblem dummy;
+    std::memset(&dummy, 0, sizeof(dummy));
+    const SkinnyProblem& s = single ? *single : dummy;
+    if (!dev_probs && !single) return IZB_ERR_BAD_ARG;
+    switch (h.fmt) {
+        case IZB_W_BF16: return launch_fmt<IZB_W_BF16>(ctx, stream, h, dev_probs, s);
+        case IZB_W_Q8_0: return launch_fmt<IZB_W_Q8_0>(ctx, stream, h, dev_probs, s);
+        case IZB_W_Q4_K: return launch_fmt<IZB_W_Q4_K>(ctx, stream, h, dev_probs, s);
+        default: return IZB_ERR_BAD_ARG;
+    }
+}
+
+}  // namespace izb

@@ -1,0 +1,133 @@
+"""Torch-tensor plumbing over the C ABI: tensors supply device pointers and the
+current stream, nothing else.  Every function launches the CUDA kernels of
+libizwi_b200.so; none has a PyTorch or CPU fallback."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+
+WFMT = {"bf16": L.IZB_W_BF16, "q8_0": L.IZB_W_Q8_0, "q4_k": L.IZB_W_Q4_K}
+BLOCK_SIZE = {"bf16": 1, "q8_0": 32, "q4_k": 256}
+TYPE_SIZE = {"bf16": 2, "q8_0": 34, "q4_k": 144}
+
+
+class Context:
+    """One izb_ctx per device (see include/izwi_b200.h)."""
+
+    _by_device: dict[int, "Context"] = {}
+
+    def __init__(self, device: int = 0):
+        handle = C.c_void_p()
+        L.check(L.lib().izb_ctx_create(device, C.byref(handle)), "izb_ctx_create")
+        self.handle = handle
+        self.device = device
+
+    @classmethod
+    def get(cls, device: int | None = None) -> "Context":
+        if device is None:
+            device = torch.cuda.current_device()
+        ctx = cls._by_device.get(device)
+        if ctx is None:
+            ctx = cls._by_device[device] = Context(device)
+        return ctx
+
+    def check(self) -> None:
+        L.check(L.lib().izb_ctx_check(self.handle, _stream()), "izb_ctx_check")
+
+    @property
+    def launch_count(self) -> int:
+        return int(L.lib().izb_ctx_launch_count(self.handle))
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def quantized_storage_bytes(rows: int, cols: int, fmt: str) -> int:
+    out = C.c_size_t()
+    L.check(L.lib().izb_quantized_storage_bytes(WFMT[fmt], rows, cols, C.byref(out)), "izb_quantized_storage_bytes")
+    return out.value
+
+
+def dequantize(raw: torch.Tensor, fmt: str, n_elems: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    assert raw.is_cuda and raw.dtype == torch.uint8 and raw.is_contiguous()
+    out = torch.empty(n_elems, device=raw.device, dtype=dtype)
+    code = L.IZB_F32 if dtype == torch.float32 else L.IZB_BF16
+    ctx = Context.get(raw.device.index)
+    L.check(L.lib().izb_dequantize(ctx.handle, _stream(), WFMT[fmt], _ptr(raw), n_elems, code, _ptr(out)),
+            "izb_dequantize")
+    return out
+
+
+def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: torch.Tensor,
+                bias: torch.Tensor | None = None) -> L.LinearArgs:
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    assert y.dim() == 2 and y.stride(1) == 1 and y.shape[0] == x.shape[0]
+    a = L.LinearArgs()
+    a.wfmt = WFMT[fmt]
+    a.y_dtype = L.IZB_F32 if y.dtype == torch.float32 else L.IZB_BF16
+    a.x, a.w, a.bias, a.y = x.data_ptr(), w.data_ptr(), (0 if bias is None else bias.data_ptr()), y.data_ptr()
+    a.M, a.N, a.K = x.shape[0], n, k
+    a.ldx, a.ldy = x.stride(0), y.stride(0)
+    a.workspace, a.workspace_bytes = None, 0
+    return a
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = None, k: int | None = None,
+           bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
+           out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Y = X . W^T (+ bias).  `x` may have any number of leading dimensions
+    (flattened to M like the reference's Linear); `w` is [N, K] bf16 or the raw
+    GGML bytes of N rows of K values."""
+    if fmt == "bf16":
+        n, k = w.shape
+    assert n is not None and k is not None
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.shape[1] != k:
+        raise ValueError(f"linear: input dim {x2.shape[1]} != weight in-dim {k}")
+    y = out if out is not None else torch.empty(x2.shape[0], n, device=x.device, dtype=out_dtype)
+    a = linear_args(x2, w, fmt, n, k, y.reshape(-1, n), bias)
+    ctx = Context.get(x.device.index)
+    L.check(L.lib().izb_linear(ctx.handle, _stream(), C.byref(a)), "izb_linear")
+    return y.reshape(*lead, n)
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    assert gate.shape == up.shape and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16
+    g2, u2 = gate.reshape(-1, gate.shape[-1]), up.reshape(-1, up.shape[-1])
+    assert g2.stride(1) == 1 and u2.stride(1) == 1
+    o = out if out is not None else torch.empty(gate.shape, device=gate.device, dtype=torch.bfloat16)
+    o2 = o.reshape(-1, o.shape[-1])
+    ctx = Context.get(gate.device.index)
+    L.check(L.lib().izb_silu_mul(ctx.handle, _stream(), _ptr(g2), _ptr(u2), _ptr(o2), g2.shape[0], g2.shape[1],
+                                 g2.stride(0), u2.stride(0), o2.stride(0)), "izb_silu_mul")
+    return o
+
+
+class LinearGroup:
+    """A set of independent small-M linear layers run by one persistent launch
+    (izb_linear_group_*).  Keeps the tensors alive and owns the device copy of
+    the plan."""
+
+    def __init__(self, problems: list[L.LinearArgs], device: torch.device, keepalive=None):
+        self.n = len(problems)
+        self.ctx = Context.get(device.index)
+        arr = (L.LinearArgs * self.n)(*problems)
+        nbytes = L.lib().izb_linear_group_plan_bytes(self.n)
+        self.host_plan = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+        L.check(L.lib().izb_linear_group_plan(self.ctx.handle, arr, self.n, C.c_void_p(self.host_plan.data_ptr()),
+                                              nbytes), "izb_linear_group_plan")
+        self.dev_plan = self.host_plan.to(device)
+        self.keepalive = keepalive
+
+    def launch(self) -> None:
+        L.check(L.lib().izb_linear_group_launch(self.ctx.handle, _stream(), C.c_void_p(self.host_plan.data_ptr()),
+                                                C.c_void_p(self.dev_plan.data_ptr())), "izb_linear_group_launch")

@@ -1,0 +1,122 @@
+"""Linear layers on the GPU through the C ABI, checked against the oracle on the
+same seeded inputs.  Gates: max relative error <= 2e-2 (relative to the row's
+max |y|) and cosine >= 0.9999, the tolerance stated for bf16 matmul outputs
+accumulated in fp32."""
+import numpy as np
+import pytest
+import torch
+
+import izwi_oracle as o
+from gpu_util import assert_matmul_close, bf16_np, make_weight_np, to_np, upload_weight
+
+pytestmark = pytest.mark.gpu
+
+QWEN06 = [(4096, 1024), (1024, 2048), (6144, 1024), (1024, 3072)]
+
+
+def run_linear(cuda, fmt, m, n, k, seed, bias=False, out_dtype=torch.bfloat16):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(seed)
+    raw, wf = make_weight_np(fmt, n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (m, k)))
+    b = bf16_np(rng.normal(0, 0.5, n)) if bias else None
+    want = o.linear(x, wf, b)
+    xd = torch.from_numpy(x).to(cuda).to(torch.bfloat16)
+    bd = None if b is None else torch.from_numpy(b).to(cuda).to(torch.bfloat16)
+    got = ops.linear(xd, upload_weight(fmt, raw, cuda), fmt, n=n, k=k, bias=bd, out_dtype=out_dtype)
+    ops.Context.get(0).check()
+    return assert_matmul_close(got, want, f"{fmt} M={m} N={n} K={k}")
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "q8_0", "q4_k"])
+@pytest.mark.parametrize("m", [1, 4, 16, 64])
+def test_qwen3_0_6b_projection_shapes(cuda, fmt, m):
+    for i, (n, k) in enumerate(QWEN06):
+        run_linear(cuda, fmt, m, n, k, seed=100 + i)
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "q8_0", "q4_k"])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 256), (3, 17, 256), (7, 16, 512), (8, 130, 768), (9, 1000, 256),
+                                   (33, 64, 1280), (2, 48, 5120), (5, 257, 2304)])
+def test_ragged_shapes(cuda, fmt, m, n, k):
+    run_linear(cuda, fmt, m, n, k, seed=m * 1000 + n)
+
+
+@pytest.mark.parametrize("tile_rows", ["16", "32", "64", "128"])
+@pytest.mark.parametrize("fmt", ["bf16", "q8_0", "q4_k"])
+def test_every_tile_configuration(cuda, fmt, tile_rows, monkeypatch):
+    """Each row-tile / k-split variant of the streaming kernel, forced in turn."""
+    monkeypatch.setenv("IZB_SKINNY_TILE_ROWS", tile_rows)
+    for m in (2, 12):
+        run_linear(cuda, fmt, m, 336, 1536, seed=int(tile_rows) + m)
+
+
+def test_small_k_chunks_and_two_stages(cuda, monkeypatch):
+    """Many k-chunks per tile and the shallowest ring: exercises barrier phase wrap-around."""
+    monkeypatch.setenv("IZB_SKINNY_STAGE_KB", "4")
+    monkeypatch.setenv("IZB_SKINNY_STAGES", "2")
+    for fmt in ("bf16", "q8_0", "q4_k"):
+        run_linear(cuda, fmt, 5, 200, 4096, seed=77)
+
+
+def test_bias_and_f32_output(cuda):
+    run_linear(cuda, "bf16", 3, 1280, 1280, seed=5, bias=True)
+    run_linear(cuda, "bf16", 6, 640, 1024, seed=6, bias=True, out_dtype=torch.float32)
+    run_linear(cuda, "q8_0", 2, 512, 1024, seed=7, out_dtype=torch.float32)
+
+
+def test_m_above_64_is_chunked(cuda):
+    run_linear(cuda, "bf16", 150, 384, 512, seed=8)
+    run_linear(cuda, "q4_k", 70, 256, 512, seed=9)
+
+
+def test_strided_rows_and_leading_dims(cuda):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(3)
+    n, k = 96, 256
+    raw, wf = make_weight_np("bf16", n, k, rng)
+    w = upload_weight("bf16", raw, cuda)
+    x = bf16_np(rng.normal(0, 1, (2, 3, k)))
+    xd = torch.from_numpy(x).to(cuda).to(torch.bfloat16)
+    got = ops.linear(xd, w)
+    assert got.shape == (2, 3, n)
+    assert_matmul_close(got, o.linear(x, wf), "3-D input")
+    big = torch.zeros(5, 2 * k, device=cuda, dtype=torch.bfloat16)
+    big[:, :k] = xd.reshape(6, k)[:5]
+    ybig = torch.zeros(5, 3 * n, device=cuda, dtype=torch.bfloat16)
+    ops.linear(big[:, :k], w, out=ybig[:, n:2 * n])
+    assert_matmul_close(ybig[:, n:2 * n], o.linear(x.reshape(6, k)[:5], wf), "strided")
+    assert float(ybig[:, :n].abs().max()) == 0.0 and float(ybig[:, 2 * n:].abs().max()) == 0.0
+
+
+def test_linearity_property_full_size(cuda):
+    """Full-size gate/up projection of the 8B shape: W(a+b) = Wa + Wb and scaling,
+    within bf16 output rounding; no CPU product needed at this size."""
+    from izwi_b200 import ops
+    gen = torch.Generator(device=cuda).manual_seed(3)
+    n, k = 24576, 4096
+    w = (torch.randn(n, k, device=cuda, generator=gen) * 0.02).to(torch.bfloat16)
+    a = torch.randn(1, k, device=cuda, generator=gen).to(torch.bfloat16)
+    ya = ops.linear(a, w, out_dtype=torch.float32)
+    y2 = ops.linear((a.float() * 2).to(torch.bfloat16), w, out_dtype=torch.float32)
+    assert torch.allclose(y2, 2 * ya, rtol=1e-5, atol=1e-5)
+    rows = torch.randint(0, n, (64,), device=cuda, generator=gen)
+    want = (w[rows].double() @ a.double().T).squeeze(1)
+    assert torch.allclose(ya[0, rows].double(), want, rtol=1e-3, atol=1e-3)
+
+
+def test_rejects_bad_arguments(cuda):
+    from izwi_b200 import IzbError, ops
+    w = torch.zeros(64, 256, device=cuda, dtype=torch.bfloat16)
+    x = torch.zeros(2, 256, device=cuda, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        ops.linear(torch.zeros(2, 128, device=cuda, dtype=torch.bfloat16), w)
+    with pytest.raises(IzbError) as e:      # K not a multiple of 64
+        ops.linear(torch.zeros(2, 40, device=cuda, dtype=torch.bfloat16),
+                   torch.zeros(8, 40, device=cuda, dtype=torch.bfloat16))
+    assert e.value.status == -2
+    with pytest.raises(IzbError) as e:      # misaligned weight pointer
+        ops.linear(x, torch.zeros(64 * 256 + 8, device=cuda, dtype=torch.bfloat16)[1:64 * 256 + 1].reshape(64, 256))
+    assert e.value.status == -1
+    assert ops.linear(torch.zeros(0, 256, device=cuda, dtype=torch.bfloat16), w).shape == (0, 64)
+    ops.Context.get(0).check()
