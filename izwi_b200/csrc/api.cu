@@ -306,14 +306,14 @@ size_t izb_linear_group_plan_bytes(int32_t n_problems) {
 int32_t izb_linear_group_plan(izb_ctx* ctx, const izb_linear_args* problems, int32_t n_problems, void* host_plan,
                               size_t host_plan_bytes) {
     if (!ctx || !problems || !host_plan || n_problems <= 0) return IZB_ERR_BAD_ARG;
-    if (host_plan_bytes < izb_linear_group_plan_bytes(n_problems) || !izb_aligned(host_plan, 16)) return IZB_ERR_BAD_ARG;
+    if (host_plan_bytes < izb_linear_group_plan_bytes(n_problems) || !izb_aligned(host_plan, 64)) return IZB_ERR_BAD_ARG;
     auto* hdr = static_cast<SkinnyPlanHeader*>(host_plan);
     auto* probs = reinterpret_cast<SkinnyProblem*>(static_cast<uint8_t*>(host_plan) + sizeof(SkinnyPlanHeader));
     return skinny_plan_build(ctx, problems, n_problems, hdr, probs);
 }
 
 int32_t izb_linear_group_launch(izb_ctx* ctx, izb_stream stream, const void* host_plan, const void* dev_plan) {
-    if (!ctx || !host_plan || !dev_plan || !izb_aligned(dev_plan, 16)) return IZB_ERR_BAD_ARG;
+    if (!ctx || !host_plan || !dev_plan || !izb_aligned(dev_plan, 64)) return IZB_ERR_BAD_ARG;
     const auto* hdr = static_cast<const SkinnyPlanHeader*>(host_plan);
     const auto* dev = reinterpret_cast<const SkinnyProblem*>(static_cast<const uint8_t*>(dev_plan) + sizeof(SkinnyPlanHeader));
     return skinny_launch(ctx, static_cast<cudaStream_t>(stream), *hdr, dev, nullptr);

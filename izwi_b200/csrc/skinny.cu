@@ -4,35 +4,9 @@
 #include <cstring>
 
 #include "skinny.cuh"
+#include "tma.cuh"
 
 namespace izb {
-
-// ---------------------------------------------------------------------------
-// per-format constants
-// ---------------------------------------------------------------------------
-template <int FMT>
-struct Fmt;
-template <>
-struct Fmt<IZB_W_BF16> {
-    static constexpr int kUnit = 64;          // k values a consumer warp handles per inner step
-    static constexpr int kAlign = 64;         // K must be a multiple of this
-    static constexpr int kXStrideMod = 64;    // x row stride == this (mod 128) -> conflict-free LDS.128
-    __host__ __device__ static constexpr int bytes(int k) { return k * 2; }
-};
-template <>
-struct Fmt<IZB_W_Q8_0> {
-    static constexpr int kUnit = 64;   // one pair of 34-byte blocks = 17 aligned words
-    static constexpr int kAlign = 256; // 8 blocks = 272 bytes: smallest 16-byte aligned run
-    static constexpr int kXStrideMod = 32;  // LDS.64 activation loads
-    __host__ __device__ static constexpr int bytes(int k) { return k / 32 * 34; }
-};
-template <>
-struct Fmt<IZB_W_Q4_K> {
-    static constexpr int kUnit = 256;  // one 144-byte super-block
-    static constexpr int kAlign = 256;
-    static constexpr int kXStrideMod = 64;
-    __host__ __device__ static constexpr int bytes(int k) { return k / 256 * 144; }
-};
 
 __device__ __forceinline__ float half_bits_to_f32(uint32_t h) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
@@ -57,33 +31,44 @@ __device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t 
     return d;
 }
 
-__device__ __forceinline__ uint32_t bcast_bf16x2(float v) {
-    return pack_bf16x2(v, v);
-}
+__device__ __forceinline__ uint32_t bcast_bf16x2(float v) { return pack_bf16x2(v, v); }
+
+// Row permutations that make the shared-memory loads bank-conflict free under the 128-byte
+// swizzle (16-byte chunk index ^= row & 7).  Fragment row/column g of an mma maps to
+// shared-memory row perm(g) inside its group of eight.
+//   kPermQuad: for 16-byte loads by lane quads   [0,4,1,5,2,6,3,7]
+//   kPermPair: for  8-byte loads by lane quads   [0,2,4,6,1,3,5,7]
+__device__ __forceinline__ int perm_quad(int g) { return (g >> 1) | ((g & 1) << 2); }
+__device__ __forceinline__ int perm_pair(int g) { return ((g & 3) << 1) | (g >> 2); }
 
 // ---------------------------------------------------------------------------
-// consumer inner loops: one k-chunk of one stage
+// consumer inner loops: one pipeline stage
 //   wbase/xbase: shared-memory byte addresses of the stage's weight / activation regions
+//   the activation region is [k/64 chunks][8*NT token rows][128 bytes], swizzled
 //   rowbase: first row (inside the tile) of this warp; g = lane/4, t = lane%4
 // ---------------------------------------------------------------------------
+
+// bf16: one weight box = 64 k = [TILE_ROWS][128 bytes], swizzled like the activations.
 template <int NT, int RT, int KS>
-__device__ __forceinline__ void chunk_bf16(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase, int ws, int xs,
-                                           int kcur, int rowbase, int ks, int g, int t) {
-    const int units = kcur >> 6;
-    for (int u = ks; u < units; u += KS) {
+__device__ __forceinline__ void stage_bf16(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase,
+                                           const SkinnyProblem& P, int rowbase, int ks, int g, int t) {
+    const int pg = perm_quad(g);
+    for (int b = ks; b < P.nb; b += KS) {
+        const uint32_t wbox = wbase + static_cast<uint32_t>(b * P.w_box_bytes);
+        const uint32_t xbox = xbase + static_cast<uint32_t>(b * (NT * 1024));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t koff = static_cast<uint32_t>((u * 64 + h * 32 + t * 8) * 2);
+            const uint32_t col = static_cast<uint32_t>(((4 * h + t) ^ pg) << 4);
             uint4 wa[RT], wb[RT];
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
-                const uint32_t ra = wbase + static_cast<uint32_t>((rowbase + rt * 16 + g) * ws) + koff;
+                const uint32_t ra = wbox + static_cast<uint32_t>((rowbase + rt * 16 + pg) * 128) + col;
                 wa[rt] = lds128(ra);
-                wb[rt] = lds128(ra + 8 * ws);
+                wb[rt] = lds128(ra + 8 * 128);
             }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint4 xb = lds128(xbase + static_cast<uint32_t>((nt * 8 + g) * xs) + koff);
+                const uint4 xb = lds128(xbox + static_cast<uint32_t>((nt * 8 + pg) * 128) + col);
 #pragma unroll
                 for (int rt = 0; rt < RT; ++rt) {
                     mma_bf16_16816(acc[rt][nt], wa[rt].x, wb[rt].x, wa[rt].y, wb[rt].y, xb.x, xb.y);
@@ -94,23 +79,26 @@ __device__ __forceinline__ void chunk_bf16(float (&acc)[RT][NT][4], uint32_t wba
     }
 }
 
-// Q8_0.  A pair of blocks is 68 bytes = 17 aligned words:
+// Q8_0: one weight box = 256 k = [TILE_ROWS][272 bytes] = 4 pairs of 34-byte blocks.
+// A pair is 68 bytes = 17 aligned words:
 //   word 0 = [d0 | q0[0..1]], words 1..7 = q0[2..29], word 8 = [q0[30..31] | d1], words 9..16 = q1[0..31].
 // Block 0's codes sit half a word off, so each logical word is funnelled out of two neighbours.
 // The integer codes go through the tensor core exactly; the block scale is applied in fp32.
 template <int NT, int RT, int KS>
-__device__ __forceinline__ void chunk_q8_0(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase, int ws, int xs,
-                                           int kcur, int rowbase, int ks, int g, int t) {
-    const int units = kcur >> 6;
+__device__ __forceinline__ void stage_q8_0(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase,
+                                           const SkinnyProblem& P, int rowbase, int ks, int g, int t) {
+    const int pg = perm_pair(g);
+    const int units = P.nb * 4;
     for (int u = ks; u < units; u += KS) {
+        const uint32_t wbox = wbase + static_cast<uint32_t>((u >> 2) * P.w_box_bytes + (u & 3) * 68);
+        const uint32_t xchunk = xbase + static_cast<uint32_t>(u * (NT * 1024));
         uint32_t a[RT][4][4];  // [tile][step][a0..a3]
         float d[RT][2][2];     // [tile][block][row a / row b]
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const uint32_t wr =
-                    wbase + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * ws) + static_cast<uint32_t>(u * 68);
+                const uint32_t wr = wbox + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * 272);
                 const uint32_t w0 = lds32(wr), w8 = lds32(wr + 32);
                 const uint32_t l0 = lds32(wr + 4 * t), l1 = lds32(wr + 4 * t + 4);
                 const uint32_t h0 = lds32(wr + 16 + 4 * t), h1 = lds32(wr + 20 + 4 * t);
@@ -126,10 +114,11 @@ __device__ __forceinline__ void chunk_q8_0(float (&acc)[RT][NT][4], uint32_t wba
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t xr = xbase + static_cast<uint32_t>((nt * 8 + g) * xs) + static_cast<uint32_t>((u * 64 + 4 * t) * 2);
+            // step s covers k = 16 s + 4 t .. +3 of the pair: byte 32 s + 8 t of the 128-byte token row
+            const uint32_t xr = xchunk + static_cast<uint32_t>((nt * 8 + pg) * 128 + (t & 1) * 8);
             uint2 xv[4];
 #pragma unroll
-            for (int s = 0; s < 4; ++s) xv[s] = lds64(xr + s * 32);
+            for (int s = 0; s < 4; ++s) xv[s] = lds64(xr + static_cast<uint32_t>(((2 * s + (t >> 1)) ^ pg) << 4));
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
 #pragma unroll
@@ -149,23 +138,27 @@ __device__ __forceinline__ void chunk_q8_0(float (&acc)[RT][NT][4], uint32_t wba
     }
 }
 
-// Q4_K.  Super-block = [d, dmin (fp16) | 12 scale bytes | 4 groups of 32 code bytes]; group j holds
+// Q4_K: one weight box = kbox/256 super-blocks of 144 bytes per row.
+// Super-block = [d, dmin (fp16) | 12 scale bytes | 4 groups of 32 code bytes]; group j holds
 // sub-block 2j in the low nibbles and 2j+1 in the high nibbles.  A nibble n is lifted to the bf16
 // value 16+n with one shift and one logic op (0x4180 | n<<3), then one bf16x2 fma with the
 // sub-block's (d*sc) and -(16*d*sc + dmin*m) turns it into the dequantised weight.  Lane t of a
 // quad decodes the scales of sub-blocks 2t and 2t+1 and hands them round by shuffle.
 template <int NT, int RT, int KS>
-__device__ __forceinline__ void chunk_q4_k(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase, int ws, int xs,
-                                           int kcur, int rowbase, int ks, int g, int t, int lane) {
-    const int nsb = kcur >> 8;
+__device__ __forceinline__ void stage_q4_k(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase,
+                                           const SkinnyProblem& P, int rowbase, int ks, int g, int t, int lane) {
+    const int pg = perm_quad(g);
+    const int sbb = P.kbox >> 8;  // super-blocks per box
+    const int nsb = P.nb * sbb;
+    const int wrow = P.w_row_bytes;
     for (int sb = ks; sb < nsb; sb += KS) {
+        const uint32_t wsb = wbase + static_cast<uint32_t>((sb / sbb) * P.w_box_bytes + (sb % sbb) * 144);
         uint32_t my_s[RT][2][2], my_c[RT][2][2];  // [tile][row a/b][own sub-block 0/1]
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const uint4 hd = lds128(wbase + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * ws) +
-                                        static_cast<uint32_t>(sb * 144));
+                const uint4 hd = lds128(wsb + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * wrow));
                 const float dd = half_bits_to_f32(hd.x), dmin = half_bits_to_f32(hd.x >> 16);
                 const uint32_t sc_lo = hd.y & 0x3F3F3F3Fu, mn_lo = hd.z & 0x3F3F3F3Fu;
                 const uint32_t sc_hi = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
@@ -194,8 +187,8 @@ __device__ __forceinline__ void chunk_q4_k(float (&acc)[RT][NT][4], uint32_t wba
                     const uint32_t s1 = __shfl_sync(0xFFFFFFFFu, my_s[rt][half][1], src);
                     const uint32_t c0 = __shfl_sync(0xFFFFFFFFu, my_c[rt][half][0], src);
                     const uint32_t c1 = __shfl_sync(0xFFFFFFFFu, my_c[rt][half][1], src);
-                    const uint2 wv = lds64(wbase + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * ws) +
-                                           static_cast<uint32_t>(sb * 144 + 16 + j * 32 + t * 8));
+                    const uint2 wv = lds64(wsb + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * wrow) +
+                                           static_cast<uint32_t>(16 + j * 32 + t * 8));
 #pragma unroll
                     for (int wd = 0; wd < 2; ++wd) {
                         const uint32_t w = wd ? wv.y : wv.x;
@@ -208,13 +201,14 @@ __device__ __forceinline__ void chunk_q4_k(float (&acc)[RT][NT][4], uint32_t wba
                     }
                 }
             }
+            // group j of super-block sb is activation chunk sb*4 + j: bytes [0,64) = sub-block 2j, [64,128) = 2j+1
+            const uint32_t xchunk = xbase + static_cast<uint32_t>((sb * 4 + j) * (NT * 1024));
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint32_t xr = xbase + static_cast<uint32_t>((nt * 8 + g) * xs) +
-                                    static_cast<uint32_t>((sb * 256 + j * 64 + t * 8) * 2);
+                const uint32_t xr = xchunk + static_cast<uint32_t>((nt * 8 + pg) * 128);
 #pragma unroll
                 for (int sub = 0; sub < 2; ++sub) {
-                    const uint4 xq = lds128(xr + sub * 64);
+                    const uint4 xq = lds128(xr + static_cast<uint32_t>(((4 * sub + t) ^ pg) << 4));
                     // word 0 covers x[0..3] -> operand pairs (x0,x2),(x1,x3); word 1 covers x[4..7]
                     const uint32_t b00 = prmt(xq.x, xq.y, 0x5410), b01 = prmt(xq.x, xq.y, 0x7632);
                     const uint32_t b10 = prmt(xq.z, xq.w, 0x5410), b11 = prmt(xq.z, xq.w, 0x7632);
@@ -256,7 +250,7 @@ __global__ void __launch_bounds__(SK_THREADS)
     constexpr int TILE_ROWS = RG * RT * 16;
     constexpr int ACC = RT * NT * 4;
 
-    extern __shared__ __align__(128) uint8_t dyn_smem[];
+    extern __shared__ __align__(1024) uint8_t dyn_smem[];
     __shared__ SkinnyShared sh;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -276,42 +270,39 @@ __global__ void __launch_bounds__(SK_THREADS)
     const uint32_t stage0 = smem_u32(dyn_smem) + static_cast<uint32_t>(red_bytes);
 
     if (warp == SK_CONSUMER_WARPS) {
-        // ---------------- producer ----------------
+        // ---------------- producer: one lane issues two tiled copies per stage ----------------
+        if (lane != 0) return;
         int stage = 0;
         uint32_t phase = 0;
         long long issued = 0;
         bool ok = true;
-        int p = 0;
-        SkinnyProblem P = plist[0];
+        int p = -1;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            bool moved = false;
+            bool moved = p < 0;
+            if (p < 0) p = 0;
             while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) {
                 ++p;
                 moved = true;
             }
-            if (moved) P = plist[p];
-            const int row0 = (tile - P.tile_start) * TILE_ROWS;
-            const int rows = min(TILE_ROWS, P.N - row0);
-            for (int c = 0; c < P.n_chunks; ++c) {
-                const int kcur = min(P.kc, P.K - c * P.kc);
-                const uint32_t wbytes = static_cast<uint32_t>(Fmt<FMT>::bytes(kcur));
-                const uint32_t xbytes = static_cast<uint32_t>(kcur * 2);
-                const uint32_t fbar = smem_u32(&sh.full[stage]);
+            const SkinnyProblem* P = plist + p;
+            if (moved && probs) {
+                tma_fence_descriptor(&P->tmap_w);
+                tma_fence_descriptor(&P->tmap_x);
+            }
+            const int row0 = (tile - P->tile_start) * TILE_ROWS;
+            const int n_chunks = P->n_chunks, nb = P->nb, x_off = P->x_off;
+            const uint32_t tx = static_cast<uint32_t>(P->stage_tx);
+            const int xchunks = nb * (P->kbox >> 6);
+            for (int c = 0; c < n_chunks; ++c) {
                 if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
-                if (lane == 0) mbar_expect_tx(fbar, static_cast<uint32_t>(rows) * wbytes + static_cast<uint32_t>(P.M) * xbytes);
-                __syncwarp();
+                const uint32_t fbar = smem_u32(&sh.full[stage]);
                 const uint32_t sbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
-                const uint8_t* wsrc = P.w + static_cast<long long>(row0) * P.row_bytes + static_cast<long long>(c) * P.chunk_bytes;
-                for (int r = lane; r < rows; r += 32)
-                    bulk_g2s(sbase + static_cast<uint32_t>(r * P.w_stride), wsrc + static_cast<long long>(r) * P.row_bytes, wbytes,
-                             fbar);
-                const __nv_bfloat16* xsrc = P.x + static_cast<long long>(c) * P.kc;
-                for (int m = lane; m < P.M; m += 32)
-                    bulk_g2s(sbase + static_cast<uint32_t>(P.x_off + m * P.x_stride), xsrc + static_cast<long long>(m) * P.ldx,
-                             xbytes, fbar);
+                mbar_expect_tx(fbar, tx);
+                tma_load_3d(sbase, &P->tmap_w, 0, row0, c * nb, fbar);
+                tma_load_3d(sbase + static_cast<uint32_t>(x_off), &P->tmap_x, 0, 0, c * xchunks, fbar);
                 ++issued;
                 if (++stage == n_stages) {
                     stage = 0;
@@ -340,7 +331,7 @@ __global__ void __launch_bounds__(SK_THREADS)
                     if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) break;
                 }
             }
-            if (lane == 0) atomicExch(status, 1);
+            atomicExch(status, 1);
         }
         return;
     }
@@ -356,15 +347,12 @@ __global__ void __launch_bounds__(SK_THREADS)
     bool ok = true;
     int p = 0;
     int tile_parity = 0;
-    SkinnyProblem P = plist[0];
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_parity ^= 1) {
-        bool moved = false;
-        while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) {
-            ++p;
-            moved = true;
-        }
-        if (moved) P = plist[p];
+        while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) ++p;
+        const SkinnyProblem& P = plist[p];
         const int row0 = (tile - P.tile_start) * TILE_ROWS;
+        const int n_chunks = P.n_chunks;
+        const uint32_t x_off = static_cast<uint32_t>(P.x_off);
 
         float acc[RT][NT][4];
 #pragma unroll
@@ -374,18 +362,17 @@ __global__ void __launch_bounds__(SK_THREADS)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[rt][nt][i] = 0.f;
 
-        for (int c = 0; c < P.n_chunks; ++c) {
-            const int kcur = min(P.kc, P.K - c * P.kc);
+        for (int c = 0; c < n_chunks; ++c) {
             if (ok && !mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) ok = false;
             if (ok) {
                 const uint32_t wbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
-                const uint32_t xbase = wbase + static_cast<uint32_t>(P.x_off);
+                const uint32_t xbase = wbase + x_off;
                 if constexpr (FMT == IZB_W_BF16)
-                    chunk_bf16<NT, RT, KS>(acc, wbase, xbase, P.w_stride, P.x_stride, kcur, rowbase, ks, g, t);
+                    stage_bf16<NT, RT, KS>(acc, wbase, xbase, P, rowbase, ks, g, t);
                 else if constexpr (FMT == IZB_W_Q8_0)
-                    chunk_q8_0<NT, RT, KS>(acc, wbase, xbase, P.w_stride, P.x_stride, kcur, rowbase, ks, g, t);
+                    stage_q8_0<NT, RT, KS>(acc, wbase, xbase, P, rowbase, ks, g, t);
                 else
-                    chunk_q4_k<NT, RT, KS>(acc, wbase, xbase, P.w_stride, P.x_stride, kcur, rowbase, ks, g, t, lane);
+                    stage_q4_k<NT, RT, KS>(acc, wbase, xbase, P, rowbase, ks, g, t, lane);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh.empty[stage]));
@@ -424,21 +411,27 @@ __global__ void __launch_bounds__(SK_THREADS)
         }
 
         if (ks == 0 && ok) {
+            // Fragment row g sits in tile row perm(g) for bf16 (swizzled tile), g otherwise;
+            // fragment column n sits in token perm(n) of its group of eight.
+            const int rsel = FMT == IZB_W_BF16 ? perm_quad(g) : g;
+            const int N = P.N, M = P.M, ldy = P.ldy;
+            const __nv_bfloat16* bias = P.bias;
+            void* y = P.y;
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
-                const int ra = row0 + rowbase + rt * 16 + g;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    const int row = ra + half * 8;
-                    if (row < P.N) {
-                        const float b = P.bias ? __bfloat162float(P.bias[row]) : 0.f;
+                    const int row = row0 + rowbase + rt * 16 + rsel + half * 8;
+                    if (row < N) {
+                        const float b = bias ? __bfloat162float(bias[row]) : 0.f;
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                             for (int i = 0; i < 2; ++i) {
-                                const int tok = nt * 8 + 2 * t + i;
-                                if (tok < P.M)
-                                    store_out(P.y, y_dtype, static_cast<long long>(tok) * P.ldy + row,
+                                const int n = 2 * t + i;
+                                const int tok = nt * 8 + (FMT == IZB_W_Q8_0 ? perm_pair(n) : perm_quad(n));
+                                if (tok < M)
+                                    store_out(y, y_dtype, static_cast<long long>(tok) * ldy + row,
                                               acc[rt][nt][half * 2 + i] + b);
                             }
                         }
@@ -459,30 +452,6 @@ int env_int(const char* name, int dflt) {
     const char* v = std::getenv(name);
     if (!v || !*v) return dflt;
     return std::atoi(v);
-}
-
-int fmt_bytes(int fmt, int k) {
-    switch (fmt) {
-        case IZB_W_BF16: return Fmt<IZB_W_BF16>::bytes(k);
-        case IZB_W_Q8_0: return Fmt<IZB_W_Q8_0>::bytes(k);
-        default: return Fmt<IZB_W_Q4_K>::bytes(k);
-    }
-}
-int fmt_unit(int fmt) { return fmt == IZB_W_Q4_K ? 256 : 64; }
-int fmt_kalign(int fmt) { return fmt == IZB_W_BF16 ? 64 : 256; }
-int fmt_xmod(int fmt) { return fmt == IZB_W_Q8_0 ? 32 : 64; }
-
-// Padded shared-memory row stride that keeps the consumers' loads free of bank conflicts.
-int w_stride_for(int fmt, int chunk_bytes) {
-    switch (fmt) {
-        case IZB_W_BF16: return chunk_bytes + ((64 - chunk_bytes % 128) + 128) % 128;  // == 64 (mod 128)
-        case IZB_W_Q8_0: return chunk_bytes + ((16 - chunk_bytes % 32) + 32) % 32;     // == 16 (mod 32)
-        default: return chunk_bytes + ((32 - chunk_bytes % 128) + 128) % 128;          // == 32 (mod 128)
-    }
-}
-int x_stride_for(int fmt, int kc) {
-    const int raw = kc * 2, mod = fmt_xmod(fmt);
-    return raw + ((mod - raw % 128) + 128) % 128;
 }
 
 template <int FMT, int NT, int RT, int KS>
@@ -531,6 +500,22 @@ int launch_fmt(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, con
     }
 }
 
+struct BoxGeom {
+    int kbox;         // k values per weight box
+    int w_row_bytes;  // bytes per row of a box
+};
+
+BoxGeom box_geom(int fmt, int K) {
+    switch (fmt) {
+        case IZB_W_BF16: return {64, 128};
+        case IZB_W_Q8_0: return {256, 272};
+        default:
+            // two super-blocks per box keep the 8-byte code loads conflict free (288 = 32 mod 128);
+            // an odd super-block count per row falls back to one (144-byte rows, 2-way conflicts)
+            return (K % 512 == 0) ? BoxGeom{512, 288} : BoxGeom{256, 144};
+    }
+}
+
 }  // namespace
 
 int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, SkinnyPlanHeader* hdr,
@@ -539,8 +524,9 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const int fmt = probs[0].wfmt, y_dtype = probs[0].y_dtype;
     if (fmt != IZB_W_BF16 && fmt != IZB_W_Q8_0 && fmt != IZB_W_Q4_K) return IZB_ERR_BAD_ARG;
     if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
+    const int kalign = fmt == IZB_W_BF16 ? 64 : 256;
 
-    int64_t max_m = 0, total_rows = 0;
+    int64_t max_m = 0;
     for (int i = 0; i < n; ++i) {
         const izb_linear_args& a = probs[i];
         if (a.wfmt != fmt || a.y_dtype != y_dtype) return IZB_ERR_BAD_ARG;
@@ -548,13 +534,12 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         if (a.M <= 0 || a.N <= 0 || a.K <= 0) return IZB_ERR_BAD_ARG;
         if (a.M > 64) return IZB_ERR_UNSUPPORTED;
         if (a.N > (1 << 24) || a.K > (1 << 20)) return IZB_ERR_UNSUPPORTED;
-        if (a.K % fmt_kalign(fmt) != 0) return IZB_ERR_UNSUPPORTED;
+        if (a.K % kalign != 0) return IZB_ERR_UNSUPPORTED;
         if (a.ldx < a.K || a.ldy < a.N || a.ldx % 8 != 0) return IZB_ERR_BAD_ARG;
         if (!izb_aligned(a.x, 16) || !izb_aligned(a.w, 16)) return IZB_ERR_BAD_ARG;
         if (!izb_aligned(a.y, y_dtype == IZB_F32 ? 4 : 2)) return IZB_ERR_BAD_ARG;
         if (a.bias && !izb_aligned(a.bias, 2)) return IZB_ERR_BAD_ARG;
         max_m = std::max<int64_t>(max_m, a.M);
-        total_rows += a.N;
     }
     const int nt = max_m <= 8 ? 1 : max_m <= 16 ? 2 : max_m <= 32 ? 4 : 8;
     const int mp = nt * 8;
@@ -562,8 +547,19 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", 2));
     const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
     const int max_grid = ctx->sm_count * ctas_per_sm;
+    const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_cast<int>(sizeof(SkinnyShared));
 
-    // Largest row tile that still leaves every CTA a few tiles to balance with.
+    // Bytes of the smallest possible stage (one weight box + its activation chunks) of a row tile.
+    auto min_stage = [&](int rows) {
+        int worst = 0;
+        for (int i = 0; i < n; ++i) {
+            const BoxGeom bg = box_geom(fmt, static_cast<int>(probs[i].K));
+            worst = std::max(worst, rows * bg.w_row_bytes + (bg.kbox / 64) * mp * 128);
+        }
+        return worst;
+    };
+
+    // Largest row tile that leaves every CTA a few tiles to balance with and room for >= 3 stages.
     struct Cand { int rt, ks, rows; };
     const Cand cands[4] = {{2, 1, 128}, {1, 1, 64}, {1, 2, 32}, {1, 4, 16}};
     int pick = 3;
@@ -576,49 +572,75 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         }
         int64_t tiles = 0;
         for (int i = 0; i < n; ++i) tiles += (probs[i].N + cands[c].rows - 1) / cands[c].rows;
-        if (tiles >= 4LL * max_grid) { pick = c; break; }
+        if (tiles >= 4LL * max_grid && 3 * min_stage(cands[c].rows) <= budget) { pick = c; break; }
     }
     const int rt = cands[pick].rt, ks = cands[pick].ks, tile_rows = cands[pick].rows;
     const int rg = SK_CONSUMER_WARPS / ks;
 
     int stage_bytes = 0, tile_cursor = 0;
-    const int unit = fmt_kalign(fmt);
     for (int i = 0; i < n; ++i) {
         const izb_linear_args& a = probs[i];
         SkinnyProblem& q = out[i];
         std::memset(&q, 0, sizeof(q));
-        const int K = static_cast<int>(a.K);
-        // Largest k-chunk (multiple of the format's aligned unit) whose stage fits the target;
-        // at least enough for every k-slice of the CTA to have one inner unit.
-        int kc = unit;
-        const int kmin = std::min(K, std::max(unit, fmt_unit(fmt) * ks));
-        for (int cand = unit; cand <= K; cand += unit) {
-            const int sz = tile_rows * w_stride_for(fmt, fmt_bytes(fmt, cand)) + mp * x_stride_for(fmt, cand);
-            if (cand <= kmin || sz <= stage_target) kc = cand; else break;
-        }
-        q.w = static_cast<const uint8_t*>(a.w);
-        q.x = static_cast<const __nv_bfloat16*>(a.x);
+        const int K = static_cast<int>(a.K), N = static_cast<int>(a.N), M = static_cast<int>(a.M);
+        const BoxGeom bg = box_geom(fmt, K);
+        const int boxes_total = K / bg.kbox;
+        const int box_stage = tile_rows * bg.w_row_bytes + (bg.kbox / 64) * mp * 128;
+        // k-boxes per stage: fill the stage target, keep every k-slice busy, divide the row evenly
+        int nb = std::max(1, std::min(boxes_total, stage_target / box_stage));
+        const int units_per_box = fmt == IZB_W_BF16 ? 1 : fmt == IZB_W_Q8_0 ? 4 : bg.kbox / 256;
+        while (nb * units_per_box < ks && nb < boxes_total && (nb + 1) * box_stage <= 2 * stage_target) ++nb;
+        while (nb > 1 && boxes_total % nb != 0) --nb;
+        nb = std::min(nb, 256);
+
         q.y = a.y;
         q.bias = static_cast<const __nv_bfloat16*>(a.bias);
-        q.row_bytes = fmt_bytes(fmt, K);
-        q.N = static_cast<int>(a.N);
-        q.K = K;
-        q.M = static_cast<int>(a.M);
-        q.ldx = static_cast<int>(a.ldx);
+        q.N = N; q.K = K; q.M = M;
         q.ldy = static_cast<int>(a.ldy);
         q.tile_start = tile_cursor;
-        q.kc = kc;
-        q.n_chunks = (K + kc - 1) / kc;
-        q.chunk_bytes = fmt_bytes(fmt, kc);
-        q.w_stride = w_stride_for(fmt, q.chunk_bytes);
-        q.x_stride = x_stride_for(fmt, kc);
-        q.x_off = (tile_rows * q.w_stride + 127) / 128 * 128;
-        stage_bytes = std::max(stage_bytes, (q.x_off + mp * q.x_stride + 127) / 128 * 128);
-        tile_cursor += (q.N + tile_rows - 1) / tile_rows;
+        q.nb = nb;
+        q.kbox = bg.kbox;
+        q.n_chunks = (boxes_total + nb - 1) / nb;
+        q.w_row_bytes = bg.w_row_bytes;
+        q.w_box_bytes = tile_rows * bg.w_row_bytes;
+        q.x_off = (nb * q.w_box_bytes + 1023) / 1024 * 1024;
+        const int x_bytes = nb * (bg.kbox / 64) * mp * 128;
+        q.stage_tx = nb * q.w_box_bytes + x_bytes;
+        stage_bytes = std::max(stage_bytes, (q.x_off + x_bytes + 1023) / 1024 * 1024);
+        tile_cursor += (N + tile_rows - 1) / tile_rows;
+
+        // weights: [k-box][row][elements of one box row]
+        int rc;
+        if (fmt == IZB_W_BF16) {
+            const uint64_t dims[3] = {64, static_cast<uint64_t>(N), static_cast<uint64_t>(boxes_total)};
+            const uint64_t strides[2] = {static_cast<uint64_t>(K) * 2, 128};
+            const uint32_t box[3] = {64, static_cast<uint32_t>(tile_rows), static_cast<uint32_t>(nb)};
+            rc = tma_encode(&q.tmap_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.w, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+        } else {
+            const uint64_t row_bytes = fmt == IZB_W_Q8_0 ? static_cast<uint64_t>(K) / 32 * 34
+                                                         : static_cast<uint64_t>(K) / 256 * 144;
+            const uint32_t words = static_cast<uint32_t>(bg.w_row_bytes / 4);
+            const uint64_t dims[3] = {words, static_cast<uint64_t>(N), static_cast<uint64_t>(boxes_total)};
+            const uint64_t strides[2] = {row_bytes, static_cast<uint64_t>(bg.w_row_bytes)};
+            const uint32_t box[3] = {words, static_cast<uint32_t>(tile_rows), static_cast<uint32_t>(nb)};
+            rc = tma_encode(&q.tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, a.w, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_NONE);
+        }
+        if (rc != IZB_OK) return rc;
+        // activations: [k/64][token][64 bf16]; rows past M read as zero
+        {
+            const uint64_t dims[3] = {64, static_cast<uint64_t>(M), static_cast<uint64_t>(K / 64)};
+            const uint64_t strides[2] = {static_cast<uint64_t>(a.ldx) * 2, 128};
+            const uint32_t box[3] = {64, static_cast<uint32_t>(mp), static_cast<uint32_t>(nb * (bg.kbox / 64))};
+            rc = tma_encode(&q.tmap_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.x, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc != IZB_OK) return rc;
+        }
     }
 
-    const int red_bytes = ks > 1 ? 2 * (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
-    const int budget = ctx->max_smem_optin / ctas_per_sm - 1024 - static_cast<int>(sizeof(SkinnyShared));
+    const int red_raw = ks > 1 ? 2 * (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
+    const int red_bytes = (red_raw + 1023) / 1024 * 1024;
     int n_stages = (budget - red_bytes) / stage_bytes;
     const int forced_stages = env_int("IZB_SKINNY_STAGES", 0);
     if (forced_stages) n_stages = forced_stages;
@@ -626,7 +648,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     if (n_stages < 2) {
         // A single stage pair must still fit one CTA per SM.
         n_stages = 2;
-        if (red_bytes + 2 * stage_bytes > ctx->max_smem_optin - 1024) return IZB_ERR_UNSUPPORTED;
+        if (red_bytes + 2 * stage_bytes > ctx->max_smem_optin - 2048) return IZB_ERR_UNSUPPORTED;
     }
 
     std::memset(hdr, 0, sizeof(*hdr));
@@ -640,7 +662,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     hdr->n_stages = n_stages;
     hdr->stage_bytes = stage_bytes;
     hdr->red_bytes = red_bytes;
-    hdr->smem_bytes = red_bytes + n_stages * stage_bytes;
+    hdr->smem_bytes = red_bytes + n_stages * stage_bytes + 1024;  // slack to align the ring to 1024 bytes
     hdr->grid = std::min(tile_cursor, max_grid);
     hdr->y_dtype = y_dtype;
     return IZB_OK;
@@ -649,10 +671,9 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
 int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev_probs,
                   const SkinnyProblem* single) {
     if (h.magic != SK_PLAN_MAGIC) return IZB_ERR_BAD_ARG;
-    SkinnyProblem dummy;
-    std::memset(&dummy, 0, sizeof(dummy));
-    const SkinnyProblem& s = single ? *single : dummy;
     if (!dev_probs && !single) return IZB_ERR_BAD_ARG;
+    static const SkinnyProblem dummy = {};
+    const SkinnyProblem& s = single ? *single : dummy;
     switch (h.fmt) {
         case IZB_W_BF16: return launch_fmt<IZB_W_BF16>(ctx, stream, h, dev_probs, s);
         case IZB_W_Q8_0: return launch_fmt<IZB_W_Q8_0>(ctx, stream, h, dev_probs, s);

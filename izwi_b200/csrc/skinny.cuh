@@ -1,16 +1,18 @@
 // Small-M (decode) linear layers: persistent weight-streaming kernel.
 //
 // One CTA = 1 producer warp + 4 consumer warps.  The producer streams raw
-// weight rows (bf16, or GGML Q8_0 / Q4_K blocks exactly as stored) and the
-// matching activation slice into a shared-memory ring with 1-D bulk copies
-// (TMA engine) signalled on mbarriers; it runs ahead across tile and problem
-// boundaries, so HBM stays busy while consumers finish a tile.  Consumers
-// dequantise in registers and feed mma.sync m16n8k16 (bf16, fp32 accumulate)
-// with the weight rows as the 16-row operand and up to 8*NT tokens as the
-// 8-column operand.  The k order inside an mma step is permuted freely (the
-// same permutation on both operands), which is what lets each lane build its
-// fragment from the words it loaded without any shuffles.
+// weight tiles (bf16, or GGML Q8_0 / Q4_K blocks exactly as stored) and the
+// matching activation slice into a shared-memory ring with tiled TMA copies
+// (one 3-D box per operand per stage) signalled on mbarriers; it runs ahead
+// across tile and problem boundaries, so HBM stays busy while consumers finish
+// a tile.  Consumers dequantise in registers and feed mma.sync m16n8k16 (bf16,
+// fp32 accumulate) with 16 weight rows as the row operand and up to 8*NT tokens
+// as the column operand.  The k order inside an mma step is permuted freely
+// (the same permutation on both operands), which lets each lane build its
+// fragment from the words it loaded without shuffles.
 #pragma once
+
+#include <cuda.h>
 
 #include "izb_common.cuh"
 
@@ -19,28 +21,26 @@ namespace izb {
 constexpr int SK_CONSUMER_WARPS = 4;
 constexpr int SK_THREADS = 32 * (SK_CONSUMER_WARPS + 1);
 constexpr int SK_MAX_STAGES = 8;
-constexpr uint32_t SK_PLAN_MAGIC = 0x495A4231u;  // "IZB1"
+constexpr uint32_t SK_PLAN_MAGIC = 0x495A4232u;  // "IZB2"
 
-struct alignas(16) SkinnyProblem {
-    const uint8_t* w;
-    const __nv_bfloat16* x;
+struct alignas(64) SkinnyProblem {
+    CUtensorMap tmap_w;  // weights viewed as [k-box][row][bytes of one k-box of a row]
+    CUtensorMap tmap_x;  // activations viewed as [k/64][token][64 bf16], 128-byte swizzle
     void* y;
     const __nv_bfloat16* bias;
-    long long row_bytes;  // bytes of one weight row in global memory
-    int N, K, M;
-    int ldx, ldy;
+    int N, K, M, ldy;
     int tile_start;   // global id of this problem's first row tile
-    int kc;           // k values per pipeline stage
-    int n_chunks;     // ceil(K / kc)
-    int chunk_bytes;  // bytes of a full k-chunk of one weight row
-    int w_stride;     // shared-memory bytes between weight rows of a stage
-    int x_stride;     // shared-memory bytes between activation rows of a stage
+    int n_chunks;     // pipeline stages per row tile
+    int nb;           // weight k-boxes per stage
+    int kbox;         // k values per weight box
+    int w_row_bytes;  // shared-memory bytes per weight row inside one box
+    int w_box_bytes;  // TILE_ROWS * w_row_bytes
     int x_off;        // byte offset of the activation region inside a stage
-    int pad_[3];
+    int stage_tx;     // bytes one full stage delivers (both boxes)
 };
-static_assert(sizeof(SkinnyProblem) == 112, "SkinnyProblem layout");
+static_assert(sizeof(SkinnyProblem) == 320, "SkinnyProblem layout");
 
-struct alignas(16) SkinnyPlanHeader {
+struct alignas(64) SkinnyPlanHeader {
     uint32_t magic;
     int fmt, nt, rt, ks;
     int n_probs, total_tiles;
