@@ -215,10 +215,13 @@ class CpuStack:
         return n, dt
 
 
+LAYERS_OVERRIDE = None  # --layers: a shorter stack, for profiler captures only
+
+
 def make_stack(workload: str, device):
     from izwi_b200 import workloads as wl
     fmt, m = WORKLOADS[workload]
-    return wl.make_linear_stack(wl.QWEN3_0_6B, fmt, m, device, WEIGHT_SEED, ACT_SEED)
+    return wl.make_linear_stack(wl.QWEN3_0_6B, fmt, m, device, WEIGHT_SEED, ACT_SEED, layers=LAYERS_OVERRIDE)
 
 
 def measure_case(workload: str, device, steps: int, warmup: int, peak: float):
@@ -389,7 +392,11 @@ def main():
     ap.add_argument("--case-steps", type=int, default=300)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cases", action="store_true")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="shorter stack for profiler captures (the reported line is then not the benchmark)")
     args = ap.parse_args()
+    global LAYERS_OVERRIDE
+    LAYERS_OVERRIDE = args.layers
     if args.impl == "reference":
         run_reference(args)
     else:

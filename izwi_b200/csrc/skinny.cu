@@ -12,17 +12,32 @@ __device__ __forceinline__ float half_bits_to_f32(uint32_t h) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
 }
 
-// Four int8 in a word -> two bf16x2 registers holding the exact integers.
-// byte ^ 0x80 is q+128 as an unsigned byte; placed in the low mantissa bits of
-// 2^23 it reads as 8388608 + q + 128, and one subtraction leaves q.
-__device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t& p01, uint32_t& p23) {
+// Four int8 in a word -> two f16x2 registers holding the exact integers.
+// byte ^ 0x80 is q+128 as an unsigned byte; under the high byte 0x64 it reads as the fp16
+// value 1024 + q + 128 (fp16 has a unit step from 1024 to 2048), and one packed subtraction
+// of 1152 leaves q.
+__device__ __forceinline__ void s8x4_to_f16x4(uint32_t w, uint32_t& p01, uint32_t& p23) {
     const uint32_t u = w ^ 0x80808080u;
-    const float f0 = __uint_as_float(prmt(u, 0x4B000000u, 0x7440)) - 8388736.0f;
-    const float f1 = __uint_as_float(prmt(u, 0x4B000000u, 0x7441)) - 8388736.0f;
-    const float f2 = __uint_as_float(prmt(u, 0x4B000000u, 0x7442)) - 8388736.0f;
-    const float f3 = __uint_as_float(prmt(u, 0x4B000000u, 0x7443)) - 8388736.0f;
-    p01 = pack_bf16x2(f0, f1);
-    p23 = pack_bf16x2(f2, f3);
+    const uint32_t h01 = prmt(u, 0x64646464u, 0x5140), h23 = prmt(u, 0x64646464u, 0x7362);
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p01) : "r"(h01), "r"(0x64806480u));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p23) : "r"(h23), "r"(0x64806480u));
+}
+
+// A bf16 pair -> the same two values as an fp16 pair.  Exact for 2^-24 <= |x| <= 65504 (bf16
+// carries 8 significant bits, fp16 11); larger magnitudes saturate to +-65504.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t b) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(b & 0xFFFF0000u)), "f"(__uint_as_float(b << 16)));
+    return r;
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t c) {
@@ -83,7 +98,9 @@ __device__ __forceinline__ void stage_bf16(float (&acc)[RT][NT][4], uint32_t wba
 // A pair is 68 bytes = 17 aligned words:
 //   word 0 = [d0 | q0[0..1]], words 1..7 = q0[2..29], word 8 = [q0[30..31] | d1], words 9..16 = q1[0..31].
 // Block 0's codes sit half a word off, so each logical word is funnelled out of two neighbours.
-// The integer codes go through the tensor core exactly; the block scale is applied in fp32.
+// The integer codes go through the tensor core exactly as fp16 (an int8 -> fp16 lift costs a
+// third of the int8 -> bf16 one), against activations converted bf16 -> fp16 on the fly; the
+// block scale is applied in fp32.
 template <int NT, int RT, int KS>
 __device__ __forceinline__ void stage_q8_0(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase,
                                            const SkinnyProblem& P, int rowbase, int ks, int g, int t) {
@@ -92,10 +109,23 @@ __device__ __forceinline__ void stage_q8_0(float (&acc)[RT][NT][4], uint32_t wba
     for (int u = ks; u < units; u += KS) {
         const uint32_t wbox = wbase + static_cast<uint32_t>((u >> 2) * P.w_box_bytes + (u & 3) * 68);
         const uint32_t xchunk = xbase + static_cast<uint32_t>(u * (NT * 1024));
-        uint32_t a[RT][4][4];  // [tile][step][a0..a3]
-        float d[RT][2][2];     // [tile][block][row a / row b]
+        // activations of this pair for every token group, converted once and reused by all row tiles;
+        // step s covers k = 16 s + 4 t .. +3 of the pair: byte 32 s + 8 t of the 128-byte token row
+        uint2 xv[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t xr = xchunk + static_cast<uint32_t>((nt * 8 + pg) * 128 + (t & 1) * 8);
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint2 v = lds64(xr + static_cast<uint32_t>(((2 * s + (t >> 1)) ^ pg) << 4));
+                xv[nt][s].x = bf16x2_to_f16x2(v.x);
+                xv[nt][s].y = bf16x2_to_f16x2(v.y);
+            }
+        }
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) {
+            uint32_t a[4][4];  // [step][a0..a3]
+            float d[2][2];     // [block][row a / row b]
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const uint32_t wr = wbox + static_cast<uint32_t>((rowbase + rt * 16 + g + half * 8) * 272);
@@ -104,34 +134,26 @@ __device__ __forceinline__ void stage_q8_0(float (&acc)[RT][NT][4], uint32_t wba
                 const uint32_t h0 = lds32(wr + 16 + 4 * t), h1 = lds32(wr + 20 + 4 * t);
                 const uint32_t q2 = lds32(wr + 36 + 4 * t), q3 = lds32(wr + 52 + 4 * t);
                 const uint32_t q0 = prmt(l0, l1, 0x5432), q1 = prmt(h0, h1, 0x5432);
-                d[rt][0][half] = half_bits_to_f32(w0);
-                d[rt][1][half] = half_bits_to_f32(w8 >> 16);
-                s8x4_to_bf16x4(q0, a[rt][0][half], a[rt][0][half + 2]);
-                s8x4_to_bf16x4(q1, a[rt][1][half], a[rt][1][half + 2]);
-                s8x4_to_bf16x4(q2, a[rt][2][half], a[rt][2][half + 2]);
-                s8x4_to_bf16x4(q3, a[rt][3][half], a[rt][3][half + 2]);
+                d[0][half] = half_bits_to_f32(w0);
+                d[1][half] = half_bits_to_f32(w8 >> 16);
+                s8x4_to_f16x4(q0, a[0][half], a[0][half + 2]);
+                s8x4_to_f16x4(q1, a[1][half], a[1][half + 2]);
+                s8x4_to_f16x4(q2, a[2][half], a[2][half + 2]);
+                s8x4_to_f16x4(q3, a[3][half], a[3][half + 2]);
             }
-        }
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            // step s covers k = 16 s + 4 t .. +3 of the pair: byte 32 s + 8 t of the 128-byte token row
-            const uint32_t xr = xchunk + static_cast<uint32_t>((nt * 8 + pg) * 128 + (t & 1) * 8);
-            uint2 xv[4];
-#pragma unroll
-            for (int s = 0; s < 4; ++s) xv[s] = lds64(xr + static_cast<uint32_t>(((2 * s + (t >> 1)) ^ pg) << 4));
-#pragma unroll
-            for (int rt = 0; rt < RT; ++rt) {
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
                     float tmp[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_bf16_16816(tmp, a[rt][2 * b][0], a[rt][2 * b][1], a[rt][2 * b][2], a[rt][2 * b][3], xv[2 * b].x,
-                                   xv[2 * b].y);
-                    mma_bf16_16816(tmp, a[rt][2 * b + 1][0], a[rt][2 * b + 1][1], a[rt][2 * b + 1][2],
-                                   a[rt][2 * b + 1][3], xv[2 * b + 1].x, xv[2 * b + 1].y);
-                    acc[rt][nt][0] = fmaf(d[rt][b][0], tmp[0], acc[rt][nt][0]);
-                    acc[rt][nt][1] = fmaf(d[rt][b][0], tmp[1], acc[rt][nt][1]);
-                    acc[rt][nt][2] = fmaf(d[rt][b][1], tmp[2], acc[rt][nt][2]);
-                    acc[rt][nt][3] = fmaf(d[rt][b][1], tmp[3], acc[rt][nt][3]);
+                    mma_f16_16816(tmp, a[2 * b][0], a[2 * b][1], a[2 * b][2], a[2 * b][3], xv[nt][2 * b].x,
+                                  xv[nt][2 * b].y);
+                    mma_f16_16816(tmp, a[2 * b + 1][0], a[2 * b + 1][1], a[2 * b + 1][2], a[2 * b + 1][3],
+                                  xv[nt][2 * b + 1].x, xv[nt][2 * b + 1].y);
+                    acc[rt][nt][0] = fmaf(d[b][0], tmp[0], acc[rt][nt][0]);
+                    acc[rt][nt][1] = fmaf(d[b][0], tmp[1], acc[rt][nt][1]);
+                    acc[rt][nt][2] = fmaf(d[b][1], tmp[2], acc[rt][nt][2]);
+                    acc[rt][nt][3] = fmaf(d[b][1], tmp[3], acc[rt][nt][3]);
                 }
             }
         }
@@ -346,8 +368,7 @@ __global__ void __launch_bounds__(SK_THREADS)
     uint32_t phase = 0;
     bool ok = true;
     int p = 0;
-    int tile_parity = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_parity ^= 1) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) ++p;
         const SkinnyProblem& P = plist[p];
         const int row0 = (tile - P.tile_start) * TILE_ROWS;
@@ -384,10 +405,8 @@ __global__ void __launch_bounds__(SK_THREADS)
 
         if constexpr (KS > 1) {
             // k-slices 1..KS-1 park their partial sums in shared memory; slice 0 adds them up.
-            // Two buffers alternate by tile so one barrier per tile is enough.
-            float* buf = red + tile_parity * ((KS - 1) * RG * ACC * 32);
             if (ks > 0) {
-                float* dst = buf + ((ks - 1) * RG + rg) * ACC * 32 + lane;
+                float* dst = red + ((ks - 1) * RG + rg) * ACC * 32 + lane;
 #pragma unroll
                 for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
@@ -399,7 +418,7 @@ __global__ void __launch_bounds__(SK_THREADS)
             if (ks == 0) {
 #pragma unroll
                 for (int s = 1; s < KS; ++s) {
-                    const float* src = buf + ((s - 1) * RG + rg) * ACC * 32 + lane;
+                    const float* src = red + ((s - 1) * RG + rg) * ACC * 32 + lane;
 #pragma unroll
                     for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
@@ -408,6 +427,7 @@ __global__ void __launch_bounds__(SK_THREADS)
                             for (int i = 0; i < 4; ++i) acc[rt][nt][i] += src[((rt * NT + nt) * 4 + i) * 32];
                 }
             }
+            named_bar_sync(2, SK_CONSUMER_WARPS * 32);  // the buffer is free for the next tile
         }
 
         if (ks == 0 && ok) {
@@ -472,18 +492,30 @@ int launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, con
     return IZB_OK;
 }
 
+template <int FMT, int NT, int RT>
+int launch_ks(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+              const SkinnyProblem& single) {
+    switch (h.ks) {
+        case 1:
+            if constexpr (RT <= 2) return launch_one<FMT, NT, RT, 1>(ctx, stream, h, dev, single);
+            return IZB_ERR_UNSUPPORTED;
+        case 2: return launch_one<FMT, NT, RT, 2>(ctx, stream, h, dev, single);
+        case 4: return launch_one<FMT, NT, RT, 4>(ctx, stream, h, dev, single);
+        default: return IZB_ERR_UNSUPPORTED;
+    }
+}
+
 template <int FMT, int NT>
 int launch_cfg(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
                const SkinnyProblem& single) {
-    if (h.rt == 2 && h.ks == 1) {
-        if constexpr (NT <= 2) return launch_one<FMT, NT, 2, 1>(ctx, stream, h, dev, single);
-        return IZB_ERR_UNSUPPORTED;
-    }
-    if (h.rt != 1) return IZB_ERR_UNSUPPORTED;
-    switch (h.ks) {
-        case 1: return launch_one<FMT, NT, 1, 1>(ctx, stream, h, dev, single);
-        case 2: return launch_one<FMT, NT, 1, 2>(ctx, stream, h, dev, single);
-        case 4: return launch_one<FMT, NT, 1, 4>(ctx, stream, h, dev, single);
+    switch (h.rt) {
+        case 1: return launch_ks<FMT, NT, 1>(ctx, stream, h, dev, single);
+        case 2:
+            if constexpr (NT <= 4) return launch_ks<FMT, NT, 2>(ctx, stream, h, dev, single);
+            return IZB_ERR_UNSUPPORTED;
+        case 4:
+            if constexpr (NT <= 2) return launch_ks<FMT, NT, 4>(ctx, stream, h, dev, single);
+            return IZB_ERR_UNSUPPORTED;
         default: return IZB_ERR_UNSUPPORTED;
     }
 }
@@ -544,7 +576,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const int nt = max_m <= 8 ? 1 : max_m <= 16 ? 2 : max_m <= 32 ? 4 : 8;
     const int mp = nt * 8;
 
-    const int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", 2));
+    // measured best residency: three CTAs per SM for Q8_0 (most ALU work per byte), two otherwise
+    const int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", fmt == IZB_W_Q8_0 ? 3 : 2));
     const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
     const int max_grid = ctx->sm_count * ctas_per_sm;
     const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_cast<int>(sizeof(SkinnyShared));
@@ -559,22 +592,37 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         return worst;
     };
 
-    // Largest row tile that leaves every CTA a few tiles to balance with and room for >= 3 stages.
-    struct Cand { int rt, ks, rows; };
-    const Cand cands[4] = {{2, 1, 128}, {1, 1, 64}, {1, 2, 32}, {1, 4, 16}};
-    int pick = 3;
+    // Row tile = 16 * RT * (4 / KS) rows: RT row tiles per warp share every converted activation
+    // fragment, KS warps split k.  Candidates in order of preference per format; the first that
+    // leaves every CTA a few tiles to balance with and room for two stages wins, else the
+    // smallest tile (most CTAs busy on a single small problem).
+    struct Cand { int rt, ks; };
+    static const Cand pref_q8[] = {{2, 2}, {2, 1}, {1, 1}, {1, 2}, {1, 4}};
+    static const Cand pref_q4[] = {{2, 1}, {2, 2}, {1, 1}, {1, 2}, {1, 4}};
+    static const Cand pref_bf[] = {{2, 1}, {1, 1}, {1, 2}, {1, 4}};
+    const Cand* pref = fmt == IZB_W_Q8_0 ? pref_q8 : fmt == IZB_W_Q4_K ? pref_q4 : pref_bf;
+    const int n_pref = fmt == IZB_W_BF16 ? 4 : 5;
+    int rt = 1, ks = 4;
+    const int forced_rt = env_int("IZB_SKINNY_RT", 0), forced_ks = env_int("IZB_SKINNY_KS", 0);
     const int forced_rows = env_int("IZB_SKINNY_TILE_ROWS", 0);
-    for (int c = 0; c < 4; ++c) {
-        if (cands[c].rt == 2 && nt > 2) continue;
-        if (forced_rows) {
-            if (cands[c].rows == forced_rows) { pick = c; break; }
-            continue;
+    if (forced_rt && forced_ks) {
+        rt = forced_rt;
+        ks = forced_ks;
+        if (rt * nt > 8 || (rt == 4 && ks == 1)) return IZB_ERR_UNSUPPORTED;
+    } else {
+        for (int c = 0; c < n_pref; ++c) {
+            const int rows = 16 * pref[c].rt * (SK_CONSUMER_WARPS / pref[c].ks);
+            if (pref[c].rt * nt > 8) continue;
+            if (forced_rows) {
+                if (rows == forced_rows) { rt = pref[c].rt; ks = pref[c].ks; break; }
+                continue;
+            }
+            int64_t tiles = 0;
+            for (int i = 0; i < n; ++i) tiles += (probs[i].N + rows - 1) / rows;
+            if (tiles >= 2LL * max_grid && 2 * min_stage(rows) <= budget) { rt = pref[c].rt; ks = pref[c].ks; break; }
         }
-        int64_t tiles = 0;
-        for (int i = 0; i < n; ++i) tiles += (probs[i].N + cands[c].rows - 1) / cands[c].rows;
-        if (tiles >= 4LL * max_grid && 3 * min_stage(cands[c].rows) <= budget) { pick = c; break; }
     }
-    const int rt = cands[pick].rt, ks = cands[pick].ks, tile_rows = cands[pick].rows;
+    const int tile_rows = 16 * rt * (SK_CONSUMER_WARPS / ks);
     const int rg = SK_CONSUMER_WARPS / ks;
 
     int stage_bytes = 0, tile_cursor = 0;
@@ -639,7 +687,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         }
     }
 
-    const int red_raw = ks > 1 ? 2 * (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
+    const int red_raw = ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
     const int red_bytes = (red_raw + 1023) / 1024 * 1024;
     int n_stages = (budget - red_bytes) / stage_bytes;
     const int forced_stages = env_int("IZB_SKINNY_STAGES", 0);

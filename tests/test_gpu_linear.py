@@ -42,13 +42,31 @@ def test_ragged_shapes(cuda, fmt, m, n, k):
     run_linear(cuda, fmt, m, n, k, seed=m * 1000 + n)
 
 
-@pytest.mark.parametrize("tile_rows", ["16", "32", "64", "128"])
+@pytest.mark.parametrize("rt,ks", [(1, 1), (1, 2), (1, 4), (2, 1), (2, 2), (2, 4), (4, 2), (4, 4)])
 @pytest.mark.parametrize("fmt", ["bf16", "q8_0", "q4_k"])
-def test_every_tile_configuration(cuda, fmt, tile_rows, monkeypatch):
-    """Each row-tile / k-split variant of the streaming kernel, forced in turn."""
-    monkeypatch.setenv("IZB_SKINNY_TILE_ROWS", tile_rows)
-    for m in (2, 12):
-        run_linear(cuda, fmt, m, 336, 1536, seed=int(tile_rows) + m)
+def test_every_tile_configuration(cuda, fmt, rt, ks, monkeypatch):
+    """Each (row tiles per warp, k-split) variant of the streaming kernel, forced in turn,
+    for every token-group count it is compiled for."""
+    monkeypatch.setenv("IZB_SKINNY_RT", str(rt))
+    monkeypatch.setenv("IZB_SKINNY_KS", str(ks))
+    for m in (2, 12, 20, 40):
+        if rt * ((m + 7) // 8 if m <= 16 else (4 if m <= 32 else 8)) > 8:
+            continue
+        run_linear(cuda, fmt, m, 336, 1536, seed=rt * 10 + ks + m)
+
+
+def test_q8_0_large_activations_stay_exact(cuda):
+    """The Q8_0 path lifts bf16 activations to fp16; that is exact up to |x| = 65504."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(12)
+    n, k, m = 128, 512, 3
+    raw, wf = make_weight_np("q8_0", n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (m, k)) * np.array([[1.0], [900.0], [2.0e4]]))
+    assert np.abs(x).max() < 65504
+    got = ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight("q8_0", raw, cuda), "q8_0", n=n, k=k,
+                     out_dtype=torch.float32)
+    want = o.linear(x, wf)
+    assert np.abs(to_np(got) - want).max() <= 1e-4 * np.abs(want).max()
 
 
 def test_small_k_chunks_and_two_stages(cuda, monkeypatch):
