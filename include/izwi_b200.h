@@ -70,6 +70,15 @@ int32_t izb_quantized_storage_bytes(int32_t wfmt, int64_t rows, int64_t cols, si
 int32_t izb_dequantize(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void* raw,
                        int64_t n_elems, int32_t out_dtype, void* out);
 
+/* Element-wise function fused into the output of a linear layer. */
+typedef enum izb_epilogue {
+    IZB_EPI_NONE = 0,
+    IZB_EPI_GELU = 1,   /* exact erf GELU: Whisper `mlp_linear1` + GELU (whisper/model.rs:311-317) */
+    IZB_EPI_SILU = 2,   /* x*sigmoid(x): FastConformer feed-forward (parakeet/asr/mod.rs:766-772) */
+    IZB_EPI_SWIGLU = 3  /* W = [gate; up] rows: y[:, j] = silu(gate_j) * up_j, y has N/2 columns:
+                           `Qwen3Mlp::forward` gate/up + silu-mul in one pass (qwen3/core.rs:1787-1795) */
+} izb_epilogue;
+
 /* One linear layer.  Replaces `impl Module for Qwen3Projection::forward`
  * (qwen3/core.rs:791-832): Dense -> `Linear::forward` (:794), Quantized ->
  * `QMatMul::forward` (:812) with the dtype casts around it folded away
@@ -85,8 +94,14 @@ typedef struct izb_linear_args {
     int64_t ldx, ldy;  /* row strides in elements */
     void* workspace;   /* NULL unless izb_linear_workspace_bytes() > 0 */
     size_t workspace_bytes;
+    int32_t epilogue;  /* izb_epilogue fused after the bias add */
+    int32_t reserved_;
 } izb_linear_args;
 
+/* M <= 32 (or <= 64 for the block formats) runs the weight-streaming kernel; larger M runs the
+ * tcgen05/TMEM GEMM.  Block-quantised weights with M > 64 are first dequantised to bf16 into
+ * `workspace` (N*K*2 bytes, see izb_linear_workspace_bytes); without a workspace they are
+ * processed 64 token rows at a time by the streaming kernel instead. */
 size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K);
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args);
 

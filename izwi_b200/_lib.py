@@ -19,6 +19,7 @@ IZB_ERR_NO_DEVICE = -5
 
 IZB_BF16, IZB_F32 = 0, 1
 IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K = 0, 1, 2
+IZB_EPI_NONE, IZB_EPI_GELU, IZB_EPI_SILU, IZB_EPI_SWIGLU = 0, 1, 2, 3
 
 
 class LinearArgs(C.Structure):
@@ -28,6 +29,7 @@ class LinearArgs(C.Structure):
         ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
         ("ldx", C.c_int64), ("ldy", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("epilogue", C.c_int32), ("reserved_", C.c_int32),
     ]
 
 

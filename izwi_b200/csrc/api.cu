@@ -3,6 +3,7 @@
 #include <new>
 
 #include "izb_common.cuh"
+#include "gemm_tc.cuh"
 #include "skinny.cuh"
 
 namespace izb {
@@ -169,7 +170,9 @@ int32_t izb_ctx_check(izb_ctx* ctx, izb_stream stream) {
     int host[IZB_STATUS_WORDS] = {0};
     IZB_CUDA_TRY(cudaMemcpyAsync(host, ctx->d_status, sizeof(host), cudaMemcpyDeviceToHost, s));
     IZB_CUDA_TRY(cudaStreamSynchronize(s));
-    if (host[0] != 0) {
+    bool any = false;
+    for (int i = 0; i < IZB_STATUS_WORDS; ++i) any = any || host[i] != 0;
+    if (any) {
         IZB_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(host), s));
         IZB_CUDA_TRY(cudaStreamSynchronize(s));
         return IZB_ERR_TIMEOUT;
@@ -246,17 +249,47 @@ int32_t izb_silu_mul(izb_ctx* ctx, izb_stream stream, const void* gate, const vo
     return IZB_OK;
 }
 
+// Above this many token rows the tcgen05 GEMM takes over from the weight-streaming kernel.
+static constexpr int64_t kStreamMaxM_bf16 = 32;
+static constexpr int64_t kStreamMaxM_quant = 64;
+
 size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K) {
-    (void)wfmt; (void)M; (void)N; (void)K;
+    if ((wfmt == IZB_W_Q8_0 || wfmt == IZB_W_Q4_K) && M > kStreamMaxM_quant && N > 0 && K > 0)
+        return static_cast<size_t>(N) * static_cast<size_t>(K) * 2;
     return 0;
 }
 
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args) {
     if (!ctx || !args) return IZB_ERR_BAD_ARG;
     if (args->M < 0 || args->N < 0 || args->K < 0) return IZB_ERR_BAD_ARG;
+    if (args->epilogue < IZB_EPI_NONE || args->epilogue > IZB_EPI_SWIGLU) return IZB_ERR_BAD_ARG;
     if (args->M == 0 || args->N == 0) return IZB_OK;
     if (args->K == 0) return IZB_ERR_UNSUPPORTED;
+    if (args->M > INT32_MAX || args->N > INT32_MAX || args->K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool quant = args->wfmt == IZB_W_Q8_0 || args->wfmt == IZB_W_Q4_K;
+    if (!quant && args->wfmt != IZB_W_BF16) return IZB_ERR_BAD_ARG;
+
+    const void* w_dense = args->w;
+    bool use_gemm = !quant && (args->M > kStreamMaxM_bf16 || args->epilogue != IZB_EPI_NONE);
+    if (quant && (args->M > kStreamMaxM_quant || args->epilogue != IZB_EPI_NONE)) {
+        const size_t need = static_cast<size_t>(args->N) * static_cast<size_t>(args->K) * 2;
+        if (args->workspace && args->workspace_bytes >= need && izb_aligned(args->workspace, 16)) {
+            const int rc = izb_dequantize(ctx, stream, args->wfmt, args->w, args->N * args->K, IZB_BF16, args->workspace);
+            if (rc != IZB_OK) return rc;
+            w_dense = args->workspace;
+            use_gemm = true;
+        } else if (args->epilogue != IZB_EPI_NONE) {
+            return IZB_ERR_BAD_ARG;  // a fused epilogue over block-quantised weights needs the workspace
+        }
+    }
+    if (use_gemm) {
+        if (!args->x || !args->y || !w_dense) return IZB_ERR_BAD_ARG;
+        if (args->ldx < args->K) return IZB_ERR_BAD_ARG;
+        return gemm_tc_launch(ctx, s, args->x, args->ldx, w_dense, args->bias, args->y, args->ldy, args->y_dtype,
+                              static_cast<int>(args->M), static_cast<int>(args->N), static_cast<int>(args->K),
+                              args->epilogue, nullptr, 1);
+    }
     // Token rows are processed 64 at a time by the weight-streaming kernel.
     const size_t ybytes = args->y_dtype == IZB_F32 ? 4 : 2;
     for (int64_t m0 = 0; m0 < args->M; m0 += 64) {
@@ -264,8 +297,8 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
         a.M = args->M - m0 < 64 ? args->M - m0 : 64;
         a.x = static_cast<const uint8_t*>(args->x) + static_cast<size_t>(m0) * args->ldx * 2;
         a.y = static_cast<uint8_t*>(args->y) + static_cast<size_t>(m0) * args->ldy * ybytes;
+        alignas(64) SkinnyProblem prob;
         SkinnyPlanHeader hdr;
-        SkinnyProblem prob;
         int rc = skinny_plan_build(ctx, &a, 1, &hdr, &prob);
         if (rc != IZB_OK) return rc;
         rc = skinny_launch(ctx, s, hdr, nullptr, &prob);

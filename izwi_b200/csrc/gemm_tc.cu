@@ -1,0 +1,421 @@
+// Dense bf16 GEMM on tcgen05 tensor cores with TMEM accumulators (see gemm_tc.cuh).
+#include <algorithm>
+#include <cstring>
+
+#include "gemm_tc.cuh"
+#include "tma.cuh"
+
+namespace izb {
+
+constexpr int GT_BM = 128;       // rows of X per tile = TMEM lanes
+constexpr int GT_BK = 64;        // k per pipeline stage = one 128-byte swizzle row of bf16
+constexpr int GT_UMMA_K = 16;    // k per tcgen05.mma (bf16)
+constexpr int GT_THREADS = 192;  // producer warp, MMA warp, 4 epilogue warps
+constexpr int GT_MAX_STAGES = 8;
+constexpr int GT_MAX_EXPERTS = 512;
+
+struct GemmShared {
+    unsigned long long full[GT_MAX_STAGES];
+    unsigned long long empty[GT_MAX_STAGES];
+    unsigned long long tmem_full[2];
+    unsigned long long tmem_empty[2];
+    unsigned long long drain;
+    uint32_t tmem_base;
+    int abort_flag;
+    int tile_prefix[GT_MAX_EXPERTS + 1];  // grouped: first m-tile of each expert
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------
+__device__ __forceinline__ void tc_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile stored as rows of 128 bytes under the
+// 128-byte swizzle: groups of 8 rows are 1024 bytes apart; k advances inside the swizzle row.
+__device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;          // stride between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;                  // descriptor version of this architecture
+    d |= static_cast<uint64_t>(2) << 61;                  // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = bn.
+__host__ __device__ inline uint32_t umma_idesc_bf16(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+           (static_cast<uint32_t>(GT_BM >> 4) << 24);
+}
+
+struct TileCoord {
+    int m0;        // first row of X
+    int rows_end;  // rows at or past this are not stored
+    int n_blk;     // column block (in units of the tile's output columns)
+    int expert;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, const GemmParams& p, const int* prefix) {
+    TileCoord c;
+    const int mt = tile % m_tiles;
+    c.n_blk = tile / m_tiles;
+    if (p.seg_offsets == nullptr) {
+        c.expert = 0;
+        c.m0 = mt * GT_BM;
+        c.rows_end = p.M;
+    } else {
+        int lo = 0, hi = p.n_experts;  // last expert whose first tile is <= mt
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (prefix[mid] <= mt) lo = mid; else hi = mid;
+        }
+        c.expert = lo;
+        c.m0 = p.seg_offsets[lo] + (mt - prefix[lo]) * GT_BM;
+        c.rows_end = p.seg_offsets[lo + 1];
+    }
+    return c;
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long row, int col0, const float (&v)[32]) {
+    // 32 consecutive output columns of one row
+    if (p.y_dtype == IZB_F32) {
+        float* dst = static_cast<float*>(p.y) + row * p.ldy + col0;
+        if (col0 + 32 <= p.n_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+            for (int i = 0; i < 32 && col0 + i < p.n_out; ++i) dst[i] = v[i];
+        }
+    } else {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.y) + row * p.ldy + col0;
+        if (col0 + 32 <= p.n_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 q;
+                q.x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
+                q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+                q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+                q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+                reinterpret_cast<uint4*>(dst)[i] = q;
+            }
+        } else {
+            for (int i = 0; i < 32 && col0 + i < p.n_out; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(GT_THREADS, 1)
+    gemm_tc_kernel(const __grid_constant__ GemmParams p, int n_stages, int* status) {
+    extern __shared__ __align__(1024) uint8_t dyn_smem[];
+    __shared__ GemmShared sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bn = p.bn;
+    const bool swiglu = p.epilogue == GEMM_EPI_SWIGLU;
+    const int out_cols = swiglu ? bn / 2 : bn;  // output columns one tile produces
+    const uint32_t a_bytes = GT_BM * GT_BK * 2, b_bytes = static_cast<uint32_t>(bn) * GT_BK * 2;
+    const uint32_t stage_bytes = a_bytes + b_bytes;
+    const uint32_t smem0 = smem_u32(dyn_smem);
+    const int n_kb = (p.K + GT_BK - 1) / GT_BK;
+    volatile int* abort_flag = &sh.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < n_stages; ++s) {
+            mbar_init(smem_u32(&sh.full[s]), 1);
+            mbar_init(smem_u32(&sh.empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&sh.tmem_full[a]), 1);
+            mbar_init(smem_u32(&sh.tmem_empty[a]), 4);
+        }
+        mbar_init(smem_u32(&sh.drain), 1);
+        sh.abort_flag = 0;
+        mbar_fence_init();
+        // grouped: m-tile prefix over the expert segments
+        if (p.seg_offsets != nullptr) {
+            int acc = 0;
+            for (int e = 0; e < p.n_experts; ++e) {
+                sh.tile_prefix[e] = acc;
+                acc += (p.seg_offsets[e + 1] - p.seg_offsets[e] + GT_BM - 1) / GT_BM;
+            }
+            sh.tile_prefix[p.n_experts] = acc;
+        }
+    }
+    if (warp == 1) tc_alloc(smem_u32(&sh.tmem_base), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    const uint32_t tmem_base = sh.tmem_base;
+    const int m_tiles = p.seg_offsets ? sh.tile_prefix[p.n_experts] : (p.M + GT_BM - 1) / GT_BM;
+    const int n_tiles = (p.n_out + out_cols - 1) / out_cols;
+    const int total_tiles = m_tiles * n_tiles;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            long long issued = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileCoord c = tile_coord(tile, m_tiles, p, sh.tile_prefix);
+                const int n0 = c.n_blk * out_cols;
+                for (int kb = 0; kb < n_kb; ++kb) {
+                    if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fbar = smem_u32(&sh.full[stage]);
+                    const uint32_t sa = smem0 + static_cast<uint32_t>(stage) * stage_bytes, sb = sa + a_bytes;
+                    mbar_expect_tx(fbar, stage_bytes);
+                    tma_load_2d(sa, &p.tmap_a, kb * GT_BK, c.m0, fbar);
+                    if (swiglu) {
+                        tma_load_3d(sb, &p.tmap_b, kb * GT_BK, n0, c.expert, fbar);
+                        tma_load_3d(sb + b_bytes / 2, &p.tmap_b, kb * GT_BK, p.n_out + n0, c.expert, fbar);
+                    } else {
+                        tma_load_3d(sb, &p.tmap_b, kb * GT_BK, n0, c.expert, fbar);
+                    }
+                    ++issued;
+                    if (++stage == n_stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // let copies still in flight land before shared memory is released
+                const long long first = issued > n_stages ? issued - n_stages : 0;
+                for (long long f = first; f < issued; ++f) {
+                    const uint32_t bar = smem_u32(&sh.full[f % n_stages]);
+                    const uint32_t par = static_cast<uint32_t>((f / n_stages) & 1);
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bar, par)) {
+                        if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(bn);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+                if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[acc]), acc_phase ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
+                for (int kb = 0; kb < n_kb; ++kb) {
+                    if (!mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem0 + static_cast<uint32_t>(stage) * stage_bytes, sb = sa + a_bytes;
+                    const uint64_t adesc = umma_desc_k_major_sw128(sa), bdesc = umma_desc_k_major_sw128(sb);
+#pragma unroll
+                    for (int k = 0; k < GT_BK / GT_UMMA_K; ++k) {
+                        // 16 bf16 = 32 bytes further along the swizzle row: +2 in 16-byte units
+                        tc_mma_f16(d_tmem, adesc + static_cast<uint64_t>(2 * k), bdesc + static_cast<uint64_t>(2 * k), idesc,
+                                   (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&sh.empty[stage]));  // slot free once these MMAs have read it
+                    if (++stage == n_stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(smem_u32(&sh.tmem_full[acc]));  // accumulator complete
+            }
+            // every MMA issued by this thread has retired before TMEM is released
+            tc_commit(smem_u32(&sh.drain));
+            const long long t0 = clock64();
+            while (!mbar_try_wait(smem_u32(&sh.drain), 0)) {
+                if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                    ok = false;
+                    break;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lane group = warp % 4 ----------------
+        const int lg = warp & 3;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int acc = it & 1;
+            const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+            const TileCoord c = tile_coord(tile, m_tiles, p, sh.tile_prefix);
+            if (ok && !mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_phase, abort_flag)) ok = false;
+            if (!ok) break;
+            tc_fence_after();
+            const long long row = static_cast<long long>(c.m0) + lg * 32 + lane;
+            const bool row_ok = row < c.rows_end;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(acc * 256);
+            const __nv_bfloat16* bias = p.bias ? p.bias + static_cast<long long>(c.expert) * p.N : nullptr;
+            const int col_base = c.n_blk * out_cols;
+            for (int cc = 0; cc < out_cols; cc += 32) {
+                float v[32];
+                tc_ld_32x32(t_row + static_cast<uint32_t>(cc), v);
+                const int col0 = col_base + cc;
+                if (swiglu) {
+                    float u[32];
+                    tc_ld_32x32(t_row + static_cast<uint32_t>(bn / 2 + cc), u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float gate = v[i], up = u[i];
+                        if (bias && col0 + i < p.n_out) {
+                            gate += __bfloat162float(bias[col0 + i]);
+                            up += __bfloat162float(bias[p.n_out + col0 + i]);
+                        }
+                        v[i] = silu(gate) * up;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float x = v[i];
+                        if (bias && col0 + i < p.n_out) x += __bfloat162float(bias[col0 + i]);
+                        if (p.epilogue == GEMM_EPI_GELU) x = gelu_erf(x);
+                        else if (p.epilogue == GEMM_EPI_SILU) x = silu(x);
+                        v[i] = x;
+                    }
+                }
+                if (row_ok && col0 < p.n_out) store_row_chunk(p, row, col0, v);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tc_dealloc(tmem_base, 512);
+    }
+    if ((!ok || sh.abort_flag) && lane == 0) atomicExch(status, 2);
+}
+
+int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long ldx, const void* w, const void* bias,
+                   void* y, long long ldy, int y_dtype, int M, int N, int K, int epilogue, const int* seg_offsets,
+                   int n_experts) {
+    if (!ctx || !x || !w || !y) return IZB_ERR_BAD_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || n_experts <= 0) return IZB_ERR_BAD_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0 || ldx < K) return IZB_ERR_UNSUPPORTED;
+    if (!izb_aligned(x, 16) || !izb_aligned(w, 16)) return IZB_ERR_BAD_ARG;
+    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
+    if (epilogue < GEMM_EPI_NONE || epilogue > GEMM_EPI_SWIGLU) return IZB_ERR_BAD_ARG;
+    if (seg_offsets && n_experts > GT_MAX_EXPERTS) return IZB_ERR_UNSUPPORTED;
+    if (!seg_offsets && n_experts != 1) return IZB_ERR_BAD_ARG;
+    const bool swiglu = epilogue == GEMM_EPI_SWIGLU;
+    if (swiglu && N % 2 != 0) return IZB_ERR_BAD_ARG;
+    const int n_out = swiglu ? N / 2 : N;
+    if (ldy < n_out) return IZB_ERR_BAD_ARG;
+
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    // Accumulator width: the widest tile that still gives every SM work.
+    const long long m_tiles = seg_offsets ? (static_cast<long long>(M) + GT_BM - 1) / GT_BM + n_experts
+                                          : (static_cast<long long>(M) + GT_BM - 1) / GT_BM;
+    int bn = 256;
+    while (bn > 64) {
+        const int oc = swiglu ? bn / 2 : bn;
+        if (m_tiles * ((n_out + oc - 1) / oc) >= ctx->sm_count) break;
+        bn >>= 1;
+    }
+    const int out_cols = swiglu ? bn / 2 : bn;
+    p.bn = bn;
+    p.y = y;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.seg_offsets = seg_offsets;
+    p.ldy = ldy;
+    p.M = M; p.N = N; p.K = K;
+    p.n_experts = n_experts;
+    p.epilogue = epilogue;
+    p.y_dtype = y_dtype;
+    p.n_out = n_out;
+
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
+        const uint32_t box[2] = {GT_BK, GT_BM};
+        const int rc = tma_encode(&p.tmap_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box,
+                                  CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != IZB_OK) return rc;
+    }
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(n_experts)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(K) * 2, static_cast<uint64_t>(N) * static_cast<uint64_t>(K) * 2};
+        const uint32_t box[3] = {GT_BK, static_cast<uint32_t>(swiglu ? bn / 2 : bn), 1};
+        const int rc = tma_encode(&p.tmap_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, w, dims, strides, box,
+                                  CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != IZB_OK) return rc;
+    }
+
+    const int stage_bytes = (GT_BM + bn) * GT_BK * 2;
+    int n_stages = std::min(GT_MAX_STAGES, (ctx->max_smem_optin - 4096 - static_cast<int>(sizeof(GemmShared))) / stage_bytes);
+    if (n_stages < 2) return IZB_ERR_UNSUPPORTED;
+    const int smem_bytes = n_stages * stage_bytes + 1024;
+    static std::atomic<int> smem_set[16];
+    const int slot = ctx->device & 15;
+    if (smem_set[slot].load(std::memory_order_relaxed) < smem_bytes) {
+        IZB_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        smem_set[slot].store(smem_bytes, std::memory_order_relaxed);
+    }
+    const long long tiles_bound = m_tiles * ((n_out + out_cols - 1) / out_cols);
+    const int grid = static_cast<int>(std::min<long long>(tiles_bound, ctx->sm_count));
+    gemm_tc_kernel<<<grid, GT_THREADS, smem_bytes, stream>>>(p, n_stages, ctx->d_status + 1);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+}  // namespace izb

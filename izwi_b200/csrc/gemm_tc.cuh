@@ -1,0 +1,47 @@
+// Dense bf16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), plain and grouped.
+//
+//   Y[M, N] = X[M, K] . W[N, K]^T (+ bias) with an optional fused epilogue.
+//
+// Persistent, warp-specialised, one CTA per SM:
+//   warp 0      TMA producer: 128x64 tiles of X and BNx64 tiles of W into a shared-memory ring
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (128 x BN x 16) into one of two
+//               TMEM accumulators, commits ring slots back to the producer and accumulators to
+//               the epilogue through mbarriers
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes), bias /
+//               activation in fp32, bf16 or fp32 stores
+// Both operands are K-major with the 128-byte swizzle; no cluster multicast anywhere.
+#pragma once
+
+#include <cuda.h>
+
+#include "izb_common.cuh"
+
+namespace izb {
+
+enum GemmEpilogue : int {
+    GEMM_EPI_NONE = 0,
+    GEMM_EPI_GELU = 1,    // exact (erf) GELU, Whisper fc1
+    GEMM_EPI_SILU = 2,    // x * sigmoid(x), FastConformer feed-forward
+    GEMM_EPI_SWIGLU = 3,  // W = [gate ; up] rows: out[:, j] = silu(gate_j) * up_j, N_out = N / 2
+};
+
+struct GemmParams {
+    CUtensorMap tmap_a;  // X  viewed as [rows][K], box 64 x 128, 128-byte swizzle
+    CUtensorMap tmap_b;  // W  viewed as [expert][N][K], box 64 x BN(/2) x 1, 128-byte swizzle
+    void* y;
+    const __nv_bfloat16* bias;  // [N] (per expert: [E][N]) or null
+    const int* seg_offsets;     // grouped: [E + 1] row offsets of the expert segments, else null
+    long long ldy;
+    int M, N, K;                // grouped: M = total rows of X
+    int n_experts;              // 1 when not grouped
+    int epilogue;
+    int y_dtype;
+    int bn;                     // accumulator width in columns: 64, 128 or 256
+    int n_out;                  // columns of Y
+};
+
+int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long ldx, const void* w, const void* bias,
+                   void* y, long long ldy, int y_dtype, int M, int N, int K, int epilogue, const int* seg_offsets,
+                   int n_experts);
+
+}  // namespace izb

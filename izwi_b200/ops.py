@@ -66,8 +66,13 @@ def dequantize(raw: torch.Tensor, fmt: str, n_elems: int, dtype: torch.dtype = t
     return out
 
 
+EPILOGUE = {None: L.IZB_EPI_NONE, "none": L.IZB_EPI_NONE, "gelu": L.IZB_EPI_GELU, "silu": L.IZB_EPI_SILU,
+            "swiglu": L.IZB_EPI_SWIGLU}
+
+
 def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: torch.Tensor,
-                bias: torch.Tensor | None = None) -> L.LinearArgs:
+                bias: torch.Tensor | None = None, epilogue: str | None = None,
+                workspace: torch.Tensor | None = None) -> L.LinearArgs:
     assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
     assert y.dim() == 2 and y.stride(1) == 1 and y.shape[0] == x.shape[0]
     a = L.LinearArgs()
@@ -76,16 +81,20 @@ def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: t
     a.x, a.w, a.bias, a.y = x.data_ptr(), w.data_ptr(), (0 if bias is None else bias.data_ptr()), y.data_ptr()
     a.M, a.N, a.K = x.shape[0], n, k
     a.ldx, a.ldy = x.stride(0), y.stride(0)
-    a.workspace, a.workspace_bytes = None, 0
+    a.workspace = None if workspace is None else workspace.data_ptr()
+    a.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    a.epilogue = EPILOGUE[epilogue]
     return a
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = None, k: int | None = None,
            bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
-           out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """Y = X . W^T (+ bias).  `x` may have any number of leading dimensions
+           out_dtype: torch.dtype = torch.bfloat16, epilogue: str | None = None,
+           workspace: torch.Tensor | None | bool = True) -> torch.Tensor:
+    """Y = epilogue(X . W^T + bias).  `x` may have any number of leading dimensions
     (flattened to M like the reference's Linear); `w` is [N, K] bf16 or the raw
-    GGML bytes of N rows of K values."""
+    GGML bytes of N rows of K values.  `workspace=True` lets this wrapper provide
+    the scratch buffer the library asks for (it never allocates itself)."""
     if fmt == "bf16":
         n, k = w.shape
     assert n is not None and k is not None
@@ -93,11 +102,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = 
     x2 = x.reshape(-1, x.shape[-1])
     if x2.shape[1] != k:
         raise ValueError(f"linear: input dim {x2.shape[1]} != weight in-dim {k}")
-    y = out if out is not None else torch.empty(x2.shape[0], n, device=x.device, dtype=out_dtype)
-    a = linear_args(x2, w, fmt, n, k, y.reshape(-1, n), bias)
+    n_out = n // 2 if epilogue == "swiglu" else n
+    y = out if out is not None else torch.empty(x2.shape[0], n_out, device=x.device, dtype=out_dtype)
+    if workspace is True:
+        need = L.lib().izb_linear_workspace_bytes(WFMT[fmt], x2.shape[0], n, k)
+        if epilogue not in (None, "none") and fmt != "bf16":
+            need = n * k * 2
+        workspace = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
+    elif workspace is False:
+        workspace = None
+    a = linear_args(x2, w, fmt, n, k, y.reshape(-1, n_out), bias, epilogue, workspace)
     ctx = Context.get(x.device.index)
     L.check(L.lib().izb_linear(ctx.handle, _stream(), C.byref(a)), "izb_linear")
-    return y.reshape(*lead, n)
+    return y.reshape(*lead, n_out)
 
 
 def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
