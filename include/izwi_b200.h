@@ -35,7 +35,8 @@ typedef enum izb_status {
     IZB_ERR_UNSUPPORTED = -2, /* shape or dtype outside what the kernels cover */
     IZB_ERR_LAUNCH = -3,      /* CUDA runtime refused the launch or the copy */
     IZB_ERR_TIMEOUT = -4,     /* a bounded device-side wait gave up */
-    IZB_ERR_NO_DEVICE = -5    /* no sm_100 device / driver entry point missing */
+    IZB_ERR_NO_DEVICE = -5,   /* no sm_100 device / driver entry point missing */
+    IZB_ERR_SCRATCH_TOO_SMALL = -6 /* the problem needs more than the library's fixed scratch array */
 } izb_status;
 
 typedef enum izb_dtype { IZB_BF16 = 0, IZB_F32 = 1 } izb_dtype;
@@ -126,6 +127,30 @@ int32_t izb_linear_group_plan(izb_ctx* ctx, const izb_linear_args* problems, int
                               void* host_plan, size_t host_plan_bytes);
 int32_t izb_linear_group_launch(izb_ctx* ctx, izb_stream stream, const void* host_plan,
                                 const void* dev_plan);
+
+/* Size of the scratch array built into the library image (bytes). */
+#define IZB_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+size_t izb_static_scratch_bytes(void);
+
+/* Prefill-size linear layer over Q8_0 / Q4_K weights for callers that cannot hand over a
+ * workspace and must not trigger a device allocation: host runtimes that gave the whole device to
+ * their own memory pool at start-up, and latency-sensitive audio threads for which a cudaMalloc
+ * (which can synchronise the whole device) in the middle of a request is not acceptable.
+ * Same result as izb_linear with a workspace: the weights are dequantised to bf16 and multiplied
+ * on the tensor cores; the bf16 copy goes into a fixed IZB_STATIC_SCRATCH_BYTES array that every
+ * GPU loading this library holds until the process exits.  x is [M, K] bf16 contiguous, y is
+ * [M, N] (N/2 columns with IZB_EPI_SWIGLU) contiguous.
+ *   - N*K*2 bytes must fit the array, else IZB_ERR_SCRATCH_TOO_SMALL and nothing is launched.
+ *   - calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - the first call on a device looks up the array's device address (a one-off host-side
+ *     query); make that first call outside any stream capture.
+ *   - all calls on a device share the one array and it keeps the previous call's contents (each
+ *     call rewrites the part it reads, so nothing needs clearing): two calls that may overlap
+ *     on the GPU (different streams) race and must be ordered by the caller.
+ * This entry point has no counterpart in the reference. */
+int32_t izb_linear_quantized_static(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void* x,
+                                    const void* w, const void* bias, void* y, int32_t y_dtype,
+                                    int64_t M, int64_t N, int64_t K, int32_t epilogue);
 
 /* out = silu(gate) * up, fp32 math, bf16 storage; gate/up/out are [rows, cols]
  * views with their own row strides so the two halves of a fused gate/up

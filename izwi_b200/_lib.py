@@ -16,6 +16,7 @@ IZB_ERR_UNSUPPORTED = -2
 IZB_ERR_LAUNCH = -3
 IZB_ERR_TIMEOUT = -4
 IZB_ERR_NO_DEVICE = -5
+IZB_ERR_SCRATCH_TOO_SMALL = -6
 
 IZB_BF16, IZB_F32 = 0, 1
 IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K = 0, 1, 2
@@ -53,6 +54,9 @@ _SIGNATURES = {
     "izb_linear_group_plan_bytes": (C.c_size_t, [C.c_int32]),
     "izb_linear_group_plan": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_int32, C.c_void_p, C.c_size_t]),
     "izb_linear_group_launch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "izb_static_scratch_bytes": (C.c_size_t, []),
+    "izb_linear_quantized_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
     "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
 }

@@ -120,6 +120,7 @@ const char* izb_status_string(int32_t status) {
         case IZB_ERR_LAUNCH: return "CUDA launch or copy failed";
         case IZB_ERR_TIMEOUT: return "a bounded device-side wait gave up";
         case IZB_ERR_NO_DEVICE: return "no usable sm_100 device";
+        case IZB_ERR_SCRATCH_TOO_SMALL: return "problem exceeds the library's fixed scratch array";
         default: return "unknown status";
     }
 }
