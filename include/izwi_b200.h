@@ -160,6 +160,51 @@ int32_t izb_linear_quantized_static(izb_ctx* ctx, izb_stream stream, int32_t wfm
 int32_t izb_silu_mul(izb_ctx* ctx, izb_stream stream, const void* gate, const void* up, void* out,
                      int64_t rows, int64_t cols, int64_t ld_gate, int64_t ld_up, int64_t ld_out);
 
+/* ---- top-k mixture-of-experts feed-forward ------------------------------------------------
+ * The reference has no MoE code (no counterpart to cite); the rules are this library's own:
+ * experts are picked by router logit, equal logits resolve to the lowest expert id, the weights
+ * are the softmax over the picked logits, permuted rows are ordered by expert and then by
+ * ascending (token, slot), and the combine adds slots in ascending order in fp32. */
+
+/* logits [T, E] fp32 -> idx [T, k] int32 (descending logit) and weights [T, k] fp32. */
+int32_t izb_moe_topk(izb_ctx* ctx, izb_stream stream, const void* logits, int64_t T, int64_t E,
+                     int32_t top_k, void* idx_out, void* weights_out);
+/* idx [pairs] int32 -> offsets [E + 1], perm [pairs] (pair id landing in each permuted row) and
+ * inv [pairs] (permuted row of each pair); pair id = token * k + slot. */
+int32_t izb_moe_permute(izb_ctx* ctx, izb_stream stream, const void* idx, int64_t pairs, int64_t E,
+                        void* offsets_out, void* perm_out, void* inv_out);
+/* x_perm[r, :] = x[perm[r] / k, :], bf16 rows of H values. */
+int32_t izb_moe_gather(izb_ctx* ctx, izb_stream stream, const void* x, int64_t ldx, const void* perm,
+                       int32_t top_k, int64_t rows, int64_t H, void* x_perm);
+/* For every expert e: y[offsets[e]:offsets[e+1]] = epilogue(x_perm[same rows] . w[e]^T), w is
+ * [E, N, K] bf16; tcgen05 GEMM over row tiles that never cross an expert boundary. */
+int32_t izb_moe_grouped_gemm(izb_ctx* ctx, izb_stream stream, const void* x_perm, const void* w,
+                             const void* offsets, void* y, int32_t y_dtype, int64_t rows, int64_t N,
+                             int64_t K, int64_t E, int32_t epilogue);
+/* y[t, :] = sum_slot weights[t, slot] * y_perm[inv[t*k + slot], :]  (bf16 in, fp32 sum, bf16 out). */
+int32_t izb_moe_combine(izb_ctx* ctx, izb_stream stream, const void* y_perm, const void* inv,
+                        const void* weights, int64_t T, int32_t top_k, int64_t H, void* y);
+
+typedef struct izb_moe_args {
+    const void* x;            /* [T, H] bf16 */
+    const void* w_router;     /* [E, H] bf16 */
+    const void* router_bias;  /* [E] bf16 or NULL */
+    const void* w_gate_up;    /* [E, 2*I, H] bf16: gate rows then up rows of each expert */
+    const void* w_down;       /* [E, H, I] bf16 */
+    void* y;                  /* [T, H] bf16 */
+    int64_t T, H, I, E;
+    int32_t top_k;
+    int32_t reserved_;
+    void* workspace;          /* izb_moe_workspace_bytes(), 256-byte aligned */
+    size_t workspace_bytes;
+} izb_moe_args;
+
+size_t izb_moe_workspace_bytes(int64_t T, int64_t H, int64_t I, int64_t E, int32_t top_k);
+/* router -> top-k -> permute -> gather -> grouped gate/up GEMM with SwiGLU -> grouped down GEMM ->
+ * combine, all on `stream`.  The workspace starts with logits [T,E] fp32, idx [T,k] int32 and
+ * weights [T,k] fp32 (each region 256-byte aligned), which callers may read back. */
+int32_t izb_moe_forward(izb_ctx* ctx, izb_stream stream, const izb_moe_args* args);
+
 #ifdef __cplusplus
 }
 #endif

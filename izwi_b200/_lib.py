@@ -34,6 +34,16 @@ class LinearArgs(C.Structure):
     ]
 
 
+class MoeArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w_router", C.c_void_p), ("router_bias", C.c_void_p), ("w_gate_up", C.c_void_p),
+        ("w_down", C.c_void_p), ("y", C.c_void_p),
+        ("T", C.c_int64), ("H", C.c_int64), ("I", C.c_int64), ("E", C.c_int64),
+        ("top_k", C.c_int32), ("reserved_", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 _SIGNATURES = {
     "izb_version": (C.c_int32, []),
     "izb_status_string": (C.c_char_p, [C.c_int32]),
@@ -57,6 +67,17 @@ _SIGNATURES = {
     "izb_static_scratch_bytes": (C.c_size_t, []),
     "izb_linear_quantized_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                                 C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "izb_moe_topk": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "izb_moe_permute": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                                    C.c_void_p]),
+    "izb_moe_gather": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int64,
+                                   C.c_int64, C.c_void_p]),
+    "izb_moe_grouped_gemm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "izb_moe_combine": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                    C.c_int64, C.c_void_p]),
+    "izb_moe_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "izb_moe_forward": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(MoeArgs)]),
     "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
 }

@@ -1,0 +1,312 @@
+// Mixture-of-experts glue around the grouped GEMM: top-k routing, the stable (expert, token)
+// permutation, row gather and the weighted combine.  The rules (this project's specification,
+// the reference has no MoE code): experts are chosen by logit, ties go to the lowest expert id;
+// weights are the softmax over the chosen logits; permuted rows are ordered by expert and, inside
+// one expert, by ascending (token, slot); the combine adds slots in ascending slot order in fp32.
+#include <cstring>
+
+#include "gemm_tc.cuh"
+#include "izb_common.cuh"
+
+namespace izb {
+
+constexpr int MOE_MAX_EXPERTS = 512;
+constexpr int MOE_MAX_TOPK = 32;
+
+// One warp per token.  Each lane keeps experts lane, lane+32, ...; k rounds of warp arg-max.
+__global__ void moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int* __restrict__ idx,
+                                float* __restrict__ wts) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_block) {
+        const float* row = logits + static_cast<long long>(t) * E;
+        float v[MOE_MAX_EXPERTS / 32];
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) {
+            const int e = lane + 32 * i;
+            v[i] = e < E ? row[e] : -INFINITY;
+        }
+        float first = 0.f, sum = 0.f, mine = 0.f;
+        for (int j = 0; j < k; ++j) {
+            float best = -INFINITY;
+            int best_e = 0x7FFFFFFF;
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) {
+                const int e = lane + 32 * i;
+                if (e < E && (v[i] > best || (v[i] == best && e < best_e))) {
+                    best = v[i];
+                    best_e = e;
+                }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+                const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, off);
+                if (ob > best || (ob == best && oe < best_e)) {
+                    best = ob;
+                    best_e = oe;
+                }
+            }
+            if (best_e == 0x7FFFFFFF) best_e = j < E ? j : 0;  // every remaining logit is -inf or NaN
+            if ((best_e & 31) == lane) {
+#pragma unroll
+                for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i)
+                    if (i == (best_e >> 5)) v[i] = -INFINITY;
+            }
+            if (j == 0) first = best;
+            const float ex = expf(best - first);
+            sum += ex;
+            if (lane == j) mine = ex;
+            if (lane == 0) idx[static_cast<long long>(t) * k + j] = best_e;
+        }
+        if (lane < k) wts[static_cast<long long>(t) * k + lane] = mine / sum;
+    }
+}
+
+// One block per expert e.  Pass 1 counts the pairs routed to experts below e (the segment start)
+// and to e; pass 2 walks the pairs in order again and hands out positions, so equal experts keep
+// ascending pair order.  No block depends on another.
+__global__ void moe_permute_kernel(const int* __restrict__ idx, int pairs, int E, int* __restrict__ offsets,
+                                   int* __restrict__ perm, int* __restrict__ inv) {
+    __shared__ int warp_sums[32];
+    __shared__ int base_s, count_s, running_s;
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+
+    int below = 0, equal = 0;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int x = idx[p];
+        below += x < e;
+        equal += x == e;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        below += __shfl_xor_sync(0xFFFFFFFFu, below, off);
+        equal += __shfl_xor_sync(0xFFFFFFFFu, equal, off);
+    }
+    if (threadIdx.x == 0) {
+        base_s = 0;
+        count_s = 0;
+    }
+    __syncthreads();
+    if (lane == 0) {
+        atomicAdd(&base_s, below);   // integer sums: order does not matter
+        atomicAdd(&count_s, equal);
+    }
+    __syncthreads();
+    const int base = base_s;
+    if (threadIdx.x == 0) {
+        offsets[e] = base;
+        if (e == E - 1) offsets[E] = base + count_s;
+        running_s = 0;
+    }
+    __syncthreads();
+
+    for (int p0 = 0; p0 < pairs; p0 += blockDim.x) {
+        const int p = p0 + threadIdx.x;
+        const bool hit = p < pairs && idx[p] == e;
+        const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
+        if (lane == 0) warp_sums[warp] = __popc(ballot);
+        __syncthreads();
+        int before = running_s;
+        for (int w = 0; w < warp; ++w) before += warp_sums[w];
+        if (hit) {
+            const int pos = base + before + __popc(ballot & ((1u << lane) - 1u));
+            perm[pos] = p;
+            inv[p] = pos;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < nwarps; ++w) tot += warp_sums[w];
+            running_s += tot;
+        }
+        __syncthreads();
+    }
+}
+
+// x_perm[r] = x[perm[r] / k], 16 bytes per thread.
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ perm, int k, int rows,
+                                  int vec_per_row, long long ldx_vec, uint4* __restrict__ out) {
+    const long long total = static_cast<long long>(rows) * vec_per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int r = static_cast<int>(i / vec_per_row), c = static_cast<int>(i % vec_per_row);
+        out[i] = x[static_cast<long long>(perm[r] / k) * ldx_vec + c];
+    }
+}
+
+// y[t] = sum over slots (ascending) of w[t, slot] * yp[inv[t*k + slot]], fp32 accumulate, 8 columns per thread.
+__global__ void moe_combine_kernel(const uint4* __restrict__ yp, const int* __restrict__ inv, const float* __restrict__ wts,
+                                   int T, int k, int vec_per_row, uint4* __restrict__ y) {
+    const long long total = static_cast<long long>(T) * vec_per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int t = static_cast<int>(i / vec_per_row), c = static_cast<int>(i % vec_per_row);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < k; ++s) {
+            const float w = wts[static_cast<long long>(t) * k + s];
+            const uint4 v = yp[static_cast<long long>(inv[static_cast<long long>(t) * k + s]) * vec_per_row + c];
+            const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[2 * j] = fmaf(w, bf16_lo_to_f32(q[j]), acc[2 * j]);
+                acc[2 * j + 1] = fmaf(w, bf16_hi_to_f32(q[j]), acc[2 * j + 1]);
+            }
+        }
+        y[i] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                          pack_bf16x2(acc[6], acc[7]));
+    }
+}
+
+static int blocks_for(const izb_ctx* ctx, long long items, int threads) {
+    const long long want = (items + threads - 1) / threads, cap = static_cast<long long>(ctx->sm_count) * 16;
+    return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace izb
+
+using namespace izb;
+
+extern "C" {
+
+int32_t izb_moe_topk(izb_ctx* ctx, izb_stream stream, const void* logits, int64_t T, int64_t E, int32_t top_k,
+                     void* idx_out, void* weights_out) {
+    if (!ctx || T < 0 || E <= 0 || top_k <= 0) return IZB_ERR_BAD_ARG;
+    if (E > MOE_MAX_EXPERTS || top_k > MOE_MAX_TOPK || top_k > E) return IZB_ERR_UNSUPPORTED;
+    if (T == 0) return IZB_OK;
+    if (!logits || !idx_out || !weights_out) return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(logits, 4) || !izb_aligned(idx_out, 4) || !izb_aligned(weights_out, 4)) return IZB_ERR_BAD_ARG;
+    const int threads = 128;
+    moe_topk_kernel<<<blocks_for(ctx, T * 32, threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float*>(logits), static_cast<int>(T), static_cast<int>(E), top_k, static_cast<int*>(idx_out),
+        static_cast<float*>(weights_out));
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_moe_permute(izb_ctx* ctx, izb_stream stream, const void* idx, int64_t pairs, int64_t E, void* offsets_out,
+                        void* perm_out, void* inv_out) {
+    if (!ctx || pairs < 0 || E <= 0) return IZB_ERR_BAD_ARG;
+    if (E > 65535 || pairs > INT32_MAX) return IZB_ERR_UNSUPPORTED;
+    if (!offsets_out || (pairs > 0 && (!idx || !perm_out || !inv_out))) return IZB_ERR_BAD_ARG;
+    moe_permute_kernel<<<static_cast<int>(E), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const int*>(idx), static_cast<int>(pairs), static_cast<int>(E), static_cast<int*>(offsets_out),
+        static_cast<int*>(perm_out), static_cast<int*>(inv_out));
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_moe_gather(izb_ctx* ctx, izb_stream stream, const void* x, int64_t ldx, const void* perm, int32_t top_k,
+                       int64_t rows, int64_t H, void* x_perm) {
+    if (!ctx || rows < 0 || H <= 0 || top_k <= 0 || ldx < H) return IZB_ERR_BAD_ARG;
+    if (rows == 0) return IZB_OK;
+    if (!x || !perm || !x_perm) return IZB_ERR_BAD_ARG;
+    if (H % 8 != 0 || ldx % 8 != 0 || !izb_aligned(x, 16) || !izb_aligned(x_perm, 16)) return IZB_ERR_UNSUPPORTED;
+    const int threads = 256;
+    moe_gather_kernel<<<blocks_for(ctx, rows * (H / 8), threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(x), static_cast<const int*>(perm), top_k, static_cast<int>(rows),
+        static_cast<int>(H / 8), ldx / 8, static_cast<uint4*>(x_perm));
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_moe_grouped_gemm(izb_ctx* ctx, izb_stream stream, const void* x_perm, const void* w, const void* offsets,
+                             void* y, int32_t y_dtype, int64_t rows, int64_t N, int64_t K, int64_t E, int32_t epilogue) {
+    if (!ctx || rows < 0 || N <= 0 || K <= 0 || E <= 0) return IZB_ERR_BAD_ARG;
+    if (rows == 0) return IZB_OK;
+    if (rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
+    if (!offsets) return IZB_ERR_BAD_ARG;
+    const int64_t n_out = epilogue == IZB_EPI_SWIGLU ? N / 2 : N;
+    return gemm_tc_launch(ctx, static_cast<cudaStream_t>(stream), x_perm, K, w, nullptr, y, n_out, y_dtype,
+                          static_cast<int>(rows), static_cast<int>(N), static_cast<int>(K), epilogue,
+                          static_cast<const int*>(offsets), static_cast<int>(E));
+}
+
+int32_t izb_moe_combine(izb_ctx* ctx, izb_stream stream, const void* y_perm, const void* inv, const void* weights,
+                        int64_t T, int32_t top_k, int64_t H, void* y) {
+    if (!ctx || T < 0 || H <= 0 || top_k <= 0) return IZB_ERR_BAD_ARG;
+    if (T == 0) return IZB_OK;
+    if (!y_perm || !inv || !weights || !y) return IZB_ERR_BAD_ARG;
+    if (H % 8 != 0 || !izb_aligned(y_perm, 16) || !izb_aligned(y, 16)) return IZB_ERR_UNSUPPORTED;
+    const int threads = 256;
+    moe_combine_kernel<<<blocks_for(ctx, T * (H / 8), threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(y_perm), static_cast<const int*>(inv), static_cast<const float*>(weights),
+        static_cast<int>(T), top_k, static_cast<int>(H / 8), static_cast<uint4*>(y));
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// whole MoE feed-forward layer out of the pieces above
+// ---------------------------------------------------------------------------
+namespace {
+struct MoeWorkspace {
+    size_t logits, idx, wts, offsets, perm, inv, x_perm, hidden, y_perm, total;
+};
+size_t align_up(size_t v) { return (v + 255) / 256 * 256; }
+MoeWorkspace moe_layout(int64_t T, int64_t H, int64_t I, int64_t E, int64_t k) {
+    MoeWorkspace w;
+    size_t at = 0;
+    const size_t pairs = static_cast<size_t>(T) * static_cast<size_t>(k);
+    w.logits = at; at = align_up(at + static_cast<size_t>(T) * E * 4);
+    w.idx = at; at = align_up(at + pairs * 4);
+    w.wts = at; at = align_up(at + pairs * 4);
+    w.offsets = at; at = align_up(at + (static_cast<size_t>(E) + 1) * 4);
+    w.perm = at; at = align_up(at + pairs * 4);
+    w.inv = at; at = align_up(at + pairs * 4);
+    w.x_perm = at; at = align_up(at + pairs * H * 2);
+    w.hidden = at; at = align_up(at + pairs * I * 2);
+    w.y_perm = at; at = align_up(at + pairs * H * 2);
+    w.total = at;
+    return w;
+}
+}  // namespace
+
+extern "C" {
+
+size_t izb_moe_workspace_bytes(int64_t T, int64_t H, int64_t I, int64_t E, int32_t top_k) {
+    if (T <= 0 || H <= 0 || I <= 0 || E <= 0 || top_k <= 0) return 0;
+    return moe_layout(T, H, I, E, top_k).total;
+}
+
+int32_t izb_moe_forward(izb_ctx* ctx, izb_stream stream, const izb_moe_args* a) {
+    if (!ctx || !a) return IZB_ERR_BAD_ARG;
+    if (a->T < 0 || a->H <= 0 || a->I <= 0 || a->E <= 0 || a->top_k <= 0) return IZB_ERR_BAD_ARG;
+    if (a->T == 0) return IZB_OK;
+    if (!a->x || !a->w_router || !a->w_gate_up || !a->w_down || !a->y || !a->workspace) return IZB_ERR_BAD_ARG;
+    const MoeWorkspace L = moe_layout(a->T, a->H, a->I, a->E, a->top_k);
+    if (a->workspace_bytes < L.total || !izb_aligned(a->workspace, 256)) return IZB_ERR_BAD_ARG;
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    const int64_t pairs = a->T * a->top_k;
+
+    izb_linear_args r;
+    memset(&r, 0, sizeof(r));
+    r.wfmt = IZB_W_BF16;
+    r.y_dtype = IZB_F32;
+    r.x = a->x; r.w = a->w_router; r.bias = a->router_bias; r.y = ws + L.logits;
+    r.M = a->T; r.N = a->E; r.K = a->H; r.ldx = a->H; r.ldy = a->E;
+    int rc = izb_linear(ctx, stream, &r);
+    if (rc != IZB_OK) return rc;
+    rc = izb_moe_topk(ctx, stream, ws + L.logits, a->T, a->E, a->top_k, ws + L.idx, ws + L.wts);
+    if (rc != IZB_OK) return rc;
+    rc = izb_moe_permute(ctx, stream, ws + L.idx, pairs, a->E, ws + L.offsets, ws + L.perm, ws + L.inv);
+    if (rc != IZB_OK) return rc;
+    rc = izb_moe_gather(ctx, stream, a->x, a->H, ws + L.perm, a->top_k, pairs, a->H, ws + L.x_perm);
+    if (rc != IZB_OK) return rc;
+    rc = izb_moe_grouped_gemm(ctx, stream, ws + L.x_perm, a->w_gate_up, ws + L.offsets, ws + L.hidden, IZB_BF16, pairs,
+                              2 * a->I, a->H, a->E, IZB_EPI_SWIGLU);
+    if (rc != IZB_OK) return rc;
+    rc = izb_moe_grouped_gemm(ctx, stream, ws + L.hidden, a->w_down, ws + L.offsets, ws + L.y_perm, IZB_BF16, pairs,
+                              a->H, a->I, a->E, IZB_EPI_NONE);
+    if (rc != IZB_OK) return rc;
+    return izb_moe_combine(ctx, stream, ws + L.y_perm, ws + L.inv, ws + L.wts, a->T, a->top_k, a->H, a->y);
+}
+
+}  // extern "C"
