@@ -205,6 +205,29 @@ size_t izb_moe_workspace_bytes(int64_t T, int64_t H, int64_t I, int64_t E, int32
  * weights [T,k] fp32 (each region 256-byte aligned), which callers may read back. */
 int32_t izb_moe_forward(izb_ctx* ctx, izb_stream stream, const izb_moe_args* args);
 
+/* ---- sharded configurations: NCCL over NVLink --------------------------------------------
+ * One process per GPU.  The reference is single-device (device ordinal fixed to 0,
+ * backends/device.rs:632-636) and has no collective call site, so there is nothing to cite.
+ * Rank 0 makes a 128-byte id, the host passes it to every rank by its own means, each rank calls
+ * izb_comm_init.  All calls of a communicator must be issued in the same order on every rank. */
+typedef struct izb_comm izb_comm;
+int32_t izb_comm_unique_id(void* out_128_bytes);
+int32_t izb_comm_init(izb_ctx* ctx, int32_t world, int32_t rank, const void* unique_id_128_bytes,
+                      izb_comm** out);
+int32_t izb_comm_destroy(izb_comm* comm);
+/* Tensor parallel: in-place sum of `count` elements over all ranks (after a row-split O or down
+ * projection). */
+int32_t izb_tp_allreduce(izb_comm* comm, izb_stream stream, void* buf, int64_t count, int32_t dtype);
+/* Every rank contributes bytes_per_rank bytes; recv holds world * bytes_per_rank (routing counts). */
+int32_t izb_comm_allgather(izb_comm* comm, izb_stream stream, const void* send, void* recv,
+                           int64_t bytes_per_rank);
+/* Expert parallel: rows of row_bytes bytes; send holds the rows for rank 0, then rank 1, ...
+ * (host_send_rows[p] of them), recv receives host_recv_rows[p] rows from each rank in rank
+ * order.  The row counts are host arrays of `world` entries. */
+int32_t izb_ep_alltoall(izb_comm* comm, izb_stream stream, const void* send,
+                        const int64_t* host_send_rows, void* recv, const int64_t* host_recv_rows,
+                        int64_t row_bytes);
+
 #ifdef __cplusplus
 }
 #endif

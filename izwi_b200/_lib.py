@@ -78,6 +78,13 @@ _SIGNATURES = {
                                     C.c_int64, C.c_void_p]),
     "izb_moe_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
     "izb_moe_forward": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(MoeArgs)]),
+    "izb_comm_unique_id": (C.c_int32, [C.c_void_p]),
+    "izb_comm_init": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "izb_comm_destroy": (C.c_int32, [C.c_void_p]),
+    "izb_tp_allreduce": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32]),
+    "izb_comm_allgather": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
+    "izb_ep_alltoall": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p,
+                                    C.POINTER(C.c_int64), C.c_int64]),
     "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
 }

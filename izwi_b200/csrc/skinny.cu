@@ -56,6 +56,12 @@ __device__ __forceinline__ uint32_t bcast_bf16x2(float v) { return pack_bf16x2(v
 __device__ __forceinline__ int perm_quad(int g) { return (g >> 1) | ((g & 1) << 2); }
 __device__ __forceinline__ int perm_pair(int g) { return ((g & 3) << 1) | (g >> 2); }
 
+// The few descriptor fields the inner loops need, copied to registers once per tile (the
+// descriptor itself lives in global or parameter memory).
+struct StageGeom {
+    int nb, kbox, w_row_bytes, w_box_bytes;
+};
+
 // ---------------------------------------------------------------------------
 // consumer inner loops: one pipeline stage
 //   wbase/xbase: shared-memory byte addresses of the stage's weight / activation regions
@@ -66,7 +72,7 @@ __device__ __forceinline__ int perm_pair(int g) { return ((g & 3) << 1) | (g >> 
 // bf16: one weight box = 64 k = [TILE_ROWS][128 bytes], swizzled like the activations.
 template <int NT, int RT, int KS>
 __device__ __forceinline__ void stage_bf16(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase,
-                                           const SkinnyProblem& P, int rowbase, int ks, int g, int t) {
+                                           const StageGeom P, int rowbase, int ks, int g, int t) {
     const int pg = perm_quad(g);
     for (int b = ks; b < P.nb; b += KS) {
         const uint32_t wbox = wbase + static_cast<uint32_t>(b * P.w_box_bytes);
@@ -103,7 +109,7 @@ __device__ __forceinline__ void stage_bf16(float (&acc)[RT][NT][4], uint32_t wba
 // block scale is applied in fp32.
 template <int NT, int RT, int KS>
 __device__ __forceinline__ void stage_q8_0(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase,
-                                           const SkinnyProblem& P, int rowbase, int ks, int g, int t) {
+                                           const StageGeom P, int rowbase, int ks, int g, int t) {
     const int pg = perm_pair(g);
     const int units = P.nb * 4;
     for (int u = ks; u < units; u += KS) {
@@ -168,7 +174,7 @@ __device__ __forceinline__ void stage_q8_0(float (&acc)[RT][NT][4], uint32_t wba
 // quad decodes the scales of sub-blocks 2t and 2t+1 and hands them round by shuffle.
 template <int NT, int RT, int KS>
 __device__ __forceinline__ void stage_q4_k(float (&acc)[RT][NT][4], uint32_t wbase, uint32_t xbase,
-                                           const SkinnyProblem& P, int rowbase, int ks, int g, int t, int lane) {
+                                           const StageGeom P, int rowbase, int ks, int g, int t, int lane) {
     const int pg = perm_quad(g);
     const int sbb = P.kbox >> 8;  // super-blocks per box
     const int nsb = P.nb * sbb;
@@ -370,10 +376,11 @@ __global__ void __launch_bounds__(SK_THREADS)
     int p = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) ++p;
-        const SkinnyProblem& P = plist[p];
-        const int row0 = (tile - P.tile_start) * TILE_ROWS;
-        const int n_chunks = P.n_chunks;
-        const uint32_t x_off = static_cast<uint32_t>(P.x_off);
+        const SkinnyProblem& PD = plist[p];
+        const int row0 = (tile - PD.tile_start) * TILE_ROWS;
+        const int n_chunks = PD.n_chunks;
+        const uint32_t x_off = static_cast<uint32_t>(PD.x_off);
+        const StageGeom P = {PD.nb, PD.kbox, PD.w_row_bytes, PD.w_box_bytes};
 
         float acc[RT][NT][4];
 #pragma unroll
@@ -434,9 +441,9 @@ __global__ void __launch_bounds__(SK_THREADS)
             // Fragment row g sits in tile row perm(g) for bf16 (swizzled tile), g otherwise;
             // fragment column n sits in token perm(n) of its group of eight.
             const int rsel = FMT == IZB_W_BF16 ? perm_quad(g) : g;
-            const int N = P.N, M = P.M, ldy = P.ldy;
-            const __nv_bfloat16* bias = P.bias;
-            void* y = P.y;
+            const int N = PD.N, M = PD.M, ldy = PD.ldy;
+            const __nv_bfloat16* bias = PD.bias;
+            void* y = PD.y;
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
 #pragma unroll

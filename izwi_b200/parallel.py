@@ -1,0 +1,239 @@
+"""Sharding of the hot path over the GPUs of one box: tensor-parallel projections with one
+all-reduce per block, expert-parallel MoE with an all-to-all each way, batch-parallel encoders.
+
+The partition arithmetic is plain Python / NumPy so it can be tested on CPU ranks; the data path
+uses the C ABI (izb_comm_*, izb_tp_allreduce, izb_ep_alltoall) and the CUDA kernels.  The
+reference is single-device, so none of this mirrors reference code.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+# ----------------------------------------------------------------------------------------------
+# partition arithmetic (no torch, no GPU)
+# ----------------------------------------------------------------------------------------------
+
+
+def split_range(n: int, parts: int, index: int) -> tuple[int, int]:
+    """Contiguous block `index` of `n` items cut into `parts` near-equal blocks (first blocks larger)."""
+    if parts <= 0 or not 0 <= index < parts:
+        raise ValueError("bad partition index")
+    base, rem = divmod(n, parts)
+    lo = index * base + min(index, rem)
+    return lo, lo + base + (1 if index < rem else 0)
+
+
+def tp_qkv_rows(q_heads: int, kv_heads: int, head_dim: int, tp: int, rank: int) -> np.ndarray:
+    """Rows of the fused [q; k; v] weight that rank `rank` owns: its query heads and the kv heads
+    they attend with (kv heads are replicated when tp exceeds their number)."""
+    if q_heads % tp != 0:
+        raise ValueError(f"{q_heads} query heads do not split {tp} ways")
+    qh = q_heads // tp
+    q_rows = np.arange(rank * qh * head_dim, (rank + 1) * qh * head_dim)
+    if kv_heads % tp == 0:
+        kh = kv_heads // tp
+        kv = np.arange(rank * kh * head_dim, (rank + 1) * kh * head_dim)
+    elif tp % kv_heads == 0:
+        head = rank // (tp // kv_heads)
+        kv = np.arange(head * head_dim, (head + 1) * head_dim)
+    else:
+        raise ValueError(f"{kv_heads} kv heads do not split or replicate {tp} ways")
+    q_total, kv_total = q_heads * head_dim, kv_heads * head_dim
+    return np.concatenate([q_rows, q_total + kv, q_total + kv_total + kv])
+
+
+def tp_gate_up_rows(intermediate: int, tp: int, rank: int) -> np.ndarray:
+    """Rows of the fused [gate; up] weight for a rank: gate_i and up_i of the same columns stay together."""
+    lo, hi = split_range(intermediate, tp, rank)
+    return np.concatenate([np.arange(lo, hi), intermediate + np.arange(lo, hi)])
+
+
+def tp_row_split_cols(k: int, tp: int, rank: int) -> tuple[int, int]:
+    """Input columns of a row-split (O / down) projection owned by a rank."""
+    return split_range(k, tp, rank)
+
+
+def ep_expert_range(n_experts: int, ep: int, rank: int) -> tuple[int, int]:
+    """Experts [lo, hi) living on a rank: contiguous blocks."""
+    if n_experts % ep != 0:
+        raise ValueError(f"{n_experts} experts do not split {ep} ways")
+    per = n_experts // ep
+    return rank * per, (rank + 1) * per
+
+
+def ep_send_rows(offsets: np.ndarray, ep: int) -> np.ndarray:
+    """Rows this rank sends to each rank, from its permuted-row offsets [E+1] (rows are ordered by
+    expert, so the rows of one destination are contiguous)."""
+    e = len(offsets) - 1
+    per = e // ep
+    return np.array([int(offsets[(r + 1) * per] - offsets[r * per]) for r in range(ep)], dtype=np.int64)
+
+
+def ep_recv_plan(all_offsets: np.ndarray, ep: int, rank: int) -> tuple[np.ndarray, np.ndarray]:
+    """From every rank's offsets [ep, E+1]: rows received from each rank, and the local expert id
+    of every received row in arrival order (source-major, expert-minor)."""
+    e = all_offsets.shape[1] - 1
+    lo, hi = ep_expert_range(e, ep, rank)
+    counts = np.diff(all_offsets, axis=1)[:, lo:hi]              # [src, local expert]
+    recv_rows = counts.sum(axis=1).astype(np.int64)
+    local_ids = np.concatenate([np.repeat(np.arange(hi - lo), counts[s]) for s in range(ep)]) if counts.sum() else \
+        np.zeros(0, np.int64)
+    return recv_rows, local_ids.astype(np.int32)
+
+
+def batch_split(batch: int, world: int, rank: int) -> tuple[int, int]:
+    """Utterances [lo, hi) a rank encodes (weights replicated, no collective)."""
+    return split_range(batch, world, rank)
+
+
+# ----------------------------------------------------------------------------------------------
+# NCCL communicator over the C ABI
+# ----------------------------------------------------------------------------------------------
+
+
+class Comm:
+    """izb_comm built from an initialised torch.distributed group (used only to pass the id)."""
+
+    def __init__(self, device_index: int):
+        import torch
+        import torch.distributed as dist
+
+        from . import _lib as L
+        from .ops import Context
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        self.ctx = Context.get(device_index)
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if self.rank == 0:
+            buf = (C.c_ubyte * 128)()
+            L.check(L.lib().izb_comm_unique_id(buf), "izb_comm_unique_id")
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        ident = ident.to(torch.device("cuda", device_index))
+        dist.broadcast(ident, src=0)
+        raw = bytes(ident.cpu().tolist())
+        handle = C.c_void_p()
+        L.check(L.lib().izb_comm_init(self.ctx.handle, self.world, self.rank, raw, C.byref(handle)), "izb_comm_init")
+        self.handle = handle
+
+    def allreduce_(self, t):
+        import torch
+
+        from . import _lib as L
+        from .ops import _ptr, _stream
+        assert t.is_contiguous()
+        code = L.IZB_F32 if t.dtype == torch.float32 else L.IZB_BF16
+        L.check(L.lib().izb_tp_allreduce(self.handle, _stream(), _ptr(t), t.numel(), code), "izb_tp_allreduce")
+        return t
+
+    def allgather_bytes(self, send, recv):
+        from . import _lib as L
+        from .ops import _ptr, _stream
+        L.check(L.lib().izb_comm_allgather(self.handle, _stream(), _ptr(send), _ptr(recv),
+                                           send.numel() * send.element_size()), "izb_comm_allgather")
+
+    def alltoall_rows(self, send, send_rows, recv, recv_rows, row_bytes: int):
+        from . import _lib as L
+        from .ops import _ptr, _stream
+        s = (C.c_int64 * self.world)(*[int(v) for v in send_rows])
+        r = (C.c_int64 * self.world)(*[int(v) for v in recv_rows])
+        L.check(L.lib().izb_ep_alltoall(self.handle, _stream(), _ptr(send), s, _ptr(recv), r, row_bytes),
+                "izb_ep_alltoall")
+
+    def close(self):
+        from . import _lib as L
+        if self.handle:
+            L.lib().izb_comm_destroy(self.handle)
+            self.handle = None
+
+
+# ----------------------------------------------------------------------------------------------
+# sharded layers (GPU)
+# ----------------------------------------------------------------------------------------------
+
+
+class TpDecoderLayer:
+    """Linear stack of one decoder layer under tensor parallelism: column-split QKV, row-split O with
+    an all-reduce, column-split gate/up (pairs kept together) with SwiGLU, row-split down with an
+    all-reduce.  Attention itself is outside this path: O takes the rank's slice of its input."""
+
+    def __init__(self, comm: Comm | None, w_qkv, w_o, w_gate_up, w_down):
+        self.comm = comm
+        self.w_qkv, self.w_o, self.w_gate_up, self.w_down = w_qkv, w_o, w_gate_up, w_down
+        self.inter_local = w_gate_up.shape[0] // 2
+
+    @classmethod
+    def from_full(cls, comm, shape, w_qkv, w_o, w_gate_up, w_down, tp: int, rank: int):
+        import torch
+        dev = w_qkv.device
+        rows = torch.from_numpy(tp_qkv_rows(shape.q_heads, shape.kv_heads, shape.head_dim, tp, rank)).to(dev)
+        gu = torch.from_numpy(tp_gate_up_rows(shape.intermediate, tp, rank)).to(dev)
+        olo, ohi = tp_row_split_cols(w_o.shape[1], tp, rank)
+        dlo, dhi = tp_row_split_cols(w_down.shape[1], tp, rank)
+        return cls(comm, w_qkv[rows].contiguous(), w_o[:, olo:ohi].contiguous(), w_gate_up[gu].contiguous(),
+                   w_down[:, dlo:dhi].contiguous())
+
+    def forward(self, x_attn_in, x_o_in, x_mlp_in):
+        """x_attn_in [M, H] -> qkv_local; x_o_in [M, K_o/tp] -> attention block output (reduced);
+        x_mlp_in [M, H] -> MLP block output (reduced)."""
+        from . import ops
+        qkv = ops.linear(x_attn_in, self.w_qkv)
+        o = ops.linear(x_o_in, self.w_o)
+        if self.comm is not None:
+            self.comm.allreduce_(o)
+        m = x_mlp_in.shape[0]
+        if m > 32:
+            hidden = ops.linear(x_mlp_in, self.w_gate_up, epilogue="swiglu")
+        else:
+            gu = ops.linear(x_mlp_in, self.w_gate_up)
+            hidden = ops.silu_mul(gu[:, : self.inter_local], gu[:, self.inter_local:])
+        down = ops.linear(hidden, self.w_down)
+        if self.comm is not None:
+            self.comm.allreduce_(down)
+        return qkv, o, down
+
+
+class EpMoeLayer:
+    """MoE feed-forward layer with the experts spread over ranks in contiguous blocks; tokens are
+    data-parallel, the router is replicated.  Rows travel to the rank that owns their expert,
+    are regrouped by local expert there, and travel back for the weighted combine."""
+
+    def __init__(self, comm: Comm, w_router, router_bias, w_gate_up_local, w_down_local, n_experts: int, top_k: int):
+        self.comm = comm
+        self.w_router, self.router_bias = w_router, router_bias
+        self.w_gate_up, self.w_down = w_gate_up_local.contiguous(), w_down_local.contiguous()
+        self.E, self.k = n_experts, top_k
+        self.H = w_router.shape[1]
+        self.E_local = self.w_gate_up.shape[0]
+
+    def forward(self, x):
+        import torch
+
+        from . import moe, ops
+        dev, ep, rank = x.device, self.comm.world, self.comm.rank
+        t = x.shape[0]
+        logits = ops.linear(x, self.w_router, bias=self.router_bias, out_dtype=torch.float32)
+        idx, wts = moe.topk(logits, self.k)
+        offsets, perm, inv = moe.permute(idx, self.E)
+        x_perm = moe.gather(x, perm, self.k)
+        # routing counts of every rank (the row counts of the exchange must be known on the host)
+        all_off = torch.empty(ep, self.E + 1, device=dev, dtype=torch.int32)
+        self.comm.allgather_bytes(offsets, all_off)
+        all_off_h = all_off.cpu().numpy()
+        send_rows = ep_send_rows(all_off_h[rank], ep)
+        recv_rows, local_ids = ep_recv_plan(all_off_h, ep, rank)
+        r_total = int(recv_rows.sum())
+        recv = torch.empty(max(r_total, 1), self.H, device=dev, dtype=torch.bfloat16)
+        self.comm.alltoall_rows(x_perm, send_rows, recv, recv_rows, self.H * 2)
+        if r_total > 0:
+            ids = torch.from_numpy(local_ids).to(dev)
+            l_off, l_perm, l_inv = moe.permute(ids, self.E_local)
+            xs = moe.gather(recv, l_perm, 1)
+            hid = moe.grouped_gemm(xs, self.w_gate_up, l_off, "swiglu")
+            ys = moe.grouped_gemm(hid, self.w_down, l_off)
+            back = moe.gather(ys, l_inv, 1)            # arrival order again
+        else:
+            back = recv
+        y_perm = torch.empty(max(t * self.k, 1), self.H, device=dev, dtype=torch.bfloat16)
+        self.comm.alltoall_rows(back, recv_rows, y_perm, send_rows, self.H * 2)
+        return moe.combine(y_perm[: t * self.k], inv, wts), idx, wts
