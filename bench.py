@@ -50,7 +50,10 @@ WEIGHT_SEED, ACT_SEED = 0, 2
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the grouped kernel, from the ncu
 # capture summarised under profiles/ (None until a capture exists for that workload).
-NCU_DRAM_BYTES_PER_LAUNCH = {}
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    # (133.85 MB read + 3.6 MB written) on an 8-layer stack, scaled to 28 layers: profiles/skinny_q8_0_m1_qwen3-0.6b-stack.md
+    "qwen3-0.6b-q8_0-m1": 481_000_000,
+}
 
 
 def load_peaks():
