@@ -17,6 +17,23 @@ NVCC_FLAGS = [
 ]
 
 
+HOST_SELFTEST = PKG_DIR / "host" / "host_selftest"
+
+
+def build_host_selftest() -> Path:
+    """The C++ host layer's own test program (links the library; rpath points back at it)."""
+    nvcc = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, "-O2", "-std=c++17", "-o", str(HOST_SELFTEST), str(PKG_DIR / "host" / "host_selftest.cpp"),
+           "-L", str(PKG_DIR), "-lizwi_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."]
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    proc = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
+    return HOST_SELFTEST
+
+
 def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
 

@@ -1,6 +1,7 @@
 // Dense bf16 GEMM on tcgen05 tensor cores with TMEM accumulators (see gemm_tc.cuh).
 #include <algorithm>
 #include <cstring>
+#include <cstdlib>
 
 #include "gemm_tc.cuh"
 #include "tma.cuh"
@@ -13,6 +14,8 @@ constexpr int GT_UMMA_K = 16;    // k per tcgen05.mma (bf16)
 constexpr int GT_THREADS = 192;  // producer warp, MMA warp, 4 epilogue warps
 constexpr int GT_MAX_STAGES = 8;
 constexpr int GT_MAX_EXPERTS = 512;
+constexpr int GT_GROUP_M = 16;  // row blocks per rasterisation band
+constexpr int GT_STAGING_PER_WARP = 32 * 128;  // 32 rows x 128 bytes of output staging per epilogue warp
 
 struct GemmShared {
     unsigned long long full[GT_MAX_STAGES];
@@ -82,6 +85,14 @@ __host__ __device__ inline uint32_t umma_idesc_bf16(int bn) {
            (static_cast<uint32_t>(GT_BM >> 4) << 24);
 }
 
+#ifdef IZB_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[4096];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define GT_TRACE(slot, it) do { if (blockIdx.x == 0 && (it) < 16) g_gemm_trace[(slot) * 16 + (it)] = gtime(); } while (0)
+#else
+#define GT_TRACE(slot, it) do { } while (0)
+#endif
+
 struct TileCoord {
     int m0;        // first row of X
     int rows_end;  // rows at or past this are not stored
@@ -89,10 +100,16 @@ struct TileCoord {
     int expert;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, const GemmParams& p, const int* prefix) {
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, int n_tiles, const GemmParams& p, const int* prefix) {
     TileCoord c;
-    const int mt = tile % m_tiles;
-    c.n_blk = tile / m_tiles;
+    // Band rasterisation: tiles are walked in bands of GT_GROUP_M row blocks, column-major inside a
+    // band, so the CTAs running at one time cover a near-square patch of the output; each X and W
+    // tile is then shared by a dozen CTAs through L2 instead of one W tile by all of them.
+    const int band_tiles = GT_GROUP_M * n_tiles;
+    const int band = tile / band_tiles, within = tile - band * band_tiles;
+    const int gm = min(GT_GROUP_M, m_tiles - band * GT_GROUP_M);
+    const int mt = band * GT_GROUP_M + within % gm;
+    c.n_blk = within / gm;
     if (p.seg_offsets == nullptr) {
         c.expert = 0;
         c.m0 = mt * GT_BM;
@@ -110,37 +127,12 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, const Gem
     return c;
 }
 
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
-
-__device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long row, int col0, const float (&v)[32]) {
-    // 32 consecutive output columns of one row
-    if (p.y_dtype == IZB_F32) {
-        float* dst = static_cast<float*>(p.y) + row * p.ldy + col0;
-        if (col0 + 32 <= p.n_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        } else {
-            for (int i = 0; i < 32 && col0 + i < p.n_out; ++i) dst[i] = v[i];
-        }
-    } else {
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.y) + row * p.ldy + col0;
-        if (col0 + 32 <= p.n_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint4 q;
-                q.x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
-                q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-                q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-                q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-                reinterpret_cast<uint4*>(dst)[i] = q;
-            }
-        } else {
-            for (int i = 0; i < 32 && col0 + i < p.n_out; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-        }
-    }
-}
 
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ GemmParams p, int n_stages, int* status) {
@@ -156,6 +148,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     const uint32_t smem0 = smem_u32(dyn_smem);
     const int n_kb = (p.K + GT_BK - 1) / GT_BK;
     volatile int* abort_flag = &sh.abort_flag;
+    const bool f32_out = p.y_dtype == IZB_F32;
+    const uint32_t stage_out = smem0 + static_cast<uint32_t>(n_stages) * stage_bytes;  // output staging after the ring
+    // 16-byte global stores need an aligned base and row stride
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (p.ldy * (f32_out ? 4 : 2)) % 16 == 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) {
@@ -196,9 +192,11 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             int stage = 0;
             uint32_t phase = 0;
             long long issued = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = tile_coord(tile, m_tiles, p, sh.tile_prefix);
+            int pit = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++pit) {
+                const TileCoord c = tile_coord(tile, m_tiles, n_tiles, p, sh.tile_prefix);
                 const int n0 = c.n_blk * out_cols;
+                GT_TRACE(0, pit);
                 for (int kb = 0; kb < n_kb; ++kb) {
                     if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
                         ok = false;
@@ -249,6 +247,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                     break;
                 }
                 tc_fence_after();
+                GT_TRACE(1, it);
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
                 for (int kb = 0; kb < n_kb; ++kb) {
                     if (!mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) {
@@ -272,6 +271,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                 }
                 if (!ok) break;
                 tc_commit(smem_u32(&sh.tmem_full[acc]));  // accumulator complete
+                GT_TRACE(2, it);
             }
             // every MMA issued by this thread has retired before TMEM is released
             tc_commit(smem_u32(&sh.drain));
@@ -290,45 +290,107 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
-            const TileCoord c = tile_coord(tile, m_tiles, p, sh.tile_prefix);
+            const TileCoord c = tile_coord(tile, m_tiles, n_tiles, p, sh.tile_prefix);
             if (ok && !mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_phase, abort_flag)) ok = false;
             if (!ok) break;
             tc_fence_after();
-            const long long row = static_cast<long long>(c.m0) + lg * 32 + lane;
-            const bool row_ok = row < c.rows_end;
+            if (warp == 2 && lane == 0) GT_TRACE(3, it);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(acc * 256);
             const __nv_bfloat16* bias = p.bias ? p.bias + static_cast<long long>(c.expert) * p.N : nullptr;
             const int col_base = c.n_blk * out_cols;
+            // Staging: each thread owns one output row, but a row-per-thread store scatters 16-byte
+            // pieces over 32 rows.  The warp parks 128 bytes per row in shared memory (16-byte chunks
+            // XOR-swizzled by row) and writes them back 8 lanes per row, i.e. whole 128-byte lines.
+            const int cols_per_flush = f32_out ? 32 : 64;
+            const uint32_t stg = stage_out + static_cast<uint32_t>(lg) * GT_STAGING_PER_WARP;
             for (int cc = 0; cc < out_cols; cc += 32) {
                 float v[32];
                 tc_ld_32x32(t_row + static_cast<uint32_t>(cc), v);
                 const int col0 = col_base + cc;
+                // The mode tests sit outside the element loops on purpose: inside, the compiler turns
+                // them into selects and evaluates erf and exp for every element of every mode.
                 if (swiglu) {
                     float u[32];
                     tc_ld_32x32(t_row + static_cast<uint32_t>(bn / 2 + cc), u);
+                    if (bias) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float gate = v[i], up = u[i];
-                        if (bias && col0 + i < p.n_out) {
-                            gate += __bfloat162float(bias[col0 + i]);
-                            up += __bfloat162float(bias[p.n_out + col0 + i]);
+                        for (int i = 0; i < 32; ++i) {
+                            if (col0 + i < p.n_out) {
+                                v[i] += __bfloat162float(bias[col0 + i]);
+                                u[i] += __bfloat162float(bias[p.n_out + col0 + i]);
+                            }
                         }
-                        v[i] = silu(gate) * up;
                     }
-                } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float x = v[i];
-                        if (bias && col0 + i < p.n_out) x += __bfloat162float(bias[col0 + i]);
-                        if (p.epilogue == GEMM_EPI_GELU) x = gelu_erf(x);
-                        else if (p.epilogue == GEMM_EPI_SILU) x = silu(x);
-                        v[i] = x;
+                    for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
+                } else {
+                    if (bias) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < p.n_out) v[i] += __bfloat162float(bias[col0 + i]);
+                    }
+                    if (p.epilogue == GEMM_EPI_GELU) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+                    } else if (p.epilogue == GEMM_EPI_SILU) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = silu(v[i]);
                     }
                 }
-                if (row_ok && col0 < p.n_out) store_row_chunk(p, row, col0, v);
+                // park this thread's 32 values in its staging row
+                const uint32_t my_row = stg + static_cast<uint32_t>(lane) * 128;
+                if (f32_out) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        sts128(my_row + static_cast<uint32_t>((q ^ (lane & 7)) << 4), __float_as_uint(v[4 * q]),
+                               __float_as_uint(v[4 * q + 1]), __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+                } else {
+                    const int half = (cc >> 5) & 1;  // first or second 64 bytes of the 128-byte row
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        sts128(my_row + static_cast<uint32_t>(((half * 4 + q) ^ (lane & 7)) << 4),
+                               pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                               pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+                }
+                const bool row_full = f32_out || ((cc >> 5) & 1) || cc + 32 >= out_cols;
+                if (!row_full) continue;
+                __syncwarp();
+                const int flush_col0 = col_base + (f32_out ? cc : (cc & ~63));
+                const int valid_cols = min(cols_per_flush, cc + 32 - (f32_out ? cc : (cc & ~63)));
+                const int vec = f32_out ? 4 : 8;  // elements per 16 bytes
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = 4 * j + (lane >> 3), ch = lane & 7;
+                    const long long grow = static_cast<long long>(c.m0) + lg * 32 + r;
+                    const int col = flush_col0 + ch * vec;
+                    if (grow < c.rows_end && ch * vec < valid_cols && col < p.n_out) {
+                        const uint4 d = lds128(stg + static_cast<uint32_t>(r * 128 + ((ch ^ (r & 7)) << 4)));
+                        if (f32_out) {
+                            float* dst = static_cast<float*>(p.y) + grow * p.ldy + col;
+                            if (vec_ok && col + 4 <= p.n_out) {
+                                *reinterpret_cast<uint4*>(dst) = d;
+                            } else {
+                                const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+                                for (int e = 0; e < 4 && col + e < p.n_out; ++e) dst[e] = __uint_as_float(w[e]);
+                            }
+                        } else {
+                            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.y) + grow * p.ldy + col;
+                            if (vec_ok && col + 8 <= p.n_out) {
+                                *reinterpret_cast<uint4*>(dst) = d;
+                            } else {
+                                const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+                                for (int e = 0; e < 8 && col + e < p.n_out; ++e)
+                                    reinterpret_cast<unsigned short*>(dst)[e] =
+                                        static_cast<unsigned short>((w[e >> 1] >> ((e & 1) * 16)) & 0xFFFFu);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
+            if (warp == 2 && lane == 0) GT_TRACE(4, it);
             if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
         }
     }
@@ -401,9 +463,11 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     }
 
     const int stage_bytes = (GT_BM + bn) * GT_BK * 2;
-    int n_stages = std::min(GT_MAX_STAGES, (ctx->max_smem_optin - 4096 - static_cast<int>(sizeof(GemmShared))) / stage_bytes);
+    const int staging = 4 * GT_STAGING_PER_WARP;
+    int n_stages = std::min(GT_MAX_STAGES,
+                            (ctx->max_smem_optin - 4096 - staging - static_cast<int>(sizeof(GemmShared))) / stage_bytes);
     if (n_stages < 2) return IZB_ERR_UNSUPPORTED;
-    const int smem_bytes = n_stages * stage_bytes + 1024;
+    const int smem_bytes = n_stages * stage_bytes + staging + 1024;
     static std::atomic<int> smem_set[16];
     const int slot = ctx->device & 15;
     if (smem_set[slot].load(std::memory_order_relaxed) < smem_bytes) {
@@ -419,3 +483,9 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
 }
 
 }  // namespace izb
+
+#ifdef IZB_GEMM_TRACE
+extern "C" int izb_debug_gemm_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, izb::g_gemm_trace, sizeof(unsigned long long) * 16 * 5) == cudaSuccess ? 0 : -3;
+}
+#endif
