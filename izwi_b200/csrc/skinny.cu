@@ -256,6 +256,40 @@ __device__ __forceinline__ void stage_q4_k(float (&acc)[RT][NT][4], uint32_t wba
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
+// The scalar fields of a problem descriptor, cached in shared memory at kernel start: a CTA meets
+// a different problem on almost every tile, and walking the descriptors in global memory was a
+// chain of dependent long-latency loads per tile.
+struct alignas(16) ProbLite {
+    void* y;
+    const __nv_bfloat16* bias;
+    int N, M, ldy, tile_start;
+    int n_chunks, nb, kbox, w_row_bytes;
+    int w_box_bytes, x_off, stage_tx, pad_;
+};
+static_assert(sizeof(ProbLite) == 64, "ProbLite layout");
+constexpr int SK_LITE_MAX = 160;  // problems cached; beyond that the descriptor is read from global memory
+
+__device__ __forceinline__ ProbLite lite_from(const SkinnyProblem& q) {
+    ProbLite l;
+    l.y = q.y; l.bias = q.bias;
+    l.N = q.N; l.M = q.M; l.ldy = q.ldy; l.tile_start = q.tile_start;
+    l.n_chunks = q.n_chunks; l.nb = q.nb; l.kbox = q.kbox; l.w_row_bytes = q.w_row_bytes;
+    l.w_box_bytes = q.w_box_bytes; l.x_off = q.x_off; l.stage_tx = q.stage_tx; l.pad_ = 0;
+    return l;
+}
+
+// Index of the problem that owns `tile`: last p with tile_start[p] <= tile (binary search).
+__device__ __forceinline__ int find_problem(const ProbLite* lite, int n_cached, const SkinnyProblem* plist, int n_probs,
+                                            int tile) {
+    int lo = 0, hi = n_probs;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        const int start = mid < n_cached ? lite[mid].tile_start : plist[mid].tile_start;
+        if (start <= tile) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
 struct SkinnyShared {
     unsigned long long full[SK_MAX_STAGES];
     unsigned long long empty[SK_MAX_STAGES];
@@ -273,7 +307,8 @@ __device__ __forceinline__ void store_out(void* y, int y_dtype, long long idx, f
 template <int FMT, int NT, int RT, int KS>
 __global__ void __launch_bounds__(SK_THREADS)
     skinny_kernel(const SkinnyProblem* __restrict__ probs, const __grid_constant__ SkinnyProblem single, int n_probs,
-                  int total_tiles, int n_stages, int stage_bytes, int red_bytes, int y_dtype, int* status) {
+                  int total_tiles, int n_stages, int stage_bytes, int red_bytes, int lite_bytes, int y_dtype,
+                  int* status) {
     constexpr int RG = SK_CONSUMER_WARPS / KS;
     constexpr int TILE_ROWS = RG * RT * 16;
     constexpr int ACC = RT * NT * 4;
@@ -292,10 +327,14 @@ __global__ void __launch_bounds__(SK_THREADS)
         sh.abort_flag = 0;
         mbar_fence_init();
     }
+    // dynamic shared memory: [descriptor cache][k-split reduction buffer][stage ring]
+    ProbLite* lite = reinterpret_cast<ProbLite*>(dyn_smem);
+    const int n_cached = min(n_probs, lite_bytes / static_cast<int>(sizeof(ProbLite)));
+    for (int i = threadIdx.x; i < n_cached; i += blockDim.x) lite[i] = lite_from(plist[i]);
     __syncthreads();
 
     volatile int* abort_flag = &sh.abort_flag;
-    const uint32_t stage0 = smem_u32(dyn_smem) + static_cast<uint32_t>(red_bytes);
+    const uint32_t stage0 = smem_u32(dyn_smem) + static_cast<uint32_t>(lite_bytes + red_bytes);
 
     if (warp == SK_CONSUMER_WARPS) {
         // ---------------- producer: one lane issues two tiled copies per stage ----------------
@@ -306,21 +345,19 @@ __global__ void __launch_bounds__(SK_THREADS)
         bool ok = true;
         int p = -1;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            bool moved = p < 0;
-            if (p < 0) p = 0;
-            while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) {
-                ++p;
-                moved = true;
-            }
+            const int np = find_problem(lite, n_cached, plist, n_probs, tile);
+            const bool moved = np != p;
+            p = np;
             const SkinnyProblem* P = plist + p;
             if (moved && probs) {
                 tma_fence_descriptor(&P->tmap_w);
                 tma_fence_descriptor(&P->tmap_x);
             }
-            const int row0 = (tile - P->tile_start) * TILE_ROWS;
-            const int n_chunks = P->n_chunks, nb = P->nb, x_off = P->x_off;
-            const uint32_t tx = static_cast<uint32_t>(P->stage_tx);
-            const int xchunks = nb * (P->kbox >> 6);
+            const ProbLite L = p < n_cached ? lite[p] : lite_from(*P);
+            const int row0 = (tile - L.tile_start) * TILE_ROWS;
+            const int n_chunks = L.n_chunks, nb = L.nb, x_off = L.x_off;
+            const uint32_t tx = static_cast<uint32_t>(L.stage_tx);
+            const int xchunks = nb * (L.kbox >> 6);
             for (int c = 0; c < n_chunks; ++c) {
                 if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
                     ok = false;
@@ -368,15 +405,15 @@ __global__ void __launch_bounds__(SK_THREADS)
     const int g = lane >> 2, t = lane & 3;
     const int rg = warp / KS, ks = warp % KS;
     const int rowbase = rg * RT * 16;
-    float* red = reinterpret_cast<float*>(dyn_smem);
+    float* red = reinterpret_cast<float*>(dyn_smem + lite_bytes);
 
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     int p = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        while (p + 1 < n_probs && tile >= plist[p + 1].tile_start) ++p;
-        const SkinnyProblem& PD = plist[p];
+        p = find_problem(lite, n_cached, plist, n_probs, tile);
+        const ProbLite PD = p < n_cached ? lite[p] : lite_from(plist[p]);
         const int row0 = (tile - PD.tile_start) * TILE_ROWS;
         const int n_chunks = PD.n_chunks;
         const uint32_t x_off = static_cast<uint32_t>(PD.x_off);
@@ -493,7 +530,7 @@ int launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, con
         smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);
     }
     kern<<<h.grid, SK_THREADS, h.smem_bytes, stream>>>(dev, single, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes,
-                                                       h.red_bytes, h.y_dtype, ctx->d_status);
+                                                       h.red_bytes, h.lite_bytes, h.y_dtype, ctx->d_status);
     IZB_CUDA_TRY(cudaGetLastError());
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
@@ -696,14 +733,15 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
 
     const int red_raw = ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
     const int red_bytes = (red_raw + 1023) / 1024 * 1024;
-    int n_stages = (budget - red_bytes) / stage_bytes;
+    const int lite_bytes = (std::min(n, SK_LITE_MAX) * static_cast<int>(sizeof(ProbLite)) + 1023) / 1024 * 1024;
+    int n_stages = (budget - red_bytes - lite_bytes) / stage_bytes;
     const int forced_stages = env_int("IZB_SKINNY_STAGES", 0);
     if (forced_stages) n_stages = forced_stages;
     n_stages = std::min(n_stages, SK_MAX_STAGES);
     if (n_stages < 2) {
         // A single stage pair must still fit one CTA per SM.
         n_stages = 2;
-        if (red_bytes + 2 * stage_bytes > ctx->max_smem_optin - 2048) return IZB_ERR_UNSUPPORTED;
+        if (lite_bytes + red_bytes + 2 * stage_bytes > ctx->max_smem_optin - 2048) return IZB_ERR_UNSUPPORTED;
     }
 
     std::memset(hdr, 0, sizeof(*hdr));
@@ -717,7 +755,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     hdr->n_stages = n_stages;
     hdr->stage_bytes = stage_bytes;
     hdr->red_bytes = red_bytes;
-    hdr->smem_bytes = red_bytes + n_stages * stage_bytes + 1024;  // slack to align the ring to 1024 bytes
+    hdr->lite_bytes = lite_bytes;
+    hdr->smem_bytes = lite_bytes + red_bytes + n_stages * stage_bytes + 1024;  // slack to align the ring to 1024 bytes
     hdr->grid = std::min(tile_cursor, max_grid);
     hdr->y_dtype = y_dtype;
     return IZB_OK;

@@ -46,7 +46,8 @@ struct alignas(64) SkinnyPlanHeader {
     int n_probs, total_tiles;
     int n_stages, stage_bytes, red_bytes, smem_bytes;
     int grid, y_dtype;
-    int pad_[3];
+    int lite_bytes;  // shared-memory bytes of the descriptor cache
+    int pad_[2];
 };
 static_assert(sizeof(SkinnyPlanHeader) == 64, "SkinnyPlanHeader layout");
 
