@@ -247,6 +247,102 @@ def measure_case(workload: str, device, steps: int, warmup: int, peak: float):
     return out
 
 
+def load_tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), "measured burst"
+    return 1590.0, "fallback"
+
+
+def _time_call(fn, iters: int, warmup: int = 3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def measure_gemm_cases(device):
+    """Prefill (Qwen3-8B shape, M = 2048) and ASR-encoder GEMMs through izb_linear: TFLOP/s against the
+    measured bf16 tensor peak.  Operands are a few hundred MB, so successive calls do not reuse L2 for
+    the large ones; the small ones are reported as measured (L2-resident, as they would be in a layer loop)."""
+    import torch
+    from izwi_b200 import ops
+    peak, kind = load_tensor_peak()
+    gen = torch.Generator(device=device).manual_seed(3)
+    shapes = [
+        ("qwen3-8b-prefill-qkv", 2048, 6144, 4096, None, False),
+        ("qwen3-8b-prefill-o", 2048, 4096, 4096, None, False),
+        ("qwen3-8b-prefill-gate_up+swiglu", 2048, 24576, 4096, "swiglu", False),
+        ("qwen3-8b-prefill-down", 2048, 4096, 12288, None, False),
+        ("fastconformer-b32-ffn1+silu", 12000, 4096, 1024, "silu", False),
+        ("fastconformer-b32-ffn2", 12000, 1024, 4096, None, False),
+        ("fastconformer-b32-attn", 12000, 1024, 1024, None, False),
+        ("whisper-b32-qkv+bias", 48000, 3840, 1280, None, True),
+        ("whisper-b32-fc1+bias+gelu", 48000, 5120, 1280, "gelu", True),
+        ("whisper-b32-fc2+bias", 48000, 1280, 5120, None, True),
+        ("whisper-b1-fc1+bias+gelu", 1500, 5120, 1280, "gelu", True),
+        ("fastconformer-b1-ffn1+silu", 375, 4096, 1024, "silu", False),
+    ]
+    out = []
+    for name, m, n, k, epi, has_bias in shapes:
+        x = torch.randn(m, k, device=device, generator=gen).to(torch.bfloat16)
+        w = (torch.randn(n, k, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        b = (torch.randn(n, device=device, generator=gen) * 0.1).to(torch.bfloat16) if has_bias else None
+        y = torch.empty(m, n // 2 if epi == "swiglu" else n, device=device, dtype=torch.bfloat16)
+        ms = _time_call(lambda: ops.linear(x, w, bias=b, out=y, epilogue=epi), 20)
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out.append({"workload": name, "M": m, "N": n, "K": k, "ms": round(ms, 4), "tflops": round(tf, 1),
+                    "tensor_frac": round(tf / peak, 4), "peak_kind": f"of {kind} {peak}"})
+        del x, w, y
+    ops.Context.get(device.index).check()
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_moe_cases(device):
+    """One Qwen3-30B-A3B-shaped MoE layer (H 2048, I 768, 128 experts, top-8, router bias ~N(0, 0.5))
+    through izb_moe_forward at T = 1, 64, 4096; rotating over 3 layers' weights (3.6 GB) so the
+    small-T cases stream expert weights from HBM rather than L2."""
+    import torch
+    from izwi_b200 import moe, ops
+    peak_tf, _ = load_tensor_peak()
+    peak_bw, _ = load_peaks()
+    gen = torch.Generator(device=device).manual_seed(4)
+    h, i, e, k = 2048, 768, 128, 8
+    rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
+    layers = [moe.MoeLayer(rn(e, h, std=h ** -0.5), rn(e, std=0.5), rn(e, 2 * i, h, std=0.02), rn(e, h, i, std=0.02), k)
+              for _ in range(3)]
+    out = []
+    for t in (1, 64, 4096):
+        x = rn(t, h)
+        state = {"i": 0}
+
+        def step():
+            layers[state["i"] % 3].forward(x)
+            state["i"] += 1
+        ms = _time_call(step, 30)
+        _, _, idx, _ = layers[0].forward(x)
+        touched = int(torch.unique(idx).numel())
+        flops = 2.0 * t * k * 3 * i * h + 2.0 * t * e * h
+        wbytes = touched * 3 * i * h * 2 + e * h * 2
+        out.append({"workload": f"qwen3-30b-a3b-moe-layer-T{t}", "ms": round(ms, 4), "experts_touched": touched,
+                    "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "tensor_frac": round(flops / (ms * 1e-3) / 1e12 / peak_tf, 4),
+                    "weight_gbs": round(wbytes / (ms * 1e-3) / 1e9, 1), "hbm_frac_of_measured": round(wbytes / (ms * 1e-3) / 1e9 / peak_bw, 4),
+                    "kernels_per_layer": 8})
+    ops.Context.get(device.index).check()
+    del layers
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     import torch
     from izwi_b200 import workloads as wl
@@ -345,6 +441,8 @@ def run_ours(args):
                     continue
                 cases.append(measure_case(wname, device, args.case_steps, 5, peak))
             line["cases"] = cases
+            line["gemm_cases"] = measure_gemm_cases(device)
+            line["moe_cases"] = measure_moe_cases(device)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

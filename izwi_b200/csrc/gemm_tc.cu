@@ -11,9 +11,10 @@ namespace izb {
 constexpr int GT_BM = 128;       // rows of X per tile = TMEM lanes
 constexpr int GT_BK = 64;        // k per pipeline stage = one 128-byte swizzle row of bf16
 constexpr int GT_UMMA_K = 16;    // k per tcgen05.mma (bf16)
-constexpr int GT_THREADS = 192;  // producer warp, MMA warp, 4 epilogue warps
+constexpr int GT_EPI_WARPS = 8;   // two warps per TMEM lane quarter, each takes half of the tile's columns
+constexpr int GT_THREADS = 32 * (2 + GT_EPI_WARPS);  // producer warp, MMA warp, epilogue warps
 constexpr int GT_MAX_STAGES = 8;
-constexpr int GT_MAX_EXPERTS = 512;
+constexpr int GT_MAX_EXPERTS = 256;
 constexpr int GT_GROUP_M = 16;  // row blocks per rasterisation band
 constexpr int GT_STAGING_PER_WARP = 32 * 128;  // 32 rows x 128 bytes of output staging per epilogue warp
 
@@ -132,7 +133,13 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 }
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+// x * sigmoid(x) = 0.5 x (1 + tanh(x / 2)): one special-function instruction per element
+// (tanh.approx, relative error ~2^-11, below the bf16 rounding of the result).
+__device__ __forceinline__ float silu(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+    return fmaf(0.5f * x, t, 0.5f * x);
+}
 
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ GemmParams p, int n_stages, int* status) {
@@ -160,7 +167,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&sh.tmem_full[a]), 1);
-            mbar_init(smem_u32(&sh.tmem_empty[a]), 4);
+            mbar_init(smem_u32(&sh.tmem_empty[a]), GT_EPI_WARPS);
         }
         mbar_init(smem_u32(&sh.drain), 1);
         sh.abort_flag = 0;
@@ -284,8 +291,12 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5, TMEM lane group = warp % 4 ----------------
+        // ---------------- epilogue: warps 2..9, TMEM lane group = warp % 4, column half = (warp-2)/4 ----
         const int lg = warp & 3;
+        const int ew = warp - 2;
+        // narrow tiles (fewer than 64 output columns) are handled by the first warp of each lane group
+        const int cc_begin = out_cols >= 64 ? (ew >> 2) * (out_cols / 2) : 0;
+        const int cc_end = out_cols >= 64 ? cc_begin + out_cols / 2 : ((ew >> 2) == 0 ? out_cols : 0);
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int acc = it & 1;
@@ -302,8 +313,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             // pieces over 32 rows.  The warp parks 128 bytes per row in shared memory (16-byte chunks
             // XOR-swizzled by row) and writes them back 8 lanes per row, i.e. whole 128-byte lines.
             const int cols_per_flush = f32_out ? 32 : 64;
-            const uint32_t stg = stage_out + static_cast<uint32_t>(lg) * GT_STAGING_PER_WARP;
-            for (int cc = 0; cc < out_cols; cc += 32) {
+            const uint32_t stg = stage_out + static_cast<uint32_t>(ew) * GT_STAGING_PER_WARP;
+            for (int cc = cc_begin; cc < cc_end; cc += 32) {
                 float v[32];
                 tc_ld_32x32(t_row + static_cast<uint32_t>(cc), v);
                 const int col0 = col_base + cc;
@@ -345,18 +356,20 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                         sts128(my_row + static_cast<uint32_t>((q ^ (lane & 7)) << 4), __float_as_uint(v[4 * q]),
                                __float_as_uint(v[4 * q + 1]), __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
                 } else {
-                    const int half = (cc >> 5) & 1;  // first or second 64 bytes of the 128-byte row
+                    const int half = ((cc - cc_begin) >> 5) & 1;  // first or second 64 bytes of the 128-byte row
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
                         sts128(my_row + static_cast<uint32_t>(((half * 4 + q) ^ (lane & 7)) << 4),
                                pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
                                pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
                 }
-                const bool row_full = f32_out || ((cc >> 5) & 1) || cc + 32 >= out_cols;
+                const int rel = cc - cc_begin;
+                const bool row_full = f32_out || ((rel >> 5) & 1) || cc + 32 >= cc_end;
                 if (!row_full) continue;
                 __syncwarp();
-                const int flush_col0 = col_base + (f32_out ? cc : (cc & ~63));
-                const int valid_cols = min(cols_per_flush, cc + 32 - (f32_out ? cc : (cc & ~63)));
+                const int flush_rel = f32_out ? rel : (rel & ~63);
+                const int flush_col0 = col_base + cc_begin + flush_rel;
+                const int valid_cols = min(cols_per_flush, rel + 32 - flush_rel);
                 const int vec = f32_out ? 4 : 8;  // elements per 16 bytes
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -463,11 +476,12 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     }
 
     const int stage_bytes = (GT_BM + bn) * GT_BK * 2;
-    const int staging = 4 * GT_STAGING_PER_WARP;
+    const int staging = GT_EPI_WARPS * GT_STAGING_PER_WARP;
     int n_stages = std::min(GT_MAX_STAGES,
-                            (ctx->max_smem_optin - 4096 - staging - static_cast<int>(sizeof(GemmShared))) / stage_bytes);
+                            (ctx->max_smem_optin - 2048 - staging) / stage_bytes);  // 2048: static barriers + tile prefix, padded
     if (n_stages < 2) return IZB_ERR_UNSUPPORTED;
-    const int smem_bytes = n_stages * stage_bytes + staging + 1024;
+    static_assert(sizeof(GemmShared) <= 2048, "static shared memory budget");
+    const int smem_bytes = n_stages * stage_bytes + staging;
     static std::atomic<int> smem_set[16];
     const int slot = ctx->device & 15;
     if (smem_set[slot].load(std::memory_order_relaxed) < smem_bytes) {
