@@ -191,7 +191,8 @@ int32_t izb_moe_permute(izb_ctx* ctx, izb_stream stream, const void* idx, int64_
     if (!ctx || pairs < 0 || E <= 0) return IZB_ERR_BAD_ARG;
     if (E > 65535 || pairs > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     if (!offsets_out || (pairs > 0 && (!idx || !perm_out || !inv_out))) return IZB_ERR_BAD_ARG;
-    moe_permute_kernel<<<static_cast<int>(E), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    // 1024 threads: the in-order pass costs three block barriers per 1024 pairs
+    moe_permute_kernel<<<static_cast<int>(E), pairs >= 4096 ? 1024 : 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int*>(idx), static_cast<int>(pairs), static_cast<int>(E), static_cast<int*>(offsets_out),
         static_cast<int*>(perm_out), static_cast<int*>(inv_out));
     IZB_CUDA_TRY(cudaGetLastError());

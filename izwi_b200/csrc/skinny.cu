@@ -621,7 +621,10 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const int mp = nt * 8;
 
     // measured best residency: three CTAs per SM for Q8_0 (most ALU work per byte), two otherwise
-    const int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", fmt == IZB_W_Q8_0 ? 3 : 2));
+    // measured best residency: three CTAs per SM for Q8_0 at up to 16 tokens (most ALU work per
+    // byte), two otherwise; wide token groups need the whole SM's shared memory for one CTA
+    int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", fmt == IZB_W_Q8_0 && nt <= 2 ? 3 : 2));
+    if (nt == 8 && !env_int("IZB_SKINNY_CTAS_PER_SM", 0)) ctas_per_sm = 1;
     const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
     const int max_grid = ctx->sm_count * ctas_per_sm;
     const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_cast<int>(sizeof(SkinnyShared));
@@ -641,10 +644,11 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     // leaves every CTA a few tiles to balance with and room for two stages wins, else the
     // smallest tile (most CTAs busy on a single small problem).
     struct Cand { int rt, ks; };
-    static const Cand pref_q8[] = {{2, 2}, {2, 1}, {1, 1}, {1, 2}, {1, 4}};
+    static const Cand pref_q8[] = {{2, 2}, {2, 1}, {1, 1}, {1, 2}, {1, 4}};   // up to 16 tokens
+    static const Cand pref_q8w[] = {{2, 1}, {1, 1}, {2, 2}, {1, 2}, {1, 4}};  // 17..64 tokens
     static const Cand pref_q4[] = {{2, 1}, {2, 2}, {1, 1}, {1, 2}, {1, 4}};
     static const Cand pref_bf[] = {{2, 1}, {1, 1}, {1, 2}, {1, 4}};
-    const Cand* pref = fmt == IZB_W_Q8_0 ? pref_q8 : fmt == IZB_W_Q4_K ? pref_q4 : pref_bf;
+    const Cand* pref = fmt == IZB_W_Q8_0 ? (nt <= 2 ? pref_q8 : pref_q8w) : fmt == IZB_W_Q4_K ? pref_q4 : pref_bf;
     const int n_pref = fmt == IZB_W_BF16 ? 4 : 5;
     int rt = 1, ks = 4;
     const int forced_rt = env_int("IZB_SKINNY_RT", 0), forced_ks = env_int("IZB_SKINNY_KS", 0);
