@@ -450,6 +450,134 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------
+# sharded workloads (run with --gpus N under torch.distributed.run; N = 1 gives the baseline point)
+# ----------------------------------------------------------------------------------------------
+SHARDED = {
+    # name: (kind, parameter)
+    "qwen3-8b-tp-decode-m1": ("tp", 1), "qwen3-8b-tp-decode-m8": ("tp", 8), "qwen3-8b-tp-decode-m32": ("tp", 32),
+    "qwen3-8b-tp-prefill-m2048": ("tp", 2048),
+    "qwen3-30b-a3b-ep-t64": ("ep", 64), "qwen3-30b-a3b-ep-t4096": ("ep", 4096),
+    "fastconformer-b32": ("enc", ("fastconformer", 24, 1024, 4096, 375, 32, False, "silu")),
+    "whisper-large-v3-b32": ("enc", ("whisper", 32, 1280, 5120, 1500, 32, True, "gelu")),
+}
+
+
+def run_sharded(args):
+    import torch
+    from izwi_b200 import moe, ops, parallel
+    from izwi_b200 import workloads as wl
+
+    world, rank, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    kind, param = SHARDED[args.workload]
+    comm = parallel.Comm(local) if world > 1 else None
+    gen = torch.Generator(device=device).manual_seed(3)       # same stream of weights on every rank
+    rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
+    cfg = {"workload": args.workload, "l2": "weights larger than L2"}
+    flops = 0.0
+
+    if kind == "tp":
+        shape, m = wl.QWEN3_8B, param
+        (_, n_qkv, h), (_, _, k_o), (_, n_gu, _), (_, _, k_d) = shape.projections
+        layers = []
+        for _ in range(shape.layers):
+            full = (rn(n_qkv, h, std=0.02), rn(h, k_o, std=0.02), rn(n_gu, h, std=0.02), rn(h, k_d, std=0.02))
+            layers.append(parallel.TpDecoderLayer.from_full(comm, shape, *full, world, rank) if world > 1
+                          else parallel.TpDecoderLayer(None, *full))
+            del full
+        lo, hi = parallel.tp_row_split_cols(k_o, world, rank)
+        x_a, x_o, x_m = rn(m, h), rn(m, hi - lo), rn(m, h)
+
+        def step():
+            for layer in layers:
+                layer.forward(x_a, x_o, x_m)
+        units, unit_name = m, "tokens/s"
+        flops = 2.0 * m * shape.layers * shape.weights_per_layer
+        cfg.update(model="qwen3-8b linear stack", tokens_per_step=m, layers=shape.layers,
+                   parallelism=f"tp{world}: column-split QKV and gate/up, row-split O and down, 2 all-reduces per layer")
+    elif kind == "ep":
+        t_total, n_layers = param, 8
+        h, inter, e, k = 2048, 768, 128, 8
+        lo_e, hi_e = parallel.ep_expert_range(e, world, rank)
+        layers = []
+        for _ in range(n_layers):
+            wr, br = rn(e, h, std=h ** -0.5), rn(e, std=0.5)
+            wgu, wd = rn(e, 2 * inter, h, std=0.02), rn(e, h, inter, std=0.02)
+            if world > 1:
+                layers.append(parallel.EpMoeLayer(comm, wr, br, wgu[lo_e:hi_e].clone(), wd[lo_e:hi_e].clone(), e, k))
+            else:
+                layers.append(moe.MoeLayer(wr, br, wgu, wd, k))
+            del wgu, wd
+        lo_t, hi_t = parallel.split_range(t_total, world, rank)
+        x = rn(t_total, h)[lo_t:hi_t].contiguous()
+
+        def step():
+            for layer in layers:
+                layer.forward(x)
+        units, unit_name = t_total, "tokens/s"
+        flops = 2.0 * t_total * k * 3 * inter * h * n_layers
+        cfg.update(model="qwen3-30b-a3b MoE FFN layers", tokens_per_step=t_total, layers=n_layers,
+                   note="8 of the 48 layers (each layer is 1.2 GB of expert weights)",
+                   parallelism=f"ep{world}: {e // world} experts per rank, tokens split, all-to-all each way")
+    else:
+        name, n_layers, d, ff, frames, batch, has_bias, act = param
+        lo_b, hi_b = parallel.batch_split(batch, world, rank)
+        m = (hi_b - lo_b) * frames
+        layers = []
+        for _ in range(n_layers):
+            ws = {"qkv": rn(3 * d, d, std=0.02), "o": rn(d, d, std=0.02), "fc1": rn(ff, d, std=0.02), "fc2": rn(d, ff, std=0.02)}
+            bs = {kk: (rn(v.shape[0], std=0.1) if has_bias else None) for kk, v in ws.items()}
+            layers.append((ws, bs))
+        n_ffn = 2 if name == "fastconformer" else 1                   # two macaron feed-forwards per layer
+        x = rn(max(m, 1), d)
+        bufs = {"qkv": torch.empty(max(m, 1), 3 * d, device=device, dtype=torch.bfloat16),
+                "d": torch.empty(max(m, 1), d, device=device, dtype=torch.bfloat16),
+                "ff": torch.empty(max(m, 1), ff, device=device, dtype=torch.bfloat16)}
+
+        def step():
+            if m == 0:
+                return
+            for ws, bs in layers:
+                ops.linear(x, ws["qkv"], bias=bs["qkv"], out=bufs["qkv"])
+                ops.linear(x, ws["o"], bias=bs["o"], out=bufs["d"])
+                for _ in range(n_ffn):
+                    ops.linear(x, ws["fc1"], bias=bs["fc1"], out=bufs["ff"], epilogue=act)
+                    ops.linear(bufs["ff"], ws["fc2"], bias=bs["fc2"], out=bufs["d"])
+        units, unit_name = batch, "utterances/s"
+        flops = 2.0 * batch * frames * n_layers * (4 * d * d + n_ffn * 2 * d * ff)
+        cfg.update(model=f"{name} encoder GEMMs (QKV, O, FFN)", batch=batch, frames=frames, layers=n_layers,
+                   parallelism=f"batch split over {world} ranks, weights replicated, no collective")
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ctx = ops.Context.get(local)
+    launches0 = ctx.launch_count
+    ms, t0, t1 = time_steps(step, args.steps, world)
+    launches = ctx.launch_count - launches0
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    ctx.check()
+    per_ms = ms / args.steps
+    peak_tf, kind_tf = load_tensor_peak()
+    line = {"metric": f"{args.workload}_{unit_name.split('/')[0]}_per_s", "value": round(units / (per_ms * 1e-3), 2),
+            "unit": unit_name, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(per_ms, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": cfg,
+            "tflops_total": round(flops / (per_ms * 1e-3) / 1e12, 1),
+            "tensor_frac_per_gpu": round(flops / (per_ms * 1e-3) / 1e12 / world / peak_tf, 4),
+            "gpu_launches": int(launches), "clocks": sampler.summary(t0, t1)}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        comm.close()
+        dist.destroy_process_group()
+
+
 def run_reference(args):
     """The reference arm: the CPU restatement of the same stack on the host cores (the reference's
     own Candle CPU path cannot be built without a Rust toolchain)."""
@@ -488,7 +616,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(SHARDED))
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--case-steps", type=int, default=300)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -498,7 +626,14 @@ def main():
     args = ap.parse_args()
     global LAYERS_OVERRIDE
     LAYERS_OVERRIDE = args.layers
-    if args.impl == "reference":
+    if args.workload in SHARDED:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm covers the default workload only"}))
+            return
+        if args.steps == 20000:
+            args.steps = 20
+        run_sharded(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
