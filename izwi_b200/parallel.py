@@ -177,20 +177,48 @@ class TpDecoderLayer:
         """x_attn_in [M, H] -> qkv_local; x_o_in [M, K_o/tp] -> attention block output (reduced);
         x_mlp_in [M, H] -> MLP block output (reduced)."""
         from . import ops
+        m = x_mlp_in.shape[0]
+        if m <= 32:
+            return self._forward_decode(x_attn_in, x_o_in, x_mlp_in)
         qkv = ops.linear(x_attn_in, self.w_qkv)
         o = ops.linear(x_o_in, self.w_o)
         if self.comm is not None:
             self.comm.allreduce_(o)
-        m = x_mlp_in.shape[0]
-        if m > 32:
-            hidden = ops.linear(x_mlp_in, self.w_gate_up, epilogue="swiglu")
-        else:
-            gu = ops.linear(x_mlp_in, self.w_gate_up)
-            hidden = ops.silu_mul(gu[:, : self.inter_local], gu[:, self.inter_local:])
+        hidden = ops.linear(x_mlp_in, self.w_gate_up, epilogue="swiglu")
         down = ops.linear(hidden, self.w_down)
         if self.comm is not None:
             self.comm.allreduce_(down)
         return qkv, o, down
+
+    def _forward_decode(self, x_attn_in, x_o_in, x_mlp_in):
+        """Decode sizes: the three projections that do not depend on one another go out as one grouped
+        persistent launch, then SiLU-multiply, then the down projection; plans and output buffers are
+        built once per set of input buffers and reused every step."""
+        import torch
+
+        from . import ops
+        key = (x_attn_in.data_ptr(), x_o_in.data_ptr(), x_mlp_in.data_ptr(), x_mlp_in.shape[0])
+        st = getattr(self, "_decode_state", None)
+        if st is None or st["key"] != key:
+            dev, m = x_mlp_in.device, x_mlp_in.shape[0]
+            mk = lambda n: torch.empty(m, n, device=dev, dtype=torch.bfloat16)  # noqa: E731
+            qkv, o, gu = mk(self.w_qkv.shape[0]), mk(self.w_o.shape[0]), mk(self.w_gate_up.shape[0])
+            hidden, down = mk(self.inter_local), mk(self.w_down.shape[0])
+            first = ops.LinearGroup([
+                ops.linear_args(x_attn_in, self.w_qkv, "bf16", *self.w_qkv.shape, qkv),
+                ops.linear_args(x_o_in, self.w_o, "bf16", *self.w_o.shape, o),
+                ops.linear_args(x_mlp_in, self.w_gate_up, "bf16", *self.w_gate_up.shape, gu)], dev)
+            second = ops.LinearGroup([ops.linear_args(hidden, self.w_down, "bf16", *self.w_down.shape, down)], dev)
+            st = self._decode_state = dict(key=key, qkv=qkv, o=o, gu=gu, hidden=hidden, down=down, first=first,
+                                           second=second, keep=(x_attn_in, x_o_in, x_mlp_in))
+        st["first"].launch()
+        if self.comm is not None:
+            self.comm.allreduce_(st["o"])
+        ops.silu_mul(st["gu"][:, : self.inter_local], st["gu"][:, self.inter_local:], out=st["hidden"])
+        st["second"].launch()
+        if self.comm is not None:
+            self.comm.allreduce_(st["down"])
+        return st["qkv"], st["o"], st["down"]
 
 
 class EpMoeLayer:
