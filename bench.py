@@ -472,6 +472,8 @@ def run_sharded(args):
     device = torch.device("cuda", local)
     kind, param = SHARDED[args.workload]
     comm = parallel.Comm(local) if world > 1 else None
+    if comm is not None and kind == "tp":
+        comm.enable_peer_allreduce(1 << 20)      # decode-size sums go through NVLink peer memory, not NCCL
     gen = torch.Generator(device=device).manual_seed(3)       # same stream of weights on every rank
     rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
     cfg = {"workload": args.workload, "l2": "weights larger than L2"}
@@ -552,6 +554,16 @@ def run_sharded(args):
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
+    if kind == "tp" and param <= 32 and not args.no_graph:
+        # the decode step is a fixed sequence of launches: replay it as one CUDA graph
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        eager_step, step = step, graph.replay
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        cfg["launch"] = "CUDA graph replay of the whole step"
     sampler = ClockSampler(local)
     sampler.start()
     ctx = ops.Context.get(local)
@@ -621,6 +633,7 @@ def main():
     ap.add_argument("--case-steps", type=int, default=300)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cases", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="sharded decode workloads: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=None,
                     help="shorter stack for profiler captures (the reported line is then not the benchmark)")
     args = ap.parse_args()

@@ -228,6 +228,21 @@ int32_t izb_ep_alltoall(izb_comm* comm, izb_stream stream, const void* send,
                         const int64_t* host_send_rows, void* recv, const int64_t* host_recv_rows,
                         int64_t row_bytes);
 
+/* One-shot all-reduce over NVLink peer memory for decode-size messages (a few KB to 1 MB): one
+ * kernel pushes this rank's partial sums into every peer's buffer with plain stores, signals,
+ * waits (bounded) for the peers and adds the contributions in rank order (deterministic).  Set-up:
+ * every rank calls izb_ar_create (allocates its buffer), passes its 64-byte handle to all ranks,
+ * and calls izb_ar_connect with the `world` handles in rank order.  izb_ar_allreduce is in place,
+ * needs count*elem_size <= max_bytes, a 4-byte aligned buffer and a byte size that is a multiple
+ * of 4; it can be replayed from a CUDA graph.  No counterpart in the reference (single device). */
+typedef struct izb_ar izb_ar;
+int32_t izb_ar_create(izb_ctx* ctx, int32_t world, int32_t rank, size_t max_bytes, izb_ar** out);
+int32_t izb_ar_local_handle(izb_ar* ar, void* out_64_bytes);
+int32_t izb_ar_connect(izb_ar* ar, const void* handles_world_x_64_bytes);
+size_t izb_ar_max_bytes(const izb_ar* ar);
+int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count, int32_t dtype);
+int32_t izb_ar_destroy(izb_ar* ar);
+
 #ifdef __cplusplus
 }
 #endif

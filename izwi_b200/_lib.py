@@ -85,6 +85,12 @@ _SIGNATURES = {
     "izb_comm_allgather": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
     "izb_ep_alltoall": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p,
                                     C.POINTER(C.c_int64), C.c_int64]),
+    "izb_ar_create": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "izb_ar_local_handle": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "izb_ar_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "izb_ar_max_bytes": (C.c_size_t, [C.c_void_p]),
+    "izb_ar_allreduce": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32]),
+    "izb_ar_destroy": (C.c_int32, [C.c_void_p]),
     "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
 }

@@ -123,7 +123,11 @@ class Comm:
         from .ops import _ptr, _stream
         assert t.is_contiguous()
         code = L.IZB_F32 if t.dtype == torch.float32 else L.IZB_BF16
-        L.check(L.lib().izb_tp_allreduce(self.handle, _stream(), _ptr(t), t.numel(), code), "izb_tp_allreduce")
+        nbytes = t.numel() * t.element_size()
+        if getattr(self, "ar", None) and nbytes <= self.ar_max and nbytes % 4 == 0 and t.data_ptr() % 4 == 0:
+            L.check(L.lib().izb_ar_allreduce(self.ar, _stream(), _ptr(t), t.numel(), code), "izb_ar_allreduce")
+        else:
+            L.check(L.lib().izb_tp_allreduce(self.handle, _stream(), _ptr(t), t.numel(), code), "izb_tp_allreduce")
         return t
 
     def allgather_bytes(self, send, recv):
@@ -140,8 +144,27 @@ class Comm:
         L.check(L.lib().izb_ep_alltoall(self.handle, _stream(), _ptr(send), s, _ptr(recv), r, row_bytes),
                 "izb_ep_alltoall")
 
+    def enable_peer_allreduce(self, max_bytes: int = 1 << 20):
+        """Sets up the one-shot all-reduce over NVLink peer memory for messages up to max_bytes;
+        larger ones keep going through NCCL.  Collective: every rank must call it."""
+        import torch.distributed as dist
+
+        from . import _lib as L
+        ar = C.c_void_p()
+        L.check(L.lib().izb_ar_create(self.ctx.handle, self.world, self.rank, max_bytes, C.byref(ar)), "izb_ar_create")
+        mine = (C.c_ubyte * 64)()
+        L.check(L.lib().izb_ar_local_handle(ar, mine), "izb_ar_local_handle")
+        every = [None] * self.world
+        dist.all_gather_object(every, bytes(mine))
+        L.check(L.lib().izb_ar_connect(ar, b"".join(every)), "izb_ar_connect")
+        dist.barrier()
+        self.ar, self.ar_max = ar, max_bytes
+
     def close(self):
         from . import _lib as L
+        if getattr(self, "ar", None):
+            L.lib().izb_ar_destroy(self.ar)
+            self.ar = None
         if self.handle:
             L.lib().izb_comm_destroy(self.handle)
             self.handle = None

@@ -45,6 +45,34 @@ def main():
     comm.allreduce_(t)
     assert float(t[0]) == world * (world + 1) / 2
 
+    # ---- one-shot all-reduce over peer memory against NCCL, many calls in a row ----
+    comm.enable_peer_allreduce(1 << 20)
+    g2 = torch.Generator(device=dev).manual_seed(100 + rank)       # different partial sums per rank
+    for n, dt in ((8, torch.bfloat16), (4096, torch.bfloat16), (131072, torch.bfloat16), (524288, torch.bfloat16),
+                  (4, torch.float32), (65536, torch.float32)) * 3:
+        part = torch.randn(n, device=dev, generator=g2).to(dt)
+        want = part.clone()
+        dist.all_reduce(want)
+        got = part.clone()
+        comm.allreduce_(got)
+        assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2), ("peer all-reduce", n, dt)
+    ints = torch.full((2048,), float(rank + 1), device=dev, dtype=torch.float32)
+    for _ in range(50):
+        t2 = ints.clone()
+        comm.allreduce_(t2)
+        assert float(t2[0]) == world * (world + 1) / 2 and float(t2[-1]) == world * (world + 1) / 2
+    ops.Context.get(rank).check()
+    # the tensor-parallel layer again, now reducing through peer memory
+    for m in (1, 8):
+        x_a, x_o, x_m = rn(m, 512), rn(m, k_o), rn(m, 512)
+        layer = parallel.TpDecoderLayer.from_full(comm, shape, w_qkv, w_o, w_gu, w_d, world, rank)
+        lo, hi = parallel.tp_row_split_cols(k_o, world, rank)
+        _, o, down = layer.forward(x_a, x_o[:, lo:hi].contiguous(), x_m)
+        _, o_f, down_f = parallel.TpDecoderLayer(None, w_qkv, w_o, w_gu, w_d).forward(x_a, x_o, x_m)
+        for got, want, what in ((o, o_f, "o"), (down, down_f, "down")):
+            err = float((got.float() - want.float()).abs().max()) / float(want.float().abs().max())
+            assert err < 2e-2, ("peer tp", what, m, err)
+
     # ---- expert parallel ----
     h, inter, e, k = 512, 256, 16, 4
     wr, br = rn(e, h, std=h ** -0.5), rn(e, std=0.5)
