@@ -8,46 +8,6 @@
 
 namespace izb {
 
-__device__ __forceinline__ float half_bits_to_f32(uint32_t h) {
-    return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
-}
-
-// Four int8 in a word -> two f16x2 registers holding the exact integers.
-// byte ^ 0x80 is q+128 as an unsigned byte; under the high byte 0x64 it reads as the fp16
-// value 1024 + q + 128 (fp16 has a unit step from 1024 to 2048), and one packed subtraction
-// of 1152 leaves q.
-__device__ __forceinline__ void s8x4_to_f16x4(uint32_t w, uint32_t& p01, uint32_t& p23) {
-    const uint32_t u = w ^ 0x80808080u;
-    const uint32_t h01 = prmt(u, 0x64646464u, 0x5140), h23 = prmt(u, 0x64646464u, 0x7362);
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(p01) : "r"(h01), "r"(0x64806480u));
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(p23) : "r"(h23), "r"(0x64806480u));
-}
-
-// A bf16 pair -> the same two values as an fp16 pair.  Exact for 2^-24 <= |x| <= 65504 (bf16
-// carries 8 significant bits, fp16 11); larger magnitudes saturate to +-65504.
-__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t b) {
-    uint32_t r;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(b & 0xFFFF0000u)), "f"(__uint_as_float(b << 16)));
-    return r;
-}
-
-// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
-__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-
-__device__ __forceinline__ uint32_t bcast_bf16x2(float v) { return pack_bf16x2(v, v); }
-
 // Row permutations that make the shared-memory loads bank-conflict free under the 128-byte
 // swizzle (16-byte chunk index ^= row & 7).  Fragment row/column g of an mma maps to
 // shared-memory row perm(g) inside its group of eight.
@@ -256,40 +216,6 @@ __device__ __forceinline__ void stage_q4_k(float (&acc)[RT][NT][4], uint32_t wba
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-// The scalar fields of a problem descriptor, cached in shared memory at kernel start: a CTA meets
-// a different problem on almost every tile, and walking the descriptors in global memory was a
-// chain of dependent long-latency loads per tile.
-struct alignas(16) ProbLite {
-    void* y;
-    const __nv_bfloat16* bias;
-    int N, M, ldy, tile_start;
-    int n_chunks, nb, kbox, w_row_bytes;
-    int w_box_bytes, x_off, stage_tx, pad_;
-};
-static_assert(sizeof(ProbLite) == 64, "ProbLite layout");
-constexpr int SK_LITE_MAX = 160;  // problems cached; beyond that the descriptor is read from global memory
-
-__device__ __forceinline__ ProbLite lite_from(const SkinnyProblem& q) {
-    ProbLite l;
-    l.y = q.y; l.bias = q.bias;
-    l.N = q.N; l.M = q.M; l.ldy = q.ldy; l.tile_start = q.tile_start;
-    l.n_chunks = q.n_chunks; l.nb = q.nb; l.kbox = q.kbox; l.w_row_bytes = q.w_row_bytes;
-    l.w_box_bytes = q.w_box_bytes; l.x_off = q.x_off; l.stage_tx = q.stage_tx; l.pad_ = 0;
-    return l;
-}
-
-// Index of the problem that owns `tile`: last p with tile_start[p] <= tile (binary search).
-__device__ __forceinline__ int find_problem(const ProbLite* lite, int n_cached, const SkinnyProblem* plist, int n_probs,
-                                            int tile) {
-    int lo = 0, hi = n_probs;
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        const int start = mid < n_cached ? lite[mid].tile_start : plist[mid].tile_start;
-        if (start <= tile) lo = mid; else hi = mid;
-    }
-    return lo;
-}
-
 struct SkinnyShared {
     unsigned long long full[SK_MAX_STAGES];
     unsigned long long empty[SK_MAX_STAGES];
@@ -581,14 +507,15 @@ struct BoxGeom {
     int w_row_bytes;  // bytes per row of a box
 };
 
-BoxGeom box_geom(int fmt, int K) {
+BoxGeom box_geom(int fmt, int K, bool tc = false) {
     switch (fmt) {
         case IZB_W_BF16: return {64, 128};
         case IZB_W_Q8_0: return {256, 272};
         default:
             // two super-blocks per box keep the 8-byte code loads conflict free (288 = 32 mod 128);
             // an odd super-block count per row falls back to one (144-byte rows, 2-way conflicts)
-            return (K % 512 == 0) ? BoxGeom{512, 288} : BoxGeom{256, 144};
+            // (the tcgen05 variant reads a row per thread and keeps stages small: always one)
+            return (K % 512 == 0 && !tc) ? BoxGeom{512, 288} : BoxGeom{256, 144};
     }
 }
 
@@ -619,12 +546,14 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     }
     const int nt = max_m <= 8 ? 1 : max_m <= 16 ? 2 : max_m <= 32 ? 4 : 8;
     const int mp = nt * 8;
+    // 17..64 tokens over block-quantised weights: dequantise once into shared memory, multiply on tcgen05
+    const bool tc = fmt != IZB_W_BF16 && nt >= env_int("IZB_SKINNY_TC_MIN_NT", 4);
 
     // measured best residency: three CTAs per SM for Q8_0 (most ALU work per byte), two otherwise
     // measured best residency: three CTAs per SM for Q8_0 at up to 16 tokens (most ALU work per
     // byte), two otherwise; wide token groups need the whole SM's shared memory for one CTA
     int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", fmt == IZB_W_Q8_0 && nt <= 2 ? 3 : 2));
-    if (nt == 8 && !env_int("IZB_SKINNY_CTAS_PER_SM", 0)) ctas_per_sm = 1;
+    if ((nt == 8 || tc) && !env_int("IZB_SKINNY_CTAS_PER_SM", 0)) ctas_per_sm = 1;
     const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
     const int max_grid = ctx->sm_count * ctas_per_sm;
     const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_cast<int>(sizeof(SkinnyShared));
@@ -633,7 +562,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     auto min_stage = [&](int rows) {
         int worst = 0;
         for (int i = 0; i < n; ++i) {
-            const BoxGeom bg = box_geom(fmt, static_cast<int>(probs[i].K));
+            const BoxGeom bg = box_geom(fmt, static_cast<int>(probs[i].K), tc);
             worst = std::max(worst, rows * bg.w_row_bytes + (bg.kbox / 64) * mp * 128);
         }
         return worst;
@@ -653,7 +582,10 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     int rt = 1, ks = 4;
     const int forced_rt = env_int("IZB_SKINNY_RT", 0), forced_ks = env_int("IZB_SKINNY_KS", 0);
     const int forced_rows = env_int("IZB_SKINNY_TILE_ROWS", 0);
-    if (forced_rt && forced_ks) {
+    if (tc) {
+        rt = 2;  // 128-row tiles = the 128 TMEM lanes of one accumulator
+        ks = 1;
+    } else if (forced_rt && forced_ks) {
         rt = forced_rt;
         ks = forced_ks;
         if (rt * nt > 8 || (rt == 4 && ks == 1)) return IZB_ERR_UNSUPPORTED;
@@ -679,7 +611,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         SkinnyProblem& q = out[i];
         std::memset(&q, 0, sizeof(q));
         const int K = static_cast<int>(a.K), N = static_cast<int>(a.N), M = static_cast<int>(a.M);
-        const BoxGeom bg = box_geom(fmt, K);
+        const BoxGeom bg = box_geom(fmt, K, tc);
         const int boxes_total = K / bg.kbox;
         const int box_stage = tile_rows * bg.w_row_bytes + (bg.kbox / 64) * mp * 128;
         // k-boxes per stage: fill the stage target, keep every k-slice busy, divide the row evenly
@@ -735,7 +667,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         }
     }
 
-    const int red_raw = ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
+    // tc: this region holds the four 16 KB dequantised operand slices instead of k-split partial sums
+    const int red_raw = tc ? 4 * 128 * 128 : ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
     const int red_bytes = (red_raw + 1023) / 1024 * 1024;
     const int lite_bytes = (std::min(n, SK_LITE_MAX) * static_cast<int>(sizeof(ProbLite)) + 1023) / 1024 * 1024;
     int n_stages = (budget - red_bytes - lite_bytes) / stage_bytes;
@@ -760,6 +693,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     hdr->stage_bytes = stage_bytes;
     hdr->red_bytes = red_bytes;
     hdr->lite_bytes = lite_bytes;
+    hdr->tc = tc ? 1 : 0;
     hdr->smem_bytes = lite_bytes + red_bytes + n_stages * stage_bytes + 1024;  // slack to align the ring to 1024 bytes
     hdr->grid = std::min(tile_cursor, max_grid);
     hdr->y_dtype = y_dtype;
@@ -770,6 +704,7 @@ int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, 
                   const SkinnyProblem* single) {
     if (h.magic != SK_PLAN_MAGIC) return IZB_ERR_BAD_ARG;
     if (!dev_probs && !single) return IZB_ERR_BAD_ARG;
+    if (h.tc) return skinny_tc_launch(ctx, stream, h, dev_probs, single);
     static const SkinnyProblem dummy = {};
     const SkinnyProblem& s = single ? *single : dummy;
     switch (h.fmt) {

@@ -47,14 +47,95 @@ struct alignas(64) SkinnyPlanHeader {
     int n_stages, stage_bytes, red_bytes, smem_bytes;
     int grid, y_dtype;
     int lite_bytes;  // shared-memory bytes of the descriptor cache
-    int pad_[2];
+    int tc;          // 1: the dequantise-into-tcgen05 kernel (17..64 tokens over block-quantised weights)
+    int pad_[1];
 };
 static_assert(sizeof(SkinnyPlanHeader) == 64, "SkinnyPlanHeader layout");
+
+#ifdef __CUDACC__
+// The scalar fields of a problem descriptor, cached in shared memory at kernel start: a CTA meets
+// a different problem on almost every tile, and walking the descriptors in global memory was a
+// chain of dependent long-latency loads per tile.
+struct alignas(16) ProbLite {
+    void* y;
+    const __nv_bfloat16* bias;
+    int N, M, ldy, tile_start;
+    int n_chunks, nb, kbox, w_row_bytes;
+    int w_box_bytes, x_off, stage_tx, pad_;
+};
+static_assert(sizeof(ProbLite) == 64, "ProbLite layout");
+constexpr int SK_LITE_MAX = 160;  // problems cached; beyond that the descriptor is read from global memory
+
+__device__ __forceinline__ ProbLite lite_from(const SkinnyProblem& q) {
+    ProbLite l;
+    l.y = q.y; l.bias = q.bias;
+    l.N = q.N; l.M = q.M; l.ldy = q.ldy; l.tile_start = q.tile_start;
+    l.n_chunks = q.n_chunks; l.nb = q.nb; l.kbox = q.kbox; l.w_row_bytes = q.w_row_bytes;
+    l.w_box_bytes = q.w_box_bytes; l.x_off = q.x_off; l.stage_tx = q.stage_tx; l.pad_ = 0;
+    return l;
+}
+
+// Index of the problem that owns `tile`: last p with tile_start[p] <= tile (binary search).
+__device__ __forceinline__ int find_problem(const ProbLite* lite, int n_cached, const SkinnyProblem* plist, int n_probs,
+                                            int tile) {
+    int lo = 0, hi = n_probs;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        const int start = mid < n_cached ? lite[mid].tile_start : plist[mid].tile_start;
+        if (start <= tile) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float half_bits_to_f32(uint32_t h) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
+}
+
+// Four int8 in a word -> two f16x2 registers holding the exact integers.
+// byte ^ 0x80 is q+128 as an unsigned byte; under the high byte 0x64 it reads as the fp16
+// value 1024 + q + 128 (fp16 has a unit step from 1024 to 2048), and one packed subtraction
+// of 1152 leaves q.
+__device__ __forceinline__ void s8x4_to_f16x4(uint32_t w, uint32_t& p01, uint32_t& p23) {
+    const uint32_t u = w ^ 0x80808080u;
+    const uint32_t h01 = prmt(u, 0x64646464u, 0x5140), h23 = prmt(u, 0x64646464u, 0x7362);
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p01) : "r"(h01), "r"(0x64806480u));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p23) : "r"(h23), "r"(0x64806480u));
+}
+
+// A bf16 pair -> the same two values as an fp16 pair.  Exact for 2^-24 <= |x| <= 65504 (bf16
+// carries 8 significant bits, fp16 11); larger magnitudes saturate to +-65504.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t b) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(b & 0xFFFF0000u)), "f"(__uint_as_float(b << 16)));
+    return r;
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t bcast_bf16x2(float v) { return pack_bf16x2(v, v); }
+
+#endif  // __CUDACC__
 
 // Host side (skinny.cu)
 int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, SkinnyPlanHeader* hdr,
                       SkinnyProblem* out);
 int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
                   const SkinnyProblem* single);
+// skinny_tc.cu
+int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
+                     const SkinnyProblem* single);
 
 }  // namespace izb
