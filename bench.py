@@ -38,10 +38,12 @@ WORKLOADS = {
     "qwen3-0.6b-q8_0-m1": ("q8_0", 1),
     "qwen3-0.6b-q8_0-m4": ("q8_0", 4),
     "qwen3-0.6b-q8_0-m16": ("q8_0", 16),
+    "qwen3-0.6b-q8_0-m32": ("q8_0", 32),
     "qwen3-0.6b-q8_0-m64": ("q8_0", 64),
     "qwen3-0.6b-q4_k-m1": ("q4_k", 1),
     "qwen3-0.6b-q4_k-m4": ("q4_k", 4),
     "qwen3-0.6b-q4_k-m16": ("q4_k", 16),
+    "qwen3-0.6b-q4_k-m32": ("q4_k", 32),
     "qwen3-0.6b-q4_k-m64": ("q4_k", 64),
     "qwen3-0.6b-bf16-m1": ("bf16", 1),
 }

@@ -615,7 +615,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         const int boxes_total = K / bg.kbox;
         const int box_stage = tile_rows * bg.w_row_bytes + (bg.kbox / 64) * mp * 128;
         // k-boxes per stage: fill the stage target, keep every k-slice busy, divide the row evenly
-        int nb = std::max(1, std::min(boxes_total, stage_target / box_stage));
+        int nb = tc ? 1 : std::max(1, std::min(boxes_total, stage_target / box_stage));  // tc: one box per stage
         const int units_per_box = fmt == IZB_W_BF16 ? 1 : fmt == IZB_W_Q8_0 ? 4 : bg.kbox / 256;
         while (nb * units_per_box < ks && nb < boxes_total && (nb + 1) * box_stage <= 2 * stage_target) ++nb;
         while (nb > 1 && boxes_total % nb != 0) --nb;
@@ -634,7 +634,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         q.x_off = (nb * q.w_box_bytes + 1023) / 1024 * 1024;
         const int x_bytes = nb * (bg.kbox / 64) * mp * 128;
         q.stage_tx = nb * q.w_box_bytes + x_bytes;
-        stage_bytes = std::max(stage_bytes, (q.x_off + x_bytes + 1023) / 1024 * 1024);
+        // tc: weights and activations travel in separate rings; stage_bytes describes the weight ring
+        stage_bytes = std::max(stage_bytes, tc ? q.x_off : (q.x_off + x_bytes + 1023) / 1024 * 1024);
         tile_cursor += (N + tile_rows - 1) / tile_rows;
 
         // weights: [k-box][row][elements of one box row]
@@ -672,13 +673,30 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const int red_bytes = (red_raw + 1023) / 1024 * 1024;
     const int lite_bytes = (std::min(n, SK_LITE_MAX) * static_cast<int>(sizeof(ProbLite)) + 1023) / 1024 * 1024;
     int n_stages = (budget - red_bytes - lite_bytes) / stage_bytes;
+    int x_stages = 0;
     const int forced_stages = env_int("IZB_SKINNY_STAGES", 0);
-    if (forced_stages) n_stages = forced_stages;
-    n_stages = std::min(n_stages, SK_MAX_STAGES);
-    if (n_stages < 2) {
-        // A single stage pair must still fit one CTA per SM.
+    if (tc) {
+        // two rings: raw weight boxes (released as soon as they are in registers) and activation
+        // slices (released when the MMAs complete); grow them in turn while they fit
+        const int x_stage = 4 * mp * 128;
+        int room = budget - red_bytes - lite_bytes - 2 * stage_bytes - 2 * x_stage;
+        if (room < 0) return IZB_ERR_UNSUPPORTED;
         n_stages = 2;
-        if (lite_bytes + red_bytes + 2 * stage_bytes > ctx->max_smem_optin - 2048) return IZB_ERR_UNSUPPORTED;
+        x_stages = 2;
+        for (bool grew = true; grew;) {
+            grew = false;
+            if (n_stages < std::min(4, SK_MAX_STAGES) && room >= stage_bytes) { ++n_stages; room -= stage_bytes; grew = true; }
+            if (x_stages < 3 && room >= x_stage) { ++x_stages; room -= x_stage; grew = true; }
+        }
+        if (forced_stages) n_stages = std::min(forced_stages, n_stages);
+    } else {
+        if (forced_stages) n_stages = forced_stages;
+        n_stages = std::min(n_stages, SK_MAX_STAGES);
+        if (n_stages < 2) {
+            // A single stage pair must still fit one CTA per SM.
+            n_stages = 2;
+            if (lite_bytes + red_bytes + 2 * stage_bytes > ctx->max_smem_optin - 2048) return IZB_ERR_UNSUPPORTED;
+        }
     }
 
     std::memset(hdr, 0, sizeof(*hdr));
@@ -694,7 +712,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     hdr->red_bytes = red_bytes;
     hdr->lite_bytes = lite_bytes;
     hdr->tc = tc ? 1 : 0;
-    hdr->smem_bytes = lite_bytes + red_bytes + n_stages * stage_bytes + 1024;  // slack to align the ring to 1024 bytes
+    hdr->x_stages = x_stages;
+    hdr->smem_bytes = lite_bytes + red_bytes + n_stages * stage_bytes + x_stages * 4 * mp * 128 + 1024;  // slack to align the ring to 1024 bytes
     hdr->grid = std::min(tile_cursor, max_grid);
     hdr->y_dtype = y_dtype;
     return IZB_OK;

@@ -48,9 +48,10 @@ struct alignas(64) SkinnyPlanHeader {
     int grid, y_dtype;
     int lite_bytes;  // shared-memory bytes of the descriptor cache
     int tc;          // 1: the dequantise-into-tcgen05 kernel (17..64 tokens over block-quantised weights)
-    int pad_[1];
+    int x_stages;    // tc: depth of the separate activation ring (n_stages / stage_bytes describe the raw weight ring)
+    int pad_[16];
 };
-static_assert(sizeof(SkinnyPlanHeader) == 64, "SkinnyPlanHeader layout");
+static_assert(sizeof(SkinnyPlanHeader) == 128, "SkinnyPlanHeader layout");
 
 #ifdef __CUDACC__
 // The scalar fields of a problem descriptor, cached in shared memory at kernel start: a CTA meets
