@@ -83,6 +83,25 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
+// Same, for waiters that can afford to wake late (copy producers several stages ahead): sleeps
+// between polls instead of competing with the computing warps for issue slots.
+__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        __nanosleep(64);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 0xFFu) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
 // 1-D bulk copy global -> shared (TMA engine), completion counted on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {

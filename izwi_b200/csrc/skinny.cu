@@ -546,8 +546,9 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     }
     const int nt = max_m <= 8 ? 1 : max_m <= 16 ? 2 : max_m <= 32 ? 4 : 8;
     const int mp = nt * 8;
-    // 17..64 tokens over block-quantised weights: dequantise once into shared memory, multiply on tcgen05
-    const bool tc = fmt != IZB_W_BF16 && nt >= env_int("IZB_SKINNY_TC_MIN_NT", 4);
+    // wide token groups over block-quantised weights: dequantise once into shared memory, multiply
+    // on tcgen05.  Measured crossover against the mma.sync consumers: Q4_K from 17 tokens, Q8_0 from 33.
+    const bool tc = fmt != IZB_W_BF16 && nt >= env_int("IZB_SKINNY_TC_MIN_NT", fmt == IZB_W_Q8_0 ? 8 : 4);
 
     // measured best residency: three CTAs per SM for Q8_0 (most ALU work per byte), two otherwise
     // measured best residency: three CTAs per SM for Q8_0 at up to 16 tokens (most ALU work per

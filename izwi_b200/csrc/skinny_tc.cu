@@ -17,8 +17,8 @@
 
 namespace izb {
 
-constexpr int STC_DQ_WARPS = 16;                      // dequantise (all) + epilogue (first eight)
-constexpr int STC_EPI_WARPS = 8;
+constexpr int STC_DQ_WARPS = 16;                      // dequantise + epilogue
+constexpr int STC_EPI_WARPS = STC_DQ_WARPS;  // every converting warp reads out 16 token columns of its lane quarter
 constexpr int STC_WPROD_WARP = STC_DQ_WARPS, STC_XPROD_WARP = STC_DQ_WARPS + 1, STC_MMA_WARP = STC_DQ_WARPS + 2;
 constexpr int STC_THREADS = 32 * (STC_DQ_WARPS + 3);  // + two producer warps + MMA warp
 constexpr int STC_MAX_X_STAGES = 4;
@@ -189,27 +189,31 @@ __device__ __forceinline__ bool convert_box(StcShared& sh, uint32_t wrow, uint32
     return true;
 }
 
-// Accumulator -> y for one finished tile: warp w of the first eight reads TMEM lanes 32 (w%4) .. +31
-// (weight rows) and token columns 32 (w/4) .. +31.
+// Accumulator -> y for one finished tile: warp w reads TMEM lanes 32 (w%4) .. +31 (weight rows) and
+// token columns 16 (w/4) .. +15; every store instruction writes 32 consecutive rows of one token.
+template <typename T>
+__device__ __forceinline__ void stc_store_cols(T* y, long long ldy, const float (&v)[16], float b, int n_tok) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        if (i < n_tok) {
+            if constexpr (sizeof(T) == 4) *y = v[i] + b;
+            else *y = __float2bfloat16_rn(v[i] + b);
+        }
+        y += ldy;
+    }
+}
 __device__ __forceinline__ void stc_epilogue(const ProbLite& L, int row0, uint32_t tmem_acc, int warp, int lane, int mp,
                                              int y_dtype) {
-    const int cc = (warp >> 2) * 32;
+    const int cc = (warp >> 2) * 16;
     if (cc >= mp) return;
     const int row = row0 + (warp & 3) * 32 + lane;
-    const float b = (L.bias && row < L.N) ? __bfloat162float(L.bias[row]) : 0.f;
-    float v[32];
-    tc_ld_32x32(tmem_acc + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(cc), v);
-    if (row < L.N) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int tok = cc + i;
-            if (tok < L.M) {
-                const long long idx = static_cast<long long>(tok) * L.ldy + row;
-                if (y_dtype == IZB_F32) static_cast<float*>(L.y)[idx] = v[i] + b;
-                else static_cast<__nv_bfloat16*>(L.y)[idx] = __float2bfloat16_rn(v[i] + b);
-            }
-        }
-    }
+    float v[16];
+    tc_ld_32x16(tmem_acc + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(cc), v);
+    if (row >= L.N || cc >= L.M) return;
+    const float b = L.bias ? __bfloat162float(L.bias[row]) : 0.f;
+    const long long first = static_cast<long long>(cc) * L.ldy + row;
+    if (y_dtype == IZB_F32) stc_store_cols(static_cast<float*>(L.y) + first, L.ldy, v, b, L.M - cc);
+    else stc_store_cols(static_cast<__nv_bfloat16*>(L.y) + first, L.ldy, v, b, L.M - cc);
 }
 
 // Waits (bounded) for every copy a producer still has in flight on ring `full`, so that no TMA
@@ -295,7 +299,7 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                 const ProbLite L = p < n_cached ? lite[p] : lite_from(*P);
                 const int row0 = (tile - L.tile_start) * STC_TILE_ROWS;
                 for (int c = 0; c < L.n_chunks; ++c) {
-                    if (!mbar_wait_bounded(smem_u32(&empty[stage]), phase ^ 1u, abort_flag)) {
+                    if (!mbar_wait_bounded_relaxed(smem_u32(&empty[stage]), phase ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
@@ -393,7 +397,9 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
         unsigned int n = 0;
         int prev_p = 0, prev_row0 = 0;
         [[maybe_unused]] int tr = 0;
-        [[maybe_unused]] const int role = (lane != 0) ? -1 : warp == 0 ? 1 : warp == STC_DQ_WARPS - 1 ? 2 : -1;
+        [[maybe_unused]] const int role = (lane != 0) ? -1 : warp == 0 ? 1 : -1;
+        [[maybe_unused]] const int erole = (lane == 0 && warp == 0) ? 2 : -1;
+        [[maybe_unused]] int etr = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int p = find_problem(lite, n_cached, plist, n_probs, tile);
             const int n_chunks = p < n_cached ? lite[p].n_chunks : plist[p].n_chunks;
@@ -421,14 +427,17 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                 // have had time to finish, and the tensor core already works on this tile meanwhile
                 if (c == 0 && it > 0 && warp < STC_EPI_WARPS && ok) {
                     const int acc = (it - 1) & 1;
+                    STC_TRACE(erole, etr);
                     if (!mbar_wait_bounded(smem_u32(&sh.acc_full[acc]), static_cast<uint32_t>(((it - 1) >> 1) & 1), abort_flag)) {
                         ok = false;
                         break;
                     }
+                    STC_TRACE(erole, etr);
                     tc_fence_after();
                     stc_epilogue(prev_p < n_cached ? lite[prev_p] : lite_from(plist[prev_p]), prev_row0,
                                  tmem_base + static_cast<uint32_t>(acc * STC_ACC_COLS), warp, lane, mp, y_dtype);
                     tc_fence_before();
+                    STC_TRACE(erole, etr);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sh.acc_empty[acc]));
                 }
