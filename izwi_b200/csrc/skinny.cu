@@ -549,21 +549,27 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     // wide token groups over block-quantised weights: dequantise once into shared memory, multiply
     // on tcgen05.  Measured crossover against the mma.sync consumers: Q4_K from 17 tokens, Q8_0 from 33.
     const bool tc = fmt != IZB_W_BF16 && nt >= env_int("IZB_SKINNY_TC_MIN_NT", fmt == IZB_W_Q8_0 ? 8 : 4);
+    // one to four tokens over block-quantised weights: integer dot products against activations in
+    // 16-bit block fixed point (skinny_gemv.cu); gemv = tokens the kernel is instantiated for
+    const int gemv_max = env_int("IZB_SKINNY_GEMV_MAX_M", 2);
+    const int gemv = (fmt != IZB_W_BF16 && max_m <= std::min(gemv_max, 4)) ? (max_m <= 1 ? 1 : max_m <= 2 ? 2 : 4) : 0;
+    const bool one_sb = tc || gemv != 0;  // one Q4_K super-block per box row
 
     // measured best residency: three CTAs per SM for Q8_0 (most ALU work per byte), two otherwise
     // measured best residency: three CTAs per SM for Q8_0 at up to 16 tokens (most ALU work per
     // byte), two otherwise; wide token groups need the whole SM's shared memory for one CTA
-    int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", fmt == IZB_W_Q8_0 && nt <= 2 ? 3 : 2));
+    int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", gemv ? 4 : (fmt == IZB_W_Q8_0 && nt <= 2) ? 3 : 2));
     if ((nt == 8 || tc) && !env_int("IZB_SKINNY_CTAS_PER_SM", 0)) ctas_per_sm = 1;
     const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
     const int max_grid = ctx->sm_count * ctas_per_sm;
-    const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_cast<int>(sizeof(SkinnyShared));
+    const int static_smem = gemv ? 256 + 512 * gemv : static_cast<int>(sizeof(SkinnyShared));  // barriers (+ gemv: k-half sums)
+    const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_smem;
 
     // Bytes of the smallest possible stage (one weight box + its activation chunks) of a row tile.
     auto min_stage = [&](int rows) {
         int worst = 0;
         for (int i = 0; i < n; ++i) {
-            const BoxGeom bg = box_geom(fmt, static_cast<int>(probs[i].K), tc);
+            const BoxGeom bg = box_geom(fmt, static_cast<int>(probs[i].K), one_sb);
             worst = std::max(worst, rows * bg.w_row_bytes + (bg.kbox / 64) * mp * 128);
         }
         return worst;
@@ -586,6 +592,9 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     if (tc) {
         rt = 2;  // 128-row tiles = the 128 TMEM lanes of one accumulator
         ks = 1;
+    } else if (gemv) {
+        rt = 2;  // 64-row tiles: two warps per k-half, one row per thread
+        ks = 2;
     } else if (forced_rt && forced_ks) {
         rt = forced_rt;
         ks = forced_ks;
@@ -606,15 +615,15 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const int tile_rows = 16 * rt * (SK_CONSUMER_WARPS / ks);
     const int rg = SK_CONSUMER_WARPS / ks;
 
-    int stage_bytes = 0, tile_cursor = 0;
+    int stage_bytes = 0, tile_cursor = 0, xq_stage = 0;
     for (int i = 0; i < n; ++i) {
         const izb_linear_args& a = probs[i];
         SkinnyProblem& q = out[i];
         std::memset(&q, 0, sizeof(q));
         const int K = static_cast<int>(a.K), N = static_cast<int>(a.N), M = static_cast<int>(a.M);
-        const BoxGeom bg = box_geom(fmt, K, tc);
+        const BoxGeom bg = box_geom(fmt, K, one_sb);
         const int boxes_total = K / bg.kbox;
-        const int box_stage = tile_rows * bg.w_row_bytes + (bg.kbox / 64) * mp * 128;
+        const int box_stage = tile_rows * bg.w_row_bytes + (bg.kbox / 64) * (gemv ? gemv : mp) * 128;
         // k-boxes per stage: fill the stage target, keep every k-slice busy, divide the row evenly
         int nb = tc ? 1 : std::max(1, std::min(boxes_total, stage_target / box_stage));  // tc: one box per stage
         const int units_per_box = fmt == IZB_W_BF16 ? 1 : fmt == IZB_W_Q8_0 ? 4 : bg.kbox / 256;
@@ -633,9 +642,13 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         q.w_row_bytes = bg.w_row_bytes;
         q.w_box_bytes = tile_rows * bg.w_row_bytes;
         q.x_off = (nb * q.w_box_bytes + 1023) / 1024 * 1024;
-        const int x_bytes = nb * (bg.kbox / 64) * mp * 128;
+        // gemv: only the tokens the kernel is instantiated for are copied, unswizzled (no tensor-core read)
+        const int x_rows = gemv ? gemv : mp;
+        const int x_bytes = nb * (bg.kbox / 64) * x_rows * 128;
         q.stage_tx = nb * q.w_box_bytes + x_bytes;
         // tc: weights and activations travel in separate rings; stage_bytes describes the weight ring
+        // gemv: converted activations (576 bytes per token and box) live beside the ring, one slot per stage
+        xq_stage = std::max(xq_stage, gemv ? nb * gemv * 576 : 0);
         stage_bytes = std::max(stage_bytes, tc ? q.x_off : (q.x_off + x_bytes + 1023) / 1024 * 1024);
         tile_cursor += (N + tile_rows - 1) / tile_rows;
 
@@ -662,17 +675,23 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         {
             const uint64_t dims[3] = {64, static_cast<uint64_t>(M), static_cast<uint64_t>(K / 64)};
             const uint64_t strides[2] = {static_cast<uint64_t>(a.ldx) * 2, 128};
-            const uint32_t box[3] = {64, static_cast<uint32_t>(mp), static_cast<uint32_t>(nb * (bg.kbox / 64))};
+            const uint32_t box[3] = {64, static_cast<uint32_t>(x_rows), static_cast<uint32_t>(nb * (bg.kbox / 64))};
             rc = tma_encode(&q.tmap_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.x, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
+                            gemv ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc != IZB_OK) return rc;
         }
     }
 
-    // tc: this region holds the four 16 KB dequantised operand slices instead of k-split partial sums
-    const int red_raw = tc ? 4 * 128 * 128 : ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
-    const int red_bytes = (red_raw + 1023) / 1024 * 1024;
     const int lite_bytes = (std::min(n, SK_LITE_MAX) * static_cast<int>(sizeof(ProbLite)) + 1023) / 1024 * 1024;
+    // this region holds: tc, the four 16 KB operand slices; gemv, the converted activations of every stage;
+    // otherwise the k-split partial sums
+    int red_raw = tc ? 4 * 128 * 128 : ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
+    if (gemv) {
+        int s = SK_MAX_STAGES;
+        while (s > 2 && lite_bytes + (s * xq_stage + 1023) / 1024 * 1024 + s * stage_bytes > budget) --s;
+        red_raw = s * xq_stage;
+    }
+    const int red_bytes = (red_raw + 1023) / 1024 * 1024;
     int n_stages = (budget - red_bytes - lite_bytes) / stage_bytes;
     int x_stages = 0;
     const int forced_stages = env_int("IZB_SKINNY_STAGES", 0);
@@ -714,6 +733,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     hdr->lite_bytes = lite_bytes;
     hdr->tc = tc ? 1 : 0;
     hdr->x_stages = x_stages;
+    hdr->gemv = gemv;
+    hdr->xq_stage_bytes = xq_stage;
     hdr->smem_bytes = lite_bytes + red_bytes + n_stages * stage_bytes + x_stages * 4 * mp * 128 + 1024;  // slack to align the ring to 1024 bytes
     hdr->grid = std::min(tile_cursor, max_grid);
     hdr->y_dtype = y_dtype;
@@ -725,6 +746,7 @@ int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, 
     if (h.magic != SK_PLAN_MAGIC) return IZB_ERR_BAD_ARG;
     if (!dev_probs && !single) return IZB_ERR_BAD_ARG;
     if (h.tc) return skinny_tc_launch(ctx, stream, h, dev_probs, single);
+    if (h.gemv) return skinny_gemv_launch(ctx, stream, h, dev_probs, single);
     static const SkinnyProblem dummy = {};
     const SkinnyProblem& s = single ? *single : dummy;
     switch (h.fmt) {

@@ -49,7 +49,9 @@ struct alignas(64) SkinnyPlanHeader {
     int lite_bytes;  // shared-memory bytes of the descriptor cache
     int tc;          // 1: the dequantise-into-tcgen05 kernel (17..64 tokens over block-quantised weights)
     int x_stages;    // tc: depth of the separate activation ring (n_stages / stage_bytes describe the raw weight ring)
-    int pad_[16];
+    int gemv;        // 1, 2 or 4: the integer-dot-product kernel for that many tokens (block-quantised weights); 0: off
+    int xq_stage_bytes;  // gemv: bytes of converted activations per stage (red_bytes holds all stages)
+    int pad_[14];
 };
 static_assert(sizeof(SkinnyPlanHeader) == 128, "SkinnyPlanHeader layout");
 
@@ -138,5 +140,8 @@ int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr
 // skinny_tc.cu
 int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
                      const SkinnyProblem* single);
+// skinny_gemv.cu
+int skinny_gemv_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
+                       const SkinnyProblem* single);
 
 }  // namespace izb

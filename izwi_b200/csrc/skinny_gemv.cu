@@ -1,0 +1,449 @@
+// Block-quantised linear layers for 1..4 tokens: integer dot products on the CUDA cores.
+//
+// Same plan, descriptors and TMA producer as the weight-streaming kernel (skinny.cu).  Lifting every
+// int8 / 4-bit code to a floating-point tensor-core operand costs 3..4 instructions per weight, which
+// bounds that kernel below the HBM rate.  Here the codes stay integers: one extra warp re-expresses
+// each 32-value block of the activations as 16-bit fixed point (X = round(x * 2^(14-e)), e the
+// exponent of the block maximum: exact for every bf16 value within 2^-7 of the maximum, absolute
+// error <= 2^-15 of the maximum otherwise), split into a signed high byte and an unsigned low byte,
+// and the consumers accumulate code * X with dp4a (four products per instruction, exact in int32).
+// One conversion to fp32 and one multiply by (block scale * 2^(e-14)) per block and token finish the
+// job: about one instruction per weight for one token.
+//
+// Tile = 64 weight rows; warps 0,1 take the first 128 k of every 256-k box for 32 rows each, warps
+// 2,3 the second 128 k; one thread owns one row (16-byte loads, rows 272 or 144 bytes apart: no
+// bank conflicts).  Warp 4 issues the copies, warp 5 converts the activations of each stage.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "skinny.cuh"
+#include "tma.cuh"
+
+namespace izb {
+
+constexpr int GV_CONSUMER_WARPS = 4;
+constexpr int GV_PROD_WARP = GV_CONSUMER_WARPS, GV_CONV_WARP = GV_CONSUMER_WARPS + 1;
+constexpr int GV_THREADS = 32 * (GV_CONSUMER_WARPS + 2);
+constexpr int GV_TILE_ROWS = 64;
+// converted activations of one token and one 256-k box: high bytes, low bytes, 8 block scales, 8 block sums
+constexpr int GV_XQ_BYTES = 256 + 256 + 32 + 32;
+constexpr int GV_XQ_XL = 256, GV_XQ_XS = 512, GV_XQ_SX = 544;
+
+template <int MT>
+struct GvShared {
+    unsigned long long full[SK_MAX_STAGES];    // copies landed
+    unsigned long long xready[SK_MAX_STAGES];  // activations of the stage converted
+    unsigned long long empty[SK_MAX_STAGES];   // consumers done with the stage
+    float red[2][GV_TILE_ROWS * MT];           // partial sums of the second k-half, double-buffered by tile parity
+    int abort_flag;
+};
+
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+    uint32_t d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(static_cast<uint32_t>(c)));
+    return static_cast<int>(d);
+}
+__device__ __forceinline__ void sts64v(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void sts32f(uint32_t addr, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+
+// Exact int32 -> fp32 for |v| < 2^22 on the integer and fp32 pipes (the conversion unit runs at a
+// quarter of their rate): 1.5 * 2^23 + v is representable, so its bit pattern is the magic's plus v.
+__device__ __forceinline__ float small_int_to_f32(int v) {
+    return __int_as_float(0x4B400000 + v) - 12582912.0f;
+}
+
+// One lane's share of the conversion: 8 consecutive activations (one 16-byte unit) of one token;
+// the four lanes of a 32-value block agree on the block exponent by shuffle.
+__device__ __forceinline__ void gv_convert_unit(const uint4 v, uint32_t dst, int lane) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t amax = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) amax = max(amax, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const uint32_t eb = amax >> 7;  // biased exponent of the block maximum
+    // X = x * 2^(14-e) rounds into [-32640, 32640]; blocks below 2^-111 count as zero, Inf/NaN poison the scale
+    const float sf = (eb >= 16u && eb < 255u) ? __uint_as_float((268u - eb) << 23) : 0.f;
+    const float xs = eb == 255u ? __uint_as_float(0x7FC00000u) : eb >= 16u ? __uint_as_float((eb - 14u) << 23) : 0.f;
+    int X[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        X[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * sf);
+        X[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * sf);
+    }
+    int isum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) isum += X[i];
+    isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 1);
+    isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 2);
+    // bytes 0 (low) and 1 (high) of four values each into one word per plane
+    const uint32_t u0 = prmt(X[0], X[1], 0x5140), v0 = prmt(X[2], X[3], 0x5140);
+    const uint32_t u1 = prmt(X[4], X[5], 0x5140), v1 = prmt(X[6], X[7], 0x5140);
+    sts64v(dst + static_cast<uint32_t>(8 * lane), prmt(u0, v0, 0x7632), prmt(u1, v1, 0x7632));
+    sts64v(dst + static_cast<uint32_t>(GV_XQ_XL + 8 * lane), prmt(u0, v0, 0x5410), prmt(u1, v1, 0x5410));
+    if ((lane & 3) == 0) {
+        sts32f(dst + static_cast<uint32_t>(GV_XQ_XS + lane), xs);  // block lane/4: 4 bytes each
+        sts32f(dst + static_cast<uint32_t>(GV_XQ_SX + lane), xs * static_cast<float>(isum));
+    }
+}
+
+// Q8_0: blocks 2P and 2P+1 (P = 0..3: pair of the 256-k box) of one row against MT tokens.
+// The pair is the 68 bytes from byte 68 P of the row = words P .. P+16 of the five 16-byte units
+// that start at byte 64 P (see skinny_tc.cu for the same extraction).
+template <int P, int MT>
+__device__ __forceinline__ void gv_pair_q8_0(float (&acc)[MT], uint32_t wrow, uint32_t xq, int xq_tok_stride) {
+    uint32_t W[20];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+        const uint4 v = lds128(wrow + static_cast<uint32_t>(64 * P + 16 * i));
+        W[4 * i] = v.x; W[4 * i + 1] = v.y; W[4 * i + 2] = v.z; W[4 * i + 3] = v.w;
+    }
+    uint32_t q[2][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        q[0][i] = prmt(W[P + i], W[P + i + 1], 0x5432);  // codes start 2 bytes into word P
+        q[1][i] = W[P + 9 + i];
+    }
+    const float d0 = half_bits_to_f32(W[P]), d1 = half_bits_to_f32(W[P + 8] >> 16);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const uint32_t xm = xq + static_cast<uint32_t>(m * xq_tok_stride);
+        const float xs0 = lds32f(xm + static_cast<uint32_t>(GV_XQ_XS + 8 * P));
+        const float xs1 = lds32f(xm + static_cast<uint32_t>(GV_XQ_XS + 8 * P + 4));
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            int th[2] = {0, 0}, tl[2] = {0, 0};  // two chains each: the dot products of a block are independent
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint4 xh = lds128(xm + static_cast<uint32_t>(64 * P + 32 * b + 16 * i));
+                const uint4 xl = lds128(xm + static_cast<uint32_t>(GV_XQ_XL + 64 * P + 32 * b + 16 * i));
+                th[0] = dp4a_ss(q[b][4 * i], xh.x, th[0]); tl[0] = dp4a_su(q[b][4 * i], xl.x, tl[0]);
+                th[1] = dp4a_ss(q[b][4 * i + 1], xh.y, th[1]); tl[1] = dp4a_su(q[b][4 * i + 1], xl.y, tl[1]);
+                th[0] = dp4a_ss(q[b][4 * i + 2], xh.z, th[0]); tl[0] = dp4a_su(q[b][4 * i + 2], xl.z, tl[0]);
+                th[1] = dp4a_ss(q[b][4 * i + 3], xh.w, th[1]); tl[1] = dp4a_su(q[b][4 * i + 3], xl.w, tl[1]);
+            }
+            // |sum of 32 code * byte products| < 2^20: exact through the magic-number conversion
+            const float t = fmaf(small_int_to_f32(th[0] + th[1]), 256.0f, small_int_to_f32(tl[0] + tl[1]));
+            acc[m] = fmaf((b ? d1 : d0) * (b ? xs1 : xs0), t, acc[m]);
+        }
+    }
+}
+
+// Q4_K: sub-blocks 4 KH .. 4 KH + 3 (code groups 2 KH, 2 KH + 1) of one 144-byte super-block row.
+template <int KH, int MT>
+__device__ __forceinline__ void gv_half_q4_k(float (&acc)[MT], uint32_t wrow, uint32_t xq, int xq_tok_stride) {
+    const uint4 hd = lds128(wrow);
+    const float d = half_bits_to_f32(hd.x), dmin = half_bits_to_f32(hd.x >> 16);
+    uint32_t sc4, mn4;  // the four 6-bit scales / minimums of this half, one per byte
+    if (KH == 0) {
+        sc4 = hd.y & 0x3F3F3F3Fu;
+        mn4 = hd.z & 0x3F3F3F3Fu;
+    } else {
+        sc4 = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+        mn4 = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+    }
+    // the four scale * d and minimum * dmin products of this half (6-bit integers lifted exactly)
+    float dsc[4], dm[4];
+#pragma unroll
+    for (int sl = 0; sl < 4; ++sl) {
+        dsc[sl] = d * small_int_to_f32(static_cast<int>((sc4 >> (8 * sl)) & 0xFFu)) * ((sl & 1) ? 0.0625f : 1.0f);
+        dm[sl] = dmin * small_int_to_f32(static_cast<int>((mn4 >> (8 * sl)) & 0xFFu));
+    }
+    uint4 xsv[MT], sxv[MT];  // block scales and block sums of the activations for sub-blocks 4 KH .. 4 KH + 3
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        xsv[m] = lds128(xq + static_cast<uint32_t>(m * xq_tok_stride + GV_XQ_XS + 16 * KH));
+        sxv[m] = lds128(xq + static_cast<uint32_t>(m * xq_tok_stride + GV_XQ_SX + 16 * KH));
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {  // code group 2 KH + j: low nibbles sub-block s, high nibbles s + 1
+        const uint4 c0 = lds128(wrow + static_cast<uint32_t>(16 + (2 * KH + j) * 32));
+        const uint4 c1 = lds128(wrow + static_cast<uint32_t>(32 + (2 * KH + j) * 32));
+        const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+            const int sl = 2 * j + hi;  // sub-block inside this half
+            uint32_t n[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) n[i] = hi ? (cw[i] & 0xF0F0F0F0u) : (cw[i] & 0x0F0F0F0Fu);  // hi: 16 n (scale / 16)
+            const int s = 4 * KH + sl;  // sub-block of the super-block = 32-value block of the box
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const uint32_t xm = xq + static_cast<uint32_t>(m * xq_tok_stride);
+                int th[2] = {0, 0}, tl[2] = {0, 0};
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint4 xh = lds128(xm + static_cast<uint32_t>(32 * s + 16 * i));
+                    const uint4 xl = lds128(xm + static_cast<uint32_t>(GV_XQ_XL + 32 * s + 16 * i));
+                    th[0] = dp4a_us(n[4 * i], xh.x, th[0]); tl[0] = dp4a_uu(n[4 * i], xl.x, tl[0]);
+                    th[1] = dp4a_us(n[4 * i + 1], xh.y, th[1]); tl[1] = dp4a_uu(n[4 * i + 1], xl.y, tl[1]);
+                    th[0] = dp4a_us(n[4 * i + 2], xh.z, th[0]); tl[0] = dp4a_uu(n[4 * i + 2], xl.z, tl[0]);
+                    th[1] = dp4a_us(n[4 * i + 3], xh.w, th[1]); tl[1] = dp4a_uu(n[4 * i + 3], xl.w, tl[1]);
+                }
+                // |sum| <= 32 * 240 * 255 < 2^21: exact through the magic-number conversion
+                const float t = fmaf(small_int_to_f32(th[0] + th[1]), 256.0f, small_int_to_f32(tl[0] + tl[1]));
+                const float xs = __uint_as_float(sl == 0 ? xsv[m].x : sl == 1 ? xsv[m].y : sl == 2 ? xsv[m].z : xsv[m].w);
+                const float sx = __uint_as_float(sl == 0 ? sxv[m].x : sl == 1 ? sxv[m].y : sl == 2 ? sxv[m].z : sxv[m].w);
+                acc[m] = fmaf(dsc[sl] * xs, t, acc[m]);
+                acc[m] = fmaf(-dm[sl], sx, acc[m]);
+            }
+        }
+    }
+}
+
+template <int FMT, int MT>
+__global__ void __launch_bounds__(GV_THREADS)
+    skinny_gemv_kernel(const SkinnyProblem* __restrict__ probs, const __grid_constant__ SkinnyProblem single, int n_probs,
+                       int total_tiles, int n_stages, int stage_bytes, int xq_stage_bytes, int xq_bytes, int lite_bytes,
+                       int y_dtype, int* status) {
+    extern __shared__ __align__(1024) uint8_t dyn_smem[];
+    __shared__ GvShared<MT> sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const SkinnyProblem* plist = probs ? probs : &single;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < n_stages; ++s) {
+            mbar_init(smem_u32(&sh.full[s]), 1);
+            mbar_init(smem_u32(&sh.xready[s]), 1);
+            mbar_init(smem_u32(&sh.empty[s]), GV_CONSUMER_WARPS);
+        }
+        sh.abort_flag = 0;
+        mbar_fence_init();
+    }
+    // dynamic shared memory: [descriptor cache][converted activations per stage][stage ring]; stage = [weight boxes][activations]
+    ProbLite* lite = reinterpret_cast<ProbLite*>(dyn_smem);
+    const int n_cached = min(n_probs, lite_bytes / static_cast<int>(sizeof(ProbLite)));
+    for (int i = threadIdx.x; i < n_cached; i += blockDim.x) lite[i] = lite_from(plist[i]);
+    __syncthreads();
+
+    volatile int* abort_flag = &sh.abort_flag;
+    const uint32_t xq0 = smem_u32(dyn_smem) + static_cast<uint32_t>(lite_bytes);
+    const uint32_t stage0 = xq0 + static_cast<uint32_t>(xq_bytes);
+
+    if (warp == GV_PROD_WARP) {
+        // ---------------- producer: one lane issues two tiled copies per stage ----------------
+        if (lane != 0) return;
+        int stage = 0, p = -1;
+        uint32_t phase = 0;
+        long long issued = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int np = find_problem(lite, n_cached, plist, n_probs, tile);
+            const bool moved = np != p;
+            p = np;
+            const SkinnyProblem* P = plist + p;
+            if (moved && probs) {
+                tma_fence_descriptor(&P->tmap_w);
+                tma_fence_descriptor(&P->tmap_x);
+            }
+            const ProbLite L = p < n_cached ? lite[p] : lite_from(*P);
+            const int row0 = (tile - L.tile_start) * GV_TILE_ROWS;
+            const int xchunks = L.nb * 4;
+            for (int c = 0; c < L.n_chunks; ++c) {
+                if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t fbar = smem_u32(&sh.full[stage]);
+                const uint32_t sbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
+                mbar_expect_tx(fbar, static_cast<uint32_t>(L.stage_tx));
+                tma_load_3d(sbase, &P->tmap_w, 0, row0, c * L.nb, fbar);
+                tma_load_3d(sbase + static_cast<uint32_t>(L.x_off), &P->tmap_x, 0, 0, c * xchunks, fbar);
+                ++issued;
+                if (++stage == n_stages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        if (!ok) {
+            // A wait gave up: let the copies still in flight land before the CTA's shared memory goes away.
+            const long long first = issued > n_stages ? issued - n_stages : 0;
+            for (long long f = first; f < issued; ++f) {
+                const uint32_t bar = smem_u32(&sh.full[f % n_stages]);
+                const uint32_t par = static_cast<uint32_t>((f / n_stages) & 1);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar, par)) {
+                    if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) break;
+                }
+            }
+            atomicExch(status, 5);
+        }
+        return;
+    }
+
+    if (warp == GV_CONV_WARP) {
+        // ---------------- converter: bf16 activations of each stage -> 16-bit block fixed point ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int p = find_problem(lite, n_cached, plist, n_probs, tile);
+            const ProbLite L = p < n_cached ? lite[p] : lite_from(plist[p]);
+            const int M = min(L.M, MT);
+            for (int c = 0; c < L.n_chunks; ++c) {
+                if (!mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t sbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
+                for (int b = 0; b < L.nb; ++b) {
+                    for (int m = 0; m < M; ++m) {
+                        // copied activations: [64-k chunk][token][128 bytes]; lane = chunk lane/8, 16-byte unit lane%8
+                        const uint4 v = lds128(sbase + static_cast<uint32_t>(L.x_off) +
+                                               static_cast<uint32_t>(((b * 4 + (lane >> 3)) * MT + m) * 128 + (lane & 7) * 16));
+                        gv_convert_unit(v, xq0 + static_cast<uint32_t>(stage * xq_stage_bytes + (b * MT + m) * GV_XQ_BYTES), lane);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh.xready[stage]));
+                if (++stage == n_stages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        if (!ok && lane == 0) atomicExch(status, 5);
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int kh = warp & 1;                  // which 128 k of every 256-k box
+    const int row = (warp >> 1) * 32 + lane;  // row inside the tile
+    int stage = 0, it = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        const int p = find_problem(lite, n_cached, plist, n_probs, tile);
+        const ProbLite L = p < n_cached ? lite[p] : lite_from(plist[p]);
+        const int row0 = (tile - L.tile_start) * GV_TILE_ROWS;
+
+        float acc[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+
+        for (int c = 0; c < L.n_chunks; ++c) {
+            if (ok && !mbar_wait_bounded(smem_u32(&sh.xready[stage]), phase, abort_flag)) ok = false;
+            if (ok && !mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) ok = false;  // already complete
+            if (ok) {
+                const uint32_t sbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
+                for (int b = 0; b < L.nb; ++b) {
+                    const uint32_t wrow = sbase + static_cast<uint32_t>(b * L.w_box_bytes + row * L.w_row_bytes);
+                    const uint32_t xq = xq0 + static_cast<uint32_t>(stage * xq_stage_bytes + b * MT * GV_XQ_BYTES);
+                    if constexpr (FMT == IZB_W_Q8_0) {
+                        if (kh == 0) {
+                            gv_pair_q8_0<0, MT>(acc, wrow, xq, GV_XQ_BYTES);
+                            gv_pair_q8_0<1, MT>(acc, wrow, xq, GV_XQ_BYTES);
+                        } else {
+                            gv_pair_q8_0<2, MT>(acc, wrow, xq, GV_XQ_BYTES);
+                            gv_pair_q8_0<3, MT>(acc, wrow, xq, GV_XQ_BYTES);
+                        }
+                    } else {
+                        if (kh == 0) gv_half_q4_k<0, MT>(acc, wrow, xq, GV_XQ_BYTES);
+                        else gv_half_q4_k<1, MT>(acc, wrow, xq, GV_XQ_BYTES);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.empty[stage]));
+            if (++stage == n_stages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+
+        // the second k-half parks its sums in shared memory; the first adds them and stores the rows
+        float* red = sh.red[it & 1];
+        if (kh == 1) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) red[m * GV_TILE_ROWS + row] = acc[m];
+        }
+        named_bar_sync(1, GV_CONSUMER_WARPS * 32);
+        if (kh == 0 && ok) {
+            const int grow = row0 + row;
+            if (grow < L.N) {
+                const float bias = L.bias ? __bfloat162float(L.bias[grow]) : 0.f;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    if (m < L.M) {
+                        const float v = acc[m] + red[m * GV_TILE_ROWS + row] + bias;
+                        const long long idx = static_cast<long long>(m) * L.ldy + grow;
+                        if (y_dtype == IZB_F32) static_cast<float*>(L.y)[idx] = v;
+                        else static_cast<__nv_bfloat16*>(L.y)[idx] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0) atomicExch(status, 5);
+}
+
+template <int FMT, int MT>
+static int gemv_launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+                           const SkinnyProblem& single) {
+    auto kern = skinny_gemv_kernel<FMT, MT>;
+    static std::atomic<int> smem_set[16];
+    const int dev_slot = ctx->device & 15;
+    if (smem_set[dev_slot].load(std::memory_order_relaxed) < h.smem_bytes) {
+        IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));
+        smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);
+    }
+    kern<<<h.grid, GV_THREADS, h.smem_bytes, stream>>>(dev, single, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes,
+                                                       h.xq_stage_bytes, h.red_bytes, h.lite_bytes, h.y_dtype,
+                                                       ctx->d_status + 4);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+template <int FMT>
+static int gemv_launch_fmt(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+                           const SkinnyProblem& single) {
+    switch (h.gemv) {
+        case 1: return gemv_launch_one<FMT, 1>(ctx, stream, h, dev, single);
+        case 2: return gemv_launch_one<FMT, 2>(ctx, stream, h, dev, single);
+        case 4: return gemv_launch_one<FMT, 4>(ctx, stream, h, dev, single);
+        default: return IZB_ERR_BAD_ARG;
+    }
+}
+
+int skinny_gemv_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev_probs,
+                       const SkinnyProblem* single) {
+    if (h.magic != SK_PLAN_MAGIC || !h.gemv) return IZB_ERR_BAD_ARG;
+    if (!dev_probs && !single) return IZB_ERR_BAD_ARG;
+    static const SkinnyProblem dummy = {};
+    const SkinnyProblem& s = single ? *single : dummy;
+    switch (h.fmt) {
+        case IZB_W_Q8_0: return gemv_launch_fmt<IZB_W_Q8_0>(ctx, stream, h, dev_probs, s);
+        case IZB_W_Q4_K: return gemv_launch_fmt<IZB_W_Q4_K>(ctx, stream, h, dev_probs, s);
+        default: return IZB_ERR_BAD_ARG;
+    }
+}
+
+}  // namespace izb
