@@ -138,3 +138,85 @@ def test_rejects_bad_arguments(cuda):
     assert e.value.status == -1
     assert ops.linear(torch.zeros(0, 256, device=cuda, dtype=torch.bfloat16), w).shape == (0, 64)
     ops.Context.get(0).check()
+
+
+# ---- one and two tokens over Q8_0 / Q4_K: the integer dot-product kernel ----
+# Activations travel as 16-bit block fixed point (exponent of each 32-value block's maximum), the
+# dot products are exact integers, so with fp32 output the result sits far inside the bf16 gates.
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+@pytest.mark.parametrize("m", [1, 2])
+def test_integer_dot_kernel_is_tight_in_fp32(cuda, fmt, m):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(500 + m)
+    n, k = 192, 2048
+    raw, wf = make_weight_np(fmt, n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (m, k)))
+    got = ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight(fmt, raw, cuda), fmt, n=n, k=k,
+                     out_dtype=torch.float32)
+    ops.Context.get(0).check()
+    want = o.linear(x, wf)
+    assert np.abs(to_np(got) - want).max() <= 2e-4 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+def test_integer_dot_kernel_outliers_zeros_and_tiny_blocks(cuda, fmt):
+    """Blocks whose maximum dwarfs the other values (those lose low bits: absolute error at most
+    2^-15 of the block maximum), all-zero blocks, blocks of very small magnitude, a zero token."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(77)
+    n, k = 130, 1024
+    raw, wf = make_weight_np(fmt, n, k, rng)
+    x = rng.normal(0, 1, (2, k)).astype(np.float32)
+    x[0, 5] = 3000.0            # outlier inside block 0
+    x[0, 300] = -4.0e4          # a second, larger one
+    x[0, 64:96] = 0.0           # an all-zero block
+    x[0, 128:160] *= 1e-30      # a block far below every other
+    x[1, :] = 0.0               # a token of zeros
+    x = bf16_np(x)
+    got = ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight(fmt, raw, cuda), fmt, n=n, k=k,
+                     out_dtype=torch.float32)
+    ops.Context.get(0).check()
+    g = to_np(got)
+    want = o.linear(x, wf)
+    assert np.isfinite(g).all()
+    assert np.all(g[1] == 0.0)
+    # per-block error bound: 32 values * 2^-15 * block max * max |w|, summed over the blocks
+    blk_max = np.abs(x[0]).reshape(-1, 32).max(axis=1)
+    bound = (32 * 2.0 ** -15 * blk_max).sum() * np.abs(wf).max() + 1e-5 * np.abs(want[0]).max()
+    assert np.abs(g[0] - want[0]).max() <= bound
+    assert_matmul_close(got, want, f"{fmt} outliers")
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+def test_integer_dot_kernel_matches_tensor_core_path(cuda, fmt, monkeypatch):
+    """The same call through the mma.sync consumers (integer kernel switched off) agrees within the gates."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(91)
+    n, k = 320, 1536
+    raw, wf = make_weight_np(fmt, n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (2, k)))
+    xd, wd = torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight(fmt, raw, cuda)
+    a = ops.linear(xd, wd, fmt, n=n, k=k, out_dtype=torch.float32)
+    monkeypatch.setenv("IZB_SKINNY_GEMV_MAX_M", "0")
+    b = ops.linear(xd, wd, fmt, n=n, k=k, out_dtype=torch.float32)
+    ops.Context.get(0).check()
+    want = o.linear(x, wf)
+    assert_matmul_close(a, want, "integer kernel")
+    assert_matmul_close(b, want, "tensor-core consumers")
+    assert np.abs(to_np(a) - to_np(b)).max() <= 2e-2 * np.abs(want).max()
+
+
+def test_integer_dot_kernel_non_finite_activation_poisons_only_its_token(cuda):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(5)
+    n, k = 64, 512
+    raw, wf = make_weight_np("q8_0", n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (2, k)))
+    x[0, 40] = np.inf
+    got = to_np(ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight("q8_0", raw, cuda), "q8_0",
+                           n=n, k=k, out_dtype=torch.float32))
+    ops.Context.get(0).check()
+    assert not np.isfinite(got[0]).any()
+    assert np.isfinite(got[1]).all()
+    assert np.abs(got[1] - o.linear(x[1:2], wf)[0]).max() <= 2e-4 * np.abs(got[1]).max()
