@@ -53,8 +53,13 @@ WEIGHT_SEED, ACT_SEED = 0, 2
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the grouped kernel, from the ncu
 # capture summarised under profiles/ (None until a capture exists for that workload).
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    # (133.85 MB read + 3.6 MB written) on an 8-layer stack, scaled to 28 layers: profiles/skinny_q8_0_m1_qwen3-0.6b-stack.md
-    "qwen3-0.6b-q8_0-m1": 481_000_000,
+    # (134.27 MB read + 3.9 MB written) on an 8-layer stack, scaled to 28 layers: profiles/skinny_gemv_q8_0_m1_qwen3-0.6b-stack.md
+    "qwen3-0.6b-q8_0-m1": 483_600_000,
+    # (70.93 + 1.1) MB x 28/8: profiles/skinny_gemv_q4_k_m1_qwen3-0.6b-stack.md
+    "qwen3-0.6b-q4_k-m1": 252_100_000,
+    # (141.1 + 8.7) MB x 28/8 and (78.2 + 4.4) MB x 28/8: profiles/skinny_tc_m64_qwen3-0.6b-stack.md
+    "qwen3-0.6b-q8_0-m64": 524_300_000,
+    "qwen3-0.6b-q4_k-m64": 289_100_000,
 }
 
 
@@ -271,7 +276,7 @@ def _time_call(fn, iters: int, warmup: int = 3):
     return e0.elapsed_time(e1) / iters
 
 
-def measure_gemm_cases(device):
+def measure_gemm_cases(device, only=None, iters=20):
     """Prefill (Qwen3-8B shape, M = 2048) and ASR-encoder GEMMs through izb_linear: TFLOP/s against the
     measured bf16 tensor peak.  Operands are a few hundred MB, so successive calls do not reuse L2 for
     the large ones; the small ones are reported as measured (L2-resident, as they would be in a layer loop)."""
@@ -295,11 +300,13 @@ def measure_gemm_cases(device):
     ]
     out = []
     for name, m, n, k, epi, has_bias in shapes:
+        if only is not None and name != only:
+            continue
         x = torch.randn(m, k, device=device, generator=gen).to(torch.bfloat16)
         w = (torch.randn(n, k, device=device, generator=gen) * 0.02).to(torch.bfloat16)
         b = (torch.randn(n, device=device, generator=gen) * 0.1).to(torch.bfloat16) if has_bias else None
         y = torch.empty(m, n // 2 if epi == "swiglu" else n, device=device, dtype=torch.bfloat16)
-        ms = _time_call(lambda: ops.linear(x, w, bias=b, out=y, epilogue=epi), 20)
+        ms = _time_call(lambda: ops.linear(x, w, bias=b, out=y, epilogue=epi), iters)
         tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
         out.append({"workload": name, "M": m, "N": n, "K": k, "ms": round(ms, 4), "tflops": round(tf, 1),
                     "tensor_frac": round(tf / peak, 4), "peak_kind": f"of {kind} {peak}"})
@@ -636,11 +643,18 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cases", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="sharded decode workloads: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--gemm-case", default=None,
+                    help="profiler captures: run only this prefill / encoder GEMM shape (a name from gemm_cases) and exit")
     ap.add_argument("--layers", type=int, default=None,
                     help="shorter stack for profiler captures (the reported line is then not the benchmark)")
     args = ap.parse_args()
     global LAYERS_OVERRIDE
     LAYERS_OVERRIDE = args.layers
+    if args.gemm_case:
+        import torch
+        res = measure_gemm_cases(torch.device("cuda", 0), only=args.gemm_case, iters=max(1, min(args.steps, 20)))
+        print(json.dumps({"gemm_case": res}), flush=True)
+        return
     if args.workload in SHARDED:
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm covers the default workload only"}))
