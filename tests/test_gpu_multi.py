@@ -16,6 +16,7 @@ def test_tp_and_ep_on_two_gpus(cuda):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"  # plain peer paths only: a rank that dies on a failed check must not hold a multicast binding
     port = 29600 + os.getpid() % 1000
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "multi_gpu_worker.py")]
