@@ -99,10 +99,15 @@ typedef struct izb_linear_args {
     int32_t reserved_;
 } izb_linear_args;
 
-/* M <= 32 (or <= 64 for the block formats) runs the weight-streaming kernel; larger M runs the
+/* M <= 32 (or <= 64 for the block formats) runs a weight-streaming kernel; larger M runs the
  * tcgen05/TMEM GEMM.  Block-quantised weights with M > 64 are first dequantised to bf16 into
  * `workspace` (N*K*2 bytes, see izb_linear_workspace_bytes); without a workspace they are
- * processed 64 token rows at a time by the streaming kernel instead. */
+ * processed 64 token rows at a time by the streaming kernels instead.
+ * Streaming kernels for the block formats: one or two tokens take integer dot products of the codes
+ * with the activations re-expressed per 32-value block as 16-bit fixed point (absolute error at most
+ * 2^-15 of the block's largest magnitude; a non-finite activation makes its token's outputs
+ * non-finite); 3..16 tokens (Q8_0: ..32) lift the codes to fp16 / bf16 tensor-core operands in
+ * registers; up to 64 tokens dequantise to bf16 in shared memory for tcgen05.  All accumulate in fp32. */
 size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K);
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args);
 
