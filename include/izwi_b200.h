@@ -42,8 +42,11 @@ typedef enum izb_status {
 typedef enum izb_dtype { IZB_BF16 = 0, IZB_F32 = 1 } izb_dtype;
 
 /* Weight storage formats: dense bf16 (Candle `Linear` weight) or raw GGML
- * blocks exactly as they sit in a GGUF file (Candle `QTensor` data). */
-typedef enum izb_wfmt { IZB_W_BF16 = 0, IZB_W_Q8_0 = 1, IZB_W_Q4_K = 2 } izb_wfmt;
+ * blocks exactly as they sit in a GGUF file (Candle `QTensor` data).
+ * Q8_0 and Q4_K are multiplied in place by the streaming kernels.  Q6_K (some tensors of
+ * Q4_K_M files; 210-byte super-blocks, so rows are not 16-byte aligned for tiled copies) is
+ * supported by izb_dequantize and, in izb_linear, through the bf16 copy in `workspace`. */
+typedef enum izb_wfmt { IZB_W_BF16 = 0, IZB_W_Q8_0 = 1, IZB_W_Q4_K = 2, IZB_W_Q6_K = 3 } izb_wfmt;
 
 int32_t izb_version(void);
 const char* izb_status_string(int32_t status);
@@ -64,7 +67,7 @@ int64_t izb_ctx_launch_count(const izb_ctx* ctx);
 int32_t izb_quantized_storage_bytes(int32_t wfmt, int64_t rows, int64_t cols, size_t* out_bytes);
 
 /* Block dequantisation, bit-exact with GGML: Q8_0 `d*q`; Q4_K
- * `(d*sc)*q - (dmin*m)` with separately rounded products.  `out_dtype` F32 is
+ * `(d*sc)*q - (dmin*m)`; Q6_K `(d*sc)*q`; every product rounded separately.  `out_dtype` F32 is
  * exact; BF16 rounds the fp32 value to nearest-even.
  * Replaces `QTensor::dequantize` at models/shared/weights/gguf.rs:131 and
  * qwen3/core.rs:853-858. */
@@ -102,7 +105,8 @@ typedef struct izb_linear_args {
 /* M <= 32 (or <= 64 for the block formats) runs a weight-streaming kernel; larger M runs the
  * tcgen05/TMEM GEMM.  Block-quantised weights with M > 64 are first dequantised to bf16 into
  * `workspace` (N*K*2 bytes, see izb_linear_workspace_bytes); without a workspace they are
- * processed 64 token rows at a time by the streaming kernels instead.
+ * processed 64 token rows at a time by the streaming kernels instead.  Q6_K weights always go
+ * through the workspace (any M; IZB_ERR_BAD_ARG without one).
  * Streaming kernels for the block formats: one or two tokens take integer dot products of the codes
  * with the activations re-expressed per 32-value block as 16-bit fixed point (absolute error at most
  * 2^-15 of the block's largest magnitude; a non-finite activation makes its token's outputs

@@ -19,7 +19,7 @@ IZB_ERR_NO_DEVICE = -5
 IZB_ERR_SCRATCH_TOO_SMALL = -6
 
 IZB_BF16, IZB_F32 = 0, 1
-IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K = 0, 1, 2
+IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K, IZB_W_Q6_K = 0, 1, 2, 3
 IZB_EPI_NONE, IZB_EPI_GELU, IZB_EPI_SILU, IZB_EPI_SWIGLU = 0, 1, 2, 3
 
 

@@ -68,6 +68,31 @@ __global__ void dequant_q4_k_kernel(const uint8_t* __restrict__ raw, OutT* __res
     }
 }
 
+// Q6_K: one thread per (super-block, 4-value run).  Value i of a block (half n = i / 128, group
+// g = (i % 128) / 32, l = i % 32): low nibble from ql[64 n + 32 (g & 1) + l] (high nibble for
+// g >= 2), bits 2g..2g+1 of qh[32 n + l], scale[8 n + l / 16 + 2 g]; value = (d * scale) * (code - 32).
+template <typename OutT>
+__global__ void dequant_q6_k_kernel(const uint8_t* __restrict__ raw, OutT* __restrict__ out, long long n_blocks) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_blocks * 64; i += stride) {
+        const long long b = i >> 6;
+        const int run = static_cast<int>(i & 63);  // values 4 run .. 4 run + 3 of the block
+        const int n = run >> 5, g = (run >> 3) & 3, l0 = (run & 7) * 4;
+        const uint8_t* blk = raw + b * 210;
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(blk[208] | (blk[209] << 8))));
+        const float sc = static_cast<float>(reinterpret_cast<const int8_t*>(blk + 192)[8 * n + (l0 >> 4) + 2 * g]);
+        const float dsc = __fmul_rn(d, sc);
+        const uint8_t* ql = blk + 64 * n + 32 * (g & 1) + l0;
+        const uint8_t* qh = blk + 128 + 32 * n + l0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int nib = g < 2 ? (ql[j] & 0x0F) : (ql[j] >> 4);
+            const int q = (nib | (((qh[j] >> (2 * g)) & 3) << 4)) - 32;
+            store_val(out, b * 256 + run * 4 + j, __fmul_rn(dsc, static_cast<float>(q)));
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // out = silu(gate) * up
 // ---------------------------------------------------------------------------
@@ -190,6 +215,7 @@ int32_t izb_quantized_storage_bytes(int32_t wfmt, int64_t rows, int64_t cols, si
         case IZB_W_BF16: block = 1; type = 2; break;
         case IZB_W_Q8_0: block = 32; type = 34; break;
         case IZB_W_Q4_K: block = 256; type = 144; break;
+        case IZB_W_Q6_K: block = 256; type = 210; break;
         default: return IZB_ERR_BAD_ARG;
     }
     if (cols != 0 && rows > INT64_MAX / cols) return IZB_ERR_BAD_ARG;  // element count overflows
@@ -204,7 +230,7 @@ int32_t izb_dequantize(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void
                        int32_t out_dtype, void* out) {
     if (!ctx || n_elems < 0) return IZB_ERR_BAD_ARG;
     if (out_dtype != IZB_F32 && out_dtype != IZB_BF16) return IZB_ERR_BAD_ARG;
-    if (wfmt != IZB_W_Q8_0 && wfmt != IZB_W_Q4_K) return IZB_ERR_UNSUPPORTED;
+    if (wfmt != IZB_W_Q8_0 && wfmt != IZB_W_Q4_K && wfmt != IZB_W_Q6_K) return IZB_ERR_UNSUPPORTED;
     const int64_t block = wfmt == IZB_W_Q8_0 ? 32 : 256;
     if (n_elems % block != 0) return IZB_ERR_BAD_ARG;
     if (n_elems == 0) return IZB_OK;
@@ -219,12 +245,18 @@ int32_t izb_dequantize(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void
             dequant_q8_0_kernel<float><<<grid, threads, 0, s>>>(r, static_cast<float*>(out), nb);
         else
             dequant_q8_0_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(r, static_cast<__nv_bfloat16*>(out), nb);
-    } else {
+    } else if (wfmt == IZB_W_Q4_K) {
         const int grid = grid_for(ctx, nb * 64, threads);
         if (out_dtype == IZB_F32)
             dequant_q4_k_kernel<float><<<grid, threads, 0, s>>>(r, static_cast<float*>(out), nb);
         else
             dequant_q4_k_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(r, static_cast<__nv_bfloat16*>(out), nb);
+    } else {
+        const int grid = grid_for(ctx, nb * 64, threads);
+        if (out_dtype == IZB_F32)
+            dequant_q6_k_kernel<float><<<grid, threads, 0, s>>>(r, static_cast<float*>(out), nb);
+        else
+            dequant_q6_k_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(r, static_cast<__nv_bfloat16*>(out), nb);
     }
     IZB_CUDA_TRY(cudaGetLastError());
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
@@ -257,6 +289,7 @@ static constexpr int64_t kStreamMaxM_quant = 64;
 size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K) {
     if ((wfmt == IZB_W_Q8_0 || wfmt == IZB_W_Q4_K) && M > kStreamMaxM_quant && N > 0 && K > 0)
         return static_cast<size_t>(N) * static_cast<size_t>(K) * 2;
+    if (wfmt == IZB_W_Q6_K && M > 0 && N > 0 && K > 0) return static_cast<size_t>(N) * static_cast<size_t>(K) * 2;
     return 0;
 }
 
@@ -268,6 +301,20 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
     if (args->K == 0) return IZB_ERR_UNSUPPORTED;
     if (args->M > INT32_MAX || args->N > INT32_MAX || args->K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (args->wfmt == IZB_W_Q6_K) {
+        // no in-place kernel for 210-byte super-blocks: multiply the bf16 copy in the workspace
+        const size_t need = static_cast<size_t>(args->N) * static_cast<size_t>(args->K) * 2;
+        if ((args->N * args->K) % 256 != 0) return IZB_ERR_BAD_ARG;
+        if (!args->workspace || args->workspace_bytes < need || !izb_aligned(args->workspace, 16)) return IZB_ERR_BAD_ARG;
+        const int rc = izb_dequantize(ctx, stream, IZB_W_Q6_K, args->w, args->N * args->K, IZB_BF16, args->workspace);
+        if (rc != IZB_OK) return rc;
+        izb_linear_args dense = *args;
+        dense.wfmt = IZB_W_BF16;
+        dense.w = args->workspace;
+        dense.workspace = nullptr;
+        dense.workspace_bytes = 0;
+        return izb_linear(ctx, stream, &dense);
+    }
     const bool quant = args->wfmt == IZB_W_Q8_0 || args->wfmt == IZB_W_Q4_K;
     if (!quant && args->wfmt != IZB_W_BF16) return IZB_ERR_BAD_ARG;
 

@@ -9,9 +9,9 @@ import torch
 
 from . import _lib as L
 
-WFMT = {"bf16": L.IZB_W_BF16, "q8_0": L.IZB_W_Q8_0, "q4_k": L.IZB_W_Q4_K}
-BLOCK_SIZE = {"bf16": 1, "q8_0": 32, "q4_k": 256}
-TYPE_SIZE = {"bf16": 2, "q8_0": 34, "q4_k": 144}
+WFMT = {"bf16": L.IZB_W_BF16, "q8_0": L.IZB_W_Q8_0, "q4_k": L.IZB_W_Q4_K, "q6_k": L.IZB_W_Q6_K}
+BLOCK_SIZE = {"bf16": 1, "q8_0": 32, "q4_k": 256, "q6_k": 256}
+TYPE_SIZE = {"bf16": 2, "q8_0": 34, "q4_k": 144, "q6_k": 210}
 
 
 class Context:

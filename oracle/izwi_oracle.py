@@ -153,9 +153,9 @@ def mlp_forward(x, w_gate_up, w_down, inter, round_bf16=False):
 # GGML block formats (Q8_0, Q4_K)
 # ----------------------------------------------------------------------------
 
-Q8_0, Q4_K = "q8_0", "q4_k"
-BLOCK_SIZE = {Q8_0: 32, Q4_K: 256}
-TYPE_SIZE = {Q8_0: 34, Q4_K: 144}
+Q8_0, Q4_K, Q6_K = "q8_0", "q4_k", "q6_k"
+BLOCK_SIZE = {Q8_0: 32, Q4_K: 256, Q6_K: 256}
+TYPE_SIZE = {Q8_0: 34, Q4_K: 144, Q6_K: 210}
 
 
 def quantized_storage_bytes(rows: int, cols: int, fmt: str) -> int:
@@ -253,12 +253,50 @@ def dequantize_q4_k(raw: np.ndarray) -> np.ndarray:
     return y.astype(np.float32).reshape(-1)
 
 
+def dequantize_q6_k(raw: np.ndarray) -> np.ndarray:
+    """Q6_K (the format of some tensors inside Q4_K_M files): 210-byte super-blocks of 256 values:
+    128 bytes of low nibbles `ql`, 64 bytes of 2-bit high parts `qh`, 16 int8 scales (one per 16
+    values), fp16 d.  In each half of 128 values, value l + 32 g (l < 32, g < 4) takes its low
+    nibble from ql[l + 32 (g & 1)] (low nibble for g < 2, high nibble otherwise), its high two
+    bits from bits 2g..2g+1 of qh[l], and scale index l / 16 + 2 g; code = that 6-bit number - 32.
+    value = (d * scale) * code, the two products rounded to fp32 separately."""
+    blocks = np.asarray(raw, dtype=np.uint8).reshape(-1, 210)
+    nb = blocks.shape[0]
+    ql = blocks[:, 0:128].reshape(nb, 2, 2, 32)          # [block, half, g & 1, l]
+    qh = blocks[:, 128:192].reshape(nb, 2, 32)           # [block, half, l]
+    sc = blocks[:, 192:208].copy().view(np.int8).astype(np.float32).reshape(nb, 2, 8)
+    d = blocks[:, 208:210].copy().view(np.float16).astype(np.float32)  # [nb, 1]
+    out = np.empty((nb, 2, 4, 32), dtype=np.float32)
+    for g in range(4):
+        nib = (ql[:, :, g & 1, :] & 0x0F) if g < 2 else (ql[:, :, g & 1, :] >> 4)
+        hi = (qh >> (2 * g)) & 3
+        q = (nib | (hi << 4)).astype(np.int16) - 32
+        scale = sc[:, :, 2 * g:2 * g + 2]                  # [nb, 2, 2]: l / 16 selects
+        dsc = (d[:, :, None] * scale).astype(np.float32)  # [nb, 2, 2]
+        dsc_l = np.repeat(dsc, 16, axis=2)                 # [nb, 2, 32]
+        out[:, :, g, :] = dsc_l * q.astype(np.float32)
+    return out.reshape(-1)
+
+
 def dequantize(raw: np.ndarray, fmt: str) -> np.ndarray:
     if fmt == Q8_0:
         return dequantize_q8_0(raw)
     if fmt == Q4_K:
         return dequantize_q4_k(raw)
+    if fmt == Q6_K:
+        return dequantize_q6_k(raw)
     raise ValueError(f"unknown format {fmt}")
+
+
+def make_q6_k_blocks(rng: np.random.Generator, n_blocks: int, d_scale=2e-4) -> np.ndarray:
+    """Synthetic Q6_K super-blocks built field by field: uniform 6-bit codes, int8 scales uniform
+    in [-128, 127], fp16 d ~ |N(0, scale)|."""
+    out = np.empty((n_blocks, 210), dtype=np.uint8)
+    out[:, 0:192] = rng.integers(0, 256, (n_blocks, 192), dtype=np.uint8)
+    out[:, 192:208] = rng.integers(-128, 128, (n_blocks, 16), dtype=np.int8).view(np.uint8)
+    d = np.abs(rng.normal(0.0, d_scale, n_blocks)).astype(np.float16)
+    out[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
 
 
 def make_q4_k_blocks(rng: np.random.Generator, n_blocks: int, d_scale=0.002, dmin_scale=0.002) -> np.ndarray:

@@ -2,7 +2,7 @@
 
 Run from the repository root:  python tests/golden/make_golden.py
 
-  ggml_dequant.npz   seeded Q8_0 / Q4_K blocks together with the fp32 values that
+  ggml_dequant.npz   seeded Q8_0 / Q4_K / Q6_K blocks together with the fp32 values that
                      gguf-py 0.19.0 (`gguf.quants.dequantize`, the GGML project's own
                      Python statement of ggml-quants.c) produces for them, plus Q8_0
                      quantisation of a seeded fp32 matrix.
@@ -42,12 +42,22 @@ def main():
     q4 = np.concatenate([q4, q4e.reshape(-1)])
     f = rng.normal(0, 0.05, (6, 96)).astype(np.float32)
     f[0, :32] = 0
+    # drawn after everything above so that the earlier vectors keep their values
+    q6 = o.make_q6_k_blocks(rng, 20)
+    q6e = q6[: 210 * 3].copy().reshape(3, 210)
+    q6e[0, 0:192] = 0xFF                                   # largest codes (+31)
+    q6e[1, 0:192] = 0x00                                   # smallest codes (-32)
+    q6e[1, 192:208] = np.int8(-128).view(np.uint8)         # extreme scales
+    q6e[2, 208:210] = 0                                    # zero super-block scale
+    q6 = np.concatenate([q6, q6e.reshape(-1)])
     np.savez_compressed(
         HERE / "ggml_dequant.npz",
         q8_0_raw=q8,
         q8_0_f32=quants.dequantize(q8.reshape(1, -1), T.Q8_0).reshape(-1),
         q4_k_raw=q4,
         q4_k_f32=quants.dequantize(q4.reshape(1, -1), T.Q4_K).reshape(-1),
+        q6_k_raw=q6,
+        q6_k_f32=quants.dequantize(q6.reshape(1, -1), T.Q6_K).reshape(-1),
         quant_in=f,
         quant_q8_0=quants.quantize(f, T.Q8_0).reshape(-1),
     )

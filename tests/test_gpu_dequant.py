@@ -10,7 +10,7 @@ from gpu_util import to_np
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k", "q6_k"])
 def test_golden_vectors_bit_exact(cuda, golden_dir, fmt):
     from izwi_b200 import ops
     vec = np.load(golden_dir / "ggml_dequant.npz")
@@ -22,11 +22,11 @@ def test_golden_vectors_bit_exact(cuda, golden_dir, fmt):
     assert np.array_equal(to_np(got16).view(np.uint32), o.bf16_round(want).view(np.uint32))
 
 
-@pytest.mark.parametrize("fmt,n_blocks", [("q8_0", 1), ("q8_0", 4099), ("q4_k", 1), ("q4_k", 2053)])
+@pytest.mark.parametrize("fmt,n_blocks", [("q8_0", 1), ("q8_0", 4099), ("q4_k", 1), ("q4_k", 2053), ("q6_k", 1), ("q6_k", 1031)])
 def test_seeded_blocks_bit_exact(cuda, fmt, n_blocks):
     from izwi_b200 import ops
     rng = np.random.default_rng(n_blocks)
-    raw = (o.make_q8_0_blocks if fmt == "q8_0" else o.make_q4_k_blocks)(rng, n_blocks)
+    raw = {"q8_0": o.make_q8_0_blocks, "q4_k": o.make_q4_k_blocks, "q6_k": o.make_q6_k_blocks}[fmt](rng, n_blocks)
     want = o.dequantize(raw, fmt)
     got = ops.dequantize(torch.from_numpy(raw).to(cuda), fmt, want.size)
     assert np.array_equal(to_np(got).view(np.uint32), want.view(np.uint32))

@@ -220,3 +220,27 @@ def test_integer_dot_kernel_non_finite_activation_poisons_only_its_token(cuda):
     assert not np.isfinite(got[0]).any()
     assert np.isfinite(got[1]).all()
     assert np.abs(got[1] - o.linear(x[1:2], wf)[0]).max() <= 2e-4 * np.abs(got[1]).max()
+
+
+# ---- Q6_K (tensors of Q4_K_M files): dequantised into the workspace, multiplied by the bf16 kernels ----
+
+@pytest.mark.parametrize("m", [1, 7, 40, 300])
+def test_q6_k_linear_through_workspace(cuda, m):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(600 + m)
+    n, k = 136, 1024
+    raw = o.make_q6_k_blocks(rng, n * k // 256)
+    wf = o.dequantize(raw, "q6_k").reshape(n, k)
+    x = bf16_np(rng.normal(0, 1, (m, k)))
+    got = ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), torch.from_numpy(raw).to(cuda), "q6_k", n=n, k=k)
+    ops.Context.get(0).check()
+    assert_matmul_close(got, o.linear(x, wf), f"q6_k M={m}")
+
+
+def test_q6_k_linear_needs_the_workspace(cuda):
+    from izwi_b200 import IzbError, ops
+    raw = torch.zeros(4 * 210, dtype=torch.uint8, device=cuda)
+    x = torch.zeros(1, 1024, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(IzbError) as e:
+        ops.linear(x, raw, "q6_k", n=1, k=1024, workspace=False)
+    assert e.value.status == -1

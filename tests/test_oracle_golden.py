@@ -37,6 +37,17 @@ def test_q4_k_dequant_bit_exact(vec):
     assert np.array_equal(got.view(np.uint32), vec["q4_k_f32"].view(np.uint32))
 
 
+def test_q6_k_dequant_bit_exact(vec):
+    got = o.dequantize_q6_k(vec["q6_k_raw"])
+    assert np.array_equal(got.view(np.uint32), vec["q6_k_f32"].view(np.uint32))
+
+
+def test_q6_k_storage_bytes():
+    assert o.quantized_storage_bytes(4, 512, "q6_k") == 8 * 210
+    with pytest.raises(Exception):
+        o.quantized_storage_bytes(1, 100, "q6_k")
+
+
 def test_q8_0_quantize_matches_ggml(vec):
     assert np.array_equal(o.quantize_q8_0(vec["quant_in"]), vec["quant_q8_0"])
 
