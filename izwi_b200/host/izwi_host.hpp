@@ -79,8 +79,10 @@ class Context {
     izb_ctx* ctx_ = nullptr;
 };
 
-inline const char* wfmt_name(int32_t f) { return f == IZB_W_Q8_0 ? "Q8_0" : f == IZB_W_Q4_K ? "Q4K" : "BF16"; }
-inline int64_t wfmt_block(int32_t f) { return f == IZB_W_Q8_0 ? 32 : f == IZB_W_Q4_K ? 256 : 1; }
+inline const char* wfmt_name(int32_t f) {
+    return f == IZB_W_Q8_0 ? "Q8_0" : f == IZB_W_Q4_K ? "Q4K" : f == IZB_W_Q6_K ? "Q6K" : "BF16";
+}
+inline int64_t wfmt_block(int32_t f) { return f == IZB_W_Q8_0 ? 32 : (f == IZB_W_Q4_K || f == IZB_W_Q6_K) ? 256 : 1; }
 
 inline size_t quantized_storage_bytes(int64_t rows, int64_t cols, int32_t dtype) {
     size_t out = 0;
