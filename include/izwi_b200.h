@@ -252,6 +252,46 @@ size_t izb_ar_max_bytes(const izb_ar* ar);
 int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count, int32_t dtype);
 int32_t izb_ar_destroy(izb_ar* ar);
 
+/* ---- GGUF files -------------------------------------------------------------------------------
+ * Read-only view of a GGUF v2 / v3 file (header, metadata, tensor directory; the file is mapped,
+ * not copied).  Replaces the use of Candle's gguf_file::Content behind GgufLoader
+ * (models/shared/weights/gguf.rs:36-143): from_path -> izb_gguf_open; has_tensor / tensor_shape ->
+ * izb_gguf_find; tensor names -> izb_gguf_tensor_at; get_metadata_{string,u64} -> izb_gguf_meta_*;
+ * load_qtensor -> izb_gguf_find + izb_gguf_upload (the kernels take the raw block bytes as they
+ * are, no repacking); load_tensor -> the same followed by izb_dequantize.
+ * Every length and offset in the file is validated against its size: a malformed file gives
+ * IZB_ERR_BAD_ARG, an unknown GGUF version or tensor type IZB_ERR_UNSUPPORTED, a name or key that
+ * is not present IZB_ERR_UNSUPPORTED. */
+typedef struct izb_gguf izb_gguf;
+typedef struct izb_gguf_tensor {
+    const char* name;  /* owned by the izb_gguf */
+    int32_t ggml_type; /* on-disk GGML type id (0 F32, 1 F16, 8 Q8_0, 12 Q4_K, 14 Q6_K, 30 BF16, ...) */
+    int32_t wfmt;      /* izb_wfmt accepted by izb_linear / izb_dequantize for these bytes, or -1 */
+    int32_t n_dims;
+    int32_t reserved_;
+    int64_t dims[4];   /* outermost first, as Candle reports shapes (the file stores them reversed) */
+    int64_t rows;      /* product of all dims but the last */
+    int64_t cols;      /* last dim: the contiguous one, K of a weight */
+    const void* data;  /* host pointer into the mapping */
+    size_t bytes;
+} izb_gguf_tensor;
+int32_t izb_gguf_open(const char* path, izb_gguf** out);
+int32_t izb_gguf_close(izb_gguf* g);
+int32_t izb_gguf_version(const izb_gguf* g);
+int64_t izb_gguf_tensor_count(const izb_gguf* g);
+int32_t izb_gguf_tensor_at(const izb_gguf* g, int64_t index, izb_gguf_tensor* out);
+int32_t izb_gguf_find(const izb_gguf* g, const char* name, izb_gguf_tensor* out);
+int64_t izb_gguf_meta_count(const izb_gguf* g);
+const char* izb_gguf_meta_key(const izb_gguf* g, int64_t index);
+/* Scalars of any integer / bool type as u64 (signed values sign-extended); any numeric type as f64;
+ * strings as pointer + length into the mapping (not NUL-terminated). */
+int32_t izb_gguf_meta_u64(const izb_gguf* g, const char* key, uint64_t* out);
+int32_t izb_gguf_meta_f64(const izb_gguf* g, const char* key, double* out);
+int32_t izb_gguf_meta_str(const izb_gguf* g, const char* key, const char** out, size_t* len);
+/* Copies the tensor's bytes to device memory on `stream` (needs dst_bytes >= t->bytes). */
+int32_t izb_gguf_upload(const izb_gguf* g, const izb_gguf_tensor* t, void* dev_dst, size_t dst_bytes,
+                        izb_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

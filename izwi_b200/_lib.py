@@ -93,7 +93,26 @@ _SIGNATURES = {
     "izb_ar_destroy": (C.c_int32, [C.c_void_p]),
     "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
+    "izb_gguf_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "izb_gguf_close": (C.c_int32, [C.c_void_p]),
+    "izb_gguf_version": (C.c_int32, [C.c_void_p]),
+    "izb_gguf_tensor_count": (C.c_int64, [C.c_void_p]),
+    "izb_gguf_tensor_at": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p]),
+    "izb_gguf_find": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_void_p]),
+    "izb_gguf_meta_count": (C.c_int64, [C.c_void_p]),
+    "izb_gguf_meta_key": (C.c_char_p, [C.c_void_p, C.c_int64]),
+    "izb_gguf_meta_u64": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "izb_gguf_meta_f64": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(C.c_double)]),
+    "izb_gguf_meta_str": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
+    "izb_gguf_upload": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
 }
+
+
+class GgufTensor(C.Structure):
+    """Mirror of izb_gguf_tensor."""
+    _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_int32), ("wfmt", C.c_int32), ("n_dims", C.c_int32),
+                ("reserved_", C.c_int32), ("dims", C.c_int64 * 4), ("rows", C.c_int64), ("cols", C.c_int64),
+                ("data", C.c_void_p), ("bytes", C.c_size_t)]
 
 _lib = None
 

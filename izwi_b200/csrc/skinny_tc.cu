@@ -106,7 +106,7 @@ __device__ __forceinline__ void q4_sub_to_row(const uint32_t (&words)[8], uint32
 // 6-bit scale and minimum of sub-block S from the twelve packed bytes (hd.y, hd.z, hd.w) of a super-block.
 template <int S>
 __device__ __forceinline__ void q4_scale_min(const uint4& hd, uint32_t& sc, uint32_t& mn) {
-    if (S < 4) {
+    if constexpr (S < 4) {
         sc = (hd.y >> (8 * S)) & 0x3Fu;
         mn = (hd.z >> (8 * S)) & 0x3Fu;
     } else {
