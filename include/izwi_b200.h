@@ -252,6 +252,23 @@ size_t izb_ar_max_bytes(const izb_ar* ar);
 int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count, int32_t dtype);
 int32_t izb_ar_destroy(izb_ar* ar);
 
+/* ---- glue around the projections of a decode step ---------------------------------------------
+ * RMS normalisation of bf16 rows: out = h * rsqrt(mean(h^2) + eps) * weight, fp32 arithmetic, one
+ * rounding; h = x, or x + residual rounded to bf16 (the reference adds the residual as a bf16
+ * tensor first), in which case `sum_out` (may alias neither input) receives h when not NULL.
+ * Serves the layer norms and, with rows = tokens * heads and cols = head_dim, the q/k norms.
+ * Replaces try_fused_rms_norm (kernels/mod.rs:143-157, kernels/cuda.rs:78-84 -> candle_nn::ops::
+ * rms_norm) and RmsNorm::forward at models/architectures/qwen3/core.rs:1446-1463. */
+int32_t izb_rms_norm(izb_ctx* ctx, izb_stream stream, const void* x, const void* weight,
+                     const void* residual, void* out, void* sum_out, int64_t rows, int64_t cols,
+                     int64_t ld_x, int64_t ld_residual, int64_t ld_out, int64_t ld_sum, float eps);
+/* Arg-max of every row of a bf16 / fp32 matrix (greedy token choice over the lm_head logits):
+ * the lowest index among equal maxima; NaN is never selected (a row of only NaN gives 0, -inf).
+ * `out_val` may be NULL.  Replaces `argmax` (models/architectures/qwen3/chat.rs:574-601), which
+ * copies the logits row to the host and reduces there. */
+int32_t izb_argmax_rows(izb_ctx* ctx, izb_stream stream, const void* x, int32_t x_dtype, int64_t rows,
+                        int64_t cols, int64_t ld_x, int32_t* out_idx, float* out_val);
+
 /* ---- GGUF files -------------------------------------------------------------------------------
  * Read-only view of a GGUF v2 / v3 file (header, metadata, tensor directory; the file is mapped,
  * not copied).  Replaces the use of Candle's gguf_file::Content behind GgufLoader

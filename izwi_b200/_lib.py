@@ -93,6 +93,10 @@ _SIGNATURES = {
     "izb_ar_destroy": (C.c_int32, [C.c_void_p]),
     "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
+    "izb_rms_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float]),
+    "izb_argmax_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
+                                    C.c_void_p, C.c_void_p]),
     "izb_gguf_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "izb_gguf_close": (C.c_int32, [C.c_void_p]),
     "izb_gguf_version": (C.c_int32, [C.c_void_p]),

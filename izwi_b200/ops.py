@@ -129,6 +129,46 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = No
     return o
 
 
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+             return_sum: bool = False):
+    """`candle_nn::ops::rms_norm` behind `try_fused_rms_norm` (kernels/mod.rs:143-157), optionally after a
+    residual add.  Rows are the leading dimensions flattened; returns out, or (out, x + residual)."""
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape == (x.shape[-1],)
+    x2 = x.reshape(-1, x.shape[-1])
+    assert x2.stride(1) == 1
+    out = torch.empty(x.shape, device=x.device, dtype=torch.bfloat16)
+    o2 = out.reshape(-1, out.shape[-1])
+    r2 = s2 = None
+    total = None
+    if residual is not None:
+        assert residual.shape == x.shape and residual.dtype == torch.bfloat16
+        r2 = residual.reshape(-1, x.shape[-1])
+        assert r2.stride(1) == 1
+        if return_sum:
+            total = torch.empty(x.shape, device=x.device, dtype=torch.bfloat16)
+            s2 = total.reshape(-1, x.shape[-1])
+    ctx = Context.get(x.device.index)
+    L.check(L.lib().izb_rms_norm(ctx.handle, _stream(), _ptr(x2), _ptr(weight), None if r2 is None else _ptr(r2), _ptr(o2),
+                                 None if s2 is None else _ptr(s2), x2.shape[0], x2.shape[1], x2.stride(0),
+                                 0 if r2 is None else r2.stride(0), o2.stride(0), 0 if s2 is None else s2.stride(0),
+                                 float(eps)), "izb_rms_norm")
+    return (out, total) if return_sum else out
+
+
+def argmax_rows(x: torch.Tensor, return_values: bool = False):
+    """Greedy token choice over logits rows (`argmax`, qwen3/chat.rs:574-601) without the host copy."""
+    assert x.dtype in (torch.bfloat16, torch.float32)
+    x2 = x.reshape(-1, x.shape[-1])
+    assert x2.stride(1) == 1
+    idx = torch.empty(x2.shape[0], device=x.device, dtype=torch.int32)
+    val = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32) if return_values else None
+    ctx = Context.get(x.device.index)
+    L.check(L.lib().izb_argmax_rows(ctx.handle, _stream(), _ptr(x2), L.IZB_F32 if x.dtype == torch.float32 else L.IZB_BF16, x2.shape[0], x2.shape[1],
+                                    x2.stride(0), _ptr(idx), None if val is None else _ptr(val)), "izb_argmax_rows")
+    idx = idx.reshape(x.shape[:-1])
+    return (idx, val.reshape(x.shape[:-1])) if return_values else idx
+
+
 class LinearGroup:
     """A set of independent small-M linear layers run by one persistent launch
     (izb_linear_group_*).  Keeps the tensors alive and owns the device copy of

@@ -449,3 +449,29 @@ def rel_err_and_cosine(got: np.ndarray, want: np.ndarray) -> tuple:
     gn, wn = np.linalg.norm(g), np.linalg.norm(w)
     cos = float((g * w).sum() / (gn * wn)) if gn > 0 and wn > 0 else 1.0
     return rel, cos
+
+
+# ---------------------------------------------------------------------------
+# glue around the projections of a decode step
+# ---------------------------------------------------------------------------
+def rms_norm(x: np.ndarray, weight: np.ndarray, eps: float, residual: np.ndarray | None = None):
+    """`candle_nn::ops::rms_norm` as called by `try_fused_rms_norm` (kernels/cuda.rs:78-84) and by
+    `RmsNorm::forward` for the q/k norms (qwen3/core.rs:1446-1463): x * rsqrt(mean(x^2) + eps) *
+    weight over the last dimension, fp32 arithmetic on bf16 inputs, one rounding to bf16.  With a
+    residual the sum is first rounded to bf16, as the reference's bf16 tensor add does.
+    Returns (out, h) with h the (rounded) input of the normalisation."""
+    h = np.asarray(x, dtype=np.float32)
+    if residual is not None:
+        h = bf16_round(h + np.asarray(residual, dtype=np.float32))
+    ms = (h.astype(np.float64) ** 2).mean(axis=-1, keepdims=True)
+    scale = (1.0 / np.sqrt(ms + eps)).astype(np.float32)
+    out = bf16_round(h * scale * np.asarray(weight, dtype=np.float32))
+    return out, h
+
+
+def argmax_rows(x: np.ndarray):
+    """Greedy choice over logits rows (`argmax`, qwen3/chat.rs:574-601): lowest index among equal
+    maxima; NaN is never selected (a row of only NaN gives index 0)."""
+    x = np.asarray(x, dtype=np.float32)
+    clean = np.where(np.isnan(x), -np.inf, x)
+    return clean.argmax(axis=-1).astype(np.int32), clean.max(axis=-1)

@@ -184,3 +184,16 @@ def test_moe_permute_stable():
     off, perm = o.moe_permute(idx, 4)
     assert off.tolist() == [0, 2, 4, 4, 6]
     assert perm.tolist() == [3, 5, 1, 2, 0, 4]
+
+
+def test_rms_norm_known_answer_and_residual():
+    out, h = o.rms_norm(np.array([[3.0, 4.0]], dtype=np.float32), np.array([1.0, 2.0], dtype=np.float32), 0.0)
+    assert np.allclose(out, [[3 / np.sqrt(12.5), 8 / np.sqrt(12.5)]], rtol=2 ** -8)
+    out2, h2 = o.rms_norm(np.array([[1.0, 1.0]], dtype=np.float32), np.ones(2, dtype=np.float32), 0.0,
+                          residual=np.array([[2.0, 3.0]], dtype=np.float32))
+    assert np.array_equal(h2, [[3.0, 4.0]]) and np.allclose(out2, [[3 / np.sqrt(12.5), 4 / np.sqrt(12.5)]], rtol=2 ** -8)
+
+
+def test_argmax_rows_ties_and_nan():
+    idx, val = o.argmax_rows(np.array([[1.0, 5.0, 5.0, np.nan], [np.nan, np.nan, np.nan, np.nan]]))
+    assert list(idx) == [1, 0] and val[0] == 5.0 and val[1] == -np.inf
