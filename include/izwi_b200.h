@@ -269,6 +269,30 @@ int32_t izb_rms_norm(izb_ctx* ctx, izb_stream stream, const void* x, const void*
 int32_t izb_argmax_rows(izb_ctx* ctx, izb_stream stream, const void* x, int32_t x_dtype, int64_t rows,
                         int64_t cols, int64_t ld_x, int32_t* out_idx, float* out_val);
 
+/* Rotary position embedding of q [tokens, q_heads, head_dim] and k [tokens, k_heads, head_dim]
+ * (bf16, in place, token rows ld_q / ld_k elements apart) with bf16 tables cos_half, sin_half
+ * [tokens, head_dim / 2]: first half = x1 cos - x2 sin, second half = x1 sin + x2 cos, fp32
+ * arithmetic, one rounding.  Replaces apply_rotary_emb (models/architectures/qwen3/core.rs:
+ * 2402-2415) and try_fused_rope_pair_bshd (kernels/mod.rs:159-173; Metal only in the reference). */
+int32_t izb_rope_pair(izb_ctx* ctx, izb_stream stream, void* q, void* k, const void* cos_half,
+                      const void* sin_half, int64_t tokens, int32_t q_heads, int32_t k_heads,
+                      int32_t head_dim, int64_t ld_q, int64_t ld_k);
+/* One query token per sequence against a head-major KV cache: q [batch, heads, head_dim] (rows ld_q
+ * apart), k_cache / v_cache [batch, kv_heads, kv_capacity, head_dim] bf16 contiguous of which the
+ * first kv_len positions are valid, out [batch, heads, head_dim] (rows ld_out apart);
+ * out = softmax(q k^T * scale) v per head, query head h reading KV head h / (heads / kv_heads).
+ * head_dim 64 or 128, heads / kv_heads <= 8.  The cache is split over CTAs; `workspace` holds
+ * their partial results (izb_decode_gqa_attention_workspace_bytes; 0 for short caches).
+ * Replaces dense_decode_attention (models/architectures/qwen3/core.rs:2189-2225) and
+ * try_fused_decode_gqa_attention_with_kv_len (kernels/mod.rs:196-221; Metal only in the reference). */
+size_t izb_decode_gqa_attention_workspace_bytes(const izb_ctx* ctx, int64_t batch, int32_t heads,
+                                                int32_t kv_heads, int32_t head_dim, int64_t kv_len);
+int32_t izb_decode_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q, const void* k_cache,
+                                 const void* v_cache, void* out, int64_t batch, int32_t heads,
+                                 int32_t kv_heads, int32_t head_dim, int64_t kv_len,
+                                 int64_t kv_capacity, int64_t ld_q, int64_t ld_out, float scale,
+                                 void* workspace, size_t workspace_bytes);
+
 /* ---- GGUF files -------------------------------------------------------------------------------
  * Read-only view of a GGUF v2 / v3 file (header, metadata, tensor directory; the file is mapped,
  * not copied).  Replaces the use of Candle's gguf_file::Content behind GgufLoader

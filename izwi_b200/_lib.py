@@ -97,6 +97,13 @@ _SIGNATURES = {
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float]),
     "izb_argmax_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                     C.c_void_p, C.c_void_p]),
+    "izb_rope_pair": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                  C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
+    "izb_decode_gqa_attention_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                                             C.c_int64]),
+    "izb_decode_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
+                                             C.c_int64, C.c_float, C.c_void_p, C.c_size_t]),
     "izb_gguf_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "izb_gguf_close": (C.c_int32, [C.c_void_p]),
     "izb_gguf_version": (C.c_int32, [C.c_void_p]),

@@ -1,0 +1,300 @@
+// The step between the QKV and O projections of a decode token: rotary embedding of q and k, and
+// single-query grouped-query attention over a head-major KV cache (flash-decoding: the cache is
+// split over CTAs, each keeps a running max / sum / weighted value sum, a second kernel merges).
+// HBM-bound on the K and V bytes, which every CTA reads exactly once, coalesced.
+#include "izb_common.cuh"
+
+namespace {
+
+constexpr int ATT_THREADS = 128;  // 4 warps; also the number of cache positions per tile
+constexpr int ATT_MAX_G = 8;      // query heads per KV head
+
+// out_first = x1 cos - x2 sin, out_second = x1 sin + x2 cos over the two halves of every head
+// (the non-interleaved form), fp32 arithmetic, one rounding.  In place.
+__global__ void rope_pair_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k,
+                                 const __nv_bfloat16* __restrict__ cos_half, const __nv_bfloat16* __restrict__ sin_half,
+                                 long long tokens, int q_heads, int k_heads, int head_dim, long long ld_q, long long ld_k) {
+    const int half = head_dim >> 1;
+    const long long per_tok = static_cast<long long>(q_heads + k_heads) * half;
+    const long long total = tokens * per_tok;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long t = i / per_tok;
+        const int r = static_cast<int>(i - t * per_tok);
+        const int head = r / half, j = r - head * half;
+        __nv_bfloat16* base = head < q_heads ? q + t * ld_q + static_cast<long long>(head) * head_dim
+                                             : k + t * ld_k + static_cast<long long>(head - q_heads) * head_dim;
+        const float c = __bfloat162float(cos_half[t * half + j]), s = __bfloat162float(sin_half[t * half + j]);
+        const float x1 = __bfloat162float(base[j]), x2 = __bfloat162float(base[j + half]);
+        base[j] = __float2bfloat16_rn(x1 * c - x2 * s);
+        base[j + half] = __float2bfloat16_rn(x1 * s + x2 * c);
+    }
+}
+
+struct AttShared {
+    float m[ATT_MAX_G], l[ATT_MAX_G], alpha[ATT_MAX_G];
+};
+
+// grid (splits, kv_heads, batch).  G query heads share the K / V rows of their KV head.
+template <int D, int G>
+__global__ void __launch_bounds__(ATT_THREADS)
+    decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                      const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out, float* __restrict__ part,
+                      int heads, int kv_heads, int g_real, long long ld_q_tok, long long ld_out_tok, long long kv_cap,
+                      int kv_len, float scale) {
+    constexpr int DV = D / 32;  // output values per lane
+    extern __shared__ float dyn[];
+    float* qs = dyn;                       // [G][D]
+    float* S = qs + G * D;                 // [G][ATT_THREADS]: scores, then probabilities of the tile
+    float* red = S + G * ATT_THREADS;      // [4][G][D] cross-warp sums
+    __shared__ AttShared sh;
+
+    const int split = blockIdx.x, n_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = ((kv_len + n_splits - 1) / n_splits + ATT_THREADS - 1) / ATT_THREADS * ATT_THREADS;
+    const int t_begin = split * per, t_end = min(kv_len, t_begin + per);
+
+    for (int i = tid; i < G * D; i += ATT_THREADS) {
+        const int g = i / D, d = i - g * D;
+        qs[i] = g < g_real ? __bfloat162float(q[b * ld_q_tok + static_cast<long long>(kh * g_real + g) * D + d]) * scale : 0.f;
+    }
+    if (tid < G) {
+        sh.m[tid] = -INFINITY;
+        sh.l[tid] = 0.f;
+    }
+    float acc[G][DV];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < DV; ++j) acc[g][j] = 0.f;
+    __syncthreads();
+
+    const __nv_bfloat16* kbase = kc + (static_cast<long long>(b) * kv_heads + kh) * kv_cap * D;
+    const __nv_bfloat16* vbase = vc + (static_cast<long long>(b) * kv_heads + kh) * kv_cap * D;
+
+    for (int t0 = t_begin; t0 < t_end; t0 += ATT_THREADS) {
+        const int n = min(ATT_THREADS, t_end - t0);
+        // ---- scores: one cache position per thread ----
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] = 0.f;
+        if (tid < n) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<long long>(t0 + tid) * D);
+#pragma unroll 4
+            for (int c = 0; c < D / 8; ++c) {
+                const uint4 kv = kr[c];
+                const float k0 = izb::bf16_lo_to_f32(kv.x), k1 = izb::bf16_hi_to_f32(kv.x), k2 = izb::bf16_lo_to_f32(kv.y),
+                            k3 = izb::bf16_hi_to_f32(kv.y), k4 = izb::bf16_lo_to_f32(kv.z), k5 = izb::bf16_hi_to_f32(kv.z),
+                            k6 = izb::bf16_lo_to_f32(kv.w), k7 = izb::bf16_hi_to_f32(kv.w);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float4 qa = *reinterpret_cast<const float4*>(qs + g * D + c * 8);
+                    const float4 qb = *reinterpret_cast<const float4*>(qs + g * D + c * 8 + 4);
+                    s[g] += qa.x * k0 + qa.y * k1 + qa.z * k2 + qa.w * k3 + qb.x * k4 + qb.y * k5 + qb.z * k6 + qb.w * k7;
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) S[g * ATT_THREADS + tid] = tid < n ? s[g] : -INFINITY;
+        __syncthreads();
+        // ---- running max and sum per query head: warp w takes heads w, w + 4 ----
+        for (int g = warp; g < G; g += 4) {
+            float v[4], mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[j] = S[g * ATT_THREADS + lane + 32 * j];
+                mx = fmaxf(mx, v[j]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+            const float m_old = sh.m[g], m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float p = __expf(v[j] - m_new);  // -inf (past the end) -> 0
+                S[g * ATT_THREADS + lane + 32 * j] = p;
+                sum += p;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+            if (lane == 0) {
+                const float a = __expf(m_old - m_new);  // first tile: exp(-inf) = 0
+                sh.alpha[g] = a;
+                sh.m[g] = m_new;
+                sh.l[g] = sh.l[g] * a + sum;
+            }
+        }
+        __syncthreads();
+        // ---- weighted values: warp w takes positions w, w + 4, ...; lane owns DV output values ----
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float a = sh.alpha[g];
+#pragma unroll
+            for (int j = 0; j < DV; ++j) acc[g][j] *= a;
+        }
+        for (int i = warp; i < n; i += 4) {
+            const __nv_bfloat16* vr = vbase + static_cast<long long>(t0 + i) * D + lane * DV;
+            float vv[DV];
+            if constexpr (DV == 4) {
+                const uint2 w = *reinterpret_cast<const uint2*>(vr);
+                vv[0] = izb::bf16_lo_to_f32(w.x); vv[1] = izb::bf16_hi_to_f32(w.x);
+                vv[2] = izb::bf16_lo_to_f32(w.y); vv[3] = izb::bf16_hi_to_f32(w.y);
+            } else {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(vr);
+                vv[0] = izb::bf16_lo_to_f32(w); vv[1] = izb::bf16_hi_to_f32(w);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float p = S[g * ATT_THREADS + i];
+#pragma unroll
+                for (int j = 0; j < DV; ++j) acc[g][j] = fmaf(p, vv[j], acc[g][j]);
+            }
+        }
+        __syncthreads();  // S is rewritten by the next tile
+    }
+
+    // ---- sum the four warps' partial outputs ----
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < DV; ++j) red[(warp * G + g) * D + lane * DV + j] = acc[g][j];
+    __syncthreads();
+    for (int i = tid; i < g_real * D; i += ATT_THREADS) {
+        const int g = i / D, d = i - g * D;
+        const float v = red[(0 * G + g) * D + d] + red[(1 * G + g) * D + d] + red[(2 * G + g) * D + d] + red[(3 * G + g) * D + d];
+        const int head = kh * g_real + g;
+        if (n_splits == 1) {
+            out[b * ld_out_tok + static_cast<long long>(head) * D + d] = __float2bfloat16_rn(v / sh.l[g]);
+        } else {
+            // partials: [batch][head][split][D + 2] = unnormalised sum, then max and sum of weights
+            float* p = part + ((static_cast<long long>(b) * heads + head) * n_splits + split) * (D + 2);
+            p[d] = v;
+            if (d == 0) {
+                p[D] = sh.m[g];
+                p[D + 1] = sh.l[g];
+            }
+        }
+    }
+}
+
+// grid (heads, batch): merges the splits' (max, sum, weighted values).
+template <int D>
+__global__ void __launch_bounds__(D)
+    decode_gqa_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int heads, int n_splits,
+                            long long ld_out_tok) {
+    const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const float* p = part + (static_cast<long long>(b) * heads + head) * n_splits * (D + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, p[s * (D + 2) + D]);
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float w = __expf(p[s * (D + 2) + D] - m);  // a split past the end carries max = -inf, weight 0
+        num = fmaf(w, p[s * (D + 2) + d], num);
+        den = fmaf(w, p[s * (D + 2) + D + 1], den);
+    }
+    out[b * ld_out_tok + static_cast<long long>(head) * D + d] = __float2bfloat16_rn(num / den);
+}
+
+int att_splits(const izb_ctx* ctx, int64_t batch, int64_t kv_heads, int64_t kv_len) {
+    const int64_t tiles = (kv_len + ATT_THREADS - 1) / ATT_THREADS;
+    int64_t want = (2 * static_cast<int64_t>(ctx ? ctx->sm_count : 148) + batch * kv_heads - 1) / (batch * kv_heads);
+    if (want < 1) want = 1;
+    if (want > tiles) want = tiles;
+    if (want > 64) want = 64;
+    return static_cast<int>(want);
+}
+
+template <int D, int G>
+int launch_att(izb_ctx* ctx, cudaStream_t s, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+               __nv_bfloat16* out, float* part, int batch, int heads, int kv_heads, int g_real, long long ld_q,
+               long long ld_out, long long kv_cap, int kv_len, float scale, int splits) {
+    const size_t smem = static_cast<size_t>(G * D + G * ATT_THREADS + 4 * G * D) * sizeof(float);
+    auto kern = decode_gqa_kernel<D, G>;
+    static std::atomic<int> smem_set[16];
+    const int slot = ctx->device & 15;
+    if (smem > 48 * 1024 && smem_set[slot].load(std::memory_order_relaxed) < static_cast<int>(smem)) {
+        IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        smem_set[slot].store(static_cast<int>(smem), std::memory_order_relaxed);
+    }
+    kern<<<dim3(splits, kv_heads, batch), ATT_THREADS, smem, s>>>(q, k, v, out, part, heads, kv_heads, g_real, ld_q, ld_out,
+                                                                 kv_cap, kv_len, scale);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    if (splits > 1) {
+        decode_gqa_merge_kernel<D><<<dim3(heads, batch), D, 0, s>>>(part, out, heads, splits, ld_out);
+        IZB_CUDA_TRY(cudaGetLastError());
+        ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return IZB_OK;
+}
+
+template <int D>
+int launch_att_g(izb_ctx* ctx, cudaStream_t s, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                 __nv_bfloat16* out, float* part, int batch, int heads, int kv_heads, int g, long long ld_q, long long ld_out,
+                 long long kv_cap, int kv_len, float scale, int splits) {
+    if (g == 1) return launch_att<D, 1>(ctx, s, q, k, v, out, part, batch, heads, kv_heads, g, ld_q, ld_out, kv_cap, kv_len, scale, splits);
+    if (g == 2) return launch_att<D, 2>(ctx, s, q, k, v, out, part, batch, heads, kv_heads, g, ld_q, ld_out, kv_cap, kv_len, scale, splits);
+    if (g <= 4) return launch_att<D, 4>(ctx, s, q, k, v, out, part, batch, heads, kv_heads, g, ld_q, ld_out, kv_cap, kv_len, scale, splits);
+    return launch_att<D, 8>(ctx, s, q, k, v, out, part, batch, heads, kv_heads, g, ld_q, ld_out, kv_cap, kv_len, scale, splits);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t izb_rope_pair(izb_ctx* ctx, izb_stream stream, void* q, void* k, const void* cos_half, const void* sin_half,
+                      int64_t tokens, int32_t q_heads, int32_t k_heads, int32_t head_dim, int64_t ld_q, int64_t ld_k) {
+    if (!ctx || tokens < 0 || q_heads < 0 || k_heads < 0 || head_dim <= 0 || (head_dim & 1)) return IZB_ERR_BAD_ARG;
+    if (tokens == 0 || q_heads + k_heads == 0) return IZB_OK;
+    if (!cos_half || !sin_half || (q_heads && !q) || (k_heads && !k)) return IZB_ERR_BAD_ARG;
+    if (ld_q < static_cast<int64_t>(q_heads) * head_dim || ld_k < static_cast<int64_t>(k_heads) * head_dim) return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(q, 2) || !izb_aligned(k, 2) || !izb_aligned(cos_half, 2) || !izb_aligned(sin_half, 2)) return IZB_ERR_BAD_ARG;
+    const long long total = tokens * static_cast<long long>(q_heads + k_heads) * (head_dim / 2);
+    const long long cap = static_cast<long long>(ctx->sm_count) * 16;
+    const long long blocks = (total + 255) / 256;
+    rope_pair_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(cos_half),
+        static_cast<const __nv_bfloat16*>(sin_half), tokens, q_heads, k_heads, head_dim, ld_q, ld_k);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+size_t izb_decode_gqa_attention_workspace_bytes(const izb_ctx* ctx, int64_t batch, int32_t heads, int32_t kv_heads,
+                                                int32_t head_dim, int64_t kv_len) {
+    if (batch <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || kv_len <= 0) return 0;
+    const int splits = att_splits(ctx, batch, kv_heads, kv_len);
+    if (splits <= 1) return 0;
+    return static_cast<size_t>(batch) * heads * splits * (head_dim + 2) * sizeof(float);
+}
+
+int32_t izb_decode_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q, const void* k_cache, const void* v_cache,
+                                 void* out, int64_t batch, int32_t heads, int32_t kv_heads, int32_t head_dim, int64_t kv_len,
+                                 int64_t kv_capacity, int64_t ld_q, int64_t ld_out, float scale, void* workspace,
+                                 size_t workspace_bytes) {
+    if (!ctx || batch < 0 || heads <= 0 || kv_heads <= 0) return IZB_ERR_BAD_ARG;
+    if (batch == 0) return IZB_OK;
+    if (!q || !k_cache || !v_cache || !out) return IZB_ERR_BAD_ARG;
+    if (head_dim != 64 && head_dim != 128) return IZB_ERR_UNSUPPORTED;
+    if (heads % kv_heads != 0 || heads / kv_heads > ATT_MAX_G) return IZB_ERR_UNSUPPORTED;
+    if (kv_len <= 0 || kv_len > kv_capacity || kv_len > INT32_MAX || batch > 65535 || kv_heads > 65535) return IZB_ERR_BAD_ARG;
+    if (ld_q < static_cast<int64_t>(heads) * head_dim || ld_out < static_cast<int64_t>(heads) * head_dim) return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(q, 2) || !izb_aligned(out, 2) || !izb_aligned(k_cache, 16) || !izb_aligned(v_cache, 16)) return IZB_ERR_BAD_ARG;
+    const int splits = att_splits(ctx, batch, kv_heads, kv_len);
+    const size_t need = splits > 1 ? static_cast<size_t>(batch) * heads * splits * (head_dim + 2) * sizeof(float) : 0;
+    if (need && (!workspace || workspace_bytes < need || !izb_aligned(workspace, 4))) return IZB_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const auto* qp = static_cast<const __nv_bfloat16*>(q);
+    const auto* kp = static_cast<const __nv_bfloat16*>(k_cache);
+    const auto* vp = static_cast<const __nv_bfloat16*>(v_cache);
+    auto* op = static_cast<__nv_bfloat16*>(out);
+    float* part = static_cast<float*>(workspace);
+    const int g = heads / kv_heads;
+    if (head_dim == 128)
+        return launch_att_g<128>(ctx, s, qp, kp, vp, op, part, static_cast<int>(batch), heads, kv_heads, g, ld_q, ld_out,
+                                 kv_capacity, static_cast<int>(kv_len), scale, splits);
+    return launch_att_g<64>(ctx, s, qp, kp, vp, op, part, static_cast<int>(batch), heads, kv_heads, g, ld_q, ld_out, kv_capacity,
+                            static_cast<int>(kv_len), scale, splits);
+}
+
+}  // extern "C"

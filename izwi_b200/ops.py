@@ -169,6 +169,39 @@ def argmax_rows(x: torch.Tensor, return_values: bool = False):
     return (idx, val.reshape(x.shape[:-1])) if return_values else idx
 
 
+def rope_pair_(q: torch.Tensor, k: torch.Tensor, cos_half: torch.Tensor, sin_half: torch.Tensor) -> None:
+    """`apply_rotary_emb` on q and k (qwen3/core.rs:2402-2415), in place.  q [tokens, q_heads, d],
+    k [tokens, k_heads, d], tables [tokens, d / 2]; all bf16."""
+    assert q.dtype == k.dtype == cos_half.dtype == sin_half.dtype == torch.bfloat16
+    tokens, qh, d = q.shape
+    assert k.shape[0] == tokens and k.shape[2] == d and cos_half.shape == sin_half.shape == (tokens, d // 2)
+    assert q.stride(2) == 1 and q.stride(1) == d and k.stride(2) == 1 and k.stride(1) == d
+    assert cos_half.is_contiguous() and sin_half.is_contiguous()
+    ctx = Context.get(q.device.index)
+    L.check(L.lib().izb_rope_pair(ctx.handle, _stream(), _ptr(q), _ptr(k), _ptr(cos_half), _ptr(sin_half), tokens, qh,
+                                  k.shape[1], d, q.stride(0), k.stride(0)), "izb_rope_pair")
+
+
+def decode_gqa_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: int,
+                         scale: float | None = None) -> torch.Tensor:
+    """`dense_decode_attention` (qwen3/core.rs:2189-2225): q [batch, heads, d], caches
+    [batch, kv_heads, capacity, d] (head-major), the first kv_len positions valid."""
+    assert q.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    b, h, d = q.shape
+    assert k_cache.shape == v_cache.shape and k_cache.shape[0] == b and k_cache.shape[3] == d
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and q.stride(2) == 1 and q.stride(1) == d
+    kvh, cap = k_cache.shape[1], k_cache.shape[2]
+    out = torch.empty(b, h, d, device=q.device, dtype=torch.bfloat16)
+    ctx = Context.get(q.device.index)
+    need = L.lib().izb_decode_gqa_attention_workspace_bytes(ctx.handle, b, h, kvh, d, kv_len)
+    ws = torch.empty(need, device=q.device, dtype=torch.uint8) if need else None
+    L.check(L.lib().izb_decode_gqa_attention(ctx.handle, _stream(), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), b, h,
+                                             kvh, d, kv_len, cap, q.stride(0), out.stride(0),
+                                             float(d ** -0.5 if scale is None else scale), _ptr(ws), need),
+            "izb_decode_gqa_attention")
+    return out
+
+
 class LinearGroup:
     """A set of independent small-M linear layers run by one persistent launch
     (izb_linear_group_*).  Keeps the tensors alive and owns the device copy of

@@ -475,3 +475,33 @@ def argmax_rows(x: np.ndarray):
     x = np.asarray(x, dtype=np.float32)
     clean = np.where(np.isnan(x), -np.inf, x)
     return clean.argmax(axis=-1).astype(np.int32), clean.max(axis=-1)
+
+
+def rope_pair(x: np.ndarray, cos_half: np.ndarray, sin_half: np.ndarray) -> np.ndarray:
+    """`apply_rotary_emb` (qwen3/core.rs:2402-2415) on x [tokens, heads, d] with tables
+    [tokens, d / 2]: first half x1 cos - x2 sin, second half x1 sin + x2 cos; fp32, one rounding."""
+    x = np.asarray(x, dtype=np.float32)
+    half = x.shape[-1] // 2
+    c = np.asarray(cos_half, dtype=np.float32)[:, None, :]
+    s = np.asarray(sin_half, dtype=np.float32)[:, None, :]
+    x1, x2 = x[..., :half], x[..., half:]
+    return bf16_round(np.concatenate([x1 * c - x2 * s, x1 * s + x2 * c], axis=-1))
+
+
+def decode_gqa_attention(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, kv_len: int, scale: float) -> np.ndarray:
+    """`dense_decode_attention` (qwen3/core.rs:2189-2225): q [batch, heads, d] against head-major
+    caches [batch, kv_heads, capacity, d]; softmax(q k^T * scale) v per head in fp64, query head h
+    reading KV head h // (heads // kv_heads) (`repeat_kv`).  Returns fp32 (not rounded)."""
+    q = np.asarray(q, dtype=np.float64)
+    b, h, d = q.shape
+    kvh = k_cache.shape[1]
+    g = h // kvh
+    out = np.empty((b, h, d), dtype=np.float64)
+    for bi in range(b):
+        for hi in range(h):
+            k = np.asarray(k_cache[bi, hi // g, :kv_len], dtype=np.float64)
+            v = np.asarray(v_cache[bi, hi // g, :kv_len], dtype=np.float64)
+            s = k @ q[bi, hi] * scale
+            p = np.exp(s - s.max())
+            out[bi, hi] = (p / p.sum()) @ v
+    return out.astype(np.float32)

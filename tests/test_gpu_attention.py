@@ -1,0 +1,71 @@
+"""RoPE and single-query GQA attention on the GPU through the C ABI against the oracle.
+Gates for the attention output (bf16, fp32 accumulation, `__expf`): max abs error <= 2e-2 of the
+largest |out| and cosine >= 0.9999, the matmul gates of this project."""
+import numpy as np
+import pytest
+import torch
+
+import izwi_oracle as o
+from gpu_util import assert_matmul_close, bf16_np, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, cuda):
+    return torch.from_numpy(a).to(cuda).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("tokens,qh,kh,d", [(1, 16, 8, 128), (5, 32, 8, 128), (3, 4, 4, 64), (64, 8, 2, 128)])
+def test_rope_pair(cuda, tokens, qh, kh, d):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(tokens + d)
+    q, k = bf16_np(rng.normal(0, 1, (tokens, qh, d))), bf16_np(rng.normal(0, 1, (tokens, kh, d)))
+    ang = rng.uniform(0, 6.28, (tokens, d // 2))
+    c, s = bf16_np(np.cos(ang)), bf16_np(np.sin(ang))
+    qd, kd = _dev(q, cuda), _dev(k, cuda)
+    ops.rope_pair_(qd, kd, _dev(c, cuda), _dev(s, cuda))
+    ops.Context.get(0).check()
+    for got, x in ((qd, q), (kd, k)):
+        want = o.rope_pair(x, c, s)
+        g = to_np(got)
+        assert (np.abs(g - want) <= np.maximum(np.abs(want), 2.0 ** -6) * 2.0 ** -7).all()
+        assert (g == want).mean() > 0.97
+
+
+@pytest.mark.parametrize("b,h,kvh,d,kv_len,cap", [
+    (1, 16, 8, 128, 1, 8), (1, 16, 8, 128, 127, 128), (1, 16, 8, 128, 129, 256), (2, 32, 8, 128, 1000, 1024),
+    (1, 32, 4, 128, 4096, 4096), (3, 8, 8, 64, 333, 400), (1, 12, 4, 128, 700, 700), (4, 16, 2, 64, 2049, 4096)])
+def test_decode_gqa_attention(cuda, b, h, kvh, d, kv_len, cap):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(kv_len + h)
+    q = bf16_np(rng.normal(0, 1, (b, h, d)))
+    k = bf16_np(rng.normal(0, 1, (b, kvh, cap, d)))
+    v = bf16_np(rng.normal(0, 1, (b, kvh, cap, d)))
+    k[:, :, kv_len:] = 1e30  # positions past kv_len must never be read into the result
+    v[:, :, kv_len:] = 1e30
+    got = ops.decode_gqa_attention(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), kv_len)
+    ops.Context.get(0).check()
+    want = o.decode_gqa_attention(q, k, v, kv_len, d ** -0.5)
+    assert_matmul_close(got.reshape(b * h, d), want.reshape(b * h, d), f"attention kv_len={kv_len}")
+
+
+def test_decode_gqa_attention_peaked_scores_and_arguments(cuda):
+    """One position dominates (large logit): the running-max rescaling must not lose it."""
+    from izwi_b200 import IzbError, ops
+    rng = np.random.default_rng(2)
+    b, h, kvh, d, kv_len = 1, 8, 2, 128, 900
+    q = bf16_np(rng.normal(0, 1, (b, h, d)))
+    k = bf16_np(rng.normal(0, 1, (b, kvh, kv_len, d)))
+    v = bf16_np(rng.normal(0, 1, (b, kvh, kv_len, d)))
+    k[0, :, 777] = bf16_np(q[0, ::4] * 6.0)  # aligned with query heads 0 and 4: scores near 6 |q|^2 / sqrt(d)
+    got = ops.decode_gqa_attention(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), kv_len)
+    want = o.decode_gqa_attention(q, k, v, kv_len, d ** -0.5)
+    assert_matmul_close(got.reshape(h, d), want.reshape(h, d), "peaked")
+    with pytest.raises(IzbError) as e:
+        ops.decode_gqa_attention(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), kv_len + 1)  # beyond the capacity
+    assert e.value.status == -1
+    q96 = torch.zeros(1, 8, 96, dtype=torch.bfloat16, device=cuda)
+    kv96 = torch.zeros(1, 2, 16, 96, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(IzbError) as e:
+        ops.decode_gqa_attention(q96, kv96, kv96, 16)
+    assert e.value.status == -2
