@@ -277,6 +277,12 @@ int32_t izb_argmax_rows(izb_ctx* ctx, izb_stream stream, const void* x, int32_t 
 int32_t izb_rope_pair(izb_ctx* ctx, izb_stream stream, void* q, void* k, const void* cos_half,
                       const void* sin_half, int64_t tokens, int32_t q_heads, int32_t k_heads,
                       int32_t head_dim, int64_t ld_q, int64_t ld_k);
+/* Writes the new token's k and v [batch, kv_heads, head_dim] (rows ld_k / ld_v apart) at position
+ * `pos` of the head-major caches [batch, kv_heads, kv_capacity, head_dim].  Replaces the cache
+ * append inside Qwen3Attention::forward (models/architectures/qwen3/core.rs:1624-1732). */
+int32_t izb_kv_append(izb_ctx* ctx, izb_stream stream, const void* k, const void* v, void* k_cache,
+                      void* v_cache, int64_t batch, int32_t kv_heads, int32_t head_dim, int64_t pos,
+                      int64_t kv_capacity, int64_t ld_k, int64_t ld_v);
 /* One query token per sequence against a head-major KV cache: q [batch, heads, head_dim] (rows ld_q
  * apart), k_cache / v_cache [batch, kv_heads, kv_capacity, head_dim] bf16 contiguous of which the
  * first kv_len positions are valid, out [batch, heads, head_dim] (rows ld_out apart);

@@ -99,6 +99,8 @@ _SIGNATURES = {
                                     C.c_void_p, C.c_void_p]),
     "izb_rope_pair": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                   C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
+    "izb_kv_append": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                  C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
     "izb_decode_gqa_attention_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                                              C.c_int64]),
     "izb_decode_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

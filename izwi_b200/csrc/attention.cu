@@ -31,6 +31,22 @@ __global__ void rope_pair_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* _
     }
 }
 
+// k, v [batch, kv_heads, head_dim] of the new token -> position `pos` of the head-major caches.
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                 __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, long long batch, int kv_heads,
+                                 int head_dim, long long pos, long long cap, long long ld_k, long long ld_v) {
+    const long long per = static_cast<long long>(kv_heads) * head_dim, total = batch * per;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long b = i / per;
+        const int r = static_cast<int>(i - b * per);
+        const int kh = r / head_dim, d = r - kh * head_dim;
+        const long long dst = ((b * kv_heads + kh) * cap + pos) * head_dim + d;
+        kc[dst] = k[b * ld_k + r];
+        vc[dst] = v[b * ld_v + r];
+    }
+}
+
 struct AttShared {
     float m[ATT_MAX_G], l[ATT_MAX_G], alpha[ATT_MAX_G];
 };
@@ -255,6 +271,24 @@ int32_t izb_rope_pair(izb_ctx* ctx, izb_stream stream, void* q, void* k, const v
     rope_pair_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(cos_half),
         static_cast<const __nv_bfloat16*>(sin_half), tokens, q_heads, k_heads, head_dim, ld_q, ld_k);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_kv_append(izb_ctx* ctx, izb_stream stream, const void* k, const void* v, void* k_cache, void* v_cache,
+                      int64_t batch, int32_t kv_heads, int32_t head_dim, int64_t pos, int64_t kv_capacity, int64_t ld_k,
+                      int64_t ld_v) {
+    if (!ctx || batch < 0 || kv_heads <= 0 || head_dim <= 0) return IZB_ERR_BAD_ARG;
+    if (batch == 0) return IZB_OK;
+    if (!k || !v || !k_cache || !v_cache || pos < 0 || pos >= kv_capacity) return IZB_ERR_BAD_ARG;
+    const int64_t per = static_cast<int64_t>(kv_heads) * head_dim;
+    if (ld_k < per || ld_v < per) return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(k, 2) || !izb_aligned(v, 2) || !izb_aligned(k_cache, 2) || !izb_aligned(v_cache, 2)) return IZB_ERR_BAD_ARG;
+    const long long total = batch * per, cap = static_cast<long long>(ctx->sm_count) * 8, blocks = (total + 255) / 256;
+    kv_append_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(k_cache),
+        static_cast<__nv_bfloat16*>(v_cache), batch, kv_heads, head_dim, pos, kv_capacity, ld_k, ld_v);
     IZB_CUDA_TRY(cudaGetLastError());
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;

@@ -1,0 +1,85 @@
+"""One decode token through a Qwen3 decoder layer, assembled from the C-ABI entry points: the
+host-side mirror of `Qwen3DecoderLayer::forward` / `Qwen3Attention::forward` for seq_len = 1
+(crates/izwi-core/src/models/architectures/qwen3/core.rs:1863-1881, 1624-1732).
+
+    normed = input_layernorm(x)                        izb_rms_norm (+ the previous layer's residual add)
+    qkv    = qkv_proj(normed)                          izb_linear (fused QKV)
+    q, k   = q_norm(q), k_norm(k); rope(q, k)          izb_rms_norm on head rows, izb_rope_pair
+    cache  <- k, v                                     izb_kv_append
+    attn   = softmax(q k^T / sqrt(d)) v                izb_decode_gqa_attention
+    x      = x + o_proj(attn)                          izb_linear; the add is fused into the next norm
+    normed = post_attention_layernorm(x)               izb_rms_norm with residual
+    x      = x + down(silu(gate) * up)                 izb_linear, izb_silu_mul, izb_linear; add deferred likewise
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+
+
+@dataclass
+class Qwen3LayerWeights:
+    fmt: str                      # "bf16" | "q8_0" | "q4_k": storage of the four projections
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    intermediate: int
+    input_layernorm: torch.Tensor            # [hidden] bf16
+    post_attention_layernorm: torch.Tensor   # [hidden] bf16
+    q_norm: torch.Tensor | None              # [head_dim] bf16
+    k_norm: torch.Tensor | None
+    qkv: torch.Tensor             # rows: q heads, k heads, v heads (fused at load, core.rs:931-981)
+    o: torch.Tensor
+    gate_up: torch.Tensor         # rows: gate then up (core.rs:1132-1168)
+    down: torch.Tensor
+    eps: float = 1e-6
+
+
+class KvCache:
+    """Head-major cache of one layer: [batch, kv_heads, capacity, head_dim] for k and v."""
+
+    def __init__(self, batch: int, kv_heads: int, capacity: int, head_dim: int, device):
+        self.k = torch.zeros(batch, kv_heads, capacity, head_dim, device=device, dtype=torch.bfloat16)
+        self.v = torch.zeros_like(self.k)
+        self.capacity = capacity
+
+
+class Qwen3DecoderLayer:
+    def __init__(self, w: Qwen3LayerWeights):
+        self.w = w
+
+    def forward(self, attn_in: torch.Tensor, residual: torch.Tensor | None, cos_half: torch.Tensor,
+                sin_half: torch.Tensor, cache: KvCache, pos: int):
+        """attn_in [batch, hidden]: the layer input, or the previous layer's MLP output when `residual`
+        (the previous layer's pre-MLP stream) is given; returns (mlp_out, stream) so that the caller's
+        next norm performs `stream + mlp_out`.  cos_half / sin_half [batch, head_dim / 2] for position `pos`."""
+        w = self.w
+        b = attn_in.shape[0]
+        qd, kd = w.heads * w.head_dim, w.kv_heads * w.head_dim
+        if residual is None:
+            x = attn_in
+            normed = ops.rms_norm(x, w.input_layernorm, w.eps)
+        else:
+            normed, x = ops.rms_norm(attn_in, w.input_layernorm, w.eps, residual=residual, return_sum=True)
+        qkv = ops.linear(normed, w.qkv, w.fmt, n=qd + 2 * kd, k=w.hidden)
+        q = qkv[:, :qd].reshape(b, w.heads, w.head_dim)           # views of the fused output (narrow, core.rs:975-981)
+        k = qkv[:, qd:qd + kd].reshape(b, w.kv_heads, w.head_dim)
+        v = qkv[:, qd + kd:].reshape(b, w.kv_heads, w.head_dim)
+        if w.q_norm is not None:
+            q = ops.rms_norm(q, w.q_norm, w.eps)
+            k = ops.rms_norm(k, w.k_norm, w.eps)
+        else:
+            q, k = q.contiguous(), k.contiguous()
+        ops.rope_pair_(q, k, cos_half, sin_half)
+        ops.kv_append_(k, v, cache.k, cache.v, pos)
+        attn = ops.decode_gqa_attention(q, cache.k, cache.v, pos + 1)
+        o = ops.linear(attn.reshape(b, qd), w.o, w.fmt, n=w.hidden, k=qd)
+        normed2, x = ops.rms_norm(o, w.post_attention_layernorm, w.eps, residual=x, return_sum=True)
+        gu = ops.linear(normed2, w.gate_up, w.fmt, n=2 * w.intermediate, k=w.hidden)
+        act = ops.silu_mul(gu[:, :w.intermediate], gu[:, w.intermediate:])
+        mlp_out = ops.linear(act, w.down, w.fmt, n=w.hidden, k=w.intermediate)
+        return mlp_out, x

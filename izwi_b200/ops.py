@@ -182,6 +182,17 @@ def rope_pair_(q: torch.Tensor, k: torch.Tensor, cos_half: torch.Tensor, sin_hal
                                   k.shape[1], d, q.stride(0), k.stride(0)), "izb_rope_pair")
 
 
+def kv_append_(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: int) -> None:
+    """New token's k, v [batch, kv_heads, d] (views allowed: last two dims dense) into position `pos` of the caches."""
+    b, kvh, d = k.shape
+    assert v.shape == k.shape and k_cache.shape == v_cache.shape and k_cache.shape[:2] == (b, kvh) and k_cache.shape[3] == d
+    assert k.stride(2) == 1 and k.stride(1) == d and v.stride(2) == 1 and v.stride(1) == d
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    ctx = Context.get(k.device.index)
+    L.check(L.lib().izb_kv_append(ctx.handle, _stream(), _ptr(k), _ptr(v), _ptr(k_cache), _ptr(v_cache), b, kvh, d, pos,
+                                  k_cache.shape[2], k.stride(0), v.stride(0)), "izb_kv_append")
+
+
 def decode_gqa_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: int,
                          scale: float | None = None) -> torch.Tensor:
     """`dense_decode_attention` (qwen3/core.rs:2189-2225): q [batch, heads, d], caches

@@ -1,0 +1,87 @@
+"""Whole decode tokens through two Qwen3 decoder layers assembled from the C-ABI entry points
+(izwi_b200/decoder.py) against the same composition of oracle functions, with a growing KV cache.
+Every op output is bf16 on both sides; the composition is compared after each token.  Gate for the
+composed stream: max error <= 3e-2 of the largest magnitude and cosine >= 0.9995 (the per-op gates
+are 2e-2 / 0.9999; differences of one bf16 step per op accumulate over ~20 ops per token)."""
+import numpy as np
+import pytest
+import torch
+
+import izwi_oracle as o
+from gpu_util import bf16_np, to_np
+
+pytestmark = pytest.mark.gpu
+
+HID, HEADS, KVH, D, INTER, EPS = 512, 8, 4, 64, 1024, 1e-6
+
+
+def _layer_np(rng, fmt):
+    def w(n, k):
+        if fmt == "q8_0":
+            raw = o.make_q8_0_blocks(rng, n * k // 32, d_scale=4e-4)
+            return raw, o.dequantize(raw, fmt).reshape(n, k)
+        raw = o.make_q4_k_blocks(rng, n * k // 256, d_scale=2e-4, dmin_scale=1.5e-3)
+        return raw, o.dequantize(raw, fmt).reshape(n, k)
+    qd, kd = HEADS * D, KVH * D
+    return {"ln1": bf16_np(rng.normal(1, 0.1, HID)), "ln2": bf16_np(rng.normal(1, 0.1, HID)),
+            "qn": bf16_np(rng.normal(1, 0.1, D)), "kn": bf16_np(rng.normal(1, 0.1, D)),
+            "qkv": w(qd + 2 * kd, HID), "o": w(HID, qd), "gu": w(2 * INTER, HID), "down": w(HID, INTER)}
+
+
+def _oracle_layer(L, x, kc, vc, pos, cos, sin):
+    """x [b, hid] fp32 holding bf16 values; kc, vc [b, kvh, cap, d] updated in place."""
+    b = x.shape[0]
+    qd, kd = HEADS * D, KVH * D
+    lin = lambda a, w: o.bf16_round(o.linear(a, w))  # noqa: E731
+    normed, _ = o.rms_norm(x, L["ln1"], EPS)
+    qkv = lin(normed, L["qkv"][1])
+    q = qkv[:, :qd].reshape(b, HEADS, D)
+    k = qkv[:, qd:qd + kd].reshape(b, KVH, D)
+    v = qkv[:, qd + kd:].reshape(b, KVH, D)
+    q, _ = o.rms_norm(q, L["qn"], EPS)
+    k, _ = o.rms_norm(k, L["kn"], EPS)
+    q, k = o.rope_pair(q, cos, sin), o.rope_pair(k, cos, sin)
+    kc[:, :, pos], vc[:, :, pos] = k, v
+    attn = o.bf16_round(o.decode_gqa_attention(q, kc, vc, pos + 1, D ** -0.5))
+    out = lin(attn.reshape(b, qd), L["o"][1])
+    normed2, x1 = o.rms_norm(out, L["ln2"], EPS, residual=x)
+    gu = lin(normed2, L["gu"][1])
+    act = o.bf16_round(o.silu_mul(gu[:, :INTER], gu[:, INTER:]))
+    return o.bf16_round(x1 + lin(act, L["down"][1]))
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+def test_three_tokens_two_layers(cuda, fmt):
+    from izwi_b200 import decoder, ops
+    rng = np.random.default_rng(21)
+    layers_np = [_layer_np(rng, fmt), _layer_np(rng, fmt)]
+    dev = lambda a: torch.from_numpy(a).to(cuda).to(torch.bfloat16)  # noqa: E731
+    layers = [decoder.Qwen3DecoderLayer(decoder.Qwen3LayerWeights(
+        fmt, HID, HEADS, KVH, D, INTER, dev(L["ln1"]), dev(L["ln2"]), dev(L["qn"]), dev(L["kn"]),
+        torch.from_numpy(L["qkv"][0]).to(cuda), torch.from_numpy(L["o"][0]).to(cuda),
+        torch.from_numpy(L["gu"][0]).to(cuda), torch.from_numpy(L["down"][0]).to(cuda), EPS)) for L in layers_np]
+    b, cap = 2, 16
+    caches = [decoder.KvCache(b, KVH, cap, D, cuda) for _ in layers]
+    kcs = [np.zeros((b, KVH, cap, D), dtype=np.float32) for _ in layers]
+    vcs = [np.zeros((b, KVH, cap, D), dtype=np.float32) for _ in layers]
+    inv = 1.0 / (10000.0 ** (np.arange(0, D, 2) / D))
+    for pos in range(3):
+        x = bf16_np(rng.normal(0, 1, (b, HID)))
+        ang = np.repeat((pos * inv)[None, :], b, axis=0)
+        cos, sin = bf16_np(np.cos(ang)), bf16_np(np.sin(ang))
+        # GPU: the residual add after each MLP is carried into the next norm
+        out, stream = dev(x), None
+        for layer, cache in zip(layers, caches):
+            out, stream = layer.forward(out, stream, dev(cos), dev(sin), cache, pos)
+        got = to_np((stream.float() + out.float()).to(torch.bfloat16))
+        ops.Context.get(0).check()
+        want = x
+        for L, kc, vc in zip(layers_np, kcs, vcs):
+            want = _oracle_layer(L, want, kc, vc, pos, cos, sin)
+        rel, cosine = o.rel_err_and_cosine(got, want)
+        assert np.isfinite(got).all()
+        assert rel <= 3e-2 and cosine >= 0.9995, (fmt, pos, rel, cosine)
+    # the caches hold the same keys on both sides (up to one bf16 step from the fused arithmetic)
+    for cache, kc in zip(caches, kcs):
+        k_got = to_np(cache.k[:, :, :3])
+        assert np.abs(k_got - kc[:, :, :3]).max() <= 3e-2 * np.abs(kc).max()
