@@ -316,6 +316,42 @@ def measure_gemm_cases(device, only=None, iters=20):
     return out
 
 
+def measure_attention_cases(device):
+    """Single-query GQA attention over a head-major KV cache (Qwen3-8B heads: 32 query, 8 KV, d 128)
+    through izb_decode_gqa_attention: K + V bytes per second against the measured HBM rate.  Caches of
+    36 layers are rotated so that successive calls do not find theirs in L2."""
+    import torch
+    from izwi_b200 import ops
+    peak_bw, _ = load_peaks()
+    gen = torch.Generator(device=device).manual_seed(5)
+    h, kvh, d = 32, 8, 128
+    out = []
+    for batch, kv_len in ((1, 4096), (1, 32768), (16, 4096)):
+        n_layers = max(2, min(36, int(4e9 // (2 * batch * kvh * kv_len * d * 2))))
+        caches = [(torch.randn(batch, kvh, kv_len, d, device=device, generator=gen).to(torch.bfloat16),
+                   torch.randn(batch, kvh, kv_len, d, device=device, generator=gen).to(torch.bfloat16))
+                  for _ in range(n_layers)]
+        q = torch.randn(batch, h, d, device=device, generator=gen).to(torch.bfloat16)
+        y = torch.empty(batch, h, d, device=device, dtype=torch.bfloat16)
+        ws = torch.empty(64 << 20, device=device, dtype=torch.uint8)
+        state = {"i": 0}
+
+        def step():
+            k, v = caches[state["i"] % n_layers]
+            ops.decode_gqa_attention(q, k, v, kv_len, out=y, workspace=ws)
+            state["i"] += 1
+        ms = _time_call(step, 50)
+        kv_bytes = 2 * batch * kvh * kv_len * d * 2
+        gbs = kv_bytes / (ms * 1e-3) / 1e9
+        out.append({"workload": f"qwen3-8b-decode-attention-b{batch}-kv{kv_len}", "ms": round(ms, 4),
+                    "kv_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak_bw, 4),
+                    "layers_rotated": n_layers, "kv_bytes_per_call": kv_bytes})
+        del caches
+        torch.cuda.empty_cache()
+    ops.Context.get(device.index).check()
+    return out
+
+
 def measure_moe_cases(device):
     """One Qwen3-30B-A3B-shaped MoE layer (H 2048, I 768, 128 experts, top-8, router bias ~N(0, 0.5))
     through izb_moe_forward at T = 1, 64, 4096; rotating over 3 layers' weights (3.6 GB) so the
@@ -452,6 +488,7 @@ def run_ours(args):
             line["cases"] = cases
             line["gemm_cases"] = measure_gemm_cases(device)
             line["moe_cases"] = measure_moe_cases(device)
+            line["attention_cases"] = measure_attention_cases(device)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -213,7 +213,8 @@ __global__ void __launch_bounds__(D)
 
 int att_splits(const izb_ctx* ctx, int64_t batch, int64_t kv_heads, int64_t kv_len) {
     const int64_t tiles = (kv_len + ATT_THREADS - 1) / ATT_THREADS;
-    int64_t want = (2 * static_cast<int64_t>(ctx ? ctx->sm_count : 148) + batch * kv_heads - 1) / (batch * kv_heads);
+    // about six CTAs of four warps per SM: the loads of a cache position are a dependent chain
+    int64_t want = (6 * static_cast<int64_t>(ctx ? ctx->sm_count : 148) + batch * kv_heads - 1) / (batch * kv_heads);
     if (want < 1) want = 1;
     if (want > tiles) want = tiles;
     if (want > 64) want = 64;

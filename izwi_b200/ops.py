@@ -194,7 +194,8 @@ def kv_append_(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache:
 
 
 def decode_gqa_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: int,
-                         scale: float | None = None) -> torch.Tensor:
+                         scale: float | None = None, out: torch.Tensor | None = None,
+                         workspace: torch.Tensor | None = None) -> torch.Tensor:
     """`dense_decode_attention` (qwen3/core.rs:2189-2225): q [batch, heads, d], caches
     [batch, kv_heads, capacity, d] (head-major), the first kv_len positions valid."""
     assert q.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
@@ -202,10 +203,12 @@ def decode_gqa_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     assert k_cache.shape == v_cache.shape and k_cache.shape[0] == b and k_cache.shape[3] == d
     assert k_cache.is_contiguous() and v_cache.is_contiguous() and q.stride(2) == 1 and q.stride(1) == d
     kvh, cap = k_cache.shape[1], k_cache.shape[2]
-    out = torch.empty(b, h, d, device=q.device, dtype=torch.bfloat16)
+    if out is None:
+        out = torch.empty(b, h, d, device=q.device, dtype=torch.bfloat16)
     ctx = Context.get(q.device.index)
     need = L.lib().izb_decode_gqa_attention_workspace_bytes(ctx.handle, b, h, kvh, d, kv_len)
-    ws = torch.empty(need, device=q.device, dtype=torch.uint8) if need else None
+    ws = workspace if workspace is not None and workspace.numel() * workspace.element_size() >= need else (
+        torch.empty(need, device=q.device, dtype=torch.uint8) if need else None)
     L.check(L.lib().izb_decode_gqa_attention(ctx.handle, _stream(), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), b, h,
                                              kvh, d, kv_len, cap, q.stride(0), out.stride(0),
                                              float(d ** -0.5 if scale is None else scale), _ptr(ws), need),
