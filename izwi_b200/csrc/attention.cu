@@ -60,8 +60,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
                       int kv_len, float scale) {
     constexpr int DV = D / 32;  // output values per lane
     extern __shared__ float dyn[];
-    float* qs = dyn;                       // [G][D]
-    float* S = qs + G * D;                 // [G][ATT_THREADS]: scores, then probabilities of the tile
+    float* S = dyn;                        // [G][ATT_THREADS]: scores, then probabilities of the tile
     float* red = S + G * ATT_THREADS;      // [4][G][D] cross-warp sums
     __shared__ AttShared sh;
 
@@ -70,9 +69,28 @@ __global__ void __launch_bounds__(ATT_THREADS)
     const int per = ((kv_len + n_splits - 1) / n_splits + ATT_THREADS - 1) / ATT_THREADS * ATT_THREADS;
     const int t_begin = split * per, t_end = min(kv_len, t_begin + per);
 
-    for (int i = tid; i < G * D; i += ATT_THREADS) {
-        const int g = i / D, d = i - g * D;
-        qs[i] = g < g_real ? __bfloat162float(q[b * ld_q_tok + static_cast<long long>(kh * g_real + g) * D + d]) * scale : 0.f;
+    // Scores on mma.sync (16 cache positions x 8 head columns x 16 d per instruction, K rows as the A
+    // operand, q as B).  Any permutation of d is free as long as both operands use it: lane (gq, tq)
+    // takes d = 32 tq .. 32 tq + 31 (16 tq .. for d = 64) of its rows, i.e. 16-byte loads, and step s
+    // consumes words 2s, 2s + 1 of them.  The q fragments stay in registers for the whole CTA.
+    constexpr int STEPS = D / 16;  // MMA steps per row; words of one lane's share of a row = 2 STEPS
+    const int gq = lane >> 2, tq = lane & 3;
+    uint32_t qf[STEPS][2];
+    {
+        uint4 tmp[STEPS / 2];
+#pragma unroll
+        for (int j = 0; j < STEPS / 2; ++j) tmp[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (gq < g_real) {
+            const uint4* qr = reinterpret_cast<const uint4*>(q + b * ld_q_tok + static_cast<long long>(kh * g_real + gq) * D +
+                                                             tq * (D / 4));
+#pragma unroll
+            for (int j = 0; j < STEPS / 2; ++j) tmp[j] = qr[j];
+        }
+#pragma unroll
+        for (int j = 0; j < STEPS / 2; ++j) {
+            qf[2 * j][0] = tmp[j].x; qf[2 * j][1] = tmp[j].y;
+            qf[2 * j + 1][0] = tmp[j].z; qf[2 * j + 1][1] = tmp[j].w;
+        }
     }
     if (tid < G) {
         sh.m[tid] = -INFINITY;
@@ -90,28 +108,39 @@ __global__ void __launch_bounds__(ATT_THREADS)
 
     for (int t0 = t_begin; t0 < t_end; t0 += ATT_THREADS) {
         const int n = min(ATT_THREADS, t_end - t0);
-        // ---- scores: one cache position per thread ----
-        float s[G];
+        // ---- scores: warp w takes positions 32 w .. 32 w + 31 of the tile, sixteen per MMA group ----
 #pragma unroll
-        for (int g = 0; g < G; ++g) s[g] = 0.f;
-        if (tid < n) {
-            const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<long long>(t0 + tid) * D);
-#pragma unroll 4
-            for (int c = 0; c < D / 8; ++c) {
-                const uint4 kv = kr[c];
-                const float k0 = izb::bf16_lo_to_f32(kv.x), k1 = izb::bf16_hi_to_f32(kv.x), k2 = izb::bf16_lo_to_f32(kv.y),
-                            k3 = izb::bf16_hi_to_f32(kv.y), k4 = izb::bf16_lo_to_f32(kv.z), k5 = izb::bf16_hi_to_f32(kv.z),
-                            k6 = izb::bf16_lo_to_f32(kv.w), k7 = izb::bf16_hi_to_f32(kv.w);
+        for (int grp = 0; grp < 2; ++grp) {
+            const int r0 = warp * 32 + grp * 16 + gq, r1 = r0 + 8;  // this lane's two rows inside the tile
+            uint4 ka[STEPS / 2], kb[STEPS / 2];
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const float4 qa = *reinterpret_cast<const float4*>(qs + g * D + c * 8);
-                    const float4 qb = *reinterpret_cast<const float4*>(qs + g * D + c * 8 + 4);
-                    s[g] += qa.x * k0 + qa.y * k1 + qa.z * k2 + qa.w * k3 + qb.x * k4 + qb.y * k5 + qb.z * k6 + qb.w * k7;
-                }
+            for (int j = 0; j < STEPS / 2; ++j) ka[j] = kb[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (r0 < n) {
+                const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<long long>(t0 + r0) * D + tq * (D / 4));
+#pragma unroll
+                for (int j = 0; j < STEPS / 2; ++j) ka[j] = kr[j];
+            }
+            if (r1 < n) {
+                const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<long long>(t0 + r1) * D + tq * (D / 4));
+#pragma unroll
+                for (int j = 0; j < STEPS / 2; ++j) kb[j] = kr[j];
+            }
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < STEPS / 2; ++j) {
+                izb::mma_bf16_16816(c, ka[j].x, kb[j].x, ka[j].y, kb[j].y, qf[2 * j][0], qf[2 * j][1]);
+                izb::mma_bf16_16816(c, ka[j].z, kb[j].z, ka[j].w, kb[j].w, qf[2 * j + 1][0], qf[2 * j + 1][1]);
+            }
+            // c0, c1: position r0 x heads 2 tq, 2 tq + 1;  c2, c3: position r1
+            if (2 * tq < G) {
+                S[(2 * tq) * ATT_THREADS + r0] = r0 < n ? c[0] * scale : -INFINITY;
+                S[(2 * tq) * ATT_THREADS + r1] = r1 < n ? c[2] * scale : -INFINITY;
+            }
+            if (2 * tq + 1 < G) {
+                S[(2 * tq + 1) * ATT_THREADS + r0] = r0 < n ? c[1] * scale : -INFINITY;
+                S[(2 * tq + 1) * ATT_THREADS + r1] = r1 < n ? c[3] * scale : -INFINITY;
             }
         }
-#pragma unroll
-        for (int g = 0; g < G; ++g) S[g * ATT_THREADS + tid] = tid < n ? s[g] : -INFINITY;
         __syncthreads();
         // ---- running max and sum per query head: warp w takes heads w, w + 4 ----
         for (int g = warp; g < G; g += 4) {
@@ -225,7 +254,7 @@ template <int D, int G>
 int launch_att(izb_ctx* ctx, cudaStream_t s, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                __nv_bfloat16* out, float* part, int batch, int heads, int kv_heads, int g_real, long long ld_q,
                long long ld_out, long long kv_cap, int kv_len, float scale, int splits) {
-    const size_t smem = static_cast<size_t>(G * D + G * ATT_THREADS + 4 * G * D) * sizeof(float);
+    const size_t smem = static_cast<size_t>(G * ATT_THREADS + 4 * G * D) * sizeof(float);
     auto kern = decode_gqa_kernel<D, G>;
     static std::atomic<int> smem_set[16];
     const int slot = ctx->device & 15;
