@@ -187,7 +187,8 @@ int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count
     if (!buf || !izb_aligned(buf, 4) || bytes % 4 != 0) return IZB_ERR_BAD_ARG;
     if (2 * bytes > ar->slot_bytes) return IZB_ERR_UNSUPPORTED;
     const long long n_words = static_cast<long long>(bytes / 4);
-    int grid = static_cast<int>((n_words + 4095) / 4096);
+    // latency, not bandwidth: one word per thread while the CTA limit allows (an 8 KB message = 8 CTAs)
+    int grid = static_cast<int>((n_words + 255) / 256);
     grid = grid < 1 ? 1 : (grid > AR_MAX_CTAS ? AR_MAX_CTAS : grid);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == IZB_F32)
