@@ -252,6 +252,34 @@ size_t izb_ar_max_bytes(const izb_ar* ar);
 int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count, int32_t dtype);
 int32_t izb_ar_destroy(izb_ar* ar);
 
+/* Expert-parallel dispatch and return over NVLink peer memory (no host read per layer, no NCCL
+ * launch): tokens are data-parallel, experts sit in contiguous blocks of n_experts / world per rank.
+ * Set-up as for izb_ar_*: izb_ep_create on every rank (allocates the rank's receive and return
+ * buffers for at most max_tokens_local tokens per rank and step), exchange the 64-byte handles,
+ * izb_ep_connect.  Per layer, after the local routing (izb_moe_topk / permute / gather):
+ *   izb_ep_dispatch(x_perm, offsets, pairs): exchanges the per-expert counts, stores every row into
+ *     its owner's receive buffer (rows grouped by local expert, then source rank) and waits for the
+ *     rows of all ranks; afterwards izb_ep_recv_rows() / izb_ep_recv_offsets() [local experts + 1]
+ *     feed izb_moe_grouped_gemm with rows = izb_ep_recv_capacity_rows();
+ *   izb_ep_return(y_rows): stores each result row back to the rank it came from, at the row it left
+ *     from in that rank's permuted order, and waits for this rank's rows: izb_ep_returned_rows()
+ *     then feeds izb_moe_combine.
+ * All waits are bounded (izb_ctx_check reports IZB_ERR_TIMEOUT); the launches can be captured in a
+ * CUDA graph.  No counterpart in the reference (single device). */
+typedef struct izb_ep izb_ep;
+int32_t izb_ep_create(izb_ctx* ctx, int32_t world, int32_t rank, int32_t n_experts, int32_t hidden,
+                      int64_t max_tokens_local, int32_t top_k, izb_ep** out);
+int32_t izb_ep_local_handle(izb_ep* ep, void* out_64_bytes);
+int32_t izb_ep_connect(izb_ep* ep, const void* handles_world_x_64_bytes);
+int64_t izb_ep_recv_capacity_rows(const izb_ep* ep);
+void* izb_ep_recv_rows(const izb_ep* ep);
+const void* izb_ep_recv_offsets(const izb_ep* ep);
+const void* izb_ep_returned_rows(const izb_ep* ep);
+int32_t izb_ep_dispatch(izb_ep* ep, izb_stream stream, const void* x_perm, const void* offsets,
+                        int64_t pairs);
+int32_t izb_ep_return(izb_ep* ep, izb_stream stream, const void* y_rows);
+int32_t izb_ep_destroy(izb_ep* ep);
+
 /* ---- glue around the projections of a decode step ---------------------------------------------
  * RMS normalisation of bf16 rows: out = h * rsqrt(mean(h^2) + eps) * weight, fp32 arithmetic, one
  * rounding; h = x, or x + residual rounded to bf16 (the reference adds the residual as a bf16

@@ -1,0 +1,411 @@
+// Expert-parallel dispatch and return over NVLink peer memory, without the host in the loop.
+//
+// Tokens are data-parallel, experts live in contiguous blocks of E / world per rank.  After the local
+// routing (top-k, stable permutation into expert-major rows) a rank has rows for every expert and
+// their counts on the device.  Per layer:
+//   1. counts: every rank pushes its E counts into every peer's region as 8-byte {count, sequence}
+//      stores and polls its own region for the others (as in peer_allreduce.cu); from the full
+//      [world][E] matrix each rank derives where its rows go on the owners, where the rows it
+//      receives start per (local expert, source), the segment offsets of the grouped GEMM, and where
+//      results return to;
+//   2. dispatch: rows are stored straight into the owner's receive buffer at their final position
+//      (grouped by local expert, then source rank, then source order); a system-scope fence, then the
+//      last CTA raises this rank's flag on every peer;
+//   3. the owner waits (bounded) for all flags, runs the grouped GEMMs on the receive buffer with the
+//      device-side segment offsets;
+//   4. return: result rows are stored into the source's buffer at the row they left from in its own
+//      permuted order, flags again; the source waits and runs its ordered combine.
+// Plain peer loads / stores only: no TMA on peer memory, no multimem.  Every wait is bounded and
+// reports through the context's status word.  The step number lives in device memory, so the four
+// launches can be replayed from a CUDA graph.
+#include <cstddef>
+#include <cstring>
+#include <new>
+
+#include "izb_common.cuh"
+
+constexpr int EP_MAX_WORLD = 8;
+constexpr int EP_MAX_EXPERTS = 256;
+
+struct EpHeader {          // first 256 bytes of a rank's region
+    unsigned int seq;      // steps completed on this rank
+    unsigned int done_dispatch, done_return;  // CTA counters of the step in flight
+};
+
+struct EpPeers {
+    unsigned char* base[EP_MAX_WORLD];
+};
+
+struct EpLayout {  // byte offsets inside a region
+    size_t counts, flag_dispatch, flag_return, x_recv, y_ret, total;
+};
+
+struct EpTables {  // device-local tables rebuilt every step by the counts kernel
+    int cnt[EP_MAX_WORLD][EP_MAX_EXPERTS];       // rows rank s has for expert e
+    int dst_row[EP_MAX_EXPERTS];                 // first row, in the owner's receive buffer, of this rank's rows for expert e
+    int recv_start[EP_MAX_EXPERTS * EP_MAX_WORLD / 2 + 1];  // [local expert][source] -> first received row; last = total
+    int seg[EP_MAX_EXPERTS + 1];                 // grouped-GEMM offsets over local experts
+    int ret_start[EP_MAX_WORLD][EP_MAX_EXPERTS]; // [source][local expert] -> row in the source's permuted order
+    unsigned int step;                           // sequence number of the step in flight
+};
+
+struct izb_ep {
+    izb_ctx* ctx;
+    int world, rank, n_experts, e_local, hidden, top_k;
+    long long max_pairs_local, recv_cap;
+    EpLayout lay;
+    unsigned char* local;
+    EpPeers peers;
+    EpTables* tables;
+    bool connected;
+};
+
+namespace {
+
+constexpr size_t EP_HEADER = 256;
+
+__device__ __forceinline__ void ep_st_pair(uint2* p, uint32_t data, uint32_t seq) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint2 ep_ld_pair(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void ep_st_flag(unsigned int* p, unsigned int v) {
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ep_ld_flag(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One CTA.  offsets: this rank's [E + 1] expert offsets of the permuted rows.
+__global__ void __launch_bounds__(256)
+    ep_counts_kernel(EpPeers peers, EpLayout lay, EpTables* __restrict__ tb, const int* __restrict__ offsets, int world,
+                     int rank, int n_experts, int e_local, long long recv_cap, int* status) {
+    __shared__ int bad;
+    EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
+    const unsigned int seq = hdr->seq + 1;
+    if (threadIdx.x == 0) {
+        bad = 0;
+        tb->step = seq;
+    }
+    __syncthreads();
+    // push my counts to every rank (mine included)
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const unsigned int c = static_cast<unsigned int>(offsets[e + 1] - offsets[e]);
+        for (int p = 0; p < world; ++p) {
+            uint2* dst = reinterpret_cast<uint2*>(peers.base[(rank + p) % world] + lay.counts) + rank * n_experts + e;
+            ep_st_pair(dst, c, seq);
+        }
+    }
+    // collect everyone's
+    const long long t0 = clock64();
+    bool ok = true;
+    for (int i = threadIdx.x; i < world * n_experts && ok; i += blockDim.x) {
+        const uint2* src = reinterpret_cast<const uint2*>(peers.base[rank] + lay.counts) + i;
+        uint2 v = ep_ld_pair(src);
+        while (v.y != seq) {
+            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                ok = false;
+                break;
+            }
+            v = ep_ld_pair(src);
+        }
+        tb->cnt[i / n_experts][i % n_experts] = ok ? static_cast<int>(v.x) : 0;
+    }
+    if (!ok) bad = 1;
+    __syncthreads();
+    if (bad) {
+        if (threadIdx.x == 0) atomicExch(status, 6);
+        // leave consistent (empty) tables so that the following kernels do nothing harmful
+        for (int e = threadIdx.x; e <= e_local; e += blockDim.x) tb->seg[e] = 0;
+        for (int i = threadIdx.x; i <= e_local * world; i += blockDim.x) tb->recv_start[i] = 0;
+        for (int e = threadIdx.x; e < n_experts; e += blockDim.x) tb->dst_row[e] = -1;
+        return;
+    }
+    // where my rows for expert e start on its owner: all rows of the owner's earlier experts, then the
+    // rows of lower ranks for e
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int first = e / e_local * e_local;
+        long long at = 0;
+        for (int e2 = first; e2 < e; ++e2)
+            for (int s = 0; s < world; ++s) at += tb->cnt[s][e2];
+        for (int s = 0; s < rank; ++s) at += tb->cnt[s][e];
+        tb->dst_row[e] = at + (offsets[e + 1] - offsets[e]) <= recv_cap ? static_cast<int>(at) : -1;
+    }
+    // rows I receive: [local expert][source] starts, and the GEMM's segment offsets
+    if (threadIdx.x == 0) {
+        long long at = 0;
+        for (int el = 0; el < e_local; ++el) {
+            tb->seg[el] = static_cast<int>(at < recv_cap ? at : recv_cap);
+            for (int s = 0; s < world; ++s) {
+                tb->recv_start[el * world + s] = static_cast<int>(at < recv_cap ? at : recv_cap);
+                at += tb->cnt[s][rank * e_local + el];
+            }
+        }
+        const int total = static_cast<int>(at < recv_cap ? at : recv_cap);
+        tb->seg[e_local] = total;
+        tb->recv_start[e_local * world] = total;
+        if (at > recv_cap) atomicExch(status, 7);  // more rows than the receive buffer holds: a rank exceeded its token limit
+    }
+    // where results go back: source s keeps its rows of expert e at its own offsets[e] = sum of its earlier counts
+    for (int i = threadIdx.x; i < world * e_local; i += blockDim.x) {
+        const int s = i / e_local, el = i % e_local, e = rank * e_local + el;
+        int at = 0;
+        for (int e2 = 0; e2 < e; ++e2) at += tb->cnt[s][e2];
+        tb->ret_start[s][el] = at;
+    }
+}
+
+// Copies one row of `row_units` 16-byte units with the whole CTA.
+__device__ __forceinline__ void ep_copy_row(uint4* __restrict__ dst, const uint4* __restrict__ src, int row_units) {
+    for (int u = threadIdx.x; u < row_units; u += blockDim.x) dst[u] = src[u];
+}
+
+// After a CTA's stores: fence to system scope, count the CTA in; the last one raises this rank's
+// flag (the step number) on every rank.
+__device__ __forceinline__ void ep_signal(unsigned int* counter, EpPeers peers, size_t flag_off, int world, int rank,
+                                          unsigned int seq) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(counter, 1u);
+        if (prev == gridDim.x - 1) {
+            *counter = 0;
+            __threadfence_system();
+            for (int p = 0; p < world; ++p)
+                ep_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + p) % world] + flag_off) + rank, seq);
+        }
+    }
+}
+
+// x_perm: this rank's rows in expert-major order.  Row r of expert e goes to the owner's receive
+// buffer at dst_row[e] + (r - offsets[e]).
+__global__ void __launch_bounds__(256)
+    ep_dispatch_kernel(EpPeers peers, EpLayout lay, const EpTables* __restrict__ tb, const uint4* __restrict__ x_perm,
+                       const int* __restrict__ offsets, long long pairs, int n_experts, int e_local, int row_units, int world,
+                       int rank) {
+    __shared__ int s_e, s_dst;
+    for (long long r = blockIdx.x; r < pairs; r += gridDim.x) {
+        if (threadIdx.x == 0) {
+            int lo = 0, hi = n_experts;  // last e with offsets[e] <= r
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (offsets[mid] <= r) lo = mid; else hi = mid;
+            }
+            s_e = lo;
+            s_dst = tb->dst_row[lo] < 0 ? -1 : tb->dst_row[lo] + static_cast<int>(r - offsets[lo]);
+        }
+        __syncthreads();
+        if (s_dst >= 0) {
+            uint4* dst = reinterpret_cast<uint4*>(peers.base[s_e / e_local] + lay.x_recv) + static_cast<long long>(s_dst) * row_units;
+            ep_copy_row(dst, x_perm + r * row_units, row_units);
+        }
+        __syncthreads();
+    }
+    EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
+    ep_signal(&hdr->done_dispatch, peers, lay.flag_dispatch, world, rank, tb->step);
+}
+
+// y: results for the received rows, same order.  Row i (local expert el, source s, position j) goes
+// to the source's return buffer at ret_start[s][el] + j.
+__global__ void __launch_bounds__(256)
+    ep_return_kernel(EpPeers peers, EpLayout lay, const EpTables* __restrict__ tb, const uint4* __restrict__ y, int e_local,
+                     int row_units, int world, int rank) {
+    __shared__ int s_src, s_dst;
+    const int groups = e_local * world;
+    const int total = tb->recv_start[groups];
+    for (int i = blockIdx.x; i < total; i += gridDim.x) {
+        if (threadIdx.x == 0) {
+            int lo = 0, hi = groups;  // last group whose start <= i (empty groups share a start: take the last)
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (tb->recv_start[mid] <= i) lo = mid; else hi = mid;
+            }
+            const int el = lo / world, s = lo % world;
+            s_src = s;
+            s_dst = tb->ret_start[s][el] + (i - tb->recv_start[lo]);
+        }
+        __syncthreads();
+        uint4* dst = reinterpret_cast<uint4*>(peers.base[s_src] + lay.y_ret) + static_cast<long long>(s_dst) * row_units;
+        ep_copy_row(dst, y + static_cast<long long>(i) * row_units, row_units);
+        __syncthreads();
+    }
+    EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
+    ep_signal(&hdr->done_return, peers, lay.flag_return, world, rank, tb->step);
+}
+
+// One CTA of `world` threads: thread s waits (bounded) for rank s's flag of this step.
+// closes: the step is complete on this rank, advance its sequence number.
+__global__ void ep_wait_kernel(unsigned char* local, size_t flag_off, const EpTables* __restrict__ tb, int world, int closes,
+                               int* status) {
+    const unsigned int seq = tb->step;
+    const unsigned int* flags = reinterpret_cast<const unsigned int*>(local + flag_off);
+    if (static_cast<int>(threadIdx.x) < world) {
+        const long long t0 = clock64();
+        while (ep_ld_flag(flags + threadIdx.x) != seq) {
+            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                atomicExch(status, 6);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (closes && threadIdx.x == 0) reinterpret_cast<EpHeader*>(local)->seq = seq;
+}
+
+EpLayout ep_layout(int world, int n_experts, int hidden, long long recv_cap, long long max_pairs_local) {
+    EpLayout l;
+    size_t at = EP_HEADER;
+    auto take = [&](size_t bytes) {
+        const size_t start = at;
+        at = (at + bytes + 255) / 256 * 256;
+        return start;
+    };
+    l.counts = take(static_cast<size_t>(world) * n_experts * sizeof(uint2));
+    l.flag_dispatch = take(static_cast<size_t>(world) * sizeof(unsigned int));
+    l.flag_return = take(static_cast<size_t>(world) * sizeof(unsigned int));
+    l.x_recv = take(static_cast<size_t>(recv_cap) * hidden * 2);
+    l.y_ret = take(static_cast<size_t>(max_pairs_local) * hidden * 2);
+    l.total = at;
+    return l;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t izb_ep_create(izb_ctx* ctx, int32_t world, int32_t rank, int32_t n_experts, int32_t hidden, int64_t max_tokens_local,
+                      int32_t top_k, izb_ep** out) {
+    if (!ctx || !out || world <= 0 || world > EP_MAX_WORLD || rank < 0 || rank >= world) return IZB_ERR_BAD_ARG;
+    if (n_experts <= 0 || n_experts > EP_MAX_EXPERTS || n_experts % world != 0) return IZB_ERR_BAD_ARG;
+    if (hidden <= 0 || hidden % 8 != 0 || max_tokens_local <= 0 || top_k <= 0 || top_k > n_experts) return IZB_ERR_BAD_ARG;
+    if ((n_experts / world) * world > EP_MAX_EXPERTS * EP_MAX_WORLD / 2) return IZB_ERR_UNSUPPORTED;
+    *out = nullptr;
+    izb_ep* ep = new (std::nothrow) izb_ep();
+    if (!ep) return IZB_ERR_LAUNCH;
+    ep->ctx = ctx;
+    ep->world = world; ep->rank = rank; ep->n_experts = n_experts; ep->e_local = n_experts / world;
+    ep->hidden = hidden; ep->top_k = top_k;
+    ep->max_pairs_local = max_tokens_local * top_k;
+    ep->recv_cap = ep->max_pairs_local * world;  // every pair of every rank could choose this rank's experts
+    if (ep->recv_cap > INT32_MAX / 2) {
+        delete ep;
+        return IZB_ERR_UNSUPPORTED;
+    }
+    ep->lay = ep_layout(world, n_experts, hidden, ep->recv_cap, ep->max_pairs_local);
+    ep->connected = false;
+    ep->tables = nullptr;
+    std::memset(&ep->peers, 0, sizeof(ep->peers));
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != ctx->device) cudaSetDevice(ctx->device);
+    void* p = nullptr;
+    void* t = nullptr;
+    // only the control words need a defined start; the row buffers are written before they are read
+    const bool ok = cudaMalloc(&p, ep->lay.total) == cudaSuccess && cudaMemset(p, 0, ep->lay.x_recv) == cudaSuccess &&
+                    cudaMalloc(&t, sizeof(EpTables)) == cudaSuccess && cudaMemset(t, 0, sizeof(EpTables)) == cudaSuccess &&
+                    cudaDeviceSynchronize() == cudaSuccess;
+    if (cur != ctx->device) cudaSetDevice(cur);
+    if (!ok) {
+        (void)cudaGetLastError();
+        if (p) cudaFree(p);
+        if (t) cudaFree(t);
+        delete ep;
+        return IZB_ERR_LAUNCH;
+    }
+    ep->local = static_cast<unsigned char*>(p);
+    ep->tables = static_cast<EpTables*>(t);
+    *out = ep;
+    return IZB_OK;
+}
+
+int32_t izb_ep_local_handle(izb_ep* ep, void* out_64_bytes) {
+    if (!ep || !out_64_bytes) return IZB_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    IZB_CUDA_TRY(cudaIpcGetMemHandle(&h, ep->local));
+    std::memcpy(out_64_bytes, &h, 64);
+    return IZB_OK;
+}
+
+int32_t izb_ep_connect(izb_ep* ep, const void* handles_world_x_64_bytes) {
+    if (!ep || !handles_world_x_64_bytes || ep->connected) return IZB_ERR_BAD_ARG;
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != ep->ctx->device) cudaSetDevice(ep->ctx->device);
+    int rc = IZB_OK;
+    for (int r = 0; r < ep->world && rc == IZB_OK; ++r) {
+        if (r == ep->rank) {
+            ep->peers.base[r] = ep->local;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, static_cast<const unsigned char*>(handles_world_x_64_bytes) + 64 * r, 64);
+        void* p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            (void)cudaGetLastError();
+            rc = IZB_ERR_LAUNCH;
+        }
+        ep->peers.base[r] = static_cast<unsigned char*>(p);
+    }
+    if (cur != ep->ctx->device) cudaSetDevice(cur);
+    ep->connected = rc == IZB_OK;
+    return rc;
+}
+
+int64_t izb_ep_recv_capacity_rows(const izb_ep* ep) { return ep ? ep->recv_cap : 0; }
+void* izb_ep_recv_rows(const izb_ep* ep) { return ep ? ep->local + ep->lay.x_recv : nullptr; }
+const void* izb_ep_recv_offsets(const izb_ep* ep) {
+    return ep ? reinterpret_cast<const unsigned char*>(ep->tables) + offsetof(EpTables, seg) : nullptr;
+}
+const void* izb_ep_returned_rows(const izb_ep* ep) { return ep ? ep->local + ep->lay.y_ret : nullptr; }
+
+int32_t izb_ep_dispatch(izb_ep* ep, izb_stream stream, const void* x_perm, const void* offsets, int64_t pairs) {
+    if (!ep || !ep->connected || pairs < 0 || pairs > ep->max_pairs_local) return IZB_ERR_BAD_ARG;
+    if (!offsets || (pairs > 0 && !x_perm) || !izb_aligned(x_perm, 16) || !izb_aligned(offsets, 4)) return IZB_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int* status = ep->ctx->d_status + 5;
+    ep_counts_kernel<<<1, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const int*>(offsets), ep->world, ep->rank,
+                                       ep->n_experts, ep->e_local, ep->recv_cap, status);
+    IZB_CUDA_TRY(cudaGetLastError());
+    const long long cap = static_cast<long long>(ep->ctx->sm_count) * 4;
+    const int grid = static_cast<int>(pairs < 1 ? 1 : (pairs < cap ? pairs : cap));
+    ep_dispatch_kernel<<<grid, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const uint4*>(x_perm),
+                                            static_cast<const int*>(offsets), pairs, ep->n_experts, ep->e_local, ep->hidden / 8,
+                                            ep->world, ep->rank);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ep_wait_kernel<<<1, 32, 0, s>>>(ep->local, ep->lay.flag_dispatch, ep->tables, ep->world, 0, status);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ep->ctx->launches.fetch_add(3, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_ep_return(izb_ep* ep, izb_stream stream, const void* y_rows) {
+    if (!ep || !ep->connected || !y_rows || !izb_aligned(y_rows, 16)) return IZB_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int* status = ep->ctx->d_status + 5;
+    const int grid = ep->ctx->sm_count * 4;
+    ep_return_kernel<<<grid, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const uint4*>(y_rows), ep->e_local,
+                                          ep->hidden / 8, ep->world, ep->rank);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ep_wait_kernel<<<1, 32, 0, s>>>(ep->local, ep->lay.flag_return, ep->tables, ep->world, 1, status);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ep->ctx->launches.fetch_add(2, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_ep_destroy(izb_ep* ep) {
+    if (!ep) return IZB_ERR_BAD_ARG;
+    for (int r = 0; r < ep->world; ++r)
+        if (r != ep->rank && ep->peers.base[r]) (void)cudaIpcCloseMemHandle(ep->peers.base[r]);
+    if (ep->local) (void)cudaFree(ep->local);
+    if (ep->tables) (void)cudaFree(ep->tables);
+    delete ep;
+    return IZB_OK;
+}
+
+}  // extern "C"

@@ -160,8 +160,29 @@ class Comm:
         dist.barrier()
         self.ar, self.ar_max = ar, max_bytes
 
+    def enable_peer_ep(self, n_experts: int, hidden: int, max_tokens_local: int, top_k: int):
+        """Sets up expert-parallel dispatch / return over NVLink peer memory (izb_ep_*) for layers of
+        this shape and at most max_tokens_local tokens per rank and step.  Collective."""
+        import torch.distributed as dist
+
+        from . import _lib as L
+        ep = C.c_void_p()
+        L.check(L.lib().izb_ep_create(self.ctx.handle, self.world, self.rank, n_experts, hidden, max_tokens_local, top_k,
+                                      C.byref(ep)), "izb_ep_create")
+        mine = (C.c_ubyte * 64)()
+        L.check(L.lib().izb_ep_local_handle(ep, mine), "izb_ep_local_handle")
+        every = [None] * self.world
+        dist.all_gather_object(every, bytes(mine))
+        L.check(L.lib().izb_ep_connect(ep, b"".join(every)), "izb_ep_connect")
+        dist.barrier()
+        self.ep = ep
+        self.ep_shape = (n_experts, hidden, max_tokens_local, top_k)
+
     def close(self):
         from . import _lib as L
+        if getattr(self, "ep", None):
+            L.lib().izb_ep_destroy(self.ep)
+            self.ep = None
         if getattr(self, "ar", None):
             L.lib().izb_ar_destroy(self.ar)
             self.ar = None
@@ -267,6 +288,9 @@ class EpMoeLayer:
         idx, wts = moe.topk(logits, self.k)
         offsets, perm, inv = moe.permute(idx, self.E)
         x_perm = moe.gather(x, perm, self.k)
+        if getattr(self.comm, "ep", None) is not None and self.comm.ep_shape[:2] == (self.E, self.H) \
+                and self.comm.ep_shape[3] == self.k and t <= self.comm.ep_shape[2]:
+            return self._forward_peer(x_perm, offsets, inv, wts, idx, t)
         # routing counts of every rank (the row counts of the exchange must be known on the host)
         all_off = torch.empty(ep, self.E + 1, device=dev, dtype=torch.int32)
         self.comm.allgather_bytes(offsets, all_off)
@@ -288,3 +312,30 @@ class EpMoeLayer:
         y_perm = torch.empty(max(t * self.k, 1), self.H, device=dev, dtype=torch.bfloat16)
         self.comm.alltoall_rows(back, recv_rows, y_perm, send_rows, self.H * 2)
         return moe.combine(y_perm[: t * self.k], inv, wts), idx, wts
+
+    def _forward_peer(self, x_perm, offsets, inv, wts, idx, t):
+        """Dispatch and return through peer memory: five launches of this library, no host read."""
+        import torch
+
+        from . import _lib as L
+        from . import moe
+        from .ops import Context, _ptr, _stream
+        lib, ep, dev = L.lib(), self.comm.ep, x_perm.device
+        ctx = Context.get(dev.index)
+        cap = lib.izb_ep_recv_capacity_rows(ep)
+        inter = self.w_down.shape[2]
+        if getattr(self, "_peer_bufs", None) is None or self._peer_bufs[0].shape[0] != cap:
+            self._peer_bufs = (torch.empty(cap, inter, device=dev, dtype=torch.bfloat16),
+                               torch.empty(cap, self.H, device=dev, dtype=torch.bfloat16))
+        hid, ys = self._peer_bufs
+        L.check(lib.izb_ep_dispatch(ep, _stream(), _ptr(x_perm), _ptr(offsets), t * self.k), "izb_ep_dispatch")
+        recv, seg = C.c_void_p(lib.izb_ep_recv_rows(ep)), C.c_void_p(lib.izb_ep_recv_offsets(ep))
+        L.check(lib.izb_moe_grouped_gemm(ctx.handle, _stream(), recv, _ptr(self.w_gate_up), seg, _ptr(hid), L.IZB_BF16, cap,
+                                         2 * inter, self.H, self.E_local, moe.EPILOGUE["swiglu"]), "izb_moe_grouped_gemm")
+        L.check(lib.izb_moe_grouped_gemm(ctx.handle, _stream(), _ptr(hid), _ptr(self.w_down), seg, _ptr(ys), L.IZB_BF16, cap,
+                                         self.H, inter, self.E_local, moe.EPILOGUE[None]), "izb_moe_grouped_gemm")
+        L.check(lib.izb_ep_return(ep, _stream(), _ptr(ys)), "izb_ep_return")
+        y = torch.empty(t, self.H, device=dev, dtype=torch.bfloat16)
+        L.check(lib.izb_moe_combine(ctx.handle, _stream(), C.c_void_p(lib.izb_ep_returned_rows(ep)), _ptr(inv), _ptr(wts), t,
+                                    self.k, self.H, _ptr(y)), "izb_moe_combine")
+        return y, idx, wts

@@ -89,6 +89,19 @@ def main():
         err = float((y.float() - y_ref[lo_t:hi_t].float()).abs().max()) / float(y_ref.float().abs().max())
         assert err < 2e-2, ("ep", t_total, err)
     ops.Context.get(rank).check()
+    # the same layer with dispatch and return over peer memory: identical routing, same tolerance,
+    # many steps in a row (sequence numbers, buffer reuse), ragged and empty shares
+    comm.enable_peer_ep(e, h, 600, k)
+    for step, t_total in enumerate((world, 64, 1000, world + 1, 333, 1000, 1000)):
+        x_all = rn(t_total, h)
+        lo_t, hi_t = parallel.split_range(t_total, world, rank)
+        y, idx, wts = ep_layer.forward(x_all[lo_t:hi_t].contiguous())
+        y_ref, _, idx_ref, _ = ref_layer.forward(x_all)
+        assert torch.equal(idx, idx_ref[lo_t:hi_t]), "peer ep routing"
+        if hi_t > lo_t:
+            err = float((y.float() - y_ref[lo_t:hi_t].float()).abs().max()) / float(y_ref.float().abs().max())
+            assert err < 2e-2, ("peer ep", step, t_total, err)
+        ops.Context.get(rank).check()
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
