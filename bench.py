@@ -559,6 +559,9 @@ def run_sharded(args):
             del wgu, wd
         lo_t, hi_t = parallel.split_range(t_total, world, rank)
         x = rn(t_total, h)[lo_t:hi_t].contiguous()
+        if world > 1 and not args.nccl_ep:
+            # rows travel through NVLink peer memory with device-side counts (no host read per layer)
+            comm.enable_peer_ep(e, h, (t_total + world - 1) // world, k)
 
         def step():
             for layer in layers:
@@ -567,7 +570,8 @@ def run_sharded(args):
         flops = 2.0 * t_total * k * 3 * inter * h * n_layers
         cfg.update(model="qwen3-30b-a3b MoE FFN layers", tokens_per_step=t_total, layers=n_layers,
                    note="8 of the 48 layers (each layer is 1.2 GB of expert weights)",
-                   parallelism=f"ep{world}: {e // world} experts per rank, tokens split, all-to-all each way")
+                   parallelism=f"ep{world}: {e // world} experts per rank, tokens split, dispatch and return each way "
+                               + ("over NCCL with host-side counts" if args.nccl_ep or world == 1 else "over peer memory"))
     else:
         name, n_layers, d, ff, frames, batch, has_bias, act = param
         lo_b, hi_b = parallel.batch_split(batch, world, rank)
@@ -679,6 +683,7 @@ def main():
     ap.add_argument("--case-steps", type=int, default=300)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cases", action="store_true")
+    ap.add_argument("--nccl-ep", action="store_true", help="expert-parallel workloads: exchange rows with NCCL instead of peer memory")
     ap.add_argument("--no-graph", action="store_true", help="sharded decode workloads: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--gemm-case", default=None,
                     help="profiler captures: run only this prefill / encoder GEMM shape (a name from gemm_cases) and exit")
