@@ -83,6 +83,31 @@ def ep_recv_plan(all_offsets: np.ndarray, ep: int, rank: int) -> tuple[np.ndarra
     return recv_rows, local_ids.astype(np.int32)
 
 
+def ep_peer_tables(counts: np.ndarray, rank: int) -> dict:
+    """The placement tables of the peer-memory dispatch (izb_ep_dispatch derives the same on the
+    device from the exchanged counts).  counts [world, E]: rows rank s holds for expert e.
+      dst_row[e]       first row, in the owner's receive buffer, of this rank's rows for expert e
+      recv_start[l, s] first received row of (local expert l, source s); rows are grouped by local
+                       expert, then source rank, then source order
+      seg[l]           grouped-GEMM offsets over the local experts (seg[-1] = rows received)
+      ret_start[s, l]  row, in source s's own expert-major order, where its rows of local expert l begin
+    """
+    world, e = counts.shape
+    per = e // world
+    dst_row = np.zeros(e, dtype=np.int64)
+    for ex in range(e):
+        first = ex // per * per
+        dst_row[ex] = counts[:, first:ex].sum() + counts[:rank, ex].sum()
+    mine = counts[:, rank * per:(rank + 1) * per]                  # [source, local expert]
+    flat = mine.T.reshape(-1)                                      # local expert major, source minor
+    starts = np.concatenate([[0], np.cumsum(flat)])
+    recv_start = starts[:-1].reshape(per, world)
+    seg = np.concatenate([recv_start[:, 0], [starts[-1]]])
+    src_offsets = np.concatenate([np.zeros((world, 1), dtype=np.int64), np.cumsum(counts, axis=1)], axis=1)
+    ret_start = src_offsets[:, rank * per:(rank + 1) * per]
+    return {"dst_row": dst_row, "recv_start": recv_start, "seg": seg, "ret_start": ret_start, "total": int(starts[-1])}
+
+
 def batch_split(batch: int, world: int, rank: int) -> tuple[int, int]:
     """Utterances [lo, hi) a rank encodes (weights replicated, no collective)."""
     return split_range(batch, world, rank)

@@ -140,3 +140,51 @@ def test_two_gloo_ranks_ep_and_tp():
     for rank, err, err_tp in results:
         assert err < 1e-4, (rank, err)
         assert err_tp < 1e-4, (rank, err_tp)
+
+
+@pytest.mark.parametrize("world,e", [(2, 16), (4, 16), (8, 128), (8, 8)])
+def test_peer_ep_tables_route_every_row_to_its_expert_and_home(world, e):
+    """Simulates the peer-memory dispatch and return with the placement tables on random routing,
+    hot experts and empty (expert, source) groups included: every row lands in a slot of its own on
+    the rank that owns its expert, inside that expert's segment, in (source, order) sequence, and the
+    return puts it back on the row it left from."""
+    rng = np.random.default_rng(world * 100 + e)
+    per = e // world
+    p = rng.dirichlet(np.full(e, 0.3))
+    counts = np.stack([rng.multinomial(int(rng.integers(0, 300)), p) for _ in range(world)])  # [source, expert]
+    counts[:, rng.integers(0, e)] = 0                                                      # an expert nobody chose
+    tabs = [P.ep_peer_tables(counts, r) for r in range(world)]
+    # source rows: expert-major, tagged (source, expert, order)
+    recv = [np.full((tabs[r]["total"], 3), -1, dtype=np.int64) for r in range(world)]
+    for s in range(world):
+        for ex in range(e):
+            owner = ex // per
+            for j in range(counts[s, ex]):
+                slot = tabs[s]["dst_row"][ex] + j
+                assert (recv[owner][slot] == -1).all(), "two rows stored to one slot"
+                recv[owner][slot] = (s, ex, j)
+    home = [np.full(counts[s].sum(), -1, dtype=np.int64) for s in range(world)]
+    for r in range(world):
+        assert (recv[r] >= 0).all(), "a received slot was never written"
+        seg = tabs[r]["seg"]
+        assert seg[0] == 0 and seg[-1] == counts[:, r * per:(r + 1) * per].sum()
+        for l in range(per):
+            rows = recv[r][seg[l]:seg[l + 1]]
+            assert (rows[:, 1] == r * per + l).all()                                       # only this expert's rows
+            key = rows[:, 0] * 10 ** 6 + rows[:, 2]
+            assert (np.diff(key) > 0).all()                                               # source-major, in source order
+            for s in range(world):
+                a = tabs[r]["recv_start"][l, s]
+                assert (recv[r][a:a + counts[s, r * per + l], 0] == s).all()
+        # return: row i of (local expert l, source s, order j) goes home to ret_start[s, l] + j
+        for i, (s, ex, j) in enumerate(recv[r]):
+            slot = tabs[r]["ret_start"][s, ex - r * per] + j
+            assert home[s][slot] == -1
+            home[s][slot] = ex
+    for s in range(world):
+        assert np.array_equal(home[s], np.repeat(np.arange(e), counts[s]))                # its own expert-major order
+    # consistent with the host planner of the NCCL path
+    for r in range(world):
+        offs = np.concatenate([np.zeros((world, 1), dtype=np.int64), np.cumsum(counts, axis=1)], axis=1)
+        recv_rows, _ = P.ep_recv_plan(offs, world, r)
+        assert recv_rows.sum() == tabs[r]["total"]
