@@ -257,9 +257,11 @@ int32_t izb_ar_destroy(izb_ar* ar);
  * Set-up as for izb_ar_*: izb_ep_create on every rank (allocates the rank's receive and return
  * buffers for at most max_tokens_local tokens per rank and step), exchange the 64-byte handles,
  * izb_ep_connect.  Per layer, after the local routing (izb_moe_topk / permute / gather):
- *   izb_ep_dispatch(x_perm, offsets, pairs): exchanges the per-expert counts, stores every row into
- *     its owner's receive buffer (rows grouped by local expert, then source rank) and waits for the
- *     rows of all ranks; afterwards izb_ep_recv_rows() / izb_ep_recv_offsets() [local experts + 1]
+ *   izb_ep_dispatch(x, ld_x, perm, offsets, pairs): exchanges the per-expert counts, stores every row
+ *     into its owner's receive buffer (rows grouped by local expert, then source rank) and waits for
+ *     the rows of all ranks; with perm = NULL x holds the `pairs` rows already in expert-major order
+ *     (izb_moe_gather's output), otherwise x is the token matrix [tokens, hidden] (rows ld_x apart)
+ *     and row r is read from x[perm[r] / top_k]: the gather is fused into the dispatch; afterwards izb_ep_recv_rows() / izb_ep_recv_offsets() [local experts + 1]
  *     feed izb_moe_grouped_gemm with rows = izb_ep_recv_capacity_rows();
  *   izb_ep_return(y_rows): stores each result row back to the rank it came from, at the row it left
  *     from in that rank's permuted order, and waits for this rank's rows: izb_ep_returned_rows()
@@ -275,8 +277,8 @@ int64_t izb_ep_recv_capacity_rows(const izb_ep* ep);
 void* izb_ep_recv_rows(const izb_ep* ep);
 const void* izb_ep_recv_offsets(const izb_ep* ep);
 const void* izb_ep_returned_rows(const izb_ep* ep);
-int32_t izb_ep_dispatch(izb_ep* ep, izb_stream stream, const void* x_perm, const void* offsets,
-                        int64_t pairs);
+int32_t izb_ep_dispatch(izb_ep* ep, izb_stream stream, const void* x, int64_t ld_x, const void* perm,
+                        const void* offsets, int64_t pairs);
 int32_t izb_ep_return(izb_ep* ep, izb_stream stream, const void* y_rows);
 int32_t izb_ep_destroy(izb_ep* ep);
 

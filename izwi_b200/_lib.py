@@ -101,7 +101,7 @@ _SIGNATURES = {
     "izb_ep_recv_rows": (C.c_void_p, [C.c_void_p]),
     "izb_ep_recv_offsets": (C.c_void_p, [C.c_void_p]),
     "izb_ep_returned_rows": (C.c_void_p, [C.c_void_p]),
-    "izb_ep_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
+    "izb_ep_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64]),
     "izb_ep_return": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "izb_ep_destroy": (C.c_int32, [C.c_void_p]),
     "izb_rms_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -160,9 +160,17 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-// Copies one row of `row_units` 16-byte units with the whole CTA.
-__device__ __forceinline__ void ep_copy_row(uint4* __restrict__ dst, const uint4* __restrict__ src, int row_units) {
-    for (int u = threadIdx.x; u < row_units; u += blockDim.x) dst[u] = src[u];
+// Copies one row of `row_units` 16-byte units with one warp: eight loads in flight per lane.
+__device__ __forceinline__ void ep_copy_row(uint4* __restrict__ dst, const uint4* __restrict__ src, int row_units, int lane) {
+    int u = lane;
+    for (; u + 7 * 32 < row_units; u += 8 * 32) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = src[u + 32 * j];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[u + 32 * j] = v[j];
+    }
+    for (; u < row_units; u += 32) dst[u] = src[u];
 }
 
 // After a CTA's stores: fence to system scope, count the CTA in; the last one raises this rank's
@@ -182,57 +190,62 @@ __device__ __forceinline__ void ep_signal(unsigned int* counter, EpPeers peers, 
     }
 }
 
-// x_perm: this rank's rows in expert-major order.  Row r of expert e goes to the owner's receive
-// buffer at dst_row[e] + (r - offsets[e]).
+// Row r (expert-major order) of expert e goes to the owner's receive buffer at dst_row[e] +
+// (r - offsets[e]).  Its source is x_perm[r], or, with `perm` given, x[perm[r] / top_k] (the gather
+// of the routing fused into the dispatch).  One warp per row.
 __global__ void __launch_bounds__(256)
-    ep_dispatch_kernel(EpPeers peers, EpLayout lay, const EpTables* __restrict__ tb, const uint4* __restrict__ x_perm,
-                       const int* __restrict__ offsets, long long pairs, int n_experts, int e_local, int row_units, int world,
-                       int rank) {
-    __shared__ int s_e, s_dst;
-    for (long long r = blockIdx.x; r < pairs; r += gridDim.x) {
-        if (threadIdx.x == 0) {
+    ep_dispatch_kernel(EpPeers peers, EpLayout lay, const EpTables* __restrict__ tb, const uint4* __restrict__ x,
+                       const int* __restrict__ perm, int top_k, long long ld_units, const int* __restrict__ offsets,
+                       long long pairs, int n_experts, int e_local, int row_units, int world, int rank) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    for (long long r = static_cast<long long>(blockIdx.x) * wpb + warp; r < pairs; r += static_cast<long long>(gridDim.x) * wpb) {
+        int e = 0, dst_row = -1;
+        long long src_row = r;
+        if (lane == 0) {
             int lo = 0, hi = n_experts;  // last e with offsets[e] <= r
             while (hi - lo > 1) {
                 const int mid = (lo + hi) >> 1;
                 if (offsets[mid] <= r) lo = mid; else hi = mid;
             }
-            s_e = lo;
-            s_dst = tb->dst_row[lo] < 0 ? -1 : tb->dst_row[lo] + static_cast<int>(r - offsets[lo]);
+            e = lo;
+            dst_row = tb->dst_row[lo] < 0 ? -1 : tb->dst_row[lo] + static_cast<int>(r - offsets[lo]);
+            if (perm) src_row = perm[r] / top_k;
         }
-        __syncthreads();
-        if (s_dst >= 0) {
-            uint4* dst = reinterpret_cast<uint4*>(peers.base[s_e / e_local] + lay.x_recv) + static_cast<long long>(s_dst) * row_units;
-            ep_copy_row(dst, x_perm + r * row_units, row_units);
+        e = __shfl_sync(0xFFFFFFFFu, e, 0);
+        dst_row = __shfl_sync(0xFFFFFFFFu, dst_row, 0);
+        src_row = __shfl_sync(0xFFFFFFFFu, src_row, 0);
+        if (dst_row >= 0) {
+            uint4* dst = reinterpret_cast<uint4*>(peers.base[e / e_local] + lay.x_recv) + static_cast<long long>(dst_row) * row_units;
+            ep_copy_row(dst, x + src_row * ld_units, row_units, lane);
         }
-        __syncthreads();
     }
     EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
     ep_signal(&hdr->done_dispatch, peers, lay.flag_dispatch, world, rank, tb->step);
 }
 
 // y: results for the received rows, same order.  Row i (local expert el, source s, position j) goes
-// to the source's return buffer at ret_start[s][el] + j.
+// to the source's return buffer at ret_start[s][el] + j.  One warp per row.
 __global__ void __launch_bounds__(256)
     ep_return_kernel(EpPeers peers, EpLayout lay, const EpTables* __restrict__ tb, const uint4* __restrict__ y, int e_local,
                      int row_units, int world, int rank) {
-    __shared__ int s_src, s_dst;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     const int groups = e_local * world;
     const int total = tb->recv_start[groups];
-    for (int i = blockIdx.x; i < total; i += gridDim.x) {
-        if (threadIdx.x == 0) {
+    for (int i = blockIdx.x * wpb + warp; i < total; i += gridDim.x * wpb) {
+        int src = 0, dst_row = 0;
+        if (lane == 0) {
             int lo = 0, hi = groups;  // last group whose start <= i (empty groups share a start: take the last)
             while (hi - lo > 1) {
                 const int mid = (lo + hi) >> 1;
                 if (tb->recv_start[mid] <= i) lo = mid; else hi = mid;
             }
-            const int el = lo / world, s = lo % world;
-            s_src = s;
-            s_dst = tb->ret_start[s][el] + (i - tb->recv_start[lo]);
+            src = lo % world;
+            dst_row = tb->ret_start[src][lo / world] + (i - tb->recv_start[lo]);
         }
-        __syncthreads();
-        uint4* dst = reinterpret_cast<uint4*>(peers.base[s_src] + lay.y_ret) + static_cast<long long>(s_dst) * row_units;
-        ep_copy_row(dst, y + static_cast<long long>(i) * row_units, row_units);
-        __syncthreads();
+        src = __shfl_sync(0xFFFFFFFFu, src, 0);
+        dst_row = __shfl_sync(0xFFFFFFFFu, dst_row, 0);
+        uint4* dst = reinterpret_cast<uint4*>(peers.base[src] + lay.y_ret) + static_cast<long long>(dst_row) * row_units;
+        ep_copy_row(dst, y + static_cast<long long>(i) * row_units, row_units, lane);
     }
     EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
     ep_signal(&hdr->done_return, peers, lay.flag_return, world, rank, tb->step);
@@ -364,19 +377,21 @@ const void* izb_ep_recv_offsets(const izb_ep* ep) {
 }
 const void* izb_ep_returned_rows(const izb_ep* ep) { return ep ? ep->local + ep->lay.y_ret : nullptr; }
 
-int32_t izb_ep_dispatch(izb_ep* ep, izb_stream stream, const void* x_perm, const void* offsets, int64_t pairs) {
+int32_t izb_ep_dispatch(izb_ep* ep, izb_stream stream, const void* x, int64_t ld_x, const void* perm, const void* offsets,
+                        int64_t pairs) {
     if (!ep || !ep->connected || pairs < 0 || pairs > ep->max_pairs_local) return IZB_ERR_BAD_ARG;
-    if (!offsets || (pairs > 0 && !x_perm) || !izb_aligned(x_perm, 16) || !izb_aligned(offsets, 4)) return IZB_ERR_BAD_ARG;
+    if (!offsets || (pairs > 0 && !x) || !izb_aligned(x, 16) || !izb_aligned(offsets, 4) || !izb_aligned(perm, 4)) return IZB_ERR_BAD_ARG;
+    if (ld_x < ep->hidden || ld_x % 8 != 0) return IZB_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int* status = ep->ctx->d_status + 5;
     ep_counts_kernel<<<1, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const int*>(offsets), ep->world, ep->rank,
                                        ep->n_experts, ep->e_local, ep->recv_cap, status);
     IZB_CUDA_TRY(cudaGetLastError());
-    const long long cap = static_cast<long long>(ep->ctx->sm_count) * 4;
-    const int grid = static_cast<int>(pairs < 1 ? 1 : (pairs < cap ? pairs : cap));
-    ep_dispatch_kernel<<<grid, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const uint4*>(x_perm),
-                                            static_cast<const int*>(offsets), pairs, ep->n_experts, ep->e_local, ep->hidden / 8,
-                                            ep->world, ep->rank);
+    const long long cap = static_cast<long long>(ep->ctx->sm_count) * 4, blocks = (pairs + 7) / 8;
+    const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+    ep_dispatch_kernel<<<grid, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const uint4*>(x),
+                                            static_cast<const int*>(perm), ep->top_k, ld_x / 8, static_cast<const int*>(offsets),
+                                            pairs, ep->n_experts, ep->e_local, ep->hidden / 8, ep->world, ep->rank);
     IZB_CUDA_TRY(cudaGetLastError());
     ep_wait_kernel<<<1, 32, 0, s>>>(ep->local, ep->lay.flag_dispatch, ep->tables, ep->world, 0, status);
     IZB_CUDA_TRY(cudaGetLastError());

@@ -312,10 +312,10 @@ class EpMoeLayer:
         logits = ops.linear(x, self.w_router, bias=self.router_bias, out_dtype=torch.float32)
         idx, wts = moe.topk(logits, self.k)
         offsets, perm, inv = moe.permute(idx, self.E)
-        x_perm = moe.gather(x, perm, self.k)
         if getattr(self.comm, "ep", None) is not None and self.comm.ep_shape[:2] == (self.E, self.H) \
-                and self.comm.ep_shape[3] == self.k and t <= self.comm.ep_shape[2]:
-            return self._forward_peer(x_perm, offsets, inv, wts, idx, t)
+                and self.comm.ep_shape[3] == self.k and t <= self.comm.ep_shape[2] and x.stride(1) == 1:
+            return self._forward_peer(x, perm, offsets, inv, wts, idx, t)
+        x_perm = moe.gather(x, perm, self.k)
         # routing counts of every rank (the row counts of the exchange must be known on the host)
         all_off = torch.empty(ep, self.E + 1, device=dev, dtype=torch.int32)
         self.comm.allgather_bytes(offsets, all_off)
@@ -338,14 +338,14 @@ class EpMoeLayer:
         self.comm.alltoall_rows(back, recv_rows, y_perm, send_rows, self.H * 2)
         return moe.combine(y_perm[: t * self.k], inv, wts), idx, wts
 
-    def _forward_peer(self, x_perm, offsets, inv, wts, idx, t):
-        """Dispatch and return through peer memory: five launches of this library, no host read."""
+    def _forward_peer(self, x, perm, offsets, inv, wts, idx, t):
+        """Dispatch (with the gather fused in) and return through peer memory: no host read."""
         import torch
 
         from . import _lib as L
         from . import moe
         from .ops import Context, _ptr, _stream
-        lib, ep, dev = L.lib(), self.comm.ep, x_perm.device
+        lib, ep, dev = L.lib(), self.comm.ep, x.device
         ctx = Context.get(dev.index)
         cap = lib.izb_ep_recv_capacity_rows(ep)
         inter = self.w_down.shape[2]
@@ -353,7 +353,8 @@ class EpMoeLayer:
             self._peer_bufs = (torch.empty(cap, inter, device=dev, dtype=torch.bfloat16),
                                torch.empty(cap, self.H, device=dev, dtype=torch.bfloat16))
         hid, ys = self._peer_bufs
-        L.check(lib.izb_ep_dispatch(ep, _stream(), _ptr(x_perm), _ptr(offsets), t * self.k), "izb_ep_dispatch")
+        L.check(lib.izb_ep_dispatch(ep, _stream(), _ptr(x), x.stride(0), _ptr(perm), _ptr(offsets), t * self.k),
+                "izb_ep_dispatch")
         recv, seg = C.c_void_p(lib.izb_ep_recv_rows(ep)), C.c_void_p(lib.izb_ep_recv_offsets(ep))
         L.check(lib.izb_moe_grouped_gemm(ctx.handle, _stream(), recv, _ptr(self.w_gate_up), seg, _ptr(hid), L.IZB_BF16, cap,
                                          2 * inter, self.H, self.E_local, moe.EPILOGUE["swiglu"]), "izb_moe_grouped_gemm")
