@@ -519,7 +519,8 @@ def run_sharded(args):
     kind, param = SHARDED[args.workload]
     comm = parallel.Comm(local) if world > 1 else None
     if comm is not None and kind == "tp":
-        comm.enable_peer_allreduce(1 << 20)      # decode-size sums go through NVLink peer memory, not NCCL
+        # sums go through NVLink peer memory, not NCCL: one-shot up to 1 MB, two-shot up to 64 MB
+        comm.enable_peer_allreduce(1 << 20 if args.nccl_ep else 64 << 20)
     gen = torch.Generator(device=device).manual_seed(3)       # same stream of weights on every rank
     rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
     cfg = {"workload": args.workload, "l2": "weights larger than L2"}

@@ -243,7 +243,12 @@ int32_t izb_ep_alltoall(izb_comm* comm, izb_stream stream, const void* send,
  * every rank calls izb_ar_create (allocates its buffer), passes its 64-byte handle to all ranks,
  * and calls izb_ar_connect with the `world` handles in rank order.  izb_ar_allreduce is in place,
  * needs count*elem_size <= max_bytes, a 4-byte aligned buffer and a byte size that is a multiple
- * of 4; it can be replayed from a CUDA graph.  No counterpart in the reference (single device). */
+ * of 4; it can be replayed from a CUDA graph.
+ * Messages above 1 MB (when max_bytes allows them: the sums after a row-split projection at
+ * prefill sizes) take a two-shot bandwidth path instead: the operand is copied into the rank's
+ * region, each rank reduces 1/world of it with peer loads and stores the result chunk into every
+ * region, and the result is copied out (three launches; 16-byte aligned buffer, byte size a
+ * multiple of 16, IZB_ERR_UNSUPPORTED otherwise).  No counterpart in the reference (single device). */
 typedef struct izb_ar izb_ar;
 int32_t izb_ar_create(izb_ctx* ctx, int32_t world, int32_t rank, size_t max_bytes, izb_ar** out);
 int32_t izb_ar_local_handle(izb_ar* ar, void* out_64_bytes);

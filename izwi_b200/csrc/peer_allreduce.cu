@@ -4,18 +4,28 @@
 // (bounded) its own buffer for the words of all ranks and adds them in rank order.  One kernel, no
 // NCCL launch, no multimem, no TMA on peer memory.  Slots are double-buffered by call parity; the
 // call sequence number lives in device memory so the launch can be replayed from a CUDA graph.
+#include <cstddef>
 #include <cstring>
 #include <new>
 
 #include "izb_common.cuh"
 
 constexpr int AR_MAX_WORLD = 8;
-constexpr int AR_MAX_CTAS = 16;  // all CTAs must be resident at once (they wait on other GPUs)
+constexpr int AR_MAX_CTAS = 16;
+constexpr size_t AR_LL_MAX_BYTES = 1 << 20;  // above this the two-shot bandwidth path takes over  // all CTAs must be resident at once (they wait on other GPUs)
 
 struct ArDevState {
-    unsigned int seq;   // calls completed so far on this rank (0 = none; slots start zeroed, so no stale word matches)
-    unsigned int done;  // CTAs of the current call that finished reducing
+    unsigned int seq;   // one-shot calls completed so far on this rank (0 = none; slots start zeroed, so no stale word matches)
+    unsigned int done;  // CTAs of the current one-shot call that finished reducing
+    // two-shot path (large messages)
+    unsigned int big_seq;                  // two-shot calls completed on this rank
+    unsigned int done_a, done_b, done_c;   // CTA counters of its three kernels
+    unsigned int pad_[10];
+    unsigned int flag_a[AR_MAX_WORLD];     // rank s has copied its operand into its region (value = call number)
+    unsigned int pad2_[8];
+    unsigned int flag_b[AR_MAX_WORLD];     // rank s has stored its reduced chunk into this region
 };
+static_assert(sizeof(ArDevState) <= 256, "ArDevState must fit the region header");
 
 struct ArPeers {
     unsigned char* base[AR_MAX_WORLD];  // every rank's region: [ArDevState (256 B)][2][world][slot_bytes]
@@ -25,6 +35,8 @@ struct izb_ar {
     izb_ctx* ctx;
     int world, rank;
     size_t slot_bytes;
+    size_t big_bytes;  // capacity of the two-shot operand / result buffers (0: path off)
+    size_t big_in, big_res;  // their byte offsets inside a region
     unsigned char* local;
     ArPeers peers;
     bool connected;
@@ -108,6 +120,139 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(ArPeers peers, int 
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two-shot all-reduce for large messages (the sums after a row-split projection at prefill sizes):
+// bandwidth-bound, so every byte crosses NVLink once in each direction.  Three launches:
+//   a. copy the operand into this rank's region, fence, raise flag_a on every rank;
+//   b. wait for all flag_a; reduce this rank's 1/world chunk by loading it from every region (peer
+//      loads), summing in fp32 in rank order, and storing the result chunk into every region;
+//      fence, raise flag_b on every rank;
+//   c. wait for all flag_b; copy the assembled result out.
+// Stream order is the barrier inside a GPU; the flags (the call number) order the GPUs.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ar_st_flag(unsigned int* p, unsigned int v) {
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ar_ld_flag(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ar_ld_peer(const uint4* p) {  // not through L1: the line may be a previous call's
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// After a CTA's stores: system-scope fence, count the CTA in; the last one raises flag[rank] = value on every rank.
+__device__ __forceinline__ void ar_signal_all(unsigned int* counter, const ArPeers& peers, size_t flag_field, int world, int rank,
+                                              unsigned int value) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(counter, 1u);
+        if (prev == gridDim.x - 1) {
+            *counter = 0;
+            __threadfence_system();
+            for (int p = 0; p < world; ++p)
+                ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + p) % world] + flag_field) + rank, value);
+        }
+    }
+}
+
+// Threads 0 .. world-1 of the CTA wait (bounded) for flag[s] == value; returns false on time-out.
+__device__ __forceinline__ bool ar_wait_all(const unsigned char* local, size_t flag_field, int world, unsigned int value, int* status) {
+    __shared__ int timed_out;
+    if (threadIdx.x == 0) timed_out = 0;
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < world) {
+        const unsigned int* f = reinterpret_cast<const unsigned int*>(local + flag_field) + threadIdx.x;
+        const long long t0 = clock64();
+        while (ar_ld_flag(f) != value) {
+            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                timed_out = 1;
+                atomicExch(status, 3);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    return timed_out == 0;
+}
+
+__global__ void __launch_bounds__(512)
+    ar2_copy_in_kernel(ArPeers peers, int world, int rank, size_t big_in, const uint4* __restrict__ buf, long long n_units) {
+    ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
+    const unsigned int call = st->big_seq + 1;
+    uint4* dst = reinterpret_cast<uint4*>(peers.base[rank] + big_in);
+    for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < n_units;
+         u += static_cast<long long>(gridDim.x) * blockDim.x)
+        dst[u] = buf[u];
+    ar_signal_all(&st->done_a, peers, offsetof(ArDevState, flag_a), world, rank, call);
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(512)
+    ar2_reduce_kernel(ArPeers peers, int world, int rank, size_t big_in, size_t big_res, long long n_units, int* status) {
+    ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
+    const unsigned int call = st->big_seq + 1;
+    const bool ok = ar_wait_all(peers.base[rank], offsetof(ArDevState, flag_a), world, call, status);
+    if (ok) {
+        const long long per = (n_units + world - 1) / world;
+        const long long lo = per * rank, hi = lo + per < n_units ? lo + per : n_units;
+        for (long long u = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < hi;
+             u += static_cast<long long>(gridDim.x) * blockDim.x) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+            for (int r = 0; r < world; ++r) {
+                const uint4 v = ar_ld_peer(reinterpret_cast<const uint4*>(peers.base[r] + big_in) + u);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (F32) {
+                        acc[j] += __uint_as_float(w[j]);
+                    } else {
+                        acc[2 * j] += izb::bf16_lo_to_f32(w[j]);
+                        acc[2 * j + 1] += izb::bf16_hi_to_f32(w[j]);
+                    }
+                }
+            }
+            uint4 o;
+            if (F32) {
+                o = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+            } else {
+                o = make_uint4(izb::pack_bf16x2(acc[0], acc[1]), izb::pack_bf16x2(acc[2], acc[3]), izb::pack_bf16x2(acc[4], acc[5]),
+                               izb::pack_bf16x2(acc[6], acc[7]));
+            }
+            for (int p = 0; p < world; ++p) reinterpret_cast<uint4*>(peers.base[(rank + p) % world] + big_res)[u] = o;
+        }
+    }
+    ar_signal_all(&st->done_b, peers, offsetof(ArDevState, flag_b), world, rank, call);
+}
+
+__global__ void __launch_bounds__(512)
+    ar2_copy_out_kernel(ArPeers peers, int world, int rank, size_t big_res, uint4* __restrict__ buf, long long n_units, int* status) {
+    ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
+    const unsigned int call = st->big_seq + 1;
+    if (ar_wait_all(peers.base[rank], offsetof(ArDevState, flag_b), world, call, status)) {
+        const uint4* src = reinterpret_cast<const uint4*>(peers.base[rank] + big_res);
+        for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < n_units;
+             u += static_cast<long long>(gridDim.x) * blockDim.x)
+            buf[u] = ar_ld_peer(src + u);
+    }
+    // the last CTA out closes the call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&st->done_c, 1u) == gridDim.x - 1) {
+            st->done_c = 0;
+            __threadfence();
+            st->big_seq = call;
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -121,15 +266,21 @@ int32_t izb_ar_create(izb_ctx* ctx, int32_t world, int32_t rank, size_t max_byte
     ar->ctx = ctx;
     ar->world = world;
     ar->rank = rank;
-    ar->slot_bytes = (2 * max_bytes + 255) / 256 * 256;  // every 4 payload bytes travel as an 8-byte pair
+    // messages up to 1 MB take the one-shot latency path; larger ones (up to max_bytes) the two-shot bandwidth path
+    const size_t ll_max = max_bytes < AR_LL_MAX_BYTES ? max_bytes : AR_LL_MAX_BYTES;
+    ar->slot_bytes = (2 * ll_max + 255) / 256 * 256;  // every 4 payload bytes travel as an 8-byte pair
+    ar->big_bytes = max_bytes > AR_LL_MAX_BYTES ? (max_bytes + 255) / 256 * 256 : 0;
+    ar->big_in = AR_HEADER + 2 * static_cast<size_t>(world) * ar->slot_bytes;
+    ar->big_res = ar->big_in + ar->big_bytes;
     ar->connected = false;
     std::memset(&ar->peers, 0, sizeof(ar->peers));
-    const size_t total = AR_HEADER + 2 * static_cast<size_t>(world) * ar->slot_bytes;
+    const size_t total = ar->big_res + ar->big_bytes;
+    const size_t zeroed = ar->big_in;  // header and one-shot slots; the two-shot buffers are written before they are read
     int cur = -1;
     cudaGetDevice(&cur);
     if (cur != ctx->device) cudaSetDevice(ctx->device);
     void* p = nullptr;
-    const bool ok = cudaMalloc(&p, total) == cudaSuccess && cudaMemset(p, 0, total) == cudaSuccess &&
+    const bool ok = cudaMalloc(&p, total) == cudaSuccess && cudaMemset(p, 0, zeroed) == cudaSuccess &&
                     cudaDeviceSynchronize() == cudaSuccess;
     if (cur != ctx->device) cudaSetDevice(cur);
     if (!ok) {
@@ -177,7 +328,7 @@ int32_t izb_ar_connect(izb_ar* ar, const void* handles_world_x_64_bytes) {
     return rc;
 }
 
-size_t izb_ar_max_bytes(const izb_ar* ar) { return ar ? ar->slot_bytes / 2 : 0; }
+size_t izb_ar_max_bytes(const izb_ar* ar) { return ar ? (ar->big_bytes ? ar->big_bytes : ar->slot_bytes / 2) : 0; }
 
 int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count, int32_t dtype) {
     if (!ar || count < 0 || (dtype != IZB_BF16 && dtype != IZB_F32)) return IZB_ERR_BAD_ARG;
@@ -185,7 +336,31 @@ int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count
     if (count == 0) return IZB_OK;
     const size_t bytes = static_cast<size_t>(count) * (dtype == IZB_F32 ? 4 : 2);
     if (!buf || !izb_aligned(buf, 4) || bytes % 4 != 0) return IZB_ERR_BAD_ARG;
-    if (2 * bytes > ar->slot_bytes) return IZB_ERR_UNSUPPORTED;
+    if (2 * bytes > ar->slot_bytes) {
+        // two-shot path: whole 16-byte units, operand 16-byte aligned
+        if (bytes > ar->big_bytes) return IZB_ERR_UNSUPPORTED;
+        if (bytes % 16 != 0 || !izb_aligned(buf, 16)) return IZB_ERR_UNSUPPORTED;
+        const long long n_units = static_cast<long long>(bytes / 16);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        int* status = ar->ctx->d_status + 2;
+        const int copy_grid = ar->ctx->sm_count * 2;
+        const long long chunk = (n_units + ar->world - 1) / ar->world;
+        long long rg = (chunk + 511) / 512;
+        const int reduce_grid = static_cast<int>(rg < 1 ? 1 : (rg > ar->ctx->sm_count * 2 ? ar->ctx->sm_count * 2 : rg));
+        ar2_copy_in_kernel<<<copy_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_in, static_cast<const uint4*>(buf),
+                                                     n_units);
+        IZB_CUDA_TRY(cudaGetLastError());
+        if (dtype == IZB_F32)
+            ar2_reduce_kernel<true><<<reduce_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_in, ar->big_res, n_units, status);
+        else
+            ar2_reduce_kernel<false><<<reduce_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_in, ar->big_res, n_units, status);
+        IZB_CUDA_TRY(cudaGetLastError());
+        ar2_copy_out_kernel<<<copy_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_res, static_cast<uint4*>(buf), n_units,
+                                                      status);
+        IZB_CUDA_TRY(cudaGetLastError());
+        ar->ctx->launches.fetch_add(3, std::memory_order_relaxed);
+        return IZB_OK;
+    }
     const long long n_words = static_cast<long long>(bytes / 4);
     // latency, not bandwidth: one word per thread while the CTA limit allows (an 8 KB message = 8 CTAs)
     int grid = static_cast<int>((n_words + 255) / 256);

@@ -46,10 +46,12 @@ def main():
     assert float(t[0]) == world * (world + 1) / 2
 
     # ---- one-shot all-reduce over peer memory against NCCL, many calls in a row ----
-    comm.enable_peer_allreduce(1 << 20)
+    comm.enable_peer_allreduce(32 << 20)                           # one-shot up to 1 MB, two-shot above
     g2 = torch.Generator(device=dev).manual_seed(100 + rank)       # different partial sums per rank
     for n, dt in ((8, torch.bfloat16), (4096, torch.bfloat16), (131072, torch.bfloat16), (524288, torch.bfloat16),
-                  (4, torch.float32), (65536, torch.float32)) * 3:
+                  (4, torch.float32), (65536, torch.float32), (524296, torch.bfloat16), (4 << 20, torch.bfloat16),
+                  (16 << 20, torch.bfloat16), (1 << 20, torch.float32), ((1 << 20) + 4, torch.float32),
+                  ((2 << 20) + 6, torch.bfloat16)) * 3:
         part = torch.randn(n, device=dev, generator=g2).to(dt)
         want = part.clone()
         dist.all_reduce(want)
