@@ -686,6 +686,8 @@ def main():
     ap.add_argument("--no-cases", action="store_true")
     ap.add_argument("--nccl-ep", action="store_true", help="expert-parallel workloads: exchange rows with NCCL instead of peer memory")
     ap.add_argument("--no-graph", action="store_true", help="sharded decode workloads: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--attention-cases", action="store_true",
+                    help="profiler captures: run only the decode-attention cases and exit")
     ap.add_argument("--gemm-case", default=None,
                     help="profiler captures: run only this prefill / encoder GEMM shape (a name from gemm_cases) and exit")
     ap.add_argument("--layers", type=int, default=None,
@@ -693,6 +695,10 @@ def main():
     args = ap.parse_args()
     global LAYERS_OVERRIDE
     LAYERS_OVERRIDE = args.layers
+    if args.attention_cases:
+        import torch
+        print(json.dumps({"attention_cases": measure_attention_cases(torch.device("cuda", 0))}), flush=True)
+        return
     if args.gemm_case:
         import torch
         res = measure_gemm_cases(torch.device("cuda", 0), only=args.gemm_case, iters=max(1, min(args.steps, 20)))
