@@ -352,6 +352,60 @@ def measure_attention_cases(device):
     return out
 
 
+def measure_decode_token_cases(device):
+    """A whole greedy decode token of a Qwen3-0.6B-shaped model with Q8_0 projections (embedding, 28
+    layers of norm / fused QKV / q,k norm / RoPE / KV append / GQA attention / O / norm / gate-up /
+    SiLU-multiply / down, final norm, lm_head over 151,936 tokens, arg-max), captured once in a CUDA
+    graph at a fixed context length and replayed: what the linear stack of the headline sits in."""
+    import torch
+    from izwi_b200 import decoder, ops
+    from izwi_b200 import workloads as wl
+    peak_bw, _ = load_peaks()
+    shape = wl.QWEN3_0_6B
+    gen = torch.Generator(device=device).manual_seed(6)
+    vocab, hid, qd, kd = 151936, shape.hidden, shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
+    ones = lambda n: (1.0 + 0.1 * torch.randn(n, device=device, generator=gen)).to(torch.bfloat16)  # noqa: E731
+    layers = []
+    for _ in range(shape.layers):
+        layers.append(decoder.Qwen3DecoderLayer(decoder.Qwen3LayerWeights(
+            "q8_0", hid, shape.q_heads, shape.kv_heads, shape.head_dim, shape.intermediate, ones(hid), ones(hid),
+            ones(shape.head_dim), ones(shape.head_dim), wl.make_q8_0_weight(qd + 2 * kd, hid, gen),
+            wl.make_q8_0_weight(hid, qd, gen), wl.make_q8_0_weight(2 * shape.intermediate, hid, gen),
+            wl.make_q8_0_weight(hid, shape.intermediate, gen))))
+    embed = (torch.randn(vocab, hid, device=device, generator=gen) * 0.5).to(torch.bfloat16)
+    model = decoder.Qwen3Decoder(embed, layers, ones(hid), wl.make_q8_0_weight(vocab, hid, gen), "q8_0")
+    weight_bytes = sum(w.numel() for l in layers for w in (l.w.qkv, l.w.o, l.w.gate_up, l.w.down)) + model.lm_head.numel()
+    out = []
+    for ctx_len in (512, 4096):
+        caches = [decoder.KvCache(1, shape.kv_heads, ctx_len + 8, shape.head_dim, device) for _ in layers]
+        for c in caches:
+            c.k.normal_(generator=gen)
+            c.v.normal_(generator=gen)
+        tok = torch.tensor([17], device=device)
+        cos, sin = model.rope_tables(ctx_len, 1)
+        launches0 = ops.Context.get(device.index).launch_count
+        for _ in range(2):
+            nxt = model.step(tok, caches, ctx_len, cos, sin)
+        torch.cuda.synchronize()
+        launches = (ops.Context.get(device.index).launch_count - launches0) // 2
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            nxt = model.step(tok, caches, ctx_len, cos, sin)
+        ms = _time_call(graph.replay, 30)
+        ops.Context.get(device.index).check()
+        kv_bytes = shape.layers * 2 * shape.kv_heads * (ctx_len + 1) * shape.head_dim * 2
+        gbs = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+        out.append({"workload": f"qwen3-0.6b-q8_0-greedy-token-ctx{ctx_len}", "ms_per_token": round(ms, 4),
+                    "tokens_per_s": round(1e3 / ms, 1), "kernels_per_token": int(launches),
+                    "weight_and_kv_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak_bw, 4),
+                    "next_token": int(nxt[0])})
+        del caches, graph
+        torch.cuda.empty_cache()
+    del model, layers, embed
+    torch.cuda.empty_cache()
+    return out
+
+
 def measure_moe_cases(device):
     """One Qwen3-30B-A3B-shaped MoE layer (H 2048, I 768, 128 experts, top-8, router bias ~N(0, 0.5))
     through izb_moe_forward at T = 1, 64, 4096; rotating over 3 layers' weights (3.6 GB) so the
@@ -489,6 +543,7 @@ def run_ours(args):
             line["gemm_cases"] = measure_gemm_cases(device)
             line["moe_cases"] = measure_moe_cases(device)
             line["attention_cases"] = measure_attention_cases(device)
+            line["decode_token_cases"] = measure_decode_token_cases(device)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

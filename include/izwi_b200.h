@@ -318,6 +318,20 @@ int32_t izb_rope_pair(izb_ctx* ctx, izb_stream stream, void* q, void* k, const v
 int32_t izb_kv_append(izb_ctx* ctx, izb_stream stream, const void* k, const void* v, void* k_cache,
                       void* v_cache, int64_t batch, int32_t kv_heads, int32_t head_dim, int64_t pos,
                       int64_t kv_capacity, int64_t ld_k, int64_t ld_v);
+/* The three steps above in one launch, for the fused QKV output [batch, (heads + 2 kv_heads) *
+ * head_dim] of one decode token per sequence: q rows are RMS-normalised (q_norm_weight, may be NULL
+ * together with k_norm_weight), rotated and written to q_out [batch, heads, head_dim]; k rows
+ * likewise into position `pos` of the K cache; v rows are copied into the V cache.  fp32
+ * arithmetic with a single rounding (the separate calls round after the norm and after the
+ * rotation).  head_dim 64 or 128.  Replaces apply_qk_norm_pair + apply_rope_pair + the cache append
+ * of Qwen3Attention::forward (qwen3/core.rs:1465-1575, 1624-1732), which the reference fuses only on
+ * Metal (try_fused_qk_rms_norm, try_fused_rope_pair_bshd). */
+int32_t izb_qk_norm_rope_append(izb_ctx* ctx, izb_stream stream, const void* qkv, int64_t ld_qkv,
+                                const void* q_norm_weight, const void* k_norm_weight, float eps,
+                                const void* cos_half, const void* sin_half, void* q_out,
+                                int64_t ld_q_out, void* k_cache, void* v_cache, int64_t batch,
+                                int32_t heads, int32_t kv_heads, int32_t head_dim, int64_t pos,
+                                int64_t kv_capacity);
 /* One query token per sequence against a head-major KV cache: q [batch, heads, head_dim] (rows ld_q
  * apart), k_cache / v_cache [batch, kv_heads, kv_capacity, head_dim] bf16 contiguous of which the
  * first kv_len positions are valid, out [batch, heads, head_dim] (rows ld_out apart);

@@ -112,6 +112,9 @@ _SIGNATURES = {
                                   C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
     "izb_kv_append": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                   C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
+    "izb_qk_norm_rope_append": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_float,
+                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
+                                            C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
     "izb_decode_gqa_attention_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                                              C.c_int64]),
     "izb_decode_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -47,6 +47,61 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv
     }
 }
 
+// One warp per head row of the fused QKV output of one decode token per sequence:
+//   q rows: RMS-normalise with q_w (optional), rotate, write to q_out;
+//   k rows: the same with k_w, written into position `pos` of the head-major K cache;
+//   v rows: copied into the V cache.
+// fp32 arithmetic, one rounding (the unfused sequence rounds after the norm and again after the rotation).
+template <int D>
+__global__ void __launch_bounds__(256)
+    qk_norm_rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv, const __nv_bfloat16* __restrict__ q_w,
+                               const __nv_bfloat16* __restrict__ k_w, float eps, const __nv_bfloat16* __restrict__ cos_half,
+                               const __nv_bfloat16* __restrict__ sin_half, __nv_bfloat16* __restrict__ q_out, long long ld_q_out,
+                               __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, long long batch, int heads,
+                               int kv_heads, long long pos, long long cap) {
+    constexpr int E = D / 32;  // elements per lane; the rotation partner of element j is j +- D/2: lane ^ 16
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rows_per_tok = heads + 2 * kv_heads;
+    const long long rows = batch * rows_per_tok;
+    for (long long row = static_cast<long long>(blockIdx.x) * 8 + warp; row < rows; row += static_cast<long long>(gridDim.x) * 8) {
+        const long long b = row / rows_per_tok;
+        const int r = static_cast<int>(row - b * rows_per_tok);
+        const __nv_bfloat16* src = qkv + b * ld_qkv + static_cast<long long>(r) * D + lane * E;
+        float x[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) x[j] = __bfloat162float(src[j]);
+        __nv_bfloat16* dst;
+        if (r >= heads + kv_heads) {  // v: straight into the cache
+            dst = vc + ((b * kv_heads + (r - heads - kv_heads)) * cap + pos) * D + lane * E;
+        } else {
+            const bool is_q = r < heads;
+            const __nv_bfloat16* w = is_q ? q_w : k_w;
+            if (w) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < E; ++j) ss += x[j] * x[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                const float scale = rsqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+                for (int j = 0; j < E; ++j) x[j] = x[j] * scale * __bfloat162float(w[lane * E + j]);
+            }
+            // lanes 0..15 hold the first half (x1), lanes 16..31 the second (x2) of the same pair index
+            const int jh = (lane & 15) * E;
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                const float other = __shfl_xor_sync(0xFFFFFFFFu, x[j], 16);
+                const float c = __bfloat162float(cos_half[b * (D / 2) + jh + j]), s = __bfloat162float(sin_half[b * (D / 2) + jh + j]);
+                x[j] = lane < 16 ? x[j] * c - other * s : other * s + x[j] * c;
+            }
+            dst = is_q ? q_out + b * ld_q_out + static_cast<long long>(r) * D + lane * E
+                       : kc + ((b * kv_heads + (r - heads)) * cap + pos) * D + lane * E;
+        }
+#pragma unroll
+        for (int j = 0; j < E; ++j) dst[j] = __float2bfloat16_rn(x[j]);
+    }
+}
+
 struct AttShared {
     float m[ATT_MAX_G], l[ATT_MAX_G], alpha[ATT_MAX_G];
 };
@@ -319,6 +374,41 @@ int32_t izb_kv_append(izb_ctx* ctx, izb_stream stream, const void* k, const void
     kv_append_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(k_cache),
         static_cast<__nv_bfloat16*>(v_cache), batch, kv_heads, head_dim, pos, kv_capacity, ld_k, ld_v);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_qk_norm_rope_append(izb_ctx* ctx, izb_stream stream, const void* qkv, int64_t ld_qkv, const void* q_norm_weight,
+                                const void* k_norm_weight, float eps, const void* cos_half, const void* sin_half, void* q_out,
+                                int64_t ld_q_out, void* k_cache, void* v_cache, int64_t batch, int32_t heads, int32_t kv_heads,
+                                int32_t head_dim, int64_t pos, int64_t kv_capacity) {
+    if (!ctx || batch < 0 || heads <= 0 || kv_heads <= 0) return IZB_ERR_BAD_ARG;
+    if (batch == 0) return IZB_OK;
+    if (head_dim != 64 && head_dim != 128) return IZB_ERR_UNSUPPORTED;
+    if (!qkv || !cos_half || !sin_half || !q_out || !k_cache || !v_cache) return IZB_ERR_BAD_ARG;
+    if ((q_norm_weight == nullptr) != (k_norm_weight == nullptr) || !(eps >= 0.f)) return IZB_ERR_BAD_ARG;
+    if (pos < 0 || pos >= kv_capacity) return IZB_ERR_BAD_ARG;
+    if (ld_qkv < static_cast<int64_t>(heads + 2 * kv_heads) * head_dim || ld_q_out < static_cast<int64_t>(heads) * head_dim)
+        return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(qkv, 2) || !izb_aligned(q_out, 2) || !izb_aligned(k_cache, 2) || !izb_aligned(v_cache, 2)) return IZB_ERR_BAD_ARG;
+    const long long rows = batch * (heads + 2 * kv_heads), blocks = (rows + 7) / 8, cap = static_cast<long long>(ctx->sm_count) * 8;
+    const int grid = static_cast<int>(blocks < cap ? blocks : cap);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const auto* in = static_cast<const __nv_bfloat16*>(qkv);
+    const auto* qw = static_cast<const __nv_bfloat16*>(q_norm_weight);
+    const auto* kw = static_cast<const __nv_bfloat16*>(k_norm_weight);
+    const auto* cs = static_cast<const __nv_bfloat16*>(cos_half);
+    const auto* sn = static_cast<const __nv_bfloat16*>(sin_half);
+    auto* qo = static_cast<__nv_bfloat16*>(q_out);
+    auto* kc = static_cast<__nv_bfloat16*>(k_cache);
+    auto* vc = static_cast<__nv_bfloat16*>(v_cache);
+    if (head_dim == 128)
+        qk_norm_rope_append_kernel<128><<<grid, 256, 0, s>>>(in, ld_qkv, qw, kw, eps, cs, sn, qo, ld_q_out, kc, vc, batch, heads,
+                                                             kv_heads, pos, kv_capacity);
+    else
+        qk_norm_rope_append_kernel<64><<<grid, 256, 0, s>>>(in, ld_qkv, qw, kw, eps, cs, sn, qo, ld_q_out, kc, vc, batch, heads,
+                                                            kv_heads, pos, kv_capacity);
     IZB_CUDA_TRY(cudaGetLastError());
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;

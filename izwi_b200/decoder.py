@@ -49,8 +49,9 @@ class KvCache:
 
 
 class Qwen3DecoderLayer:
-    def __init__(self, w: Qwen3LayerWeights):
+    def __init__(self, w: Qwen3LayerWeights, fused_qk: bool = True):
         self.w = w
+        self.fused_qk = fused_qk and w.head_dim in (64, 128)
 
     def forward(self, attn_in: torch.Tensor, residual: torch.Tensor | None, cos_half: torch.Tensor,
                 sin_half: torch.Tensor, cache: KvCache, pos: int):
@@ -66,16 +67,20 @@ class Qwen3DecoderLayer:
         else:
             normed, x = ops.rms_norm(attn_in, w.input_layernorm, w.eps, residual=residual, return_sum=True)
         qkv = ops.linear(normed, w.qkv, w.fmt, n=qd + 2 * kd, k=w.hidden)
-        q = qkv[:, :qd].reshape(b, w.heads, w.head_dim)           # views of the fused output (narrow, core.rs:975-981)
-        k = qkv[:, qd:qd + kd].reshape(b, w.kv_heads, w.head_dim)
-        v = qkv[:, qd + kd:].reshape(b, w.kv_heads, w.head_dim)
-        if w.q_norm is not None:
-            q = ops.rms_norm(q, w.q_norm, w.eps)
-            k = ops.rms_norm(k, w.k_norm, w.eps)
+        if self.fused_qk:
+            # q/k norms, rotation and cache append in one launch, reading the fused QKV output in place
+            q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, w.eps, cos_half, sin_half, cache.k, cache.v, w.heads, pos)
         else:
-            q, k = q.contiguous(), k.contiguous()
-        ops.rope_pair_(q, k, cos_half, sin_half)
-        ops.kv_append_(k, v, cache.k, cache.v, pos)
+            q = qkv[:, :qd].reshape(b, w.heads, w.head_dim)       # views of the fused output (narrow, core.rs:975-981)
+            k = qkv[:, qd:qd + kd].reshape(b, w.kv_heads, w.head_dim)
+            v = qkv[:, qd + kd:].reshape(b, w.kv_heads, w.head_dim)
+            if w.q_norm is not None:
+                q = ops.rms_norm(q, w.q_norm, w.eps)
+                k = ops.rms_norm(k, w.k_norm, w.eps)
+            else:
+                q, k = q.contiguous(), k.contiguous()
+            ops.rope_pair_(q, k, cos_half, sin_half)
+            ops.kv_append_(k, v, cache.k, cache.v, pos)
         attn = ops.decode_gqa_attention(q, cache.k, cache.v, pos + 1)
         o = ops.linear(attn.reshape(b, qd), w.o, w.fmt, n=w.hidden, k=qd)
         normed2, x = ops.rms_norm(o, w.post_attention_layernorm, w.eps, residual=x, return_sum=True)
@@ -83,3 +88,34 @@ class Qwen3DecoderLayer:
         act = ops.silu_mul(gu[:, :w.intermediate], gu[:, w.intermediate:])
         mlp_out = ops.linear(act, w.down, w.fmt, n=w.hidden, k=w.intermediate)
         return mlp_out, x
+
+
+class Qwen3Decoder:
+    """Embedding, decoder layers, final norm, lm_head and greedy choice for one token per sequence:
+    the device side of `Qwen3Model::forward` + `argmax` for seq_len = 1
+    (qwen3/core.rs:2099-2125, qwen3/chat.rs:574-601)."""
+
+    def __init__(self, embed: torch.Tensor, layers: list, final_norm: torch.Tensor, lm_head: torch.Tensor, lm_head_fmt: str,
+                 rope_theta: float = 1e6):
+        self.embed, self.layers, self.final_norm = embed, layers, final_norm
+        self.lm_head, self.lm_head_fmt = lm_head, lm_head_fmt
+        w = layers[0].w
+        self.w = w
+        self.inv_freq = 1.0 / (rope_theta ** (torch.arange(0, w.head_dim, 2, device=embed.device, dtype=torch.float32)
+                                              / w.head_dim))
+
+    def rope_tables(self, pos: int, batch: int):
+        ang = (pos * self.inv_freq)[None, :].expand(batch, -1)
+        return ang.cos().to(torch.bfloat16).contiguous(), ang.sin().to(torch.bfloat16).contiguous()
+
+    def step(self, tokens: torch.Tensor, caches: list, pos: int, cos_half=None, sin_half=None) -> torch.Tensor:
+        """tokens [batch] int64 -> next tokens [batch] int32 (greedy)."""
+        if cos_half is None:
+            cos_half, sin_half = self.rope_tables(pos, tokens.shape[0])
+        out, stream = self.embed[tokens], None
+        for layer, cache in zip(self.layers, caches):
+            out, stream = layer.forward(out, stream, cos_half, sin_half, cache, pos)
+        hidden = ops.rms_norm(out, self.final_norm, self.w.eps, residual=stream)
+        vocab = self.embed.shape[0]
+        logits = ops.linear(hidden, self.lm_head, self.lm_head_fmt, n=vocab, k=self.w.hidden, out_dtype=torch.float32)
+        return ops.argmax_rows(logits)

@@ -193,6 +193,23 @@ def kv_append_(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache:
                                   k_cache.shape[2], k.stride(0), v.stride(0)), "izb_kv_append")
 
 
+def qk_norm_rope_append(qkv: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
+                        cos_half: torch.Tensor, sin_half: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        heads: int, pos: int) -> torch.Tensor:
+    """q/k head norms, rotation and cache append of one decode token per sequence in one launch;
+    qkv [batch, (heads + 2 kv_heads) * d] -> q [batch, heads, d]."""
+    b = qkv.shape[0]
+    kvh, cap, d = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (heads + 2 * kvh) * d
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and cos_half.is_contiguous() and sin_half.is_contiguous()
+    q = torch.empty(b, heads, d, device=qkv.device, dtype=torch.bfloat16)
+    ctx = Context.get(qkv.device.index)
+    L.check(L.lib().izb_qk_norm_rope_append(ctx.handle, _stream(), _ptr(qkv), qkv.stride(0), _ptr(q_norm), _ptr(k_norm),
+                                            float(eps), _ptr(cos_half), _ptr(sin_half), _ptr(q), q.stride(0), _ptr(k_cache),
+                                            _ptr(v_cache), b, heads, kvh, d, pos, cap), "izb_qk_norm_rope_append")
+    return q
+
+
 def decode_gqa_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: int,
                          scale: float | None = None, out: torch.Tensor | None = None,
                          workspace: torch.Tensor | None = None) -> torch.Tensor:

@@ -69,3 +69,48 @@ def test_decode_gqa_attention_peaked_scores_and_arguments(cuda):
     with pytest.raises(IzbError) as e:
         ops.decode_gqa_attention(q96, kv96, kv96, 16)
     assert e.value.status == -2
+
+
+@pytest.mark.parametrize("b,h,kvh,d,with_norm", [(1, 16, 8, 128, True), (3, 8, 4, 64, True), (2, 32, 8, 128, False)])
+def test_fused_qk_norm_rope_append(cuda, b, h, kvh, d, with_norm):
+    """One launch against the composition norm -> rotation -> append of the oracle.  The fused kernel
+    rounds once where the composition rounds after the norm and after the rotation: at most two bf16
+    steps apart, equal for most elements."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(b * 10 + d)
+    qkv = bf16_np(rng.normal(0, 1, (b, (h + 2 * kvh) * d)))
+    qn, kn = bf16_np(rng.normal(1, 0.1, d)), bf16_np(rng.normal(1, 0.1, d))
+    ang = rng.uniform(0, 6.28, (b, d // 2))
+    c, s = bf16_np(np.cos(ang)), bf16_np(np.sin(ang))
+    cap, pos = 9, 5
+    kc = torch.zeros(b, kvh, cap, d, device=cuda, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q = ops.qk_norm_rope_append(_dev(qkv, cuda), _dev(qn, cuda) if with_norm else None, _dev(kn, cuda) if with_norm else None,
+                                1e-6, _dev(c, cuda), _dev(s, cuda), kc, vc, h, pos)
+    ops.Context.get(0).check()
+    q_in = qkv[:, :h * d].reshape(b, h, d)
+    k_in = qkv[:, h * d:(h + kvh) * d].reshape(b, kvh, d)
+    v_in = qkv[:, (h + kvh) * d:].reshape(b, kvh, d)
+    def single_rounding(x, w):
+        """The fused arithmetic restated: norm and rotation in fp32, one rounding at the end."""
+        y = x.astype(np.float32)
+        if with_norm:
+            ms = (y.astype(np.float64) ** 2).mean(axis=-1, keepdims=True)
+            y = y * (1.0 / np.sqrt(ms + 1e-6)).astype(np.float32) * w
+        half = d // 2
+        cc, ss = c[:, None, :], s[:, None, :]
+        return y, o.bf16_round(np.concatenate([y[..., :half] * cc - y[..., half:] * ss,
+                                               y[..., :half] * ss + y[..., half:] * cc], axis=-1))
+
+    for got, x, w in ((to_np(q), q_in, qn), (to_np(kc[:, :, pos]), k_in, kn)):
+        y, want1 = single_rounding(x, w)
+        mag = np.abs(y).max(axis=-1, keepdims=True)                     # the rotation can cancel: bound by the inputs
+        assert (np.abs(got - want1) <= mag * 2.0 ** -8).all()
+        assert (got == want1).mean() > 0.97
+        # against the reference's sequence (norm rounded to bf16, then rotated and rounded again)
+        xn = o.rms_norm(x, w, 1e-6)[0] if with_norm else x
+        want2 = o.rope_pair(xn, c, s)
+        assert (np.abs(got - want2) <= mag * 2.0 ** -6).all()
+    assert np.array_equal(to_np(vc[:, :, pos]), v_in)
+    untouched = torch.cat([kc[:, :, :pos], kc[:, :, pos + 1:]], dim=2)
+    assert float(untouched.abs().max()) == 0.0

@@ -50,8 +50,9 @@ def _oracle_layer(L, x, kc, vc, pos, cos, sin):
     return o.bf16_round(x1 + lin(act, L["down"][1]))
 
 
+@pytest.mark.parametrize("fused_qk", [True, False])
 @pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
-def test_three_tokens_two_layers(cuda, fmt):
+def test_three_tokens_two_layers(cuda, fmt, fused_qk):
     from izwi_b200 import decoder, ops
     rng = np.random.default_rng(21)
     layers_np = [_layer_np(rng, fmt), _layer_np(rng, fmt)]
@@ -59,7 +60,8 @@ def test_three_tokens_two_layers(cuda, fmt):
     layers = [decoder.Qwen3DecoderLayer(decoder.Qwen3LayerWeights(
         fmt, HID, HEADS, KVH, D, INTER, dev(L["ln1"]), dev(L["ln2"]), dev(L["qn"]), dev(L["kn"]),
         torch.from_numpy(L["qkv"][0]).to(cuda), torch.from_numpy(L["o"][0]).to(cuda),
-        torch.from_numpy(L["gu"][0]).to(cuda), torch.from_numpy(L["down"][0]).to(cuda), EPS)) for L in layers_np]
+        torch.from_numpy(L["gu"][0]).to(cuda), torch.from_numpy(L["down"][0]).to(cuda), EPS), fused_qk=fused_qk)
+        for L in layers_np]
     b, cap = 2, 16
     caches = [decoder.KvCache(b, KVH, cap, D, cuda) for _ in layers]
     kcs = [np.zeros((b, KVH, cap, D), dtype=np.float32) for _ in layers]
