@@ -58,6 +58,11 @@ int32_t izb_ctx_destroy(izb_ctx* ctx);
 /* Synchronises `stream`, then returns IZB_ERR_TIMEOUT if any kernel launched
  * through this context recorded a wait that gave up (and clears the record). */
 int32_t izb_ctx_check(izb_ctx* ctx, izb_stream stream);
+/* Launches a one-warp kernel that waits on a barrier nothing completes, through the bounded wait all
+ * pipeline kernels share: after the limit (about a second) it records the time-out and returns, so
+ * the next izb_ctx_check reports IZB_ERR_TIMEOUT once and the context stays usable.  Lets a host
+ * test its handling of that status without any kernel misbehaving.  No counterpart in the reference. */
+int32_t izb_ctx_selftest_wait_timeout(izb_ctx* ctx, izb_stream stream);
 /* Number of kernels this context has launched so far (diagnostic counter). */
 int64_t izb_ctx_launch_count(const izb_ctx* ctx);
 

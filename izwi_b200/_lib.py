@@ -51,6 +51,7 @@ _SIGNATURES = {
     "izb_ctx_destroy": (C.c_int32, [C.c_void_p]),
     "izb_ctx_check": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "izb_ctx_launch_count": (C.c_int64, [C.c_void_p]),
+    "izb_ctx_selftest_wait_timeout": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "izb_quantized_storage_bytes": (C.c_int32, [C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_size_t)]),
     "izb_dequantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "izb_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int64, C.c_int64]),

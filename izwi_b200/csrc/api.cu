@@ -93,6 +93,21 @@ __global__ void dequant_q6_k_kernel(const uint8_t* __restrict__ raw, OutT* __res
     }
 }
 
+// Waits on a barrier that nothing ever completes, through the same bounded wait every pipeline
+// kernel uses: it gives up after the limit, records it in the status word and returns normally.
+__global__ void selftest_wait_kernel(int* status) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const bool done = mbar_wait_bounded(smem_u32(&bar), 0, &abort_flag);
+    if (!done && threadIdx.x == 0) atomicExch(status, 1);
+}
+
 // ---------------------------------------------------------------------------
 // out = silu(gate) * up
 // ---------------------------------------------------------------------------
@@ -207,6 +222,14 @@ int32_t izb_ctx_check(izb_ctx* ctx, izb_stream stream) {
 }
 
 int64_t izb_ctx_launch_count(const izb_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
+
+int32_t izb_ctx_selftest_wait_timeout(izb_ctx* ctx, izb_stream stream) {
+    if (!ctx) return IZB_ERR_BAD_ARG;
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctx->d_status + 7);
+    IZB_CUDA_TRY(cudaGetLastError());
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
 
 int32_t izb_quantized_storage_bytes(int32_t wfmt, int64_t rows, int64_t cols, size_t* out_bytes) {
     if (!out_bytes || rows < 0 || cols < 0) return IZB_ERR_BAD_ARG;
