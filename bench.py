@@ -376,7 +376,11 @@ def measure_decode_token_cases(device):
     model = decoder.Qwen3Decoder(embed, layers, ones(hid), wl.make_q8_0_weight(vocab, hid, gen), "q8_0")
     weight_bytes = sum(w.numel() for l in layers for w in (l.w.qkv, l.w.o, l.w.gate_up, l.w.down)) + model.lm_head.numel()
     out = []
-    for ctx_len in (512, 4096):
+    for ctx_len, fused in ((512, True), (4096, True), (512, False)):
+        # fused: norms, SiLU-multiply and residual adds ride inside the one-token projections
+        for l in layers:
+            l.fused_linear = fused
+            l.fusion_max_tokens = ops.linear_fusion_max_tokens("q8_0") if fused else 0
         caches = [decoder.KvCache(1, shape.kv_heads, ctx_len + 8, shape.head_dim, device) for _ in layers]
         for c in caches:
             c.k.normal_(generator=gen)
@@ -396,7 +400,7 @@ def measure_decode_token_cases(device):
         kv_bytes = shape.layers * 2 * shape.kv_heads * (ctx_len + 1) * shape.head_dim * 2
         gbs = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
         out.append({"workload": f"qwen3-0.6b-q8_0-greedy-token-ctx{ctx_len}", "ms_per_token": round(ms, 4),
-                    "tokens_per_s": round(1e3 / ms, 1), "kernels_per_token": int(launches),
+                    "tokens_per_s": round(1e3 / ms, 1), "kernels_per_token": int(launches), "fused_projections": fused,
                     "weight_and_kv_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak_bw, 4),
                     "next_token": int(nxt[0])})
         del caches, graph

@@ -88,6 +88,16 @@ typedef enum izb_epilogue {
                            `Qwen3Mlp::forward` gate/up + silu-mul in one pass (qwen3/core.rs:1787-1795) */
 } izb_epilogue;
 
+/* Function of the activations fused in front of a linear layer (decode step, one or two tokens).
+ * Both skip the bf16 rounding of the intermediate the separate launches would store. */
+typedef enum izb_prologue {
+    IZB_PRO_NONE = 0,
+    IZB_PRO_RMSNORM = 1,  /* y = W (x * rsqrt(mean(x^2) + eps) * norm_weight): the RmsNorm in front of the
+                             QKV and gate/up projections (qwen3/core.rs:1868, 1874) */
+    IZB_PRO_SILU_MUL = 2  /* x is [M, 2K] = [gate | up]; y = W (silu(gate) * up): the product in front of
+                             `down_proj` (qwen3/core.rs:1787-1795) */
+} izb_prologue;
+
 /* One linear layer.  Replaces `impl Module for Qwen3Projection::forward`
  * (qwen3/core.rs:791-832): Dense -> `Linear::forward` (:794), Quantized ->
  * `QMatMul::forward` (:812) with the dtype casts around it folded away
@@ -104,6 +114,14 @@ typedef struct izb_linear_args {
     void* workspace;   /* NULL unless izb_linear_workspace_bytes() > 0 */
     size_t workspace_bytes;
     int32_t epilogue;  /* izb_epilogue fused after the bias add */
+    int32_t prologue;  /* izb_prologue applied to x on its way into the product */
+    /* Decode-step fusions: only the one- and two-token block-format kernel takes them (see
+     * izb_linear_fusion_max_tokens); any other route answers IZB_ERR_UNSUPPORTED and the caller
+     * runs izb_rms_norm / izb_silu_mul / the add as launches of their own. */
+    const void* norm_weight; /* IZB_PRO_RMSNORM: bf16 [K], 16-byte aligned */
+    const void* residual;    /* bf16 [M, ld_residual] added to the output after the bias; NULL = none */
+    int64_t ld_residual;
+    float norm_eps;
     int32_t reserved_;
 } izb_linear_args;
 
@@ -119,6 +137,9 @@ typedef struct izb_linear_args {
  * registers; up to 64 tokens dequantise to bf16 in shared memory for tcgen05.  All accumulate in fp32. */
 size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K);
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args);
+/* Largest M for which izb_linear / izb_linear_batch accept `prologue`, `residual` for weights in
+ * `wfmt` (0: never). */
+int32_t izb_linear_fusion_max_tokens(int32_t wfmt);
 
 /* Thin typed forms of izb_linear (y is bf16, contiguous strides). */
 int32_t izb_linear_bf16(izb_ctx* ctx, izb_stream stream, const void* x, const void* w,

@@ -30,7 +30,9 @@ class LinearArgs(C.Structure):
         ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
         ("ldx", C.c_int64), ("ldy", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("epilogue", C.c_int32), ("reserved_", C.c_int32),
+        ("epilogue", C.c_int32), ("prologue", C.c_int32),
+        ("norm_weight", C.c_void_p), ("residual", C.c_void_p), ("ld_residual", C.c_int64),
+        ("norm_eps", C.c_float), ("reserved_", C.c_int32),
     ]
 
 
@@ -56,6 +58,7 @@ _SIGNATURES = {
     "izb_dequantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "izb_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
     "izb_linear": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(LinearArgs)]),
+    "izb_linear_fusion_max_tokens": (C.c_int32, [C.c_int32]),
     "izb_linear_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_int64, C.c_int64, C.c_int64]),
     "izb_linear_q8_0": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

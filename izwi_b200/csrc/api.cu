@@ -316,13 +316,23 @@ size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K)
     return 0;
 }
 
+int32_t izb_linear_fusion_max_tokens(int32_t wfmt) {
+    if (wfmt != IZB_W_Q8_0 && wfmt != IZB_W_Q4_K) return 0;
+    return skinny_gemv_max_tokens();
+}
+
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args) {
     if (!ctx || !args) return IZB_ERR_BAD_ARG;
     if (args->M < 0 || args->N < 0 || args->K < 0) return IZB_ERR_BAD_ARG;
     if (args->epilogue < IZB_EPI_NONE || args->epilogue > IZB_EPI_SWIGLU) return IZB_ERR_BAD_ARG;
+    if (args->prologue < IZB_PRO_NONE || args->prologue > IZB_PRO_SILU_MUL) return IZB_ERR_BAD_ARG;
     if (args->M == 0 || args->N == 0) return IZB_OK;
     if (args->K == 0) return IZB_ERR_UNSUPPORTED;
     if (args->M > INT32_MAX || args->N > INT32_MAX || args->K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
+    if (args->prologue != IZB_PRO_NONE || args->residual) {
+        // only the integer-dot-product kernel fuses these; every other route declines
+        if (args->M > izb_linear_fusion_max_tokens(args->wfmt) || args->epilogue != IZB_EPI_NONE) return IZB_ERR_UNSUPPORTED;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (args->wfmt == IZB_W_Q6_K) {
         // no in-place kernel for 210-byte super-blocks: multiply the bf16 copy in the workspace

@@ -521,6 +521,8 @@ BoxGeom box_geom(int fmt, int K, bool tc = false) {
 
 }  // namespace
 
+int skinny_gemv_max_tokens() { return std::max(0, std::min(env_int("IZB_SKINNY_GEMV_MAX_M", 2), 4)); }
+
 int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, SkinnyPlanHeader* hdr,
                       SkinnyProblem* out) {
     if (!ctx || !probs || !hdr || !out || n <= 0) return IZB_ERR_BAD_ARG;
@@ -530,6 +532,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const int kalign = fmt == IZB_W_BF16 ? 64 : 256;
 
     int64_t max_m = 0;
+    bool any_extras = false;
     for (int i = 0; i < n; ++i) {
         const izb_linear_args& a = probs[i];
         if (a.wfmt != fmt || a.y_dtype != y_dtype) return IZB_ERR_BAD_ARG;
@@ -543,6 +546,11 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         if (!izb_aligned(a.y, y_dtype == IZB_F32 ? 4 : 2)) return IZB_ERR_BAD_ARG;
         if (a.bias && !izb_aligned(a.bias, 2)) return IZB_ERR_BAD_ARG;
         max_m = std::max<int64_t>(max_m, a.M);
+        if (a.prologue < IZB_PRO_NONE || a.prologue > IZB_PRO_SILU_MUL) return IZB_ERR_BAD_ARG;
+        if (a.prologue == IZB_PRO_RMSNORM && (!a.norm_weight || !izb_aligned(a.norm_weight, 16))) return IZB_ERR_BAD_ARG;
+        if (a.prologue == IZB_PRO_SILU_MUL && a.ldx < 2 * a.K) return IZB_ERR_BAD_ARG;
+        if (a.residual && (a.ld_residual < a.N || a.ld_residual > INT32_MAX || !izb_aligned(a.residual, 2))) return IZB_ERR_BAD_ARG;
+        any_extras = any_extras || a.prologue != IZB_PRO_NONE || a.residual != nullptr;
     }
     const int nt = max_m <= 8 ? 1 : max_m <= 16 ? 2 : max_m <= 32 ? 4 : 8;
     const int mp = nt * 8;
@@ -551,8 +559,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     const bool tc = fmt != IZB_W_BF16 && nt >= env_int("IZB_SKINNY_TC_MIN_NT", fmt == IZB_W_Q8_0 ? 8 : 4);
     // one to four tokens over block-quantised weights: integer dot products against activations in
     // 16-bit block fixed point (skinny_gemv.cu); gemv = tokens the kernel is instantiated for
-    const int gemv_max = env_int("IZB_SKINNY_GEMV_MAX_M", 2);
-    const int gemv = (fmt != IZB_W_BF16 && max_m <= std::min(gemv_max, 4)) ? (max_m <= 1 ? 1 : max_m <= 2 ? 2 : 4) : 0;
+    const int gemv = (fmt != IZB_W_BF16 && max_m <= skinny_gemv_max_tokens()) ? (max_m <= 1 ? 1 : max_m <= 2 ? 2 : 4) : 0;
+    if (any_extras && !gemv) return IZB_ERR_UNSUPPORTED;  // only that kernel fuses a prologue or a residual
     const bool one_sb = tc || gemv != 0;  // one Q4_K super-block per box row
 
     // measured best residency: three CTAs per SM for Q8_0 (most ALU work per byte), two otherwise
@@ -644,7 +652,16 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         q.x_off = (nb * q.w_box_bytes + 1023) / 1024 * 1024;
         // gemv: only the tokens the kernel is instantiated for are copied, unswizzled (no tensor-core read)
         const int x_rows = gemv ? gemv : mp;
-        const int x_bytes = nb * (bg.kbox / 64) * x_rows * 128;
+        const bool silu_mul = a.prologue == IZB_PRO_SILU_MUL;  // gate and up chunks travel side by side
+        const int x_half = nb * (bg.kbox / 64) * x_rows * 128;
+        const int x_bytes = silu_mul ? 2 * x_half : x_half;
+        q.norm_w = static_cast<const __nv_bfloat16*>(a.prologue == IZB_PRO_RMSNORM ? a.norm_weight : nullptr);
+        q.residual = static_cast<const __nv_bfloat16*>(a.residual);
+        q.ld_res = static_cast<int>(a.ld_residual);
+        q.prologue = a.prologue;
+        q.eps = a.norm_eps;
+        q.up_chunk0 = K / 64;
+        q.x_half = x_half;
         q.stage_tx = nb * q.w_box_bytes + x_bytes;
         // tc: weights and activations travel in separate rings; stage_bytes describes the weight ring
         // gemv: converted activations (576 bytes per token and box) live beside the ring, one slot per stage
@@ -673,7 +690,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         if (rc != IZB_OK) return rc;
         // activations: [k/64][token][64 bf16]; rows past M read as zero
         {
-            const uint64_t dims[3] = {64, static_cast<uint64_t>(M), static_cast<uint64_t>(K / 64)};
+            const uint64_t dims[3] = {64, static_cast<uint64_t>(M), static_cast<uint64_t>((silu_mul ? 2 * K : K) / 64)};
             const uint64_t strides[2] = {static_cast<uint64_t>(a.ldx) * 2, 128};
             const uint32_t box[3] = {64, static_cast<uint32_t>(x_rows), static_cast<uint32_t>(nb * (bg.kbox / 64))};
             rc = tma_encode(&q.tmap_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.x, dims, strides, box,
@@ -735,6 +752,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     hdr->x_stages = x_stages;
     hdr->gemv = gemv;
     hdr->xq_stage_bytes = xq_stage;
+    hdr->extras = any_extras ? 1 : 0;
     hdr->smem_bytes = lite_bytes + red_bytes + n_stages * stage_bytes + x_stages * 4 * mp * 128 + 1024;  // slack to align the ring to 1024 bytes
     hdr->grid = std::min(tile_cursor, max_grid);
     hdr->y_dtype = y_dtype;

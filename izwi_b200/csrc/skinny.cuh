@@ -37,8 +37,17 @@ struct alignas(64) SkinnyProblem {
     int w_box_bytes;  // TILE_ROWS * w_row_bytes
     int x_off;        // byte offset of the activation region inside a stage
     int stage_tx;     // bytes one full stage delivers (both boxes)
+    // decode-step fusions (integer-dot-product kernel only)
+    const __nv_bfloat16* norm_w;    // RmsNorm weight [K], or null
+    const __nv_bfloat16* residual;  // [M, ld_res] added to the output, or null
+    int ld_res;
+    int prologue;    // izb_prologue
+    float eps;
+    int up_chunk0;   // SILU_MUL: 64-k chunk index where the `up` half of the activation rows starts
+    int x_half;      // SILU_MUL: byte offset of the `up` chunks inside the stage's activation region
+    int pad_[3];
 };
-static_assert(sizeof(SkinnyProblem) == 320, "SkinnyProblem layout");
+static_assert(sizeof(SkinnyProblem) == 384, "SkinnyProblem layout");
 
 struct alignas(64) SkinnyPlanHeader {
     uint32_t magic;
@@ -51,7 +60,8 @@ struct alignas(64) SkinnyPlanHeader {
     int x_stages;    // tc: depth of the separate activation ring (n_stages / stage_bytes describe the raw weight ring)
     int gemv;        // 1, 2 or 4: the integer-dot-product kernel for that many tokens (block-quantised weights); 0: off
     int xq_stage_bytes;  // gemv: bytes of converted activations per stage (red_bytes holds all stages)
-    int pad_[14];
+    int extras;          // gemv: some problem carries a prologue or a residual
+    int pad_[13];
 };
 static_assert(sizeof(SkinnyPlanHeader) == 128, "SkinnyPlanHeader layout");
 
@@ -64,7 +74,8 @@ struct alignas(16) ProbLite {
     const __nv_bfloat16* bias;
     int N, M, ldy, tile_start;
     int n_chunks, nb, kbox, w_row_bytes;
-    int w_box_bytes, x_off, stage_tx, pad_;
+    int w_box_bytes, x_off, stage_tx;
+    int extras;  // the problem carries a prologue or a residual: the roles read those fields from its descriptor
 };
 static_assert(sizeof(ProbLite) == 64, "ProbLite layout");
 constexpr int SK_LITE_MAX = 160;  // problems cached; beyond that the descriptor is read from global memory
@@ -74,7 +85,8 @@ __device__ __forceinline__ ProbLite lite_from(const SkinnyProblem& q) {
     l.y = q.y; l.bias = q.bias;
     l.N = q.N; l.M = q.M; l.ldy = q.ldy; l.tile_start = q.tile_start;
     l.n_chunks = q.n_chunks; l.nb = q.nb; l.kbox = q.kbox; l.w_row_bytes = q.w_row_bytes;
-    l.w_box_bytes = q.w_box_bytes; l.x_off = q.x_off; l.stage_tx = q.stage_tx; l.pad_ = 0;
+    l.w_box_bytes = q.w_box_bytes; l.x_off = q.x_off; l.stage_tx = q.stage_tx;
+    l.extras = (q.prologue != 0 || q.residual != nullptr) ? 1 : 0;
     return l;
 }
 
@@ -141,6 +153,7 @@ int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr
 int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
                      const SkinnyProblem* single);
 // skinny_gemv.cu
+int skinny_gemv_max_tokens();  // widest token group the planner hands to the integer-dot-product kernel
 int skinny_gemv_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
                        const SkinnyProblem* single);
 

@@ -30,12 +30,14 @@ constexpr int GV_TILE_ROWS = 64;
 constexpr int GV_XQ_BYTES = 256 + 256 + 32 + 32;
 constexpr int GV_XQ_XL = 256, GV_XQ_XS = 512, GV_XQ_SX = 544;
 
-template <int MT>
+template <int MT, bool EX>
 struct GvShared {
     unsigned long long full[SK_MAX_STAGES];    // copies landed
     unsigned long long xready[SK_MAX_STAGES];  // activations of the stage converted
     unsigned long long empty[SK_MAX_STAGES];   // consumers done with the stage
     float red[2][GV_TILE_ROWS * MT];           // partial sums of the second k-half, double-buffered by tile parity
+    // fused RmsNorm: 1 / rms of every token, left by the converter in the slot of the tile's last stage
+    float rs[EX ? SK_MAX_STAGES : 1][MT];
     int abort_flag;
 };
 
@@ -77,6 +79,25 @@ __device__ __forceinline__ float small_int_to_f32(int v) {
     return __int_as_float(0x4B400000 + v) - 12582912.0f;
 }
 
+// Eight fixed-point values of one lane -> the two byte planes, plus (one lane in four) the block's
+// scale and scaled sum.
+__device__ __forceinline__ void gv_store_unit(const int (&X)[8], float xs, uint32_t dst, int lane) {
+    int isum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) isum += X[i];
+    isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 1);
+    isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 2);
+    // bytes 0 (low) and 1 (high) of four values each into one word per plane
+    const uint32_t u0 = prmt(X[0], X[1], 0x5140), v0 = prmt(X[2], X[3], 0x5140);
+    const uint32_t u1 = prmt(X[4], X[5], 0x5140), v1 = prmt(X[6], X[7], 0x5140);
+    sts64v(dst + static_cast<uint32_t>(8 * lane), prmt(u0, v0, 0x7632), prmt(u1, v1, 0x7632));
+    sts64v(dst + static_cast<uint32_t>(GV_XQ_XL + 8 * lane), prmt(u0, v0, 0x5410), prmt(u1, v1, 0x5410));
+    if ((lane & 3) == 0) {
+        sts32f(dst + static_cast<uint32_t>(GV_XQ_XS + lane), xs);  // block lane/4: 4 bytes each
+        sts32f(dst + static_cast<uint32_t>(GV_XQ_SX + lane), xs * static_cast<float>(isum));
+    }
+}
+
 // One lane's share of the conversion: 8 consecutive activations (one 16-byte unit) of one token;
 // the four lanes of a 32-value block agree on the block exponent by shuffle.
 __device__ __forceinline__ void gv_convert_unit(const uint4 v, uint32_t dst, int lane) {
@@ -96,20 +117,24 @@ __device__ __forceinline__ void gv_convert_unit(const uint4 v, uint32_t dst, int
         X[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * sf);
         X[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * sf);
     }
-    int isum = 0;
+    gv_store_unit(X, xs, dst, lane);
+}
+
+// The same for eight fp32 values (activations that went through a fused prologue): fp32 mantissas
+// can round up to 2^15, which the signed high byte cannot hold, so the top is clamped to 32767.
+__device__ __forceinline__ void gv_convert_unit_f32(const float (&v)[8], uint32_t dst, int lane) {
+    uint32_t amax = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) isum += X[i];
-    isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 1);
-    isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 2);
-    // bytes 0 (low) and 1 (high) of four values each into one word per plane
-    const uint32_t u0 = prmt(X[0], X[1], 0x5140), v0 = prmt(X[2], X[3], 0x5140);
-    const uint32_t u1 = prmt(X[4], X[5], 0x5140), v1 = prmt(X[6], X[7], 0x5140);
-    sts64v(dst + static_cast<uint32_t>(8 * lane), prmt(u0, v0, 0x7632), prmt(u1, v1, 0x7632));
-    sts64v(dst + static_cast<uint32_t>(GV_XQ_XL + 8 * lane), prmt(u0, v0, 0x5410), prmt(u1, v1, 0x5410));
-    if ((lane & 3) == 0) {
-        sts32f(dst + static_cast<uint32_t>(GV_XQ_XS + lane), xs);  // block lane/4: 4 bytes each
-        sts32f(dst + static_cast<uint32_t>(GV_XQ_SX + lane), xs * static_cast<float>(isum));
-    }
+    for (int i = 0; i < 8; ++i) amax = max(amax, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const uint32_t eb = amax >> 23;
+    const float sf = (eb >= 16u && eb < 255u) ? __uint_as_float((268u - eb) << 23) : 0.f;
+    const float xs = eb == 255u ? __uint_as_float(0x7FC00000u) : eb >= 16u ? __uint_as_float((eb - 14u) << 23) : 0.f;
+    int X[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) X[i] = min(__float2int_rn(v[i] * sf), 32767);
+    gv_store_unit(X, xs, dst, lane);
 }
 
 // Q8_0: blocks 2P and 2P+1 (P = 0..3: pair of the 256-k box) of one row against MT tokens.
@@ -216,13 +241,15 @@ __device__ __forceinline__ void gv_half_q4_k(float (&acc)[MT], uint32_t wrow, ui
     }
 }
 
-template <int FMT, int MT>
+// EX: some problem of the launch carries a fused prologue (RmsNorm, silu(gate) * up) or a residual;
+// the plain instantiation compiles none of that.
+template <int FMT, int MT, bool EX>
 __global__ void __launch_bounds__(GV_THREADS)
     skinny_gemv_kernel(const SkinnyProblem* __restrict__ probs, const __grid_constant__ SkinnyProblem single, int n_probs,
                        int total_tiles, int n_stages, int stage_bytes, int xq_stage_bytes, int xq_bytes, int lite_bytes,
                        int y_dtype, int* status) {
     extern __shared__ __align__(1024) uint8_t dyn_smem[];
-    __shared__ GvShared<MT> sh;
+    __shared__ GvShared<MT, EX> sh;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const SkinnyProblem* plist = probs ? probs : &single;
@@ -265,6 +292,11 @@ __global__ void __launch_bounds__(GV_THREADS)
             const ProbLite L = p < n_cached ? lite[p] : lite_from(*P);
             const int row0 = (tile - L.tile_start) * GV_TILE_ROWS;
             const int xchunks = L.nb * 4;
+            int up_chunk0 = 0, x_half = 0;
+            if (EX && L.extras && P->prologue == IZB_PRO_SILU_MUL) {
+                up_chunk0 = P->up_chunk0;
+                x_half = P->x_half;
+            }
             for (int c = 0; c < L.n_chunks; ++c) {
                 if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
                     ok = false;
@@ -275,6 +307,8 @@ __global__ void __launch_bounds__(GV_THREADS)
                 mbar_expect_tx(fbar, static_cast<uint32_t>(L.stage_tx));
                 tma_load_3d(sbase, &P->tmap_w, 0, row0, c * L.nb, fbar);
                 tma_load_3d(sbase + static_cast<uint32_t>(L.x_off), &P->tmap_x, 0, 0, c * xchunks, fbar);
+                if (EX && up_chunk0)  // silu(gate) * up: the matching chunks of the second half of the rows
+                    tma_load_3d(sbase + static_cast<uint32_t>(L.x_off + x_half), &P->tmap_x, 0, 0, up_chunk0 + c * xchunks, fbar);
                 ++issued;
                 if (++stage == n_stages) {
                     stage = 0;
@@ -307,6 +341,20 @@ __global__ void __launch_bounds__(GV_THREADS)
             const int p = find_problem(lite, n_cached, plist, n_probs, tile);
             const ProbLite L = p < n_cached ? lite[p] : lite_from(plist[p]);
             const int M = min(L.M, MT);
+            int pro = IZB_PRO_NONE, x_half = 0, K = 1;
+            const __nv_bfloat16* norm_w = nullptr;
+            float eps = 0.f;
+            float ss[MT];  // fused RmsNorm: this lane's share of every token's sum of squares over the tile's k
+#pragma unroll
+            for (int m = 0; m < MT; ++m) ss[m] = 0.f;
+            if (EX && L.extras) {
+                const SkinnyProblem* P = plist + p;
+                pro = P->prologue;
+                x_half = P->x_half;
+                norm_w = P->norm_w;
+                eps = P->eps;
+                K = P->K;
+            }
             for (int c = 0; c < L.n_chunks; ++c) {
                 if (!mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) {
                     ok = false;
@@ -314,11 +362,52 @@ __global__ void __launch_bounds__(GV_THREADS)
                 }
                 const uint32_t sbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
                 for (int b = 0; b < L.nb; ++b) {
-                    for (int m = 0; m < M; ++m) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        if (m >= M) break;
                         // copied activations: [64-k chunk][token][128 bytes]; lane = chunk lane/8, 16-byte unit lane%8
-                        const uint4 v = lds128(sbase + static_cast<uint32_t>(L.x_off) +
-                                               static_cast<uint32_t>(((b * 4 + (lane >> 3)) * MT + m) * 128 + (lane & 7) * 16));
-                        gv_convert_unit(v, xq0 + static_cast<uint32_t>(stage * xq_stage_bytes + (b * MT + m) * GV_XQ_BYTES), lane);
+                        const uint32_t xaddr = sbase + static_cast<uint32_t>(L.x_off) +
+                                               static_cast<uint32_t>(((b * 4 + (lane >> 3)) * MT + m) * 128 + (lane & 7) * 16);
+                        const uint32_t dst = xq0 + static_cast<uint32_t>(stage * xq_stage_bytes + (b * MT + m) * GV_XQ_BYTES);
+                        const uint4 v = lds128(xaddr);
+                        if (!EX || pro == IZB_PRO_NONE) {
+                            gv_convert_unit(v, dst, lane);
+                        } else {
+                            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                f[2 * i] = __uint_as_float(w[i] << 16);
+                                f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                            }
+                            uint4 o;  // the other factor of every value: norm weights, or the `up` half of the row
+                            if (pro == IZB_PRO_RMSNORM) {
+                                const int k = (c * L.nb + b) * 256 + (lane >> 3) * 64 + (lane & 7) * 8;
+                                o = __ldg(reinterpret_cast<const uint4*>(norm_w + k));
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) ss[m] = fmaf(f[i], f[i], ss[m]);
+                            } else {
+                                o = lds128(xaddr + static_cast<uint32_t>(x_half));
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) f[i] = f[i] / (1.0f + __expf(-f[i]));
+                            }
+                            const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                f[2 * i] *= __uint_as_float(ow[i] << 16);
+                                f[2 * i + 1] *= __uint_as_float(ow[i] & 0xFFFF0000u);
+                            }
+                            gv_convert_unit_f32(f, dst, lane);
+                        }
+                    }
+                }
+                if (EX && c == L.n_chunks - 1) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        float t = ss[m];
+#pragma unroll
+                        for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, d);
+                        if (lane == 0) sh.rs[stage][m] = pro == IZB_PRO_RMSNORM ? rsqrtf(t / static_cast<float>(K) + eps) : 1.0f;
                     }
                 }
                 __syncwarp();
@@ -344,9 +433,18 @@ __global__ void __launch_bounds__(GV_THREADS)
         const ProbLite L = p < n_cached ? lite[p] : lite_from(plist[p]);
         const int row0 = (tile - L.tile_start) * GV_TILE_ROWS;
 
-        float acc[MT];
+        float acc[MT], rsv[MT];
 #pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+        for (int m = 0; m < MT; ++m) {
+            acc[m] = 0.f;
+            rsv[m] = 1.0f;
+        }
+        const __nv_bfloat16* residual = nullptr;
+        int ld_res = 0;
+        if (EX && L.extras) {
+            residual = plist[p].residual;
+            ld_res = plist[p].ld_res;
+        }
 
         for (int c = 0; c < L.n_chunks; ++c) {
             if (ok && !mbar_wait_bounded(smem_u32(&sh.xready[stage]), phase, abort_flag)) ok = false;
@@ -370,6 +468,10 @@ __global__ void __launch_bounds__(GV_THREADS)
                     }
                 }
             }
+            if (EX && ok && c == L.n_chunks - 1) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) rsv[m] = sh.rs[stage][m];
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh.empty[stage]));
             if (++stage == n_stages) {
@@ -392,7 +494,10 @@ __global__ void __launch_bounds__(GV_THREADS)
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
                     if (m < L.M) {
-                        const float v = acc[m] + red[m * GV_TILE_ROWS + row] + bias;
+                        float v = acc[m] + red[m * GV_TILE_ROWS + row];
+                        if (EX) v *= rsv[m];
+                        v += bias;
+                        if (EX && residual) v += __bfloat162float(residual[static_cast<long long>(m) * ld_res + grow]);
                         const long long idx = static_cast<long long>(m) * L.ldy + grow;
                         if (y_dtype == IZB_F32) static_cast<float*>(L.y)[idx] = v;
                         else static_cast<__nv_bfloat16*>(L.y)[idx] = __float2bfloat16_rn(v);
@@ -404,10 +509,10 @@ __global__ void __launch_bounds__(GV_THREADS)
     if (!ok && lane == 0) atomicExch(status, 5);
 }
 
-template <int FMT, int MT>
+template <int FMT, int MT, bool EX>
 static int gemv_launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
                            const SkinnyProblem& single) {
-    auto kern = skinny_gemv_kernel<FMT, MT>;
+    auto kern = skinny_gemv_kernel<FMT, MT, EX>;
     static std::atomic<int> smem_set[16];
     const int dev_slot = ctx->device & 15;
     if (smem_set[dev_slot].load(std::memory_order_relaxed) < h.smem_bytes) {
@@ -426,9 +531,12 @@ template <int FMT>
 static int gemv_launch_fmt(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
                            const SkinnyProblem& single) {
     switch (h.gemv) {
-        case 1: return gemv_launch_one<FMT, 1>(ctx, stream, h, dev, single);
-        case 2: return gemv_launch_one<FMT, 2>(ctx, stream, h, dev, single);
-        case 4: return gemv_launch_one<FMT, 4>(ctx, stream, h, dev, single);
+        case 1: return h.extras ? gemv_launch_one<FMT, 1, true>(ctx, stream, h, dev, single)
+                                : gemv_launch_one<FMT, 1, false>(ctx, stream, h, dev, single);
+        case 2: return h.extras ? gemv_launch_one<FMT, 2, true>(ctx, stream, h, dev, single)
+                                : gemv_launch_one<FMT, 2, false>(ctx, stream, h, dev, single);
+        case 4: return h.extras ? gemv_launch_one<FMT, 4, true>(ctx, stream, h, dev, single)
+                                : gemv_launch_one<FMT, 4, false>(ctx, stream, h, dev, single);
         default: return IZB_ERR_BAD_ARG;
     }
 }

@@ -10,6 +10,9 @@ host-side mirror of `Qwen3DecoderLayer::forward` / `Qwen3Attention::forward` for
     x      = x + o_proj(attn)                          izb_linear; the add is fused into the next norm
     normed = post_attention_layernorm(x)               izb_rms_norm with residual
     x      = x + down(silu(gate) * up)                 izb_linear, izb_silu_mul, izb_linear; add deferred likewise
+
+For one or two tokens over block-quantised weights the norms, the silu-mul and both residual adds ride
+inside the projections (`fused_linear`): six launches per layer instead of ten.
 """
 from __future__ import annotations
 
@@ -49,24 +52,33 @@ class KvCache:
 
 
 class Qwen3DecoderLayer:
-    def __init__(self, w: Qwen3LayerWeights, fused_qk: bool = True):
+    def __init__(self, w: Qwen3LayerWeights, fused_qk: bool = True, fused_linear: bool = True):
         self.w = w
         self.fused_qk = fused_qk and w.head_dim in (64, 128)
+        self.fused_linear = fused_linear
+        self.fusion_max_tokens = ops.linear_fusion_max_tokens(w.fmt) if fused_linear else 0
 
     def forward(self, attn_in: torch.Tensor, residual: torch.Tensor | None, cos_half: torch.Tensor,
                 sin_half: torch.Tensor, cache: KvCache, pos: int):
         """attn_in [batch, hidden]: the layer input, or the previous layer's MLP output when `residual`
         (the previous layer's pre-MLP stream) is given; returns (mlp_out, stream) so that the caller's
-        next norm performs `stream + mlp_out`.  cos_half / sin_half [batch, head_dim / 2] for position `pos`."""
+        next norm performs `stream + mlp_out`; with the projections fusing the adds, (stream, None).
+        cos_half / sin_half [batch, head_dim / 2] for position `pos`."""
         w = self.w
         b = attn_in.shape[0]
         qd, kd = w.heads * w.head_dim, w.kv_heads * w.head_dim
-        if residual is None:
+        fuse = b <= self.fusion_max_tokens
+        if residual is None and fuse:
             x = attn_in
-            normed = ops.rms_norm(x, w.input_layernorm, w.eps)
+            qkv = ops.linear(x, w.qkv, w.fmt, n=qd + 2 * kd, k=w.hidden, prologue="rms_norm",
+                             norm_weight=w.input_layernorm, norm_eps=w.eps)
         else:
-            normed, x = ops.rms_norm(attn_in, w.input_layernorm, w.eps, residual=residual, return_sum=True)
-        qkv = ops.linear(normed, w.qkv, w.fmt, n=qd + 2 * kd, k=w.hidden)
+            if residual is None:
+                x = attn_in
+                normed = ops.rms_norm(x, w.input_layernorm, w.eps)
+            else:
+                normed, x = ops.rms_norm(attn_in, w.input_layernorm, w.eps, residual=residual, return_sum=True)
+            qkv = ops.linear(normed, w.qkv, w.fmt, n=qd + 2 * kd, k=w.hidden)
         if self.fused_qk:
             # q/k norms, rotation and cache append in one launch, reading the fused QKV output in place
             q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, w.eps, cos_half, sin_half, cache.k, cache.v, w.heads, pos)
@@ -82,6 +94,11 @@ class Qwen3DecoderLayer:
             ops.rope_pair_(q, k, cos_half, sin_half)
             ops.kv_append_(k, v, cache.k, cache.v, pos)
         attn = ops.decode_gqa_attention(q, cache.k, cache.v, pos + 1)
+        if fuse:
+            x = ops.linear(attn.reshape(b, qd), w.o, w.fmt, n=w.hidden, k=qd, residual=x)
+            gu = ops.linear(x, w.gate_up, w.fmt, n=2 * w.intermediate, k=w.hidden, prologue="rms_norm",
+                            norm_weight=w.post_attention_layernorm, norm_eps=w.eps)
+            return ops.linear(gu, w.down, w.fmt, n=w.hidden, k=w.intermediate, prologue="silu_mul", residual=x), None
         o = ops.linear(attn.reshape(b, qd), w.o, w.fmt, n=w.hidden, k=qd)
         normed2, x = ops.rms_norm(o, w.post_attention_layernorm, w.eps, residual=x, return_sum=True)
         gu = ops.linear(normed2, w.gate_up, w.fmt, n=2 * w.intermediate, k=w.hidden)
@@ -115,7 +132,11 @@ class Qwen3Decoder:
         out, stream = self.embed[tokens], None
         for layer, cache in zip(self.layers, caches):
             out, stream = layer.forward(out, stream, cos_half, sin_half, cache, pos)
-        hidden = ops.rms_norm(out, self.final_norm, self.w.eps, residual=stream)
         vocab = self.embed.shape[0]
-        logits = ops.linear(hidden, self.lm_head, self.lm_head_fmt, n=vocab, k=self.w.hidden, out_dtype=torch.float32)
+        if stream is None and self.layers[0].fused_linear and out.shape[0] <= ops.linear_fusion_max_tokens(self.lm_head_fmt):
+            logits = ops.linear(out, self.lm_head, self.lm_head_fmt, n=vocab, k=self.w.hidden, out_dtype=torch.float32,
+                                prologue="rms_norm", norm_weight=self.final_norm, norm_eps=self.w.eps)
+        else:
+            hidden = ops.rms_norm(out, self.final_norm, self.w.eps, residual=stream)
+            logits = ops.linear(hidden, self.lm_head, self.lm_head_fmt, n=vocab, k=self.w.hidden, out_dtype=torch.float32)
         return ops.argmax_rows(logits)

@@ -68,11 +68,14 @@ def dequantize(raw: torch.Tensor, fmt: str, n_elems: int, dtype: torch.dtype = t
 
 EPILOGUE = {None: L.IZB_EPI_NONE, "none": L.IZB_EPI_NONE, "gelu": L.IZB_EPI_GELU, "silu": L.IZB_EPI_SILU,
             "swiglu": L.IZB_EPI_SWIGLU}
+PROLOGUE = {None: 0, "none": 0, "rms_norm": 1, "silu_mul": 2}  # izb_prologue
 
 
 def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: torch.Tensor,
                 bias: torch.Tensor | None = None, epilogue: str | None = None,
-                workspace: torch.Tensor | None = None) -> L.LinearArgs:
+                workspace: torch.Tensor | None = None, prologue: str | None = None,
+                norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0,
+                residual: torch.Tensor | None = None) -> L.LinearArgs:
     assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
     assert y.dim() == 2 and y.stride(1) == 1 and y.shape[0] == x.shape[0]
     a = L.LinearArgs()
@@ -84,23 +87,35 @@ def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: t
     a.workspace = None if workspace is None else workspace.data_ptr()
     a.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     a.epilogue = EPILOGUE[epilogue]
+    a.prologue = PROLOGUE[prologue]
+    if prologue == "rms_norm":
+        assert norm_weight is not None and norm_weight.dtype == torch.bfloat16 and norm_weight.shape == (k,)
+        a.norm_weight, a.norm_eps = norm_weight.data_ptr(), float(norm_eps)
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.dim() == 2 and residual.stride(1) == 1
+        assert residual.shape == (x.shape[0], n)
+        a.residual, a.ld_residual = residual.data_ptr(), residual.stride(0)
     return a
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = None, k: int | None = None,
            bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
            out_dtype: torch.dtype = torch.bfloat16, epilogue: str | None = None,
-           workspace: torch.Tensor | None | bool = True) -> torch.Tensor:
-    """Y = epilogue(X . W^T + bias).  `x` may have any number of leading dimensions
+           workspace: torch.Tensor | None | bool = True, prologue: str | None = None,
+           norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    """Y = epilogue(prologue(X) . W^T + bias) + residual.  `x` may have any number of leading dimensions
     (flattened to M like the reference's Linear); `w` is [N, K] bf16 or the raw
     GGML bytes of N rows of K values.  `workspace=True` lets this wrapper provide
-    the scratch buffer the library asks for (it never allocates itself)."""
+    the scratch buffer the library asks for (it never allocates itself).
+    `prologue` "rms_norm" (with `norm_weight`, `norm_eps`) or "silu_mul" (x is [.., 2K] = gate | up) and
+    `residual` are taken only for at most `linear_fusion_max_tokens(fmt)` token rows."""
     if fmt == "bf16":
         n, k = w.shape
     assert n is not None and k is not None
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
-    if x2.shape[1] != k:
+    if x2.shape[1] != (2 * k if prologue == "silu_mul" else k):
         raise ValueError(f"linear: input dim {x2.shape[1]} != weight in-dim {k}")
     n_out = n // 2 if epilogue == "swiglu" else n
     y = out if out is not None else torch.empty(x2.shape[0], n_out, device=x.device, dtype=out_dtype)
@@ -111,10 +126,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = 
         workspace = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
     elif workspace is False:
         workspace = None
-    a = linear_args(x2, w, fmt, n, k, y.reshape(-1, n_out), bias, epilogue, workspace)
+    a = linear_args(x2, w, fmt, n, k, y.reshape(-1, n_out), bias, epilogue, workspace, prologue, norm_weight, norm_eps,
+                    None if residual is None else residual.reshape(-1, n_out))
     ctx = Context.get(x.device.index)
     L.check(L.lib().izb_linear(ctx.handle, _stream(), C.byref(a)), "izb_linear")
     return y.reshape(*lead, n_out)
+
+
+def linear_fusion_max_tokens(fmt: str) -> int:
+    """Most token rows for which `linear` takes a prologue or a residual with weights stored as `fmt`."""
+    return int(L.lib().izb_linear_fusion_max_tokens(WFMT[fmt]))
 
 
 def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

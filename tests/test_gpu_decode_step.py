@@ -50,9 +50,9 @@ def _oracle_layer(L, x, kc, vc, pos, cos, sin):
     return o.bf16_round(x1 + lin(act, L["down"][1]))
 
 
-@pytest.mark.parametrize("fused_qk", [True, False])
+@pytest.mark.parametrize("fused_qk,fused_linear", [(True, True), (True, False), (False, False)])
 @pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
-def test_three_tokens_two_layers(cuda, fmt, fused_qk):
+def test_three_tokens_two_layers(cuda, fmt, fused_qk, fused_linear):
     from izwi_b200 import decoder, ops
     rng = np.random.default_rng(21)
     layers_np = [_layer_np(rng, fmt), _layer_np(rng, fmt)]
@@ -60,7 +60,8 @@ def test_three_tokens_two_layers(cuda, fmt, fused_qk):
     layers = [decoder.Qwen3DecoderLayer(decoder.Qwen3LayerWeights(
         fmt, HID, HEADS, KVH, D, INTER, dev(L["ln1"]), dev(L["ln2"]), dev(L["qn"]), dev(L["kn"]),
         torch.from_numpy(L["qkv"][0]).to(cuda), torch.from_numpy(L["o"][0]).to(cuda),
-        torch.from_numpy(L["gu"][0]).to(cuda), torch.from_numpy(L["down"][0]).to(cuda), EPS), fused_qk=fused_qk)
+        torch.from_numpy(L["gu"][0]).to(cuda), torch.from_numpy(L["down"][0]).to(cuda), EPS), fused_qk=fused_qk,
+        fused_linear=fused_linear)
         for L in layers_np]
     b, cap = 2, 16
     caches = [decoder.KvCache(b, KVH, cap, D, cuda) for _ in layers]
@@ -71,11 +72,12 @@ def test_three_tokens_two_layers(cuda, fmt, fused_qk):
         x = bf16_np(rng.normal(0, 1, (b, HID)))
         ang = np.repeat((pos * inv)[None, :], b, axis=0)
         cos, sin = bf16_np(np.cos(ang)), bf16_np(np.sin(ang))
-        # GPU: the residual add after each MLP is carried into the next norm
+        # GPU: the residual add after each MLP is carried into the next norm, or done by the down projection
         out, stream = dev(x), None
         for layer, cache in zip(layers, caches):
             out, stream = layer.forward(out, stream, dev(cos), dev(sin), cache, pos)
-        got = to_np((stream.float() + out.float()).to(torch.bfloat16))
+        assert (stream is None) == fused_linear  # two tokens: the projections take the norms and adds
+        got = to_np(out if stream is None else (stream.float() + out.float()).to(torch.bfloat16))
         ops.Context.get(0).check()
         want = x
         for L, kc, vc in zip(layers_np, kcs, vcs):
