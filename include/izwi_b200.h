@@ -325,8 +325,11 @@ int32_t izb_rms_norm(izb_ctx* ctx, izb_stream stream, const void* x, const void*
                      int64_t ld_x, int64_t ld_residual, int64_t ld_out, int64_t ld_sum, float eps);
 /* Arg-max of every row of a bf16 / fp32 matrix (greedy token choice over the lm_head logits):
  * the lowest index among equal maxima; NaN is never selected (a row of only NaN gives 0, -inf).
- * `out_val` may be NULL.  Replaces `argmax` (models/architectures/qwen3/chat.rs:574-601), which
- * copies the logits row to the host and reduces there. */
+ * `out_val` may be NULL.  A few long rows (16384 columns or more) are split across CTAs through a
+ * small per-context scratch area, so such calls on one context must be ordered with respect to one
+ * another (one stream, or events between streams).  Replaces `argmax`
+ * (models/architectures/qwen3/chat.rs:574-601), which copies the logits row to the host and reduces
+ * there. */
 int32_t izb_argmax_rows(izb_ctx* ctx, izb_stream stream, const void* x, int32_t x_dtype, int64_t rows,
                         int64_t cols, int64_t ld_x, int32_t* out_idx, float* out_val);
 

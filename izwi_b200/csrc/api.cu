@@ -1,4 +1,5 @@
 // C ABI: context, block dequantisation, SwiGLU glue and the linear-layer entry points.
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -116,6 +117,8 @@ __device__ __forceinline__ float silu_mul_f(float g, float u) { return g / (1.0f
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                                 __nv_bfloat16* __restrict__ out, long long rows, long long cols, long long ldg,
                                 long long ldu, long long ldo, int vec) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long cols_v = vec ? cols / 8 : cols;
     const long long total = rows * cols_v;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -185,14 +188,22 @@ int32_t izb_ctx_create(int32_t device, izb_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
     ctx->launches.store(0);
+    {
+        const char* e = std::getenv("IZB_PDL");
+        ctx->pdl = (e && e[0] == '0') ? 0 : 1;
+    }
     ctx->d_status = nullptr;
-    if (cudaMalloc(&ctx->d_status, IZB_STATUS_WORDS * sizeof(int)) != cudaSuccess ||
-        cudaMemset(ctx->d_status, 0, IZB_STATUS_WORDS * sizeof(int)) != cudaSuccess) {
+    // one allocation: status words (padded to 64 bytes), then the arg-max keys and counters
+    const size_t dev_bytes = 64 + static_cast<size_t>(IZB_ARGMAX_SPLIT_ROWS) * (sizeof(unsigned long long) + sizeof(unsigned int));
+    static_assert(IZB_STATUS_WORDS * sizeof(int) <= 64, "status words outgrew their slot");
+    if (cudaMalloc(&ctx->d_status, dev_bytes) != cudaSuccess || cudaMemset(ctx->d_status, 0, dev_bytes) != cudaSuccess) {
         (void)cudaGetLastError();
         delete ctx;
         (void)cudaSetDevice(prev);
         return IZB_ERR_LAUNCH;
     }
+    ctx->d_argmax_keys = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(ctx->d_status) + 64);
+    ctx->d_argmax_done = reinterpret_cast<unsigned int*>(ctx->d_argmax_keys + IZB_ARGMAX_SPLIT_ROWS);
     (void)cudaSetDevice(prev);
     *out = ctx;
     return IZB_OK;
@@ -297,10 +308,10 @@ int32_t izb_silu_mul(izb_ctx* ctx, izb_stream stream, const void* gate, const vo
                      izb_aligned(up, 16) && izb_aligned(out, 16);
     const long long items = rows * (vec ? cols / 8 : cols);
     const int threads = 256;
-    silu_mul_kernel<<<grid_for(ctx, items, threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out),
-        rows, cols, ld_gate, ld_up, ld_out, vec ? 1 : 0);
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(izb::launch_chained(ctx, silu_mul_kernel, dim3(grid_for(ctx, items, threads)), dim3(threads), 0,
+                                     static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(gate),
+                                     static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), rows, cols, ld_gate,
+                                     ld_up, ld_out, vec ? 1 : 0));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }

@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(256)
                                const __nv_bfloat16* __restrict__ sin_half, __nv_bfloat16* __restrict__ q_out, long long ld_q_out,
                                __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, long long batch, int heads,
                                int kv_heads, long long pos, long long cap) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     constexpr int E = D / 32;  // elements per lane; the rotation partner of element j is j +- D/2: lane ^ 16
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rows_per_tok = heads + 2 * kv_heads;
@@ -113,6 +115,8 @@ __global__ void __launch_bounds__(ATT_THREADS)
                       const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out, float* __restrict__ part,
                       int heads, int kv_heads, int g_real, long long ld_q_tok, long long ld_out_tok, long long kv_cap,
                       int kv_len, float scale) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     constexpr int DV = D / 32;  // output values per lane
     extern __shared__ float dyn[];
     float* S = dyn;                        // [G][ATT_THREADS]: scores, then probabilities of the tile
@@ -282,6 +286,8 @@ template <int D>
 __global__ void __launch_bounds__(D)
     decode_gqa_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int heads, int n_splits,
                             long long ld_out_tok) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const float* p = part + (static_cast<long long>(b) * heads + head) * n_splits * (D + 2);
     float m = -INFINITY;
@@ -317,13 +323,12 @@ int launch_att(izb_ctx* ctx, cudaStream_t s, const __nv_bfloat16* q, const __nv_
         IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         smem_set[slot].store(static_cast<int>(smem), std::memory_order_relaxed);
     }
-    kern<<<dim3(splits, kv_heads, batch), ATT_THREADS, smem, s>>>(q, k, v, out, part, heads, kv_heads, g_real, ld_q, ld_out,
-                                                                 kv_cap, kv_len, scale);
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(izb::launch_chained(ctx, kern, dim3(splits, kv_heads, batch), dim3(ATT_THREADS), smem, s, q, k, v, out, part, heads,
+                                     kv_heads, g_real, ld_q, ld_out, kv_cap, kv_len, scale));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     if (splits > 1) {
-        decode_gqa_merge_kernel<D><<<dim3(heads, batch), D, 0, s>>>(part, out, heads, splits, ld_out);
-        IZB_CUDA_TRY(cudaGetLastError());
+        IZB_CUDA_TRY(izb::launch_chained(ctx, decode_gqa_merge_kernel<D>, dim3(heads, batch), dim3(D), 0, s,
+                                         static_cast<const float*>(part), out, heads, splits, ld_out));
         ctx->launches.fetch_add(1, std::memory_order_relaxed);
     }
     return IZB_OK;
@@ -404,12 +409,11 @@ int32_t izb_qk_norm_rope_append(izb_ctx* ctx, izb_stream stream, const void* qkv
     auto* kc = static_cast<__nv_bfloat16*>(k_cache);
     auto* vc = static_cast<__nv_bfloat16*>(v_cache);
     if (head_dim == 128)
-        qk_norm_rope_append_kernel<128><<<grid, 256, 0, s>>>(in, ld_qkv, qw, kw, eps, cs, sn, qo, ld_q_out, kc, vc, batch, heads,
-                                                             kv_heads, pos, kv_capacity);
+        IZB_CUDA_TRY(izb::launch_chained(ctx, qk_norm_rope_append_kernel<128>, dim3(grid), dim3(256), 0, s, in, ld_qkv, qw, kw, eps, cs,
+                                         sn, qo, ld_q_out, kc, vc, batch, heads, kv_heads, pos, kv_capacity));
     else
-        qk_norm_rope_append_kernel<64><<<grid, 256, 0, s>>>(in, ld_qkv, qw, kw, eps, cs, sn, qo, ld_q_out, kc, vc, batch, heads,
-                                                            kv_heads, pos, kv_capacity);
-    IZB_CUDA_TRY(cudaGetLastError());
+        IZB_CUDA_TRY(izb::launch_chained(ctx, qk_norm_rope_append_kernel<64>, dim3(grid), dim3(256), 0, s, in, ld_qkv, qw, kw, eps, cs,
+                                         sn, qo, ld_q_out, kc, vc, batch, heads, kv_heads, pos, kv_capacity));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }

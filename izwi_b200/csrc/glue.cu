@@ -1,6 +1,8 @@
 // Row-wise glue around the projections of a decode step: RMS normalisation (optionally after a
 // residual add) and arg-max over logits.  HBM-bound, one pass over the data, 16-byte accesses
 // when the rows allow.
+#include <algorithm>
+
 #include "izb_common.cuh"
 
 namespace {
@@ -25,6 +27,8 @@ __global__ void __launch_bounds__(256)
                     const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
                     __nv_bfloat16* __restrict__ sum_out, long long rows, int cols, long long ldx, long long ldr,
                     long long ldo, long long lds, float eps) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     __shared__ float partial[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int group = WARP_ROW ? 32 : blockDim.x;
@@ -68,6 +72,8 @@ template <typename T>
 __global__ void __launch_bounds__(512)
     argmax_rows_kernel(const T* __restrict__ x, long long rows, long long cols, long long ldx, int32_t* __restrict__ out_idx,
                        float* __restrict__ out_val) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     __shared__ float sv[16];
     __shared__ long long si[16];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -110,6 +116,76 @@ __global__ void __launch_bounds__(512)
     }
 }
 
+// A few very long rows (the logits of a decode step): `splits` CTAs share a row.  Each folds its
+// best (value, index) into one 64-bit key per row with atomicMax: the value's bits made monotonic
+// in the high word, the complemented index in the low word, so the largest key is the largest value
+// at its lowest index.  The last CTA to arrive writes the row's result and zeroes key and counter
+// for the next call.
+__device__ __forceinline__ unsigned long long argmax_key(float v, long long idx) {
+    const uint32_t b = v == 0.f ? 0u : __float_as_uint(v);  // -0 and +0 are equal maxima
+    const uint32_t hi = b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+    const uint32_t lo = 0xFFFFFFFFu - static_cast<uint32_t>(idx > 0xFFFFFFFFll ? 0xFFFFFFFFll : idx);
+    return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+    argmax_rows_split_kernel(const T* __restrict__ x, long long cols, long long ldx, int splits, int32_t* __restrict__ out_idx,
+                             float* __restrict__ out_val, unsigned long long* __restrict__ keys,
+                             unsigned int* __restrict__ done) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
+    __shared__ float sv[16];
+    __shared__ long long si[16];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x / splits, part = blockIdx.x % splits;
+    const long long chunk = (cols + splits - 1) / splits;
+    const long long c0 = part * chunk, c1 = min(cols, c0 + chunk);
+    const T* xr = x + static_cast<long long>(row) * ldx;
+    float best = -INFINITY;
+    long long bi = 0x7FFFFFFFFFFFFFFFll;
+    for (long long c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+        const float v = static_cast<float>(xr[c]);
+        if (v > best) {
+            best = v;
+            bi = c;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        const long long oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (blockDim.x >> 5); ++w) {
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+                best = sv[w];
+                bi = si[w];
+            }
+        }
+        atomicMax(&keys[row], argmax_key(best, bi));
+        __threadfence();
+        if (atomicAdd(&done[row], 1u) == static_cast<unsigned int>(splits - 1)) {
+            __threadfence();
+            const unsigned long long k = atomicExch(&keys[row], 0ull);
+            done[row] = 0;
+            const uint32_t hi = static_cast<uint32_t>(k >> 32), lo = static_cast<uint32_t>(k);
+            const uint32_t idx = 0xFFFFFFFFu - lo;  // 0xFFFFFFFF: nothing but NaN in the row
+            out_idx[row] = idx == 0xFFFFFFFFu ? 0 : static_cast<int32_t>(idx);
+            if (out_val) out_val[row] = __uint_as_float(hi ^ ((hi >> 31) ? 0x80000000u : 0xFFFFFFFFu));
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -136,13 +212,13 @@ int32_t izb_rms_norm(izb_ctx* ctx, izb_stream stream, const void* x, const void*
     const long long cap = static_cast<long long>(ctx->sm_count) * 16;
     if (cols <= 512) {  // short rows (head-wise q/k norm): a warp per row, eight rows per block
         const long long blocks = (rows + 7) / 8;
-        rms_norm_kernel<true><<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, s>>>(
-            xp, wp, rp, op, sp, rows, static_cast<int>(cols), ld_x, ld_residual, ld_out, ld_sum, eps);
+        IZB_CUDA_TRY(izb::launch_chained(ctx, rms_norm_kernel<true>, dim3(static_cast<int>(blocks < cap ? blocks : cap)), dim3(256), 0,
+                                         s, xp, wp, rp, op, sp, rows, static_cast<int>(cols), ld_x, ld_residual, ld_out, ld_sum,
+                                         eps));
     } else {
-        rms_norm_kernel<false><<<static_cast<int>(rows < cap ? rows : cap), 256, 0, s>>>(
-            xp, wp, rp, op, sp, rows, static_cast<int>(cols), ld_x, ld_residual, ld_out, ld_sum, eps);
+        IZB_CUDA_TRY(izb::launch_chained(ctx, rms_norm_kernel<false>, dim3(static_cast<int>(rows < cap ? rows : cap)), dim3(256), 0, s,
+                                         xp, wp, rp, op, sp, rows, static_cast<int>(cols), ld_x, ld_residual, ld_out, ld_sum, eps));
     }
-    IZB_CUDA_TRY(cudaGetLastError());
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
@@ -158,13 +234,28 @@ int32_t izb_argmax_rows(izb_ctx* ctx, izb_stream stream, const void* x, int32_t 
         return IZB_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long cap = static_cast<long long>(ctx->sm_count) * 4;
+    // few long rows: several CTAs per row, at least 8192 values each
+    const long long splits = std::min<long long>(cols / 8192, cap / rows);
+    if (rows <= IZB_ARGMAX_SPLIT_ROWS && splits >= 2) {
+        const int grid = static_cast<int>(rows * splits);
+        if (x_dtype == IZB_F32)
+            IZB_CUDA_TRY(izb::launch_chained(ctx, argmax_rows_split_kernel<float>, dim3(grid), dim3(512), 0, s,
+                                             static_cast<const float*>(x), cols, ld_x, static_cast<int>(splits), out_idx, out_val,
+                                             ctx->d_argmax_keys, ctx->d_argmax_done));
+        else
+            IZB_CUDA_TRY(izb::launch_chained(ctx, argmax_rows_split_kernel<__nv_bfloat16>, dim3(grid), dim3(512), 0, s,
+                                             static_cast<const __nv_bfloat16*>(x), cols, ld_x, static_cast<int>(splits), out_idx,
+                                             out_val, ctx->d_argmax_keys, ctx->d_argmax_done));
+        ctx->launches.fetch_add(1, std::memory_order_relaxed);
+        return IZB_OK;
+    }
     const int grid = static_cast<int>(rows < cap ? rows : cap);
     if (x_dtype == IZB_F32)
-        argmax_rows_kernel<float><<<grid, 512, 0, s>>>(static_cast<const float*>(x), rows, cols, ld_x, out_idx, out_val);
+        IZB_CUDA_TRY(izb::launch_chained(ctx, argmax_rows_kernel<float>, dim3(grid), dim3(512), 0, s, static_cast<const float*>(x), rows,
+                                         cols, ld_x, out_idx, out_val));
     else
-        argmax_rows_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, ld_x, out_idx,
-                                                               out_val);
-    IZB_CUDA_TRY(cudaGetLastError());
+        IZB_CUDA_TRY(izb::launch_chained(ctx, argmax_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(512), 0, s,
+                                         static_cast<const __nv_bfloat16*>(x), rows, cols, ld_x, out_idx, out_val));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }

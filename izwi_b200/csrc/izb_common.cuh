@@ -16,9 +16,15 @@ struct izb_ctx {
     int max_smem_optin;
     int* d_status;  // [IZB_STATUS_WORDS] device status words written by kernels on a failed wait
     std::atomic<int64_t> launches;
+    // arg-max over a few very long rows, split across CTAs: one packed (value, index) key and one
+    // arrival counter per row; the last CTA of a row writes the result and zeroes both again
+    unsigned long long* d_argmax_keys;  // [IZB_ARGMAX_SPLIT_ROWS]
+    unsigned int* d_argmax_done;        // [IZB_ARGMAX_SPLIT_ROWS]
+    int pdl;  // launch the decode-step kernels with programmatic stream serialisation (IZB_PDL=0 turns it off)
 };
 
 constexpr int IZB_STATUS_WORDS = 8;
+constexpr int IZB_ARGMAX_SPLIT_ROWS = 1024;
 // Bounded device-side waits give up after this many clock64 ticks (~1 s).
 constexpr long long IZB_WAIT_LIMIT_CLOCKS = 2000000000LL;
 
@@ -35,6 +41,32 @@ static inline bool izb_aligned(const void* p, size_t a) { return (reinterpret_ca
 
 #ifdef __CUDACC__
 namespace izb {
+
+// Programmatic dependent launch.  The kernels of a decode step are a chain of short launches, each
+// reading what the one before wrote.  Launched through launch_chained, a kernel may start while its
+// predecessor in the stream still runs: its CTAs set up shared memory and barriers, then pdl_wait()
+// blocks until the predecessor has completed and its writes are visible.  Every kernel launched this
+// way calls pdl_wait() before its first access to global memory that another kernel writes, and
+// before its own first write; pdl_launch_dependents() at its top lets the successor do the same.
+// Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(const izb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (ctx && ctx->pdl) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -568,9 +568,17 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     // byte), two otherwise; wide token groups need the whole SM's shared memory for one CTA
     int ctas_per_sm = std::max(1, env_int("IZB_SKINNY_CTAS_PER_SM", gemv ? 4 : (fmt == IZB_W_Q8_0 && nt <= 2) ? 3 : 2));
     if ((nt == 8 || tc) && !env_int("IZB_SKINNY_CTAS_PER_SM", 0)) ctas_per_sm = 1;
+    if (gemv && !env_int("IZB_SKINNY_CTAS_PER_SM", 0)) {
+        // a lone projection of a decode step has fewer 64-row tiles than four per SM: fewer CTAs per
+        // SM then, each with a deeper ring, since with so few CTAs it is the bytes in flight per CTA
+        // that set the rate
+        int64_t tiles = 0;
+        for (int i = 0; i < n; ++i) tiles += (probs[i].N + 63) / 64;
+        ctas_per_sm = static_cast<int>(std::min<int64_t>(4, std::max<int64_t>(1, (tiles + ctx->sm_count - 1) / ctx->sm_count)));
+    }
     const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
     const int max_grid = ctx->sm_count * ctas_per_sm;
-    const int static_smem = gemv ? 256 + 512 * gemv : static_cast<int>(sizeof(SkinnyShared));  // barriers (+ gemv: k-half sums)
+    const int static_smem = gemv ? 384 + 512 * gemv : static_cast<int>(sizeof(SkinnyShared));  // barriers (+ gemv: k-half sums)
     const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_smem;
 
     // Bytes of the smallest possible stage (one weight box + its activation chunks) of a row tile.
@@ -704,7 +712,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     // otherwise the k-split partial sums
     int red_raw = tc ? 4 * 128 * 128 : ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
     if (gemv) {
-        int s = SK_MAX_STAGES;
+        int s = GV_MAX_STAGES;
         while (s > 2 && lite_bytes + (s * xq_stage + 1023) / 1024 * 1024 + s * stage_bytes > budget) --s;
         red_raw = s * xq_stage;
     }
@@ -728,7 +736,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         if (forced_stages) n_stages = std::min(forced_stages, n_stages);
     } else {
         if (forced_stages) n_stages = forced_stages;
-        n_stages = std::min(n_stages, SK_MAX_STAGES);
+        n_stages = std::min(n_stages, gemv ? GV_MAX_STAGES : SK_MAX_STAGES);
         if (n_stages < 2) {
             // A single stage pair must still fit one CTA per SM.
             n_stages = 2;

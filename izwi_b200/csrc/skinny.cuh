@@ -21,6 +21,7 @@ namespace izb {
 constexpr int SK_CONSUMER_WARPS = 4;
 constexpr int SK_THREADS = 32 * (SK_CONSUMER_WARPS + 1);
 constexpr int SK_MAX_STAGES = 8;
+constexpr int GV_MAX_STAGES = 12;  // the integer-dot-product kernel alone on an SM runs a deeper ring
 constexpr uint32_t SK_PLAN_MAGIC = 0x495A4232u;  // "IZB2"
 
 struct alignas(64) SkinnyProblem {

@@ -32,12 +32,12 @@ constexpr int GV_XQ_XL = 256, GV_XQ_XS = 512, GV_XQ_SX = 544;
 
 template <int MT, bool EX>
 struct GvShared {
-    unsigned long long full[SK_MAX_STAGES];    // copies landed
-    unsigned long long xready[SK_MAX_STAGES];  // activations of the stage converted
-    unsigned long long empty[SK_MAX_STAGES];   // consumers done with the stage
+    unsigned long long full[GV_MAX_STAGES];    // copies landed
+    unsigned long long xready[GV_MAX_STAGES];  // activations of the stage converted
+    unsigned long long empty[GV_MAX_STAGES];   // consumers done with the stage
     float red[2][GV_TILE_ROWS * MT];           // partial sums of the second k-half, double-buffered by tile parity
     // fused RmsNorm: 1 / rms of every token, left by the converter in the slot of the tile's last stage
-    float rs[EX ? SK_MAX_STAGES : 1][MT];
+    float rs[EX ? GV_MAX_STAGES : 1][MT];
     int abort_flag;
 };
 
@@ -253,6 +253,7 @@ __global__ void __launch_bounds__(GV_THREADS)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const SkinnyProblem* plist = probs ? probs : &single;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) {
@@ -266,8 +267,9 @@ __global__ void __launch_bounds__(GV_THREADS)
     // dynamic shared memory: [descriptor cache][converted activations per stage][stage ring]; stage = [weight boxes][activations]
     ProbLite* lite = reinterpret_cast<ProbLite*>(dyn_smem);
     const int n_cached = min(n_probs, lite_bytes / static_cast<int>(sizeof(ProbLite)));
-    for (int i = threadIdx.x; i < n_cached; i += blockDim.x) lite[i] = lite_from(plist[i]);
+    for (int i = threadIdx.x; i < n_cached; i += blockDim.x) lite[i] = lite_from(plist[i]);  // the plan: written by the host
     __syncthreads();
+    pdl_wait();  // activations, residual and the output buffer belong to the kernels before this one
 
     volatile int* abort_flag = &sh.abort_flag;
     const uint32_t xq0 = smem_u32(dyn_smem) + static_cast<uint32_t>(lite_bytes);
@@ -355,13 +357,31 @@ __global__ void __launch_bounds__(GV_THREADS)
                 eps = P->eps;
                 K = P->K;
             }
+            // norm weights of this lane's 8 values in the first two boxes of a chunk, fetched one chunk
+            // ahead: a load from global memory inside the chunk loop would stall every stage by its latency
+            const int klane = (lane >> 3) * 64 + (lane & 7) * 8;
+            uint4 gnext[2] = {};
+            if (EX && pro == IZB_PRO_RMSNORM) {
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+                    if (b < L.nb) gnext[b] = __ldg(reinterpret_cast<const uint4*>(norm_w + b * 256 + klane));
+            }
             for (int c = 0; c < L.n_chunks; ++c) {
+                uint4 gcur[2] = {gnext[0], gnext[1]};
+                if (EX && pro == IZB_PRO_RMSNORM && c + 1 < L.n_chunks) {
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+                        if (b < L.nb) gnext[b] = __ldg(reinterpret_cast<const uint4*>(norm_w + ((c + 1) * L.nb + b) * 256 + klane));
+                }
                 if (!mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) {
                     ok = false;
                     break;
                 }
                 const uint32_t sbase = stage0 + static_cast<uint32_t>(stage) * static_cast<uint32_t>(stage_bytes);
                 for (int b = 0; b < L.nb; ++b) {
+                    uint4 gw = {};
+                    if (EX && pro == IZB_PRO_RMSNORM)
+                        gw = b == 0 ? gcur[0] : b == 1 ? gcur[1] : __ldg(reinterpret_cast<const uint4*>(norm_w + (c * L.nb + b) * 256 + klane));
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
                         if (m >= M) break;
@@ -382,8 +402,7 @@ __global__ void __launch_bounds__(GV_THREADS)
                             }
                             uint4 o;  // the other factor of every value: norm weights, or the `up` half of the row
                             if (pro == IZB_PRO_RMSNORM) {
-                                const int k = (c * L.nb + b) * 256 + (lane >> 3) * 64 + (lane & 7) * 8;
-                                o = __ldg(reinterpret_cast<const uint4*>(norm_w + k));
+                                o = gw;
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) ss[m] = fmaf(f[i], f[i], ss[m]);
                             } else {
@@ -439,11 +458,17 @@ __global__ void __launch_bounds__(GV_THREADS)
             acc[m] = 0.f;
             rsv[m] = 1.0f;
         }
-        const __nv_bfloat16* residual = nullptr;
-        int ld_res = 0;
-        if (EX && L.extras) {
-            residual = plist[p].residual;
-            ld_res = plist[p].ld_res;
+        // EX: bias and residual of this thread's row are fetched before the k loop, not at its end
+        float addv[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) addv[m] = 0.f;
+        if (EX && kh == 0 && row0 + row < L.N) {
+            const float bias = L.bias ? __bfloat162float(L.bias[row0 + row]) : 0.f;
+            const __nv_bfloat16* residual = L.extras ? plist[p].residual : nullptr;
+            const int ld_res = residual ? plist[p].ld_res : 0;
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                addv[m] = bias + ((residual && m < L.M) ? __bfloat162float(residual[static_cast<long long>(m) * ld_res + row0 + row]) : 0.f);
         }
 
         for (int c = 0; c < L.n_chunks; ++c) {
@@ -490,14 +515,13 @@ __global__ void __launch_bounds__(GV_THREADS)
         if (kh == 0 && ok) {
             const int grow = row0 + row;
             if (grow < L.N) {
-                const float bias = L.bias ? __bfloat162float(L.bias[grow]) : 0.f;
+                const float bias = (!EX && L.bias) ? __bfloat162float(L.bias[grow]) : 0.f;
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
                     if (m < L.M) {
                         float v = acc[m] + red[m * GV_TILE_ROWS + row];
-                        if (EX) v *= rsv[m];
-                        v += bias;
-                        if (EX && residual) v += __bfloat162float(residual[static_cast<long long>(m) * ld_res + grow]);
+                        if (EX) v = fmaf(v, rsv[m], addv[m]);
+                        else v += bias;
                         const long long idx = static_cast<long long>(m) * L.ldy + grow;
                         if (y_dtype == IZB_F32) static_cast<float*>(L.y)[idx] = v;
                         else static_cast<__nv_bfloat16*>(L.y)[idx] = __float2bfloat16_rn(v);
@@ -519,10 +543,9 @@ static int gemv_launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHe
         IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));
         smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);
     }
-    kern<<<h.grid, GV_THREADS, h.smem_bytes, stream>>>(dev, single, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes,
-                                                       h.xq_stage_bytes, h.red_bytes, h.lite_bytes, h.y_dtype,
-                                                       ctx->d_status + 4);
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(launch_chained(ctx, kern, dim3(h.grid), dim3(GV_THREADS), h.smem_bytes, stream, dev, single, h.n_probs,
+                                h.total_tiles, h.n_stages, h.stage_bytes, h.xq_stage_bytes, h.red_bytes, h.lite_bytes, h.y_dtype,
+                                ctx->d_status + 4));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }

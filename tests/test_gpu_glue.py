@@ -85,6 +85,36 @@ def test_argmax_rows(cuda, dtype):
     assert int(i2[0]) == 0 and float(v2[0]) == float("-inf")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_argmax_long_rows_split_across_ctas(cuda, dtype):
+    """Rows of a vocabulary's length take several CTAs each: ties across the CTA boundaries, -inf and
+    NaN rows, and back-to-back calls (the per-row scratch must come back clean)."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(19)
+    cols = 151936
+    for rows in (1, 2, 7):
+        x = rng.normal(0, 3, (rows, cols)).astype(np.float32)
+        x[0, [8440, 8441, 75968, cols - 1]] = 40.0   # equal maxima in different CTAs' ranges
+        if rows > 1:
+            x[1, :] = -np.inf
+            x[1, 90000] = -1e30
+        if rows > 2:
+            x[2, :] = np.nan
+            x[3, :] = -np.inf
+            x[4, :] = np.nan
+            x[4, cols - 1] = -np.inf
+            x[5, :] = -0.0
+            x[5, 131072] = 0.0                        # +0 == -0: the lowest index still wins
+        xd = torch.from_numpy(x).to(cuda).to(dtype)
+        for _ in range(3):
+            idx, val = ops.argmax_rows(xd, return_values=True)
+        ops.Context.get(0).check()
+        want_i, want_v = o.argmax_rows(to_np(xd))
+        assert np.array_equal(idx.cpu().numpy(), want_i), (rows, idx.cpu().numpy(), want_i)
+        assert np.array_equal(val.cpu().numpy(), want_v)
+        assert want_i[0] == 8440
+
+
 def test_lm_head_greedy_token(cuda):
     """lm_head GEMV over Q8_0 weights followed by the on-device arg-max equals the oracle's choice."""
     from izwi_b200 import ops
