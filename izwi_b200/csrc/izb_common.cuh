@@ -52,20 +52,38 @@ namespace izb {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// `cluster_x` > 1 launches thread-block clusters of that many CTAs along x.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_chained(const izb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                  cudaStream_t stream, Args... args) {
+inline cudaError_t launch_chained_cluster(const izb_ctx* ctx, int cluster_x, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                          size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr = {};
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = (ctx && ctx->pdl) ? 1 : 0;
+    cudaLaunchAttribute attr[2] = {};
+    unsigned n = 0;
+    if (ctx && ctx->pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(const izb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args... args) {
+    return launch_chained_cluster(ctx, 1, kernel, grid, block, smem, stream, args...);
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -141,6 +159,50 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
+}
+
+// Thread-block clusters: address of a shared-memory location in another CTA of the cluster, a store
+// and an mbarrier arrival there (release at cluster scope, so the stores before it are visible to a
+// waiter that acquires at cluster scope), and the barrier over all threads of the cluster.
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((++spins & 0x3FFu) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {

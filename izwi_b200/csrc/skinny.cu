@@ -578,7 +578,8 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     }
     const int stage_target = std::max(4, env_int("IZB_SKINNY_STAGE_KB", 24)) * 1024;
     const int max_grid = ctx->sm_count * ctas_per_sm;
-    const int static_smem = gemv ? 384 + 512 * gemv : static_cast<int>(sizeof(SkinnyShared));  // barriers (+ gemv: k-half sums)
+    // barriers (+ gemv: k-half sums, and with one CTA per SM room for the partial sums of a cluster's other CTAs)
+    const int static_smem = gemv ? 384 + 512 * gemv + (ctas_per_sm == 1 ? 2048 * gemv : 0) : static_cast<int>(sizeof(SkinnyShared));
     const int budget = ctx->max_smem_optin / ctas_per_sm - 2048 - static_smem;
 
     // Bytes of the smallest possible stage (one weight box + its activation chunks) of a row tile.
@@ -707,12 +708,26 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         }
     }
 
+    // A lone small projection: split the k chunks of every row tile over a cluster of CTAs, as many as
+    // keep the grid within one CTA per SM (skinny_gemv.cu); each CTA then needs a ring no deeper than its share.
+    int ksplit = 1, ring_cap = GV_MAX_STAGES;
+    const int ksplit_max = std::min(env_int("IZB_SKINNY_GEMV_KSPLIT", 8), 8);
+    if (gemv && gemv <= 2 && ctas_per_sm == 1 && ksplit_max > 1) {
+        int min_chunks = INT32_MAX, max_chunks = 0;
+        for (int i = 0; i < n; ++i) {
+            min_chunks = std::min(min_chunks, out[i].n_chunks);
+            max_chunks = std::max(max_chunks, out[i].n_chunks);
+        }
+        while (ksplit * 2 <= ksplit_max && ksplit * 2 <= min_chunks && tile_cursor * ksplit * 2 <= ctx->sm_count) ksplit *= 2;
+        if (ksplit > 1) ring_cap = std::max(2, (max_chunks + ksplit - 1) / ksplit);
+    }
+
     const int lite_bytes = (std::min(n, SK_LITE_MAX) * static_cast<int>(sizeof(ProbLite)) + 1023) / 1024 * 1024;
     // this region holds: tc, the four 16 KB operand slices; gemv, the converted activations of every stage;
     // otherwise the k-split partial sums
     int red_raw = tc ? 4 * 128 * 128 : ks > 1 ? (ks - 1) * rg * (rt * nt * 4) * 32 * 4 : 0;
     if (gemv) {
-        int s = GV_MAX_STAGES;
+        int s = std::min(GV_MAX_STAGES, ring_cap);
         while (s > 2 && lite_bytes + (s * xq_stage + 1023) / 1024 * 1024 + s * stage_bytes > budget) --s;
         red_raw = s * xq_stage;
     }
@@ -736,7 +751,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         if (forced_stages) n_stages = std::min(forced_stages, n_stages);
     } else {
         if (forced_stages) n_stages = forced_stages;
-        n_stages = std::min(n_stages, gemv ? GV_MAX_STAGES : SK_MAX_STAGES);
+        n_stages = std::min(n_stages, gemv ? std::min(GV_MAX_STAGES, ring_cap) : SK_MAX_STAGES);
         if (n_stages < 2) {
             // A single stage pair must still fit one CTA per SM.
             n_stages = 2;
@@ -764,6 +779,15 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     hdr->smem_bytes = lite_bytes + red_bytes + n_stages * stage_bytes + x_stages * 4 * mp * 128 + 1024;  // slack to align the ring to 1024 bytes
     hdr->grid = std::min(tile_cursor, max_grid);
     hdr->y_dtype = y_dtype;
+    hdr->ksplit = 1;
+    if (ksplit > 1) {
+        hdr->ksplit = ksplit;
+        hdr->grid = tile_cursor * ksplit;
+        if (!skinny_gemv_clusters_fit(ctx, *hdr)) {  // the device cannot hold all clusters at once: no split
+            hdr->ksplit = 1;
+            hdr->grid = std::min(tile_cursor, max_grid);
+        }
+    }
     return IZB_OK;
 }
 

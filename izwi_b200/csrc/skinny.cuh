@@ -62,7 +62,8 @@ struct alignas(64) SkinnyPlanHeader {
     int gemv;        // 1, 2 or 4: the integer-dot-product kernel for that many tokens (block-quantised weights); 0: off
     int xq_stage_bytes;  // gemv: bytes of converted activations per stage (red_bytes holds all stages)
     int extras;          // gemv: some problem carries a prologue or a residual
-    int pad_[13];
+    int ksplit;          // gemv: CTAs per cluster sharing a row tile, each a slice of its k chunks (1: no clusters)
+    int pad_[12];
 };
 static_assert(sizeof(SkinnyPlanHeader) == 128, "SkinnyPlanHeader layout");
 
@@ -154,6 +155,7 @@ int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr
 int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
                      const SkinnyProblem* single);
 // skinny_gemv.cu
+bool skinny_gemv_clusters_fit(const izb_ctx* ctx, const SkinnyPlanHeader& hdr);  // all of hdr.grid / hdr.ksplit clusters resident at once
 int skinny_gemv_max_tokens();  // widest token group the planner hands to the integer-dot-product kernel
 int skinny_gemv_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
                        const SkinnyProblem* single);

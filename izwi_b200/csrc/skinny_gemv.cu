@@ -16,6 +16,8 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "skinny.cuh"
 #include "tma.cuh"
@@ -30,14 +32,21 @@ constexpr int GV_TILE_ROWS = 64;
 constexpr int GV_XQ_BYTES = 256 + 256 + 32 + 32;
 constexpr int GV_XQ_XL = 256, GV_XQ_XS = 512, GV_XQ_SX = 544;
 
-template <int MT, bool EX>
+constexpr int GV_MAX_KSPLIT = 8;  // CTAs of a cluster sharing one row tile, each a slice of k
+
+template <int MT, bool EX, bool KS>
 struct GvShared {
     unsigned long long full[GV_MAX_STAGES];    // copies landed
     unsigned long long xready[GV_MAX_STAGES];  // activations of the stage converted
     unsigned long long empty[GV_MAX_STAGES];   // consumers done with the stage
     float red[2][GV_TILE_ROWS * MT];           // partial sums of the second k-half, double-buffered by tile parity
-    // fused RmsNorm: 1 / rms of every token, left by the converter in the slot of the tile's last stage
+    // fused RmsNorm: every token's sum of squares over the k this CTA saw, left by the converter in the
+    // slot of the tile's last stage
     float rs[EX ? GV_MAX_STAGES : 1][MT];
+    // k split over a cluster: the other CTAs' sums (and sums of squares) land here in the first CTA
+    float cl_red[KS ? (GV_MAX_KSPLIT - 1) * MT * GV_TILE_ROWS : 1];
+    float cl_ss[KS ? (GV_MAX_KSPLIT - 1) * MT : 1];
+    unsigned long long cl_bar;
     int abort_flag;
 };
 
@@ -71,6 +80,14 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
+}
+
+// 1 / x to within one ulp on the special-function unit (an IEEE division costs some twenty instructions,
+// and the single converting warp does eight per lane and stage); 1 / inf = 0.
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
 }
 
 // Exact int32 -> fp32 for |v| < 2^22 on the integer and fp32 pipes (the conversion unit runs at a
@@ -243,13 +260,19 @@ __device__ __forceinline__ void gv_half_q4_k(float (&acc)[MT], uint32_t wrow, ui
 
 // EX: some problem of the launch carries a fused prologue (RmsNorm, silu(gate) * up) or a residual;
 // the plain instantiation compiles none of that.
-template <int FMT, int MT, bool EX>
+// KS: launched as clusters of `ksplit` CTAs along x; the CTAs of a cluster share one row tile and take
+// consecutive slices of its k chunks, so a lone small projection spreads over the SMs instead of
+// walking its k on a few of them.  One tile per cluster (grid = tiles * ksplit).
+template <int FMT, int MT, bool EX, bool KS>
 __global__ void __launch_bounds__(GV_THREADS)
     skinny_gemv_kernel(const SkinnyProblem* __restrict__ probs, const __grid_constant__ SkinnyProblem single, int n_probs,
                        int total_tiles, int n_stages, int stage_bytes, int xq_stage_bytes, int xq_bytes, int lite_bytes,
-                       int y_dtype, int* status) {
+                       int y_dtype, int ksplit, int* status) {
     extern __shared__ __align__(1024) uint8_t dyn_smem[];
-    __shared__ GvShared<MT, EX> sh;
+    __shared__ GvShared<MT, EX, KS> sh;
+    const int crank = KS ? static_cast<int>(blockIdx.x) % ksplit : 0;       // rank inside the cluster
+    const int tile_first = KS ? static_cast<int>(blockIdx.x) / ksplit : static_cast<int>(blockIdx.x);
+    const int tile_step = KS ? static_cast<int>(gridDim.x) / ksplit : static_cast<int>(gridDim.x);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const SkinnyProblem* plist = probs ? probs : &single;
@@ -261,6 +284,7 @@ __global__ void __launch_bounds__(GV_THREADS)
             mbar_init(smem_u32(&sh.xready[s]), 1);
             mbar_init(smem_u32(&sh.empty[s]), GV_CONSUMER_WARPS);
         }
+        if (KS) mbar_init(smem_u32(&sh.cl_bar), static_cast<uint32_t>((GV_TILE_ROWS) * (ksplit - 1)));
         sh.abort_flag = 0;
         mbar_fence_init();
     }
@@ -269,6 +293,7 @@ __global__ void __launch_bounds__(GV_THREADS)
     const int n_cached = min(n_probs, lite_bytes / static_cast<int>(sizeof(ProbLite)));
     for (int i = threadIdx.x; i < n_cached; i += blockDim.x) lite[i] = lite_from(plist[i]);  // the plan: written by the host
     __syncthreads();
+    if (KS) cluster_sync_all();  // every CTA's barriers exist before any CTA of the cluster signals one
     pdl_wait();  // activations, residual and the output buffer belong to the kernels before this one
 
     volatile int* abort_flag = &sh.abort_flag;
@@ -282,7 +307,7 @@ __global__ void __launch_bounds__(GV_THREADS)
         uint32_t phase = 0;
         long long issued = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step) {
             const int np = find_problem(lite, n_cached, plist, n_probs, tile);
             const bool moved = np != p;
             p = np;
@@ -299,7 +324,8 @@ __global__ void __launch_bounds__(GV_THREADS)
                 up_chunk0 = P->up_chunk0;
                 x_half = P->x_half;
             }
-            for (int c = 0; c < L.n_chunks; ++c) {
+            const int c0 = KS ? crank * L.n_chunks / ksplit : 0, c1 = KS ? (crank + 1) * L.n_chunks / ksplit : L.n_chunks;
+            for (int c = c0; c < c1; ++c) {
                 if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
                     ok = false;
                     break;
@@ -339,13 +365,12 @@ __global__ void __launch_bounds__(GV_THREADS)
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step) {
             const int p = find_problem(lite, n_cached, plist, n_probs, tile);
             const ProbLite L = p < n_cached ? lite[p] : lite_from(plist[p]);
             const int M = min(L.M, MT);
-            int pro = IZB_PRO_NONE, x_half = 0, K = 1;
+            int pro = IZB_PRO_NONE, x_half = 0;
             const __nv_bfloat16* norm_w = nullptr;
-            float eps = 0.f;
             float ss[MT];  // fused RmsNorm: this lane's share of every token's sum of squares over the tile's k
 #pragma unroll
             for (int m = 0; m < MT; ++m) ss[m] = 0.f;
@@ -354,21 +379,20 @@ __global__ void __launch_bounds__(GV_THREADS)
                 pro = P->prologue;
                 x_half = P->x_half;
                 norm_w = P->norm_w;
-                eps = P->eps;
-                K = P->K;
             }
             // norm weights of this lane's 8 values in the first two boxes of a chunk, fetched one chunk
             // ahead: a load from global memory inside the chunk loop would stall every stage by its latency
             const int klane = (lane >> 3) * 64 + (lane & 7) * 8;
+            const int c0 = KS ? crank * L.n_chunks / ksplit : 0, c1 = KS ? (crank + 1) * L.n_chunks / ksplit : L.n_chunks;
             uint4 gnext[2] = {};
             if (EX && pro == IZB_PRO_RMSNORM) {
 #pragma unroll
                 for (int b = 0; b < 2; ++b)
-                    if (b < L.nb) gnext[b] = __ldg(reinterpret_cast<const uint4*>(norm_w + b * 256 + klane));
+                    if (b < L.nb) gnext[b] = __ldg(reinterpret_cast<const uint4*>(norm_w + (c0 * L.nb + b) * 256 + klane));
             }
-            for (int c = 0; c < L.n_chunks; ++c) {
+            for (int c = c0; c < c1; ++c) {
                 uint4 gcur[2] = {gnext[0], gnext[1]};
-                if (EX && pro == IZB_PRO_RMSNORM && c + 1 < L.n_chunks) {
+                if (EX && pro == IZB_PRO_RMSNORM && c + 1 < c1) {
 #pragma unroll
                     for (int b = 0; b < 2; ++b)
                         if (b < L.nb) gnext[b] = __ldg(reinterpret_cast<const uint4*>(norm_w + ((c + 1) * L.nb + b) * 256 + klane));
@@ -408,7 +432,7 @@ __global__ void __launch_bounds__(GV_THREADS)
                             } else {
                                 o = lds128(xaddr + static_cast<uint32_t>(x_half));
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) f[i] = f[i] / (1.0f + __expf(-f[i]));
+                                for (int i = 0; i < 8; ++i) f[i] *= rcp_approx(1.0f + __expf(-f[i]));  // silu: x * sigmoid(x)
                             }
                             const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
@@ -420,13 +444,13 @@ __global__ void __launch_bounds__(GV_THREADS)
                         }
                     }
                 }
-                if (EX && c == L.n_chunks - 1) {
+                if (EX && c == c1 - 1) {
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
                         float t = ss[m];
 #pragma unroll
                         for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, d);
-                        if (lane == 0) sh.rs[stage][m] = pro == IZB_PRO_RMSNORM ? rsqrtf(t / static_cast<float>(K) + eps) : 1.0f;
+                        if (lane == 0) sh.rs[stage][m] = t;
                     }
                 }
                 __syncwarp();
@@ -447,16 +471,21 @@ __global__ void __launch_bounds__(GV_THREADS)
     int stage = 0, it = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+    for (int tile = tile_first; tile < total_tiles; tile += tile_step, ++it) {
         const int p = find_problem(lite, n_cached, plist, n_probs, tile);
         const ProbLite L = p < n_cached ? lite[p] : lite_from(plist[p]);
         const int row0 = (tile - L.tile_start) * GV_TILE_ROWS;
 
-        float acc[MT], rsv[MT];
+        float acc[MT], rsv[MT];  // rsv: sum of squares of the token (fused RmsNorm), turned into 1 / rms at the end
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             acc[m] = 0.f;
-            rsv[m] = 1.0f;
+            rsv[m] = 0.f;
+        }
+        float inv_k = 0.f, eps = 0.f;  // inv_k > 0: the problem carries a fused RmsNorm
+        if (EX && L.extras && plist[p].prologue == IZB_PRO_RMSNORM) {
+            inv_k = 1.0f / static_cast<float>(plist[p].K);
+            eps = plist[p].eps;
         }
         // EX: bias and residual of this thread's row are fetched before the k loop, not at its end
         float addv[MT];
@@ -471,7 +500,8 @@ __global__ void __launch_bounds__(GV_THREADS)
                 addv[m] = bias + ((residual && m < L.M) ? __bfloat162float(residual[static_cast<long long>(m) * ld_res + row0 + row]) : 0.f);
         }
 
-        for (int c = 0; c < L.n_chunks; ++c) {
+        const int c0 = KS ? crank * L.n_chunks / ksplit : 0, c1 = KS ? (crank + 1) * L.n_chunks / ksplit : L.n_chunks;
+        for (int c = c0; c < c1; ++c) {
             if (ok && !mbar_wait_bounded(smem_u32(&sh.xready[stage]), phase, abort_flag)) ok = false;
             if (ok && !mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) ok = false;  // already complete
             if (ok) {
@@ -493,7 +523,7 @@ __global__ void __launch_bounds__(GV_THREADS)
                     }
                 }
             }
-            if (EX && ok && c == L.n_chunks - 1) {
+            if (EX && ok && c == c1 - 1) {
 #pragma unroll
                 for (int m = 0; m < MT; ++m) rsv[m] = sh.rs[stage][m];
             }
@@ -512,6 +542,34 @@ __global__ void __launch_bounds__(GV_THREADS)
             for (int m = 0; m < MT; ++m) red[m * GV_TILE_ROWS + row] = acc[m];
         }
         named_bar_sync(1, GV_CONSUMER_WARPS * 32);
+        if (kh == 0) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[m] += red[m * GV_TILE_ROWS + row];
+        }
+        if (KS && kh == 0) {
+            if (crank != 0) {
+                // hand this CTA's share to the first CTA of the cluster and be done with the tile
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    st_cluster_f32(cluster_map_shared(smem_u32(&sh.cl_red[((crank - 1) * MT + m) * GV_TILE_ROWS + row]), 0), acc[m]);
+                if (EX && row == 0) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) st_cluster_f32(cluster_map_shared(smem_u32(&sh.cl_ss[(crank - 1) * MT + m]), 0), rsv[m]);
+                }
+                mbar_arrive_cluster(cluster_map_shared(smem_u32(&sh.cl_bar), 0));
+                continue;
+            }
+            if (ok && !mbar_wait_cluster_bounded(smem_u32(&sh.cl_bar), 0u, abort_flag)) ok = false;
+            if (ok) {
+                for (int r = 0; r < ksplit - 1; ++r) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        acc[m] += sh.cl_red[(r * MT + m) * GV_TILE_ROWS + row];
+                        if (EX) rsv[m] += sh.cl_ss[r * MT + m];
+                    }
+                }
+            }
+        }
         if (kh == 0 && ok) {
             const int grow = row0 + row;
             if (grow < L.N) {
@@ -519,8 +577,8 @@ __global__ void __launch_bounds__(GV_THREADS)
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
                     if (m < L.M) {
-                        float v = acc[m] + red[m * GV_TILE_ROWS + row];
-                        if (EX) v = fmaf(v, rsv[m], addv[m]);
+                        float v = acc[m];
+                        if (EX) v = fmaf(v, inv_k > 0.f ? rsqrtf(fmaf(rsv[m], inv_k, eps)) : 1.0f, addv[m]);
                         else v += bias;
                         const long long idx = static_cast<long long>(m) * L.ldy + grow;
                         if (y_dtype == IZB_F32) static_cast<float*>(L.y)[idx] = v;
@@ -533,33 +591,52 @@ __global__ void __launch_bounds__(GV_THREADS)
     if (!ok && lane == 0) atomicExch(status, 5);
 }
 
-template <int FMT, int MT, bool EX>
-static int gemv_launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
-                           const SkinnyProblem& single) {
-    auto kern = skinny_gemv_kernel<FMT, MT, EX>;
+template <int FMT, int MT, bool EX, bool KS>
+static int gemv_prepare(const izb_ctx* ctx, const SkinnyPlanHeader& h) {
+    auto kern = skinny_gemv_kernel<FMT, MT, EX, KS>;
     static std::atomic<int> smem_set[16];
     const int dev_slot = ctx->device & 15;
     if (smem_set[dev_slot].load(std::memory_order_relaxed) < h.smem_bytes) {
         IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));
         smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);
     }
-    IZB_CUDA_TRY(launch_chained(ctx, kern, dim3(h.grid), dim3(GV_THREADS), h.smem_bytes, stream, dev, single, h.n_probs,
-                                h.total_tiles, h.n_stages, h.stage_bytes, h.xq_stage_bytes, h.red_bytes, h.lite_bytes, h.y_dtype,
-                                ctx->d_status + 4));
+    return IZB_OK;
+}
+
+template <int FMT, int MT, bool EX, bool KS>
+static int gemv_launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+                           const SkinnyProblem& single) {
+    auto kern = skinny_gemv_kernel<FMT, MT, EX, KS>;
+    const int rc = gemv_prepare<FMT, MT, EX, KS>(ctx, h);
+    if (rc != IZB_OK) return rc;
+    if (KS && (h.ksplit < 2 || h.ksplit > GV_MAX_KSPLIT || h.grid != h.total_tiles * h.ksplit)) return IZB_ERR_BAD_ARG;
+    IZB_CUDA_TRY(launch_chained_cluster(ctx, KS ? h.ksplit : 1, kern, dim3(h.grid), dim3(GV_THREADS), h.smem_bytes, stream, dev,
+                                        single, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes, h.xq_stage_bytes, h.red_bytes,
+                                        h.lite_bytes, h.y_dtype, KS ? h.ksplit : 1, ctx->d_status + 4));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
+}
+
+template <int FMT, int MT>
+static int gemv_launch_mt(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
+                          const SkinnyProblem& single) {
+    if constexpr (MT <= 2) {
+        if (h.ksplit > 1)
+            return h.extras ? gemv_launch_one<FMT, MT, true, true>(ctx, stream, h, dev, single)
+                            : gemv_launch_one<FMT, MT, false, true>(ctx, stream, h, dev, single);
+    }
+    if (h.ksplit > 1) return IZB_ERR_BAD_ARG;
+    return h.extras ? gemv_launch_one<FMT, MT, true, false>(ctx, stream, h, dev, single)
+                    : gemv_launch_one<FMT, MT, false, false>(ctx, stream, h, dev, single);
 }
 
 template <int FMT>
 static int gemv_launch_fmt(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev,
                            const SkinnyProblem& single) {
     switch (h.gemv) {
-        case 1: return h.extras ? gemv_launch_one<FMT, 1, true>(ctx, stream, h, dev, single)
-                                : gemv_launch_one<FMT, 1, false>(ctx, stream, h, dev, single);
-        case 2: return h.extras ? gemv_launch_one<FMT, 2, true>(ctx, stream, h, dev, single)
-                                : gemv_launch_one<FMT, 2, false>(ctx, stream, h, dev, single);
-        case 4: return h.extras ? gemv_launch_one<FMT, 4, true>(ctx, stream, h, dev, single)
-                                : gemv_launch_one<FMT, 4, false>(ctx, stream, h, dev, single);
+        case 1: return gemv_launch_mt<FMT, 1>(ctx, stream, h, dev, single);
+        case 2: return gemv_launch_mt<FMT, 2>(ctx, stream, h, dev, single);
+        case 4: return gemv_launch_mt<FMT, 4>(ctx, stream, h, dev, single);
         default: return IZB_ERR_BAD_ARG;
     }
 }
@@ -575,6 +652,66 @@ int skinny_gemv_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader
         case IZB_W_Q4_K: return gemv_launch_fmt<IZB_W_Q4_K>(ctx, stream, h, dev_probs, s);
         default: return IZB_ERR_BAD_ARG;
     }
+}
+
+// Can the device hold every cluster of the planned launch at once?  (Each cluster is one row tile and
+// the kernel does not loop over tiles when k is split.)
+template <int FMT, int MT, bool EX>
+static bool gemv_clusters_fit(const izb_ctx* ctx, const SkinnyPlanHeader& h) {
+    if (gemv_prepare<FMT, MT, EX, true>(ctx, h) != IZB_OK) return false;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(h.grid);
+    cfg.blockDim = dim3(GV_THREADS);
+    cfg.dynamicSmemBytes = h.smem_bytes;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = static_cast<unsigned>(h.ksplit);
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, skinny_gemv_kernel<FMT, MT, EX, true>, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return clusters * h.ksplit >= h.grid;
+}
+
+bool skinny_gemv_clusters_fit(const izb_ctx* ctx, const SkinnyPlanHeader& h) {
+    if (!ctx || h.ksplit < 2 || h.ksplit > GV_MAX_KSPLIT || h.gemv < 1 || h.gemv > 2) return false;
+    // the answer depends on a handful of plan fields only: remember the last few (a decode step asks
+    // the same four questions for every layer and token)
+    struct Seen { int dev, fmt, gemv, extras, ksplit, smem, grid; bool fit; };
+    static std::mutex mu;
+    static std::vector<Seen> seen;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const Seen& e : seen)
+            if (e.dev == ctx->device && e.fmt == h.fmt && e.gemv == h.gemv && e.extras == h.extras && e.ksplit == h.ksplit &&
+                e.smem == h.smem_bytes && e.grid == h.grid)
+                return e.fit;
+    }
+    int prev = 0;
+    if (cudaGetDevice(&prev) != cudaSuccess || cudaSetDevice(ctx->device) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    bool fit = false;
+    if (h.fmt == IZB_W_Q8_0) {
+        fit = h.gemv == 1 ? (h.extras ? gemv_clusters_fit<IZB_W_Q8_0, 1, true>(ctx, h) : gemv_clusters_fit<IZB_W_Q8_0, 1, false>(ctx, h))
+                          : (h.extras ? gemv_clusters_fit<IZB_W_Q8_0, 2, true>(ctx, h) : gemv_clusters_fit<IZB_W_Q8_0, 2, false>(ctx, h));
+    } else if (h.fmt == IZB_W_Q4_K) {
+        fit = h.gemv == 1 ? (h.extras ? gemv_clusters_fit<IZB_W_Q4_K, 1, true>(ctx, h) : gemv_clusters_fit<IZB_W_Q4_K, 1, false>(ctx, h))
+                          : (h.extras ? gemv_clusters_fit<IZB_W_Q4_K, 2, true>(ctx, h) : gemv_clusters_fit<IZB_W_Q4_K, 2, false>(ctx, h));
+    }
+    (void)cudaSetDevice(prev);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (seen.size() >= 64) seen.erase(seen.begin());
+        seen.push_back({ctx->device, h.fmt, h.gemv, h.extras, h.ksplit, h.smem_bytes, h.grid, fit});
+    }
+    return fit;
 }
 
 }  // namespace izb

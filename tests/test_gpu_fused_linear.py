@@ -177,3 +177,33 @@ def test_routes_that_do_not_fuse_decline(cuda):
     with pytest.raises(IzbError) as e:
         ops.LinearGroup([ops.linear_args(x, q, "q8_0", n, k, y, prologue="rms_norm", norm_weight=g, norm_eps=EPS)], cuda)
     assert e.value.status == -2
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+def test_k_split_over_a_cluster_matches_the_single_cta_walk(cuda, fmt, monkeypatch):
+    """A lone small projection splits the k chunks of each row tile over a cluster of CTAs; the sums must
+    agree with the unsplit kernel to fp32 reordering, for every cluster size and with all fusions on."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(950)
+    for m, n, k in ((1, 1024, 3072), (2, 1024, 2048), (1, 70, 4096), (2, 4096, 1024), (1, 64, 768)):
+        raw, wf = make_weight_np(fmt, n, k, rng)
+        wd = upload_weight(fmt, raw, cuda)
+        x = dev_bf16(bf16_np(rng.normal(0, 1.5, (m, k))), cuda)
+        gu = dev_bf16(bf16_np(rng.normal(0, 1.5, (m, 2 * k))), cuda)
+        g = dev_bf16(bf16_np(rng.normal(1.0, 0.3, k)), cuda)
+        res = dev_bf16(bf16_np(rng.normal(0, 1.0, (m, n))), cuda)
+
+        def run_all():
+            return [ops.linear(x, wd, fmt, n=n, k=k, out_dtype=torch.float32),
+                    ops.linear(x, wd, fmt, n=n, k=k, out_dtype=torch.float32, prologue="rms_norm", norm_weight=g, norm_eps=EPS,
+                               residual=res),
+                    ops.linear(gu, wd, fmt, n=n, k=k, out_dtype=torch.float32, prologue="silu_mul", residual=res)]
+        monkeypatch.setenv("IZB_SKINNY_GEMV_KSPLIT", "1")
+        base = run_all()
+        for cap in (2, 4, 8):
+            monkeypatch.setenv("IZB_SKINNY_GEMV_KSPLIT", str(cap))
+            for got, want in zip(run_all(), base):
+                ops.Context.get(0).check()
+                scale = float(want.abs().max())
+                assert float((got - want).abs().max()) <= 1e-5 * scale, (fmt, m, n, k, cap)
+    ops.Context.get(0).check()
