@@ -747,6 +747,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="sharded decode workloads: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--attention-cases", action="store_true",
                     help="profiler captures: run only the decode-attention cases and exit")
+    ap.add_argument("--decode-token-cases", action="store_true",
+                    help="only the whole-greedy-token cases (eager steps, then a CUDA graph replayed)")
     ap.add_argument("--gemm-case", default=None,
                     help="profiler captures: run only this prefill / encoder GEMM shape (a name from gemm_cases) and exit")
     ap.add_argument("--layers", type=int, default=None,
@@ -757,6 +759,10 @@ def main():
     if args.attention_cases:
         import torch
         print(json.dumps({"attention_cases": measure_attention_cases(torch.device("cuda", 0))}), flush=True)
+        return
+    if args.decode_token_cases:
+        import torch
+        print(json.dumps({"decode_token_cases": measure_decode_token_cases(torch.device("cuda", 0))}), flush=True)
         return
     if args.gemm_case:
         import torch
