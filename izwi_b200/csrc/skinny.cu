@@ -244,6 +244,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const SkinnyProblem* plist = probs ? probs : &single;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) {
@@ -256,8 +257,9 @@ __global__ void __launch_bounds__(SK_THREADS)
     // dynamic shared memory: [descriptor cache][k-split reduction buffer][stage ring]
     ProbLite* lite = reinterpret_cast<ProbLite*>(dyn_smem);
     const int n_cached = min(n_probs, lite_bytes / static_cast<int>(sizeof(ProbLite)));
-    for (int i = threadIdx.x; i < n_cached; i += blockDim.x) lite[i] = lite_from(plist[i]);
+    for (int i = threadIdx.x; i < n_cached; i += blockDim.x) lite[i] = lite_from(plist[i]);  // the plan: written by the host
     __syncthreads();
+    pdl_wait();  // activations and the output buffer belong to the kernels before this one
 
     volatile int* abort_flag = &sh.abort_flag;
     const uint32_t stage0 = smem_u32(dyn_smem) + static_cast<uint32_t>(lite_bytes + red_bytes);
@@ -455,9 +457,8 @@ int launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, con
         IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));
         smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);
     }
-    kern<<<h.grid, SK_THREADS, h.smem_bytes, stream>>>(dev, single, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes,
-                                                       h.red_bytes, h.lite_bytes, h.y_dtype, ctx->d_status);
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(launch_chained(ctx, kern, dim3(h.grid), dim3(SK_THREADS), h.smem_bytes, stream, dev, single, h.n_probs,
+                                h.total_tiles, h.n_stages, h.stage_bytes, h.red_bytes, h.lite_bytes, h.y_dtype, ctx->d_status));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
