@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // 16-byte global stores need an aligned base and row stride
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (p.ldy * (f32_out ? 4 : 2)) % 16 == 0;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) {
             mbar_init(smem_u32(&sh.full[s]), 1);
@@ -116,17 +117,18 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         mbar_init(smem_u32(&sh.drain), 1);
         sh.abort_flag = 0;
         mbar_fence_init();
-        // grouped: m-tile prefix over the expert segments
-        if (p.seg_offsets != nullptr) {
-            int acc = 0;
-            for (int e = 0; e < p.n_experts; ++e) {
-                sh.tile_prefix[e] = acc;
-                acc += (p.seg_offsets[e + 1] - p.seg_offsets[e] + GT_BM - 1) / GT_BM;
-            }
-            sh.tile_prefix[p.n_experts] = acc;
-        }
     }
     if (warp == 1) tc_alloc(smem_u32(&sh.tmem_base), 512);
+    pdl_wait();  // the expert offsets, the activations and the output buffer belong to the kernels before this one
+    if (threadIdx.x == 0 && p.seg_offsets != nullptr) {
+        // grouped: m-tile prefix over the expert segments
+        int acc = 0;
+        for (int e = 0; e < p.n_experts; ++e) {
+            sh.tile_prefix[e] = acc;
+            acc += (p.seg_offsets[e + 1] - p.seg_offsets[e] + GT_BM - 1) / GT_BM;
+        }
+        sh.tile_prefix[p.n_experts] = acc;
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -434,8 +436,7 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     }
     const long long tiles_bound = m_tiles * ((n_out + out_cols - 1) / out_cols);
     const int grid = static_cast<int>(std::min<long long>(tiles_bound, ctx->sm_count));
-    gemm_tc_kernel<<<grid, GT_THREADS, smem_bytes, stream>>>(p, n_stages, ctx->d_status + 1);
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(launch_chained(ctx, gemm_tc_kernel, dim3(grid), dim3(GT_THREADS), smem_bytes, stream, p, n_stages, ctx->d_status + 1));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }

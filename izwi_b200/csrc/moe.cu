@@ -16,6 +16,8 @@ constexpr int MOE_MAX_TOPK = 32;
 // One warp per token.  Each lane keeps experts lane, lane+32, ...; k rounds of warp arg-max.
 __global__ void moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int* __restrict__ idx,
                                 float* __restrict__ wts) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_block) {
@@ -68,6 +70,8 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int T, int E, 
 // ascending pair order.  No block depends on another.
 __global__ void moe_permute_kernel(const int* __restrict__ idx, int pairs, int E, int* __restrict__ offsets,
                                    int* __restrict__ perm, int* __restrict__ inv) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     __shared__ int warp_sums[32];
     __shared__ int base_s, count_s, running_s;
     const int e = blockIdx.x;
@@ -128,6 +132,8 @@ __global__ void moe_permute_kernel(const int* __restrict__ idx, int pairs, int E
 // x_perm[r] = x[perm[r] / k], 16 bytes per thread.
 __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ perm, int k, int rows,
                                   int vec_per_row, long long ldx_vec, uint4* __restrict__ out) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     const long long total = static_cast<long long>(rows) * vec_per_row;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -139,6 +145,8 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __rest
 // y[t] = sum over slots (ascending) of w[t, slot] * yp[inv[t*k + slot]], fp32 accumulate, 8 columns per thread.
 __global__ void moe_combine_kernel(const uint4* __restrict__ yp, const int* __restrict__ inv, const float* __restrict__ wts,
                                    int T, int k, int vec_per_row, uint4* __restrict__ y) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
     const long long total = static_cast<long long>(T) * vec_per_row;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -178,10 +186,9 @@ int32_t izb_moe_topk(izb_ctx* ctx, izb_stream stream, const void* logits, int64_
     if (!logits || !idx_out || !weights_out) return IZB_ERR_BAD_ARG;
     if (!izb_aligned(logits, 4) || !izb_aligned(idx_out, 4) || !izb_aligned(weights_out, 4)) return IZB_ERR_BAD_ARG;
     const int threads = 128;
-    moe_topk_kernel<<<blocks_for(ctx, T * 32, threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const float*>(logits), static_cast<int>(T), static_cast<int>(E), top_k, static_cast<int*>(idx_out),
-        static_cast<float*>(weights_out));
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(izb::launch_chained(ctx, moe_topk_kernel, dim3(blocks_for(ctx, T * 32, threads)), dim3(threads), 0,
+                                     static_cast<cudaStream_t>(stream), static_cast<const float*>(logits), static_cast<int>(T),
+                                     static_cast<int>(E), top_k, static_cast<int*>(idx_out), static_cast<float*>(weights_out)));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
@@ -192,10 +199,10 @@ int32_t izb_moe_permute(izb_ctx* ctx, izb_stream stream, const void* idx, int64_
     if (E > 65535 || pairs > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     if (!offsets_out || (pairs > 0 && (!idx || !perm_out || !inv_out))) return IZB_ERR_BAD_ARG;
     // 1024 threads: the in-order pass costs three block barriers per 1024 pairs
-    moe_permute_kernel<<<static_cast<int>(E), pairs >= 4096 ? 1024 : 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const int*>(idx), static_cast<int>(pairs), static_cast<int>(E), static_cast<int*>(offsets_out),
-        static_cast<int*>(perm_out), static_cast<int*>(inv_out));
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(izb::launch_chained(ctx, moe_permute_kernel, dim3(static_cast<int>(E)), dim3(pairs >= 4096 ? 1024 : 256), 0,
+                                     static_cast<cudaStream_t>(stream), static_cast<const int*>(idx), static_cast<int>(pairs),
+                                     static_cast<int>(E), static_cast<int*>(offsets_out), static_cast<int*>(perm_out),
+                                     static_cast<int*>(inv_out)));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
@@ -207,10 +214,10 @@ int32_t izb_moe_gather(izb_ctx* ctx, izb_stream stream, const void* x, int64_t l
     if (!x || !perm || !x_perm) return IZB_ERR_BAD_ARG;
     if (H % 8 != 0 || ldx % 8 != 0 || !izb_aligned(x, 16) || !izb_aligned(x_perm, 16)) return IZB_ERR_UNSUPPORTED;
     const int threads = 256;
-    moe_gather_kernel<<<blocks_for(ctx, rows * (H / 8), threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(x), static_cast<const int*>(perm), top_k, static_cast<int>(rows),
-        static_cast<int>(H / 8), ldx / 8, static_cast<uint4*>(x_perm));
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(izb::launch_chained(ctx, moe_gather_kernel, dim3(blocks_for(ctx, rows * (H / 8), threads)), dim3(threads), 0,
+                                     static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x), static_cast<const int*>(perm),
+                                     top_k, static_cast<int>(rows), static_cast<int>(H / 8), static_cast<long long>(ldx / 8),
+                                     static_cast<uint4*>(x_perm)));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
@@ -234,10 +241,10 @@ int32_t izb_moe_combine(izb_ctx* ctx, izb_stream stream, const void* y_perm, con
     if (!y_perm || !inv || !weights || !y) return IZB_ERR_BAD_ARG;
     if (H % 8 != 0 || !izb_aligned(y_perm, 16) || !izb_aligned(y, 16)) return IZB_ERR_UNSUPPORTED;
     const int threads = 256;
-    moe_combine_kernel<<<blocks_for(ctx, T * (H / 8), threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(y_perm), static_cast<const int*>(inv), static_cast<const float*>(weights),
-        static_cast<int>(T), top_k, static_cast<int>(H / 8), static_cast<uint4*>(y));
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(izb::launch_chained(ctx, moe_combine_kernel, dim3(blocks_for(ctx, T * (H / 8), threads)), dim3(threads), 0,
+                                     static_cast<cudaStream_t>(stream), static_cast<const uint4*>(y_perm),
+                                     static_cast<const int*>(inv), static_cast<const float*>(weights), static_cast<int>(T), top_k,
+                                     static_cast<int>(H / 8), static_cast<uint4*>(y)));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
