@@ -240,6 +240,7 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const SkinnyProblem* plist = probs ? probs : &single;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < w_stages; ++s) {
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();  // activations and the output buffer belong to the kernels before this one
 
     volatile int* abort_flag = &sh.abort_flag;
     const uint32_t tmem_base = sh.tmem_base;
@@ -492,12 +494,13 @@ int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& 
         smem_set[which][slot].store(h.smem_bytes, std::memory_order_relaxed);
     }
     if (which == 0)
-        skinny_tc_kernel<IZB_W_Q8_0><<<h.grid, STC_THREADS, h.smem_bytes, stream>>>(
-            dev_probs, s, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes, h.x_stages, h.lite_bytes, mp, h.y_dtype, ctx->d_status + 3);
+        IZB_CUDA_TRY(launch_chained(ctx, skinny_tc_kernel<IZB_W_Q8_0>, dim3(h.grid), dim3(STC_THREADS), h.smem_bytes, stream, dev_probs,
+                                    s, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes, h.x_stages, h.lite_bytes, mp, h.y_dtype,
+                                    ctx->d_status + 3));
     else
-        skinny_tc_kernel<IZB_W_Q4_K><<<h.grid, STC_THREADS, h.smem_bytes, stream>>>(
-            dev_probs, s, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes, h.x_stages, h.lite_bytes, mp, h.y_dtype, ctx->d_status + 3);
-    IZB_CUDA_TRY(cudaGetLastError());
+        IZB_CUDA_TRY(launch_chained(ctx, skinny_tc_kernel<IZB_W_Q4_K>, dim3(h.grid), dim3(STC_THREADS), h.smem_bytes, stream, dev_probs,
+                                    s, h.n_probs, h.total_tiles, h.n_stages, h.stage_bytes, h.x_stages, h.lite_bytes, mp, h.y_dtype,
+                                    ctx->d_status + 3));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
