@@ -14,6 +14,8 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = [(4096, 1024), (1024, 3072), (130, 768), (1, 256), (200, 5120)]
 EPS = 1e-6
+
+
 def dev_bf16(a, cuda):
     return torch.from_numpy(np.ascontiguousarray(a)).to(cuda).to(torch.bfloat16)
 
