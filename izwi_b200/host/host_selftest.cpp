@@ -132,6 +132,20 @@ static void gpu_tests() {
     auto op = download(yp), o1 = download(y1), o2 = download(y2);
     EXPECT(op[0] == o1[0] && op[1] == o1[1] && op[2] == o2[0]);
     EXPECT(packed.diagnostics().quantized_projection_count == 1);
+    // the residual add carried inside a one-token quantised projection == projection, then add (one bf16 step)
+    {
+        std::vector<float> resv = {0.5f, -1.25f};
+        auto resd = upload(resv, 1, 2, 2);
+        DeviceBuffer yf(2 * 2);
+        Qwen3Projection::Fusion fu;
+        fu.residual = resd->get();
+        Qwen3Projection::quantized(t1).forward(ctx, nullptr, xq->get(), 1, yf.get(), 0, 0, nullptr, 0, IZB_EPI_NONE, &fu);
+        ctx.check_device();
+        auto of = download(yf);
+        for (int c = 0; c < 2; ++c) EXPECT(std::fabs(of[c] - (o1[c] + resv[c])) <= 2e-2f * std::fmax(1.0f, std::fabs(o1[c] + resv[c])));
+        EXPECT(izb_linear_fusion_max_tokens(IZB_W_Q8_0) >= 1 && izb_linear_fusion_max_tokens(IZB_W_BF16) == 0);
+        EXPECT(throws_with([&] { q.forward(ctx, nullptr, xin->get(), 2, yq.get(), 0, 0, nullptr, 0, IZB_EPI_NONE, &fu); }, "unsupported"));
+    }
     QTensor wide{t2.data, 1, 512, IZB_W_Q8_0};
     EXPECT(throws_with([&] { packed_qmatmul_from_qtensors({t1, wide}); }, "input mismatch: expected 256, got 512"));
     QTensor other{t2.data, 1, 256, IZB_W_Q4_K};
@@ -176,6 +190,9 @@ int main(int argc, char** argv) {
         std::printf("FAIL unexpected exception: %s\n", e.what());
         return 2;
     }
+    // sizes of the structs that cross the C ABI, for bindings in other languages to compare theirs with
+    std::printf("abi: izb_linear_args=%zu izb_moe_args=%zu izb_gguf_tensor=%zu\n", sizeof(izb_linear_args), sizeof(izb_moe_args),
+                sizeof(izb_gguf_tensor));
     std::printf(g_failed ? "host_selftest: %d failure(s)\n" : "host_selftest: ok\n", g_failed);
     return g_failed ? 1 : 0;
 }

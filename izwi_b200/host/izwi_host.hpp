@@ -160,11 +160,29 @@ class Qwen3Projection {
         return {0, 0, 1};
     }
 
+    // What a decode layer does around a projection, carried inside it (one or two tokens over Q8_0 / Q4_K
+    // weights: m <= izb_linear_fusion_max_tokens(wfmt); any other shape throws "unsupported").
+    struct Fusion {
+        int32_t prologue = IZB_PRO_NONE;     // IZB_PRO_RMSNORM: x is the un-normalised stream; IZB_PRO_SILU_MUL: x is [m, 2 in] = gate | up
+        const void* norm_weight = nullptr;   // bf16 [in]
+        float norm_eps = 0.f;
+        const void* residual = nullptr;      // bf16 [m, ld_residual], added to y
+        int64_t ld_residual = 0;             // 0: out
+    };
+
     // y[M, out] = x[M, in] . W^T (+ bias); x and y are bf16 device pointers with row strides ldx / ldy.
     void forward(const Context& ctx, cudaStream_t stream, const void* x, int64_t m, void* y, int64_t ldx = 0,
                  int64_t ldy = 0, void* workspace = nullptr, size_t workspace_bytes = 0,
-                 int32_t epilogue = IZB_EPI_NONE) const {
+                 int32_t epilogue = IZB_EPI_NONE, const Fusion* fusion = nullptr) const {
         izb_linear_args a{};
+        if (fusion) {
+            a.prologue = fusion->prologue;
+            a.norm_weight = fusion->norm_weight;
+            a.norm_eps = fusion->norm_eps;
+            a.residual = fusion->residual;
+            a.ld_residual = fusion->residual ? (fusion->ld_residual ? fusion->ld_residual : out_) : 0;
+            if (!ldx && fusion->prologue == IZB_PRO_SILU_MUL) ldx = 2 * in_;
+        }
         a.wfmt = wfmt_;
         a.y_dtype = IZB_BF16;
         a.x = x;
