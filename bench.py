@@ -175,30 +175,61 @@ def time_steps(fn, steps: int, world: int):
     return max_over_ranks(e0.elapsed_time(e1), world), t0, t1
 
 
+def time_blocks(fn, steps: int, world: int, min_ms: float, max_blocks: int = 400):
+    """Blocks of exactly `steps` calls each (timed as time_steps does), repeated until the blocks add up
+    to `min_ms` of device time, so that a short `--steps` does not leave the number hanging on a
+    millisecond of measurement.  Returns (median block ms, all block ms, wall start, wall end); every
+    rank sees the same max-over-ranks block times and therefore stops after the same block."""
+    blocks, t_first, t_last = [], None, None
+    while True:
+        ms, t0, t1 = time_steps(fn, steps, world)
+        blocks.append(ms)
+        t_first = t0 if t_first is None else t_first
+        t_last = t1
+        if sum(blocks) >= min_ms or len(blocks) >= max_blocks:
+            break
+    return statistics.median(blocks), blocks, t_first, t_last
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def oracle_lib():
+    """The C restatement (CPU baseline leg and on-the-spot checker only).  The OpenMP team is sized here
+    from the cores this process may run on: a launcher such as torch.distributed.run exports
+    OMP_NUM_THREADS=1, which would otherwise leave the baseline on one core."""
     import subprocess
     so = ROOT / "oracle" / "liboracle_c.so"
     if not so.exists():
         subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True, capture_output=True)
     lib = ctypes.CDLL(str(so))
     lib.orc_num_threads.restype = ctypes.c_int
+    lib.orc_set_num_threads.argtypes = [ctypes.c_int]
+    lib.orc_set_num_threads(host_cores())
     return lib
 
 
 class CpuStack:
-    """The same stack on the host: raw weight bytes (or fp32 for bf16) + fp32 activations, run by the C port."""
+    """The same stack on the host: raw weight bytes (or fp32 for bf16) + fp32 activations, run by the C
+    port.  `layers` restricts it to some layers (the checker of the secondary cases)."""
 
-    def __init__(self, stack):
+    def __init__(self, stack, layers=None):
         import numpy as np
-        import torch
         self.lib = oracle_lib()
         self.fmt, self.m = stack.fmt, stack.m
-        self.items = []
-        for wl, al in zip(stack.weights, stack.acts):
-            for (_, n, k), w, x in zip(stack.shape.projections, wl, al):
+        self.items, self.outs = [], []
+        for li, (wl, al, ol) in enumerate(zip(stack.weights, stack.acts, stack.outs)):
+            if layers is not None and li not in layers:
+                continue
+            for (_, n, k), w, x, y in zip(stack.shape.projections, wl, al, ol):
                 wh = (w.float() if self.fmt == "bf16" else w).cpu().numpy()
                 xh = x.float().cpu().numpy()
                 self.items.append((np.ascontiguousarray(wh), np.ascontiguousarray(xh), np.empty((self.m, n), np.float32), n, k))
+                self.outs.append(y)
         self.cores = self.lib.orc_num_threads()
 
     def step(self):
@@ -211,6 +242,15 @@ class CpuStack:
                 self.lib.orc_qlinear_f32(0 if self.fmt == "q8_0" else 1, xh.ctypes.data_as(vp), wh.ctypes.data_as(vp),
                                          yh.ctypes.data_as(vp), ctypes.c_int64(self.m), ctypes.c_int64(n),
                                          ctypes.c_int64(k))
+
+    def parity(self):
+        """Worst max-relative error (to the row's largest magnitude) and cosine of the device outputs of the
+        projections held here against one CPU step."""
+        self.step()
+        worst = Parity()
+        for (wh, xh, yh, n, k), yd in zip(self.items, self.outs):
+            worst.add(yd.float().cpu().numpy(), yh)
+        return worst
 
     def timed(self, budget_s: float, max_steps: int = 400):
         self.step()  # warm-up (page in, thread pool)
@@ -225,6 +265,54 @@ class CpuStack:
         return n, dt
 
 
+class Parity:
+    """Accumulates the two gated figures over several outputs: max |got - want| relative to the largest
+    |want| of the row, and the cosine of the flattened outputs.  Gate: rel <= 2e-2, cosine >= 0.9999."""
+    GATE = "rel<=2e-2, cos>=0.9999"
+
+    def __init__(self):
+        self.rel, self.cos, self.n = 0.0, 1.0, 0
+
+    def add(self, got, want):
+        import numpy as np
+        got = np.asarray(got, dtype=np.float64).reshape(-1, got.shape[-1])
+        want = np.asarray(want, dtype=np.float64).reshape(-1, want.shape[-1])
+        denom = np.abs(want).max(axis=1, keepdims=True)
+        self.rel = max(self.rel, float((np.abs(got - want) / np.where(denom == 0, 1, denom)).max()))
+        nrm = np.linalg.norm(got) * np.linalg.norm(want)
+        self.cos = min(self.cos, float((got * want).sum() / nrm) if nrm > 0 else 1.0)
+        self.n += 1
+
+    def result(self, checked: str, **extra):
+        ok = self.rel <= 2e-2 and self.cos >= 0.9999 and all(v is not False for v in extra.values())
+        return {"max_rel_err": round(self.rel, 6), "min_cosine": round(self.cos, 7), "outputs_checked": self.n,
+                "checked": checked, "gate": self.GATE, "pass": bool(ok), **extra}
+
+
+def bf16_round_np(x):
+    """fp32/fp64 values rounded to the nearest bf16 (ties to even), returned as float64."""
+    import numpy as np
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return r.view(np.float32).astype(np.float64).reshape(np.shape(x))
+
+
+def host64(t):
+    """A device tensor as a float64 host array."""
+    return t.detach().float().cpu().numpy().astype("float64")
+
+
+def act_np(name, v):
+    """The fused epilogue functions in float64 (erf GELU, SiLU)."""
+    import math
+    import numpy as np
+    if name == "gelu":
+        return 0.5 * v * (1.0 + np.vectorize(math.erf)(v * 0.7071067811865476))
+    if name == "silu":
+        return v / (1.0 + np.exp(-v))
+    return v
+
+
 LAYERS_OVERRIDE = None  # --layers: a shorter stack, for profiler captures only
 
 
@@ -234,8 +322,9 @@ def make_stack(workload: str, device):
     return wl.make_linear_stack(wl.QWEN3_0_6B, fmt, m, device, WEIGHT_SEED, ACT_SEED, layers=LAYERS_OVERRIDE)
 
 
-def measure_case(workload: str, device, steps: int, warmup: int, peak: float):
-    """Short device-resident measurement of one more configuration (not the headline line)."""
+def measure_case(workload: str, device, steps: int, warmup: int, peak: float, check: bool = True):
+    """Short device-resident measurement of one more configuration (not the headline line), checked on
+    its first and last layer against the CPU port."""
     import torch
     from izwi_b200 import workloads as wl
     stack = make_stack(workload, device)
@@ -249,6 +338,9 @@ def measure_case(workload: str, device, steps: int, warmup: int, peak: float):
     out = {"workload": workload, "ms_per_step": round(per, 5), "tokens_per_s": round(stack.m / (per * 1e-3), 1),
            "hbm_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak, 4),
            "tflops": round(stack.flops / (per * 1e-3) / 1e12, 2)}
+    if check:
+        last = stack.shape.layers - 1
+        out["parity"] = CpuStack(stack, layers={0, last}).parity().result(f"layers 0 and {last} vs CPU port")
     del group, stack
     torch.cuda.empty_cache()
     return out
@@ -276,10 +368,28 @@ def _time_call(fn, iters: int, warmup: int = 3):
     return e0.elapsed_time(e1) / iters
 
 
+def sampled_rows(m: int):
+    return sorted({0, m // 3, m // 2, m - 1})
+
+
+def linear_rows_ref(x, w, bias, rows, epilogue=None):
+    """float64 product of the sampled activation rows with the whole weight on the host."""
+    import numpy as np
+    v = host64(x[rows]) @ host64(w).T
+    if bias is not None:
+        v = v + host64(bias)[None, :]
+    if epilogue == "swiglu":
+        half = v.shape[1] // 2
+        return act_np("silu", v[:, :half]) * v[:, half:]
+    return act_np(epilogue, v)
+
+
 def measure_gemm_cases(device, only=None, iters=20):
     """Prefill (Qwen3-8B shape, M = 2048) and ASR-encoder GEMMs through izb_linear: TFLOP/s against the
-    measured bf16 tensor peak.  Operands are a few hundred MB, so successive calls do not reuse L2 for
-    the large ones; the small ones are reported as measured (L2-resident, as they would be in a layer loop)."""
+    measured bf16 tensor peak.  The single-shape entries re-run one operand set (the large ones exceed
+    L2, the small ones are L2-resident as they would be inside a layer loop); the `-stack` entries run
+    every layer of the model with its own weights, so each weight comes from HBM once per pass.  Every
+    entry is checked on sampled rows against a float64 product on the host."""
     import torch
     from izwi_b200 import ops
     peak, kind = load_tensor_peak()
@@ -308,12 +418,42 @@ def measure_gemm_cases(device, only=None, iters=20):
         y = torch.empty(m, n // 2 if epi == "swiglu" else n, device=device, dtype=torch.bfloat16)
         ms = _time_call(lambda: ops.linear(x, w, bias=b, out=y, epilogue=epi), iters)
         tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        rows = sampled_rows(m)
+        par = Parity()
+        par.add(host64(y[rows]), linear_rows_ref(x, w, b, rows, epi))
         out.append({"workload": name, "M": m, "N": n, "K": k, "ms": round(ms, 4), "tflops": round(tf, 1),
-                    "tensor_frac": round(tf / peak, 4), "peak_kind": f"of {kind} {peak}"})
+                    "tensor_frac": round(tf / peak, 4), "peak_kind": f"of {kind} {peak}",
+                    "parity": par.result(f"{len(rows)} sampled rows x all columns vs float64 on the host")})
         del x, w, y
+    if only is None:
+        out += measure_stack_gemm_cases(device, peak, kind)
     ops.Context.get(device.index).check()
     torch.cuda.empty_cache()
     return out
+
+
+def measure_stack_gemm_cases(device, peak, kind):
+    """Whole-model passes (every layer with its own weights, HBM-cold): Qwen3-8B prefill M = 2048,
+    Whisper-large-v3 and FastConformer encoder GEMMs at batch 1 and 32."""
+    import torch
+    out = []
+    tp = TpStack(None, 1, 0, device)
+    out.append(stack_entry("qwen3-8b-prefill-m2048-stack", tp.case(2048, 5, 3), peak, kind))
+    del tp
+    torch.cuda.empty_cache()
+    for name in ("whisper-large-v3", "fastconformer"):
+        enc = EncStack(name, 1, 0, device)
+        for batch in (1, 32):
+            out.append(stack_entry(f"{name}-b{batch}-stack", enc.case(batch, 5, 3), peak, kind))
+        del enc
+        torch.cuda.empty_cache()
+    return out
+
+
+def stack_entry(name, case, peak, kind):
+    return {"workload": name, "ms": case["ms_per_step"], "tflops": case["tflops_total"],
+            "tensor_frac": round(case["tflops_total"] / peak, 4), "peak_kind": f"of {kind} {peak}",
+            "launches_per_pass": case["launches_per_step"], "parity": case["parity"]}
 
 
 def measure_attention_cases(device):
@@ -381,10 +521,13 @@ def measure_decode_token_cases(device):
         for l in layers:
             l.fused_linear = fused
             l.fusion_max_tokens = ops.linear_fusion_max_tokens("q8_0") if fused else 0
+        # the cache contents depend on the context length only, so the fused and unfused builds of one
+        # length see the same model state and must pick the same token
+        cgen = torch.Generator(device=device).manual_seed(7000 + ctx_len)
         caches = [decoder.KvCache(1, shape.kv_heads, ctx_len + 8, shape.head_dim, device) for _ in layers]
         for c in caches:
-            c.k.normal_(generator=gen)
-            c.v.normal_(generator=gen)
+            c.k.normal_(generator=cgen)
+            c.v.normal_(generator=cgen)
         tok = torch.tensor([17], device=device)
         cos, sin = model.rope_tables(ctx_len, 1)
         launches0 = ops.Context.get(device.index).launch_count
@@ -410,6 +553,38 @@ def measure_decode_token_cases(device):
     return out
 
 
+def moe_parity(x, y, idx, wts, logits_fn, w_router, router_bias, w_gate_up, w_down, top_k, tokens=None):
+    """Checks one MoE layer's routing and output on the host.  Routing: the indices of every token must
+    equal, bit for bit, the top-k (descending logit, lowest expert id among equals) of the fp32 router
+    logits the library produced, and those logits must agree with a float64 product.  Output: sampled
+    tokens against float64 expert FFNs (SiLU-multiply rounded to bf16 as stored, expert outputs rounded
+    to bf16, weighted sum in ascending slot order).  x, y, idx, wts are this rank's tokens; the expert
+    weights are the full [E, ...] tensors."""
+    import numpy as np
+    t = x.shape[0]
+    logits = logits_fn().float().cpu().numpy()
+    order = np.argsort(-logits, axis=1, kind="stable")[:, :top_k].astype(np.int32)
+    idx_h = idx.cpu().numpy()
+    exact = bool(np.array_equal(order, idx_h))
+    par = Parity()
+    ref_logits = host64(x) @ host64(w_router).T + (0 if router_bias is None else host64(router_bias)[None, :])
+    par.add(logits, ref_logits)
+    inter = w_gate_up.shape[1] // 2
+    rows = sampled_rows(t) if tokens is None else tokens
+    want = np.zeros((len(rows), x.shape[1]))
+    wts_h = wts.float().cpu().numpy().astype(np.float64)
+    for i, r in enumerate(rows):
+        xr = host64(x[r])
+        for slot in range(top_k):
+            e = int(idx_h[r, slot])
+            gu = host64(w_gate_up[e]) @ xr
+            hid = bf16_round_np(act_np("silu", gu[:inter]) * gu[inter:])
+            want[i] += wts_h[r, slot] * bf16_round_np(host64(w_down[e]) @ hid)
+    par.add(host64(y[rows]), want)
+    return par.result(f"router logits of {t} tokens and the layer output of {len(rows)} sampled tokens vs float64 on the host",
+                      routing_indices_bit_exact=exact)
+
+
 def measure_moe_cases(device):
     """One Qwen3-30B-A3B-shaped MoE layer (H 2048, I 768, 128 experts, top-8, router bias ~N(0, 0.5))
     through izb_moe_forward at T = 1, 64, 4096; rotating over 3 layers' weights (3.6 GB) so the
@@ -424,6 +599,7 @@ def measure_moe_cases(device):
     layers = [moe.MoeLayer(rn(e, h, std=h ** -0.5), rn(e, std=0.5), rn(e, 2 * i, h, std=0.02), rn(e, h, i, std=0.02), k)
               for _ in range(3)]
     out = []
+    ctx = ops.Context.get(device.index)
     for t in (1, 64, 4096):
         x = rn(t, h)
         state = {"i": 0}
@@ -431,19 +607,300 @@ def measure_moe_cases(device):
         def step():
             layers[state["i"] % 3].forward(x)
             state["i"] += 1
+        l0 = ctx.launch_count
+        step()
+        per_layer = ctx.launch_count - l0
+        state["i"] = 0
         ms = _time_call(step, 30)
-        _, _, idx, _ = layers[0].forward(x)
+        lay = layers[0]
+        y, logits, idx, wts = lay.forward(x)
         touched = int(torch.unique(idx).numel())
         flops = 2.0 * t * k * 3 * i * h + 2.0 * t * e * h
         wbytes = touched * 3 * i * h * 2 + e * h * 2
         out.append({"workload": f"qwen3-30b-a3b-moe-layer-T{t}", "ms": round(ms, 4), "experts_touched": touched,
                     "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "tensor_frac": round(flops / (ms * 1e-3) / 1e12 / peak_tf, 4),
                     "weight_gbs": round(wbytes / (ms * 1e-3) / 1e9, 1), "hbm_frac_of_measured": round(wbytes / (ms * 1e-3) / 1e9 / peak_bw, 4),
-                    "kernels_per_layer": 8})
-    ops.Context.get(device.index).check()
+                    "kernels_per_layer": int(per_layer),
+                    "parity": moe_parity(x, y, idx, wts, lambda: logits, lay.w_router, lay.router_bias, lay.w_gate_up,
+                                         lay.w_down, k)})
+    ctx.check()
     del layers
     torch.cuda.empty_cache()
     return out
+
+
+# ----------------------------------------------------------------------------------------------
+# sharded workloads: tensor-parallel Qwen3-8B, expert-parallel Qwen3-30B-A3B, batch-parallel encoders.
+# Every rank draws the same full tensors from one seed and keeps its shard, so any rank can check its
+# outputs against the unsharded weights.  world = 1 is the baseline point of the scaling curve.
+# ----------------------------------------------------------------------------------------------
+SHARDED = {
+    # name: (kind, parameter)
+    "qwen3-8b-tp-prefill-m2048": ("tp", 2048),
+    "qwen3-8b-tp-decode-m1": ("tp", 1), "qwen3-8b-tp-decode-m8": ("tp", 8), "qwen3-8b-tp-decode-m32": ("tp", 32),
+    "qwen3-30b-a3b-ep-t4096": ("ep", 4096), "qwen3-30b-a3b-ep-t64": ("ep", 64),
+    "whisper-large-v3-b32": ("whisper-large-v3", 32), "fastconformer-b32": ("fastconformer", 32),
+}
+# the ones every default run reports under `sharded_cases`
+SHARDED_DEFAULT = ["qwen3-8b-tp-prefill-m2048", "qwen3-8b-tp-decode-m1", "qwen3-8b-tp-decode-m32",
+                   "qwen3-30b-a3b-ep-t4096", "qwen3-30b-a3b-ep-t64", "whisper-large-v3-b32", "fastconformer-b32"]
+ENCODERS = {
+    # name: (layers, d_model, ffn, frames per utterance, biases, activation, feed-forwards per layer)
+    "whisper-large-v3": (32, 1280, 5120, 1500, True, "gelu", 1),
+    "fastconformer": (24, 1024, 4096, 375, False, "silu", 2),
+}
+
+
+def _timed_case(step, steps, warmup, world, device_index, graph=False):
+    """Warm-up, optional CUDA-graph capture of the step, `steps` timed calls (max over ranks)."""
+    import torch
+    from izwi_b200 import ops
+    ctx = ops.Context.get(device_index)
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count
+    step()
+    launches = ctx.launch_count - l0
+    run = step
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        run = g.replay
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+    ms, _, _ = time_steps(run, steps, world)
+    ctx.check()
+    return ms / steps, int(launches)
+
+
+class TpStack:
+    """The 36-layer Qwen3-8B linear stack, column/row split over `world` ranks."""
+
+    def __init__(self, comm, world, rank, device, use_graph=True):
+        import torch
+        from izwi_b200 import parallel
+        from izwi_b200 import workloads as wl
+        self.comm, self.world, self.rank, self.device, self.use_graph = comm, world, rank, device, use_graph
+        self.shape = shape = wl.QWEN3_8B
+        gen = torch.Generator(device=device).manual_seed(3)
+        rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
+        (_, n_qkv, h), (_, _, k_o), (_, n_gu, _), (_, _, k_d) = shape.projections
+        self.layers, self.full0 = [], None
+        for li in range(shape.layers):
+            full = (rn(n_qkv, h, std=0.02), rn(h, k_o, std=0.02), rn(n_gu, h, std=0.02), rn(h, k_d, std=0.02))
+            self.layers.append(parallel.TpDecoderLayer.from_full(comm, shape, *full, world, rank) if world > 1
+                               else parallel.TpDecoderLayer(None, *full))
+            if li == 0 and rank == 0:
+                self.full0 = full          # the unsharded first layer, for the check
+            del full
+
+    def case(self, m, steps, warmup):
+        import numpy as np
+        import torch
+        from izwi_b200 import parallel
+        shape, world, rank = self.shape, self.world, self.rank
+        (_, n_qkv, h), (_, _, k_o), _, _ = shape.projections
+        gen = torch.Generator(device=self.device).manual_seed(300 + m)
+        rn = lambda *s: torch.randn(*s, device=self.device, generator=gen).to(torch.bfloat16)  # noqa: E731
+        x_a, x_o_full, x_m = rn(m, h), rn(m, k_o), rn(m, h)
+        lo, hi = parallel.tp_row_split_cols(k_o, world, rank)
+        x_o = x_o_full[:, lo:hi].contiguous()
+
+        def step():
+            for layer in self.layers:
+                layer.forward(x_a, x_o, x_m)
+        per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index, graph=self.use_graph and m <= 32)
+        flops = 2.0 * m * shape.layers * shape.weights_per_layer
+        out = {"value": round(m / (per_ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(per_ms, 5), "n_gpus": world,
+               "scaling": "strong", "launches_per_step": launches, "tflops_total": round(flops / (per_ms * 1e-3) / 1e12, 2),
+               "weights_gbs_per_gpu": round(shape.layers * shape.weights_per_layer * 2 / world / (per_ms * 1e-3) / 1e9, 1),
+               "collective": "none (one GPU)" if world == 1 else self.layers[0].collective_name(m),
+               "parallelism": f"tp{world}: column-split QKV and gate/up, row-split O and down, 2 sums per layer"}
+        qkv, o, down = self.layers[0].forward(x_a, x_o, x_m)      # every rank: the sums are collective
+        torch.cuda.synchronize()
+        if rank == 0:
+            w_qkv, w_o, w_gu, w_d = self.full0
+            rows = sampled_rows(m)
+            mine = torch.from_numpy(parallel.tp_qkv_rows(shape.q_heads, shape.kv_heads, shape.head_dim, world, rank)).to(self.device)
+            par = Parity()
+            par.add(host64(qkv[rows]), linear_rows_ref(x_a, w_qkv[mine], None, rows))
+            par.add(host64(o[rows]), linear_rows_ref(x_o_full, w_o, None, rows))
+            hidden = bf16_round_np(linear_rows_ref(x_m, w_gu, None, rows, "swiglu"))
+            par.add(host64(down[rows]), hidden @ host64(w_d).T)
+            out["parity"] = par.result(f"layer 0, {len(rows)} sampled token rows: this rank's QKV columns, the summed O and "
+                                       "down outputs vs float64 products of the unsharded weights on the host")
+        return out
+
+
+class EpStack:
+    """Eight Qwen3-30B-A3B-shaped MoE layers, experts in contiguous blocks over `world` ranks."""
+    H, I, E, K, LAYERS = 2048, 768, 128, 8, 8
+
+    def __init__(self, comm, world, rank, device, max_tokens=4096, nccl=False):
+        import torch
+        from izwi_b200 import moe, parallel
+        self.comm, self.world, self.rank, self.device, self.nccl = comm, world, rank, device, nccl
+        gen = torch.Generator(device=device).manual_seed(4)
+        rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
+        lo_e, hi_e = parallel.ep_expert_range(self.E, world, rank)
+        self.layers, self.full0 = [], None
+        for li in range(self.LAYERS):
+            wr, br = rn(self.E, self.H, std=self.H ** -0.5), rn(self.E, std=0.5)
+            wgu, wd = rn(self.E, 2 * self.I, self.H, std=0.02), rn(self.E, self.H, self.I, std=0.02)
+            if world > 1:
+                self.layers.append(parallel.EpMoeLayer(comm, wr, br, wgu[lo_e:hi_e].clone(), wd[lo_e:hi_e].clone(), self.E, self.K))
+            else:
+                self.layers.append(moe.MoeLayer(wr, br, wgu, wd, self.K))
+            if li == 0 and rank == 0:
+                self.full0 = (wr, br, wgu, wd)
+            del wgu, wd
+        if world > 1 and not nccl:
+            # rows travel through NVLink peer memory with device-side counts (no host read per layer)
+            comm.enable_peer_ep(self.E, self.H, (max_tokens + world - 1) // world, self.K)
+
+    def case(self, t_total, steps, warmup):
+        import torch
+        from izwi_b200 import ops, parallel
+        world, rank = self.world, self.rank
+        gen = torch.Generator(device=self.device).manual_seed(400 + t_total)
+        x_all = torch.randn(t_total, self.H, device=self.device, generator=gen).to(torch.bfloat16)
+        lo_t, hi_t = parallel.split_range(t_total, world, rank)
+        x = x_all[lo_t:hi_t].contiguous()
+
+        def step():
+            for layer in self.layers:
+                layer.forward(x)
+        per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index)
+        flops = 2.0 * t_total * self.K * 3 * self.I * self.H * self.LAYERS
+        out = {"value": round(t_total / (per_ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(per_ms, 5),
+               "n_gpus": world, "scaling": "strong", "launches_per_step": launches, "layers": self.LAYERS,
+               "tflops_total": round(flops / (per_ms * 1e-3) / 1e12, 2),
+               "collective": "none (one GPU)" if world == 1 else (
+                   "counts all-gather + izb_ep_alltoall over NCCL, sizes read by the host" if self.nccl
+                   else "izb_ep_dispatch / izb_ep_return: rows stored into the owner's buffer over NVLink peer memory"),
+               "parallelism": f"ep{world}: {self.E // world} experts per rank, tokens split, one exchange each way per layer"}
+        res = self.layers[0].forward(x)                            # every rank: the exchange is collective
+        torch.cuda.synchronize()
+        if rank == 0 and hi_t > lo_t:
+            wr, br, wgu, wd = self.full0
+            y, idx, wts = (res[0], res[2], res[3]) if world == 1 else res
+            out["parity"] = moe_parity(x, y, idx, wts, lambda: ops.linear(x, wr, bias=br, out_dtype=torch.float32), wr, br,
+                                       wgu, wd, self.K)
+        return out
+
+
+class EncStack:
+    """QKV, O and feed-forward GEMMs of an ASR encoder, utterances split over ranks, weights replicated."""
+
+    def __init__(self, name, world, rank, device):
+        import torch
+        self.name, self.world, self.rank, self.device = name, world, rank, device
+        self.n_layers, self.d, self.ff, self.frames, has_bias, self.act, self.n_ffn = ENCODERS[name]
+        gen = torch.Generator(device=device).manual_seed(5)
+        rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
+        d, ff = self.d, self.ff
+        self.layers = []
+        for _ in range(self.n_layers):
+            ws = {"qkv": rn(3 * d, d, std=0.02), "o": rn(d, d, std=0.02), "fc1": rn(ff, d, std=0.02), "fc2": rn(d, ff, std=0.02)}
+            bs = {kk: (rn(v.shape[0], std=0.1) if has_bias else None) for kk, v in ws.items()}
+            self.layers.append((ws, bs))
+
+    def case(self, batch, steps, warmup):
+        import torch
+        from izwi_b200 import ops, parallel
+        world, rank, d, ff = self.world, self.rank, self.d, self.ff
+        lo_b, hi_b = parallel.batch_split(batch, world, rank)
+        m = (hi_b - lo_b) * self.frames
+        gen = torch.Generator(device=self.device).manual_seed(500 + batch)
+        x_all = torch.randn(batch * self.frames, d, device=self.device, generator=gen).to(torch.bfloat16)
+        x = x_all[lo_b * self.frames: hi_b * self.frames].contiguous() if m else x_all[:1]
+        mk = lambda n: torch.empty(max(m, 1), n, device=self.device, dtype=torch.bfloat16)  # noqa: E731
+        bufs = {"qkv": mk(3 * d), "o": mk(d), "ff": mk(ff), "d": mk(d)}
+
+        def layer_forward(ws, bs):
+            ops.linear(x, ws["qkv"], bias=bs["qkv"], out=bufs["qkv"])
+            ops.linear(x, ws["o"], bias=bs["o"], out=bufs["o"])
+            for _ in range(self.n_ffn):
+                ops.linear(x, ws["fc1"], bias=bs["fc1"], out=bufs["ff"], epilogue=self.act)
+                ops.linear(bufs["ff"], ws["fc2"], bias=bs["fc2"], out=bufs["d"])
+
+        def step():
+            if m:
+                for ws, bs in self.layers:
+                    layer_forward(ws, bs)
+        per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index)
+        flops = 2.0 * batch * self.frames * self.n_layers * (4 * d * d + self.n_ffn * 2 * d * ff)
+        out = {"value": round(batch / (per_ms * 1e-3), 2), "unit": "utterances/s", "ms_per_step": round(per_ms, 5),
+               "n_gpus": world, "scaling": "strong", "launches_per_step": launches, "batch": batch, "frames": self.frames,
+               "tflops_total": round(flops / (per_ms * 1e-3) / 1e12, 2), "collective": "none (independent utterances)",
+               "parallelism": f"batch split over {world} ranks, weights replicated"}
+        if rank == 0 and m:
+            ws, bs = self.layers[0]
+            layer_forward(ws, bs)
+            torch.cuda.synchronize()
+            rows = sampled_rows(m)
+            par = Parity()
+            par.add(host64(bufs["qkv"][rows]), linear_rows_ref(x, ws["qkv"], bs["qkv"], rows))
+            par.add(host64(bufs["o"][rows]), linear_rows_ref(x, ws["o"], bs["o"], rows))
+            hid = bf16_round_np(linear_rows_ref(x, ws["fc1"], bs["fc1"], rows, self.act))
+            par.add(host64(bufs["ff"][rows]), hid)
+            want = hid @ host64(ws["fc2"]).T + (0 if bs["fc2"] is None else host64(bs["fc2"])[None, :])
+            par.add(host64(bufs["d"][rows]), want)
+            out["parity"] = par.result(f"layer 0, {len(rows)} sampled frames: QKV, O, FFN1 + activation, FFN2 vs float64 on the host")
+        return out
+
+
+def run_sharded_cases(names, world, rank, device, comm, steps=None, warmup=3, nccl_ep=False, use_graph=True):
+    """Runs the named sharded workloads in this process group, sharing the weights of one model between
+    its cases.  Returns the list of result dicts (parity fields filled on rank 0)."""
+    import torch
+    out = []
+    kinds = [SHARDED[n][0] for n in names]
+    if "tp" in kinds:
+        tp = TpStack(comm, world, rank, device, use_graph=use_graph)
+        for n in names:
+            if SHARDED[n][0] == "tp":
+                m = SHARDED[n][1]
+                out.append({"workload": n, **tp.case(m, steps or (10 if m > 32 else 20), warmup)})
+        del tp
+        torch.cuda.empty_cache()
+    if "ep" in kinds:
+        ep = EpStack(comm, world, rank, device, max_tokens=max(SHARDED[n][1] for n in names if SHARDED[n][0] == "ep"),
+                     nccl=nccl_ep)
+        for n in names:
+            if SHARDED[n][0] == "ep":
+                out.append({"workload": n, **ep.case(SHARDED[n][1], steps or 20, warmup)})
+        del ep
+        torch.cuda.empty_cache()
+    for n in names:
+        if SHARDED[n][0] in ENCODERS:
+            enc = EncStack(SHARDED[n][0], world, rank, device)
+            out.append({"workload": n, **enc.case(SHARDED[n][1], steps or 10, warmup)})
+            del enc
+            torch.cuda.empty_cache()
+    order = {n: i for i, n in enumerate(names)}
+    return sorted(out, key=lambda c: order[c["workload"]])
+
+
+def make_comm(world, local):
+    """The communicator of the sharded workloads: NCCL for set-up and fallback, sums through NVLink peer
+    memory (one-shot up to 1 MB, two-shot up to 64 MB)."""
+    if world == 1:
+        return None
+    from izwi_b200 import parallel
+    comm = parallel.Comm(local)
+    comm.enable_peer_allreduce(64 << 20)
+    return comm
+
+
+def headline_config(workload, fmt, m, layers, weight_bytes, world):
+    return {"workload": workload, "weights": fmt, "tokens_per_step": m, "layers": layers, "projections_per_layer": 4,
+            "weight_bytes": weight_bytes, "launch": "one grouped persistent launch per step",
+            "l2": f"inputs larger than L2 ({weight_bytes / 1e6:.0f} MB streamed per step vs 126 MB)",
+            "multi_gpu": "replicas only (the 0.6B decode stack does not shard)" if world > 1 else "single GPU"}
 
 
 def run_ours(args):
@@ -465,13 +922,13 @@ def run_ours(args):
     sampler = ClockSampler(local)
     sampler.start()
     launches0 = ctx.launch_count
-    ms, t0, t1 = time_steps(group.launch, args.steps, world)
-    launches = ctx.launch_count - launches0
+    block_ms, blocks, t0, t1 = time_blocks(group.launch, args.steps, world, args.min_ms)
+    launches = (ctx.launch_count - launches0) // len(blocks)
     sampler.stop_flag.set()
     sampler.join(timeout=2)
     ctx.check()  # raises if any bounded device-side wait gave up
 
-    per_ms = ms / args.steps
+    per_ms = block_ms / args.steps
     tokens_per_s = world * m / (per_ms * 1e-3)
     achieved = stack.algorithmic_bytes / (per_ms * 1e-3) / 1e9
 
@@ -489,8 +946,8 @@ def run_ours(args):
     e2e_steps = max(3, min(args.steps, 2000))
     for _ in range(3):
         e2e_step()
-    e2e_ms, _, _ = time_steps(e2e_step, e2e_steps, world)
-    e2e_tokens = world * m / (e2e_ms / e2e_steps * 1e-3)
+    e2e_block, e2e_blocks, _, _ = time_blocks(e2e_step, e2e_steps, world, args.min_ms / 2)
+    e2e_tokens = world * m / (e2e_block / e2e_steps * 1e-3)
     ctx.check()
 
     line = {
@@ -498,11 +955,12 @@ def run_ours(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(per_ms, 6),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "weights": fmt, "tokens_per_step": m,
-                   "layers": stack.shape.layers, "projections_per_layer": 4,
-                   "weight_bytes": stack.weight_bytes, "launch": "one grouped persistent launch per step",
-                   "l2": f"inputs larger than L2 ({stack.weight_bytes / 1e6:.0f} MB streamed per step vs 126 MB)",
-                   "multi_gpu": "replicas only (the 0.6B decode stack does not shard)" if world > 1 else "single GPU"},
+        "config": headline_config(args.workload, fmt, m, stack.shape.layers, stack.weight_bytes, world),
+        "timing": {"what": f"median of {len(blocks)} blocks of exactly {args.steps} steps each (CUDA events, barrier and "
+                           "synchronise around every block, max over ranks), repeated until the blocks add up to "
+                           f"{args.min_ms:.0f} ms of device time",
+                   "blocks": len(blocks), "block_ms_min": round(min(blocks), 5), "block_ms_median": round(block_ms, 5),
+                   "block_ms_max": round(max(blocks), 5), "timed_ms_total": round(sum(blocks), 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
                      "frac_of_nominal_8000": round(achieved / 8000.0, 4),
@@ -510,199 +968,88 @@ def run_ours(args):
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)},
         "e2e": {"value": round(e2e_tokens, 2), "unit": "tokens/s",
                 "h2d_bytes_per_step": h_in.numel() * 2, "d2h_bytes_per_step": h_out.numel() * 2,
-                "steps": e2e_steps},
+                "steps": e2e_steps, "blocks": len(e2e_blocks)},
         "gpu_launches": int(launches),
         "clocks": sampler.summary(t0, t1),
     }
 
-    if rank == 0 and world == 1:
-        if not args.no_cpu_baseline:
-            cpu = CpuStack(stack)
-            # parity of the timed path against the checker, on the spot
-            import numpy as np
-            cpu.step()
-            worst_rel, worst_cos = 0.0, 1.0
-            flat_out = [y for ol in stack.outs for y in ol]
-            for (wh, xh, yh, n, k), yd in list(zip(cpu.items, flat_out))[:8]:
-                g = yd.float().cpu().numpy()
-                denom = np.abs(yh).max(axis=1, keepdims=True)
-                worst_rel = max(worst_rel, float((np.abs(g - yh) / np.where(denom == 0, 1, denom)).max()))
-                worst_cos = min(worst_cos, float((g * yh).sum() / (np.linalg.norm(g) * np.linalg.norm(yh))))
-            line["parity"] = {"max_rel_err": round(worst_rel, 6), "min_cosine": round(worst_cos, 7),
-                              "checked": "first 2 layers vs CPU port", "gate": "rel<=2e-2, cos>=0.9999"}
+    if rank == 0 and not args.no_cpu_baseline:
+        # parity of the timed path against the checker, on the spot, over every projection of the step
+        cpu = CpuStack(stack)
+        line["parity"] = cpu.parity().result(f"all {len(cpu.items)} projections of the step vs CPU port")
+        if world == 1:
             n, dt = cpu.timed(args.cpu_seconds)
             line["cpu_baseline"] = {"value": round(n * m / dt, 3), "unit": "tokens/s", "cores": cpu.cores,
                                     "kind": "port",
                                     "sample": f"{n} full decode steps of the same stack (dequantise + fp32 dot, "
                                               f"OpenMP over weight rows), {dt:.1f} s"}
-            del cpu
-        if not args.no_cases:
-            del group
-            cases = []
-            for wname in WORKLOADS:
-                if wname == args.workload:
-                    continue
-                cases.append(measure_case(wname, device, args.case_steps, 5, peak))
-            line["cases"] = cases
-            line["gemm_cases"] = measure_gemm_cases(device)
-            line["moe_cases"] = measure_moe_cases(device)
-            line["attention_cases"] = measure_attention_cases(device)
-            line["decode_token_cases"] = measure_decode_token_cases(device)
+        del cpu
+    del group, stack, h_in, h_out
+    torch.cuda.empty_cache()
+    if not args.no_sharded:
+        # the configurations that do shard, at this world size, in the same process group
+        comm = make_comm(world, local)
+        line["sharded_cases"] = run_sharded_cases(SHARDED_DEFAULT, world, rank, device, comm)
+        if comm is not None:
+            comm.close()
+    if rank == 0 and world == 1 and not args.no_cases:
+        cases = []
+        for wname in WORKLOADS:
+            if wname == args.workload:
+                continue
+            cases.append(measure_case(wname, device, args.case_steps, 5, peak, check=not args.no_cpu_baseline))
+        line["cases"] = cases
+        line["gemm_cases"] = measure_gemm_cases(device)
+        line["moe_cases"] = measure_moe_cases(device)
+        line["attention_cases"] = measure_attention_cases(device)
+        line["decode_token_cases"] = measure_decode_token_cases(device)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
+        dist.barrier()
         dist.destroy_process_group()
 
 
-# ----------------------------------------------------------------------------------------------
-# sharded workloads (run with --gpus N under torch.distributed.run; N = 1 gives the baseline point)
-# ----------------------------------------------------------------------------------------------
-SHARDED = {
-    # name: (kind, parameter)
-    "qwen3-8b-tp-decode-m1": ("tp", 1), "qwen3-8b-tp-decode-m8": ("tp", 8), "qwen3-8b-tp-decode-m32": ("tp", 32),
-    "qwen3-8b-tp-prefill-m2048": ("tp", 2048),
-    "qwen3-30b-a3b-ep-t64": ("ep", 64), "qwen3-30b-a3b-ep-t4096": ("ep", 4096),
-    "fastconformer-b32": ("enc", ("fastconformer", 24, 1024, 4096, 375, 32, False, "silu")),
-    "whisper-large-v3-b32": ("enc", ("whisper", 32, 1280, 5120, 1500, 32, True, "gelu")),
-}
-
-
 def run_sharded(args):
+    """One sharded workload on its own (`--workload <name> --gpus N` under torch.distributed.run)."""
     import torch
-    from izwi_b200 import moe, ops, parallel
-    from izwi_b200 import workloads as wl
-
+    from izwi_b200 import ops
     world, rank, local = dist_setup(args.gpus)
     device = torch.device("cuda", local)
-    kind, param = SHARDED[args.workload]
-    comm = parallel.Comm(local) if world > 1 else None
-    if comm is not None and kind == "tp":
-        # sums go through NVLink peer memory, not NCCL: one-shot up to 1 MB, two-shot up to 64 MB
-        comm.enable_peer_allreduce(1 << 20 if args.nccl_ep else 64 << 20)
-    gen = torch.Generator(device=device).manual_seed(3)       # same stream of weights on every rank
-    rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
-    cfg = {"workload": args.workload, "l2": "weights larger than L2"}
-    flops = 0.0
-
-    if kind == "tp":
-        shape, m = wl.QWEN3_8B, param
-        (_, n_qkv, h), (_, _, k_o), (_, n_gu, _), (_, _, k_d) = shape.projections
-        layers = []
-        for _ in range(shape.layers):
-            full = (rn(n_qkv, h, std=0.02), rn(h, k_o, std=0.02), rn(n_gu, h, std=0.02), rn(h, k_d, std=0.02))
-            layers.append(parallel.TpDecoderLayer.from_full(comm, shape, *full, world, rank) if world > 1
-                          else parallel.TpDecoderLayer(None, *full))
-            del full
-        lo, hi = parallel.tp_row_split_cols(k_o, world, rank)
-        x_a, x_o, x_m = rn(m, h), rn(m, hi - lo), rn(m, h)
-
-        def step():
-            for layer in layers:
-                layer.forward(x_a, x_o, x_m)
-        units, unit_name = m, "tokens/s"
-        flops = 2.0 * m * shape.layers * shape.weights_per_layer
-        cfg.update(model="qwen3-8b linear stack", tokens_per_step=m, layers=shape.layers,
-                   parallelism=f"tp{world}: column-split QKV and gate/up, row-split O and down, 2 all-reduces per layer")
-    elif kind == "ep":
-        t_total, n_layers = param, 8
-        h, inter, e, k = 2048, 768, 128, 8
-        lo_e, hi_e = parallel.ep_expert_range(e, world, rank)
-        layers = []
-        for _ in range(n_layers):
-            wr, br = rn(e, h, std=h ** -0.5), rn(e, std=0.5)
-            wgu, wd = rn(e, 2 * inter, h, std=0.02), rn(e, h, inter, std=0.02)
-            if world > 1:
-                layers.append(parallel.EpMoeLayer(comm, wr, br, wgu[lo_e:hi_e].clone(), wd[lo_e:hi_e].clone(), e, k))
-            else:
-                layers.append(moe.MoeLayer(wr, br, wgu, wd, k))
-            del wgu, wd
-        lo_t, hi_t = parallel.split_range(t_total, world, rank)
-        x = rn(t_total, h)[lo_t:hi_t].contiguous()
-        if world > 1 and not args.nccl_ep:
-            # rows travel through NVLink peer memory with device-side counts (no host read per layer)
-            comm.enable_peer_ep(e, h, (t_total + world - 1) // world, k)
-
-        def step():
-            for layer in layers:
-                layer.forward(x)
-        units, unit_name = t_total, "tokens/s"
-        flops = 2.0 * t_total * k * 3 * inter * h * n_layers
-        cfg.update(model="qwen3-30b-a3b MoE FFN layers", tokens_per_step=t_total, layers=n_layers,
-                   note="8 of the 48 layers (each layer is 1.2 GB of expert weights)",
-                   parallelism=f"ep{world}: {e // world} experts per rank, tokens split, dispatch and return each way "
-                               + ("over NCCL with host-side counts" if args.nccl_ep or world == 1 else "over peer memory"))
-    else:
-        name, n_layers, d, ff, frames, batch, has_bias, act = param
-        lo_b, hi_b = parallel.batch_split(batch, world, rank)
-        m = (hi_b - lo_b) * frames
-        layers = []
-        for _ in range(n_layers):
-            ws = {"qkv": rn(3 * d, d, std=0.02), "o": rn(d, d, std=0.02), "fc1": rn(ff, d, std=0.02), "fc2": rn(d, ff, std=0.02)}
-            bs = {kk: (rn(v.shape[0], std=0.1) if has_bias else None) for kk, v in ws.items()}
-            layers.append((ws, bs))
-        n_ffn = 2 if name == "fastconformer" else 1                   # two macaron feed-forwards per layer
-        x = rn(max(m, 1), d)
-        bufs = {"qkv": torch.empty(max(m, 1), 3 * d, device=device, dtype=torch.bfloat16),
-                "d": torch.empty(max(m, 1), d, device=device, dtype=torch.bfloat16),
-                "ff": torch.empty(max(m, 1), ff, device=device, dtype=torch.bfloat16)}
-
-        def step():
-            if m == 0:
-                return
-            for ws, bs in layers:
-                ops.linear(x, ws["qkv"], bias=bs["qkv"], out=bufs["qkv"])
-                ops.linear(x, ws["o"], bias=bs["o"], out=bufs["d"])
-                for _ in range(n_ffn):
-                    ops.linear(x, ws["fc1"], bias=bs["fc1"], out=bufs["ff"], epilogue=act)
-                    ops.linear(bufs["ff"], ws["fc2"], bias=bs["fc2"], out=bufs["d"])
-        units, unit_name = batch, "utterances/s"
-        flops = 2.0 * batch * frames * n_layers * (4 * d * d + n_ffn * 2 * d * ff)
-        cfg.update(model=f"{name} encoder GEMMs (QKV, O, FFN)", batch=batch, frames=frames, layers=n_layers,
-                   parallelism=f"batch split over {world} ranks, weights replicated, no collective")
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
-    if kind == "tp" and param <= 32 and not args.no_graph:
-        # the decode step is a fixed sequence of launches: replay it as one CUDA graph
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        eager_step, step = step, graph.replay
-        for _ in range(3):
-            step()
-        torch.cuda.synchronize()
-        cfg["launch"] = "CUDA graph replay of the whole step"
+    comm = make_comm(world, local)
     sampler = ClockSampler(local)
     sampler.start()
-    ctx = ops.Context.get(local)
-    launches0 = ctx.launch_count
-    ms, t0, t1 = time_steps(step, args.steps, world)
-    launches = ctx.launch_count - launches0
+    t0 = time.perf_counter()
+    case = run_sharded_cases([args.workload], world, rank, device, comm, steps=args.steps, warmup=args.warmup,
+                             nccl_ep=args.nccl_ep, use_graph=not args.no_graph)[0]
+    t1 = time.perf_counter()
     sampler.stop_flag.set()
     sampler.join(timeout=2)
-    ctx.check()
-    per_ms = ms / args.steps
-    peak_tf, kind_tf = load_tensor_peak()
-    line = {"metric": f"{args.workload}_{unit_name.split('/')[0]}_per_s", "value": round(units / (per_ms * 1e-3), 2),
-            "unit": unit_name, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(per_ms, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": cfg,
-            "tflops_total": round(flops / (per_ms * 1e-3) / 1e12, 1),
-            "tensor_frac_per_gpu": round(flops / (per_ms * 1e-3) / 1e12 / world / peak_tf, 4),
-            "gpu_launches": int(launches), "clocks": sampler.summary(t0, t1)}
+    peak_tf, _ = load_tensor_peak()
+    unit = case["unit"]
+    line = {"metric": f"{args.workload}_{unit.split('/')[0]}_per_s", "value": case["value"], "unit": unit, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": case["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "l2": "weights larger than L2", "parallelism": case["parallelism"],
+                       "collective": case["collective"]},
+            "tflops_total": case["tflops_total"],
+            "tensor_frac_per_gpu": round(case["tflops_total"] / world / peak_tf, 4),
+            "gpu_launches": case["launches_per_step"] * args.steps, "parity": case.get("parity"),
+            "clocks": sampler.summary(t0, t1)}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
         comm.close()
+        dist.barrier()
         dist.destroy_process_group()
 
 
 def run_reference(args):
-    """The reference arm: the CPU restatement of the same stack on the host cores (the reference's
-    own Candle CPU path cannot be built without a Rust toolchain)."""
+    """The reference arm: the CPU restatement of the same stack on all the host cores this process may
+    use (the reference's own Candle CPU path cannot be built without a Rust toolchain).  Under a
+    multi-rank launch rank 0 alone runs it; the other ranks exit."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -711,9 +1058,10 @@ def run_reference(args):
     fmt, m = WORKLOADS[args.workload]
     stack = make_stack(args.workload, dev)
     cpu = CpuStack(stack)
-    weight_bytes = stack.weight_bytes
+    weight_bytes, layers = stack.weight_bytes, stack.shape.layers
     del stack
-    for _ in range(max(1, min(args.warmup, 3))):
+    warmup = max(3, min(args.warmup, 200))
+    for _ in range(warmup):
         cpu.step()
     steps = max(1, min(args.steps, 50))  # each step is a full CPU decode step; bounded so the run ends in minutes
     t0 = time.perf_counter()
@@ -721,12 +1069,12 @@ def run_reference(args):
         cpu.step()
     dt = time.perf_counter() - t0
     v = round(steps * m / dt, 3)
-    sample = f"{steps} full decode steps of the stack on the host cores"
+    sample = f"{steps} full decode steps of the stack on {cpu.cores} host threads"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": round(dt / steps * 1e3, 3),
+        "steps": steps, "warmup": warmup, "ms_per_step": round(dt / steps * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "weights": fmt, "tokens_per_step": m, "weight_bytes": weight_bytes},
+        "config": headline_config(args.workload, fmt, m, layers, weight_bytes, args.gpus),
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cpu.cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -743,6 +1091,9 @@ def main():
     ap.add_argument("--case-steps", type=int, default=300)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cases", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sharded_cases block of the default run")
+    ap.add_argument("--min-ms", type=float, default=500.0,
+                    help="repeat the timed block of --steps steps until this much device time has been measured")
     ap.add_argument("--nccl-ep", action="store_true", help="expert-parallel workloads: exchange rows with NCCL instead of peer memory")
     ap.add_argument("--no-graph", action="store_true", help="sharded decode workloads: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--attention-cases", action="store_true",

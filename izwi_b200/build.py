@@ -9,12 +9,12 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libizwi_b200.so"
 
-NVCC_FLAGS = [
+COMPILE_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
-    "-shared",
 ]
+OBJ_DIR = PKG_DIR / "csrc" / ".obj"
 
 
 HOST_SELFTEST = PKG_DIR / "host" / "host_selftest"
@@ -46,23 +46,39 @@ def needs_build() -> bool:
     return any(p.stat().st_mtime > built for p in deps if p.is_file())
 
 
+def _run(cmd: list[str], env: dict) -> str:
+    proc = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+    return proc.stderr
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """Every source file is compiled to an object of its own (in parallel; an object newer than its
+    source and every header is reused), then the objects are linked into the shared library."""
     if not force and not needs_build():
         return LIB_PATH
+    from concurrent.futures import ThreadPoolExecutor
     nvcc = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, sources()), "-ldl"]
     env = dict(os.environ)
     # the image exports CC/CXX pointing at a gcc wrapper without its runtime specs; use the system one
     env.pop("CC", None)
     env.pop("CXX", None)
-    proc = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
+    OBJ_DIR.mkdir(exist_ok=True)
+    headers = [p for p in CSRC.glob("*") if p.suffix in (".cuh", ".h", ".hpp")] + [PKG_DIR.parent / "include" / "izwi_b200.h"]
+    newest_header = max(p.stat().st_mtime for p in headers)
+    jobs, objects = [], []
+    for src in sources():
+        obj = OBJ_DIR / (src.name + ".o")
+        objects.append(obj)
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, newest_header):
+            cmd = [nvcc, *COMPILE_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", "-o", str(obj), str(src)]
+            jobs.append(cmd)
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        logs = list(pool.map(lambda c: _run(c, env), jobs))
     if verbose:
-        print(proc.stderr)
+        print("\n".join(logs))
+    _run([nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objects), "-ldl"], env)
     return LIB_PATH
 
 

@@ -244,6 +244,17 @@ class TpDecoderLayer:
         return cls(comm, w_qkv[rows].contiguous(), w_o[:, olo:ohi].contiguous(), w_gate_up[gu].contiguous(),
                    w_down[:, dlo:dhi].contiguous())
 
+    def collective_name(self, m: int) -> str:
+        """Which sum the O and down outputs of `m` token rows go through."""
+        comm = self.comm
+        if comm is None:
+            return "none"
+        nbytes = m * self.w_o.shape[0] * 2
+        if getattr(comm, "ar", None) and nbytes <= comm.ar_max:
+            return ("izb_ar_allreduce over NVLink peer memory, "
+                    + ("one-shot (8-byte {payload, sequence} stores)" if nbytes <= (1 << 20) else "two-shot (reduce-scatter + all-gather)"))
+        return "izb_tp_allreduce (NCCL)"
+
     def forward(self, x_attn_in, x_o_in, x_mlp_in):
         """x_attn_in [M, H] -> qkv_local; x_o_in [M, K_o/tp] -> attention block output (reduced);
         x_mlp_in [M, H] -> MLP block output (reduced)."""

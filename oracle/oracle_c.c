@@ -55,6 +55,16 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Size of the OpenMP team used by the functions below (a launcher may have exported
+ * OMP_NUM_THREADS=1; the timed baseline sets the count it reports). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* One Q8_0 block: fp16 d then 32 int8; value = d*q. */
 static void dequant_row_q8_0(const uint8_t *row, int64_t k, float *out) {
     for (int64_t b = 0; b < k / 32; ++b) {
