@@ -303,11 +303,13 @@ def host64(t):
 
 
 def act_np(name, v):
-    """The fused epilogue functions in float64 (erf GELU, SiLU)."""
+    """The fused epilogue functions in float64 (erf GELU, tanh-form GELU, SiLU)."""
     import math
     import numpy as np
     if name == "gelu":
         return 0.5 * v * (1.0 + np.vectorize(math.erf)(v * 0.7071067811865476))
+    if name == "gelu_tanh":
+        return 0.5 * v * (1.0 + np.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))
     if name == "silu":
         return v / (1.0 + np.exp(-v))
     return v
@@ -403,9 +405,9 @@ def measure_gemm_cases(device, only=None, iters=20):
         ("fastconformer-b32-ffn2", 12000, 1024, 4096, None, False),
         ("fastconformer-b32-attn", 12000, 1024, 1024, None, False),
         ("whisper-b32-qkv+bias", 48000, 3840, 1280, None, True),
-        ("whisper-b32-fc1+bias+gelu", 48000, 5120, 1280, "gelu", True),
+        ("whisper-b32-fc1+bias+gelu", 48000, 5120, 1280, "gelu_tanh", True),
         ("whisper-b32-fc2+bias", 48000, 1280, 5120, None, True),
-        ("whisper-b1-fc1+bias+gelu", 1500, 5120, 1280, "gelu", True),
+        ("whisper-b1-fc1+bias+gelu", 1500, 5120, 1280, "gelu_tanh", True),
         ("fastconformer-b1-ffn1+silu", 375, 4096, 1024, "silu", False),
     ]
     out = []
@@ -646,7 +648,7 @@ SHARDED_DEFAULT = ["qwen3-8b-tp-prefill-m2048", "qwen3-8b-tp-decode-m1", "qwen3-
                    "qwen3-30b-a3b-ep-t4096", "qwen3-30b-a3b-ep-t64", "whisper-large-v3-b32", "fastconformer-b32"]
 ENCODERS = {
     # name: (layers, d_model, ffn, frames per utterance, biases, activation, feed-forwards per layer)
-    "whisper-large-v3": (32, 1280, 5120, 1500, True, "gelu", 1),
+    "whisper-large-v3": (32, 1280, 5120, 1500, True, "gelu_tanh", 1),
     "fastconformer": (24, 1024, 4096, 375, False, "silu", 2),
 }
 

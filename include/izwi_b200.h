@@ -67,7 +67,8 @@ int32_t izb_ctx_selftest_wait_timeout(izb_ctx* ctx, izb_stream stream);
 int64_t izb_ctx_launch_count(const izb_ctx* ctx);
 
 /* Byte size of `rows x cols` values in a block format; fails unless
- * rows*cols is a multiple of the block size.
+ * rows*cols is a multiple of the block size (the reference's rule; a matrix that is to be
+ * multiplied needs every row to be whole blocks, which izb_linear checks itself).
  * Replaces `quantized_storage_bytes` (models/architectures/qwen3/core.rs:891-909). */
 int32_t izb_quantized_storage_bytes(int32_t wfmt, int64_t rows, int64_t cols, size_t* out_bytes);
 
@@ -82,10 +83,18 @@ int32_t izb_dequantize(izb_ctx* ctx, izb_stream stream, int32_t wfmt, const void
 /* Element-wise function fused into the output of a linear layer. */
 typedef enum izb_epilogue {
     IZB_EPI_NONE = 0,
-    IZB_EPI_GELU = 1,   /* exact erf GELU: Whisper `mlp_linear1` + GELU (whisper/model.rs:311-317) */
+    IZB_EPI_GELU = 1,   /* exact erf GELU: the reference's `gelu_erf()` call sites
+                           (granite_speech/asr/runtime.rs:1639, qwen3/tts/speech_tokenizer.rs:670,891) */
     IZB_EPI_SILU = 2,   /* x*sigmoid(x): FastConformer feed-forward (parakeet/asr/mod.rs:766-772) */
-    IZB_EPI_SWIGLU = 3  /* W = [gate; up] rows: y[:, j] = silu(gate_j) * up_j, y has N/2 columns:
+    IZB_EPI_SWIGLU = 3, /* W = [gate; up] rows: y[:, j] = silu(gate_j) * up_j, y has N/2 columns:
                            `Qwen3Mlp::forward` gate/up + silu-mul in one pass (qwen3/core.rs:1787-1795) */
+    IZB_EPI_GELU_TANH = 4 /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))): the reference's `Tensor::gelu()` call
+                           sites, Whisper `mlp_linear1` + GELU (whisper/model.rs:311-317) and the Qwen3-ASR audio
+                           tower (qwen3/asr/audio.rs:385,667-668).  Evidence that `gelu()` is this form and not
+                           the erf one: the reference keeps the two apart (it calls `gelu_erf()` where it wants
+                           the exact form), and every GELU it writes out itself under that name is this formula
+                           (audio/codec.rs:135-137, voxtral/realtime/audio.rs:73-88, lfm25_audio/conformer.rs:
+                           1266-1280).  Candle's source is not part of the reference tree, so this is inferred. */
 } izb_epilogue;
 
 /* Function of the activations fused in front of a linear layer (decode step, one or two tokens).
@@ -111,7 +120,7 @@ typedef struct izb_linear_args {
     void* y;           /* [M, ldy] */
     int64_t M, N, K;
     int64_t ldx, ldy;  /* row strides in elements */
-    void* workspace;   /* NULL unless izb_linear_workspace_bytes() > 0 */
+    void* workspace;   /* NULL unless izb_linear_workspace_bytes_ex() > 0 for this call */
     size_t workspace_bytes;
     int32_t epilogue;  /* izb_epilogue fused after the bias add */
     int32_t prologue;  /* izb_prologue applied to x on its way into the product */
@@ -136,6 +145,16 @@ typedef struct izb_linear_args {
  * non-finite); 3..16 tokens (Q8_0: ..32) lift the codes to fp16 / bf16 tensor-core operands in
  * registers; up to 64 tokens dequantise to bf16 in shared memory for tcgen05.  All accumulate in fp32. */
 size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K);
+/* The same query for a call that also fuses `epilogue`: over Q8_0 / Q4_K weights a fused epilogue
+ * always runs on the GEMM and therefore needs the N*K*2-byte workspace, whatever M is (izb_linear
+ * returns IZB_ERR_BAD_ARG without it).  Query with the epilogue the call will carry, allocate once,
+ * pass it in `workspace`. */
+size_t izb_linear_workspace_bytes_ex(int32_t wfmt, int64_t M, int64_t N, int64_t K, int32_t epilogue);
+/* Row widths: K must be a whole number of blocks (32 for Q8_0, 256 for Q4_K / Q6_K; IZB_ERR_BAD_ARG
+ * otherwise) and a multiple of 8 for bf16.  The streaming kernels walk 256 values of a block-format
+ * row (64 of a bf16 row) at a time; other widths (a Q8_0 row of 384 values, say) run on the GEMM,
+ * for which block formats need the workspace (the query above accounts for it; without one the
+ * answer is IZB_ERR_UNSUPPORTED). */
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args);
 /* Largest M for which izb_linear / izb_linear_batch accept `prologue`, `residual` for weights in
  * `wfmt` (0: never). */

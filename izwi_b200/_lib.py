@@ -20,7 +20,7 @@ IZB_ERR_SCRATCH_TOO_SMALL = -6
 
 IZB_BF16, IZB_F32 = 0, 1
 IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K, IZB_W_Q6_K = 0, 1, 2, 3
-IZB_EPI_NONE, IZB_EPI_GELU, IZB_EPI_SILU, IZB_EPI_SWIGLU = 0, 1, 2, 3
+IZB_EPI_NONE, IZB_EPI_GELU, IZB_EPI_SILU, IZB_EPI_SWIGLU, IZB_EPI_GELU_TANH = 0, 1, 2, 3, 4
 
 
 class LinearArgs(C.Structure):
@@ -57,6 +57,7 @@ _SIGNATURES = {
     "izb_quantized_storage_bytes": (C.c_int32, [C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_size_t)]),
     "izb_dequantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "izb_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
+    "izb_linear_workspace_bytes_ex": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
     "izb_linear": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(LinearArgs)]),
     "izb_linear_fusion_max_tokens": (C.c_int32, [C.c_int32]),
     "izb_linear_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -169,7 +169,7 @@ const char* izb_status_string(int32_t status) {
 }
 
 int32_t izb_ctx_create(int32_t device, izb_ctx** out) {
-    if (!out || device < 0) return IZB_ERR_BAD_ARG;
+    if (!out || device < 0 || device >= IZB_MAX_DEVICES) return IZB_ERR_BAD_ARG;
     *out = nullptr;
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || device >= count) {
@@ -320,11 +320,21 @@ int32_t izb_silu_mul(izb_ctx* ctx, izb_stream stream, const void* gate, const vo
 static constexpr int64_t kStreamMaxM_bf16 = 32;
 static constexpr int64_t kStreamMaxM_quant = 64;
 
-size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K) {
-    if ((wfmt == IZB_W_Q8_0 || wfmt == IZB_W_Q4_K) && M > kStreamMaxM_quant && N > 0 && K > 0)
-        return static_cast<size_t>(N) * static_cast<size_t>(K) * 2;
-    if (wfmt == IZB_W_Q6_K && M > 0 && N > 0 && K > 0) return static_cast<size_t>(N) * static_cast<size_t>(K) * 2;
+// The weight-streaming kernels walk k in whole 256-value boxes of block-quantised rows (64 values of
+// bf16 rows); other widths go to the tensor-core GEMM (block formats: through the bf16 copy).
+static bool stream_width_ok(int32_t wfmt, int64_t K) { return K % (wfmt == IZB_W_BF16 ? 64 : 256) == 0; }
+
+size_t izb_linear_workspace_bytes_ex(int32_t wfmt, int64_t M, int64_t N, int64_t K, int32_t epilogue) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const size_t dense = static_cast<size_t>(N) * static_cast<size_t>(K) * 2;
+    if (wfmt == IZB_W_Q6_K) return dense;
+    if (wfmt == IZB_W_Q8_0 || wfmt == IZB_W_Q4_K)
+        return (M > kStreamMaxM_quant || epilogue != IZB_EPI_NONE || !stream_width_ok(wfmt, K)) ? dense : 0;
     return 0;
+}
+
+size_t izb_linear_workspace_bytes(int32_t wfmt, int64_t M, int64_t N, int64_t K) {
+    return izb_linear_workspace_bytes_ex(wfmt, M, N, K, IZB_EPI_NONE);
 }
 
 int32_t izb_linear_fusion_max_tokens(int32_t wfmt) {
@@ -335,7 +345,7 @@ int32_t izb_linear_fusion_max_tokens(int32_t wfmt) {
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args) {
     if (!ctx || !args) return IZB_ERR_BAD_ARG;
     if (args->M < 0 || args->N < 0 || args->K < 0) return IZB_ERR_BAD_ARG;
-    if (args->epilogue < IZB_EPI_NONE || args->epilogue > IZB_EPI_SWIGLU) return IZB_ERR_BAD_ARG;
+    if (args->epilogue < IZB_EPI_NONE || args->epilogue > IZB_EPI_GELU_TANH) return IZB_ERR_BAD_ARG;
     if (args->prologue < IZB_PRO_NONE || args->prologue > IZB_PRO_SILU_MUL) return IZB_ERR_BAD_ARG;
     if (args->M == 0 || args->N == 0) return IZB_OK;
     if (args->K == 0) return IZB_ERR_UNSUPPORTED;
@@ -361,10 +371,13 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
     }
     const bool quant = args->wfmt == IZB_W_Q8_0 || args->wfmt == IZB_W_Q4_K;
     if (!quant && args->wfmt != IZB_W_BF16) return IZB_ERR_BAD_ARG;
+    // a row must be a whole number of blocks, or the bytes of one row would run into the next
+    if (quant && args->K % (args->wfmt == IZB_W_Q8_0 ? 32 : 256) != 0) return IZB_ERR_BAD_ARG;
 
     const void* w_dense = args->w;
-    bool use_gemm = !quant && (args->M > kStreamMaxM_bf16 || args->epilogue != IZB_EPI_NONE);
-    if (quant && (args->M > kStreamMaxM_quant || args->epilogue != IZB_EPI_NONE)) {
+    const bool streams = stream_width_ok(args->wfmt, args->K);
+    bool use_gemm = !quant && (args->M > kStreamMaxM_bf16 || args->epilogue != IZB_EPI_NONE || !streams);
+    if (quant && (args->M > kStreamMaxM_quant || args->epilogue != IZB_EPI_NONE || !streams)) {
         const size_t need = static_cast<size_t>(args->N) * static_cast<size_t>(args->K) * 2;
         if (args->workspace && args->workspace_bytes >= need && izb_aligned(args->workspace, 16)) {
             const int rc = izb_dequantize(ctx, stream, args->wfmt, args->w, args->N * args->K, IZB_BF16, args->workspace);
@@ -373,9 +386,12 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
             use_gemm = true;
         } else if (args->epilogue != IZB_EPI_NONE) {
             return IZB_ERR_BAD_ARG;  // a fused epilogue over block-quantised weights needs the workspace
+        } else if (!streams) {
+            return IZB_ERR_UNSUPPORTED;  // a row width the streaming kernels do not walk, and no workspace for the GEMM
         }
     }
     if (use_gemm) {
+        if (args->prologue != IZB_PRO_NONE || args->residual) return IZB_ERR_UNSUPPORTED;
         if (!args->x || !args->y || !w_dense) return IZB_ERR_BAD_ARG;
         if (args->ldx < args->K) return IZB_ERR_BAD_ARG;
         return gemm_tc_launch(ctx, s, args->x, args->ldx, w_dense, args->bias, args->y, args->ldy, args->y_dtype,

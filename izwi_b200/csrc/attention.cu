@@ -317,8 +317,8 @@ int launch_att(izb_ctx* ctx, cudaStream_t s, const __nv_bfloat16* q, const __nv_
                long long ld_out, long long kv_cap, int kv_len, float scale, int splits) {
     const size_t smem = static_cast<size_t>(G * ATT_THREADS + 4 * G * D) * sizeof(float);
     auto kern = decode_gqa_kernel<D, G>;
-    static std::atomic<int> smem_set[16];
-    const int slot = ctx->device & 15;
+    static std::atomic<int> smem_set[IZB_MAX_DEVICES];
+    const int slot = ctx->device;
     if (smem > 48 * 1024 && smem_set[slot].load(std::memory_order_relaxed) < static_cast<int>(smem)) {
         IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         smem_set[slot].store(static_cast<int>(smem), std::memory_order_relaxed);
@@ -437,7 +437,9 @@ int32_t izb_decode_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q,
     if (heads % kv_heads != 0 || heads / kv_heads > ATT_MAX_G) return IZB_ERR_UNSUPPORTED;
     if (kv_len <= 0 || kv_len > kv_capacity || kv_len > INT32_MAX || batch > 65535 || kv_heads > 65535) return IZB_ERR_BAD_ARG;
     if (ld_q < static_cast<int64_t>(heads) * head_dim || ld_out < static_cast<int64_t>(heads) * head_dim) return IZB_ERR_BAD_ARG;
-    if (!izb_aligned(q, 2) || !izb_aligned(out, 2) || !izb_aligned(k_cache, 16) || !izb_aligned(v_cache, 16)) return IZB_ERR_BAD_ARG;
+    // q and the caches are read with 16-byte loads: the base and every token row must sit on that boundary
+    if (!izb_aligned(q, 16) || ld_q % 8 != 0 || !izb_aligned(out, 2) || !izb_aligned(k_cache, 16) || !izb_aligned(v_cache, 16))
+        return IZB_ERR_BAD_ARG;
     const int splits = att_splits(ctx, batch, kv_heads, kv_len);
     const size_t need = splits > 1 ? static_cast<size_t>(batch) * heads * splits * (head_dim + 2) * sizeof(float) : 0;
     if (need && (!workspace || workspace_bytes < need || !izb_aligned(workspace, 4))) return IZB_ERR_BAD_ARG;

@@ -30,14 +30,6 @@ struct GemmShared {
     int tile_prefix[GT_MAX_EXPERTS + 1];  // grouped: first m-tile of each expert
 };
 
-#ifdef IZB_GEMM_TRACE
-__device__ unsigned long long g_gemm_trace[4096];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define GT_TRACE(slot, it) do { if (blockIdx.x == 0 && (it) < 16) g_gemm_trace[(slot) * 16 + (it)] = gtime(); } while (0)
-#else
-#define GT_TRACE(slot, it) do { } while (0)
-#endif
-
 struct TileCoord {
     int m0;        // first row of X
     int rows_end;  // rows at or past this are not stored
@@ -79,6 +71,12 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 // x * sigmoid(x) = 0.5 x (1 + tanh(x / 2)): one special-function instruction per element
 // (tanh.approx, relative error ~2^-11, below the bf16 rounding of the result).
+// tanh-form GELU, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), on the same instruction.
+__device__ __forceinline__ float gelu_tanh(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * x * x, x, x)));
+    return fmaf(0.5f * x, t, 0.5f * x);
+}
 __device__ __forceinline__ float silu(float x) {
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
@@ -145,11 +143,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             int stage = 0;
             uint32_t phase = 0;
             long long issued = 0;
-            int pit = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++pit) {
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const TileCoord c = tile_coord(tile, m_tiles, n_tiles, p, sh.tile_prefix);
                 const int n0 = c.n_blk * out_cols;
-                GT_TRACE(0, pit);
                 for (int kb = 0; kb < n_kb; ++kb) {
                     if (!mbar_wait_bounded(smem_u32(&sh.empty[stage]), phase ^ 1u, abort_flag)) {
                         ok = false;
@@ -200,7 +196,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                     break;
                 }
                 tc_fence_after();
-                GT_TRACE(1, it);
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
                 for (int kb = 0; kb < n_kb; ++kb) {
                     if (!mbar_wait_bounded(smem_u32(&sh.full[stage]), phase, abort_flag)) {
@@ -224,7 +219,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                 }
                 if (!ok) break;
                 tc_commit(smem_u32(&sh.tmem_full[acc]));  // accumulator complete
-                GT_TRACE(2, it);
             }
             // every MMA issued by this thread has retired before TMEM is released
             tc_commit(smem_u32(&sh.drain));
@@ -251,7 +245,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             if (ok && !mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_phase, abort_flag)) ok = false;
             if (!ok) break;
             tc_fence_after();
-            if (warp == 2 && lane == 0) GT_TRACE(3, it);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(acc * 256);
             const __nv_bfloat16* bias = p.bias ? p.bias + static_cast<long long>(c.expert) * p.N : nullptr;
             const int col_base = c.n_blk * out_cols;
@@ -292,6 +285,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                     } else if (p.epilogue == GEMM_EPI_SILU) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = silu(v[i]);
+                    } else if (p.epilogue == GEMM_EPI_GELU_TANH) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
                     }
                 }
                 // park this thread's 32 values in its staging row
@@ -349,7 +345,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             }
             tc_fence_before();
             __syncwarp();
-            if (warp == 2 && lane == 0) GT_TRACE(4, it);
             if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
         }
     }
@@ -373,7 +368,7 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     if (K % 8 != 0 || ldx % 8 != 0 || ldx < K) return IZB_ERR_UNSUPPORTED;
     if (!izb_aligned(x, 16) || !izb_aligned(w, 16)) return IZB_ERR_BAD_ARG;
     if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
-    if (epilogue < GEMM_EPI_NONE || epilogue > GEMM_EPI_SWIGLU) return IZB_ERR_BAD_ARG;
+    if (epilogue < GEMM_EPI_NONE || epilogue > GEMM_EPI_GELU_TANH) return IZB_ERR_BAD_ARG;
     if (seg_offsets && n_experts > GT_MAX_EXPERTS) return IZB_ERR_UNSUPPORTED;
     if (!seg_offsets && n_experts != 1) return IZB_ERR_BAD_ARG;
     const bool swiglu = epilogue == GEMM_EPI_SWIGLU;
@@ -428,8 +423,8 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     if (n_stages < 2) return IZB_ERR_UNSUPPORTED;
     static_assert(sizeof(GemmShared) <= 2048, "static shared memory budget");
     const int smem_bytes = n_stages * stage_bytes + staging;
-    static std::atomic<int> smem_set[16];
-    const int slot = ctx->device & 15;
+    static std::atomic<int> smem_set[IZB_MAX_DEVICES];  // the attribute is per device: one record each
+    const int slot = ctx->device;
     if (smem_set[slot].load(std::memory_order_relaxed) < smem_bytes) {
         IZB_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         smem_set[slot].store(smem_bytes, std::memory_order_relaxed);
@@ -443,8 +438,3 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
 
 }  // namespace izb
 
-#ifdef IZB_GEMM_TRACE
-extern "C" int izb_debug_gemm_trace(unsigned long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, izb::g_gemm_trace, sizeof(unsigned long long) * 16 * 5) == cudaSuccess ? 0 : -3;
-}
-#endif

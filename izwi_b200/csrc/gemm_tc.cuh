@@ -7,8 +7,8 @@
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma (128 x BN x 16) into one of two
 //               TMEM accumulators, commits ring slots back to the producer and accumulators to
 //               the epilogue through mbarriers
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes), bias /
-//               activation in fp32, bf16 or fp32 stores
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (two warps per 32 TMEM lanes, half of the
+//               columns each), bias / activation in fp32, bf16 or fp32 stores
 // Both operands are K-major with the 128-byte swizzle; no cluster multicast anywhere.
 #pragma once
 
@@ -20,9 +20,10 @@ namespace izb {
 
 enum GemmEpilogue : int {
     GEMM_EPI_NONE = 0,
-    GEMM_EPI_GELU = 1,    // exact (erf) GELU, Whisper fc1
+    GEMM_EPI_GELU = 1,    // exact (erf) GELU
     GEMM_EPI_SILU = 2,    // x * sigmoid(x), FastConformer feed-forward
     GEMM_EPI_SWIGLU = 3,  // W = [gate ; up] rows: out[:, j] = silu(gate_j) * up_j, N_out = N / 2
+    GEMM_EPI_GELU_TANH = 4,  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), Whisper fc1
 };
 
 struct GemmParams {

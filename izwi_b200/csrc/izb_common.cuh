@@ -24,6 +24,7 @@ struct izb_ctx {
 };
 
 constexpr int IZB_STATUS_WORDS = 8;
+constexpr int IZB_MAX_DEVICES = 64;  // izb_ctx_create refuses device ordinals at or above this (per-device tables)
 constexpr int IZB_ARGMAX_SPLIT_ROWS = 1024;
 // Bounded device-side waits give up after this many clock64 ticks (~1 s).
 constexpr long long IZB_WAIT_LIMIT_CLOCKS = 2000000000LL;
@@ -200,6 +201,15 @@ __device__ __forceinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t
             }
         }
     }
+}
+// Waits on the clock alone (no abort flag): for a CTA that has already given up on its own work but
+// must outlive the stores its cluster peers still make into its shared memory.
+__device__ __forceinline__ bool mbar_wait_cluster_clock_only(uint32_t bar, uint32_t parity, long long limit_clocks) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if (clock64() - t0 > limit_clocks) return false;
+    }
+    return true;
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");

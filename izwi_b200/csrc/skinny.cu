@@ -451,8 +451,8 @@ int launch_one(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, con
                const SkinnyProblem& single) {
     auto kern = skinny_kernel<FMT, NT, RT, KS>;
     // The opt-in shared-memory ceiling is per function and per device; raise it only when it grows.
-    static std::atomic<int> smem_set[16];
-    const int dev_slot = ctx->device & 15;
+    static std::atomic<int> smem_set[IZB_MAX_DEVICES];
+    const int dev_slot = ctx->device;
     if (smem_set[dev_slot].load(std::memory_order_relaxed) < h.smem_bytes) {
         IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));
         smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);

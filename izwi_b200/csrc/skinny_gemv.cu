@@ -559,7 +559,15 @@ __global__ void __launch_bounds__(GV_THREADS)
                 mbar_arrive_cluster(cluster_map_shared(smem_u32(&sh.cl_bar), 0));
                 continue;
             }
-            if (ok && !mbar_wait_cluster_bounded(smem_u32(&sh.cl_bar), 0u, abort_flag)) ok = false;
+            // The other CTAs of the cluster store into this CTA's shared memory whatever became of their own
+            // waits, and signal when done.  This CTA must stay resident until they have: it waits for them
+            // even after giving up on its own pipeline (then on the clock alone, since the abort flag is
+            // already up), and only uses their sums when everything went well.
+            if (ok) {
+                if (!mbar_wait_cluster_bounded(smem_u32(&sh.cl_bar), 0u, abort_flag)) ok = false;
+            } else {
+                (void)mbar_wait_cluster_clock_only(smem_u32(&sh.cl_bar), 0u, 2 * IZB_WAIT_LIMIT_CLOCKS);
+            }
             if (ok) {
                 for (int r = 0; r < ksplit - 1; ++r) {
 #pragma unroll
@@ -594,8 +602,8 @@ __global__ void __launch_bounds__(GV_THREADS)
 template <int FMT, int MT, bool EX, bool KS>
 static int gemv_prepare(const izb_ctx* ctx, const SkinnyPlanHeader& h) {
     auto kern = skinny_gemv_kernel<FMT, MT, EX, KS>;
-    static std::atomic<int> smem_set[16];
-    const int dev_slot = ctx->device & 15;
+    static std::atomic<int> smem_set[IZB_MAX_DEVICES];
+    const int dev_slot = ctx->device;
     if (smem_set[dev_slot].load(std::memory_order_relaxed) < h.smem_bytes) {
         IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));
         smem_set[dev_slot].store(h.smem_bytes, std::memory_order_relaxed);

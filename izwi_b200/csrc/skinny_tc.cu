@@ -27,15 +27,6 @@ constexpr int STC_ABUF_BYTES = STC_TILE_ROWS * 128;   // one 64-k operand slice:
 constexpr int STC_NA = 4;        // operand slices of one 256-k weight box; warps 4q..4q+3 own slice q
 constexpr int STC_ACC_COLS = 64; // fp32 columns of one accumulator (tokens); two accumulators alternate
 
-#ifdef IZB_STC_TRACE
-// Debug build only: CTA 0 records clock64 at pipeline events (role 0 producer, 1/2 converting warps 0/15, 3 MMA).
-constexpr int STC_TRACE_N = 4096;
-__device__ long long stc_trace[4][STC_TRACE_N];
-#define STC_TRACE(role, idx) do { if (blockIdx.x == 0 && (role) >= 0 && (idx) < STC_TRACE_N) stc_trace[role][(idx)++] = clock64(); } while (0)
-#else
-#define STC_TRACE(role, idx) do { } while (0)
-#endif
-
 struct StcShared {
     unsigned long long full_w[SK_MAX_STAGES];   // raw weight boxes: filled by TMA ...
     unsigned long long empty_w[SK_MAX_STAGES];  // ... released by the converting warps once loaded into registers
@@ -120,8 +111,7 @@ __device__ __forceinline__ void q4_scale_min(const uint4& hd, uint32_t& sc, uint
 // multiplied and the half being written overlap.  n = boxes this thread has converted so far.
 template <int FMT, int Q>
 __device__ __forceinline__ bool convert_box(StcShared& sh, uint32_t wrow, uint32_t ebar, uint32_t abuf0, int row, int lane,
-                                            unsigned int n, volatile int* abort_flag, [[maybe_unused]] int role,
-                                            [[maybe_unused]] int& tr) {
+                                            unsigned int n, volatile int* abort_flag) {
     const uint32_t dst_row = abuf0 + static_cast<uint32_t>(Q * STC_ABUF_BYTES + row * 128);
     const uint32_t par = (n & 1u) ^ 1u;
     if constexpr (FMT == IZB_W_Q8_0) {
@@ -139,21 +129,17 @@ __device__ __forceinline__ bool convert_box(StcShared& sh, uint32_t wrow, uint32
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = prmt(W[Q + i], W[Q + i + 1], 0x5432);  // codes start 2 bytes into word Q
         if (!mbar_wait_bounded(smem_u32(&sh.a_free[0]), par, abort_flag)) return false;
-        STC_TRACE(role, tr);
         q8_block_to_row(q, W[Q] & 0xFFFFu, dst_row, 0, row);
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh.a_ready[0]));
-        STC_TRACE(role, tr);
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = W[Q + 9 + i];  // second block: scale in the top half of word Q+8
         if (!mbar_wait_bounded(smem_u32(&sh.a_free[1]), par, abort_flag)) return false;
-        STC_TRACE(role, tr);
         q8_block_to_row(q, W[Q + 8] >> 16, dst_row, 4, row);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh.a_ready[1]));
-        STC_TRACE(role, tr);
     } else {
         // row = one 144-byte super-block; slice Q = code group Q: low nibbles sub-block 2Q, high 2Q+1
         const uint4 hd = lds128(wrow);
@@ -169,22 +155,18 @@ __device__ __forceinline__ bool convert_box(StcShared& sh, uint32_t wrow, uint32
         // weight = (16+n)*s - (16*s + dmin*m), s already rounded to bf16
         uint32_t c2 = bcast_bf16x2(-fmaf(16.0f, bf16_hi_to_f32(s2), dmin * static_cast<float>(mn)));
         if (!mbar_wait_bounded(smem_u32(&sh.a_free[0]), par, abort_flag)) return false;
-        STC_TRACE(role, tr);
         q4_sub_to_row<false>(words, s2, c2, dst_row, row);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh.a_ready[0]));
-        STC_TRACE(role, tr);
         q4_scale_min<2 * Q + 1>(hd, sc, mn);
         s2 = bcast_bf16x2(d * static_cast<float>(sc));
         c2 = bcast_bf16x2(-fmaf(16.0f, bf16_hi_to_f32(s2), dmin * static_cast<float>(mn)));
         if (!mbar_wait_bounded(smem_u32(&sh.a_free[1]), par, abort_flag)) return false;
-        STC_TRACE(role, tr);
         q4_sub_to_row<true>(words, s2, c2, dst_row, row);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh.a_ready[1]));
-        STC_TRACE(role, tr);
     }
     return true;
 }
@@ -291,7 +273,6 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
             int stage = 0, p = -1;
             uint32_t phase = 0;
             long long issued = 0;
-            [[maybe_unused]] int tr = 0;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int np = find_problem(lite, n_cached, plist, n_probs, tile);
                 const bool moved = np != p;
@@ -307,7 +288,6 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                     }
                     const uint32_t fbar = smem_u32(&full[stage]);
                     if (is_w) {
-                        STC_TRACE(0, tr);
                         mbar_expect_tx(fbar, static_cast<uint32_t>(L.w_box_bytes));
                         tma_load_3d(wring0 + static_cast<uint32_t>(stage * w_stage_bytes), &P->tmap_w, 0, row0, c, fbar);
                     } else {
@@ -330,7 +310,6 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
             int stage = 0, it = 0;
             uint32_t phase = 0;
             unsigned int n = 0;  // weight boxes multiplied so far by this CTA
-            [[maybe_unused]] int tr = 0;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
                 const int p = find_problem(lite, n_cached, plist, n_probs, tile);
                 const int n_chunks = p < n_cached ? lite[p].n_chunks : plist[p].n_chunks;
@@ -355,7 +334,6 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                             ok = false;
                             break;
                         }
-                        STC_TRACE(3, tr);
                         tc_fence_after();
 #pragma unroll
                         for (int q = 0; q < STC_NA; ++q) {
@@ -366,11 +344,9 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                                 tc_mma_f16(tmem_acc, adesc + static_cast<uint64_t>(2 * k), bdesc + static_cast<uint64_t>(2 * k),
                                            idesc, (c | q | k) != 0 ? 1u : 0u);
                         }
-                        STC_TRACE(3, tr);
                         tc_commit(smem_u32(&sh.a_free[h]));
                     }
                     if (!ok) break;
-                    STC_TRACE(3, tr);
                     tc_commit(smem_u32(&sh.empty_x[stage]));  // the activation slices of this stage are consumed
                     if (++stage == x_stages) {
                         stage = 0;
@@ -398,10 +374,6 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
         uint32_t phase = 0;
         unsigned int n = 0;
         int prev_p = 0, prev_row0 = 0;
-        [[maybe_unused]] int tr = 0;
-        [[maybe_unused]] const int role = (lane != 0) ? -1 : warp == 0 ? 1 : -1;
-        [[maybe_unused]] const int erole = (lane == 0 && warp == 0) ? 2 : -1;
-        [[maybe_unused]] int etr = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int p = find_problem(lite, n_cached, plist, n_probs, tile);
             const int n_chunks = p < n_cached ? lite[p].n_chunks : plist[p].n_chunks;
@@ -412,14 +384,13 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                     ok = false;
                     break;
                 }
-                STC_TRACE(role, tr);
                 const uint32_t wrow = wring0 + static_cast<uint32_t>(stage * w_stage_bytes + row * w_row_bytes);
                 const uint32_t ebar = smem_u32(&sh.empty_w[stage]);
                 switch (q) {
-                    case 0: ok = convert_box<FMT, 0>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag, role, tr); break;
-                    case 1: ok = convert_box<FMT, 1>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag, role, tr); break;
-                    case 2: ok = convert_box<FMT, 2>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag, role, tr); break;
-                    default: ok = convert_box<FMT, 3>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag, role, tr); break;
+                    case 0: ok = convert_box<FMT, 0>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag); break;
+                    case 1: ok = convert_box<FMT, 1>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag); break;
+                    case 2: ok = convert_box<FMT, 2>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag); break;
+                    default: ok = convert_box<FMT, 3>(sh, wrow, ebar, abuf0, row, lane, n, abort_flag); break;
                 }
                 if (++stage == w_stages) {
                     stage = 0;
@@ -429,17 +400,14 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                 // have had time to finish, and the tensor core already works on this tile meanwhile
                 if (c == 0 && it > 0 && warp < STC_EPI_WARPS && ok) {
                     const int acc = (it - 1) & 1;
-                    STC_TRACE(erole, etr);
                     if (!mbar_wait_bounded(smem_u32(&sh.acc_full[acc]), static_cast<uint32_t>(((it - 1) >> 1) & 1), abort_flag)) {
                         ok = false;
                         break;
                     }
-                    STC_TRACE(erole, etr);
                     tc_fence_after();
                     stc_epilogue(prev_p < n_cached ? lite[prev_p] : lite_from(plist[prev_p]), prev_row0,
                                  tmem_base + static_cast<uint32_t>(acc * STC_ACC_COLS), warp, lane, mp, y_dtype);
                     tc_fence_before();
-                    STC_TRACE(erole, etr);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sh.acc_empty[acc]));
                 }
@@ -471,12 +439,6 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
     if ((!ok || sh.abort_flag) && lane == 0) atomicExch(status, 4);
 }
 
-#ifdef IZB_STC_TRACE
-extern "C" int izb_stc_trace_dump(long long* out) {
-    return cudaMemcpyFromSymbol(out, stc_trace, sizeof(stc_trace)) == cudaSuccess ? 0 : -1;
-}
-#endif
-
 int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, const SkinnyProblem* dev_probs,
                      const SkinnyProblem* single) {
     if (h.magic != SK_PLAN_MAGIC || !h.tc) return IZB_ERR_BAD_ARG;
@@ -484,8 +446,8 @@ int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& 
     static const SkinnyProblem dummy = {};
     const SkinnyProblem& s = single ? *single : dummy;
     const int mp = h.nt * 8;
-    static std::atomic<int> smem_set[2][16];
-    const int slot = ctx->device & 15, which = h.fmt == IZB_W_Q8_0 ? 0 : 1;
+    static std::atomic<int> smem_set[2][IZB_MAX_DEVICES];
+    const int slot = ctx->device, which = h.fmt == IZB_W_Q8_0 ? 0 : 1;
     if (smem_set[which][slot].load(std::memory_order_relaxed) < h.smem_bytes) {
         if (which == 0)
             IZB_CUDA_TRY(cudaFuncSetAttribute(skinny_tc_kernel<IZB_W_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem_bytes));

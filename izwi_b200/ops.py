@@ -67,7 +67,7 @@ def dequantize(raw: torch.Tensor, fmt: str, n_elems: int, dtype: torch.dtype = t
 
 
 EPILOGUE = {None: L.IZB_EPI_NONE, "none": L.IZB_EPI_NONE, "gelu": L.IZB_EPI_GELU, "silu": L.IZB_EPI_SILU,
-            "swiglu": L.IZB_EPI_SWIGLU}
+            "swiglu": L.IZB_EPI_SWIGLU, "gelu_tanh": L.IZB_EPI_GELU_TANH}
 PROLOGUE = {None: 0, "none": 0, "rms_norm": 1, "silu_mul": 2}  # izb_prologue
 
 
@@ -120,9 +120,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = 
     n_out = n // 2 if epilogue == "swiglu" else n
     y = out if out is not None else torch.empty(x2.shape[0], n_out, device=x.device, dtype=out_dtype)
     if workspace is True:
-        need = L.lib().izb_linear_workspace_bytes(WFMT[fmt], x2.shape[0], n, k)
-        if epilogue not in (None, "none") and fmt != "bf16":
-            need = n * k * 2
+        need = L.lib().izb_linear_workspace_bytes_ex(WFMT[fmt], x2.shape[0], n, k, EPILOGUE[epilogue])
         workspace = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
     elif workspace is False:
         workspace = None

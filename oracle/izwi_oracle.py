@@ -130,8 +130,18 @@ def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
         return (g / (np.float32(1.0) + np.exp(-g))) * u
 
 
+def gelu_tanh(x: np.ndarray) -> np.ndarray:
+    """tanh-form GELU, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))): what the reference writes out
+    wherever it spells GELU itself (audio/codec.rs:135-137, voxtral/realtime/audio.rs:73-88) and, by
+    its separate use of `gelu_erf()` elsewhere, what `Tensor::gelu()` after Whisper's fc1 stands for
+    (whisper/model.rs:311-317).  Candle's source is absent, so that mapping is inferred."""
+    x = np.asarray(x, dtype=np.float64)
+    return (0.5 * x * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (x + 0.044715 * x ** 3)))).astype(np.float32)
+
+
 def gelu_erf(x: np.ndarray) -> np.ndarray:
-    """Exact (erf) GELU used after Whisper's fc1 (whisper/model.rs:311-317)."""
+    """Exact (erf) GELU: the reference's `gelu_erf()` call sites (granite_speech/asr/runtime.rs:1639,
+    qwen3/tts/speech_tokenizer.rs:670)."""
     from math import sqrt
     from scipy.special import erf
     x = np.asarray(x, dtype=np.float64)

@@ -114,3 +114,31 @@ def test_fused_qk_norm_rope_append(cuda, b, h, kvh, d, with_norm):
     assert np.array_equal(to_np(vc[:, :, pos]), v_in)
     untouched = torch.cat([kc[:, :, :pos], kc[:, :, pos + 1:]], dim=2)
     assert float(untouched.abs().max()) == 0.0
+
+
+def test_unaligned_query_is_refused_before_any_launch(cuda):
+    """q is read with 16-byte loads: a base that is not 16-byte aligned, or a token stride that is not a
+    multiple of 8 elements, must come back as IZB_ERR_BAD_ARG from the host-side checks (nothing runs)."""
+    import ctypes as C
+
+    from izwi_b200 import _lib as L
+    from izwi_b200 import ops
+    ctx = ops.Context.get(0)
+    b, h, kvh, d, cap = 2, 8, 4, 64, 32
+    kc = torch.zeros(b, kvh, cap, d, device=cuda, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    qbuf = torch.zeros(b * (h * d + 8) + 8, device=cuda, dtype=torch.bfloat16)
+    out = torch.full((b, h, d), 3.0, device=cuda, dtype=torch.bfloat16)
+    launches = ctx.launch_count
+
+    def call(q_ptr, ld_q):
+        return L.lib().izb_decode_gqa_attention(ctx.handle, None, C.c_void_p(q_ptr), C.c_void_p(kc.data_ptr()),
+                                                C.c_void_p(vc.data_ptr()), C.c_void_p(out.data_ptr()), b, h, kvh, d, 16, cap,
+                                                ld_q, h * d, 0.125, None, 0)
+    assert call(qbuf.data_ptr() + 2, h * d) == L.IZB_ERR_BAD_ARG       # base 2 bytes off
+    assert call(qbuf.data_ptr(), h * d + 4) == L.IZB_ERR_BAD_ARG       # rows 8 bytes off
+    assert ctx.launch_count == launches
+    torch.cuda.synchronize()
+    assert float(out.min()) == 3.0
+    assert call(qbuf.data_ptr(), h * d + 8) == L.IZB_OK                # an aligned, padded layout is fine
+    ctx.check()

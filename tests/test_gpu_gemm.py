@@ -21,6 +21,8 @@ def run_gemm(cuda, m, n, k, seed, fmt="bf16", bias=False, epilogue=None, out_dty
     pre = o.linear(x, wf, b)
     if epilogue == "gelu":
         want = o.gelu_erf(pre)
+    elif epilogue == "gelu_tanh":
+        want = o.gelu_tanh(pre)
     elif epilogue == "silu":
         want = o.silu_mul(pre, np.ones_like(pre))
     elif epilogue == "swiglu":
@@ -60,7 +62,7 @@ def test_bias_and_f32_output(cuda):
     run_gemm(cuda, 100, 330, 512, seed=8, bias=True, out_dtype=torch.float32)
 
 
-@pytest.mark.parametrize("epilogue", ["gelu", "silu", "swiglu"])
+@pytest.mark.parametrize("epilogue", ["gelu", "gelu_tanh", "silu", "swiglu"])
 def test_fused_epilogues(cuda, epilogue):
     run_gemm(cuda, 375, 2048, 1024, seed=9, bias=(epilogue != "swiglu"), epilogue=epilogue, x_std=1.0)
     run_gemm(cuda, 70, 6144, 1024, seed=10, epilogue=epilogue)
@@ -110,3 +112,40 @@ def test_full_size_prefill_properties(cuda):
     ys = ops.linear(x[rows].contiguous(), w, out_dtype=torch.float32)   # M = 6 -> streaming kernel
     assert torch.allclose(y[rows], ys, rtol=2e-3, atol=2e-3)
     ops.Context.get(0).check()
+
+
+def _rows_f64(x, w, rows, bias=None):
+    """float64 product of sampled activation rows with the whole weight, on the host."""
+    v = x[rows].double().cpu().numpy() @ w.double().cpu().numpy().T
+    return v if bias is None else v + bias.double().cpu().numpy()[None, :]
+
+
+@pytest.mark.parametrize("name,m,n,k,epilogue,bias", [
+    ("qwen3-8b prefill qkv", 2048, 6144, 4096, None, False),
+    ("qwen3-8b prefill gate/up + SwiGLU", 2048, 24576, 4096, "swiglu", False),
+    ("qwen3-8b prefill down", 2048, 4096, 12288, None, False),
+    ("whisper b32 fc1 + bias + GELU", 48000, 5120, 1280, "gelu_tanh", True),
+    ("whisper b32 fc2 + bias", 48000, 1280, 5120, None, True),
+    ("fastconformer b32 ffn1 + SiLU", 12000, 4096, 1024, "silu", False),
+])
+def test_full_size_against_float64_on_sampled_rows(cuda, name, m, n, k, epilogue, bias):
+    """The prefill and encoder GEMMs at the full sizes of the configurations, checked against a float64
+    product of the same bf16 inputs on sampled token rows (first, last, tile edges, middle)."""
+    from izwi_b200 import ops
+    gen = torch.Generator(device=cuda).manual_seed(m + n)
+    w = (torch.randn(n, k, device=cuda, generator=gen) * 0.02).to(torch.bfloat16)
+    x = torch.randn(m, k, device=cuda, generator=gen).to(torch.bfloat16)
+    b = (torch.randn(n, device=cuda, generator=gen) * 0.1).to(torch.bfloat16) if bias else None
+    y = ops.linear(x, w, bias=b, epilogue=epilogue)
+    ops.Context.get(0).check()
+    rows = sorted({0, 1, 127, 128, m // 2, m - 129, m - 1})
+    pre = _rows_f64(x, w, rows, b).astype(np.float32)
+    if epilogue == "swiglu":
+        want = o.silu_mul(pre[:, : n // 2], pre[:, n // 2:])
+    elif epilogue == "gelu_tanh":
+        want = o.gelu_tanh(pre)
+    elif epilogue == "silu":
+        want = o.silu_mul(pre, np.ones_like(pre))
+    else:
+        want = pre
+    assert_matmul_close(y[rows], want, name)

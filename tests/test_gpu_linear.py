@@ -129,10 +129,14 @@ def test_rejects_bad_arguments(cuda):
     x = torch.zeros(2, 256, device=cuda, dtype=torch.bfloat16)
     with pytest.raises(ValueError):
         ops.linear(torch.zeros(2, 128, device=cuda, dtype=torch.bfloat16), w)
-    with pytest.raises(IzbError) as e:      # K not a multiple of 64
-        ops.linear(torch.zeros(2, 40, device=cuda, dtype=torch.bfloat16),
-                   torch.zeros(8, 40, device=cuda, dtype=torch.bfloat16))
+    with pytest.raises(IzbError) as e:      # bf16 rows must be a multiple of 8 values (16 bytes)
+        ops.linear(torch.zeros(2, 44, device=cuda, dtype=torch.bfloat16),
+                   torch.zeros(8, 44, device=cuda, dtype=torch.bfloat16))
     assert e.value.status == -2
+    with pytest.raises(IzbError) as e:      # a Q8_0 row that is not a whole number of 32-value blocks
+        ops.linear(torch.zeros(2, 48, device=cuda, dtype=torch.bfloat16),
+                   torch.zeros(2 * 48 // 32 * 34, device=cuda, dtype=torch.uint8), "q8_0", n=2, k=48)
+    assert e.value.status == -1
     with pytest.raises(IzbError) as e:      # misaligned weight pointer
         ops.linear(x, torch.zeros(64 * 256 + 8, device=cuda, dtype=torch.bfloat16)[1:64 * 256 + 1].reshape(64, 256))
     assert e.value.status == -1
@@ -244,3 +248,53 @@ def test_q6_k_linear_needs_the_workspace(cuda):
     with pytest.raises(IzbError) as e:
         ops.linear(x, raw, "q6_k", n=1, k=1024, workspace=False)
     assert e.value.status == -1
+
+
+# ---- row widths the streaming kernels do not walk, and the workspace query that goes with them ----
+
+def test_bf16_width_off_the_streaming_grid_takes_the_gemm(cuda):
+    run_linear(cuda, "bf16", 2, 8, 40, seed=700)        # K = 40: not a multiple of 64, still a multiple of 8
+    run_linear(cuda, "bf16", 5, 200, 328, seed=701)
+
+
+@pytest.mark.parametrize("m", [1, 9, 70])
+def test_q8_0_width_of_384_goes_through_the_workspace(cuda, m):
+    """An encoder width such as 384 is whole Q8_0 blocks but not whole 256-value boxes: the reference's
+    QMatMul takes it, so izb_linear does too, on the GEMM, with the workspace its query asks for."""
+    from izwi_b200 import IzbError, _lib as L, ops
+    n, k = 96, 384
+    assert L.lib().izb_linear_workspace_bytes_ex(L.IZB_W_Q8_0, m, n, k, L.IZB_EPI_NONE) == n * k * 2
+    run_linear(cuda, "q8_0", m, n, k, seed=710 + m)
+    raw = torch.zeros(n * k // 32 * 34, device=cuda, dtype=torch.uint8)
+    with pytest.raises(IzbError) as e:      # ... and says so when the caller brings none
+        ops.linear(torch.zeros(m, k, device=cuda, dtype=torch.bfloat16), raw, "q8_0", n=n, k=k, workspace=False)
+    assert e.value.status == -2
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+@pytest.mark.parametrize("m", [3, 64, 200])
+def test_workspace_query_then_call_with_a_fused_epilogue(cuda, fmt, m):
+    """What a C or Rust caller does: ask izb_linear_workspace_bytes_ex with the epilogue of the call,
+    allocate that much, pass it.  Straight through the C ABI, no Python-side sizing."""
+    import ctypes as C
+
+    from izwi_b200 import _lib as L
+    from izwi_b200 import ops
+    rng = np.random.default_rng(720 + m)
+    n, k = 512, 1024
+    raw, wf = make_weight_np(fmt, n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (m, k)))
+    lib, ctx = L.lib(), ops.Context.get(0)
+    assert lib.izb_linear_workspace_bytes(ops.WFMT[fmt], m, n, k) == (n * k * 2 if m > 64 else 0)
+    need = lib.izb_linear_workspace_bytes_ex(ops.WFMT[fmt], m, n, k, L.IZB_EPI_SWIGLU)
+    assert need == n * k * 2
+    ws = torch.empty(need, device=cuda, dtype=torch.uint8)
+    xd, wd = torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight(fmt, raw, cuda)
+    y = torch.empty(m, n // 2, device=cuda, dtype=torch.bfloat16)
+    a = ops.linear_args(xd, wd, fmt, n, k, y, epilogue="swiglu", workspace=ws)
+    assert lib.izb_linear(ctx.handle, None, C.byref(a)) == L.IZB_OK
+    ctx.check()
+    pre = o.linear(x, wf)
+    assert_matmul_close(y, o.silu_mul(pre[:, : n // 2], pre[:, n // 2:]), f"{fmt} M={m} swiglu through a queried workspace")
+    a.workspace, a.workspace_bytes = None, 0
+    assert lib.izb_linear(ctx.handle, None, C.byref(a)) == L.IZB_ERR_BAD_ARG   # the documented answer without it

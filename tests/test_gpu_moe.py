@@ -144,3 +144,35 @@ def test_moe_full_shape_properties(cuda):
             hid = ops.linear(x[tok:tok + 1], wgu[ex], epilogue="swiglu")
             acc += float(wts[tok, s]) * ops.linear(hid, wd[ex]).float()[0]
         assert torch.allclose(y[tok].float(), acc, rtol=2e-2, atol=2e-2 * float(acc.abs().max()))
+
+
+def test_moe_full_shape_sampled_tokens_against_oracle(cuda):
+    """128 experts, T = 4096: routing of every token bit-exact against the oracle's top-k of the
+    library's own logits, and the layer output of sampled tokens against the oracle's float64-checked
+    expert arithmetic (only the experts those tokens picked are copied to the host)."""
+    from izwi_b200 import moe, ops
+    gen = torch.Generator(device=cuda).manual_seed(44)
+    t, h, i, e, k = 4096, 2048, 768, 128, 8
+    rn = lambda *s, std=1.0: (torch.randn(*s, device=cuda, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
+    x = rn(t, h)
+    wr, br = rn(e, h, std=h ** -0.5), rn(e, std=0.5)
+    wgu, wd = rn(e, 2 * i, h, std=0.02), rn(e, h, i, std=0.02)
+    y, logits, idx, wts = moe.MoeLayer(wr, br, wgu, wd, k).forward(x)
+    ops.Context.get(0).check()
+    logits_np = logits.cpu().numpy()
+    want_idx, want_w = o.moe_topk(logits_np, k)
+    assert np.array_equal(idx.cpu().numpy(), want_idx)
+    assert np.abs(wts.cpu().numpy() - want_w).max() < 1e-6
+    assert_matmul_close(logits, o.moe_router_logits(to_np(x), to_np(wr), to_np(br)), "router logits, full shape")
+    toks = [0, 1, 2047, 4095]
+    want = np.zeros((len(toks), h), dtype=np.float32)
+    for n, tok in enumerate(toks):
+        xr = to_np(x[tok:tok + 1])
+        acc = np.zeros(h, dtype=np.float32)
+        for s in range(k):
+            ex = int(want_idx[tok, s])
+            gu = o.linear(xr, to_np(wgu[ex]))
+            hid = o.bf16_round(o.silu_mul(gu[:, :i], gu[:, i:]))
+            acc += want_w[tok, s] * o.bf16_round(o.linear(hid, to_np(wd[ex])))[0]
+        want[n] = acc
+    assert_matmul_close(y[toks], want, "moe layer output, full shape")

@@ -41,10 +41,12 @@ def test_matches_workspace_entry_point_twice_in_a_row(cuda, fmt):
         wd = upload_weight(fmt, raw, cuda)
         want = ops.linear(xd, wd, fmt, n=n, k=k)                  # existing entry point, caller workspace
         got = torch.full((m, n), float("nan"), device=cuda, dtype=torch.bfloat16)
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()            # the driver's figure: sees any cudaMalloc, not only torch's
         assert call_static(ctx, fmt, xd, wd, got, m, n, k) == 0
         ctx.check()
-        assert torch.cuda.memory_allocated() == before
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, "the call changed the device's free memory"
         rel, cos = o.rel_err_and_cosine(to_np(got), to_np(want))
         assert rel <= MAX_REL_ERR and cos >= MIN_COSINE, (call, rel, cos)
         assert torch.equal(got, want), f"call {call}: same kernels, same inputs, so the same bits"
@@ -68,3 +70,43 @@ def test_rejects_sizes_beyond_the_fixed_array(cuda):
     torch.cuda.synchronize()
     assert float(y.min()) == 7.0                                   # nothing was launched
     assert call_static(ctx, "bf16", x, w, y, 65, 64, 256) == L.IZB_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+@pytest.mark.parametrize("m", [5, 64, 130])
+def test_bias_epilogue_and_small_batches(cuda, fmt, m):
+    """Bias and a fused SwiGLU through the static entry point, for token counts on both sides of the 64
+    at which izb_linear would switch kernels: same bits as izb_linear with a caller workspace, and
+    within the matmul gates of the oracle."""
+    from izwi_b200 import _lib as L
+    from izwi_b200 import ops
+    ctx = ops.Context.get(0)
+    rng = np.random.default_rng(300 + m)
+    n, k = 1024, 512
+    raw, wf = make_weight_np(fmt, n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (m, k)))
+    b = bf16_np(rng.normal(0, 0.5, n))
+    xd = torch.from_numpy(x).to(cuda).to(torch.bfloat16)
+    bd = torch.from_numpy(b).to(cuda).to(torch.bfloat16)
+    wd = upload_weight(fmt, raw, cuda)
+    want = ops.linear(xd, wd, fmt, n=n, k=k, bias=bd, epilogue="swiglu")
+    got = torch.full((m, n // 2), float("nan"), device=cuda, dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert call_static(ctx, fmt, xd, wd, got, m, n, k, epilogue=L.IZB_EPI_SWIGLU, bias=bd) == 0
+    ctx.check()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.equal(got, want)
+    pre = o.linear(x, wf, b)
+    rel, cos = o.rel_err_and_cosine(to_np(got), o.silu_mul(pre[:, : n // 2], pre[:, n // 2:]))
+    assert rel <= MAX_REL_ERR and cos >= MIN_COSINE, (fmt, m, rel, cos)
+
+
+def test_rejects_rows_that_are_not_whole_blocks(cuda):
+    from izwi_b200 import _lib as L
+    from izwi_b200 import ops
+    ctx = ops.Context.get(0)
+    x = torch.zeros(70, 48, device=cuda, dtype=torch.bfloat16)
+    w = torch.zeros(2 * 48 // 32 * 34, device=cuda, dtype=torch.uint8)
+    y = torch.zeros(70, 2, device=cuda, dtype=torch.bfloat16)
+    assert call_static(ctx, "q8_0", x, w, y, 70, 2, 48) == L.IZB_ERR_BAD_ARG
