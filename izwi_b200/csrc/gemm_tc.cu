@@ -378,14 +378,26 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
 
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
-    // Accumulator width: the widest tile that still gives every SM work.
-    const long long m_tiles = seg_offsets ? (static_cast<long long>(M) + GT_BM - 1) / GT_BM + n_experts
+    // Accumulator width.  Tiles are dealt round-robin to one CTA per SM, so a pass costs
+    // ceil(tiles / SMs) rounds of one tile each; a tile's time grows with its width plus a fixed part
+    // (the 128-row operand is fetched whatever the width).  The width with the cheapest pass wins,
+    // wider on ties: 375 x 4096 takes 128 (96 tiles, one round) rather than 64 (192 tiles, two rounds).
+    // Grouped: the row tiles are only known on the device; half a tile per non-empty expert is the
+    // expected padding of ragged segments.
+    const long long m_tiles = seg_offsets ? (static_cast<long long>(M) + GT_BM - 1) / GT_BM + (std::min(n_experts, M) + 1) / 2
                                           : (static_cast<long long>(M) + GT_BM - 1) / GT_BM;
     int bn = 256;
-    while (bn > 64) {
-        const int oc = swiglu ? bn / 2 : bn;
-        if (m_tiles * ((n_out + oc - 1) / oc) >= ctx->sm_count) break;
-        bn >>= 1;
+    {
+        long long best = -1;
+        for (int cand = 256; cand >= 64; cand >>= 1) {
+            const int oc = swiglu ? cand / 2 : cand;
+            const long long tiles = m_tiles * ((n_out + oc - 1) / oc);
+            const long long cost = ((tiles + ctx->sm_count - 1) / ctx->sm_count) * (cand + 64);
+            if (best < 0 || cost < best) {
+                best = cost;
+                bn = cand;
+            }
+        }
     }
     const int out_cols = swiglu ? bn / 2 : bn;
     p.bn = bn;
