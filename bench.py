@@ -728,6 +728,8 @@ class TpStack:
         def step():
             for layer in self.layers:
                 layer.forward(x_a, x_o, x_m)
+            if self.comm is not None:
+                self.comm.join()       # the sums run on a second stream: the step ends when they have
         per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index, graph=self.use_graph and m <= 32)
         flops = 2.0 * m * shape.layers * shape.weights_per_layer
         out = {"value": round(m / (per_ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(per_ms, 5), "n_gpus": world,
@@ -736,6 +738,8 @@ class TpStack:
                "collective": "none (one GPU)" if world == 1 else self.layers[0].collective_name(m),
                "parallelism": f"tp{world}: column-split QKV and gate/up, row-split O and down, 2 sums per layer"}
         qkv, o, down = self.layers[0].forward(x_a, x_o, x_m)      # every rank: the sums are collective
+        if self.comm is not None:
+            self.comm.join()
         torch.cuda.synchronize()
         if rank == 0:
             w_qkv, w_o, w_gu, w_d = self.full0

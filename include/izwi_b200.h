@@ -197,7 +197,9 @@ size_t izb_static_scratch_bytes(void);
  *   - N*K*2 bytes must fit the array, else IZB_ERR_SCRATCH_TOO_SMALL and nothing is launched.
  *   - calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - the first call on a device looks up the array's device address (a one-off host-side
- *     query); make that first call outside any stream capture.
+ *     query); make that first call outside any stream capture.  The CUDA runtime loads a
+ *     library's device code on first use, so it is also during this first call that the array
+ *     becomes resident and the device's free memory drops by IZB_STATIC_SCRATCH_BYTES, once.
  *   - all calls on a device share the one array and it keeps the previous call's contents (each
  *     call rewrites the part it reads, so nothing needs clearing): two calls that may overlap
  *     on the GPU (different streams) race and must be ordered by the caller.
@@ -290,16 +292,28 @@ int32_t izb_ep_alltoall(izb_comm* comm, izb_stream stream, const void* send,
  * needs count*elem_size <= max_bytes, a 4-byte aligned buffer and a byte size that is a multiple
  * of 4; it can be replayed from a CUDA graph.
  * Messages above 1 MB (when max_bytes allows them: the sums after a row-split projection at
- * prefill sizes) take a two-shot bandwidth path instead: the operand is copied into the rank's
- * region, each rank reduces 1/world of it with peer loads and stores the result chunk into every
- * region, and the result is copied out (three launches; 16-byte aligned buffer, byte size a
- * multiple of 16, IZB_ERR_UNSUPPORTED otherwise).  No counterpart in the reference (single device). */
+ * prefill sizes) take a two-shot bandwidth path instead: the operand sits in the rank's region, each
+ * rank reduces 1/world of it with peer loads and stores the result chunk into every region, all in
+ * ONE kernel that returns when the whole result has landed (16-byte aligned buffer, byte size a
+ * multiple of 16, IZB_ERR_UNSUPPORTED otherwise).  izb_ar_allreduce copies the operand into the
+ * region and the result out of it (three launches).  A caller that can place the operand itself
+ * skips both copies: izb_ar_operand(which) is where the row-split projection writes its output
+ * (a local device pointer of max_bytes bytes; which = 0 or 1: two buffers, so that the sum of one
+ * projection can run on a second stream while the next projection writes the other),
+ * izb_ar_allreduce_region(which, count, dtype) sums it over the ranks (one launch), and the sum is
+ * read at izb_ar_result(which).  Calls on one buffer must be ordered by the caller (its operand is
+ * rewritten only after the previous sum on that buffer has completed; every rank issues the same
+ * calls in the same order); izb_ar_allreduce uses the same two buffers in turn, so do not interleave
+ * it with region calls.  No counterpart in the reference (single device). */
 typedef struct izb_ar izb_ar;
 int32_t izb_ar_create(izb_ctx* ctx, int32_t world, int32_t rank, size_t max_bytes, izb_ar** out);
 int32_t izb_ar_local_handle(izb_ar* ar, void* out_64_bytes);
 int32_t izb_ar_connect(izb_ar* ar, const void* handles_world_x_64_bytes);
 size_t izb_ar_max_bytes(const izb_ar* ar);
 int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count, int32_t dtype);
+void* izb_ar_operand(izb_ar* ar, int32_t which);
+const void* izb_ar_result(izb_ar* ar, int32_t which);
+int32_t izb_ar_allreduce_region(izb_ar* ar, izb_stream stream, int32_t which, int64_t count, int32_t dtype);
 int32_t izb_ar_destroy(izb_ar* ar);
 
 /* Expert-parallel dispatch and return over NVLink peer memory (no host read per layer, no NCCL

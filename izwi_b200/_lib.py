@@ -95,6 +95,9 @@ _SIGNATURES = {
     "izb_ar_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "izb_ar_max_bytes": (C.c_size_t, [C.c_void_p]),
     "izb_ar_allreduce": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32]),
+    "izb_ar_operand": (C.c_void_p, [C.c_void_p, C.c_int32]),
+    "izb_ar_result": (C.c_void_p, [C.c_void_p, C.c_int32]),
+    "izb_ar_allreduce_region": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32]),
     "izb_ar_destroy": (C.c_int32, [C.c_void_p]),
     "izb_silu_mul": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),

@@ -12,18 +12,17 @@
 
 constexpr int AR_MAX_WORLD = 8;
 constexpr int AR_MAX_CTAS = 16;
-constexpr size_t AR_LL_MAX_BYTES = 1 << 20;  // above this the two-shot bandwidth path takes over  // all CTAs must be resident at once (they wait on other GPUs)
+constexpr size_t AR_LL_MAX_BYTES = 1 << 20;  // above this the two-shot bandwidth path takes over
 
 struct ArDevState {
     unsigned int seq;   // one-shot calls completed so far on this rank (0 = none; slots start zeroed, so no stale word matches)
     unsigned int done;  // CTAs of the current one-shot call that finished reducing
-    // two-shot path (large messages)
-    unsigned int big_seq;                  // two-shot calls completed on this rank
-    unsigned int done_a, done_b, done_c;   // CTA counters of its three kernels
-    unsigned int pad_[10];
-    unsigned int flag_a[AR_MAX_WORLD];     // rank s has copied its operand into its region (value = call number)
-    unsigned int pad2_[8];
-    unsigned int flag_b[AR_MAX_WORLD];     // rank s has stored its reduced chunk into this region
+    // two-shot path (large messages): two operand / result buffers, each with its own call number
+    unsigned int big_seq[2];               // two-shot calls completed on this rank, per buffer
+    unsigned int done_b[2], done_c[2];     // CTA counters of the reduce kernel (chunk stored / leaving)
+    unsigned int pad_[8];
+    unsigned int flag_a[2][AR_MAX_WORLD];  // rank s has its operand ready in its region (value = call number)
+    unsigned int flag_b[2][AR_MAX_WORLD];  // rank s has stored its reduced chunk into this region
 };
 static_assert(sizeof(ArDevState) <= 256, "ArDevState must fit the region header");
 
@@ -35,8 +34,9 @@ struct izb_ar {
     izb_ctx* ctx;
     int world, rank;
     size_t slot_bytes;
-    size_t big_bytes;  // capacity of the two-shot operand / result buffers (0: path off)
-    size_t big_in, big_res;  // their byte offsets inside a region
+    size_t big_bytes;  // capacity of each two-shot operand / result buffer (0: path off)
+    size_t big_in[2], big_res[2];  // their byte offsets inside a region
+    int next_buf;      // buffer the next izb_ar_allreduce of a large message uses
     unsigned char* local;
     ArPeers peers;
     bool connected;
@@ -63,6 +63,8 @@ __device__ __forceinline__ uint2 ld_pair(const uint2* p) {
 template <bool F32>
 __global__ void __launch_bounds__(256) peer_allreduce_kernel(ArPeers peers, int world, int rank, size_t slot_bytes,
                                                              uint32_t* __restrict__ buf, long long n_words, int* status) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();  // buf holds the partial sums of the kernel before this one
     ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
     const unsigned int seq = st->seq + 1;  // written only by the previous call's last CTA
     const unsigned int parity = seq & 1u;
@@ -122,13 +124,20 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(ArPeers peers, int 
 
 // ---------------------------------------------------------------------------------------------
 // Two-shot all-reduce for large messages (the sums after a row-split projection at prefill sizes):
-// bandwidth-bound, so every byte crosses NVLink once in each direction.  Three launches:
-//   a. copy the operand into this rank's region, fence, raise flag_a on every rank;
-//   b. wait for all flag_a; reduce this rank's 1/world chunk by loading it from every region (peer
-//      loads), summing in fp32 in rank order, and storing the result chunk into every region;
-//      fence, raise flag_b on every rank;
-//   c. wait for all flag_b; copy the assembled result out.
-// Stream order is the barrier inside a GPU; the flags (the call number) order the GPUs.
+// bandwidth-bound, so every byte crosses NVLink once in each direction.  The operand lives in this
+// rank's region (the projection writes it there, or izb_ar_allreduce copies it in) and the result is
+// assembled in the region too, so ONE kernel does the exchange:
+//   1. CTA 0 raises flag_a[buf][rank] = call on every rank: "my operand is complete" (it is: the
+//      kernel runs after its producer in stream order);
+//   2. every CTA waits for all flag_a, then reduces its share of this rank's 1/world chunk: loads the
+//      chunk from every region (peer loads), sums in fp32 in rank order (every rank gets the same
+//      bits), stores the result into the result buffer of every region (peer stores);
+//   3. system fence; the last CTA to finish raises flag_b[buf][rank] = call on every rank;
+//   4. CTA 0 stays until all flag_b are up, so the kernel's completion means the whole result has
+//      landed here; the last CTA out advances the buffer's call number.
+// Two buffers (buf 0 / 1) let the sum of one projection overlap the next projection's writes.
+// Stream order is the barrier inside a GPU; the flags (the call number) order the GPUs.  All waits
+// are bounded.  CTAs never wait on sibling CTAs, so the grid need not be co-resident.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void ar_st_flag(unsigned int* p, unsigned int v) {
     asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -144,29 +153,13 @@ __device__ __forceinline__ uint4 ar_ld_peer(const uint4* p) {  // not through L1
     return v;
 }
 
-// After a CTA's stores: system-scope fence, count the CTA in; the last one raises flag[rank] = value on every rank.
-__device__ __forceinline__ void ar_signal_all(unsigned int* counter, const ArPeers& peers, size_t flag_field, int world, int rank,
-                                              unsigned int value) {
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int prev = atomicAdd(counter, 1u);
-        if (prev == gridDim.x - 1) {
-            *counter = 0;
-            __threadfence_system();
-            for (int p = 0; p < world; ++p)
-                ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + p) % world] + flag_field) + rank, value);
-        }
-    }
-}
-
 // Threads 0 .. world-1 of the CTA wait (bounded) for flag[s] == value; returns false on time-out.
-__device__ __forceinline__ bool ar_wait_all(const unsigned char* local, size_t flag_field, int world, unsigned int value, int* status) {
+__device__ __forceinline__ bool ar_wait_all(const unsigned int* flags, int world, unsigned int value, int* status) {
     __shared__ int timed_out;
     if (threadIdx.x == 0) timed_out = 0;
     __syncthreads();
     if (static_cast<int>(threadIdx.x) < world) {
-        const unsigned int* f = reinterpret_cast<const unsigned int*>(local + flag_field) + threadIdx.x;
+        const unsigned int* f = flags + threadIdx.x;
         const long long t0 = clock64();
         while (ar_ld_flag(f) != value) {
             if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
@@ -181,76 +174,121 @@ __device__ __forceinline__ bool ar_wait_all(const unsigned char* local, size_t f
     return timed_out == 0;
 }
 
-__global__ void __launch_bounds__(512)
-    ar2_copy_in_kernel(ArPeers peers, int world, int rank, size_t big_in, const uint4* __restrict__ buf, long long n_units) {
-    ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
-    const unsigned int call = st->big_seq + 1;
-    uint4* dst = reinterpret_cast<uint4*>(peers.base[rank] + big_in);
-    for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < n_units;
-         u += static_cast<long long>(gridDim.x) * blockDim.x)
-        dst[u] = buf[u];
-    ar_signal_all(&st->done_a, peers, offsetof(ArDevState, flag_a), world, rank, call);
-}
+constexpr int AR2_THREADS = 256;
+constexpr int AR2_UNROLL = 4;  // 16-byte units per thread and pass: world x 4 peer loads in flight per thread
 
 template <bool F32>
-__global__ void __launch_bounds__(512)
-    ar2_reduce_kernel(ArPeers peers, int world, int rank, size_t big_in, size_t big_res, long long n_units, int* status) {
+__global__ void __launch_bounds__(AR2_THREADS)
+    ar2_region_kernel(ArPeers peers, int world, int rank, int buf, size_t big_in, size_t big_res, long long n_units, int* status) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();  // the operand was written by the kernel before this one
     ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
-    const unsigned int call = st->big_seq + 1;
-    const bool ok = ar_wait_all(peers.base[rank], offsetof(ArDevState, flag_a), world, call, status);
+    const unsigned int call = st->big_seq[buf] + 1;
+    const size_t flag_a = offsetof(ArDevState, flag_a) + sizeof(unsigned int) * AR_MAX_WORLD * buf;
+    const size_t flag_b = offsetof(ArDevState, flag_b) + sizeof(unsigned int) * AR_MAX_WORLD * buf;
+    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < world) {
+        __threadfence_system();
+        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + flag_a) + rank, call);
+    }
+    const bool ok = ar_wait_all(reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_a), world, call, status);
     if (ok) {
         const long long per = (n_units + world - 1) / world;
         const long long lo = per * rank, hi = lo + per < n_units ? lo + per : n_units;
-        for (long long u = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < hi;
-             u += static_cast<long long>(gridDim.x) * blockDim.x) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-            for (int r = 0; r < world; ++r) {
-                const uint4 v = ar_ld_peer(reinterpret_cast<const uint4*>(peers.base[r] + big_in) + u);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const long long stride = static_cast<long long>(gridDim.x) * AR2_THREADS * AR2_UNROLL;
+        for (long long u0 = lo + static_cast<long long>(blockIdx.x) * AR2_THREADS * AR2_UNROLL + threadIdx.x; u0 < hi; u0 += stride) {
+            float acc[AR2_UNROLL][8];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (F32) {
-                        acc[j] += __uint_as_float(w[j]);
-                    } else {
-                        acc[2 * j] += izb::bf16_lo_to_f32(w[j]);
-                        acc[2 * j + 1] += izb::bf16_hi_to_f32(w[j]);
+            for (int j = 0; j < AR2_UNROLL; ++j)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+            for (int r = 0; r < world; ++r) {
+                const uint4* src = reinterpret_cast<const uint4*>(peers.base[r] + big_in);
+                uint4 v[AR2_UNROLL];
+#pragma unroll
+                for (int j = 0; j < AR2_UNROLL; ++j) {
+                    const long long u = u0 + static_cast<long long>(j) * AR2_THREADS;
+                    v[j] = u < hi ? ar_ld_peer(src + u) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int j = 0; j < AR2_UNROLL; ++j) {
+                    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (F32) {
+                            acc[j][e] += __uint_as_float(w[e]);
+                        } else {
+                            acc[j][2 * e] += izb::bf16_lo_to_f32(w[e]);
+                            acc[j][2 * e + 1] += izb::bf16_hi_to_f32(w[e]);
+                        }
                     }
                 }
             }
-            uint4 o;
-            if (F32) {
-                o = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
-            } else {
-                o = make_uint4(izb::pack_bf16x2(acc[0], acc[1]), izb::pack_bf16x2(acc[2], acc[3]), izb::pack_bf16x2(acc[4], acc[5]),
-                               izb::pack_bf16x2(acc[6], acc[7]));
+#pragma unroll
+            for (int j = 0; j < AR2_UNROLL; ++j) {
+                const long long u = u0 + static_cast<long long>(j) * AR2_THREADS;
+                if (u >= hi) continue;
+                uint4 o;
+                if (F32) {
+                    o = make_uint4(__float_as_uint(acc[j][0]), __float_as_uint(acc[j][1]), __float_as_uint(acc[j][2]),
+                                   __float_as_uint(acc[j][3]));
+                } else {
+                    o = make_uint4(izb::pack_bf16x2(acc[j][0], acc[j][1]), izb::pack_bf16x2(acc[j][2], acc[j][3]),
+                                   izb::pack_bf16x2(acc[j][4], acc[j][5]), izb::pack_bf16x2(acc[j][6], acc[j][7]));
+                }
+                for (int p = 0; p < world; ++p) reinterpret_cast<uint4*>(peers.base[(rank + p) % world] + big_res)[u] = o;
             }
-            for (int p = 0; p < world; ++p) reinterpret_cast<uint4*>(peers.base[(rank + p) % world] + big_res)[u] = o;
         }
     }
-    ar_signal_all(&st->done_b, peers, offsetof(ArDevState, flag_b), world, rank, call);
-}
-
-__global__ void __launch_bounds__(512)
-    ar2_copy_out_kernel(ArPeers peers, int world, int rank, size_t big_res, uint4* __restrict__ buf, long long n_units, int* status) {
-    ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
-    const unsigned int call = st->big_seq + 1;
-    if (ar_wait_all(peers.base[rank], offsetof(ArDevState, flag_b), world, call, status)) {
-        const uint4* src = reinterpret_cast<const uint4*>(peers.base[rank] + big_res);
-        for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < n_units;
-             u += static_cast<long long>(gridDim.x) * blockDim.x)
-            buf[u] = ar_ld_peer(src + u);
+    // this CTA's result stores are performed system-wide before it is counted in
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int last_to_store;
+    if (threadIdx.x == 0) {
+        last_to_store = atomicAdd(&st->done_b[buf], 1u) == gridDim.x - 1;
+        if (last_to_store) st->done_b[buf] = 0;
     }
-    // the last CTA out closes the call
+    __syncthreads();
+    if (last_to_store && static_cast<int>(threadIdx.x) < world) {
+        __threadfence_system();
+        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + threadIdx.x) % world] + flag_b) + rank, call);
+    }
+    // CTA 0 holds the kernel open until every rank's chunk has landed in this region
+    if (blockIdx.x == 0) (void)ar_wait_all(reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_b), world, call, status);
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(&st->done_c, 1u) == gridDim.x - 1) {
-            st->done_c = 0;
+        if (atomicAdd(&st->done_c[buf], 1u) == gridDim.x - 1) {
+            st->done_c[buf] = 0;
             __threadfence();
-            st->big_seq = call;
+            st->big_seq[buf] = call;
         }
     }
+}
+
+// Plain device-local copy in 16-byte units (operand into the region, result out of it).
+__global__ void __launch_bounds__(512) ar2_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n_units) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
+    for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < n_units;
+         u += static_cast<long long>(gridDim.x) * blockDim.x)
+        dst[u] = src[u];
+}
+
+int ar2_launch(izb_ar* ar, cudaStream_t st, int buf, size_t bytes, int dtype) {
+    const long long n_units = static_cast<long long>(bytes / 16);
+    const long long chunk = (n_units + ar->world - 1) / ar->world;
+    long long g = (chunk + AR2_THREADS * AR2_UNROLL - 1) / (AR2_THREADS * AR2_UNROLL);
+    const int cap = ar->ctx->sm_count * 2;
+    const int grid = static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+    int* status = ar->ctx->d_status + 2;
+    if (dtype == IZB_F32)
+        IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_region_kernel<true>, dim3(grid), dim3(AR2_THREADS), 0, st, ar->peers, ar->world,
+                                         ar->rank, buf, ar->big_in[buf], ar->big_res[buf], n_units, status));
+    else
+        IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_region_kernel<false>, dim3(grid), dim3(AR2_THREADS), 0, st, ar->peers, ar->world,
+                                         ar->rank, buf, ar->big_in[buf], ar->big_res[buf], n_units, status));
+    ar->ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
 }
 
 }  // namespace
@@ -270,12 +308,15 @@ int32_t izb_ar_create(izb_ctx* ctx, int32_t world, int32_t rank, size_t max_byte
     const size_t ll_max = max_bytes < AR_LL_MAX_BYTES ? max_bytes : AR_LL_MAX_BYTES;
     ar->slot_bytes = (2 * ll_max + 255) / 256 * 256;  // every 4 payload bytes travel as an 8-byte pair
     ar->big_bytes = max_bytes > AR_LL_MAX_BYTES ? (max_bytes + 255) / 256 * 256 : 0;
-    ar->big_in = AR_HEADER + 2 * static_cast<size_t>(world) * ar->slot_bytes;
-    ar->big_res = ar->big_in + ar->big_bytes;
+    ar->big_in[0] = AR_HEADER + 2 * static_cast<size_t>(world) * ar->slot_bytes;
+    ar->big_in[1] = ar->big_in[0] + ar->big_bytes;
+    ar->big_res[0] = ar->big_in[1] + ar->big_bytes;
+    ar->big_res[1] = ar->big_res[0] + ar->big_bytes;
+    ar->next_buf = 0;
     ar->connected = false;
     std::memset(&ar->peers, 0, sizeof(ar->peers));
-    const size_t total = ar->big_res + ar->big_bytes;
-    const size_t zeroed = ar->big_in;  // header and one-shot slots; the two-shot buffers are written before they are read
+    const size_t total = ar->big_res[1] + ar->big_bytes;
+    const size_t zeroed = ar->big_in[0];  // header and one-shot slots; the two-shot buffers are written before they are read
     int cur = -1;
     cudaGetDevice(&cur);
     if (cur != ctx->device) cudaSetDevice(ctx->device);
@@ -337,44 +378,57 @@ int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count
     const size_t bytes = static_cast<size_t>(count) * (dtype == IZB_F32 ? 4 : 2);
     if (!buf || !izb_aligned(buf, 4) || bytes % 4 != 0) return IZB_ERR_BAD_ARG;
     if (2 * bytes > ar->slot_bytes) {
-        // two-shot path: whole 16-byte units, operand 16-byte aligned
+        // two-shot path: whole 16-byte units, operand 16-byte aligned; copy in, exchange, copy out
         if (bytes > ar->big_bytes) return IZB_ERR_UNSUPPORTED;
         if (bytes % 16 != 0 || !izb_aligned(buf, 16)) return IZB_ERR_UNSUPPORTED;
         const long long n_units = static_cast<long long>(bytes / 16);
         cudaStream_t st = static_cast<cudaStream_t>(stream);
-        int* status = ar->ctx->d_status + 2;
+        const int b = ar->next_buf;
+        ar->next_buf ^= 1;
         const int copy_grid = ar->ctx->sm_count * 2;
-        const long long chunk = (n_units + ar->world - 1) / ar->world;
-        long long rg = (chunk + 511) / 512;
-        const int reduce_grid = static_cast<int>(rg < 1 ? 1 : (rg > ar->ctx->sm_count * 2 ? ar->ctx->sm_count * 2 : rg));
-        ar2_copy_in_kernel<<<copy_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_in, static_cast<const uint4*>(buf),
-                                                     n_units);
-        IZB_CUDA_TRY(cudaGetLastError());
-        if (dtype == IZB_F32)
-            ar2_reduce_kernel<true><<<reduce_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_in, ar->big_res, n_units, status);
-        else
-            ar2_reduce_kernel<false><<<reduce_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_in, ar->big_res, n_units, status);
-        IZB_CUDA_TRY(cudaGetLastError());
-        ar2_copy_out_kernel<<<copy_grid, 512, 0, st>>>(ar->peers, ar->world, ar->rank, ar->big_res, static_cast<uint4*>(buf), n_units,
-                                                      status);
-        IZB_CUDA_TRY(cudaGetLastError());
-        ar->ctx->launches.fetch_add(3, std::memory_order_relaxed);
+        IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_copy_kernel, dim3(copy_grid), dim3(512), 0, st, static_cast<const uint4*>(buf),
+                                         reinterpret_cast<uint4*>(ar->local + ar->big_in[b]), n_units));
+        const int rc = ar2_launch(ar, st, b, bytes, dtype);
+        if (rc != IZB_OK) return rc;
+        IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_copy_kernel, dim3(copy_grid), dim3(512), 0, st,
+                                         reinterpret_cast<const uint4*>(ar->local + ar->big_res[b]), static_cast<uint4*>(buf), n_units));
+        ar->ctx->launches.fetch_add(2, std::memory_order_relaxed);
         return IZB_OK;
     }
     const long long n_words = static_cast<long long>(bytes / 4);
-    // latency, not bandwidth: one word per thread while the CTA limit allows (an 8 KB message = 8 CTAs)
+    // latency, not bandwidth: one word per thread.  Every CTA first pushes, then polls words that peers'
+    // CTAs push, so all CTAs of all ranks must get to run: the grid is capped at one CTA per SM, which
+    // is resident at once on a GPU this stream has to itself (a few dozen KB need 8 .. 32 CTAs).
     int grid = static_cast<int>((n_words + 255) / 256);
-    grid = grid < 1 ? 1 : (grid > AR_MAX_CTAS ? AR_MAX_CTAS : grid);
+    const int cap = n_words <= 256 * AR_MAX_CTAS ? AR_MAX_CTAS : ar->ctx->sm_count;
+    grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == IZB_F32)
-        peer_allreduce_kernel<true><<<grid, 256, 0, s>>>(ar->peers, ar->world, ar->rank, ar->slot_bytes,
-                                                         static_cast<uint32_t*>(buf), n_words, ar->ctx->d_status + 2);
+        IZB_CUDA_TRY(izb::launch_chained(ar->ctx, peer_allreduce_kernel<true>, dim3(grid), dim3(256), 0, s, ar->peers, ar->world,
+                                         ar->rank, ar->slot_bytes, static_cast<uint32_t*>(buf), n_words, ar->ctx->d_status + 2));
     else
-        peer_allreduce_kernel<false><<<grid, 256, 0, s>>>(ar->peers, ar->world, ar->rank, ar->slot_bytes,
-                                                          static_cast<uint32_t*>(buf), n_words, ar->ctx->d_status + 2);
-    IZB_CUDA_TRY(cudaGetLastError());
+        IZB_CUDA_TRY(izb::launch_chained(ar->ctx, peer_allreduce_kernel<false>, dim3(grid), dim3(256), 0, s, ar->peers, ar->world,
+                                         ar->rank, ar->slot_bytes, static_cast<uint32_t*>(buf), n_words, ar->ctx->d_status + 2));
     ar->ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
+}
+
+void* izb_ar_operand(izb_ar* ar, int32_t which) {
+    return (ar && ar->big_bytes && (which == 0 || which == 1)) ? ar->local + ar->big_in[which] : nullptr;
+}
+
+const void* izb_ar_result(izb_ar* ar, int32_t which) {
+    return (ar && ar->big_bytes && (which == 0 || which == 1)) ? ar->local + ar->big_res[which] : nullptr;
+}
+
+int32_t izb_ar_allreduce_region(izb_ar* ar, izb_stream stream, int32_t which, int64_t count, int32_t dtype) {
+    if (!ar || count < 0 || (dtype != IZB_BF16 && dtype != IZB_F32) || (which != 0 && which != 1)) return IZB_ERR_BAD_ARG;
+    if (!ar->connected || !ar->big_bytes) return IZB_ERR_BAD_ARG;
+    if (count == 0) return IZB_OK;
+    const size_t bytes = static_cast<size_t>(count) * (dtype == IZB_F32 ? 4 : 2);
+    if (bytes > ar->big_bytes) return IZB_ERR_UNSUPPORTED;
+    if (bytes % 16 != 0) return IZB_ERR_UNSUPPORTED;
+    return ar2_launch(ar, static_cast<cudaStream_t>(stream), which, bytes, dtype);
 }
 
 int32_t izb_ar_destroy(izb_ar* ar) {

@@ -172,8 +172,10 @@ class Comm:
                 "izb_ep_alltoall")
 
     def enable_peer_allreduce(self, max_bytes: int = 1 << 20):
-        """Sets up the one-shot all-reduce over NVLink peer memory for messages up to max_bytes;
-        larger ones keep going through NCCL.  Collective: every rank must call it."""
+        """Sets up the all-reduce over NVLink peer memory for messages up to max_bytes (one-shot up to
+        1 MB, two-shot above); larger ones keep going through NCCL.  Also creates the second stream on
+        which `allreduce_async_` / `reduce_region_async` run the sums.  Collective: every rank must call it."""
+        import torch
         import torch.distributed as dist
 
         from . import _lib as L
@@ -186,6 +188,79 @@ class Comm:
         L.check(L.lib().izb_ar_connect(ar, b"".join(every)), "izb_ar_connect")
         dist.barrier()
         self.ar, self.ar_max = ar, max_bytes
+        self.side = torch.cuda.Stream(device=self.ctx.device)
+        self._pending = []            # events of sums still running on the side stream
+        self._region_done = [None, None]
+
+    # -- sums that overlap the next projection: issued on the side stream, joined by the caller --
+    def _fork(self):
+        import torch
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self.side.wait_event(ev)
+
+    def allreduce_async_(self, t):
+        """allreduce_(t) on the side stream, after everything issued so far on the current stream.
+        The current stream sees the sum after `join()`."""
+        import torch
+        self._fork()
+        with torch.cuda.stream(self.side):
+            self.allreduce_(t)
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+        self._pending.append(ev)
+        return t
+
+    def region_ok(self, n_elems: int, elem_size: int = 2) -> bool:
+        """Whether a sum of this size can take the copy-free two-shot path through the region."""
+        nbytes = n_elems * elem_size
+        return bool(getattr(self, "ar", None)) and (1 << 20) < nbytes <= self.ar_max and nbytes % 16 == 0
+
+    def region_views(self, which: int, rows: int, cols: int):
+        """(operand, result) bf16 [rows, cols] views of two-shot buffer `which` inside this rank's region."""
+        import torch
+
+        from . import _lib as L
+
+        class _Raw:
+            def __init__(self, ptr, n):
+                self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<u2", "data": (ptr, False), "version": 2}
+        n = rows * cols
+        dev = torch.device("cuda", self.ctx.device)
+        op = torch.as_tensor(_Raw(L.lib().izb_ar_operand(self.ar, which), n), device=dev).view(torch.bfloat16).view(rows, cols)
+        res = torch.as_tensor(_Raw(L.lib().izb_ar_result(self.ar, which), n), device=dev).view(torch.bfloat16).view(rows, cols)
+        return op, res
+
+    def wait_region_free(self, which: int):
+        """The current stream waits until the previous sum on buffer `which` has completed (its operand
+        may then be rewritten)."""
+        import torch
+        ev = self._region_done[which]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def reduce_region_async(self, which: int, n_elems: int):
+        """Sums buffer `which` over the ranks on the side stream, after everything issued so far on the
+        current stream (the projection that wrote the operand)."""
+        import torch
+
+        from . import _lib as L
+        self._fork()
+        with torch.cuda.stream(self.side):
+            L.check(L.lib().izb_ar_allreduce_region(self.ar, C.c_void_p(self.side.cuda_stream), which, n_elems, L.IZB_BF16),
+                    "izb_ar_allreduce_region")
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+        self._region_done[which] = ev
+        self._pending.append(ev)
+
+    def join(self):
+        """The current stream waits for every sum issued on the side stream so far."""
+        import torch
+        cur = torch.cuda.current_stream()
+        for ev in self._pending:
+            cur.wait_event(ev)
+        self._pending = []
 
     def enable_peer_ep(self, n_experts: int, hidden: int, max_tokens_local: int, top_k: int):
         """Sets up expert-parallel dispatch / return over NVLink peer memory (izb_ep_*) for layers of
@@ -228,13 +303,18 @@ class TpDecoderLayer:
     an all-reduce, column-split gate/up (pairs kept together) with SwiGLU, row-split down with an
     all-reduce.  Attention itself is outside this path: O takes the rank's slice of its input."""
 
-    def __init__(self, comm: Comm | None, w_qkv, w_o, w_gate_up, w_down):
+    def __init__(self, comm: Comm | None, w_qkv, w_o, w_gate_up, w_down, overlap: bool = True):
         self.comm = comm
+        # overlap: run the sums on the communicator's side stream, concurrently with the projections that
+        # follow them.  In this linear-stack workload nothing inside a step consumes a sum (attention
+        # and norms are outside it), so the caller joins at the end of the step (comm.join()); a full
+        # decoder layer would consume the O sum before gate/up and must join there instead.
+        self.overlap = overlap
         self.w_qkv, self.w_o, self.w_gate_up, self.w_down = w_qkv, w_o, w_gate_up, w_down
         self.inter_local = w_gate_up.shape[0] // 2
 
     @classmethod
-    def from_full(cls, comm, shape, w_qkv, w_o, w_gate_up, w_down, tp: int, rank: int):
+    def from_full(cls, comm, shape, w_qkv, w_o, w_gate_up, w_down, tp: int, rank: int, overlap: bool = True):
         import torch
         dev = w_qkv.device
         rows = torch.from_numpy(tp_qkv_rows(shape.q_heads, shape.kv_heads, shape.head_dim, tp, rank)).to(dev)
@@ -242,7 +322,7 @@ class TpDecoderLayer:
         olo, ohi = tp_row_split_cols(w_o.shape[1], tp, rank)
         dlo, dhi = tp_row_split_cols(w_down.shape[1], tp, rank)
         return cls(comm, w_qkv[rows].contiguous(), w_o[:, olo:ohi].contiguous(), w_gate_up[gu].contiguous(),
-                   w_down[:, dlo:dhi].contiguous())
+                   w_down[:, dlo:dhi].contiguous(), overlap=overlap)
 
     def collective_name(self, m: int) -> str:
         """Which sum the O and down outputs of `m` token rows go through."""
@@ -262,14 +342,32 @@ class TpDecoderLayer:
         m = x_mlp_in.shape[0]
         if m <= 32:
             return self._forward_decode(x_attn_in, x_o_in, x_mlp_in)
+        comm = self.comm
+        h = self.w_o.shape[0]
+        if comm is not None and self.overlap and comm.region_ok(m * h):
+            # The row-split projections write their partial sums straight into this rank's peer-mapped
+            # region and the sums run on the side stream (one kernel each, two buffers), so the sum of O
+            # overlaps the gate/up projection and the sum of down overlaps the next layer's QKV and O.
+            # The returned o / down are views of the region, valid after comm.join().
+            op0, res0 = comm.region_views(0, m, h)
+            op1, res1 = comm.region_views(1, m, h)
+            qkv = ops.linear(x_attn_in, self.w_qkv)
+            comm.wait_region_free(0)
+            ops.linear(x_o_in, self.w_o, out=op0)
+            comm.reduce_region_async(0, m * h)
+            hidden = ops.linear(x_mlp_in, self.w_gate_up, epilogue="swiglu")
+            comm.wait_region_free(1)
+            ops.linear(hidden, self.w_down, out=op1)
+            comm.reduce_region_async(1, m * h)
+            return qkv, res0, res1
         qkv = ops.linear(x_attn_in, self.w_qkv)
         o = ops.linear(x_o_in, self.w_o)
-        if self.comm is not None:
-            self.comm.allreduce_(o)
+        if comm is not None:
+            comm.allreduce_(o)
         hidden = ops.linear(x_mlp_in, self.w_gate_up, epilogue="swiglu")
         down = ops.linear(hidden, self.w_down)
-        if self.comm is not None:
-            self.comm.allreduce_(down)
+        if comm is not None:
+            comm.allreduce_(down)
         return qkv, o, down
 
     def _forward_decode(self, x_attn_in, x_o_in, x_mlp_in):
@@ -293,13 +391,17 @@ class TpDecoderLayer:
             second = ops.LinearGroup([ops.linear_args(hidden, self.w_down, "bf16", *self.w_down.shape, down)], dev)
             st = self._decode_state = dict(key=key, qkv=qkv, o=o, gu=gu, hidden=hidden, down=down, first=first,
                                            second=second, keep=(x_attn_in, x_o_in, x_mlp_in))
+        comm = self.comm
+        overlap = comm is not None and self.overlap and getattr(comm, "side", None) is not None
+        if overlap:
+            comm.join()                      # the previous step's sums read the buffers this step rewrites
         st["first"].launch()
-        if self.comm is not None:
-            self.comm.allreduce_(st["o"])
+        if comm is not None:
+            (comm.allreduce_async_ if overlap else comm.allreduce_)(st["o"])
         ops.silu_mul(st["gu"][:, : self.inter_local], st["gu"][:, self.inter_local:], out=st["hidden"])
         st["second"].launch()
-        if self.comm is not None:
-            self.comm.allreduce_(st["down"])
+        if comm is not None:
+            (comm.allreduce_async_ if overlap else comm.allreduce_)(st["down"])
         return st["qkv"], st["o"], st["down"]
 
 
