@@ -730,7 +730,10 @@ class TpStack:
                 layer.forward(x_a, x_o, x_m)
             if self.comm is not None:
                 self.comm.join()       # the sums run on a second stream: the step ends when they have
-        per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index, graph=self.use_graph and m <= 32)
+        if self.comm is not None:
+            self.comm.reset_events()
+        # a step is a fixed sequence of launches on two streams: captured once, replayed as a CUDA graph
+        per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index, graph=self.use_graph)
         flops = 2.0 * m * shape.layers * shape.weights_per_layer
         out = {"value": round(m / (per_ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(per_ms, 5), "n_gpus": world,
                "scaling": "strong", "launches_per_step": launches, "tflops_total": round(flops / (per_ms * 1e-3) / 1e12, 2),
@@ -793,7 +796,9 @@ class EpStack:
         def step():
             for layer in self.layers:
                 layer.forward(x)
-        per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index)
+        # with the exchange over peer memory no step needs the host (counts stay on the device), so the
+        # whole step replays from a CUDA graph; the NCCL path reads sizes on the host every layer
+        per_ms, launches = _timed_case(step, steps, warmup, world, self.device.index, graph=not (world > 1 and self.nccl))
         flops = 2.0 * t_total * self.K * 3 * self.I * self.H * self.LAYERS
         out = {"value": round(t_total / (per_ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(per_ms, 5),
                "n_gpus": world, "scaling": "strong", "launches_per_step": launches, "layers": self.LAYERS,

@@ -389,7 +389,10 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     int bn = 256;
     {
         long long best = -1;
-        for (int cand = 256; cand >= 64; cand >>= 1) {
+        static const int widths[4] = {256, 192, 128, 64};  // 192: not for SwiGLU (its halves must be whole 32-column groups)
+        for (int wi = 0; wi < 4; ++wi) {
+            const int cand = widths[wi];
+            if (swiglu && cand == 192) continue;
             const int oc = swiglu ? cand / 2 : cand;
             const long long tiles = m_tiles * ((n_out + oc - 1) / oc);
             const long long cost = ((tiles + ctx->sm_count - 1) / ctx->sm_count) * (cand + 64);

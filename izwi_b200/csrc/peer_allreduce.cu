@@ -174,7 +174,9 @@ __device__ __forceinline__ bool ar_wait_all(const unsigned int* flags, int world
     return timed_out == 0;
 }
 
-constexpr int AR2_THREADS = 256;
+// 128 threads x 64 registers: small enough to share an SM with a CTA of the tcgen05 GEMM (320 threads x
+// 166 registers, nearly all of the shared memory), so a sum on a second stream really runs beside it.
+constexpr int AR2_THREADS = 128;
 constexpr int AR2_UNROLL = 4;  // 16-byte units per thread and pass: world x 4 peer loads in flight per thread
 
 template <bool F32>

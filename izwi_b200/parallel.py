@@ -193,6 +193,25 @@ class Comm:
         self._region_done = [None, None]
 
     # -- sums that overlap the next projection: issued on the side stream, joined by the caller --
+    # Events are kept with a note of whether they were recorded while the stream was being captured into
+    # a CUDA graph.  A capture may only wait on events of the same capture (torch synchronises the device
+    # before capturing, so earlier work is complete anyway), and eager code must not wait on events that
+    # exist only inside a graph (replays are ordered on their stream as a whole).
+    @staticmethod
+    def _record(stream):
+        import torch
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        return (ev, torch.cuda.is_current_stream_capturing())
+
+    @staticmethod
+    def wait_for(marked):
+        """The current stream waits for an event returned by allreduce_async_ / kept by this class."""
+        import torch
+        ev, captured = marked
+        if captured == torch.cuda.is_current_stream_capturing():
+            torch.cuda.current_stream().wait_event(ev)
+
     def _fork(self):
         import torch
         ev = torch.cuda.Event()
@@ -201,15 +220,14 @@ class Comm:
 
     def allreduce_async_(self, t):
         """allreduce_(t) on the side stream, after everything issued so far on the current stream.
-        The current stream sees the sum after `join()`."""
+        The current stream sees the sum after `join()`, or after waiting for the returned event."""
         import torch
         self._fork()
         with torch.cuda.stream(self.side):
             self.allreduce_(t)
-            ev = torch.cuda.Event()
-            ev.record(self.side)
+            ev = self._record(self.side)
         self._pending.append(ev)
-        return t
+        return ev
 
     def region_ok(self, n_elems: int, elem_size: int = 2) -> bool:
         """Whether a sum of this size can take the copy-free two-shot path through the region."""
@@ -234,10 +252,9 @@ class Comm:
     def wait_region_free(self, which: int):
         """The current stream waits until the previous sum on buffer `which` has completed (its operand
         may then be rewritten)."""
-        import torch
         ev = self._region_done[which]
         if ev is not None:
-            torch.cuda.current_stream().wait_event(ev)
+            self.wait_for(ev)
 
     def reduce_region_async(self, which: int, n_elems: int):
         """Sums buffer `which` over the ranks on the side stream, after everything issued so far on the
@@ -249,17 +266,22 @@ class Comm:
         with torch.cuda.stream(self.side):
             L.check(L.lib().izb_ar_allreduce_region(self.ar, C.c_void_p(self.side.cuda_stream), which, n_elems, L.IZB_BF16),
                     "izb_ar_allreduce_region")
-            ev = torch.cuda.Event()
-            ev.record(self.side)
+            ev = self._record(self.side)
         self._region_done[which] = ev
         self._pending.append(ev)
 
+    def reset_events(self):
+        """Forgets the recorded events after a device-wide synchronise (call between a run that was
+        captured into a CUDA graph and the next capture: events of an ended capture cannot be waited on)."""
+        import torch
+        torch.cuda.synchronize()
+        self._pending = []
+        self._region_done = [None, None]
+
     def join(self):
         """The current stream waits for every sum issued on the side stream so far."""
-        import torch
-        cur = torch.cuda.current_stream()
         for ev in self._pending:
-            cur.wait_event(ev)
+            self.wait_for(ev)
         self._pending = []
 
     def enable_peer_ep(self, n_experts: int, hidden: int, max_tokens_local: int, top_k: int):
@@ -394,14 +416,23 @@ class TpDecoderLayer:
         comm = self.comm
         overlap = comm is not None and self.overlap and getattr(comm, "side", None) is not None
         if overlap:
-            comm.join()                      # the previous step's sums read the buffers this step rewrites
+            # this layer's previous sums (the step before) still own the buffers this step rewrites
+            for ev in st.get("events", ()):
+                comm.wait_for(ev)
+            st["events"] = []
         st["first"].launch()
         if comm is not None:
-            (comm.allreduce_async_ if overlap else comm.allreduce_)(st["o"])
+            if overlap:
+                st["events"].append(comm.allreduce_async_(st["o"]))
+            else:
+                comm.allreduce_(st["o"])
         ops.silu_mul(st["gu"][:, : self.inter_local], st["gu"][:, self.inter_local:], out=st["hidden"])
         st["second"].launch()
         if comm is not None:
-            (comm.allreduce_async_ if overlap else comm.allreduce_)(st["down"])
+            if overlap:
+                st["events"].append(comm.allreduce_async_(st["down"]))
+            else:
+                comm.allreduce_(st["down"])
         return st["qkv"], st["o"], st["down"]
 
 
