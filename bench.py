@@ -812,7 +812,8 @@ class EpStack:
         if rank == 0 and hi_t > lo_t:
             wr, br, wgu, wd = self.full0
             y, idx, wts = (res[0], res[2], res[3]) if world == 1 else res
-            out["parity"] = moe_parity(x, y, idx, wts, lambda: ops.linear(x, wr, bias=br, out_dtype=torch.float32), wr, br,
+            logits = res[1] if world == 1 else self.layers[0].logits     # the logits the routing was made from
+            out["parity"] = moe_parity(x, y, idx, wts, lambda: logits, wr, br,
                                        wgu, wd, self.K)
         return out
 

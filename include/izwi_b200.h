@@ -222,6 +222,14 @@ int32_t izb_silu_mul(izb_ctx* ctx, izb_stream stream, const void* gate, const vo
  * are the softmax over the picked logits, permuted rows are ordered by expert and then by
  * ascending (token, slot), and the combine adds slots in ascending order in fp32. */
 
+/* Router and expert choice in one launch: logits[T, E] = x[T, H] . w_router[E, H]^T (+ router_bias[E]),
+ * fp32, written to logits_out; idx_out [T, k] int32 and weights_out [T, k] fp32 as izb_moe_topk gives them
+ * for those logits.  x bf16 with rows ld_x apart, w_router and router_bias bf16.  Uses a small per-context
+ * counter area: calls on one context must be ordered with respect to one another (one stream, or events).
+ * H not a multiple of 32, unaligned operands or more than 16384 tokens run izb_linear + izb_moe_topk. */
+int32_t izb_moe_route(izb_ctx* ctx, izb_stream stream, const void* x, int64_t ld_x, const void* w_router,
+                      const void* router_bias, int64_t T, int64_t H, int64_t E, int32_t top_k,
+                      void* logits_out, void* idx_out, void* weights_out);
 /* logits [T, E] fp32 -> idx [T, k] int32 (descending logit) and weights [T, k] fp32. */
 int32_t izb_moe_topk(izb_ctx* ctx, izb_stream stream, const void* logits, int64_t T, int64_t E,
                      int32_t top_k, void* idx_out, void* weights_out);
@@ -256,8 +264,8 @@ typedef struct izb_moe_args {
 } izb_moe_args;
 
 size_t izb_moe_workspace_bytes(int64_t T, int64_t H, int64_t I, int64_t E, int32_t top_k);
-/* router -> top-k -> permute -> gather -> grouped gate/up GEMM with SwiGLU -> grouped down GEMM ->
- * combine, all on `stream`.  The workspace starts with logits [T,E] fp32, idx [T,k] int32 and
+/* router + top-k (izb_moe_route) -> permute -> gather -> grouped gate/up GEMM with SwiGLU -> grouped down
+ * GEMM -> combine, all on `stream`.  The workspace starts with logits [T,E] fp32, idx [T,k] int32 and
  * weights [T,k] fp32 (each region 256-byte aligned), which callers may read back. */
 int32_t izb_moe_forward(izb_ctx* ctx, izb_stream stream, const izb_moe_args* args);
 
@@ -322,13 +330,13 @@ int32_t izb_ar_destroy(izb_ar* ar);
  * buffers for at most max_tokens_local tokens per rank and step), exchange the 64-byte handles,
  * izb_ep_connect.  Per layer, after the local routing (izb_moe_topk / permute / gather):
  *   izb_ep_dispatch(x, ld_x, perm, offsets, pairs): exchanges the per-expert counts, stores every row
- *     into its owner's receive buffer (rows grouped by local expert, then source rank) and waits for
- *     the rows of all ranks; with perm = NULL x holds the `pairs` rows already in expert-major order
+ *     into its owner's receive buffer (rows grouped by local expert, then source rank) and, in the
+ *     same kernel, waits for the rows of all ranks (two launches in all); with perm = NULL x holds the `pairs` rows already in expert-major order
  *     (izb_moe_gather's output), otherwise x is the token matrix [tokens, hidden] (rows ld_x apart)
  *     and row r is read from x[perm[r] / top_k]: the gather is fused into the dispatch; afterwards izb_ep_recv_rows() / izb_ep_recv_offsets() [local experts + 1]
  *     feed izb_moe_grouped_gemm with rows = izb_ep_recv_capacity_rows();
  *   izb_ep_return(y_rows): stores each result row back to the rank it came from, at the row it left
- *     from in that rank's permuted order, and waits for this rank's rows: izb_ep_returned_rows()
+ *     from in that rank's permuted order, and waits for this rank's rows (one launch): izb_ep_returned_rows()
  *     then feeds izb_moe_combine.
  * All waits are bounded (izb_ctx_check reports IZB_ERR_TIMEOUT); the launches can be captured in a
  * CUDA graph.  No counterpart in the reference (single device). */

@@ -72,6 +72,8 @@ _SIGNATURES = {
     "izb_static_scratch_bytes": (C.c_size_t, []),
     "izb_linear_quantized_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                                 C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "izb_moe_route": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                  C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "izb_moe_topk": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "izb_moe_permute": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
                                     C.c_void_p]),

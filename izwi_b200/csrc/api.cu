@@ -194,7 +194,8 @@ int32_t izb_ctx_create(int32_t device, izb_ctx** out) {
     }
     ctx->d_status = nullptr;
     // one allocation: status words (padded to 64 bytes), then the arg-max keys and counters
-    const size_t dev_bytes = 64 + static_cast<size_t>(IZB_ARGMAX_SPLIT_ROWS) * (sizeof(unsigned long long) + sizeof(unsigned int));
+    const size_t dev_bytes = 64 + static_cast<size_t>(IZB_ARGMAX_SPLIT_ROWS) * (sizeof(unsigned long long) + sizeof(unsigned int)) +
+                             static_cast<size_t>(IZB_ROUTE_TILES) * sizeof(unsigned int);
     static_assert(IZB_STATUS_WORDS * sizeof(int) <= 64, "status words outgrew their slot");
     if (cudaMalloc(&ctx->d_status, dev_bytes) != cudaSuccess || cudaMemset(ctx->d_status, 0, dev_bytes) != cudaSuccess) {
         (void)cudaGetLastError();
@@ -204,6 +205,7 @@ int32_t izb_ctx_create(int32_t device, izb_ctx** out) {
     }
     ctx->d_argmax_keys = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(ctx->d_status) + 64);
     ctx->d_argmax_done = reinterpret_cast<unsigned int*>(ctx->d_argmax_keys + IZB_ARGMAX_SPLIT_ROWS);
+    ctx->d_route_done = ctx->d_argmax_done + IZB_ARGMAX_SPLIT_ROWS;
     (void)cudaSetDevice(prev);
     *out = ctx;
     return IZB_OK;

@@ -86,6 +86,8 @@ __global__ void __launch_bounds__(256)
     ep_counts_kernel(EpPeers peers, EpLayout lay, EpTables* __restrict__ tb, const int* __restrict__ offsets, int world,
                      int rank, int n_experts, int e_local, long long recv_cap, int* status) {
     __shared__ int bad;
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();  // offsets come from the permutation kernel before this one
     EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
     const unsigned int seq = hdr->seq + 1;
     if (threadIdx.x == 0) {
@@ -190,13 +192,31 @@ __device__ __forceinline__ void ep_signal(unsigned int* counter, EpPeers peers, 
     }
 }
 
+// Threads 0 .. world-1 of the calling CTA wait (bounded) until every rank's flag shows this step.
+__device__ __forceinline__ void ep_wait_flags(const unsigned char* local, size_t flag_off, unsigned int seq, int world, int* status) {
+    const unsigned int* flags = reinterpret_cast<const unsigned int*>(local + flag_off);
+    if (static_cast<int>(threadIdx.x) < world) {
+        const long long t0 = clock64();
+        while (ep_ld_flag(flags + threadIdx.x) != seq) {
+            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                atomicExch(status, 6);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+}
+
 // Row r (expert-major order) of expert e goes to the owner's receive buffer at dst_row[e] +
 // (r - offsets[e]).  Its source is x_perm[r], or, with `perm` given, x[perm[r] / top_k] (the gather
 // of the routing fused into the dispatch).  One warp per row.
 __global__ void __launch_bounds__(256)
     ep_dispatch_kernel(EpPeers peers, EpLayout lay, const EpTables* __restrict__ tb, const uint4* __restrict__ x,
                        const int* __restrict__ perm, int top_k, long long ld_units, const int* __restrict__ offsets,
-                       long long pairs, int n_experts, int e_local, int row_units, int world, int rank) {
+                       long long pairs, int n_experts, int e_local, int row_units, int world, int rank, int* status) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();  // the tables come from the counts kernel, x and perm from the routing before it
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long r = static_cast<long long>(blockIdx.x) * wpb + warp; r < pairs; r += static_cast<long long>(gridDim.x) * wpb) {
         int e = 0, dst_row = -1;
@@ -221,13 +241,18 @@ __global__ void __launch_bounds__(256)
     }
     EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
     ep_signal(&hdr->done_dispatch, peers, lay.flag_dispatch, world, rank, tb->step);
+    // CTA 0 keeps the kernel open until every rank's rows have landed here, so what follows in the stream
+    // (the grouped GEMM) needs no launch of its own to wait
+    if (blockIdx.x == 0) ep_wait_flags(peers.base[rank], lay.flag_dispatch, tb->step, world, status);
 }
 
 // y: results for the received rows, same order.  Row i (local expert el, source s, position j) goes
 // to the source's return buffer at ret_start[s][el] + j.  One warp per row.
 __global__ void __launch_bounds__(256)
     ep_return_kernel(EpPeers peers, EpLayout lay, const EpTables* __restrict__ tb, const uint4* __restrict__ y, int e_local,
-                     int row_units, int world, int rank) {
+                     int row_units, int world, int rank, int* status) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();  // y is the output of the grouped GEMM before this kernel
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     const int groups = e_local * world;
     const int total = tb->recv_start[groups];
@@ -249,26 +274,11 @@ __global__ void __launch_bounds__(256)
     }
     EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
     ep_signal(&hdr->done_return, peers, lay.flag_return, world, rank, tb->step);
-}
-
-// One CTA of `world` threads: thread s waits (bounded) for rank s's flag of this step.
-// closes: the step is complete on this rank, advance its sequence number.
-__global__ void ep_wait_kernel(unsigned char* local, size_t flag_off, const EpTables* __restrict__ tb, int world, int closes,
-                               int* status) {
-    const unsigned int seq = tb->step;
-    const unsigned int* flags = reinterpret_cast<const unsigned int*>(local + flag_off);
-    if (static_cast<int>(threadIdx.x) < world) {
-        const long long t0 = clock64();
-        while (ep_ld_flag(flags + threadIdx.x) != seq) {
-            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
-                atomicExch(status, 6);
-                break;
-            }
-        }
+    // CTA 0 waits for this rank's own rows to come back from every rank, then closes the step
+    if (blockIdx.x == 0) {
+        ep_wait_flags(peers.base[rank], lay.flag_return, tb->step, world, status);
+        if (threadIdx.x == 0) hdr->seq = tb->step;
     }
-    __threadfence_system();
-    __syncthreads();
-    if (closes && threadIdx.x == 0) reinterpret_cast<EpHeader*>(local)->seq = seq;
 }
 
 EpLayout ep_layout(int world, int n_experts, int hidden, long long recv_cap, long long max_pairs_local) {
@@ -384,18 +394,17 @@ int32_t izb_ep_dispatch(izb_ep* ep, izb_stream stream, const void* x, int64_t ld
     if (ld_x < ep->hidden || ld_x % 8 != 0) return IZB_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int* status = ep->ctx->d_status + 5;
-    ep_counts_kernel<<<1, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const int*>(offsets), ep->world, ep->rank,
-                                       ep->n_experts, ep->e_local, ep->recv_cap, status);
-    IZB_CUDA_TRY(cudaGetLastError());
+    IZB_CUDA_TRY(izb::launch_chained(ep->ctx, ep_counts_kernel, dim3(1), dim3(256), 0, s, ep->peers, ep->lay, ep->tables,
+                                     static_cast<const int*>(offsets), ep->world, ep->rank, ep->n_experts, ep->e_local, ep->recv_cap,
+                                     status));
     const long long cap = static_cast<long long>(ep->ctx->sm_count) * 4, blocks = (pairs + 7) / 8;
     const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
-    ep_dispatch_kernel<<<grid, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const uint4*>(x),
-                                            static_cast<const int*>(perm), ep->top_k, ld_x / 8, static_cast<const int*>(offsets),
-                                            pairs, ep->n_experts, ep->e_local, ep->hidden / 8, ep->world, ep->rank);
-    IZB_CUDA_TRY(cudaGetLastError());
-    ep_wait_kernel<<<1, 32, 0, s>>>(ep->local, ep->lay.flag_dispatch, ep->tables, ep->world, 0, status);
-    IZB_CUDA_TRY(cudaGetLastError());
-    ep->ctx->launches.fetch_add(3, std::memory_order_relaxed);
+    IZB_CUDA_TRY(izb::launch_chained(ep->ctx, ep_dispatch_kernel, dim3(grid), dim3(256), 0, s, ep->peers, ep->lay,
+                                     static_cast<const EpTables*>(ep->tables), static_cast<const uint4*>(x),
+                                     static_cast<const int*>(perm), ep->top_k, static_cast<long long>(ld_x / 8),
+                                     static_cast<const int*>(offsets), static_cast<long long>(pairs), ep->n_experts, ep->e_local,
+                                     ep->hidden / 8, ep->world, ep->rank, status));
+    ep->ctx->launches.fetch_add(2, std::memory_order_relaxed);
     return IZB_OK;
 }
 
@@ -404,12 +413,10 @@ int32_t izb_ep_return(izb_ep* ep, izb_stream stream, const void* y_rows) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int* status = ep->ctx->d_status + 5;
     const int grid = ep->ctx->sm_count * 4;
-    ep_return_kernel<<<grid, 256, 0, s>>>(ep->peers, ep->lay, ep->tables, static_cast<const uint4*>(y_rows), ep->e_local,
-                                          ep->hidden / 8, ep->world, ep->rank);
-    IZB_CUDA_TRY(cudaGetLastError());
-    ep_wait_kernel<<<1, 32, 0, s>>>(ep->local, ep->lay.flag_return, ep->tables, ep->world, 1, status);
-    IZB_CUDA_TRY(cudaGetLastError());
-    ep->ctx->launches.fetch_add(2, std::memory_order_relaxed);
+    IZB_CUDA_TRY(izb::launch_chained(ep->ctx, ep_return_kernel, dim3(grid), dim3(256), 0, s, ep->peers, ep->lay,
+                                     static_cast<const EpTables*>(ep->tables), static_cast<const uint4*>(y_rows), ep->e_local,
+                                     ep->hidden / 8, ep->world, ep->rank, status));
+    ep->ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
 

@@ -20,12 +20,15 @@ struct izb_ctx {
     // arrival counter per row; the last CTA of a row writes the result and zeroes both again
     unsigned long long* d_argmax_keys;  // [IZB_ARGMAX_SPLIT_ROWS]
     unsigned int* d_argmax_done;        // [IZB_ARGMAX_SPLIT_ROWS]
+    // fused router + top-k: one arrival counter per 16-token tile (zero between launches)
+    unsigned int* d_route_done;         // [IZB_ROUTE_TILES]
     int pdl;  // launch the decode-step kernels with programmatic stream serialisation (IZB_PDL=0 turns it off)
 };
 
 constexpr int IZB_STATUS_WORDS = 8;
 constexpr int IZB_MAX_DEVICES = 64;  // izb_ctx_create refuses device ordinals at or above this (per-device tables)
 constexpr int IZB_ARGMAX_SPLIT_ROWS = 1024;
+constexpr int IZB_ROUTE_TILES = 1024;
 // Bounded device-side waits give up after this many clock64 ticks (~1 s).
 constexpr long long IZB_WAIT_LIMIT_CLOCKS = 2000000000LL;
 

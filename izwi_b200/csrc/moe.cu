@@ -13,72 +13,158 @@ namespace izb {
 constexpr int MOE_MAX_EXPERTS = 512;
 constexpr int MOE_MAX_TOPK = 32;
 
-// One warp per token.  Each lane keeps experts lane, lane+32, ...; k rounds of warp arg-max.
+// Top-k of one token's logits by one warp.  Each lane keeps experts lane, lane+32, ...; k rounds of
+// warp arg-max (largest logit, lowest expert id among equals); weights = softmax over the chosen logits.
+__device__ __forceinline__ void topk_row(const volatile float* row, int lane, int E, int k, int* idx_row, float* wts_row) {
+    float v[MOE_MAX_EXPERTS / 32];
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < E ? row[e] : -INFINITY;
+    }
+    float first = 0.f, sum = 0.f, mine = 0.f;
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7FFFFFFF;
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && (v[i] > best || (v[i] == best && e < best_e))) {
+                best = v[i];
+                best_e = e;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+            const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, off);
+            if (ob > best || (ob == best && oe < best_e)) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        if (best_e == 0x7FFFFFFF) best_e = j < E ? j : 0;  // every remaining logit is -inf or NaN
+        if ((best_e & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i)
+                if (i == (best_e >> 5)) v[i] = -INFINITY;
+        }
+        if (j == 0) first = best;
+        const float ex = expf(best - first);
+        sum += ex;
+        if (lane == j) mine = ex;
+        if (lane == 0) idx_row[j] = best_e;
+    }
+    if (lane < k) wts_row[lane] = mine / sum;
+}
+
+// One warp per token.
 __global__ void moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int* __restrict__ idx,
                                 float* __restrict__ wts) {
     izb::pdl_launch_dependents();
     izb::pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
-    for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_block) {
-        const float* row = logits + static_cast<long long>(t) * E;
-        float v[MOE_MAX_EXPERTS / 32];
-#pragma unroll
-        for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) {
-            const int e = lane + 32 * i;
-            v[i] = e < E ? row[e] : -INFINITY;
+    for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_block)
+        topk_row(logits + static_cast<long long>(t) * E, lane, E, k, idx + static_cast<long long>(t) * k,
+                 wts + static_cast<long long>(t) * k);
+}
+
+// Router and top-k in one launch: logits[T, E] = x[T, H] . w[E, H]^T + bias (fp32), then the top-k of
+// every token.  A CTA computes 16 tokens x (8 NG) experts with mma.sync m16n8k16: warp (ng, ks) owns
+// the 8 experts of group ng and every KS-th 32-value block of H; both operands are read straight
+// from global memory (the router weight is a few hundred KB and stays in L2) with 16-byte loads under
+// a permutation of k that is the same for both, so each lane's 16 bytes are its fragments of two
+// k-steps.  The k-slices meet through shared memory, the logits go to global memory, and the last
+// CTA of a token tile to finish (a counter per tile, left at zero again) picks the experts of its 16
+// tokens, one warp per token.  NG x KS = 8 warps: (4, 2) in general, (1, 8) for a single token tile,
+// where E / 8 CTAs each stream eight rows of the weight instead of E / 32 CTAs thirty-two.
+constexpr int ROUTE_TOKENS = 16;
+constexpr int ROUTE_WARPS = 8;
+constexpr int ROUTE_MAX_TILES = 1024;
+
+template <int NG, int KS>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+    moe_route_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
+                     const __nv_bfloat16* __restrict__ bias, int T, int H, int E, int k, float* __restrict__ logits,
+                     int* __restrict__ idx, float* __restrict__ wts, unsigned int* __restrict__ tile_done) {
+    static_assert(NG * KS == ROUTE_WARPS, "eight warps");
+    __shared__ float part[KS][NG][32][4];
+    __shared__ int is_last;
+    izb::pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int ng = warp % NG, ks = warp / NG;
+    const int tok0 = blockIdx.x * ROUTE_TOKENS;
+    const int n0 = (blockIdx.y * NG + ng) * 8;  // first expert of this warp's group
+    const bool live = n0 < E;
+    // rows past the end repeat the last token (their results are not stored)
+    const int r_lo = min(tok0 + g, T - 1), r_hi = min(tok0 + g + 8, T - 1);
+    izb::pdl_wait();  // x is the output of the kernel before this one
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        const uint4* xa = reinterpret_cast<const uint4*>(x + r_lo * ldx) + t4;
+        const uint4* xb = reinterpret_cast<const uint4*>(x + r_hi * ldx) + t4;
+        const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(min(n0 + g, E - 1)) * H) + t4;
+        const int n_blk = H / 32;
+#pragma unroll 4
+        for (int b = ks; b < n_blk; b += KS) {
+            const uint4 a_lo = xa[b * 4], a_hi = xb[b * 4], bw = wr[b * 4];
+            mma_bf16_16816(acc, a_lo.x, a_hi.x, a_lo.y, a_hi.y, bw.x, bw.y);
+            mma_bf16_16816(acc, a_lo.z, a_hi.z, a_lo.w, a_hi.w, bw.z, bw.w);
         }
-        float first = 0.f, sum = 0.f, mine = 0.f;
-        for (int j = 0; j < k; ++j) {
-            float best = -INFINITY;
-            int best_e = 0x7FFFFFFF;
+    }
 #pragma unroll
-            for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) {
-                const int e = lane + 32 * i;
-                if (e < E && (v[i] > best || (v[i] == best && e < best_e))) {
-                    best = v[i];
-                    best_e = e;
-                }
-            }
+    for (int i = 0; i < 4; ++i) part[ks][ng][lane][i] = acc[i];
+    __syncthreads();
+    if (ks == 0 && live) {
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
-                const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, off);
-                if (ob > best || (ob == best && oe < best_e)) {
-                    best = ob;
-                    best_e = oe;
-                }
-            }
-            if (best_e == 0x7FFFFFFF) best_e = j < E ? j : 0;  // every remaining logit is -inf or NaN
-            if ((best_e & 31) == lane) {
+        for (int s2 = 1; s2 < KS; ++s2)
 #pragma unroll
-                for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i)
-                    if (i == (best_e >> 5)) v[i] = -INFINITY;
-            }
-            if (j == 0) first = best;
-            const float ex = expf(best - first);
-            sum += ex;
-            if (lane == j) mine = ex;
-            if (lane == 0) idx[static_cast<long long>(t) * k + j] = best_e;
+            for (int i = 0; i < 4; ++i) acc[i] += part[s2][ng][lane][i];
+        // c0, c1: token g, experts n0 + 2 t4, + 1; c2, c3: token g + 8
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int tok = tok0 + g + (i >> 1) * 8, e = n0 + 2 * t4 + (i & 1);
+            if (tok < T && e < E) logits[static_cast<long long>(tok) * E + e] = acc[i] + (bias ? __bfloat162float(bias[e]) : 0.f);
         }
-        if (lane < k) wts[static_cast<long long>(t) * k + lane] = mine / sum;
+    }
+    // the last CTA of this token tile to get here sees every group's logits and picks the experts
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(&tile_done[blockIdx.x], 1u);
+        is_last = prev == gridDim.y - 1;
+        if (is_last) tile_done[blockIdx.x] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int tt = warp; tt < ROUTE_TOKENS; tt += ROUTE_WARPS) {
+        const int tok = tok0 + tt;
+        if (tok < T)
+            topk_row(logits + static_cast<long long>(tok) * E, lane, E, k,
+                     idx + static_cast<long long>(tok) * k, wts + static_cast<long long>(tok) * k);
     }
 }
 
-// One block per expert e.  Pass 1 counts the pairs routed to experts below e (the segment start)
-// and to e; pass 2 walks the pairs in order again and hands out positions, so equal experts keep
-// ascending pair order.  No block depends on another.
+// One block per expert e, every warp owning one contiguous range of the pairs.  Pass 1: each warp
+// counts, in its range, the pairs routed to e and (summed over the block) to experts below e: the
+// segment start and, by a scan over the warps, where each warp's hits begin.  Pass 2: each warp walks
+// its range again in order and hands out positions, so equal experts keep ascending pair order.  No
+// block depends on another, and inside a block the warps meet once.
 __global__ void moe_permute_kernel(const int* __restrict__ idx, int pairs, int E, int* __restrict__ offsets,
                                    int* __restrict__ perm, int* __restrict__ inv) {
     izb::pdl_launch_dependents();
     izb::pdl_wait();
-    __shared__ int warp_sums[32];
-    __shared__ int base_s, count_s, running_s;
+    __shared__ int warp_equal[32], warp_below[32];
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    // ranges are whole multiples of 32 pairs so that a warp's lanes read consecutive pairs
+    const int per_warp = ((pairs + nwarps - 1) / nwarps + 31) / 32 * 32;
+    const int lo = min(warp * per_warp, pairs), hi = min(lo + per_warp, pairs);
 
     int below = 0, equal = 0;
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    for (int p = lo + lane; p < hi; p += 32) {
         const int x = idx[p];
         below += x < e;
         equal += x == e;
@@ -88,44 +174,32 @@ __global__ void moe_permute_kernel(const int* __restrict__ idx, int pairs, int E
         below += __shfl_xor_sync(0xFFFFFFFFu, below, off);
         equal += __shfl_xor_sync(0xFFFFFFFFu, equal, off);
     }
-    if (threadIdx.x == 0) {
-        base_s = 0;
-        count_s = 0;
-    }
-    __syncthreads();
     if (lane == 0) {
-        atomicAdd(&base_s, below);   // integer sums: order does not matter
-        atomicAdd(&count_s, equal);
+        warp_below[warp] = below;
+        warp_equal[warp] = equal;
     }
     __syncthreads();
-    const int base = base_s;
+    int base = 0, before = 0, total = 0;
+    for (int w = 0; w < nwarps; ++w) {
+        base += warp_below[w];
+        if (w < warp) before += warp_equal[w];
+        total += warp_equal[w];
+    }
     if (threadIdx.x == 0) {
         offsets[e] = base;
-        if (e == E - 1) offsets[E] = base + count_s;
-        running_s = 0;
+        if (e == E - 1) offsets[E] = base + total;
     }
-    __syncthreads();
-
-    for (int p0 = 0; p0 < pairs; p0 += blockDim.x) {
-        const int p = p0 + threadIdx.x;
-        const bool hit = p < pairs && idx[p] == e;
+    int at = base + before;
+    for (int p0 = lo; p0 < hi; p0 += 32) {
+        const int p = p0 + lane;
+        const bool hit = p < hi && idx[p] == e;
         const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
-        if (lane == 0) warp_sums[warp] = __popc(ballot);
-        __syncthreads();
-        int before = running_s;
-        for (int w = 0; w < warp; ++w) before += warp_sums[w];
         if (hit) {
-            const int pos = base + before + __popc(ballot & ((1u << lane) - 1u));
+            const int pos = at + __popc(ballot & ((1u << lane) - 1u));
             perm[pos] = p;
             inv[p] = pos;
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int tot = 0;
-            for (int w = 0; w < nwarps; ++w) tot += warp_sums[w];
-            running_s += tot;
-        }
-        __syncthreads();
+        at += __popc(ballot);
     }
 }
 
@@ -189,6 +263,51 @@ int32_t izb_moe_topk(izb_ctx* ctx, izb_stream stream, const void* logits, int64_
     IZB_CUDA_TRY(izb::launch_chained(ctx, moe_topk_kernel, dim3(blocks_for(ctx, T * 32, threads)), dim3(threads), 0,
                                      static_cast<cudaStream_t>(stream), static_cast<const float*>(logits), static_cast<int>(T),
                                      static_cast<int>(E), top_k, static_cast<int*>(idx_out), static_cast<float*>(weights_out)));
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+int32_t izb_moe_route(izb_ctx* ctx, izb_stream stream, const void* x, int64_t ld_x, const void* w_router,
+                      const void* router_bias, int64_t T, int64_t H, int64_t E, int32_t top_k, void* logits_out,
+                      void* idx_out, void* weights_out) {
+    if (!ctx || T < 0 || H <= 0 || E <= 0 || top_k <= 0 || ld_x < H) return IZB_ERR_BAD_ARG;
+    if (E > MOE_MAX_EXPERTS || top_k > MOE_MAX_TOPK || top_k > E) return IZB_ERR_UNSUPPORTED;
+    if (T == 0) return IZB_OK;
+    if (!x || !w_router || !logits_out || !idx_out || !weights_out) return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(logits_out, 4) || !izb_aligned(idx_out, 4) || !izb_aligned(weights_out, 4)) return IZB_ERR_BAD_ARG;
+    if (router_bias && !izb_aligned(router_bias, 2)) return IZB_ERR_BAD_ARG;
+    const int64_t tiles = (T + ROUTE_TOKENS - 1) / ROUTE_TOKENS;
+    const bool fused = H % 32 == 0 && ld_x % 8 == 0 && izb_aligned(x, 16) && izb_aligned(w_router, 16) &&
+                       tiles <= ROUTE_MAX_TILES && T <= INT32_MAX / E;
+    if (!fused) {
+        // shapes the fused kernel does not take: the linear layer, then the top-k kernel
+        izb_linear_args r;
+        memset(&r, 0, sizeof(r));
+        r.wfmt = IZB_W_BF16;
+        r.y_dtype = IZB_F32;
+        r.x = x; r.w = w_router; r.bias = router_bias; r.y = logits_out;
+        r.M = T; r.N = E; r.K = H; r.ldx = ld_x; r.ldy = E;
+        const int rc = izb_linear(ctx, stream, &r);
+        if (rc != IZB_OK) return rc;
+        return izb_moe_topk(ctx, stream, logits_out, T, E, top_k, idx_out, weights_out);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const auto* xp = static_cast<const __nv_bfloat16*>(x);
+    const auto* wp = static_cast<const __nv_bfloat16*>(w_router);
+    const auto* bp = static_cast<const __nv_bfloat16*>(router_bias);
+    auto* lp = static_cast<float*>(logits_out);
+    auto* ip = static_cast<int*>(idx_out);
+    auto* op = static_cast<float*>(weights_out);
+    const int Ti = static_cast<int>(T), Hi = static_cast<int>(H), Ei = static_cast<int>(E);
+    if (tiles == 1) {
+        const dim3 grid(1, static_cast<unsigned>((E + 7) / 8));
+        IZB_CUDA_TRY(izb::launch_chained(ctx, moe_route_kernel<1, 8>, grid, dim3(ROUTE_WARPS * 32), 0, s, xp, ld_x, wp, bp, Ti, Hi, Ei,
+                                         top_k, lp, ip, op, ctx->d_route_done));
+    } else {
+        const dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>((E + 31) / 32));
+        IZB_CUDA_TRY(izb::launch_chained(ctx, moe_route_kernel<4, 2>, grid, dim3(ROUTE_WARPS * 32), 0, s, xp, ld_x, wp, bp, Ti, Hi, Ei,
+                                         top_k, lp, ip, op, ctx->d_route_done));
+    }
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
@@ -294,15 +413,8 @@ int32_t izb_moe_forward(izb_ctx* ctx, izb_stream stream, const izb_moe_args* a) 
     uint8_t* ws = static_cast<uint8_t*>(a->workspace);
     const int64_t pairs = a->T * a->top_k;
 
-    izb_linear_args r;
-    memset(&r, 0, sizeof(r));
-    r.wfmt = IZB_W_BF16;
-    r.y_dtype = IZB_F32;
-    r.x = a->x; r.w = a->w_router; r.bias = a->router_bias; r.y = ws + L.logits;
-    r.M = a->T; r.N = a->E; r.K = a->H; r.ldx = a->H; r.ldy = a->E;
-    int rc = izb_linear(ctx, stream, &r);
-    if (rc != IZB_OK) return rc;
-    rc = izb_moe_topk(ctx, stream, ws + L.logits, a->T, a->E, a->top_k, ws + L.idx, ws + L.wts);
+    int rc = izb_moe_route(ctx, stream, a->x, a->H, a->w_router, a->router_bias, a->T, a->H, a->E, a->top_k, ws + L.logits,
+                           ws + L.idx, ws + L.wts);
     if (rc != IZB_OK) return rc;
     rc = izb_moe_permute(ctx, stream, ws + L.idx, pairs, a->E, ws + L.offsets, ws + L.perm, ws + L.inv);
     if (rc != IZB_OK) return rc;

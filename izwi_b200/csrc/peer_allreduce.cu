@@ -5,6 +5,7 @@
 // NCCL launch, no multimem, no TMA on peer memory.  Slots are double-buffered by call parity; the
 // call sequence number lives in device memory so the launch can be replayed from a CUDA graph.
 #include <cstddef>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -19,8 +20,8 @@ struct ArDevState {
     unsigned int done;  // CTAs of the current one-shot call that finished reducing
     // two-shot path (large messages): two operand / result buffers, each with its own call number
     unsigned int big_seq[2];               // two-shot calls completed on this rank, per buffer
-    unsigned int done_b[2], done_c[2];     // CTA counters of the reduce kernel (chunk stored / leaving)
-    unsigned int pad_[8];
+    unsigned int done_a[2], done_b[2], done_c[2];  // CTA counters of the kernel (chunks pushed / result stored / leaving)
+    unsigned int pad_[6];
     unsigned int flag_a[2][AR_MAX_WORLD];  // rank s has its operand ready in its region (value = call number)
     unsigned int flag_b[2][AR_MAX_WORLD];  // rank s has stored its reduced chunk into this region
 };
@@ -35,7 +36,8 @@ struct izb_ar {
     int world, rank;
     size_t slot_bytes;
     size_t big_bytes;  // capacity of each two-shot operand / result buffer (0: path off)
-    size_t big_in[2], big_res[2];  // their byte offsets inside a region
+    size_t big_in[2], big_stage[2], big_res[2];  // byte offsets inside a region: operand, received chunks, result
+    int push;          // 1: chunks are pushed to their owner (stores only cross NVLink); 0: the owner pulls them (peer loads)
     int next_buf;      // buffer the next izb_ar_allreduce of a large message uses
     unsigned char* local;
     ArPeers peers;
@@ -178,6 +180,7 @@ __device__ __forceinline__ bool ar_wait_all(const unsigned int* flags, int world
 // 166 registers, nearly all of the shared memory), so a sum on a second stream really runs beside it.
 constexpr int AR2_THREADS = 128;
 constexpr int AR2_UNROLL = 4;  // 16-byte units per thread and pass: world x 4 peer loads in flight per thread
+constexpr int AR2_BATCH = 8;   // pushing kernel: 16-byte units copied per thread and pass
 
 template <bool F32>
 __global__ void __launch_bounds__(AR2_THREADS)
@@ -267,6 +270,116 @@ __global__ void __launch_bounds__(AR2_THREADS)
     }
 }
 
+// The same exchange with stores only on the wire (posted writes do not wait a round trip the way peer
+// loads do): every rank first pushes chunk j of its operand into a staging slot of rank j's region
+// (peers visited in the order rank+1, rank+2, ... so that at any moment every receiver hears from one
+// sender), the last CTA to finish raises flag_a; after all flag_a a rank adds the world staged copies
+// of its own chunk (local reads) in rank order and stores the result chunk into every region as above.
+template <bool F32>
+__global__ void __launch_bounds__(AR2_THREADS)
+    ar2_push_kernel(ArPeers peers, int world, int rank, int buf, size_t big_in, size_t big_stage, size_t big_res, int n_units,
+                    int* status) {
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();  // the operand was written by the kernel before this one
+    ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
+    const unsigned int call = st->big_seq[buf] + 1;
+    const size_t flag_a = offsetof(ArDevState, flag_a) + sizeof(unsigned int) * AR_MAX_WORLD * buf;
+    const size_t flag_b = offsetof(ArDevState, flag_b) + sizeof(unsigned int) * AR_MAX_WORLD * buf;
+    const int per = (n_units + world - 1) / world;  // units per chunk; the last chunk may be shorter or empty
+    const uint4* mine = reinterpret_cast<const uint4*>(peers.base[rank] + big_in);
+    const int step = static_cast<int>(gridDim.x) * AR2_THREADS;
+    const int first = static_cast<int>(blockIdx.x) * AR2_THREADS + static_cast<int>(threadIdx.x);
+    __shared__ int last_flag;
+
+    // 1. push the chunks other ranks own
+    for (int p = 1; p < world; ++p) {
+        const int j = (rank + p) % world;
+        const int len = min(per, n_units - j * per);
+        uint4* dst = reinterpret_cast<uint4*>(peers.base[j] + big_stage) + static_cast<size_t>(rank) * per;
+        const uint4* src = mine + static_cast<size_t>(j) * per;
+        // AR2_BATCH loads are issued before the first store: with one CTA per SM it is the number of
+        // 16-byte loads in flight per thread that sets the rate
+        for (int i0 = first; i0 < len; i0 += step * AR2_BATCH) {
+            uint4 v[AR2_BATCH];
+#pragma unroll
+            for (int b = 0; b < AR2_BATCH; ++b) {
+                const int i = i0 + b * step;
+                if (i < len) v[b] = src[i];
+            }
+#pragma unroll
+            for (int b = 0; b < AR2_BATCH; ++b) {
+                const int i = i0 + b * step;
+                if (i < len) dst[i] = v[b];
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last_flag = atomicAdd(&st->done_a[buf], 1u) == gridDim.x - 1;
+        if (last_flag) st->done_a[buf] = 0;
+    }
+    __syncthreads();
+    if (last_flag && static_cast<int>(threadIdx.x) < world) {
+        __threadfence_system();
+        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + threadIdx.x) % world] + flag_a) + rank, call);
+    }
+    // 2. all chunks of mine have arrived: add them in rank order, store the result into every region
+    const bool ok = ar_wait_all(reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_a), world, call, status);
+    if (ok) {
+        const int lo = per * rank, len = min(per, n_units - lo);
+        const uint4* stage = reinterpret_cast<const uint4*>(peers.base[rank] + big_stage);
+        for (int i = first; i < len; i += step) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            uint4 in[AR_MAX_WORLD];
+#pragma unroll
+            for (int r = 0; r < AR_MAX_WORLD; ++r)
+                if (r < world) in[r] = r == rank ? mine[lo + i] : ar_ld_peer(stage + static_cast<size_t>(r) * per + i);
+#pragma unroll
+            for (int r = 0; r < AR_MAX_WORLD; ++r) {
+                if (r >= world) break;
+                const uint4 v = in[r];
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (F32) {
+                        acc[e] += __uint_as_float(w[e]);
+                    } else {
+                        acc[2 * e] += izb::bf16_lo_to_f32(w[e]);
+                        acc[2 * e + 1] += izb::bf16_hi_to_f32(w[e]);
+                    }
+                }
+            }
+            const uint4 o = F32 ? make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]))
+                                : make_uint4(izb::pack_bf16x2(acc[0], acc[1]), izb::pack_bf16x2(acc[2], acc[3]),
+                                             izb::pack_bf16x2(acc[4], acc[5]), izb::pack_bf16x2(acc[6], acc[7]));
+            for (int p = 0; p < world; ++p) reinterpret_cast<uint4*>(peers.base[(rank + p) % world] + big_res)[lo + i] = o;
+        }
+    }
+    // 3. as in the pulling kernel: result stores performed, last CTA raises flag_b, CTA 0 waits for everyone's
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last_flag = atomicAdd(&st->done_b[buf], 1u) == gridDim.x - 1;
+        if (last_flag) st->done_b[buf] = 0;
+    }
+    __syncthreads();
+    if (last_flag && static_cast<int>(threadIdx.x) < world) {
+        __threadfence_system();
+        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + threadIdx.x) % world] + flag_b) + rank, call);
+    }
+    if (blockIdx.x == 0) (void)ar_wait_all(reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_b), world, call, status);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&st->done_c[buf], 1u) == gridDim.x - 1) {
+            st->done_c[buf] = 0;
+            __threadfence();
+            st->big_seq[buf] = call;
+        }
+    }
+}
+
 // Plain device-local copy in 16-byte units (operand into the region, result out of it).
 __global__ void __launch_bounds__(512) ar2_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n_units) {
     izb::pdl_launch_dependents();
@@ -278,11 +391,26 @@ __global__ void __launch_bounds__(512) ar2_copy_kernel(const uint4* __restrict__
 
 int ar2_launch(izb_ar* ar, cudaStream_t st, int buf, size_t bytes, int dtype) {
     const long long n_units = static_cast<long long>(bytes / 16);
+    int* status = ar->ctx->d_status + 2;
+    if (ar->push) {
+        // every CTA waits for the flag its last sibling raises, so all of them must get an SM: one CTA per SM at most
+        long long g = (n_units + AR2_THREADS * 8 - 1) / (AR2_THREADS * 8);
+        const int grid = static_cast<int>(g < 1 ? 1 : (g > ar->ctx->sm_count ? ar->ctx->sm_count : g));
+        if (dtype == IZB_F32)
+            IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_push_kernel<true>, dim3(grid), dim3(AR2_THREADS), 0, st, ar->peers, ar->world,
+                                             ar->rank, buf, ar->big_in[buf], ar->big_stage[buf], ar->big_res[buf],
+                                             static_cast<int>(n_units), status));
+        else
+            IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_push_kernel<false>, dim3(grid), dim3(AR2_THREADS), 0, st, ar->peers, ar->world,
+                                             ar->rank, buf, ar->big_in[buf], ar->big_stage[buf], ar->big_res[buf],
+                                             static_cast<int>(n_units), status));
+        ar->ctx->launches.fetch_add(1, std::memory_order_relaxed);
+        return IZB_OK;
+    }
     const long long chunk = (n_units + ar->world - 1) / ar->world;
     long long g = (chunk + AR2_THREADS * AR2_UNROLL - 1) / (AR2_THREADS * AR2_UNROLL);
     const int cap = ar->ctx->sm_count * 2;
     const int grid = static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
-    int* status = ar->ctx->d_status + 2;
     if (dtype == IZB_F32)
         IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_region_kernel<true>, dim3(grid), dim3(AR2_THREADS), 0, st, ar->peers, ar->world,
                                          ar->rank, buf, ar->big_in[buf], ar->big_res[buf], n_units, status));
@@ -310,14 +438,22 @@ int32_t izb_ar_create(izb_ctx* ctx, int32_t world, int32_t rank, size_t max_byte
     const size_t ll_max = max_bytes < AR_LL_MAX_BYTES ? max_bytes : AR_LL_MAX_BYTES;
     ar->slot_bytes = (2 * ll_max + 255) / 256 * 256;  // every 4 payload bytes travel as an 8-byte pair
     ar->big_bytes = max_bytes > AR_LL_MAX_BYTES ? (max_bytes + 255) / 256 * 256 : 0;
-    ar->big_in[0] = AR_HEADER + 2 * static_cast<size_t>(world) * ar->slot_bytes;
-    ar->big_in[1] = ar->big_in[0] + ar->big_bytes;
-    ar->big_res[0] = ar->big_in[1] + ar->big_bytes;
-    ar->big_res[1] = ar->big_res[0] + ar->big_bytes;
+    // staging holds `world` chunks of ceil(units / world) units each: up to world - 1 units more than the message
+    const size_t stage_bytes = ar->big_bytes ? ar->big_bytes + 16 * static_cast<size_t>(world) + 256 : 0;
+    size_t at = AR_HEADER + 2 * static_cast<size_t>(world) * ar->slot_bytes;
+    for (int b = 0; b < 2; ++b) {
+        ar->big_in[b] = at; at += ar->big_bytes;
+        ar->big_stage[b] = at; at += (stage_bytes + 255) / 256 * 256;
+        ar->big_res[b] = at; at += ar->big_bytes;
+    }
+    {
+        const char* e = std::getenv("IZB_AR_PULL");
+        ar->push = (e && e[0] == '1') ? 0 : 1;
+    }
     ar->next_buf = 0;
     ar->connected = false;
     std::memset(&ar->peers, 0, sizeof(ar->peers));
-    const size_t total = ar->big_res[1] + ar->big_bytes;
+    const size_t total = at;
     const size_t zeroed = ar->big_in[0];  // header and one-shot slots; the two-shot buffers are written before they are read
     int cur = -1;
     cudaGetDevice(&cur);

@@ -20,6 +20,20 @@ def topk(logits: torch.Tensor, k: int):
     return idx, wts
 
 
+def route(x: torch.Tensor, w_router: torch.Tensor, router_bias: torch.Tensor | None, k: int):
+    """Router logits and expert choice in one launch: (logits [T, E] fp32, idx [T, k] int32, weights [T, k] fp32)."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    assert w_router.dtype == torch.bfloat16 and w_router.is_contiguous() and w_router.shape[1] == x.shape[1]
+    t, (e, h) = x.shape[0], w_router.shape
+    logits = torch.empty(t, e, device=x.device, dtype=torch.float32)
+    idx = torch.empty(t, k, device=x.device, dtype=torch.int32)
+    wts = torch.empty(t, k, device=x.device, dtype=torch.float32)
+    ctx = Context.get(x.device.index)
+    L.check(L.lib().izb_moe_route(ctx.handle, _stream(), _ptr(x), x.stride(0), _ptr(w_router), _ptr(router_bias), t, h, e, k,
+                                  _ptr(logits), _ptr(idx), _ptr(wts)), "izb_moe_route")
+    return logits, idx, wts
+
+
 def permute(idx: torch.Tensor, n_experts: int):
     assert idx.dtype == torch.int32 and idx.is_contiguous()
     pairs = idx.numel()

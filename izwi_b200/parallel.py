@@ -455,8 +455,7 @@ class EpMoeLayer:
         from . import moe, ops
         dev, ep, rank = x.device, self.comm.world, self.comm.rank
         t = x.shape[0]
-        logits = ops.linear(x, self.w_router, bias=self.router_bias, out_dtype=torch.float32)
-        idx, wts = moe.topk(logits, self.k)
+        self.logits, idx, wts = moe.route(x, self.w_router, self.router_bias, self.k)   # logits kept for checks
         offsets, perm, inv = moe.permute(idx, self.E)
         if getattr(self.comm, "ep", None) is not None and self.comm.ep_shape[:2] == (self.E, self.H) \
                 and self.comm.ep_shape[3] == self.k and t <= self.comm.ep_shape[2] and x.stride(1) == 1:

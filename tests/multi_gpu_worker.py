@@ -56,11 +56,12 @@ def main():
                   (16 << 20, torch.bfloat16), (1 << 20, torch.float32), ((1 << 20) + 4, torch.float32),
                   ((2 << 20) + 6, torch.bfloat16)) * 3:
         part = torch.randn(n, device=dev, generator=g2).to(dt)
-        want = part.clone()
-        dist.all_reduce(want)
+        want = part.float().clone()
+        dist.all_reduce(want)                                      # NCCL in fp32: the exact sum, whatever the rank count
         got = part.clone()
         comm.allreduce_(got)
-        assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2), ("peer all-reduce", n, dt)
+        # fp32 accumulation in rank order, one rounding to the message's type: within one bf16 step of the exact sum
+        assert torch.allclose(got.float(), want, rtol=8e-3 if dt == torch.bfloat16 else 1e-5, atol=1e-3), ("peer all-reduce", n, dt)
     ints = torch.full((2048,), float(rank + 1), device=dev, dtype=torch.float32)
     for _ in range(50):
         t2 = ints.clone()
@@ -146,6 +147,8 @@ def main():
     # ---- one Qwen3-30B-A3B-shaped layer (128 experts, hidden 2048, intermediate 768, top-8) over peer
     # memory against the oracle on the unsharded weights: routing of this rank's tokens bit-exact
     # against the oracle's top-k of the library's own logits, sampled tokens' outputs in tolerance ----
+    torch.cuda.synchronize()
+    dist.barrier()                       # no rank may still be storing into a buffer that is about to be freed
     L.lib().izb_ep_destroy(comm.ep)
     comm.ep = None
     h, inter, e, k = 2048, 768, 128, 8
@@ -160,7 +163,9 @@ def main():
         x = x_all[lo_t:hi_t].contiguous()
         y, idx, wts = big.forward(x)
         torch.cuda.synchronize()
-        logits = f32(ops.linear(x, wr, bias=br, out_dtype=torch.float32))
+        logits = f32(big.logits)                                    # the router logits the layer chose from
+        rel, cos = o.rel_err_and_cosine(logits, o.moe_router_logits(f32(x), f32(wr), f32(br)))
+        assert rel <= 2e-2 and cos >= 0.9999, ("ep router logits vs oracle", t_total, rel, cos)
         want_idx, want_w = o.moe_topk(logits, k)
         assert np.array_equal(idx.cpu().numpy(), want_idx), ("ep routing vs oracle", t_total)
         assert np.abs(f32(wts) - want_w).max() < 1e-6

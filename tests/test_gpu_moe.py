@@ -176,3 +176,42 @@ def test_moe_full_shape_sampled_tokens_against_oracle(cuda):
             acc += want_w[tok, s] * o.bf16_round(o.linear(hid, to_np(wd[ex])))[0]
         want[n] = acc
     assert_matmul_close(y[toks], want, "moe layer output, full shape")
+
+
+@pytest.mark.parametrize("t,e,h,k", [(1, 128, 2048, 8), (7, 128, 2048, 8), (16, 128, 2048, 8), (17, 128, 2048, 8),
+                                     (64, 128, 2048, 8), (1000, 128, 2048, 8), (5, 40, 512, 4), (300, 72, 256, 2),
+                                     (3, 16, 160, 4), (50, 16, 520, 3)])
+def test_fused_router_and_topk(cuda, t, e, h, k):
+    """izb_moe_route: logits within the matmul gates of the oracle's router, indices and weights bit-exact
+    against the oracle's top-k of the logits the launch itself wrote (ragged token tiles, expert counts
+    that are not a multiple of 32, hidden sizes the fused kernel does not take and hands to the
+    linear layer + top-k kernels instead)."""
+    from izwi_b200 import moe, ops
+    rng = np.random.default_rng(1000 + t + e)
+    x = bf16_np(rng.normal(0, 1, (t, h)))
+    wr = bf16_np(rng.normal(0, 1.0 / np.sqrt(h), (e, h)))
+    br = bf16_np(rng.normal(0, 0.5, e))
+    up = lambda a: torch.from_numpy(a).to(cuda).to(torch.bfloat16)  # noqa: E731
+    for bias in (br, None):
+        logits, idx, wts = moe.route(up(x), up(wr), None if bias is None else up(bias), k)
+        ops.Context.get(0).check()
+        assert_matmul_close(logits, o.moe_router_logits(x, wr, bias), f"router logits T={t} E={e}")
+        want_idx, want_w = o.moe_topk(logits.cpu().numpy(), k)
+        assert np.array_equal(idx.cpu().numpy(), want_idx)
+        assert np.abs(wts.cpu().numpy() - want_w).max() < 1e-6
+
+
+def test_fused_router_ties_go_to_the_lowest_expert(cuda):
+    """Identical router rows give identical logits: the choice among them must be the lowest ids, in order."""
+    from izwi_b200 import moe
+    t, e, h, k = 33, 64, 256, 4
+    w = torch.zeros(e, h, device=cuda, dtype=torch.bfloat16)
+    w[:, 0] = 1.0                                     # every expert scores x[:, 0]
+    w[40:, 1] = 1.0                                   # experts 40.. also add x[:, 1]
+    x = torch.zeros(t, h, device=cuda, dtype=torch.bfloat16)
+    x[:, 0] = 0.5
+    x[::2, 1] = 1.0                                   # even tokens prefer experts 40.., odd tokens tie everywhere
+    logits, idx, wts = moe.route(x, w, None, k)
+    got = idx.cpu().numpy()
+    assert (got[0::2] == np.arange(40, 44)).all() and (got[1::2] == np.arange(0, 4)).all()
+    assert np.allclose(wts.cpu().numpy(), 0.25)
