@@ -49,6 +49,12 @@ typedef enum izb_dtype { IZB_BF16 = 0, IZB_F32 = 1 } izb_dtype;
 typedef enum izb_wfmt { IZB_W_BF16 = 0, IZB_W_Q8_0 = 1, IZB_W_Q4_K = 2, IZB_W_Q6_K = 3 } izb_wfmt;
 
 int32_t izb_version(void);
+/* The gate of this library's kernels: the environment variable IZWI_B200_KERNELS, read once per
+ * process with the rule the reference applies to IZWI_FUSED_KERNELS (`use_fused_kernels`,
+ * kernels/mod.rs:46-57): unset means on; set, it is on only for 1 / true / yes / on (any case,
+ * surrounding blanks ignored).  The entry points do not consult it: the host layer above does, and
+ * takes its own path (the reference's Candle ops) when it returns 0. */
+int32_t izb_kernels_enabled(void);
 const char* izb_status_string(int32_t status);
 
 /* One context per device and host thread group; owns a small device status
@@ -56,7 +62,9 @@ const char* izb_status_string(int32_t status);
 int32_t izb_ctx_create(int32_t device, izb_ctx** out);
 int32_t izb_ctx_destroy(izb_ctx* ctx);
 /* Synchronises `stream`, then returns IZB_ERR_TIMEOUT if any kernel launched
- * through this context recorded a wait that gave up (and clears the record). */
+ * through this context recorded a wait that gave up, or IZB_ERR_BAD_ARG if the embedding lookup met
+ * a token id outside its table (and clears the record).  Call it with the context quiescent: a
+ * record made by a kernel of another stream while this call runs may be cleared unseen. */
 int32_t izb_ctx_check(izb_ctx* ctx, izb_stream stream);
 /* Launches a one-warp kernel that waits on a barrier nothing completes, through the bounded wait all
  * pipeline kernels share: after the limit (about a second) it records the time-out and returns, so
@@ -417,6 +425,34 @@ int32_t izb_decode_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q,
                                  int32_t kv_heads, int32_t head_dim, int64_t kv_len,
                                  int64_t kv_capacity, int64_t ld_q, int64_t ld_out, float scale,
                                  void* workspace, size_t workspace_bytes);
+
+/* ---- what a prompt needs before the first decode step -----------------------------------------
+ * out[t, :] = table[ids[t], :]: the embedding lookup in front of the first layer (`embed_tokens`,
+ * models/architectures/qwen3/core.rs:2099-2103).  table bf16 [vocab, hidden], ids int32 on the device
+ * (a decode step passes the id izb_argmax_rows left there), out rows ld_out apart.  An id outside
+ * [0, vocab) gives a zero row and makes the next izb_ctx_check return IZB_ERR_BAD_ARG. */
+int32_t izb_embed_rows(izb_ctx* ctx, izb_stream stream, const void* table, int64_t vocab, int64_t hidden,
+                       const int32_t* ids, int64_t tokens, void* out, int64_t ld_out);
+/* izb_qk_norm_rope_append for a run of q_len consecutive tokens per sequence: token i of sequence b is
+ * row b * q_len + i of qkv (rows ld_qkv apart) and of q_out, sits at cache position pos0 + i and is
+ * rotated by row i of the tables [q_len, head_dim / 2].  With q_len = 1 it equals the decode call.
+ * Replaces apply_qk_norm_pair + apply_rope_pair + the cache append of Qwen3Attention::forward for
+ * seq_len > 1 (qwen3/core.rs:1465-1575, 1624-1732). */
+int32_t izb_qk_norm_rope_append_seq(izb_ctx* ctx, izb_stream stream, const void* qkv, int64_t ld_qkv,
+                                    const void* q_norm_weight, const void* k_norm_weight, float eps,
+                                    const void* cos_half, const void* sin_half, void* q_out,
+                                    int64_t ld_q_out, void* k_cache, void* v_cache, int64_t batch,
+                                    int64_t q_len, int32_t heads, int32_t kv_heads, int32_t head_dim,
+                                    int64_t pos0, int64_t kv_capacity);
+/* Causal attention of those q_len new tokens over the cache they have just been appended to: token i
+ * attends to positions 0 .. pos0 + i.  q / out rows as above ([batch * q_len, heads * head_dim], rows
+ * ld_q / ld_out apart, q 16-byte aligned rows), caches head-major [batch, kv_heads, kv_capacity,
+ * head_dim] bf16.  head_dim 64 or 128.  Replaces the seq_len > 1 branches of Qwen3Attention::forward
+ * (qwen3/core.rs:1688-1732: causal mask + softmax + matmul). */
+int32_t izb_prefill_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q, const void* k_cache,
+                                  const void* v_cache, void* out, int64_t batch, int64_t q_len,
+                                  int32_t heads, int32_t kv_heads, int32_t head_dim, int64_t pos0,
+                                  int64_t kv_capacity, int64_t ld_q, int64_t ld_out, float scale);
 
 /* ---- GGUF files -------------------------------------------------------------------------------
  * Read-only view of a GGUF v2 / v3 file (header, metadata, tensor directory; the file is mapped,

@@ -48,6 +48,7 @@ class MoeArgs(C.Structure):
 
 _SIGNATURES = {
     "izb_version": (C.c_int32, []),
+    "izb_kernels_enabled": (C.c_int32, []),
     "izb_status_string": (C.c_char_p, [C.c_int32]),
     "izb_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(C.c_void_p)]),
     "izb_ctx_destroy": (C.c_int32, [C.c_void_p]),
@@ -130,6 +131,14 @@ _SIGNATURES = {
     "izb_decode_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                              C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                              C.c_int64, C.c_float, C.c_void_p, C.c_size_t]),
+    "izb_embed_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                   C.c_int64]),
+    "izb_qk_norm_rope_append_seq": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_float,
+                                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
+                                                C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
+    "izb_prefill_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                              C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
+                                              C.c_int64, C.c_float]),
     "izb_gguf_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "izb_gguf_close": (C.c_int32, [C.c_void_p]),
     "izb_gguf_version": (C.c_int32, [C.c_void_p]),

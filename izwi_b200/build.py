@@ -78,7 +78,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         logs = list(pool.map(lambda c: _run(c, env), jobs))
     if verbose:
         print("\n".join(logs))
-    _run([nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objects), "-ldl"], env)
+    # linked under another name and moved into place, so a reader never sees a half-written library
+    tmp = LIB_PATH.with_suffix(".so.tmp")
+    _run([nvcc, "-shared", "-o", str(tmp), *map(str, objects), "-ldl"], env)
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

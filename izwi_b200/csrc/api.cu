@@ -1,7 +1,10 @@
 // C ABI: context, block dequantisation, SwiGLU glue and the linear-layer entry points.
+#include <cctype>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
+#include <string>
 
 #include "izb_common.cuh"
 #include "gemm_tc.cuh"
@@ -155,6 +158,21 @@ extern "C" {
 
 int32_t izb_version(void) { return 100; }
 
+int32_t izb_kernels_enabled(void) {
+    static std::once_flag once;
+    static int32_t enabled = 1;
+    std::call_once(once, [] {
+        const char* raw = std::getenv("IZWI_B200_KERNELS");
+        if (!raw) return;  // unset: on
+        std::string v(raw);
+        const size_t a = v.find_first_not_of(" \t\r\n"), b = v.find_last_not_of(" \t\r\n");
+        v = a == std::string::npos ? std::string() : v.substr(a, b - a + 1);
+        for (char& c : v) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+        enabled = (v == "1" || v == "true" || v == "yes" || v == "on") ? 1 : 0;
+    });
+    return enabled;
+}
+
 const char* izb_status_string(int32_t status) {
     switch (status) {
         case IZB_OK: return "ok";
@@ -224,12 +242,15 @@ int32_t izb_ctx_check(izb_ctx* ctx, izb_stream stream) {
     int host[IZB_STATUS_WORDS] = {0};
     IZB_CUDA_TRY(cudaMemcpyAsync(host, ctx->d_status, sizeof(host), cudaMemcpyDeviceToHost, s));
     IZB_CUDA_TRY(cudaStreamSynchronize(s));
-    bool any = false;
-    for (int i = 0; i < IZB_STATUS_WORDS; ++i) any = any || host[i] != 0;
+    bool any = false, waited = false;
+    for (int i = 0; i < IZB_STATUS_WORDS; ++i) {
+        any = any || host[i] != 0;
+        waited = waited || (host[i] != 0 && i != 6);  // word 6: a token id outside the embedding table
+    }
     if (any) {
         IZB_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(host), s));
         IZB_CUDA_TRY(cudaStreamSynchronize(s));
-        return IZB_ERR_TIMEOUT;
+        return waited ? IZB_ERR_TIMEOUT : IZB_ERR_BAD_ARG;
     }
     return IZB_OK;
 }

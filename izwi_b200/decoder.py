@@ -125,8 +125,8 @@ class Qwen3Decoder:
         ang = (pos * self.inv_freq)[None, :].expand(batch, -1)
         return ang.cos().to(torch.bfloat16).contiguous(), ang.sin().to(torch.bfloat16).contiguous()
 
-    def step(self, tokens: torch.Tensor, caches: list, pos: int, cos_half=None, sin_half=None) -> torch.Tensor:
-        """tokens [batch] int64 -> next tokens [batch] int32 (greedy)."""
+    def step(self, tokens: torch.Tensor, caches: list, pos: int, cos_half=None, sin_half=None, return_logits: bool = False):
+        """tokens [batch] int64 -> next tokens [batch] int32 (greedy); with return_logits also the fp32 logits."""
         if cos_half is None:
             cos_half, sin_half = self.rope_tables(pos, tokens.shape[0])
         out, stream = self.embed[tokens], None
@@ -139,4 +139,5 @@ class Qwen3Decoder:
         else:
             hidden = ops.rms_norm(out, self.final_norm, self.w.eps, residual=stream)
             logits = ops.linear(hidden, self.lm_head, self.lm_head_fmt, n=vocab, k=self.w.hidden, out_dtype=torch.float32)
-        return ops.argmax_rows(logits)
+        nxt = ops.argmax_rows(logits)
+        return (nxt, logits) if return_logits else nxt

@@ -6,6 +6,9 @@
 #include <cstring>
 #include <functional>
 
+#include <cstdlib>
+
+#include "izwi_chat.hpp"
 #include "izwi_host.hpp"
 
 using namespace izwi_host;
@@ -177,7 +180,62 @@ static void gpu_tests() {
     EXPECT(worst <= 2e-2 * scale);
 }
 
+// `chat <model.gguf> <max_new_tokens> <logits.bin> <mode> <prompt ids...>`: loads a Qwen3 model from a GGUF file,
+// runs the prompt (mode "prefill": all tokens in one pass through the GEMM and the causal attention; mode "decode":
+// one token at a time through the decode kernels), writes the fp32 logits the first new token is chosen from to
+// logits.bin, then generates greedily with start_decode / decode_step and prints the ids.  Token 0 ends a reply.
+static int chat_main(int argc, char** argv) {
+    if (argc < 7) {
+        std::printf("usage: host_selftest chat model.gguf max_new logits.bin prefill|decode id...\n");
+        return 2;
+    }
+    try {
+        auto ctx = std::make_shared<Context>(0);
+        GgufLoader loader(argv[2]);
+        auto model = loader.load_qwen3(*ctx, 256);
+        const size_t max_new = static_cast<size_t>(std::atoi(argv[3]));
+        const bool token_by_token = std::strcmp(argv[5], "decode") == 0;
+        std::vector<uint32_t> prompt;
+        for (int i = 6; i < argc; ++i) prompt.push_back(static_cast<uint32_t>(std::atoi(argv[i])));
+        ChatSpecials specials;
+        specials.eos = 0;
+        Qwen3ChatModel chat(ctx, model, specials);
+        ChatDecodeState st = chat.start_decode(token_by_token ? std::vector<uint32_t>{prompt[0]} : prompt, max_new);
+        if (token_by_token) {
+            // the same prompt through the one-token path: every further prompt token is a forced decode step
+            for (size_t i = 1; i < prompt.size(); ++i) {
+                const int32_t id = static_cast<int32_t>(prompt[i]);
+                if (cudaMemcpy(st.next_id.get(), &id, 4, cudaMemcpyHostToDevice) != cudaSuccess) throw InferenceError("copy failed");
+                model->forward(*ctx, nullptr, static_cast<const int32_t*>(st.next_id.get()), 1, st.pos, st.cache,
+                               static_cast<float*>(st.logits.get()), st.scratch);
+                st.pos += 1;
+            }
+            ctx->check_device();
+        }
+        const auto raw = st.logits.to_host();
+        if (FILE* f = std::fopen(argv[4], "wb")) {
+            std::fwrite(raw.data(), 1, raw.size(), f);
+            std::fclose(f);
+        } else {
+            throw InferenceError("cannot write the logits file");
+        }
+        std::printf("generated:");
+        while (true) {
+            const ChatDecodeStep step = chat.decode_step(st);
+            if (step.has_token) std::printf(" %u", step.token);
+            if (step.finished) break;
+        }
+        ctx->check_device();
+        std::printf("\npositions: %lld\nchat: ok\n", static_cast<long long>(st.pos));
+        return 0;
+    } catch (const std::exception& e) {
+        std::printf("FAIL %s\n", e.what());
+        return 1;
+    }
+}
+
 int main(int argc, char** argv) {
+    if (argc > 1 && std::strcmp(argv[1], "chat") == 0) return chat_main(argc, argv);
     const bool no_gpu = argc > 1 && std::strcmp(argv[1], "--no-gpu") == 0;
     try {
         host_only_tests();

@@ -28,6 +28,11 @@ struct InferenceError : std::runtime_error {
     using std::runtime_error::runtime_error;
 };
 
+// The IZWI_B200_KERNELS gate (default on; the rule of `use_fused_kernels`, kernels/mod.rs:46-57), read once per
+// process.  Off means "take the caller's own path": a Rust shim would run Candle's ops; this layer has no other
+// path and refuses.
+inline bool use_b200_kernels() { return izb_kernels_enabled() != 0; }
+
 inline void check(int32_t status, const char* where) {
     if (status != IZB_OK) throw InferenceError(std::string(where) + ": " + izb_status_string(status));
 }
@@ -174,6 +179,8 @@ class Qwen3Projection {
     void forward(const Context& ctx, cudaStream_t stream, const void* x, int64_t m, void* y, int64_t ldx = 0,
                  int64_t ldy = 0, void* workspace = nullptr, size_t workspace_bytes = 0,
                  int32_t epilogue = IZB_EPI_NONE, const Fusion* fusion = nullptr) const {
+        if (!use_b200_kernels())
+            throw InferenceError("IZWI_B200_KERNELS is off: the B200 projection kernels are disabled");
         izb_linear_args a{};
         if (fusion) {
             a.prologue = fusion->prologue;

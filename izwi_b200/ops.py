@@ -252,6 +252,52 @@ def decode_gqa_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     return out
 
 
+def embed_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """Embedding lookup (`embed_tokens`, qwen3/core.rs:2099-2103): table [vocab, hidden] bf16, ids int32 [tokens]."""
+    assert table.dtype == torch.bfloat16 and table.is_contiguous() and ids.dtype == torch.int32 and ids.is_contiguous()
+    out = torch.empty(ids.numel(), table.shape[1], device=table.device, dtype=torch.bfloat16)
+    ctx = Context.get(table.device.index)
+    L.check(L.lib().izb_embed_rows(ctx.handle, _stream(), _ptr(table), table.shape[0], table.shape[1], _ptr(ids), ids.numel(),
+                                   _ptr(out), out.stride(0)), "izb_embed_rows")
+    return out
+
+
+def qk_norm_rope_append_seq(qkv: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
+                            cos_half: torch.Tensor, sin_half: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                            heads: int, q_len: int, pos0: int) -> torch.Tensor:
+    """q/k head norms, rotation and cache append for q_len consecutive tokens per sequence:
+    qkv [batch * q_len, (heads + 2 kv_heads) * d], tables [q_len, d / 2] -> q [batch * q_len, heads, d]."""
+    rows = qkv.shape[0]
+    b = rows // q_len
+    kvh, cap, d = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (heads + 2 * kvh) * d and b * q_len == rows
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and cos_half.is_contiguous() and sin_half.is_contiguous()
+    assert cos_half.shape == sin_half.shape == (q_len, d // 2)
+    q = torch.empty(rows, heads, d, device=qkv.device, dtype=torch.bfloat16)
+    ctx = Context.get(qkv.device.index)
+    L.check(L.lib().izb_qk_norm_rope_append_seq(ctx.handle, _stream(), _ptr(qkv), qkv.stride(0), _ptr(q_norm), _ptr(k_norm),
+                                                float(eps), _ptr(cos_half), _ptr(sin_half), _ptr(q), q.stride(0), _ptr(k_cache),
+                                                _ptr(v_cache), b, q_len, heads, kvh, d, pos0, cap), "izb_qk_norm_rope_append_seq")
+    return q
+
+
+def prefill_gqa_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, q_len: int, pos0: int,
+                          scale: float | None = None) -> torch.Tensor:
+    """Causal attention of q_len new tokens per sequence (already appended at pos0 ..) over the cache:
+    q [batch * q_len, heads, d] -> out of the same shape."""
+    assert q.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    rows, h, d = q.shape
+    b = rows // q_len
+    assert k_cache.shape == v_cache.shape and k_cache.shape[0] == b and k_cache.shape[3] == d
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and q.stride(2) == 1 and q.stride(1) == d
+    out = torch.empty(rows, h, d, device=q.device, dtype=torch.bfloat16)
+    ctx = Context.get(q.device.index)
+    L.check(L.lib().izb_prefill_gqa_attention(ctx.handle, _stream(), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), b, q_len, h,
+                                              k_cache.shape[1], d, pos0, k_cache.shape[2], q.stride(0), out.stride(0),
+                                              float(d ** -0.5 if scale is None else scale)), "izb_prefill_gqa_attention")
+    return out
+
+
 class LinearGroup:
     """A set of independent small-M linear layers run by one persistent launch
     (izb_linear_group_*).  Keeps the tensors alive and owns the device copy of

@@ -120,6 +120,11 @@ class Qwen3Projection:
         return Qwen3ProjectionDiagnostics(0, 0, 1)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from . import use_b200_kernels
+        if not use_b200_kernels():
+            # the gate next to IZWI_FUSED_KERNELS (kernels/mod.rs:46-57): off means the caller's own
+            # (Candle) path; this mirror has none to fall back to and says so
+            raise InferenceError("IZWI_B200_KERNELS is off: the B200 projection kernels are disabled")
         if not x.is_cuda:
             raise InferenceError("projection input must be a CUDA tensor")
         xb = x.to(torch.bfloat16)

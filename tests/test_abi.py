@@ -68,3 +68,19 @@ def test_ctx_create_without_device_reports_no_device(lib):
     assert lib.izb_ctx_create(0, C.byref(h)) == -5
     assert not h.value
     assert lib.izb_ctx_create(-1, C.byref(h)) == -1
+
+
+def test_kernel_gate_follows_the_reference_rule():
+    """IZWI_B200_KERNELS: unset = on; set = on only for 1 / true / yes / on (kernels/mod.rs:46-57).  Read once per
+    process, so every value is tried in a process of its own."""
+    import os
+    import subprocess
+    import sys
+    code = "import izwi_b200; print(int(izwi_b200.use_b200_kernels()))"
+    for value, want in ((None, "1"), ("1", "1"), (" TRUE ", "1"), ("on", "1"), ("Yes", "1"), ("0", "0"), ("off", "0"),
+                        ("", "0"), ("2", "0")):
+        env = {k: v for k, v in os.environ.items() if k != "IZWI_B200_KERNELS"}
+        if value is not None:
+            env["IZWI_B200_KERNELS"] = value
+        out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=str(ROOT), timeout=120)
+        assert out.stdout.strip() == want, (value, out.stdout, out.stderr)

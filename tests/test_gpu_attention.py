@@ -142,3 +142,65 @@ def test_unaligned_query_is_refused_before_any_launch(cuda):
     assert float(out.min()) == 3.0
     assert call(qbuf.data_ptr(), h * d + 8) == L.IZB_OK                # an aligned, padded layout is fine
     ctx.check()
+
+
+# ---- a prompt's tokens: embedding rows, q/k norm + rotation + append for a run of tokens, causal attention ----
+
+def test_embed_rows_and_out_of_range_id(cuda):
+    from izwi_b200 import IzbError, _lib, ops
+    rng = np.random.default_rng(5)
+    table = bf16_np(rng.normal(0, 1, (50, 64)))
+    ids = np.array([0, 49, 7, 7, 13], dtype=np.int32)
+    got = ops.embed_rows(_dev(table, cuda), torch.from_numpy(ids).to(cuda))
+    ops.Context.get(0).check()
+    assert np.array_equal(to_np(got), table[ids])
+    bad = ops.embed_rows(_dev(table, cuda), torch.tensor([3, 50, -1], dtype=torch.int32, device=cuda))
+    with pytest.raises(IzbError) as e:
+        ops.Context.get(0).check()
+    assert e.value.status == _lib.IZB_ERR_BAD_ARG          # reported after the fact, as a bad argument
+    assert np.array_equal(to_np(bad)[0], table[3]) and not to_np(bad)[1:].any()
+    ops.Context.get(0).check()
+
+
+@pytest.mark.parametrize("b,q_len,h,kvh,d,pos0,cap", [(1, 1, 16, 8, 128, 0, 8), (1, 7, 16, 8, 128, 0, 16),
+                                                     (2, 33, 8, 2, 64, 5, 64), (1, 70, 4, 4, 128, 0, 128),
+                                                     (1, 3, 32, 8, 128, 250, 256)])
+def test_prompt_tokens_norm_rope_append_and_causal_attention(cuda, b, q_len, h, kvh, d, pos0, cap):
+    """qk_norm_rope_append_seq + prefill_gqa_attention against the oracle's per-token composition: head
+    norms, rotation by the token's position, cache append, then each new token attends to everything up
+    to and including itself.  Earlier positions of the cache hold random keys and values."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(q_len * 100 + h)
+    eps = 1e-6
+    qkv = bf16_np(rng.normal(0, 1, (b * q_len, (h + 2 * kvh) * d)))
+    qn, kn = bf16_np(rng.normal(1, 0.1, d)), bf16_np(rng.normal(1, 0.1, d))
+    kc, vc = bf16_np(rng.normal(0, 1, (b, kvh, cap, d))), bf16_np(rng.normal(0, 1, (b, kvh, cap, d)))
+    inv = 1.0 / (10000.0 ** (np.arange(0, d, 2) / d))
+    ang = (pos0 + np.arange(q_len))[:, None] * inv[None, :]
+    cos, sin = bf16_np(np.cos(ang)), bf16_np(np.sin(ang))
+    kcd, vcd = _dev(kc, cuda), _dev(vc, cuda)
+    q = ops.qk_norm_rope_append_seq(_dev(qkv, cuda), _dev(qn, cuda), _dev(kn, cuda), eps, _dev(cos, cuda), _dev(sin, cuda), kcd, vcd,
+                                    h, q_len, pos0)
+    out = ops.prefill_gqa_attention(q, kcd, vcd, q_len, pos0)
+    ops.Context.get(0).check()
+    # oracle: token by token
+    want_q = np.zeros((b * q_len, h, d), dtype=np.float32)
+    want = np.zeros((b * q_len, h, d), dtype=np.float32)
+    for bi in range(b):
+        for i in range(q_len):
+            row = qkv[bi * q_len + i]
+            qh = row[: h * d].reshape(1, h, d)
+            kh = row[h * d: (h + kvh) * d].reshape(1, kvh, d)
+            vh = row[(h + kvh) * d:].reshape(kvh, d)
+            qh, _ = o.rms_norm(qh, qn, eps)
+            kh, _ = o.rms_norm(kh, kn, eps)
+            qh = o.rope_pair(qh, cos[i:i + 1], sin[i:i + 1])
+            kh = o.rope_pair(kh, cos[i:i + 1], sin[i:i + 1])
+            kc[bi, :, pos0 + i], vc[bi, :, pos0 + i] = kh[0], vh
+            want_q[bi * q_len + i] = qh[0]
+            want[bi * q_len + i] = o.decode_gqa_attention(qh, kc[bi:bi + 1], vc[bi:bi + 1], pos0 + i + 1, d ** -0.5)[0]
+    # the fused kernel rounds once where the composition rounds after the norm and after the rotation
+    assert np.abs(to_np(q) - want_q).max() <= 3e-2 * np.abs(want_q).max()
+    assert np.abs(to_np(kcd)[:, :, pos0:pos0 + q_len] - kc[:, :, pos0:pos0 + q_len]).max() <= 3e-2 * np.abs(kc).max()
+    assert np.array_equal(to_np(vcd), vc)
+    assert_matmul_close(out.reshape(b * q_len, h * d), want.reshape(b * q_len, h * d), f"causal attention q_len={q_len}")
