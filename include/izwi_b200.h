@@ -105,8 +105,8 @@ typedef enum izb_epilogue {
                            1266-1280).  Candle's source is not part of the reference tree, so this is inferred. */
 } izb_epilogue;
 
-/* Function of the activations fused in front of a linear layer (decode step, one or two tokens).
- * Both skip the bf16 rounding of the intermediate the separate launches would store. */
+/* Function of the activations in front of a linear layer.  Inside the one- and two-token kernel both
+ * skip the bf16 rounding of the intermediate the separate launches would store. */
 typedef enum izb_prologue {
     IZB_PRO_NONE = 0,
     IZB_PRO_RMSNORM = 1,  /* y = W (x * rsqrt(mean(x^2) + eps) * norm_weight): the RmsNorm in front of the
@@ -132,9 +132,14 @@ typedef struct izb_linear_args {
     size_t workspace_bytes;
     int32_t epilogue;  /* izb_epilogue fused after the bias add */
     int32_t prologue;  /* izb_prologue applied to x on its way into the product */
-    /* Decode-step fusions: only the one- and two-token block-format kernel takes them (see
-     * izb_linear_fusion_max_tokens); any other route answers IZB_ERR_UNSUPPORTED and the caller
-     * runs izb_rms_norm / izb_silu_mul / the add as launches of their own. */
+    /* What a decoder layer does around a projection (qwen3/core.rs:1863-1881), for every weight format
+     * and token count.  `residual` is added by the epilogue of whichever kernel runs the product.
+     * `prologue` is computed inside the one- and two-token block-format kernel (see
+     * izb_linear_fusion_max_tokens: nothing is stored in between); on every other route izb_linear
+     * itself launches the row norm or the SiLU-multiply into the tail of `workspace` (bf16, as the
+     * reference's separate ops store it) and runs the product on that: size the workspace with
+     * izb_linear_workspace_bytes_args.  The grouped launch (izb_linear_group_*) takes prologues only
+     * for the in-kernel case. */
     const void* norm_weight; /* IZB_PRO_RMSNORM: bf16 [K], 16-byte aligned */
     const void* residual;    /* bf16 [M, ld_residual] added to the output after the bias; NULL = none */
     int64_t ld_residual;
@@ -163,9 +168,12 @@ size_t izb_linear_workspace_bytes_ex(int32_t wfmt, int64_t M, int64_t N, int64_t
  * row (64 of a bf16 row) at a time; other widths (a Q8_0 row of 384 values, say) run on the GEMM,
  * for which block formats need the workspace (the query above accounts for it; without one the
  * answer is IZB_ERR_UNSUPPORTED). */
+/* The query for a whole call as it will be made (format, shape, epilogue AND prologue): bytes of
+ * `workspace` izb_linear needs for exactly these arguments. */
+size_t izb_linear_workspace_bytes_args(const izb_linear_args* args);
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args);
-/* Largest M for which izb_linear / izb_linear_batch accept `prologue`, `residual` for weights in
- * `wfmt` (0: never). */
+/* Largest M for which the kernel itself computes `prologue` for weights in `wfmt` (0: never; the
+ * call is still accepted above it, through the workspace). */
 int32_t izb_linear_fusion_max_tokens(int32_t wfmt);
 
 /* Thin typed forms of izb_linear (y is bf16, contiguous strides). */

@@ -59,6 +59,7 @@ _SIGNATURES = {
     "izb_dequantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "izb_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
     "izb_linear_workspace_bytes_ex": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "izb_linear_workspace_bytes_args": (C.c_size_t, [C.POINTER(LinearArgs)]),
     "izb_linear": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(LinearArgs)]),
     "izb_linear_fusion_max_tokens": (C.c_int32, [C.c_int32]),
     "izb_linear_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

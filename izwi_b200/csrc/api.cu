@@ -365,6 +365,21 @@ int32_t izb_linear_fusion_max_tokens(int32_t wfmt) {
     return skinny_gemv_max_tokens();
 }
 
+// Whether the one- and two-token integer-dot-product kernel takes this call with its prologue / residual inside.
+static bool fuses_in_kernel(const izb_linear_args* a) {
+    return (a->wfmt == IZB_W_Q8_0 || a->wfmt == IZB_W_Q4_K) && a->M <= izb_linear_fusion_max_tokens(a->wfmt) &&
+           a->epilogue == IZB_EPI_NONE && stream_width_ok(a->wfmt, a->K);
+}
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+size_t izb_linear_workspace_bytes_args(const izb_linear_args* a) {
+    if (!a || a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+    const size_t dense = izb_linear_workspace_bytes_ex(a->wfmt, a->M, a->N, a->K, a->epilogue);
+    const size_t pro = (a->prologue != IZB_PRO_NONE && !fuses_in_kernel(a))
+                           ? align256(static_cast<size_t>(a->M) * static_cast<size_t>(a->K) * 2) : 0;
+    return pro ? align256(dense) + pro : dense;
+}
+
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args) {
     if (!ctx || !args) return IZB_ERR_BAD_ARG;
     if (args->M < 0 || args->N < 0 || args->K < 0) return IZB_ERR_BAD_ARG;
@@ -373,15 +388,41 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
     if (args->M == 0 || args->N == 0) return IZB_OK;
     if (args->K == 0) return IZB_ERR_UNSUPPORTED;
     if (args->M > INT32_MAX || args->N > INT32_MAX || args->K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
-    if (args->prologue != IZB_PRO_NONE || args->residual) {
-        // only the integer-dot-product kernel fuses these; every other route declines
-        if (args->M > izb_linear_fusion_max_tokens(args->wfmt) || args->epilogue != IZB_EPI_NONE) return IZB_ERR_UNSUPPORTED;
-    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (args->prologue != IZB_PRO_NONE && !fuses_in_kernel(args)) {
+        // Routes whose kernel has no prologue stage (bf16 or Q6_K weights, more than two tokens, a fused
+        // epilogue): the normalised rows (or the SiLU-multiply) are written once to the tail of the
+        // workspace, bf16 as the reference's separate ops store them, and the product reads them there.
+        // The residual still rides in the product's epilogue.
+        const size_t dense = align256(izb_linear_workspace_bytes_ex(args->wfmt, args->M, args->N, args->K, args->epilogue));
+        const size_t pro = align256(static_cast<size_t>(args->M) * static_cast<size_t>(args->K) * 2);
+        if (!args->workspace || !izb_aligned(args->workspace, 16) || args->workspace_bytes < dense + pro) return IZB_ERR_BAD_ARG;
+        if (!args->x) return IZB_ERR_BAD_ARG;
+        void* xs = static_cast<uint8_t*>(args->workspace) + dense;
+        int rc;
+        if (args->prologue == IZB_PRO_RMSNORM) {
+            if (!args->norm_weight || args->ldx < args->K) return IZB_ERR_BAD_ARG;
+            rc = izb_rms_norm(ctx, stream, args->x, args->norm_weight, nullptr, xs, nullptr, args->M, args->K, args->ldx, 0, args->K, 0,
+                              args->norm_eps);
+        } else {
+            if (args->ldx < 2 * args->K) return IZB_ERR_BAD_ARG;
+            rc = izb_silu_mul(ctx, stream, args->x, static_cast<const uint8_t*>(args->x) + static_cast<size_t>(args->K) * 2, xs, args->M,
+                              args->K, args->ldx, args->ldx, args->K);
+        }
+        if (rc != IZB_OK) return rc;
+        izb_linear_args plain = *args;
+        plain.x = xs;
+        plain.ldx = args->K;
+        plain.prologue = IZB_PRO_NONE;
+        plain.norm_weight = nullptr;
+        plain.workspace_bytes = dense;  // what is left for the product itself
+        if (dense == 0) plain.workspace = nullptr;
+        return izb_linear(ctx, stream, &plain);
+    }
     if (args->wfmt == IZB_W_Q6_K) {
         // no in-place kernel for 210-byte super-blocks: multiply the bf16 copy in the workspace
         const size_t need = static_cast<size_t>(args->N) * static_cast<size_t>(args->K) * 2;
-        if ((args->N * args->K) % 256 != 0) return IZB_ERR_BAD_ARG;
+        if (args->K % 256 != 0) return IZB_ERR_BAD_ARG;
         if (!args->workspace || args->workspace_bytes < need || !izb_aligned(args->workspace, 16)) return IZB_ERR_BAD_ARG;
         const int rc = izb_dequantize(ctx, stream, IZB_W_Q6_K, args->w, args->N * args->K, IZB_BF16, args->workspace);
         if (rc != IZB_OK) return rc;
@@ -396,6 +437,8 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
     if (!quant && args->wfmt != IZB_W_BF16) return IZB_ERR_BAD_ARG;
     // a row must be a whole number of blocks, or the bytes of one row would run into the next
     if (quant && args->K % (args->wfmt == IZB_W_Q8_0 ? 32 : 256) != 0) return IZB_ERR_BAD_ARG;
+    if (args->residual && (args->ld_residual < (args->epilogue == IZB_EPI_SWIGLU ? args->N / 2 : args->N) || !izb_aligned(args->residual, 2)))
+        return IZB_ERR_BAD_ARG;
 
     const void* w_dense = args->w;
     const bool streams = stream_width_ok(args->wfmt, args->K);
@@ -414,12 +457,11 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
         }
     }
     if (use_gemm) {
-        if (args->prologue != IZB_PRO_NONE || args->residual) return IZB_ERR_UNSUPPORTED;
         if (!args->x || !args->y || !w_dense) return IZB_ERR_BAD_ARG;
         if (args->ldx < args->K) return IZB_ERR_BAD_ARG;
         return gemm_tc_launch(ctx, s, args->x, args->ldx, w_dense, args->bias, args->y, args->ldy, args->y_dtype,
                               static_cast<int>(args->M), static_cast<int>(args->N), static_cast<int>(args->K),
-                              args->epilogue, nullptr, 1);
+                              args->epilogue, nullptr, 1, args->residual, args->ld_residual);
     }
     // Token rows are processed 64 at a time by the weight-streaming kernel.
     const size_t ybytes = args->y_dtype == IZB_F32 ? 4 : 2;
@@ -428,6 +470,7 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
         a.M = args->M - m0 < 64 ? args->M - m0 : 64;
         a.x = static_cast<const uint8_t*>(args->x) + static_cast<size_t>(m0) * args->ldx * 2;
         a.y = static_cast<uint8_t*>(args->y) + static_cast<size_t>(m0) * args->ldy * ybytes;
+        if (args->residual) a.residual = static_cast<const uint8_t*>(args->residual) + static_cast<size_t>(m0) * args->ld_residual * 2;
         alignas(64) SkinnyProblem prob;
         SkinnyPlanHeader hdr;
         int rc = skinny_plan_build(ctx, &a, 1, &hdr, &prob);

@@ -319,7 +319,25 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                     const long long grow = static_cast<long long>(c.m0) + lg * 32 + r;
                     const int col = flush_col0 + ch * vec;
                     if (grow < c.rows_end && ch * vec < valid_cols && col < p.n_out) {
-                        const uint4 d = lds128(stg + static_cast<uint32_t>(r * 128 + ((ch ^ (r & 7)) << 4)));
+                        uint4 d = lds128(stg + static_cast<uint32_t>(r * 128 + ((ch ^ (r & 7)) << 4)));
+                        if (p.residual) {
+                            // the residual rides in here, where a lane holds 16 contiguous bytes of one output row
+                            const __nv_bfloat16* rs = p.residual + grow * p.ld_res + col;
+                            uint32_t w[4] = {d.x, d.y, d.z, d.w};
+                            if (f32_out) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (col + e < p.n_out) w[e] = __float_as_uint(__uint_as_float(w[e]) + __bfloat162float(rs[e]));
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float lo = bf16_lo_to_f32(w[e]) + (col + 2 * e < p.n_out ? __bfloat162float(rs[2 * e]) : 0.f);
+                                    const float hi = bf16_hi_to_f32(w[e]) + (col + 2 * e + 1 < p.n_out ? __bfloat162float(rs[2 * e + 1]) : 0.f);
+                                    w[e] = pack_bf16x2(lo, hi);
+                                }
+                            }
+                            d = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
                         if (f32_out) {
                             float* dst = static_cast<float*>(p.y) + grow * p.ldy + col;
                             if (vec_ok && col + 4 <= p.n_out) {
@@ -362,7 +380,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 
 int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long ldx, const void* w, const void* bias,
                    void* y, long long ldy, int y_dtype, int M, int N, int K, int epilogue, const int* seg_offsets,
-                   int n_experts) {
+                   int n_experts, const void* residual, long long ld_res) {
     if (!ctx || !x || !w || !y) return IZB_ERR_BAD_ARG;
     if (M <= 0 || N <= 0 || K <= 0 || n_experts <= 0) return IZB_ERR_BAD_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ldx < K) return IZB_ERR_UNSUPPORTED;
@@ -375,6 +393,7 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     if (swiglu && N % 2 != 0) return IZB_ERR_BAD_ARG;
     const int n_out = swiglu ? N / 2 : N;
     if (ldy < n_out) return IZB_ERR_BAD_ARG;
+    if (residual && (ld_res < n_out || !izb_aligned(residual, 2))) return IZB_ERR_BAD_ARG;
 
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
@@ -407,6 +426,8 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     p.y = y;
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.seg_offsets = seg_offsets;
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.ld_res = ld_res;
     p.ldy = ldy;
     p.M = M; p.N = N; p.K = K;
     p.n_experts = n_experts;

@@ -32,6 +32,8 @@ struct GemmParams {
     void* y;
     const __nv_bfloat16* bias;  // [N] (per expert: [E][N]) or null
     const int* seg_offsets;     // grouped: [E + 1] row offsets of the expert segments, else null
+    const __nv_bfloat16* residual;  // [M, ld_res] bf16 added to the finished (activated, rounded) output, or null
+    long long ld_res;
     long long ldy;
     int M, N, K;                // grouped: M = total rows of X
     int n_experts;              // 1 when not grouped
@@ -41,8 +43,10 @@ struct GemmParams {
     int n_out;                  // columns of Y
 };
 
+// residual (optional): bf16 [M, ld_res], added to the output after the bias and the epilogue function; the sum is
+// what a separate add of two bf16 tensors gives (the product is rounded to the output type first).
 int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long ldx, const void* w, const void* bias,
                    void* y, long long ldy, int y_dtype, int M, int N, int K, int epilogue, const int* seg_offsets,
-                   int n_experts);
+                   int n_experts, const void* residual = nullptr, long long ld_res = 0);
 
 }  // namespace izb

@@ -37,6 +37,7 @@ struct izb_ar {
     size_t slot_bytes;
     size_t big_bytes;  // capacity of each two-shot operand / result buffer (0: path off)
     size_t big_in[2], big_stage[2], big_res[2];  // byte offsets inside a region: operand, received chunks, result
+    size_t cta_flags;  // pushing kernel: [buffer][phase][source rank][CTA] call numbers
     int push;          // 1: chunks are pushed to their owner (stores only cross NVLink); 0: the owner pulls them (peer loads)
     int next_buf;      // buffer the next izb_ar_allreduce of a large message uses
     unsigned char* local;
@@ -271,34 +272,64 @@ __global__ void __launch_bounds__(AR2_THREADS)
 }
 
 // The same exchange with stores only on the wire (posted writes do not wait a round trip the way peer
-// loads do): every rank first pushes chunk j of its operand into a staging slot of rank j's region
-// (peers visited in the order rank+1, rank+2, ... so that at any moment every receiver hears from one
-// sender), the last CTA to finish raises flag_a; after all flag_a a rank adds the world staged copies
-// of its own chunk (local reads) in rank order and stores the result chunk into every region as above.
+// loads do) and no grid-wide meeting.  CTA c of every rank works on the same set of 16-byte units of
+// every chunk, so the exchange decomposes into independent per-CTA exchanges:
+//   1. CTA c pushes its units of chunk j into a staging slot of rank j's region, for every other rank j
+//      (peers visited in the order rank+1, rank+2, ... so that every receiver hears from one sender at
+//      a time), fences, and raises its own flag (the call number) on each of them;
+//   2. it waits for the same CTA's flag from every other rank, adds the staged copies of its units of
+//      this rank's chunk in rank order (local reads; every rank gets the same bits), and stores the
+//      result units into every region;
+//   3. it fences, raises its second flag on every rank, and leaves once it holds every other rank's
+//      second flag: when the kernel has completed, the whole result has landed here.
+// A CTA waits only for CTAs of other GPUs, never for a sibling, so any number of CTAs per SM is safe,
+// and CTAs proceed through the phases independently (no last-CTA tail, no atomics on the path).
+constexpr int AR2_MAX_CTAS = 160;  // flag slots per (buffer, phase, source rank); the grid never exceeds it
+
+__device__ __forceinline__ bool ar_wait_peers(const unsigned int* flags, int world, int rank, unsigned int value, int* status) {
+    // flags: [source rank][AR2_MAX_CTAS] for this CTA's column; thread t waits for rank (rank + 1 + t) % world
+    __shared__ int timed_out;
+    if (threadIdx.x == 0) timed_out = 0;
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < world - 1) {
+        const unsigned int* f = flags + ((rank + 1 + threadIdx.x) % world) * AR2_MAX_CTAS + blockIdx.x;
+        const long long t0 = clock64();
+        while (ar_ld_flag(f) != value) {
+            if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                timed_out = 1;
+                atomicExch(status, 3);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    return timed_out == 0;
+}
+
 template <bool F32>
 __global__ void __launch_bounds__(AR2_THREADS)
-    ar2_push_kernel(ArPeers peers, int world, int rank, int buf, size_t big_in, size_t big_stage, size_t big_res, int n_units,
-                    int* status) {
+    ar2_push_kernel(ArPeers peers, int world, int rank, int buf, size_t big_in, size_t big_stage, size_t big_res, size_t cta_flags,
+                    int n_units, int* status) {
     izb::pdl_launch_dependents();
     izb::pdl_wait();  // the operand was written by the kernel before this one
     ArDevState* st = reinterpret_cast<ArDevState*>(peers.base[rank]);
     const unsigned int call = st->big_seq[buf] + 1;
-    const size_t flag_a = offsetof(ArDevState, flag_a) + sizeof(unsigned int) * AR_MAX_WORLD * buf;
-    const size_t flag_b = offsetof(ArDevState, flag_b) + sizeof(unsigned int) * AR_MAX_WORLD * buf;
+    const size_t flags_a = cta_flags + sizeof(unsigned int) * AR2_MAX_CTAS * AR_MAX_WORLD * (2 * buf);
+    const size_t flags_b = cta_flags + sizeof(unsigned int) * AR2_MAX_CTAS * AR_MAX_WORLD * (2 * buf + 1);
     const int per = (n_units + world - 1) / world;  // units per chunk; the last chunk may be shorter or empty
     const uint4* mine = reinterpret_cast<const uint4*>(peers.base[rank] + big_in);
     const int step = static_cast<int>(gridDim.x) * AR2_THREADS;
     const int first = static_cast<int>(blockIdx.x) * AR2_THREADS + static_cast<int>(threadIdx.x);
-    __shared__ int last_flag;
 
-    // 1. push the chunks other ranks own
+    // 1. push this CTA's units of the chunks other ranks own
     for (int p = 1; p < world; ++p) {
         const int j = (rank + p) % world;
         const int len = min(per, n_units - j * per);
         uint4* dst = reinterpret_cast<uint4*>(peers.base[j] + big_stage) + static_cast<size_t>(rank) * per;
         const uint4* src = mine + static_cast<size_t>(j) * per;
-        // AR2_BATCH loads are issued before the first store: with one CTA per SM it is the number of
-        // 16-byte loads in flight per thread that sets the rate
+        // AR2_BATCH loads are issued before the first store: it is the number of 16-byte loads in
+        // flight per thread that sets the rate
         for (int i0 = first; i0 < len; i0 += step * AR2_BATCH) {
             uint4 v[AR2_BATCH];
 #pragma unroll
@@ -313,19 +344,13 @@ __global__ void __launch_bounds__(AR2_THREADS)
             }
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        last_flag = atomicAdd(&st->done_a[buf], 1u) == gridDim.x - 1;
-        if (last_flag) st->done_a[buf] = 0;
-    }
-    __syncthreads();
-    if (last_flag && static_cast<int>(threadIdx.x) < world) {
-        __threadfence_system();
-        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + threadIdx.x) % world] + flag_a) + rank, call);
-    }
-    // 2. all chunks of mine have arrived: add them in rank order, store the result into every region
-    const bool ok = ar_wait_all(reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_a), world, call, status);
+    __threadfence_system();  // this thread's pushes are performed everywhere ...
+    __syncthreads();         // ... and so are the whole CTA's before its flag goes out
+    if (static_cast<int>(threadIdx.x) < world - 1)
+        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + 1 + threadIdx.x) % world] + flags_a) + rank * AR2_MAX_CTAS + blockIdx.x,
+                   call);
+    // 2. the same CTA of every other rank has pushed: add in rank order, store the result everywhere
+    const bool ok = ar_wait_peers(reinterpret_cast<const unsigned int*>(peers.base[rank] + flags_a), world, rank, call, status);
     if (ok) {
         const int lo = per * rank, len = min(per, n_units - lo);
         const uint4* stage = reinterpret_cast<const uint4*>(peers.base[rank] + big_stage);
@@ -356,20 +381,13 @@ __global__ void __launch_bounds__(AR2_THREADS)
             for (int p = 0; p < world; ++p) reinterpret_cast<uint4*>(peers.base[(rank + p) % world] + big_res)[lo + i] = o;
         }
     }
-    // 3. as in the pulling kernel: result stores performed, last CTA raises flag_b, CTA 0 waits for everyone's
+    // 3. results performed everywhere, second flag out, wait for everyone else's
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        last_flag = atomicAdd(&st->done_b[buf], 1u) == gridDim.x - 1;
-        if (last_flag) st->done_b[buf] = 0;
-    }
-    __syncthreads();
-    if (last_flag && static_cast<int>(threadIdx.x) < world) {
-        __threadfence_system();
-        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + threadIdx.x) % world] + flag_b) + rank, call);
-    }
-    if (blockIdx.x == 0) (void)ar_wait_all(reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_b), world, call, status);
-    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < world - 1)
+        ar_st_flag(reinterpret_cast<unsigned int*>(peers.base[(rank + 1 + threadIdx.x) % world] + flags_b) + rank * AR2_MAX_CTAS + blockIdx.x,
+                   call);
+    (void)ar_wait_peers(reinterpret_cast<const unsigned int*>(peers.base[rank] + flags_b), world, rank, call, status);
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(&st->done_c[buf], 1u) == gridDim.x - 1) {
@@ -393,16 +411,18 @@ int ar2_launch(izb_ar* ar, cudaStream_t st, int buf, size_t bytes, int dtype) {
     const long long n_units = static_cast<long long>(bytes / 16);
     int* status = ar->ctx->d_status + 2;
     if (ar->push) {
-        // every CTA waits for the flag its last sibling raises, so all of them must get an SM: one CTA per SM at most
-        long long g = (n_units + AR2_THREADS * 8 - 1) / (AR2_THREADS * 8);
-        const int grid = static_cast<int>(g < 1 ? 1 : (g > ar->ctx->sm_count ? ar->ctx->sm_count : g));
+        // 128-thread CTAs, two per SM when the GPU is free, at most one beside a GEMM; every rank computes the
+        // same grid (CTA c exchanges with CTA c of the other ranks)
+        long long g = (n_units / ar->world + AR2_THREADS * 4 - 1) / (AR2_THREADS * 4);
+        const int cap = ar->ctx->sm_count < AR2_MAX_CTAS ? ar->ctx->sm_count : AR2_MAX_CTAS;
+        const int grid = static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
         if (dtype == IZB_F32)
             IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_push_kernel<true>, dim3(grid), dim3(AR2_THREADS), 0, st, ar->peers, ar->world,
-                                             ar->rank, buf, ar->big_in[buf], ar->big_stage[buf], ar->big_res[buf],
+                                             ar->rank, buf, ar->big_in[buf], ar->big_stage[buf], ar->big_res[buf], ar->cta_flags,
                                              static_cast<int>(n_units), status));
         else
             IZB_CUDA_TRY(izb::launch_chained(ar->ctx, ar2_push_kernel<false>, dim3(grid), dim3(AR2_THREADS), 0, st, ar->peers, ar->world,
-                                             ar->rank, buf, ar->big_in[buf], ar->big_stage[buf], ar->big_res[buf],
+                                             ar->rank, buf, ar->big_in[buf], ar->big_stage[buf], ar->big_res[buf], ar->cta_flags,
                                              static_cast<int>(n_units), status));
         ar->ctx->launches.fetch_add(1, std::memory_order_relaxed);
         return IZB_OK;
@@ -441,6 +461,9 @@ int32_t izb_ar_create(izb_ctx* ctx, int32_t world, int32_t rank, size_t max_byte
     // staging holds `world` chunks of ceil(units / world) units each: up to world - 1 units more than the message
     const size_t stage_bytes = ar->big_bytes ? ar->big_bytes + 16 * static_cast<size_t>(world) + 256 : 0;
     size_t at = AR_HEADER + 2 * static_cast<size_t>(world) * ar->slot_bytes;
+    ar->cta_flags = at;
+    at += sizeof(unsigned int) * AR2_MAX_CTAS * AR_MAX_WORLD * 4;  // [2 buffers][2 phases][ranks][CTAs]
+    at = (at + 255) / 256 * 256;
     for (int b = 0; b < 2; ++b) {
         ar->big_in[b] = at; at += ar->big_bytes;
         ar->big_stage[b] = at; at += (stage_bytes + 255) / 256 * 256;

@@ -409,6 +409,9 @@ __global__ void __launch_bounds__(SK_THREADS)
             const int N = PD.N, M = PD.M, ldy = PD.ldy;
             const __nv_bfloat16* bias = PD.bias;
             void* y = PD.y;
+            // a residual (rare: the descriptor says so) is added in fp32 with the bias, before the one rounding
+            const __nv_bfloat16* res = PD.extras ? plist[p].residual : nullptr;
+            const int ld_res = res ? plist[p].ld_res : 0;
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
 #pragma unroll
@@ -424,7 +427,8 @@ __global__ void __launch_bounds__(SK_THREADS)
                                 const int tok = nt * 8 + (FMT == IZB_W_Q8_0 ? perm_pair(n) : perm_quad(n));
                                 if (tok < M)
                                     store_out(y, y_dtype, static_cast<long long>(tok) * ldy + row,
-                                              acc[rt][nt][half * 2 + i] + b);
+                                              acc[rt][nt][half * 2 + i] + b +
+                                                  (res ? __bfloat162float(res[static_cast<long long>(tok) * ld_res + row]) : 0.f));
                             }
                         }
                     }
@@ -561,7 +565,9 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     // one to four tokens over block-quantised weights: integer dot products against activations in
     // 16-bit block fixed point (skinny_gemv.cu); gemv = tokens the kernel is instantiated for
     const int gemv = (fmt != IZB_W_BF16 && max_m <= skinny_gemv_max_tokens()) ? (max_m <= 1 ? 1 : max_m <= 2 ? 2 : 4) : 0;
-    if (any_extras && !gemv) return IZB_ERR_UNSUPPORTED;  // only that kernel fuses a prologue or a residual
+    bool any_prologue = false;
+    for (int i = 0; i < n; ++i) any_prologue = any_prologue || probs[i].prologue != IZB_PRO_NONE;
+    if (any_prologue && !gemv) return IZB_ERR_UNSUPPORTED;  // only that kernel takes a prologue; every kernel adds a residual
     const bool one_sb = tc || gemv != 0;  // one Q4_K super-block per box row
 
     // measured best residency: three CTAs per SM for Q8_0 (most ALU work per byte), two otherwise

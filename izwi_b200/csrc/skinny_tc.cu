@@ -184,14 +184,20 @@ __device__ __forceinline__ void stc_store_cols(T* y, long long ldy, const float 
         y += ldy;
     }
 }
-__device__ __forceinline__ void stc_epilogue(const ProbLite& L, int row0, uint32_t tmem_acc, int warp, int lane, int mp,
-                                             int y_dtype) {
+__device__ __forceinline__ void stc_epilogue(const ProbLite& L, const SkinnyProblem& full, int row0, uint32_t tmem_acc, int warp,
+                                             int lane, int mp, int y_dtype) {
     const int cc = (warp >> 2) * 16;
     if (cc >= mp) return;
     const int row = row0 + (warp & 3) * 32 + lane;
     float v[16];
     tc_ld_32x16(tmem_acc + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(cc), v);
     if (row >= L.N || cc >= L.M) return;
+    if (L.extras && full.residual) {
+        // residual [token, row] added in fp32 with the bias, before the one rounding
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (cc + j < L.M) v[j] += __bfloat162float(full.residual[static_cast<long long>(cc + j) * full.ld_res + row]);
+    }
     const float b = L.bias ? __bfloat162float(L.bias[row]) : 0.f;
     const long long first = static_cast<long long>(cc) * L.ldy + row;
     if (y_dtype == IZB_F32) stc_store_cols(static_cast<float*>(L.y) + first, L.ldy, v, b, L.M - cc);
@@ -405,7 +411,7 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
                         break;
                     }
                     tc_fence_after();
-                    stc_epilogue(prev_p < n_cached ? lite[prev_p] : lite_from(plist[prev_p]), prev_row0,
+                    stc_epilogue(prev_p < n_cached ? lite[prev_p] : lite_from(plist[prev_p]), plist[prev_p], prev_row0,
                                  tmem_base + static_cast<uint32_t>(acc * STC_ACC_COLS), warp, lane, mp, y_dtype);
                     tc_fence_before();
                     __syncwarp();
@@ -419,7 +425,7 @@ __global__ void __launch_bounds__(STC_THREADS, 1)
             const int acc = (it - 1) & 1;
             if (mbar_wait_bounded(smem_u32(&sh.acc_full[acc]), static_cast<uint32_t>(((it - 1) >> 1) & 1), abort_flag)) {
                 tc_fence_after();
-                stc_epilogue(prev_p < n_cached ? lite[prev_p] : lite_from(plist[prev_p]), prev_row0,
+                stc_epilogue(prev_p < n_cached ? lite[prev_p] : lite_from(plist[prev_p]), plist[prev_p], prev_row0,
                              tmem_base + static_cast<uint32_t>(acc * STC_ACC_COLS), warp, lane, mp, y_dtype);
                 tc_fence_before();
             } else {

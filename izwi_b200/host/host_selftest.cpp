@@ -147,7 +147,17 @@ static void gpu_tests() {
         auto of = download(yf);
         for (int c = 0; c < 2; ++c) EXPECT(std::fabs(of[c] - (o1[c] + resv[c])) <= 2e-2f * std::fmax(1.0f, std::fabs(o1[c] + resv[c])));
         EXPECT(izb_linear_fusion_max_tokens(IZB_W_Q8_0) >= 1 && izb_linear_fusion_max_tokens(IZB_W_BF16) == 0);
-        EXPECT(throws_with([&] { q.forward(ctx, nullptr, xin->get(), 2, yq.get(), 0, 0, nullptr, 0, IZB_EPI_NONE, &fu); }, "unsupported"));
+        // a dense projection takes the residual too (added by the streaming kernel's epilogue): sq + residual rows
+        {
+            auto res2 = upload({0.5f, -1.25f, 2.0f, 0.125f, -0.5f, 1.0f, 0.25f, -2.0f}, 2, 4, 4);
+            Qwen3Projection::Fusion fd;
+            fd.residual = res2->get();
+            DeviceBuffer yr(2 * 4 * 2);
+            q.forward(ctx, nullptr, xin->get(), 2, yr.get(), 0, 0, nullptr, 0, IZB_EPI_NONE, &fd);
+            ctx.check_device();
+            auto got = download(yr), resh = download(*res2);
+            for (int i = 0; i < 8; ++i) EXPECT(std::fabs(got[i] - (sq[i] + resh[i])) <= 2e-2f * std::fmax(1.0f, std::fabs(sq[i] + resh[i])));
+        }
     }
     QTensor wide{t2.data, 1, 512, IZB_W_Q8_0};
     EXPECT(throws_with([&] { packed_qmatmul_from_qtensors({t1, wide}); }, "input mismatch: expected 256, got 512"));

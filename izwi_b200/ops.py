@@ -93,7 +93,7 @@ def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: t
         a.norm_weight, a.norm_eps = norm_weight.data_ptr(), float(norm_eps)
     if residual is not None:
         assert residual.dtype == torch.bfloat16 and residual.dim() == 2 and residual.stride(1) == 1
-        assert residual.shape == (x.shape[0], n)
+        assert residual.shape == y.shape
         a.residual, a.ld_residual = residual.data_ptr(), residual.stride(0)
     return a
 
@@ -108,8 +108,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = 
     (flattened to M like the reference's Linear); `w` is [N, K] bf16 or the raw
     GGML bytes of N rows of K values.  `workspace=True` lets this wrapper provide
     the scratch buffer the library asks for (it never allocates itself).
-    `prologue` "rms_norm" (with `norm_weight`, `norm_eps`) or "silu_mul" (x is [.., 2K] = gate | up) and
-    `residual` are taken only for at most `linear_fusion_max_tokens(fmt)` token rows."""
+    `prologue` "rms_norm" (with `norm_weight`, `norm_eps`) or "silu_mul" (x is [.., 2K] = gate | up) is
+    computed inside the kernel for at most `linear_fusion_max_tokens(fmt)` token rows and through the
+    workspace otherwise; `residual` is added by the product's epilogue on every route."""
     if fmt == "bf16":
         n, k = w.shape
     assert n is not None and k is not None
@@ -119,13 +120,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = 
         raise ValueError(f"linear: input dim {x2.shape[1]} != weight in-dim {k}")
     n_out = n // 2 if epilogue == "swiglu" else n
     y = out if out is not None else torch.empty(x2.shape[0], n_out, device=x.device, dtype=out_dtype)
+    res2 = None if residual is None else residual.reshape(-1, n_out)
     if workspace is True:
-        need = L.lib().izb_linear_workspace_bytes_ex(WFMT[fmt], x2.shape[0], n, k, EPILOGUE[epilogue])
+        probe = linear_args(x2, w, fmt, n, k, y.reshape(-1, n_out), bias, epilogue, None, prologue, norm_weight, norm_eps, res2)
+        need = L.lib().izb_linear_workspace_bytes_args(C.byref(probe))
         workspace = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
     elif workspace is False:
         workspace = None
-    a = linear_args(x2, w, fmt, n, k, y.reshape(-1, n_out), bias, epilogue, workspace, prologue, norm_weight, norm_eps,
-                    None if residual is None else residual.reshape(-1, n_out))
+    a = linear_args(x2, w, fmt, n, k, y.reshape(-1, n_out), bias, epilogue, workspace, prologue, norm_weight, norm_eps, res2)
     ctx = Context.get(x.device.index)
     L.check(L.lib().izb_linear(ctx.handle, _stream(), C.byref(a)), "izb_linear")
     return y.reshape(*lead, n_out)

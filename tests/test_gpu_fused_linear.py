@@ -157,28 +157,80 @@ def test_edge_values(cuda):
     assert np.abs(got[1] - want[0]).max() <= 2e-4 * np.abs(want).max()
 
 
-def test_routes_that_do_not_fuse_decline(cuda):
+def test_where_the_prologue_is_computed(cuda):
     from izwi_b200 import IzbError, ops
     assert ops.linear_fusion_max_tokens("q8_0") == 2 and ops.linear_fusion_max_tokens("q4_k") == 2
     assert ops.linear_fusion_max_tokens("bf16") == 0
     k, n = 256, 8
     g = torch.ones(k, device=cuda, dtype=torch.bfloat16)
     q = torch.zeros(n * k // 32 * 34, device=cuda, dtype=torch.uint8)
-    w = torch.zeros(n, k, device=cuda, dtype=torch.bfloat16)
-    for m, wt, fmt in ((3, q, "q8_0"), (1, w, "bf16"), (80, q, "q8_0")):
-        x = torch.zeros(m, k, device=cuda, dtype=torch.bfloat16)
-        with pytest.raises(IzbError) as e:
-            ops.linear(x, wt, fmt, n=n, k=k, prologue="rms_norm", norm_weight=g, norm_eps=EPS)
-        assert e.value.status == -2
-        with pytest.raises(IzbError) as e:
-            ops.linear(x, wt, fmt, n=n, k=k, residual=torch.zeros(m, n, device=cuda, dtype=torch.bfloat16))
-        assert e.value.status == -2
-    # a group wider than two tokens declines at plan time
+    # outside the in-kernel case the prologue goes through the workspace: without one the call is refused ...
+    x = torch.zeros(3, k, device=cuda, dtype=torch.bfloat16)
+    with pytest.raises(IzbError) as e:
+        ops.linear(x, q, "q8_0", n=n, k=k, prologue="rms_norm", norm_weight=g, norm_eps=EPS, workspace=False)
+    assert e.value.status == -1
+    # ... and a group wider than two tokens declines a prologue at plan time (the grouped launch has no workspace)
     x = torch.zeros(4, k, device=cuda, dtype=torch.bfloat16)
     y = torch.zeros(4, n, device=cuda, dtype=torch.bfloat16)
     with pytest.raises(IzbError) as e:
         ops.LinearGroup([ops.linear_args(x, q, "q8_0", n, k, y, prologue="rms_norm", norm_weight=g, norm_eps=EPS)], cuda)
     assert e.value.status == -2
+
+
+@pytest.mark.parametrize("fmt,m", [("bf16", 1), ("bf16", 5), ("bf16", 32), ("bf16", 40), ("bf16", 300), ("q8_0", 3),
+                                   ("q8_0", 16), ("q8_0", 40), ("q8_0", 64), ("q8_0", 70), ("q8_0", 300), ("q4_k", 5),
+                                   ("q4_k", 24), ("q4_k", 200), ("q6_k", 1), ("q6_k", 90)])
+def test_prologue_and_residual_on_every_route(cuda, fmt, m):
+    """The decoder layer's glue for every weight format and token count: the same call as for one token.
+    Where the kernel has no prologue stage the library stores the normalised rows (bf16) and multiplies
+    them, so the result must match the oracle's composition with its bf16 intermediate; the residual is
+    added by whichever kernel runs the product."""
+    from izwi_b200 import ops
+    n, k = 768, 1024
+    rng = np.random.default_rng(900 + m)
+    if fmt == "q6_k":
+        raw = o.make_q6_k_blocks(rng, n * k // 256)
+        wf = o.dequantize(raw, "q6_k").reshape(n, k)
+        wd = torch.from_numpy(raw).to(cuda)
+    else:
+        raw, wf = make_weight_np(fmt, n, k, rng)
+        wd = upload_weight(fmt, raw, cuda)
+    x = bf16_np(rng.normal(0, 2.0, (m, k)))
+    g = bf16_np(rng.normal(1.0, 0.3, k))
+    res = bf16_np(rng.normal(0, 1.0, (m, n)))
+    normed, _ = o.rms_norm(x, g, EPS)
+    got = ops.linear(dev_bf16(x, cuda), wd, fmt, n=n, k=k, prologue="rms_norm", norm_weight=dev_bf16(g, cuda), norm_eps=EPS,
+                     residual=dev_bf16(res, cuda))
+    ops.Context.get(0).check()
+    assert_matmul_close(got, o.linear(normed, wf) + res, f"rms_norm + {fmt} + residual M={m}")
+    gu = bf16_np(rng.normal(0, 2.0, (m, 2 * k)))
+    act = bf16_np(o.silu_mul(gu[:, :k], gu[:, k:]))
+    got = ops.linear(dev_bf16(gu, cuda), wd, fmt, n=n, k=k, prologue="silu_mul", residual=dev_bf16(res, cuda))
+    ops.Context.get(0).check()
+    assert_matmul_close(got, o.linear(act, wf) + res, f"silu_mul + {fmt} + residual M={m}")
+    # residual alone, fp32 output
+    got = ops.linear(dev_bf16(x, cuda), wd, fmt, n=n, k=k, residual=dev_bf16(res, cuda), out_dtype=torch.float32)
+    ops.Context.get(0).check()
+    assert_matmul_close(got, o.linear(x, wf) + res, f"{fmt} + residual M={m} fp32 out")
+
+
+def test_residual_behind_a_fused_epilogue_and_ragged_width(cuda):
+    """GEMM route: residual after SwiGLU (half as many columns) and on a width that is not a multiple of 8."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(950)
+    m, n, k = 150, 520, 512
+    raw, wf = make_weight_np("bf16", n, k, rng)
+    x = bf16_np(rng.normal(0, 1.0, (m, k)))
+    pre = o.linear(x, wf)
+    res = bf16_np(rng.normal(0, 1.0, (m, n // 2)))
+    got = ops.linear(dev_bf16(x, cuda), upload_weight("bf16", raw, cuda), epilogue="swiglu", residual=dev_bf16(res, cuda))
+    assert_matmul_close(got, o.silu_mul(pre[:, : n // 2], pre[:, n // 2:]) + res, "swiglu + residual")
+    n2 = 515
+    raw2, wf2 = make_weight_np("bf16", n2, k, rng)
+    res2 = bf16_np(rng.normal(0, 1.0, (m, n2)))
+    got = ops.linear(dev_bf16(x, cuda), upload_weight("bf16", raw2, cuda), residual=dev_bf16(res2, cuda))
+    ops.Context.get(0).check()
+    assert_matmul_close(got, o.linear(x, wf2) + res2, "ragged width + residual")
 
 
 @pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
