@@ -96,13 +96,16 @@ typedef enum izb_epilogue {
     IZB_EPI_SILU = 2,   /* x*sigmoid(x): FastConformer feed-forward (parakeet/asr/mod.rs:766-772) */
     IZB_EPI_SWIGLU = 3, /* W = [gate; up] rows: y[:, j] = silu(gate_j) * up_j, y has N/2 columns:
                            `Qwen3Mlp::forward` gate/up + silu-mul in one pass (qwen3/core.rs:1787-1795) */
-    IZB_EPI_GELU_TANH = 4 /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))): the reference's `Tensor::gelu()` call
+    IZB_EPI_GELU_TANH = 4, /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))): the reference's `Tensor::gelu()` call
                            sites, Whisper `mlp_linear1` + GELU (whisper/model.rs:311-317) and the Qwen3-ASR audio
                            tower (qwen3/asr/audio.rs:385,667-668).  Evidence that `gelu()` is this form and not
                            the erf one: the reference keeps the two apart (it calls `gelu_erf()` where it wants
                            the exact form), and every GELU it writes out itself under that name is this formula
                            (audio/codec.rs:135-137, voxtral/realtime/audio.rs:73-88, lfm25_audio/conformer.rs:
                            1266-1280).  Candle's source is not part of the reference tree, so this is inferred. */
+    IZB_EPI_GLU = 5     /* W = [a; b] rows: y[:, j] = a_j * sigmoid(b_j), y has N/2 columns: the gated linear unit
+                           behind `pointwise_conv1` of the Conformer convolution module
+                           (parakeet/asr/mod.rs:831-834) */
 } izb_epilogue;
 
 /* Function of the activations in front of a linear layer.  Inside the one- and two-token kernel both
@@ -390,6 +393,20 @@ int32_t izb_rms_norm(izb_ctx* ctx, izb_stream stream, const void* x, const void*
 int32_t izb_argmax_rows(izb_ctx* ctx, izb_stream stream, const void* x, int32_t x_dtype, int64_t rows,
                         int64_t cols, int64_t ld_x, int32_t* out_idx, float* out_val);
 
+/* Token choice beyond the arg-max, on the device, one draw per row of a bf16 / fp32 logits matrix, by the
+ * rules of the reference's host-side samplers (`sample_from_logits`, models/architectures/lfm25_audio/
+ * sampling.rs:65-160; `sample_semantic`, models/architectures/qwen3/tts/mod.rs:2293-2440):
+ * temperature <= 1e-5 gives the arg-max; otherwise v = logit / temperature over the finite logits, the
+ * top_k largest are kept (0: all; equal values keep the lowest indices), p = softmax(v) over those, the
+ * smallest prefix in descending order of p whose mass reaches max(top_p, 1e-6) is kept (top_p >= 1: all),
+ * and the candidates are walked (in descending order when top_k or top_p cut anything, in index order
+ * otherwise) up to the first whose cumulative mass reaches uniform[row], a number in [0, 1) the caller
+ * draws (device array, one per row; may be NULL for temperature <= 1e-5).  Masses are summed in 64-bit
+ * fixed point, so the result is a pure function of its inputs.  out_idx [rows] int32 on the device. */
+int32_t izb_sample_rows(izb_ctx* ctx, izb_stream stream, const void* logits, int32_t dtype, int64_t rows,
+                        int64_t cols, int64_t ld, float temperature, int32_t top_k, float top_p,
+                        const float* uniform, int32_t* out_idx);
+
 /* Rotary position embedding of q [tokens, q_heads, head_dim] and k [tokens, k_heads, head_dim]
  * (bf16, in place, token rows ld_q / ld_k elements apart) with bf16 tables cos_half, sin_half
  * [tokens, head_dim / 2]: first half = x1 cos - x2 sin, second half = x1 sin + x2 cos, fp32
@@ -434,6 +451,64 @@ int32_t izb_decode_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q,
                                  int64_t kv_capacity, int64_t ld_q, int64_t ld_out, float scale,
                                  void* workspace, size_t workspace_bytes);
 
+/* ---- paged KV cache (models/shared/attention/paged.rs) ------------------------------------------
+ * A sequence's keys and values live in fixed-size pages of [page_size tokens, kv_heads, head_dim]
+ * drawn from a pool the caller owns; page_table [batch, max_pages_per_seq] int32 (device) names the
+ * pool pages of every sequence in order.  Storage follows the reference's KvPage (paged.rs:64-156):
+ *   IZB_KV_NONE  bf16 values;
+ *   IZB_KV_INT8  one byte per value, u8 = round(clamp(x / scale, -127, 127)) + 128, ONE fp32 scale per
+ *                page, scale = max(max|x| / 127, 1e-8) or 1 for an all-zero page, with the reference's
+ *                arithmetic in the cache dtype (every product rounded to bf16; quantize_tensor_int8 /
+ *                dequantize_tensor_int8, paged.rs:158-199);
+ *   IZB_KV_Q4_0  blocks of 32 consecutive values: fp32 scale = max|x| / 7 (1 if all zero), 4-bit codes
+ *                clamp(round(x / scale), -7, 7) + 8, two per byte, low nibble first (quantize_tensor_q4_0
+ *                / dequantize_tensor_q4_0, paged.rs:200-343).
+ * values: pool_pages * izb_kv_page_bytes() bytes; scales: pool_pages * izb_kv_page_scales() floats
+ * (NULL for IZB_KV_NONE).  The reference keeps one batch inside a page and so one Int8 scale for all
+ * of its sequences; here every sequence has pages (and scales) of its own, which is the same for
+ * batch 1, the case its decode path runs. */
+typedef enum izb_kv_quantization { IZB_KV_NONE = 0, IZB_KV_INT8 = 1, IZB_KV_Q4_0 = 2 } izb_kv_quantization;
+typedef struct izb_kv_pages {
+    void* k_values;
+    void* v_values;
+    float* k_scales;
+    float* v_scales;
+    const int32_t* page_table;
+    int32_t quantization; /* izb_kv_quantization */
+    int32_t page_size;    /* tokens per page (the reference's DEFAULT_KV_PAGE_SIZE is 64) */
+    int32_t kv_heads;
+    int32_t head_dim;     /* 64 or 128 */
+    int64_t max_pages_per_seq;
+} izb_kv_pages;
+size_t izb_kv_page_bytes(int32_t quantization, int32_t page_size, int32_t kv_heads, int32_t head_dim);
+size_t izb_kv_page_scales(int32_t quantization, int32_t page_size, int32_t kv_heads, int32_t head_dim);
+/* Appends n_new tokens to every sequence: k / v bf16, token i of sequence b at row b * n_new + i (rows
+ * ld_k / ld_v apart, kv_heads * head_dim values each); seq_lens [batch] int32 on the device holds the
+ * tokens already cached (the caller adds n_new afterwards).  A partly filled last page is rebuilt
+ * from its dequantised contents plus the new rows and quantised anew, one page per call and page, as
+ * `append_to_pages` does (paged.rs:345-388).  A sequence that outgrows max_pages_per_seq makes the
+ * next izb_ctx_check return IZB_ERR_BAD_ARG. */
+int32_t izb_kv_pages_append(izb_ctx* ctx, izb_stream stream, const izb_kv_pages* pages, const void* k,
+                            const void* v, int64_t batch, int64_t n_new, int64_t ld_k, int64_t ld_v,
+                            const int32_t* seq_lens);
+/* The cached keys (which = 0) or values (1) of every sequence as dense bf16: out[b, t, :] for
+ * t < seq_lens[b], rows ld_token apart, sequences ld_batch apart (`materialize_pages`, paged.rs:390-405). */
+int32_t izb_kv_pages_materialize(izb_ctx* ctx, izb_stream stream, const izb_kv_pages* pages, int32_t which,
+                                 int64_t batch, const int32_t* seq_lens, void* out, int64_t ld_token,
+                                 int64_t ld_batch);
+/* One query token per sequence over its pages: out = softmax(q k^T * scale) v per head with a running
+ * maximum and sum over the pages, which are dequantised in registers and never materialised
+ * (`paged_decode_attention`, paged.rs:486-628).  q / out [batch, heads, head_dim] bf16 (rows ld_q /
+ * ld_out apart); seq_lens [batch] int32 on the device counts the cached tokens, the new one included;
+ * max_seq_len bounds them (it sizes the split over CTAs and the workspace).  heads / kv_heads <= 8. */
+size_t izb_paged_decode_gqa_attention_workspace_bytes(const izb_ctx* ctx, int64_t batch, int32_t heads,
+                                                      int32_t kv_heads, int32_t head_dim,
+                                                      int64_t max_seq_len);
+int32_t izb_paged_decode_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q,
+                                       const izb_kv_pages* pages, const int32_t* seq_lens, void* out,
+                                       int64_t batch, int32_t heads, int64_t max_seq_len, int64_t ld_q,
+                                       int64_t ld_out, float scale, void* workspace, size_t workspace_bytes);
+
 /* ---- what a prompt needs before the first decode step -----------------------------------------
  * out[t, :] = table[ids[t], :]: the embedding lookup in front of the first layer (`embed_tokens`,
  * models/architectures/qwen3/core.rs:2099-2103).  table bf16 [vocab, hidden], ids int32 on the device
@@ -461,6 +536,31 @@ int32_t izb_prefill_gqa_attention(izb_ctx* ctx, izb_stream stream, const void* q
                                   const void* v_cache, void* out, int64_t batch, int64_t q_len,
                                   int32_t heads, int32_t kv_heads, int32_t head_dim, int64_t pos0,
                                   int64_t kv_capacity, int64_t ld_q, int64_t ld_out, float scale);
+
+/* ---- Conformer convolution module (parakeet/asr/mod.rs:775-864) ---------------------------------
+ * Its two pointwise (1x1) convolutions are linear layers over [batch * frames, channels] rows:
+ * izb_linear, the first with IZB_EPI_GLU.  Between them:
+ * Load time: folds an inference-mode batch norm into the depthwise convolution before it
+ * (`fold_depthwise_conv1d_batch_norm`, parakeet/asr/mod.rs:866-893): folded_weight[c, j] = conv_weight[c, j]
+ * * scale[c], folded_bias[c] = bn_bias[c] - scale[c] * running_mean[c], scale = bn_weight / sqrt(running_var
+ * + eps) (bn_weight / bn_bias NULL together: 1 and 0).  fp32 device inputs, conv_weight [channels, kernel];
+ * bf16 outputs. */
+int32_t izb_fold_depthwise_conv1d_batch_norm(izb_ctx* ctx, izb_stream stream, const float* conv_weight,
+                                             const float* bn_weight, const float* bn_bias,
+                                             const float* running_mean, const float* running_var, float eps,
+                                             int64_t channels, int32_t kernel, void* folded_weight,
+                                             void* folded_bias);
+/* out[b, t, c] = swish(bias[c] + sum_j weight[c, j] * x[b, t + j - padding, c]) with zeros beyond each
+ * utterance's ends (apply_swish = 0: without the swish).  x / out bf16 [batch * frames, channels] with
+ * channels contiguous and rows ld_x / ld_out apart, weight bf16 [channels, kernel], bias bf16 [channels]
+ * or NULL.  Odd kernel <= 31 with padding = (kernel - 1) / 2, stride and dilation 1, channels % 8 == 0.
+ * Replaces try_depthwise_conv1d_bias_swish (Metal only in the reference) and the depthwise conv + batch
+ * norm + swish sequence of ConformerConv::forward (parakeet/asr/mod.rs:836-858); the transposes to and
+ * from [batch, channels, frames] (:829, :862) are not needed in this layout. */
+int32_t izb_depthwise_conv1d_bias_swish(izb_ctx* ctx, izb_stream stream, const void* x, const void* weight,
+                                        const void* bias, void* out, int64_t batch, int64_t frames,
+                                        int64_t channels, int32_t kernel, int32_t padding, int64_t ld_x,
+                                        int64_t ld_out, int32_t apply_swish);
 
 /* ---- GGUF files -------------------------------------------------------------------------------
  * Read-only view of a GGUF v2 / v3 file (header, metadata, tensor directory; the file is mapped,

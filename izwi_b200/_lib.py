@@ -20,7 +20,7 @@ IZB_ERR_SCRATCH_TOO_SMALL = -6
 
 IZB_BF16, IZB_F32 = 0, 1
 IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K, IZB_W_Q6_K = 0, 1, 2, 3
-IZB_EPI_NONE, IZB_EPI_GELU, IZB_EPI_SILU, IZB_EPI_SWIGLU, IZB_EPI_GELU_TANH = 0, 1, 2, 3, 4
+IZB_EPI_NONE, IZB_EPI_GELU, IZB_EPI_SILU, IZB_EPI_SWIGLU, IZB_EPI_GELU_TANH, IZB_EPI_GLU = 0, 1, 2, 3, 4, 5
 
 
 class LinearArgs(C.Structure):
@@ -34,6 +34,13 @@ class LinearArgs(C.Structure):
         ("norm_weight", C.c_void_p), ("residual", C.c_void_p), ("ld_residual", C.c_int64),
         ("norm_eps", C.c_float), ("reserved_", C.c_int32),
     ]
+
+
+class KvPages(C.Structure):
+    """Mirror of izb_kv_pages."""
+    _fields_ = [("k_values", C.c_void_p), ("v_values", C.c_void_p), ("k_scales", C.c_void_p), ("v_scales", C.c_void_p),
+                ("page_table", C.c_void_p), ("quantization", C.c_int32), ("page_size", C.c_int32), ("kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("max_pages_per_seq", C.c_int64)]
 
 
 class MoeArgs(C.Structure):
@@ -120,6 +127,8 @@ _SIGNATURES = {
                                  C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float]),
     "izb_argmax_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                     C.c_void_p, C.c_void_p]),
+    "izb_sample_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_float,
+                                    C.c_int32, C.c_float, C.c_void_p, C.c_void_p]),
     "izb_rope_pair": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                   C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
     "izb_kv_append": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
@@ -132,6 +141,17 @@ _SIGNATURES = {
     "izb_decode_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                              C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                              C.c_int64, C.c_float, C.c_void_p, C.c_size_t]),
+    "izb_kv_page_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "izb_kv_page_scales": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "izb_kv_pages_append": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(KvPages), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                        C.c_int64, C.c_int64, C.c_void_p]),
+    "izb_kv_pages_materialize": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(KvPages), C.c_int32, C.c_int64, C.c_void_p,
+                                             C.c_void_p, C.c_int64, C.c_int64]),
+    "izb_paged_decode_gqa_attention_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                                                   C.c_int64]),
+    "izb_paged_decode_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(KvPages), C.c_void_p, C.c_void_p,
+                                                   C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_float, C.c_void_p,
+                                                   C.c_size_t]),
     "izb_embed_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
                                    C.c_int64]),
     "izb_qk_norm_rope_append_seq": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_float,
@@ -140,6 +160,11 @@ _SIGNATURES = {
     "izb_prefill_gqa_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                               C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                               C.c_int64, C.c_float]),
+    "izb_fold_depthwise_conv1d_batch_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                         C.c_void_p, C.c_float, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "izb_depthwise_conv1d_bias_swish": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                    C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
+                                                    C.c_int32]),
     "izb_gguf_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "izb_gguf_close": (C.c_int32, [C.c_void_p]),
     "izb_gguf_version": (C.c_int32, [C.c_void_p]),

@@ -383,7 +383,7 @@ size_t izb_linear_workspace_bytes_args(const izb_linear_args* a) {
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args) {
     if (!ctx || !args) return IZB_ERR_BAD_ARG;
     if (args->M < 0 || args->N < 0 || args->K < 0) return IZB_ERR_BAD_ARG;
-    if (args->epilogue < IZB_EPI_NONE || args->epilogue > IZB_EPI_GELU_TANH) return IZB_ERR_BAD_ARG;
+    if (args->epilogue < IZB_EPI_NONE || args->epilogue > IZB_EPI_GLU) return IZB_ERR_BAD_ARG;
     if (args->prologue < IZB_PRO_NONE || args->prologue > IZB_PRO_SILU_MUL) return IZB_ERR_BAD_ARG;
     if (args->M == 0 || args->N == 0) return IZB_OK;
     if (args->K == 0) return IZB_ERR_UNSUPPORTED;
@@ -437,7 +437,7 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
     if (!quant && args->wfmt != IZB_W_BF16) return IZB_ERR_BAD_ARG;
     // a row must be a whole number of blocks, or the bytes of one row would run into the next
     if (quant && args->K % (args->wfmt == IZB_W_Q8_0 ? 32 : 256) != 0) return IZB_ERR_BAD_ARG;
-    if (args->residual && (args->ld_residual < (args->epilogue == IZB_EPI_SWIGLU ? args->N / 2 : args->N) || !izb_aligned(args->residual, 2)))
+    if (args->residual && (args->ld_residual < ((args->epilogue == IZB_EPI_SWIGLU || args->epilogue == IZB_EPI_GLU) ? args->N / 2 : args->N) || !izb_aligned(args->residual, 2)))
         return IZB_ERR_BAD_ARG;
 
     const void* w_dense = args->w;

@@ -77,6 +77,12 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * x * x, x, x)));
     return fmaf(0.5f * x, t, 0.5f * x);
 }
+// sigmoid(x) = 0.5 (1 + tanh(x / 2)) on the same instruction
+__device__ __forceinline__ float sigmoid_fast(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+    return fmaf(0.5f, t, 0.5f);
+}
 __device__ __forceinline__ float silu(float x) {
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
@@ -90,7 +96,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bn = p.bn;
-    const bool swiglu = p.epilogue == GEMM_EPI_SWIGLU;
+    // gated epilogues: the tile's accumulator holds the matching columns of both row halves of W side by side
+    const bool swiglu = p.epilogue == GEMM_EPI_SWIGLU || p.epilogue == GEMM_EPI_GLU;
+    const bool glu = p.epilogue == GEMM_EPI_GLU;
     const int out_cols = swiglu ? bn / 2 : bn;  // output columns one tile produces
     const uint32_t a_bytes = GT_BM * GT_BK * 2, b_bytes = static_cast<uint32_t>(bn) * GT_BK * 2;
     const uint32_t stage_bytes = a_bytes + b_bytes;
@@ -271,8 +279,13 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                             }
                         }
                     }
+                    if (glu) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
+                        for (int i = 0; i < 32; ++i) v[i] = v[i] * sigmoid_fast(u[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
+                    }
                 } else {
                     if (bias) {
 #pragma unroll
@@ -386,10 +399,10 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     if (K % 8 != 0 || ldx % 8 != 0 || ldx < K) return IZB_ERR_UNSUPPORTED;
     if (!izb_aligned(x, 16) || !izb_aligned(w, 16)) return IZB_ERR_BAD_ARG;
     if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
-    if (epilogue < GEMM_EPI_NONE || epilogue > GEMM_EPI_GELU_TANH) return IZB_ERR_BAD_ARG;
+    if (epilogue < GEMM_EPI_NONE || epilogue > GEMM_EPI_GLU) return IZB_ERR_BAD_ARG;
     if (seg_offsets && n_experts > GT_MAX_EXPERTS) return IZB_ERR_UNSUPPORTED;
     if (!seg_offsets && n_experts != 1) return IZB_ERR_BAD_ARG;
-    const bool swiglu = epilogue == GEMM_EPI_SWIGLU;
+    const bool swiglu = epilogue == GEMM_EPI_SWIGLU || epilogue == GEMM_EPI_GLU;  // gated: two row halves of W per output column
     if (swiglu && N % 2 != 0) return IZB_ERR_BAD_ARG;
     const int n_out = swiglu ? N / 2 : N;
     if (ldy < n_out) return IZB_ERR_BAD_ARG;

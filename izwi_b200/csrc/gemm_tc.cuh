@@ -24,6 +24,7 @@ enum GemmEpilogue : int {
     GEMM_EPI_SILU = 2,    // x * sigmoid(x), FastConformer feed-forward
     GEMM_EPI_SWIGLU = 3,  // W = [gate ; up] rows: out[:, j] = silu(gate_j) * up_j, N_out = N / 2
     GEMM_EPI_GELU_TANH = 4,  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), Whisper fc1
+    GEMM_EPI_GLU = 5,        // W = [a ; b] rows: out[:, j] = a_j * sigmoid(b_j), N_out = N / 2 (Conformer pointwise_conv1)
 };
 
 struct GemmParams {

@@ -347,7 +347,7 @@ int32_t izb_moe_grouped_gemm(izb_ctx* ctx, izb_stream stream, const void* x_perm
     if (rows == 0) return IZB_OK;
     if (rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     if (!offsets) return IZB_ERR_BAD_ARG;
-    const int64_t n_out = epilogue == IZB_EPI_SWIGLU ? N / 2 : N;
+    const int64_t n_out = (epilogue == IZB_EPI_SWIGLU || epilogue == IZB_EPI_GLU) ? N / 2 : N;
     return gemm_tc_launch(ctx, static_cast<cudaStream_t>(stream), x_perm, K, w, nullptr, y, n_out, y_dtype,
                           static_cast<int>(rows), static_cast<int>(N), static_cast<int>(K), epilogue,
                           static_cast<const int*>(offsets), static_cast<int>(E));

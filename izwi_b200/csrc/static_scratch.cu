@@ -54,7 +54,7 @@ int32_t izb_linear_quantized_static(izb_ctx* ctx, izb_stream stream, int32_t wfm
     if (M == 0 || N == 0) return IZB_OK;
     if (K == 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     if (K % (wfmt == IZB_W_Q8_0 ? 32 : 256) != 0) return IZB_ERR_BAD_ARG;  // a row is a whole number of blocks
-    if (epilogue < IZB_EPI_NONE || epilogue > IZB_EPI_GELU_TANH) return IZB_ERR_BAD_ARG;
+    if (epilogue < IZB_EPI_NONE || epilogue > IZB_EPI_GLU) return IZB_ERR_BAD_ARG;
     if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
     // the bf16 copy of the weights must fit the fixed array
     if (static_cast<unsigned long long>(N) * static_cast<unsigned long long>(K) * 2ull > kStaticScratchBytes)
@@ -66,7 +66,7 @@ int32_t izb_linear_quantized_static(izb_ctx* ctx, izb_stream stream, int32_t wfm
     // every element of the N*K region is rewritten here, so nothing left by an earlier call is read
     rc = izb_dequantize(ctx, stream, wfmt, w, N * K, IZB_BF16, scratch);
     if (rc != IZB_OK) return rc;
-    const int n_out = epilogue == IZB_EPI_SWIGLU ? static_cast<int>(N / 2) : static_cast<int>(N);
+    const int n_out = (epilogue == IZB_EPI_SWIGLU || epilogue == IZB_EPI_GLU) ? static_cast<int>(N / 2) : static_cast<int>(N);
     return izb::gemm_tc_launch(ctx, static_cast<cudaStream_t>(stream), x, K, scratch, bias, y, n_out, y_dtype,
                                static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), epilogue, nullptr, 1);
 }

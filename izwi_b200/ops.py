@@ -67,7 +67,7 @@ def dequantize(raw: torch.Tensor, fmt: str, n_elems: int, dtype: torch.dtype = t
 
 
 EPILOGUE = {None: L.IZB_EPI_NONE, "none": L.IZB_EPI_NONE, "gelu": L.IZB_EPI_GELU, "silu": L.IZB_EPI_SILU,
-            "swiglu": L.IZB_EPI_SWIGLU, "gelu_tanh": L.IZB_EPI_GELU_TANH}
+            "swiglu": L.IZB_EPI_SWIGLU, "gelu_tanh": L.IZB_EPI_GELU_TANH, "glu": L.IZB_EPI_GLU}
 PROLOGUE = {None: 0, "none": 0, "rms_norm": 1, "silu_mul": 2}  # izb_prologue
 
 
@@ -118,7 +118,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = 
     x2 = x.reshape(-1, x.shape[-1])
     if x2.shape[1] != (2 * k if prologue == "silu_mul" else k):
         raise ValueError(f"linear: input dim {x2.shape[1]} != weight in-dim {k}")
-    n_out = n // 2 if epilogue == "swiglu" else n
+    n_out = n // 2 if epilogue in ("swiglu", "glu") else n
     y = out if out is not None else torch.empty(x2.shape[0], n_out, device=x.device, dtype=out_dtype)
     res2 = None if residual is None else residual.reshape(-1, n_out)
     if workspace is True:
@@ -188,6 +188,22 @@ def argmax_rows(x: torch.Tensor, return_values: bool = False):
                                     x2.stride(0), _ptr(idx), None if val is None else _ptr(val)), "izb_argmax_rows")
     idx = idx.reshape(x.shape[:-1])
     return (idx, val.reshape(x.shape[:-1])) if return_values else idx
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, uniform: torch.Tensor | None) -> torch.Tensor:
+    """One token per logits row by temperature / top-k / top-p sampling on the device (`sample_from_logits`,
+    lfm25_audio/sampling.rs:65-160); `uniform` holds one number in [0, 1) per row, drawn by the caller."""
+    assert logits.dtype in (torch.bfloat16, torch.float32)
+    x2 = logits.reshape(-1, logits.shape[-1])
+    assert x2.stride(1) == 1
+    if uniform is not None:
+        assert uniform.dtype == torch.float32 and uniform.is_contiguous() and uniform.numel() == x2.shape[0]
+    idx = torch.empty(x2.shape[0], device=logits.device, dtype=torch.int32)
+    ctx = Context.get(logits.device.index)
+    L.check(L.lib().izb_sample_rows(ctx.handle, _stream(), _ptr(x2), L.IZB_F32 if logits.dtype == torch.float32 else L.IZB_BF16,
+                                    x2.shape[0], x2.shape[1], x2.stride(0), float(temperature), int(top_k), float(top_p),
+                                    _ptr(uniform), _ptr(idx)), "izb_sample_rows")
+    return idx.reshape(logits.shape[:-1])
 
 
 def rope_pair_(q: torch.Tensor, k: torch.Tensor, cos_half: torch.Tensor, sin_half: torch.Tensor) -> None:

@@ -515,3 +515,202 @@ def decode_gqa_attention(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray
             p = np.exp(s - s.max())
             out[bi, hi] = (p / p.sum()) @ v
     return out.astype(np.float32)
+
+
+# ----------------------------------------------------------------------------
+# Conformer convolution module (parakeet/asr/mod.rs:775-893)
+# ----------------------------------------------------------------------------
+
+def glu(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """`x_a.broadcast_mul(&ops::sigmoid(&x_b))` behind pointwise_conv1 (parakeet/asr/mod.rs:832-834)."""
+    a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+    return (a / (1.0 + np.exp(-b))).astype(np.float32)
+
+
+def fold_depthwise_conv1d_batch_norm(conv_weight, bn_weight, bn_bias, running_mean, running_var, eps):
+    """`fold_depthwise_conv1d_batch_norm` (parakeet/asr/mod.rs:866-893): conv_weight [C, k] fp32."""
+    std = np.sqrt(np.asarray(running_var, dtype=np.float32) + np.float32(eps))
+    scale = (np.asarray(bn_weight, dtype=np.float32) / std) if bn_weight is not None else (np.float32(1.0) / std)
+    if bn_bias is not None:
+        folded_bias = np.asarray(bn_bias, dtype=np.float32) - scale * np.asarray(running_mean, dtype=np.float32)
+    else:
+        folded_bias = -(scale * np.asarray(running_mean, dtype=np.float32))
+    return (np.asarray(conv_weight, dtype=np.float32) * scale[:, None]).astype(np.float32), folded_bias.astype(np.float32)
+
+
+def depthwise_conv1d_bias_swish(x: np.ndarray, weight: np.ndarray, bias, swish: bool = True) -> np.ndarray:
+    """Depthwise "same" convolution over time, folded bias, swish (`swish`, parakeet/asr/mod.rs:1215-1217):
+    x [B, T, C], weight [C, k], zero padding (k - 1) / 2 on both ends of every utterance."""
+    x = np.asarray(x, dtype=np.float64)
+    w = np.asarray(weight, dtype=np.float64)
+    b, t, c = x.shape
+    k = w.shape[1]
+    pad = (k - 1) // 2
+    xp = np.zeros((b, t + 2 * pad, c))
+    xp[:, pad:pad + t] = x
+    out = np.zeros((b, t, c))
+    for j in range(k):
+        out += xp[:, j:j + t] * w[None, None, :, j]
+    if bias is not None:
+        out += np.asarray(bias, dtype=np.float64)[None, None, :]
+    if swish:
+        out = out / (1.0 + np.exp(-out))
+    return out.astype(np.float32)
+
+
+# ----------------------------------------------------------------------------
+# token sampling (lfm25_audio/sampling.rs:65-160, qwen3/tts/mod.rs:2293-2440)
+# ----------------------------------------------------------------------------
+
+def sample_from_logits(logits: np.ndarray, temperature: float, top_k: int, top_p: float, u: float):
+    """`sample_from_logits` restated: returns (token, margin) where margin is the distance of `u` from the
+    nearest boundary of the cumulative distribution it was compared with (a draw that close to a boundary
+    may legitimately fall either way under a different summation order).  float64 arithmetic."""
+    logits = np.asarray(logits, dtype=np.float32)
+    finite = np.isfinite(logits)
+    if temperature <= 1e-5 or not finite.any():
+        masked = np.where(finite, logits, -np.inf)
+        return int(np.argmax(masked)), 1.0
+    values = logits.astype(np.float32) * np.float32(1.0 / max(temperature, 1e-5))   # the kernel multiplies by 1 / T
+    cand = np.nonzero(finite)[0]
+    ordered = False
+    if 0 < top_k < len(cand):
+        order = np.argsort(-values[cand].astype(np.float64), kind="stable")
+        cand = cand[order][:top_k]
+        ordered = True
+    v = values[cand].astype(np.float64)
+    probs = np.exp(v - v.max())
+    probs /= probs.sum()
+    if top_p < 1.0:
+        order = np.argsort(-probs, kind="stable")
+        cand, probs = cand[order], probs[order]
+        cum = np.cumsum(probs)
+        keep = int(np.searchsorted(cum, max(top_p, 1e-6), side="left")) + 1
+        keep = max(1, min(keep, len(cand)))
+        cand, probs = cand[:keep], probs[:keep]
+        probs = probs / probs.sum()
+        ordered = True
+    cum = np.cumsum(probs)
+    pos = int(np.searchsorted(cum, u, side="left"))
+    pos = min(pos, len(cand) - 1)
+    edges = np.concatenate([[0.0], cum])
+    margin = float(np.abs(edges - u).min())
+    return int(cand[pos]), margin
+
+
+# ----------------------------------------------------------------------------
+# paged KV cache (models/shared/attention/paged.rs)
+# ----------------------------------------------------------------------------
+
+def _round_half_away(x: np.ndarray) -> np.ndarray:
+    """f32::round: halves away from zero."""
+    return np.sign(x) * np.floor(np.abs(x) + 0.5)
+
+
+def kv_quantize_int8(page: np.ndarray):
+    """`quantize_tensor_int8` (paged.rs:158-184) for a bf16 page: every product is rounded to bf16, as
+    the reference computes in the cache dtype.  Returns (u8 values, f32 scale)."""
+    x = bf16_round(np.asarray(page, dtype=np.float32))
+    max_abs = np.float32(np.abs(x).max()) if x.size else np.float32(0)
+    scale = np.float32(max(np.float32(max_abs / np.float32(127.0)), np.float32(1e-8))) if max_abs > 0 else np.float32(1.0)
+    inv = bf16_round(np.array([np.float32(1.0) / scale], dtype=np.float32))[0]
+    y = bf16_round(x * inv)
+    y = _round_half_away(np.clip(y, -127.0, 127.0))
+    return (y + 128.0).astype(np.uint8), scale
+
+
+def kv_dequantize_int8(values: np.ndarray, scale) -> np.ndarray:
+    """`dequantize_tensor_int8` (paged.rs:186-198): bf16 result."""
+    dense = values.astype(np.float32) - np.float32(128.0)
+    if abs(float(scale) - 1.0) < np.finfo(np.float32).eps:
+        return dense
+    return bf16_round(dense * bf16_round(np.array([scale], dtype=np.float32))[0])
+
+
+def kv_quantize_q4_0(page: np.ndarray):
+    """`quantize_tensor_q4_0` (paged.rs:204-268): flat blocks of 32, scale = max|x| / 7 (1 if zero), codes
+    clamp(round(x / scale), -7, 7) + 8, two per byte (low nibble first).  Returns (packed u8, f32 scales)."""
+    x = bf16_round(np.asarray(page, dtype=np.float32)).reshape(-1)
+    assert x.size % 32 == 0
+    blocks = x.reshape(-1, 32)
+    max_abs = np.abs(blocks).max(axis=1).astype(np.float32)
+    scales = np.where(max_abs > 0, max_abs / np.float32(7.0), np.float32(1.0)).astype(np.float32)
+    inv = (np.float32(1.0) / scales).astype(np.float32)
+    q = np.clip(_round_half_away((blocks * inv[:, None]).astype(np.float32)), -7, 7).astype(np.int32) + 8
+    packed = (q[:, 0::2] & 0x0F) | ((q[:, 1::2] & 0x0F) << 4)
+    return packed.astype(np.uint8).reshape(-1), scales
+
+
+def kv_dequantize_q4_0(packed: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """`dequantize_tensor_q4_0` (paged.rs:270-343), then the cast to the cache dtype (bf16)."""
+    b = packed.reshape(-1, 16)
+    q = np.empty((b.shape[0], 32), dtype=np.float32)
+    q[:, 0::2] = (b & 0x0F).astype(np.float32)
+    q[:, 1::2] = (b >> 4).astype(np.float32)
+    return bf16_round(((q - np.float32(8.0)) * scales[:, None].astype(np.float32)).reshape(-1))
+
+
+class KvPages:
+    """One sequence's pages of K or V: `append_to_pages` (paged.rs:345-388) and `materialize_pages`
+    (:390-405).  Pages hold [page_seq, kv_heads, head_dim] values (batch 1)."""
+
+    def __init__(self, page_size: int, quantization: str):
+        if page_size <= 0:
+            raise ValueError("KV page size must be greater than zero")
+        self.page_size, self.quantization, self.pages = page_size, quantization, []
+
+    def _from_dense(self, t: np.ndarray):
+        t = bf16_round(np.asarray(t, dtype=np.float32))
+        if self.quantization == "none":
+            return ("dense", t)
+        if self.quantization == "int8":
+            v, s = kv_quantize_int8(t)
+            return ("int8", v, s, t.shape)
+        v, s = kv_quantize_q4_0(t)
+        return ("q4_0", v, s, t.shape)
+
+    @staticmethod
+    def _to_dense(page) -> np.ndarray:
+        if page[0] == "dense":
+            return page[1]
+        if page[0] == "int8":
+            return kv_dequantize_int8(page[1], page[2]).reshape(page[3])
+        return kv_dequantize_q4_0(page[1], page[2]).reshape(page[3])
+
+    def append(self, rows: np.ndarray) -> None:
+        """rows [seq, kv_heads, head_dim]: the last page is filled first (and rebuilt), then new pages pushed."""
+        cursor, n = 0, rows.shape[0]
+        while cursor < n:
+            if self.pages and self._to_dense(self.pages[-1]).shape[0] < self.page_size:
+                last = self._to_dense(self.pages[-1])
+                take = min(self.page_size - last.shape[0], n - cursor)
+                self.pages[-1] = self._from_dense(np.concatenate([last, rows[cursor:cursor + take]], axis=0))
+            else:
+                take = min(self.page_size, n - cursor)
+                self.pages.append(self._from_dense(rows[cursor:cursor + take]))
+            cursor += take
+
+    def materialize(self) -> np.ndarray:
+        return np.concatenate([self._to_dense(p) for p in self.pages], axis=0)
+
+
+def paged_decode_attention(q: np.ndarray, k_pages: KvPages, v_pages: KvPages, scale: float) -> np.ndarray:
+    """`paged_decode_attention` (paged.rs:486-628) for one sequence: q [heads, d]; a running maximum, sum
+    and output over the pages, query head h reading KV head h // (heads // kv_heads).  float64."""
+    h, d = q.shape
+    run_max = np.full(h, -np.inf)
+    run_sum = np.zeros(h)
+    run_out = np.zeros((h, d))
+    for kp, vp in zip(k_pages.pages, v_pages.pages):
+        k, v = KvPages._to_dense(kp).astype(np.float64), KvPages._to_dense(vp).astype(np.float64)
+        rep = h // k.shape[1]
+        for head in range(h):
+            s = (k[:, head // rep] @ q[head].astype(np.float64)) * scale
+            m = s.max()
+            e = np.exp(s - m)
+            new_max = max(run_max[head], m)
+            cs, ps = np.exp(run_max[head] - new_max), np.exp(m - new_max)
+            run_sum[head] = run_sum[head] * cs + e.sum() * ps
+            run_out[head] = run_out[head] * cs + (e @ v[:, head // rep]) * ps
+            run_max[head] = new_max
+    return (run_out / run_sum[:, None]).astype(np.float32)
