@@ -601,6 +601,23 @@ def moe_parity(x, y, idx, wts, logits_fn, w_router, router_bias, w_gate_up, w_do
                       routing_indices_bit_exact=exact)
 
 
+def measure_moe_profile_case(device, experts: int, tokens: int, iters: int):
+    """A reduced MoE layer (Qwen3-30B-A3B expert shape, fewer experts and tokens) for profiler captures of
+    the grouped expert GEMM: a few hundred MB of weights, a handful of launches."""
+    import torch
+    from izwi_b200 import moe, ops
+    gen = torch.Generator(device=device).manual_seed(4)
+    h, i, k = 2048, 768, 8
+    rn = lambda *s, std=1.0: (torch.randn(*s, device=device, generator=gen) * std).to(torch.bfloat16)  # noqa: E731
+    layer = moe.MoeLayer(rn(experts, h, std=h ** -0.5), rn(experts, std=0.5), rn(experts, 2 * i, h, std=0.02),
+                         rn(experts, h, i, std=0.02), k)
+    x = rn(tokens, h)
+    ms = _time_call(lambda: layer.forward(x), iters, warmup=2)
+    ops.Context.get(device.index).check()
+    return {"workload": f"moe-layer-E{experts}-T{tokens}", "ms": round(ms, 4), "pairs": tokens * k,
+            "weight_mb": round(experts * 3 * i * h * 2 / 1e6, 1)}
+
+
 def measure_moe_cases(device):
     """One Qwen3-30B-A3B-shaped MoE layer (H 2048, I 768, 128 experts, top-8, router bias ~N(0, 0.5))
     through izb_moe_forward at T = 1, 64, 4096; rotating over 3 layers' weights (3.6 GB) so the
@@ -1131,6 +1148,8 @@ def main():
                     help="only the whole-greedy-token cases (eager steps, then a CUDA graph replayed)")
     ap.add_argument("--gemm-case", default=None,
                     help="profiler captures: run only this prefill / encoder GEMM shape (a name from gemm_cases) and exit")
+    ap.add_argument("--moe-case", default=None,
+                    help="profiler captures: run only a reduced MoE layer, given as EXPERTS,TOKENS (e.g. 16,512), and exit")
     ap.add_argument("--layers", type=int, default=None,
                     help="shorter stack for profiler captures (the reported line is then not the benchmark)")
     args = ap.parse_args()
@@ -1143,6 +1162,11 @@ def main():
     if args.decode_token_cases:
         import torch
         print(json.dumps({"decode_token_cases": measure_decode_token_cases(torch.device("cuda", 0))}), flush=True)
+        return
+    if args.moe_case:
+        import torch
+        e, t = (int(v) for v in args.moe_case.split(","))
+        print(json.dumps({"moe_case": measure_moe_profile_case(torch.device("cuda", 0), e, t, max(1, min(args.steps, 5)))}), flush=True)
         return
     if args.gemm_case:
         import torch
