@@ -39,7 +39,7 @@ typedef enum izb_status {
     IZB_ERR_SCRATCH_TOO_SMALL = -6 /* the problem needs more than the library's fixed scratch array */
 } izb_status;
 
-typedef enum izb_dtype { IZB_BF16 = 0, IZB_F32 = 1 } izb_dtype;
+typedef enum izb_dtype { IZB_BF16 = 0, IZB_F32 = 1, IZB_F16 = 2 } izb_dtype;
 
 /* Weight storage formats: dense bf16 (Candle `Linear` weight) or raw GGML
  * blocks exactly as they sit in a GGUF file (Candle `QTensor` data).
@@ -124,8 +124,8 @@ typedef enum izb_prologue {
  * (activations stay bf16, accumulation is fp32). */
 typedef struct izb_linear_args {
     int32_t wfmt;      /* izb_wfmt */
-    int32_t y_dtype;   /* izb_dtype of y */
-    const void* x;     /* [M, ldx] bf16 */
+    int32_t y_dtype;   /* izb_dtype of y: bf16, fp32 or fp16 */
+    const void* x;     /* [M, ldx] in x_dtype (bf16 unless set otherwise below) */
     const void* w;     /* [N, K] in wfmt, rows contiguous */
     const void* bias;  /* [N] bf16 or NULL */
     void* y;           /* [M, ldy] */
@@ -147,7 +147,12 @@ typedef struct izb_linear_args {
     const void* residual;    /* bf16 [M, ld_residual] added to the output after the bias; NULL = none */
     int64_t ld_residual;
     float norm_eps;
-    int32_t reserved_;
+    /* izb_dtype of x.  IZB_BF16 (0, so a zeroed struct keeps its meaning) feeds the kernels directly.
+     * IZB_F32 / IZB_F16 activations, the dtypes the reference's CUDA policy gives the QMatMul and Whisper
+     * / Parakeet call sites (qwen3/core.rs:772-789, backends/device.rs:466-484), are rounded to bf16 once
+     * by a cast launch into the tail of `workspace` (size it with izb_linear_workspace_bytes_args); not
+     * together with `prologue`.  The arithmetic is bf16 x bf16 -> fp32 whatever the input type. */
+    int32_t x_dtype;
 } izb_linear_args;
 
 /* M <= 32 (or <= 64 for the block formats) runs a weight-streaming kernel; larger M runs the

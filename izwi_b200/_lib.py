@@ -18,7 +18,7 @@ IZB_ERR_TIMEOUT = -4
 IZB_ERR_NO_DEVICE = -5
 IZB_ERR_SCRATCH_TOO_SMALL = -6
 
-IZB_BF16, IZB_F32 = 0, 1
+IZB_BF16, IZB_F32, IZB_F16 = 0, 1, 2
 IZB_W_BF16, IZB_W_Q8_0, IZB_W_Q4_K, IZB_W_Q6_K = 0, 1, 2, 3
 IZB_EPI_NONE, IZB_EPI_GELU, IZB_EPI_SILU, IZB_EPI_SWIGLU, IZB_EPI_GELU_TANH, IZB_EPI_GLU = 0, 1, 2, 3, 4, 5
 
@@ -32,7 +32,7 @@ class LinearArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("epilogue", C.c_int32), ("prologue", C.c_int32),
         ("norm_weight", C.c_void_p), ("residual", C.c_void_p), ("ld_residual", C.c_int64),
-        ("norm_eps", C.c_float), ("reserved_", C.c_int32),
+        ("norm_eps", C.c_float), ("x_dtype", C.c_int32),
     ]
 
 

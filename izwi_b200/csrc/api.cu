@@ -144,6 +144,23 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate, const __
     }
 }
 
+// fp32 / fp16 activation rows -> dense bf16 rows (round to nearest even), the one rounding the
+// bf16 x bf16 -> fp32 product applies to its left operand whatever type the caller holds it in.
+template <typename T>
+__global__ void cast_rows_bf16_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out, long long rows, long long cols,
+                                      long long ldx) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = rows * cols, stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long r = i / cols, c = i % cols;
+        float v;
+        if constexpr (sizeof(T) == 4) v = x[r * ldx + c];
+        else v = __half2float(x[r * ldx + c]);
+        out[i] = __float2bfloat16_rn(v);
+    }
+}
+
 static int grid_for(const izb_ctx* ctx, long long work_items, int threads) {
     const long long want = (work_items + threads - 1) / threads;
     const long long cap = static_cast<long long>(ctx->sm_count) * 16;
@@ -371,12 +388,22 @@ static bool fuses_in_kernel(const izb_linear_args* a) {
            a->epilogue == IZB_EPI_NONE && stream_width_ok(a->wfmt, a->K);
 }
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+// Bytes at the front of the workspace that the product itself uses: the bf16 copy of block-quantised
+// weights on the routes that multiply one, or (3..16 tokens on the streaming route) the activations
+// re-expressed for the integer tensor-core kernel.  The two never coincide.
+static size_t product_workspace_bytes(const izb_linear_args* a) {
+    const size_t dense = izb_linear_workspace_bytes_ex(a->wfmt, a->M, a->N, a->K, a->epilogue);
+    if (dense) return dense;
+    if (skinny_imma_format_ok(a->wfmt) && a->epilogue == IZB_EPI_NONE && a->M >= skinny_imma_min_tokens() && a->M <= skinny_imma_max_tokens())
+        return skinny_imma_xq_bytes(16, a->K);
+    return 0;
+}
 
 size_t izb_linear_workspace_bytes_args(const izb_linear_args* a) {
     if (!a || a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
-    const size_t dense = izb_linear_workspace_bytes_ex(a->wfmt, a->M, a->N, a->K, a->epilogue);
-    const size_t pro = (a->prologue != IZB_PRO_NONE && !fuses_in_kernel(a))
-                           ? align256(static_cast<size_t>(a->M) * static_cast<size_t>(a->K) * 2) : 0;
+    const size_t dense = product_workspace_bytes(a);
+    const bool staged = a->x_dtype != IZB_BF16 || (a->prologue != IZB_PRO_NONE && !fuses_in_kernel(a));
+    const size_t pro = staged ? align256(static_cast<size_t>(a->M) * static_cast<size_t>(a->K) * 2) : 0;
     return pro ? align256(dense) + pro : dense;
 }
 
@@ -389,12 +416,40 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
     if (args->K == 0) return IZB_ERR_UNSUPPORTED;
     if (args->M > INT32_MAX || args->N > INT32_MAX || args->K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (args->x_dtype != IZB_BF16) {
+        // fp32 / fp16 activations: one cast launch writes the bf16 rows to the tail of the workspace
+        if (args->x_dtype != IZB_F32 && args->x_dtype != IZB_F16) return IZB_ERR_BAD_ARG;
+        if (args->prologue != IZB_PRO_NONE) return IZB_ERR_UNSUPPORTED;
+        const size_t xb = args->x_dtype == IZB_F32 ? 4 : 2;
+        const size_t dense = align256(product_workspace_bytes(args));
+        const size_t rows = align256(static_cast<size_t>(args->M) * static_cast<size_t>(args->K) * 2);
+        if (!args->workspace || !izb_aligned(args->workspace, 16) || args->workspace_bytes < dense + rows) return IZB_ERR_BAD_ARG;
+        if (!args->x || !izb_aligned(args->x, xb) || args->ldx < args->K) return IZB_ERR_BAD_ARG;
+        auto* xs = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(args->workspace) + dense);
+        const int grid = grid_for(ctx, static_cast<long long>(args->M) * args->K, 256);
+        if (args->x_dtype == IZB_F32)
+            IZB_CUDA_TRY(launch_chained(ctx, cast_rows_bf16_kernel<float>, dim3(grid), dim3(256), 0, s, static_cast<const float*>(args->x),
+                                        xs, static_cast<long long>(args->M), static_cast<long long>(args->K),
+                                        static_cast<long long>(args->ldx)));
+        else
+            IZB_CUDA_TRY(launch_chained(ctx, cast_rows_bf16_kernel<__half>, dim3(grid), dim3(256), 0, s,
+                                        static_cast<const __half*>(args->x), xs, static_cast<long long>(args->M),
+                                        static_cast<long long>(args->K), static_cast<long long>(args->ldx)));
+        ctx->launches.fetch_add(1, std::memory_order_relaxed);
+        izb_linear_args plain = *args;
+        plain.x = xs;
+        plain.ldx = args->K;
+        plain.x_dtype = IZB_BF16;
+        plain.workspace_bytes = dense;
+        if (dense == 0) plain.workspace = nullptr;
+        return izb_linear(ctx, stream, &plain);
+    }
     if (args->prologue != IZB_PRO_NONE && !fuses_in_kernel(args)) {
         // Routes whose kernel has no prologue stage (bf16 or Q6_K weights, more than two tokens, a fused
         // epilogue): the normalised rows (or the SiLU-multiply) are written once to the tail of the
         // workspace, bf16 as the reference's separate ops store them, and the product reads them there.
         // The residual still rides in the product's epilogue.
-        const size_t dense = align256(izb_linear_workspace_bytes_ex(args->wfmt, args->M, args->N, args->K, args->epilogue));
+        const size_t dense = align256(product_workspace_bytes(args));
         const size_t pro = align256(static_cast<size_t>(args->M) * static_cast<size_t>(args->K) * 2);
         if (!args->workspace || !izb_aligned(args->workspace, 16) || args->workspace_bytes < dense + pro) return IZB_ERR_BAD_ARG;
         if (!args->x) return IZB_ERR_BAD_ARG;
@@ -464,7 +519,7 @@ int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args)
                               args->epilogue, nullptr, 1, args->residual, args->ld_residual);
     }
     // Token rows are processed 64 at a time by the weight-streaming kernel.
-    const size_t ybytes = args->y_dtype == IZB_F32 ? 4 : 2;
+    const size_t ybytes = args->y_dtype == IZB_F32 ? 4 : 2;  // bf16 and fp16 are both two bytes
     for (int64_t m0 = 0; m0 < args->M; m0 += 64) {
         izb_linear_args a = *args;
         a.M = args->M - m0 < 64 ? args->M - m0 : 64;

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     const uint32_t smem0 = smem_u32(dyn_smem);
     const int n_kb = (p.K + GT_BK - 1) / GT_BK;
     volatile int* abort_flag = &sh.abort_flag;
-    const bool f32_out = p.y_dtype == IZB_F32;
+    const bool f32_out = p.y_dtype == IZB_F32, f16_out = p.y_dtype == IZB_F16;
     const uint32_t stage_out = smem0 + static_cast<uint32_t>(n_stages) * stage_bytes;  // output staging after the ring
     // 16-byte global stores need an aligned base and row stride
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (p.ldy * (f32_out ? 4 : 2)) % 16 == 0;
@@ -313,10 +313,15 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                 } else {
                     const int half = ((cc - cc_begin) >> 5) & 1;  // first or second 64 bytes of the 128-byte row
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        sts128(my_row + static_cast<uint32_t>(((half * 4 + q) ^ (lane & 7)) << 4),
-                               pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                               pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t dst = my_row + static_cast<uint32_t>(((half * 4 + q) ^ (lane & 7)) << 4);
+                        if (f16_out)
+                            sts128(dst, pack_f16x2(v[8 * q], v[8 * q + 1]), pack_f16x2(v[8 * q + 2], v[8 * q + 3]),
+                                   pack_f16x2(v[8 * q + 4], v[8 * q + 5]), pack_f16x2(v[8 * q + 6], v[8 * q + 7]));
+                        else
+                            sts128(dst, pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                   pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+                    }
                 }
                 const int rel = cc - cc_begin;
                 const bool row_full = f32_out || ((rel >> 5) & 1) || cc + 32 >= cc_end;
@@ -344,9 +349,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                             } else {
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
-                                    const float lo = bf16_lo_to_f32(w[e]) + (col + 2 * e < p.n_out ? __bfloat162float(rs[2 * e]) : 0.f);
-                                    const float hi = bf16_hi_to_f32(w[e]) + (col + 2 * e + 1 < p.n_out ? __bfloat162float(rs[2 * e + 1]) : 0.f);
-                                    w[e] = pack_bf16x2(lo, hi);
+                                    const float r_lo = col + 2 * e < p.n_out ? __bfloat162float(rs[2 * e]) : 0.f;
+                                    const float r_hi = col + 2 * e + 1 < p.n_out ? __bfloat162float(rs[2 * e + 1]) : 0.f;
+                                    if (f16_out) {
+                                        const __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
+                                        w[e] = pack_f16x2(__low2float(h) + r_lo, __high2float(h) + r_hi);
+                                    } else {
+                                        w[e] = pack_bf16x2(bf16_lo_to_f32(w[e]) + r_lo, bf16_hi_to_f32(w[e]) + r_hi);
+                                    }
                                 }
                             }
                             d = make_uint4(w[0], w[1], w[2], w[3]);
@@ -398,7 +408,7 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     if (M <= 0 || N <= 0 || K <= 0 || n_experts <= 0) return IZB_ERR_BAD_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ldx < K) return IZB_ERR_UNSUPPORTED;
     if (!izb_aligned(x, 16) || !izb_aligned(w, 16)) return IZB_ERR_BAD_ARG;
-    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
+    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32 && y_dtype != IZB_F16) return IZB_ERR_BAD_ARG;
     if (epilogue < GEMM_EPI_NONE || epilogue > GEMM_EPI_GLU) return IZB_ERR_BAD_ARG;
     if (seg_offsets && n_experts > GT_MAX_EXPERTS) return IZB_ERR_UNSUPPORTED;
     if (!seg_offsets && n_experts != 1) return IZB_ERR_BAD_ARG;

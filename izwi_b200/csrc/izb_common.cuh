@@ -266,6 +266,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return r;
 }
 
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// One output element in the caller's type (izb_dtype): fp32, bf16 or fp16, round to nearest even.
+__device__ __forceinline__ void store_typed(void* y, int y_dtype, long long idx, float v) {
+    if (y_dtype == IZB_F32) static_cast<float*>(y)[idx] = v;
+    else if (y_dtype == IZB_F16) static_cast<__half*>(y)[idx] = __float2half_rn(v);
+    else static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+}
+
 __device__ __forceinline__ float bf16_lo_to_f32(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi_to_f32(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
 

@@ -222,14 +222,6 @@ struct SkinnyShared {
     int abort_flag;
 };
 
-__device__ __forceinline__ void store_out(void* y, int y_dtype, long long idx, float v) {
-    if (y_dtype == IZB_F32) {
-        static_cast<float*>(y)[idx] = v;
-    } else {
-        static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
-    }
-}
-
 template <int FMT, int NT, int RT, int KS>
 __global__ void __launch_bounds__(SK_THREADS)
     skinny_kernel(const SkinnyProblem* __restrict__ probs, const __grid_constant__ SkinnyProblem single, int n_probs,
@@ -426,7 +418,7 @@ __global__ void __launch_bounds__(SK_THREADS)
                                 const int n = 2 * t + i;
                                 const int tok = nt * 8 + (FMT == IZB_W_Q8_0 ? perm_pair(n) : perm_quad(n));
                                 if (tok < M)
-                                    store_out(y, y_dtype, static_cast<long long>(tok) * ldy + row,
+                                    store_typed(y, y_dtype, static_cast<long long>(tok) * ldy + row,
                                               acc[rt][nt][half * 2 + i] + b +
                                                   (res ? __bfloat162float(res[static_cast<long long>(tok) * ld_res + row]) : 0.f));
                             }
@@ -533,7 +525,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     if (!ctx || !probs || !hdr || !out || n <= 0) return IZB_ERR_BAD_ARG;
     const int fmt = probs[0].wfmt, y_dtype = probs[0].y_dtype;
     if (fmt != IZB_W_BF16 && fmt != IZB_W_Q8_0 && fmt != IZB_W_Q4_K) return IZB_ERR_BAD_ARG;
-    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
+    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32 && y_dtype != IZB_F16) return IZB_ERR_BAD_ARG;
     const int kalign = fmt == IZB_W_BF16 ? 64 : 256;
 
     int64_t max_m = 0;
@@ -541,6 +533,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
     for (int i = 0; i < n; ++i) {
         const izb_linear_args& a = probs[i];
         if (a.wfmt != fmt || a.y_dtype != y_dtype) return IZB_ERR_BAD_ARG;
+        if (a.x_dtype != IZB_BF16) return IZB_ERR_UNSUPPORTED;  // the plan holds no staging rows: izb_linear casts
         if (!a.x || !a.w || !a.y) return IZB_ERR_BAD_ARG;
         if (a.M <= 0 || a.N <= 0 || a.K <= 0) return IZB_ERR_BAD_ARG;
         if (a.M > 64) return IZB_ERR_UNSUPPORTED;
@@ -557,6 +550,7 @@ int skinny_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, S
         if (a.residual && (a.ld_residual < a.N || a.ld_residual > INT32_MAX || !izb_aligned(a.residual, 2))) return IZB_ERR_BAD_ARG;
         any_extras = any_extras || a.prologue != IZB_PRO_NONE || a.residual != nullptr;
     }
+    if (skinny_imma_takes(probs, n)) return skinny_imma_plan_build(ctx, probs, n, hdr, out);
     const int nt = max_m <= 8 ? 1 : max_m <= 16 ? 2 : max_m <= 32 ? 4 : 8;
     const int mp = nt * 8;
     // wide token groups over block-quantised weights: dequantise once into shared memory, multiply
@@ -802,6 +796,7 @@ int skinny_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& h, 
                   const SkinnyProblem* single) {
     if (h.magic != SK_PLAN_MAGIC) return IZB_ERR_BAD_ARG;
     if (!dev_probs && !single) return IZB_ERR_BAD_ARG;
+    if (h.imma) return skinny_imma_launch(ctx, stream, h, dev_probs, single);
     if (h.tc) return skinny_tc_launch(ctx, stream, h, dev_probs, single);
     if (h.gemv) return skinny_gemv_launch(ctx, stream, h, dev_probs, single);
     static const SkinnyProblem dummy = {};

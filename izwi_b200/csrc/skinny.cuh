@@ -46,7 +46,10 @@ struct alignas(64) SkinnyProblem {
     float eps;
     int up_chunk0;   // SILU_MUL: 64-k chunk index where the `up` half of the activation rows starts
     int x_half;      // SILU_MUL: byte offset of the `up` chunks inside the stage's activation region
-    int pad_[3];
+    // integer tensor-core kernel (skinny_imma.cu): its own copy of the activations, made by a kernel in front
+    int ldx;
+    uint8_t* xq;                    // converted activations in the caller's workspace
+    const __nv_bfloat16* x_rows;    // the bf16 activation rows they are made from (ldx apart)
 };
 static_assert(sizeof(SkinnyProblem) == 384, "SkinnyProblem layout");
 
@@ -63,7 +66,9 @@ struct alignas(64) SkinnyPlanHeader {
     int xq_stage_bytes;  // gemv: bytes of converted activations per stage (red_bytes holds all stages)
     int extras;          // gemv: some problem carries a prologue or a residual
     int ksplit;          // gemv: CTAs per cluster sharing a row tile, each a slice of its k chunks (1: no clusters)
-    int pad_[12];
+    int imma;            // 1 or 2: the integer tensor-core kernel for that many groups of 8 tokens; 0: off
+    int conv_grid;       // imma: blocks per problem of the activation-conversion launch
+    int pad_[10];
 };
 static_assert(sizeof(SkinnyPlanHeader) == 128, "SkinnyPlanHeader layout");
 
@@ -158,6 +163,15 @@ int skinny_tc_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& 
 bool skinny_gemv_clusters_fit(const izb_ctx* ctx, const SkinnyPlanHeader& hdr);  // all of hdr.grid / hdr.ksplit clusters resident at once
 int skinny_gemv_max_tokens();  // widest token group the planner hands to the integer-dot-product kernel
 int skinny_gemv_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
+                       const SkinnyProblem* single);
+// skinny_imma.cu
+bool skinny_imma_takes(const izb_linear_args* probs, int n);  // 3..16 tokens, block-quantised, every problem with room for its converted activations
+size_t skinny_imma_xq_bytes(int64_t M, int64_t K);            // workspace bytes of one problem's converted activations (0: not eligible)
+int skinny_imma_min_tokens();
+int skinny_imma_max_tokens();
+bool skinny_imma_format_ok(int fmt);
+int skinny_imma_plan_build(const izb_ctx* ctx, const izb_linear_args* probs, int n, SkinnyPlanHeader* hdr, SkinnyProblem* out);
+int skinny_imma_launch(izb_ctx* ctx, cudaStream_t stream, const SkinnyPlanHeader& hdr, const SkinnyProblem* dev_probs,
                        const SkinnyProblem* single);
 
 }  // namespace izb

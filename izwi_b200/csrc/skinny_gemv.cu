@@ -589,8 +589,7 @@ __global__ void __launch_bounds__(GV_THREADS)
                         if (EX) v = fmaf(v, inv_k > 0.f ? rsqrtf(fmaf(rsv[m], inv_k, eps)) : 1.0f, addv[m]);
                         else v += bias;
                         const long long idx = static_cast<long long>(m) * L.ldy + grow;
-                        if (y_dtype == IZB_F32) static_cast<float*>(L.y)[idx] = v;
-                        else static_cast<__nv_bfloat16*>(L.y)[idx] = __float2bfloat16_rn(v);
+                        store_typed(L.y, y_dtype, idx, v);
                     }
                 }
             }

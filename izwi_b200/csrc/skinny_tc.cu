@@ -11,6 +11,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <type_traits>
+
 #include "skinny.cuh"
 #include "tcgen05.cuh"
 #include "tma.cuh"
@@ -179,6 +181,7 @@ __device__ __forceinline__ void stc_store_cols(T* y, long long ldy, const float 
     for (int i = 0; i < 16; ++i) {
         if (i < n_tok) {
             if constexpr (sizeof(T) == 4) *y = v[i] + b;
+            else if constexpr (std::is_same<T, __half>::value) *y = __float2half_rn(v[i] + b);
             else *y = __float2bfloat16_rn(v[i] + b);
         }
         y += ldy;
@@ -201,6 +204,7 @@ __device__ __forceinline__ void stc_epilogue(const ProbLite& L, const SkinnyProb
     const float b = L.bias ? __bfloat162float(L.bias[row]) : 0.f;
     const long long first = static_cast<long long>(cc) * L.ldy + row;
     if (y_dtype == IZB_F32) stc_store_cols(static_cast<float*>(L.y) + first, L.ldy, v, b, L.M - cc);
+    else if (y_dtype == IZB_F16) stc_store_cols(static_cast<__half*>(L.y) + first, L.ldy, v, b, L.M - cc);
     else stc_store_cols(static_cast<__nv_bfloat16*>(L.y) + first, L.ldy, v, b, L.M - cc);
 }
 

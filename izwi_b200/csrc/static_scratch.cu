@@ -55,7 +55,7 @@ int32_t izb_linear_quantized_static(izb_ctx* ctx, izb_stream stream, int32_t wfm
     if (K == 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return IZB_ERR_UNSUPPORTED;
     if (K % (wfmt == IZB_W_Q8_0 ? 32 : 256) != 0) return IZB_ERR_BAD_ARG;  // a row is a whole number of blocks
     if (epilogue < IZB_EPI_NONE || epilogue > IZB_EPI_GLU) return IZB_ERR_BAD_ARG;
-    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32) return IZB_ERR_BAD_ARG;
+    if (y_dtype != IZB_BF16 && y_dtype != IZB_F32 && y_dtype != IZB_F16) return IZB_ERR_BAD_ARG;
     // the bf16 copy of the weights must fit the fixed array
     if (static_cast<unsigned long long>(N) * static_cast<unsigned long long>(K) * 2ull > kStaticScratchBytes)
         return IZB_ERR_SCRATCH_TOO_SMALL;

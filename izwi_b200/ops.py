@@ -69,6 +69,7 @@ def dequantize(raw: torch.Tensor, fmt: str, n_elems: int, dtype: torch.dtype = t
 EPILOGUE = {None: L.IZB_EPI_NONE, "none": L.IZB_EPI_NONE, "gelu": L.IZB_EPI_GELU, "silu": L.IZB_EPI_SILU,
             "swiglu": L.IZB_EPI_SWIGLU, "gelu_tanh": L.IZB_EPI_GELU_TANH, "glu": L.IZB_EPI_GLU}
 PROLOGUE = {None: 0, "none": 0, "rms_norm": 1, "silu_mul": 2}  # izb_prologue
+DTYPE = {torch.bfloat16: L.IZB_BF16, torch.float32: L.IZB_F32, torch.float16: L.IZB_F16}  # izb_dtype
 
 
 def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: torch.Tensor,
@@ -76,11 +77,11 @@ def linear_args(x: torch.Tensor, w: torch.Tensor, fmt: str, n: int, k: int, y: t
                 workspace: torch.Tensor | None = None, prologue: str | None = None,
                 norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0,
                 residual: torch.Tensor | None = None) -> L.LinearArgs:
-    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
-    assert y.dim() == 2 and y.stride(1) == 1 and y.shape[0] == x.shape[0]
+    assert x.is_cuda and x.dtype in DTYPE and x.dim() == 2 and x.stride(1) == 1
+    assert y.dim() == 2 and y.stride(1) == 1 and y.shape[0] == x.shape[0] and y.dtype in DTYPE
     a = L.LinearArgs()
     a.wfmt = WFMT[fmt]
-    a.y_dtype = L.IZB_F32 if y.dtype == torch.float32 else L.IZB_BF16
+    a.x_dtype, a.y_dtype = DTYPE[x.dtype], DTYPE[y.dtype]
     a.x, a.w, a.bias, a.y = x.data_ptr(), w.data_ptr(), (0 if bias is None else bias.data_ptr()), y.data_ptr()
     a.M, a.N, a.K = x.shape[0], n, k
     a.ldx, a.ldy = x.stride(0), y.stride(0)
@@ -110,7 +111,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, fmt: str = "bf16", n: int | None = 
     the scratch buffer the library asks for (it never allocates itself).
     `prologue` "rms_norm" (with `norm_weight`, `norm_eps`) or "silu_mul" (x is [.., 2K] = gate | up) is
     computed inside the kernel for at most `linear_fusion_max_tokens(fmt)` token rows and through the
-    workspace otherwise; `residual` is added by the product's epilogue on every route."""
+    workspace otherwise; `residual` is added by the product's epilogue on every route.  fp32 / fp16 `x`
+    is rounded to bf16 by one cast launch into the workspace; `out_dtype` may be bf16, fp32 or fp16."""
     if fmt == "bf16":
         n, k = w.shape
     assert n is not None and k is not None

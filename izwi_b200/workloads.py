@@ -158,8 +158,15 @@ def make_linear_stack(shape: DecoderShape, fmt: str, m: int, device: torch.devic
 def stack_group(stack: LinearStack):
     """All projections of the stack as one grouped persistent launch."""
     from . import ops
-    probs = []
+    import ctypes as C
+    from . import _lib as L
+    probs, scratch = [], []
     for wl, al, ol in zip(stack.weights, stack.acts, stack.outs):
         for (_, n, k), w, x, y in zip(stack.shape.projections, wl, al, ol):
-            probs.append(ops.linear_args(x, w, stack.fmt, n, k, y))
-    return ops.LinearGroup(probs, stack.acts_buf.device, keepalive=stack)
+            a = ops.linear_args(x, w, stack.fmt, n, k, y)
+            need = L.lib().izb_linear_workspace_bytes_args(C.byref(a))
+            if need:  # 3..16 tokens over block formats: room for the activations as the integer kernel reads them
+                scratch.append(torch.empty(need, device=x.device, dtype=torch.uint8))
+                a = ops.linear_args(x, w, stack.fmt, n, k, y, workspace=scratch[-1])
+            probs.append(a)
+    return ops.LinearGroup(probs, stack.acts_buf.device, keepalive=(stack, scratch))

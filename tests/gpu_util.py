@@ -33,6 +33,8 @@ def make_weight_np(fmt: str, n: int, k: int, rng: np.random.Generator):
         return w, w
     if fmt == "q8_0":
         raw = o.make_q8_0_blocks(rng, n * k // 32)
+    elif fmt == "q6_k":
+        raw = o.make_q6_k_blocks(rng, n * k // 256)
     else:
         raw = o.make_q4_k_blocks(rng, n * k // 256, d_scale=1e-4, dmin_scale=7.5e-4)
     return raw, o.dequantize(raw, fmt).reshape(n, k)

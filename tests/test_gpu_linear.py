@@ -49,6 +49,7 @@ def test_every_tile_configuration(cuda, fmt, rt, ks, monkeypatch):
     for every token-group count it is compiled for."""
     monkeypatch.setenv("IZB_SKINNY_RT", str(rt))
     monkeypatch.setenv("IZB_SKINNY_KS", str(ks))
+    monkeypatch.setenv("IZB_SKINNY_IMMA_MAX_M", "0")  # keep 3..16 tokens on the kernel under test
     for m in (2, 12, 20, 40):
         if rt * ((m + 7) // 8 if m <= 16 else (4 if m <= 32 else 8)) > 8:
             continue
@@ -298,3 +299,109 @@ def test_workspace_query_then_call_with_a_fused_epilogue(cuda, fmt, m):
     assert_matmul_close(y, o.silu_mul(pre[:, : n // 2], pre[:, n // 2:]), f"{fmt} M={m} swiglu through a queried workspace")
     a.workspace, a.workspace_bytes = None, 0
     assert lib.izb_linear(ctx.handle, None, C.byref(a)) == L.IZB_ERR_BAD_ARG   # the documented answer without it
+
+
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("y_dtype", [torch.float16, torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("fmt,m", [("bf16", 1), ("bf16", 24), ("bf16", 300), ("q8_0", 2), ("q8_0", 40), ("q8_0", 200),
+                                   ("q4_k", 1), ("q4_k", 12), ("q6_k", 5)])
+def test_f32_and_f16_activations_and_outputs(cuda, fmt, m, x_dtype, y_dtype):
+    """The dtypes the reference's CUDA policy hands these call sites: fp32 / fp16 activations are rounded to
+    bf16 once (the oracle rounds the same way) and the output is stored in the asked-for type, on every route:
+    one- and two-token integer kernel, streaming kernels, dequantise-then-GEMM."""
+    from izwi_b200 import ops
+    n, k = 328, 768
+    rng = np.random.default_rng(m * 7 + len(fmt))
+    raw, wf = make_weight_np(fmt, n, k, rng)
+    x_host = rng.normal(0, 1, (m, k)).astype(np.float16 if x_dtype == torch.float16 else np.float32)
+    b = bf16_np(rng.normal(0, 0.5, n))
+    want = o.linear(bf16_np(x_host.astype(np.float32)), wf, b)
+    xd = torch.from_numpy(x_host).to(cuda)
+    padded = torch.zeros(m, k + 8, device=cuda, dtype=x_dtype)  # a row stride wider than K
+    padded[:, :k] = xd
+    for src in (xd, padded[:, :k]):
+        got = ops.linear(src, upload_weight(fmt, raw, cuda), fmt, n=n, k=k, bias=torch.from_numpy(b).to(cuda).to(torch.bfloat16),
+                         out_dtype=y_dtype)
+        ops.Context.get(0).check()
+        assert got.dtype == y_dtype
+        assert_matmul_close(got, want, f"{fmt} M={m} x={x_dtype} y={y_dtype}")
+
+
+def test_f16_output_with_epilogue_and_residual(cuda):
+    from izwi_b200 import ops
+    rng = np.random.default_rng(5)
+    m, n, k = 150, 512, 640
+    raw, wf = make_weight_np("bf16", n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (m, k)))
+    res = bf16_np(rng.normal(0, 1, (m, n)))
+    want = o.linear(x, wf, None) + res
+    got = ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight("bf16", raw, cuda), "bf16",
+                     residual=torch.from_numpy(res).to(cuda).to(torch.bfloat16), out_dtype=torch.float16)
+    assert_matmul_close(got, want, "f16 out + residual")
+    want = o.gelu_erf(o.linear(x, wf, None))
+    got = ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight("bf16", raw, cuda), "bf16", epilogue="gelu",
+                     out_dtype=torch.float16)
+    assert_matmul_close(got, want, "f16 out + gelu")
+
+
+def test_typed_activations_refuse_a_prologue_and_a_missing_workspace(cuda):
+    from izwi_b200 import _lib as L
+    from izwi_b200 import ops
+    import ctypes as C
+    x = torch.randn(3, 512, device=cuda, dtype=torch.float32)
+    w = torch.randn(64, 512, device=cuda, dtype=torch.bfloat16)
+    y = torch.empty(3, 64, device=cuda, dtype=torch.bfloat16)
+    ctx = ops.Context.get(0)
+    a = ops.linear_args(x, w, "bf16", 64, 512, y)
+    assert L.lib().izb_linear_workspace_bytes_args(C.byref(a)) >= 3 * 512 * 2
+    assert L.lib().izb_linear(ctx.handle, ops._stream(), C.byref(a)) == L.IZB_ERR_BAD_ARG
+    ws = torch.empty(8192, device=cuda, dtype=torch.uint8)
+    nw = torch.ones(512, device=cuda, dtype=torch.bfloat16)
+    a = ops.linear_args(x, w, "bf16", 64, 512, y, workspace=ws, prologue="rms_norm", norm_weight=nw, norm_eps=1e-6)
+    assert L.lib().izb_linear(ctx.handle, ops._stream(), C.byref(a)) == L.IZB_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+@pytest.mark.parametrize("m", [3, 5, 8, 9, 13, 16])
+def test_integer_tensor_core_kernel_every_variant(cuda, fmt, m, monkeypatch):
+    """The int8 mma.sync kernel for 3..16 tokens, both formats and both token-group counts, whatever the
+    defaults currently route to it; residual and bias ride in its epilogue; ragged N and M."""
+    from izwi_b200 import ops
+    monkeypatch.setenv("IZB_SKINNY_IMMA_MAX_M", "16")
+    monkeypatch.setenv("IZB_SKINNY_IMMA_Q4_K", "1")
+    for i, (n, k) in enumerate([(4096, 1024), (1000, 2048), (130, 768), (17, 256), (1024, 3072)]):
+        rng = np.random.default_rng(m * 100 + i)
+        raw, wf = make_weight_np(fmt, n, k, rng)
+        x = bf16_np(rng.normal(0, 1, (m, k)))
+        b = bf16_np(rng.normal(0, 0.5, n))
+        res = bf16_np(rng.normal(0, 1, (m, n)))
+        want = o.linear(x, wf, b) + res
+        before = ops.Context.get(0).launch_count
+        got = ops.linear(torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight(fmt, raw, cuda), fmt, n=n, k=k,
+                         bias=torch.from_numpy(b).to(cuda).to(torch.bfloat16),
+                         residual=torch.from_numpy(res).to(cuda).to(torch.bfloat16), out_dtype=torch.float32)
+        assert ops.Context.get(0).launch_count - before == 2  # activation conversion + product
+        ops.Context.get(0).check()
+        rel, cos = assert_matmul_close(got, want, f"imma {fmt} M={m} N={n} K={k}")
+        assert rel < 5e-3 and cos > 0.999997  # 16-bit fixed-point activations: no visible loss against the bf16 product
+
+
+def test_integer_kernel_needs_its_workspace_and_says_so(cuda):
+    """Without room for the converted activations the call still runs (on the floating-point consumers);
+    the workspace query names the bytes that switch the faster kernel on."""
+    import ctypes as C
+    from izwi_b200 import _lib as L
+    from izwi_b200 import ops
+    rng = np.random.default_rng(3)
+    m, n, k = 4, 512, 1024
+    raw, wf = make_weight_np("q8_0", n, k, rng)
+    x = bf16_np(rng.normal(0, 1, (m, k)))
+    xd, wd = torch.from_numpy(x).to(cuda).to(torch.bfloat16), upload_weight("q8_0", raw, cuda)
+    y = torch.empty(m, n, device=cuda, dtype=torch.bfloat16)
+    a = ops.linear_args(xd, wd, "q8_0", n, k, y)
+    assert L.lib().izb_linear_workspace_bytes_args(C.byref(a)) == k // 32 * 72 * 16
+    ctx = ops.Context.get(0)
+    before = ctx.launch_count
+    got = ops.linear(xd, wd, "q8_0", n=n, k=k, workspace=False)
+    assert ctx.launch_count - before == 1
+    assert_matmul_close(got, o.linear(x, wf, None), "no workspace")
