@@ -176,8 +176,11 @@ size_t izb_linear_workspace_bytes_ex(int32_t wfmt, int64_t M, int64_t N, int64_t
  * row (64 of a bf16 row) at a time; other widths (a Q8_0 row of 384 values, say) run on the GEMM,
  * for which block formats need the workspace (the query above accounts for it; without one the
  * answer is IZB_ERR_UNSUPPORTED). */
-/* The query for a whole call as it will be made (format, shape, epilogue AND prologue): bytes of
- * `workspace` izb_linear needs for exactly these arguments. */
+/* The query for a whole call as it will be made (format, shape, epilogue, prologue AND x_dtype): bytes
+ * of `workspace` izb_linear needs for exactly these arguments.  One case is a wish, not a need: 3..8
+ * tokens over Q8_0 weights on the streaming route run on the int8 tensor-core kernel when the
+ * workspace has room for the activations in its 16-bit block fixed point (K/32 * 72 * 16 bytes, what
+ * this query returns then), and on the floating-point consumers, about 8 % slower, without it. */
 size_t izb_linear_workspace_bytes_args(const izb_linear_args* args);
 int32_t izb_linear(izb_ctx* ctx, izb_stream stream, const izb_linear_args* args);
 /* Largest M for which the kernel itself computes `prologue` for weights in `wfmt` (0: never; the
