@@ -532,8 +532,10 @@ def measure_decode_token_cases(device):
     model = decoder.Qwen3Decoder(embed, layers, ones(hid), wl.make_q8_0_weight(vocab, hid, gen), "q8_0")
     weight_bytes = sum(w.numel() for l in layers for w in (l.w.qkv, l.w.o, l.w.gate_up, l.w.down)) + model.lm_head.numel()
     out = []
-    for ctx_len, fused in ((512, True), (4096, True), (512, False)):
-        # fused: norms, SiLU-multiply and residual adds ride inside the one-token projections
+    for ctx_len, fused in ((512, "one_launch"), (4096, "one_launch"), (512, True), (4096, True), (512, False)):
+        # fused: norms, SiLU-multiply and residual adds ride inside the one-token projections;
+        # "one_launch": the whole token in one cooperative launch (izb_qwen3_decode_token)
+        one_launch = fused == "one_launch"
         for l in layers:
             l.fused_linear = fused
             l.fusion_max_tokens = ops.linear_fusion_max_tokens("q8_0") if fused else 0
@@ -544,17 +546,25 @@ def measure_decode_token_cases(device):
         for c in caches:
             c.k.normal_(generator=cgen)
             c.v.normal_(generator=cgen)
-        tok = torch.tensor([17], device=device)
+        tok = torch.tensor([17], device=device, dtype=torch.int32 if one_launch else torch.int64)
         cos, sin = model.rope_tables(ctx_len, 1)
+        if one_launch:
+            kernel = decoder.Qwen3TokenKernel(model, caches)
+            step = lambda: kernel.step(tok, ctx_len, cos, sin)  # noqa: E731
+        else:
+            step = lambda: model.step(tok, caches, ctx_len, cos, sin)  # noqa: E731
         launches0 = ops.Context.get(device.index).launch_count
         for _ in range(2):
-            nxt = model.step(tok, caches, ctx_len, cos, sin)
+            nxt = step()
         torch.cuda.synchronize()
         launches = (ops.Context.get(device.index).launch_count - launches0) // 2
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            nxt = model.step(tok, caches, ctx_len, cos, sin)
-        ms = _time_call(graph.replay, 30)
+        if one_launch:
+            ms = _time_call(step, 30)  # one launch per token: nothing for a graph to save
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                nxt = step()
+            ms = _time_call(graph.replay, 30)
         ops.Context.get(device.index).check()
         kv_bytes = shape.layers * 2 * shape.kv_heads * (ctx_len + 1) * shape.head_dim * 2
         gbs = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
@@ -562,7 +572,11 @@ def measure_decode_token_cases(device):
                     "tokens_per_s": round(1e3 / ms, 1), "kernels_per_token": int(launches), "fused_projections": fused,
                     "weight_and_kv_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak_bw, 4),
                     "next_token": int(nxt[0])})
-        del caches, graph
+        if one_launch:
+            del kernel
+        else:
+            del graph
+        del caches
         torch.cuda.empty_cache()
     del model, layers, embed
     torch.cuda.empty_cache()

@@ -329,8 +329,9 @@ int32_t izb_ep_alltoall(izb_comm* comm, izb_stream stream, const void* send,
  * Messages above 1 MB (when max_bytes allows them: the sums after a row-split projection at
  * prefill sizes) take a two-shot bandwidth path instead: the operand sits in the rank's region, each
  * rank reduces 1/world of it with peer loads and stores the result chunk into every region, all in
- * ONE kernel that returns when the whole result has landed (16-byte aligned buffer, byte size a
- * multiple of 16, IZB_ERR_UNSUPPORTED otherwise).  izb_ar_allreduce copies the operand into the
+ * ONE kernel that returns when the whole result has landed (16-byte aligned buffer,
+ * IZB_ERR_UNSUPPORTED otherwise; a last 4, 8 or 12 bytes beyond whole 16-byte units go through the
+ * one-shot kernel in a launch of their own).  izb_ar_allreduce copies the operand into the
  * region and the result out of it (three launches).  A caller that can place the operand itself
  * skips both copies: izb_ar_operand(which) is where the row-split projection writes its output
  * (a local device pointer of max_bytes bytes; which = 0 or 1: two buffers, so that the sum of one
@@ -609,6 +610,55 @@ int32_t izb_gguf_meta_str(const izb_gguf* g, const char* key, const char** out, 
 /* Copies the tensor's bytes to device memory on `stream` (needs dst_bytes >= t->bytes). */
 int32_t izb_gguf_upload(const izb_gguf* g, const izb_gguf_tensor* t, void* dev_dst, size_t dst_bytes,
                         izb_stream stream);
+
+/* ---- one decode token of a Qwen3 decoder in one launch -----------------------------------------------
+ * Qwen3Model::forward for seq_len = 1 and one sequence, plus the greedy choice of the chat decode loop
+ * (qwen3/core.rs:2099-2125, 1863-1881, 1624-1732; qwen3/chat.rs:574-601): embedding row, every decoder
+ * layer with its cache append and attention, final norm, lm_head, arg-max.  The reference reaches the
+ * same result through some ten tensor operations per layer; its FFI has no single call for it, so a
+ * binding would put this behind decode_step (chat.rs:348-388) when the model qualifies: the four
+ * projections of every layer in ONE of Q8_0 / Q4_K, lm_head in Q8_0 or Q4_K, head_dim 128, at most four
+ * query heads per KV head, hidden and intermediate multiples of 256 (hidden <= 4096, intermediate and
+ * heads * 128 <= 12288), vocab, hidden and 2 * intermediate multiples of 64; IZB_ERR_UNSUPPORTED
+ * otherwise, and the caller keeps composing the step from izb_linear / izb_qk_norm_rope_append /
+ * izb_decode_gqa_attention.  A cooperative launch of one CTA per SM; every device-side wait is bounded
+ * (izb_ctx_check: IZB_ERR_TIMEOUT; a token id outside the vocabulary: IZB_ERR_BAD_ARG, nothing read). */
+typedef struct izb_qwen3_layer_ptrs {
+    const void* input_norm; /* bf16 [hidden] */
+    const void* post_norm;  /* bf16 [hidden] */
+    const void* q_norm;     /* bf16 [head_dim], or NULL */
+    const void* k_norm;
+    const void* qkv;        /* raw blocks, rows q | k | v: [(heads + 2 kv_heads) * head_dim, hidden] */
+    const void* o;          /* [hidden, heads * head_dim] */
+    const void* gate_up;    /* rows gate | up: [2 * intermediate, hidden] */
+    const void* down;       /* [hidden, intermediate] */
+    void* k_cache;          /* bf16 [kv_heads, kv_capacity, head_dim]; position `pos` is written */
+    void* v_cache;
+} izb_qwen3_layer_ptrs;
+
+typedef struct izb_qwen3_decode_args {
+    int32_t wfmt;         /* izb_wfmt of the layers' projections */
+    int32_t lm_head_fmt;  /* izb_wfmt of lm_head */
+    int32_t n_layers, hidden, heads, kv_heads, head_dim, intermediate, vocab;
+    int32_t pos;          /* position of this token = positions already in the caches */
+    int64_t kv_capacity;
+    float eps;
+    int32_t reserved_;
+    const izb_qwen3_layer_ptrs* layers; /* DEVICE array [n_layers] */
+    const void* embed;      /* bf16 [vocab, hidden] */
+    const void* final_norm; /* bf16 [hidden] */
+    const void* lm_head;    /* raw blocks [vocab, hidden], 16-byte aligned */
+    const int32_t* token;   /* device: the token to embed (the previous call's next_token chains without a host read) */
+    const void* cos_half;   /* bf16 [head_dim / 2]: cos / sin of pos * inv_freq */
+    const void* sin_half;
+    float* logits;          /* device fp32 [vocab], or NULL */
+    int32_t* next_token;    /* device: arg-max of the logits, lowest index on ties */
+    void* workspace;        /* izb_qwen3_decode_token_workspace_bytes, 256-byte aligned; partial sums between phases */
+    size_t workspace_bytes;
+} izb_qwen3_decode_args;
+
+size_t izb_qwen3_decode_token_workspace_bytes(izb_ctx* ctx, const izb_qwen3_decode_args* args);
+int32_t izb_qwen3_decode_token(izb_ctx* ctx, izb_stream stream, const izb_qwen3_decode_args* args);
 
 #ifdef __cplusplus
 }

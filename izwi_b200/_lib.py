@@ -43,6 +43,24 @@ class KvPages(C.Structure):
                 ("head_dim", C.c_int32), ("max_pages_per_seq", C.c_int64)]
 
 
+class Qwen3LayerPtrs(C.Structure):
+    """Mirror of izb_qwen3_layer_ptrs."""
+    _fields_ = [("input_norm", C.c_void_p), ("post_norm", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("qkv", C.c_void_p), ("o", C.c_void_p), ("gate_up", C.c_void_p), ("down", C.c_void_p),
+                ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+
+
+class Qwen3DecodeArgs(C.Structure):
+    """Mirror of izb_qwen3_decode_args."""
+    _fields_ = [("wfmt", C.c_int32), ("lm_head_fmt", C.c_int32),
+                ("n_layers", C.c_int32), ("hidden", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("intermediate", C.c_int32), ("vocab", C.c_int32), ("pos", C.c_int32),
+                ("kv_capacity", C.c_int64), ("eps", C.c_float), ("reserved_", C.c_int32),
+                ("layers", C.c_void_p), ("embed", C.c_void_p), ("final_norm", C.c_void_p), ("lm_head", C.c_void_p),
+                ("token", C.c_void_p), ("cos_half", C.c_void_p), ("sin_half", C.c_void_p), ("logits", C.c_void_p),
+                ("next_token", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
 class MoeArgs(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("w_router", C.c_void_p), ("router_bias", C.c_void_p), ("w_gate_up", C.c_void_p),
@@ -165,6 +183,8 @@ _SIGNATURES = {
     "izb_depthwise_conv1d_bias_swish": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                     C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                                     C.c_int32]),
+    "izb_qwen3_decode_token_workspace_bytes": (C.c_size_t, [C.c_void_p, C.POINTER(Qwen3DecodeArgs)]),
+    "izb_qwen3_decode_token": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(Qwen3DecodeArgs)]),
     "izb_gguf_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "izb_gguf_close": (C.c_int32, [C.c_void_p]),
     "izb_gguf_version": (C.c_int32, [C.c_void_p]),

@@ -1,0 +1,792 @@
+// One decode token of a Qwen3 decoder in ONE launch: embedding row, every layer (input norm, fused QKV,
+// q/k norms, rotation, cache append, attention over the cache, O projection, residual, post-attention
+// norm, gate/up, SiLU-multiply, down, residual), final norm, lm_head and the arg-max of the logits.
+// Mirrors Qwen3Model::forward for seq_len = 1 plus the greedy choice of the chat decode loop
+// (crates/izwi-core/src/models/architectures/qwen3/core.rs:2099-2125, 1863-1881, 1624-1732;
+// qwen3/chat.rs:574-601) for one sequence over Q8_0 / Q4_K projections.
+//
+// Why one launch: at one token a 0.6B model is ~200 launches of 3..8 us each, every one of which reads
+// its few megabytes in well under a microsecond; the token costs launches, not bytes.  Here a
+// cooperative grid of one CTA per SM walks the phases of every layer and meets at a grid-wide barrier
+// between phases (five per layer).  Inside a CTA a producer warp streams this CTA's share of the weight
+// blocks through a shared-memory ring with bulk copies and runs AHEAD of the barriers (weights depend
+// on nobody), so that after a barrier the consumers find their weights already on chip and the time
+// of a phase is the barrier plus reading a few kilobytes of activations from L2.
+//
+// Work split of a projection [N, K]: units = (64-row tile, k slice); slices S per phase chosen by the
+// host so that the units cover the SMs; unit u goes to CTA u mod G.  A unit writes 64 fp32 partial sums
+// to part[slice][row]; the consumers of the NEXT phase add the S slices (fixed order: results do not
+// depend on timing), apply what sits between the two projections (residual add and bf16 rounding of the
+// stream, RmsNorm, SiLU-multiply, the merge of the attention splits) and convert to the 16-bit block
+// fixed point that the integer dot products read (gemv_dot.cuh).
+//
+// Every wait is bounded: ring barriers and the grid barrier give up after IZB_WAIT_LIMIT_CLOCKS, raise
+// the workspace's abort word (which every other wait also watches) and a context status word, and
+// the CTA leaves.
+#include <algorithm>
+#include <cstring>
+
+#include "gemv_dot.cuh"
+#include "izb_common.cuh"
+
+namespace izb {
+
+constexpr int DT_CONSUMER_WARPS = 8;
+constexpr int DT_CONSUMERS = 32 * DT_CONSUMER_WARPS;
+constexpr int DT_THREADS = DT_CONSUMERS + 32;
+constexpr int DT_TILE_ROWS = 64;
+constexpr int DT_SLOT_BYTES = DT_TILE_ROWS * 272;  // one 256-k box of 64 Q8_0 rows (Q4_K: 64 * 144 of it used)
+constexpr int DT_MAX_SLOTS = 10;
+constexpr int DT_MAX_BOXES = 48;    // K <= 12288
+constexpr int DT_MAX_HIDDEN = 4096;
+constexpr int DT_D = 128;           // head_dim
+constexpr int DT_MAX_GQ = 4;        // query heads per kv head
+constexpr int DT_MAX_SPLITS = 32;
+
+struct DtParams {
+    izb_qwen3_decode_args a;
+    int s_qkv, s_o, s_gu, s_down, att_splits;
+    int n_slots;
+    // workspace carve-up
+    float* part_qkv;   // [s_qkv][q_dim + 2 kv_dim]
+    float* part_o;     // [s_o][hidden]
+    float* part_gu;    // [s_gu][2 I]
+    float* part_down;  // [s_down][hidden]
+    float* att_part;   // [heads][att_splits][D + 2]
+    float* stream_a;   // [hidden] the layer's input stream (bf16 values)
+    float* stream_b;   // [hidden] the stream behind the attention block
+    unsigned long long* best;  // [G] packed (logit, ~index) of every CTA
+    unsigned int* counter;     // grid barrier arrivals
+    int* abort_word;
+    int* status;        // context status word of a wait that gave up
+    int* status_token;  // context status word of a token id outside the embedding table
+};
+
+struct DtShared {
+    unsigned long long full[DT_MAX_SLOTS];
+    unsigned long long empty[DT_MAX_SLOTS];
+    float red[4][DT_TILE_ROWS];
+    float warp_red[DT_CONSUMER_WARPS];
+    unsigned long long warp_best[DT_CONSUMER_WARPS];
+    float inv_rms;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void consumer_sync() { named_bar_sync(1, DT_CONSUMERS); }
+// Barrier over the consumers that also tells every one of them whether all of them passed `ok`: the
+// consumers meet at named barriers, so they must leave a loop together or not at all.
+__device__ __forceinline__ bool consumer_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(ok)), "r"(DT_CONSUMERS)
+        : "memory");
+    return r != 0;
+}
+
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// (value, index) -> one key whose unsigned order is value descending-last, lowest index winning ties.
+__device__ __forceinline__ unsigned long long best_key(float v, int idx) {
+    uint32_t b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // monotone map of float order onto unsigned order
+    return (static_cast<unsigned long long>(b) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(idx));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grid barrier: arrival n of the kernel's k-th barrier makes the counter reach k * G.  Consumers only.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, unsigned int target) {
+    consumer_sync();  // this CTA's writes of the phase are done
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(P.counter, 1u);
+        const long long t0 = clock64();
+        bool ok = true;
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.counter) : "memory");
+            if (v >= target) break;
+            int ab;
+            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(ab) : "l"(P.abort_word) : "memory");
+            if (ab != 0 || clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
+                ok = false;
+                break;
+            }
+            __nanosleep(20);
+        }
+        if (!ok) {
+            atomicExch(P.abort_word, 1);
+            atomicExch(P.status, 1);
+            sh.abort_flag = 1;
+        }
+    }
+    consumer_sync();
+    return *reinterpret_cast<volatile int*>(&sh.abort_flag) == 0;
+}
+
+// Units of a projection phase for this CTA: u = cta, cta + G, ...; unit -> (tile, slice) -> boxes [b0, b1).
+struct DtUnit {
+    int tile, slice, b0, b1;
+};
+__device__ __forceinline__ DtUnit dt_unit(int u, int S, int boxes) {
+    DtUnit r;
+    r.tile = u / S;
+    r.slice = u - r.tile * S;
+    r.b0 = r.slice * boxes / S;
+    r.b1 = (r.slice + 1) * boxes / S;
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Producer warp: the weight boxes of this CTA's units of one projection, in unit order.
+// ---------------------------------------------------------------------------------------------
+struct DtRing {
+    int slot;
+    uint32_t phase;
+    long long issued;
+};
+
+__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const uint8_t* w, int N, int K,
+                                              int S, int w_row_bytes, int lane) {
+    const int boxes = K / 256, tiles = N / DT_TILE_ROWS, units = tiles * S;
+    const size_t row_bytes = static_cast<size_t>(boxes) * w_row_bytes;
+    volatile int* abort_flag = &sh.abort_flag;
+    for (int u = static_cast<int>(blockIdx.x); u < units; u += static_cast<int>(gridDim.x)) {
+        const DtUnit un = dt_unit(u, S, boxes);
+        for (int b = un.b0; b < un.b1; ++b) {
+            bool freed = true;
+            if (R.issued >= P.n_slots) freed = mbar_wait_bounded_relaxed(smem_u32(&sh.empty[R.slot]), R.phase ^ 1u, abort_flag);
+            if (!__all_sync(0xFFFFFFFFu, freed)) return false;  // the lanes leave together
+            const uint32_t fbar = smem_u32(&sh.full[R.slot]);
+            const uint32_t dst = ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES;
+            if (lane == 0) mbar_expect_tx(fbar, static_cast<uint32_t>(DT_TILE_ROWS * w_row_bytes));
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = lane + 32 * h;
+                bulk_g2s(dst + static_cast<uint32_t>(row * w_row_bytes),
+                         w + (static_cast<size_t>(un.tile) * DT_TILE_ROWS + row) * row_bytes + static_cast<size_t>(b) * w_row_bytes,
+                         static_cast<uint32_t>(w_row_bytes), fbar);
+            }
+            ++R.issued;
+            if (++R.slot == P.n_slots) {
+                R.slot = 0;
+                R.phase ^= 1u;
+            }
+        }
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Consumers: the dot products of one unit (64 rows x boxes [b0, b1)) against the converted activations.
+// Q8_0: thread = (row, pair of blocks) of every box; Q4_K: thread = (row, half of the super-block, box parity).
+// Returns the row's sum in the threads with tid < 64.
+// ---------------------------------------------------------------------------------------------
+template <int FMT>
+__device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, uint32_t ring0, uint32_t xq0, DtRing& R, const DtUnit& un,
+                                             float& out) {
+    const int tid = threadIdx.x, row = tid & 63, quarter = tid >> 6;
+    const int w_row_bytes = FMT == IZB_W_Q8_0 ? 272 : 144;
+    volatile int* abort_flag = &sh.abort_flag;
+    float acc[1] = {0.f};
+    bool ok = true;
+    for (int b = un.b0; b < un.b1; ++b) {
+        if (ok && !mbar_wait_bounded(smem_u32(&sh.full[R.slot]), R.phase, abort_flag)) ok = false;
+        if (ok) {
+            const uint32_t wrow = ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES + static_cast<uint32_t>(row * w_row_bytes);
+            const uint32_t xq = xq0 + static_cast<uint32_t>(b * GV_XQ_BYTES);
+            if constexpr (FMT == IZB_W_Q8_0) {
+                switch (quarter) {
+                    case 0: gv_pair_q8_0<0, 1>(acc, wrow, xq, GV_XQ_BYTES); break;
+                    case 1: gv_pair_q8_0<1, 1>(acc, wrow, xq, GV_XQ_BYTES); break;
+                    case 2: gv_pair_q8_0<2, 1>(acc, wrow, xq, GV_XQ_BYTES); break;
+                    default: gv_pair_q8_0<3, 1>(acc, wrow, xq, GV_XQ_BYTES); break;
+                }
+            } else {
+                // the two halves of a super-block go to quarters 0 / 1 for even boxes of the unit, 2 / 3 for odd ones
+                if ((quarter >> 1) == ((b - un.b0) & 1)) {
+                    if (quarter & 1) gv_half_q4_k<1, 1>(acc, wrow, xq, GV_XQ_BYTES);
+                    else gv_half_q4_k<0, 1>(acc, wrow, xq, GV_XQ_BYTES);
+                }
+            }
+        }
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(smem_u32(&sh.empty[R.slot]));
+        if (++R.slot == P.n_slots) {
+            R.slot = 0;
+            R.phase ^= 1u;
+        }
+    }
+    ok = consumer_all(ok);  // also: the sums of the unit before this one have been read
+    sh.red[quarter][row] = acc[0];
+    consumer_sync();
+    out = tid < 64 ? (sh.red[0][tid] + sh.red[1][tid]) + (sh.red[2][tid] + sh.red[3][tid]) : 0.f;
+    return ok;
+}
+
+// Sum of one activation element over the k slices of the projection that produced it (fixed order).
+__device__ __forceinline__ float part_sum(const float* part, int S, int n, int i) {
+    float v = 0.f;
+    for (int s = 0; s < S; ++s) v += __ldcg(part + static_cast<size_t>(s) * n + i);
+    return v;
+}
+
+// xf[0 .. hidden) and 1 / rms over them, by all consumers.
+template <typename F>
+__device__ __forceinline__ void stage_stream(DtShared& sh, float* xf, int hidden, float eps, F value) {
+    const int tid = threadIdx.x;
+    float ss = 0.f;
+    for (int i = tid; i < hidden; i += DT_CONSUMERS) {
+        const float v = value(i);
+        xf[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if ((tid & 31) == 0) sh.warp_red[tid >> 5] = ss;
+    consumer_sync();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < DT_CONSUMER_WARPS; ++w) t += sh.warp_red[w];
+        sh.inv_rms = rsqrtf(t / static_cast<float>(hidden) + eps);
+    }
+    consumer_sync();
+}
+
+// One warp converts one 256-k box: lane = 8 consecutive values.
+template <typename F>
+__device__ __forceinline__ void convert_boxes(uint32_t xq0, int b0, int b1, unsigned long long& done, F values) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int b = b0 + warp; b < b1; b += DT_CONSUMER_WARPS) {
+        if ((done >> b) & 1ull) continue;
+        float v[8];
+        values(b * 256 + lane * 8, v);
+        gv_convert_unit_f32(v, xq0 + static_cast<uint32_t>(b * GV_XQ_BYTES), lane);
+    }
+    for (int b = b0; b < b1; ++b) done |= 1ull << b;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention phase unit: kv head `kvh`, positions [t0, t1) of the cache (position `pos` = the new token).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, float* scratch, const izb_qwen3_layer_ptrs& Lp, int kvh,
+                                               int split, int t0, int t1) {
+    const izb_qwen3_decode_args& A = P.a;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gq = A.heads / A.kv_heads, q_dim = A.heads * DT_D, kv_dim = A.kv_heads * DT_D, n_qkv = q_dim + 2 * kv_dim;
+    float* qs = scratch;                  // [gq][D] rotated query heads (bf16 values)
+    float* knew = qs + DT_MAX_GQ * DT_D;  // [D]
+    float* vnew = knew + DT_D;            // [D]
+    float* wpart = vnew + DT_D;           // [warps][gq][D + 2]
+    const __nv_bfloat16* cosv = static_cast<const __nv_bfloat16*>(A.cos_half);
+    const __nv_bfloat16* sinv = static_cast<const __nv_bfloat16*>(A.sin_half);
+    __nv_bfloat16* kc = static_cast<__nv_bfloat16*>(Lp.k_cache) + static_cast<size_t>(kvh) * A.kv_capacity * DT_D;
+    __nv_bfloat16* vc = static_cast<__nv_bfloat16*>(Lp.v_cache) + static_cast<size_t>(kvh) * A.kv_capacity * DT_D;
+    const bool owns_new = A.pos >= t0 && A.pos < t1;
+
+    // ---- the new token's rows of this kv head: warps 0 .. gq-1 a query head each, warp gq k, warp gq+1 v ----
+    if (warp < gq + 2) {
+        const int col0 = warp < gq ? (kvh * gq + warp) * DT_D : warp == gq ? q_dim + kvh * DT_D : q_dim + kv_dim + kvh * DT_D;
+        float x[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = bf16r(part_sum(P.part_qkv, P.s_qkv, n_qkv, col0 + lane * 4 + j));  // the QKV output as stored
+        if (warp <= gq) {
+            const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(warp < gq ? Lp.q_norm : Lp.k_norm);
+            if (w) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                const float scale = rsqrtf(ss / static_cast<float>(DT_D) + A.eps);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = x[j] * scale * __bfloat162float(w[lane * 4 + j]);
+            }
+            const int jh = (lane & 15) * 4;  // lanes 0..15 hold the first half of the head, 16..31 the second
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float other = __shfl_xor_sync(0xFFFFFFFFu, x[j], 16);
+                const float c = __bfloat162float(cosv[jh + j]), s = __bfloat162float(sinv[jh + j]);
+                x[j] = lane < 16 ? x[j] * c - other * s : other * s + x[j] * c;
+            }
+        }
+        float* dst = warp < gq ? qs + warp * DT_D : warp == gq ? knew : vnew;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[lane * 4 + j] = bf16r(x[j]);
+        if (warp >= gq && owns_new) {
+            __nv_bfloat16* row = (warp == gq ? kc : vc) + static_cast<size_t>(A.pos) * DT_D + lane * 4;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) row[j] = __float2bfloat16_rn(x[j]);
+        }
+    }
+    consumer_sync();
+
+    // ---- every warp: positions t0 + warp, + 8, ...; lane owns 4 of the 128 values ----
+    float q[DT_MAX_GQ][4], acc[DT_MAX_GQ][4], m[DT_MAX_GQ], l[DT_MAX_GQ];
+#pragma unroll
+    for (int g = 0; g < DT_MAX_GQ; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            q[g][j] = g < gq ? qs[g * DT_D + lane * 4 + j] : 0.f;
+            acc[g][j] = 0.f;
+        }
+    }
+    const float scale = rsqrtf(static_cast<float>(DT_D));
+    for (int t = t0 + warp; t < t1; t += DT_CONSUMER_WARPS) {
+        float kv[4], vv[4];
+        if (t == A.pos) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                kv[j] = knew[lane * 4 + j];
+                vv[j] = vnew[lane * 4 + j];
+            }
+        } else {
+            const uint2 kw = *reinterpret_cast<const uint2*>(kc + static_cast<size_t>(t) * DT_D + lane * 4);
+            const uint2 vw = *reinterpret_cast<const uint2*>(vc + static_cast<size_t>(t) * DT_D + lane * 4);
+            kv[0] = bf16_lo_to_f32(kw.x); kv[1] = bf16_hi_to_f32(kw.x); kv[2] = bf16_lo_to_f32(kw.y); kv[3] = bf16_hi_to_f32(kw.y);
+            vv[0] = bf16_lo_to_f32(vw.x); vv[1] = bf16_hi_to_f32(vw.x); vv[2] = bf16_lo_to_f32(vw.y); vv[3] = bf16_hi_to_f32(vw.y);
+        }
+#pragma unroll
+        for (int g = 0; g < DT_MAX_GQ; ++g) {
+            if (g >= gq) break;
+            float s = q[g][0] * kv[0] + q[g][1] * kv[1] + q[g][2] * kv[2] + q[g][3] * kv[3];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+            s *= scale;
+            const float m_new = fmaxf(m[g], s);
+            const float a = __expf(m[g] - m_new), p = __expf(s - m_new);  // first position: exp(-inf) = 0
+            l[g] = l[g] * a + p;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(p, vv[j], acc[g][j] * a);
+            m[g] = m_new;
+        }
+    }
+    // ---- the eight warps' (max, sum, weighted values) -> one partial per query head and split ----
+#pragma unroll
+    for (int g = 0; g < DT_MAX_GQ; ++g) {
+        if (g >= gq) break;
+        float* wp = wpart + (warp * DT_MAX_GQ + g) * (DT_D + 2);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wp[lane * 4 + j] = acc[g][j];
+        if (lane == 0) {
+            wp[DT_D] = m[g];
+            wp[DT_D + 1] = l[g];
+        }
+    }
+    consumer_sync();
+    if (warp < gq) {
+        const int g = warp;
+        float mm = -INFINITY;
+        for (int w = 0; w < DT_CONSUMER_WARPS; ++w) mm = fmaxf(mm, wpart[(w * DT_MAX_GQ + g) * (DT_D + 2) + DT_D]);
+        float num[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
+        for (int w = 0; w < DT_CONSUMER_WARPS; ++w) {
+            const float* wp = wpart + (w * DT_MAX_GQ + g) * (DT_D + 2);
+            const float wm = wp[DT_D];
+            const float f = wm == -INFINITY ? 0.f : __expf(wm - mm);  // a warp without positions
+#pragma unroll
+            for (int j = 0; j < 4; ++j) num[j] = fmaf(f, wp[lane * 4 + j], num[j]);
+            den = fmaf(f, wp[DT_D + 1], den);
+        }
+        float* out = P.att_part + (static_cast<size_t>(kvh * gq + g) * P.att_splits + split) * (DT_D + 2);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[lane * 4 + j] = num[j];
+        if (lane == 0) {
+            out[DT_D] = mm;
+            out[DT_D + 1] = den;
+        }
+    }
+    consumer_sync();  // scratch is reused by the CTA's next unit
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+template <int FMT, int LM_FMT>
+__global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const __grid_constant__ DtParams P) {
+    extern __shared__ __align__(1024) uint8_t dyn_smem[];
+    __shared__ DtShared sh;
+    const izb_qwen3_decode_args& A = P.a;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+    const int q_dim = A.heads * DT_D, kv_dim = A.kv_heads * DT_D, n_qkv = q_dim + 2 * kv_dim;
+    const int w_row = FMT == IZB_W_Q8_0 ? 272 : 144, lm_row = LM_FMT == IZB_W_Q8_0 ? 272 : 144;
+
+    if (tid == 0) {
+        for (int s = 0; s < P.n_slots; ++s) {
+            mbar_init(smem_u32(&sh.full[s]), 1);
+            mbar_init(smem_u32(&sh.empty[s]), DT_CONSUMER_WARPS);
+        }
+        sh.abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const uint32_t ring0 = smem_u32(dyn_smem);
+    uint8_t* scratch_gen = dyn_smem + static_cast<size_t>(P.n_slots) * DT_SLOT_BYTES;
+    const uint32_t xq0 = ring0 + static_cast<uint32_t>(P.n_slots) * DT_SLOT_BYTES;            // [DT_MAX_BOXES][GV_XQ_BYTES]
+    float* xf = reinterpret_cast<float*>(scratch_gen + DT_MAX_BOXES * GV_XQ_BYTES);           // [DT_MAX_HIDDEN]
+    float* att_scratch = reinterpret_cast<float*>(scratch_gen);                                // attention phase: over the same bytes
+
+    DtRing R{0, 0u, 0};
+
+    if (warp == DT_CONSUMER_WARPS) {
+        // ---------------- producer: every projection's boxes, in the consumers' order ----------------
+        bool ok = true;
+        for (int l = 0; l < A.n_layers && ok; ++l) {
+            const izb_qwen3_layer_ptrs& Lp = A.layers[l];
+            ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.qkv), n_qkv, A.hidden, P.s_qkv, w_row, lane);
+            if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.o), A.hidden, q_dim, P.s_o, w_row, lane);
+            if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.gate_up), 2 * A.intermediate, A.hidden, P.s_gu, w_row, lane);
+            if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.down), A.hidden, A.intermediate, P.s_down, w_row, lane);
+        }
+        if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(A.lm_head), A.vocab, A.hidden, 1, lm_row, lane);
+        // the copies still in flight land before the CTA's shared memory goes away
+        if (lane == 0) {
+            const long long first = R.issued > P.n_slots ? R.issued - P.n_slots : 0;
+            for (long long f = first; f < R.issued; ++f) {
+                const uint32_t bar = smem_u32(&sh.full[f % P.n_slots]);
+                const uint32_t par = static_cast<uint32_t>((f / P.n_slots) & 1);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar, par)) {
+                    if (clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) break;
+                }
+            }
+            if (!ok) {
+                atomicExch(P.abort_word, 1);
+                atomicExch(P.status, 1);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    unsigned int barriers = 0;
+    bool ok = true;
+    const int token = *A.token;
+    const __nv_bfloat16* embed_row = static_cast<const __nv_bfloat16*>(A.embed) + static_cast<size_t>(token) * A.hidden;
+    if (token < 0 || token >= A.vocab) {  // a token id outside the embedding table: nothing is read; the host sees a status word
+        if (tid == 0) {
+            atomicExch(P.abort_word, 1);
+            atomicExch(P.status_token, 1);
+        }
+        ok = false;
+    }
+
+    for (int l = 0; l < A.n_layers && ok; ++l) {
+        const izb_qwen3_layer_ptrs& Lp = A.layers[l];
+        // ===== QKV: stream = previous stream + down partials (layer 0: the embedding row); input norm =====
+        {
+            if (l == 0) stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return __bfloat162float(embed_row[i]); });
+            else stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return bf16r(__ldcg(P.stream_b + i) + part_sum(P.part_down, P.s_down, A.hidden, i)); });
+            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_a[i] = xf[i];
+            const float inv = sh.inv_rms;
+            const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(Lp.input_norm);
+            unsigned long long done = 0;
+            const int boxes = A.hidden / 256, units = (n_qkv / DT_TILE_ROWS) * P.s_qkv;
+            convert_boxes(xq0, 0, boxes, done, [&](int k0, float (&v)[8]) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = xf[k0 + j] * inv * __bfloat162float(nw[k0 + j]);
+            });
+            consumer_sync();
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_qkv, boxes);
+                float y;
+                ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
+                if (tid < 64) P.part_qkv[static_cast<size_t>(un.slice) * n_qkv + un.tile * DT_TILE_ROWS + tid] = y;
+            }
+        }
+        ok = grid_barrier(P, sh, ++barriers * G) && ok;
+        if (!ok) break;
+        // ===== attention: q/k norms, rotation, cache append, softmax(q k) v per (kv head, split) =====
+        {
+            const int ctx_len = A.pos + 1;
+            const int per = (ctx_len + P.att_splits - 1) / P.att_splits;
+            const int units = A.kv_heads * P.att_splits;
+            for (int u = cta; u < units; u += G) {
+                const int kvh = u / P.att_splits, split = u - kvh * P.att_splits;
+                const int t0 = min(ctx_len, split * per), t1 = min(ctx_len, t0 + per);
+                attention_unit(P, sh, att_scratch, Lp, kvh, split, t0, t1);
+            }
+        }
+        ok = grid_barrier(P, sh, ++barriers * G) && ok;
+        if (!ok) break;
+        // ===== O projection over the merged attention output =====
+        {
+            unsigned long long done = 0;
+            const int boxes = q_dim / 256, units = (A.hidden / DT_TILE_ROWS) * P.s_o;
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_o, boxes);
+                convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
+                    const int head = k0 / DT_D, d0 = k0 - head * DT_D;
+                    const float* p = P.att_part + static_cast<size_t>(head) * P.att_splits * (DT_D + 2);
+                    float mm = -INFINITY;
+                    for (int s = 0; s < P.att_splits; ++s) mm = fmaxf(mm, __ldcg(p + s * (DT_D + 2) + DT_D));
+                    float num[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, den = 0.f;
+                    for (int s = 0; s < P.att_splits; ++s) {
+                        const float ms = __ldcg(p + s * (DT_D + 2) + DT_D);
+                        const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);  // a split past the end of the cache
+                        den = fmaf(f, __ldcg(p + s * (DT_D + 2) + DT_D + 1), den);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) num[j] = fmaf(f, __ldcg(p + s * (DT_D + 2) + d0 + j), num[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = bf16r(num[j] / den);  // the attention output as stored
+                });
+                consumer_sync();
+                float y;
+                ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
+                if (tid < 64) P.part_o[static_cast<size_t>(un.slice) * A.hidden + un.tile * DT_TILE_ROWS + tid] = y;
+            }
+        }
+        ok = grid_barrier(P, sh, ++barriers * G) && ok;
+        if (!ok) break;
+        // ===== gate / up: stream += O partials; post-attention norm =====
+        {
+            stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return bf16r(__ldcg(P.stream_a + i) + part_sum(P.part_o, P.s_o, A.hidden, i)); });
+            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_b[i] = xf[i];
+            const float inv = sh.inv_rms;
+            const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(Lp.post_norm);
+            unsigned long long done = 0;
+            const int boxes = A.hidden / 256, units = (2 * A.intermediate / DT_TILE_ROWS) * P.s_gu;
+            convert_boxes(xq0, 0, boxes, done, [&](int k0, float (&v)[8]) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = xf[k0 + j] * inv * __bfloat162float(nw[k0 + j]);
+            });
+            consumer_sync();
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_gu, boxes);
+                float y;
+                ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
+                if (tid < 64) P.part_gu[static_cast<size_t>(un.slice) * 2 * A.intermediate + un.tile * DT_TILE_ROWS + tid] = y;
+            }
+        }
+        ok = grid_barrier(P, sh, ++barriers * G) && ok;
+        if (!ok) break;
+        // ===== down over silu(gate) * up =====
+        {
+            unsigned long long done = 0;
+            const int boxes = A.intermediate / 256, units = (A.hidden / DT_TILE_ROWS) * P.s_down;
+            const int n_gu = 2 * A.intermediate;
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_down, boxes);
+                convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float g = bf16r(part_sum(P.part_gu, P.s_gu, n_gu, k0 + j));  // gate and up as the projection stores them
+                        const float up = bf16r(part_sum(P.part_gu, P.s_gu, n_gu, A.intermediate + k0 + j));
+                        v[j] = g * rcp_approx(1.0f + __expf(-g)) * up;
+                    }
+                });
+                consumer_sync();
+                float y;
+                ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
+                if (tid < 64) P.part_down[static_cast<size_t>(un.slice) * A.hidden + un.tile * DT_TILE_ROWS + tid] = y;
+            }
+        }
+        ok = grid_barrier(P, sh, ++barriers * G) && ok;
+    }
+
+    // ===== final norm, lm_head, arg-max =====
+    unsigned long long best = 0;
+    if (ok) {
+        stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return bf16r(__ldcg(P.stream_b + i) + part_sum(P.part_down, P.s_down, A.hidden, i)); });
+        const float inv = sh.inv_rms;
+        const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(A.final_norm);
+        unsigned long long done = 0;
+        const int boxes = A.hidden / 256, units = A.vocab / DT_TILE_ROWS;
+        convert_boxes(xq0, 0, boxes, done, [&](int k0, float (&v)[8]) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = xf[k0 + j] * inv * __bfloat162float(nw[k0 + j]);
+        });
+        consumer_sync();
+        for (int u = cta; u < units; u += G) {
+            const DtUnit un = dt_unit(u, 1, boxes);
+            float y;
+            ok = consume_unit<LM_FMT>(P, sh, ring0, xq0, R, un, y) && ok;
+            if (tid < 64) {
+                const int row = un.tile * DT_TILE_ROWS + tid;
+                if (A.logits) A.logits[row] = y;
+                const unsigned long long key = best_key(y, row);
+                best = key > best ? key : best;
+            }
+        }
+        // the CTA's best row (only the first two warps hold candidates)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+            best = other > best ? other : best;
+        }
+        if (lane == 0) sh.warp_best[warp] = best;
+        consumer_sync();
+        if (tid == 0) P.best[cta] = sh.warp_best[0] > sh.warp_best[1] ? sh.warp_best[0] : sh.warp_best[1];
+        ok = grid_barrier(P, sh, ++barriers * G) && ok;
+        if (ok && cta == 0 && warp == 0) {
+            unsigned long long b = 0;
+            for (int i = lane; i < G; i += 32) {
+                const unsigned long long k = __ldcg(P.best + i);
+                b = k > b ? k : b;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, b, o);
+                b = other > b ? other : b;
+            }
+            if (lane == 0) *A.next_token = static_cast<int32_t>(~static_cast<uint32_t>(b & 0xFFFFFFFFull));
+        }
+    }
+    if (!ok && tid == 0) {
+        // the other CTAs' barrier waits and this CTA's producer see the failure at once
+        atomicExch(P.abort_word, 1);
+        if (token >= 0 && token < A.vocab) atomicExch(P.status, 1);
+        sh.abort_flag = 1;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+size_t al256(size_t v) { return (v + 255) / 256 * 256; }
+
+// k slices of a projection with `tiles` row tiles and `boxes` k boxes on G CTAs: the S (a divisor-free
+// split into nearly equal box ranges) that minimises the boxes the busiest CTA walks, smallest S on ties.
+int pick_slices(int tiles, int boxes, int G) {
+    int best_s = 1;
+    long long best_cost = -1;
+    for (int s = 1; s <= boxes && s <= 16; ++s) {
+        const long long rounds = (static_cast<long long>(tiles) * s + G - 1) / G;
+        const long long per_unit = (boxes + s - 1) / s;
+        const long long cost = rounds * per_unit * 8 + s;  // the next phase reads s partial vectors
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best_s = s;
+        }
+    }
+    return best_s;
+}
+
+struct DtLayout {
+    size_t part_qkv, part_o, part_gu, part_down, att_part, stream_a, stream_b, best, counter, total;
+};
+
+int dt_validate(const izb_qwen3_decode_args* a) {
+    if (!a) return IZB_ERR_BAD_ARG;
+    if (a->wfmt != IZB_W_Q8_0 && a->wfmt != IZB_W_Q4_K) return IZB_ERR_UNSUPPORTED;
+    if (a->lm_head_fmt != IZB_W_Q8_0 && a->lm_head_fmt != IZB_W_Q4_K) return IZB_ERR_UNSUPPORTED;
+    if (a->n_layers <= 0 || a->hidden <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->intermediate <= 0 || a->vocab <= 0) return IZB_ERR_BAD_ARG;
+    if (a->head_dim != DT_D) return IZB_ERR_UNSUPPORTED;
+    if (a->heads % a->kv_heads != 0 || a->heads / a->kv_heads > DT_MAX_GQ) return IZB_ERR_UNSUPPORTED;
+    if (a->hidden % 256 != 0 || a->hidden > DT_MAX_HIDDEN || a->intermediate % 256 != 0 || a->intermediate > DT_MAX_BOXES * 256) return IZB_ERR_UNSUPPORTED;
+    if (a->heads * DT_D > DT_MAX_BOXES * 256) return IZB_ERR_UNSUPPORTED;
+    if (a->hidden % DT_TILE_ROWS != 0 || a->vocab % DT_TILE_ROWS != 0 || (2 * a->intermediate) % DT_TILE_ROWS != 0) return IZB_ERR_UNSUPPORTED;
+    if (a->pos < 0 || a->pos >= a->kv_capacity) return IZB_ERR_BAD_ARG;
+    return IZB_OK;
+}
+
+void dt_plan(const izb_ctx* ctx, const izb_qwen3_decode_args* a, DtParams* p, DtLayout* lay) {
+    const int G = ctx->sm_count;
+    const int q_dim = a->heads * DT_D, kv_dim = a->kv_heads * DT_D, n_qkv = q_dim + 2 * kv_dim;
+    p->s_qkv = pick_slices(n_qkv / DT_TILE_ROWS, a->hidden / 256, G);
+    p->s_o = pick_slices(a->hidden / DT_TILE_ROWS, q_dim / 256, G);
+    p->s_gu = pick_slices(2 * a->intermediate / DT_TILE_ROWS, a->hidden / 256, G);
+    p->s_down = pick_slices(a->hidden / DT_TILE_ROWS, a->intermediate / 256, G);
+    p->att_splits = std::max(1, std::min(DT_MAX_SPLITS, G / a->kv_heads));
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t at = off; off += al256(bytes); return at; };
+    lay->part_qkv = take(sizeof(float) * p->s_qkv * n_qkv);
+    lay->part_o = take(sizeof(float) * p->s_o * a->hidden);
+    lay->part_gu = take(sizeof(float) * p->s_gu * 2 * a->intermediate);
+    lay->part_down = take(sizeof(float) * p->s_down * a->hidden);
+    lay->att_part = take(sizeof(float) * a->heads * p->att_splits * (DT_D + 2));
+    lay->stream_a = take(sizeof(float) * a->hidden);
+    lay->stream_b = take(sizeof(float) * a->hidden);
+    lay->best = take(sizeof(unsigned long long) * G);
+    lay->counter = take(256);  // arrival counter, abort word
+    lay->total = off;
+}
+
+constexpr int DT_SCRATCH_BYTES = DT_MAX_BOXES * GV_XQ_BYTES + DT_MAX_HIDDEN * 4;
+static_assert(DT_SCRATCH_BYTES >= static_cast<int>(sizeof(float)) * ((DT_MAX_GQ + 2) * DT_D + DT_CONSUMER_WARPS * DT_MAX_GQ * (DT_D + 2)),
+              "attention scratch fits the activation scratch");
+
+template <int FMT, int LM>
+int dt_launch(izb_ctx* ctx, cudaStream_t s, DtParams& p) {
+    auto kern = qwen3_decode_token_kernel<FMT, LM>;
+    int slots = (ctx->max_smem_optin - 2048 - static_cast<int>(sizeof(DtShared)) - DT_SCRATCH_BYTES - 1024) / DT_SLOT_BYTES;
+    slots = std::min(slots, DT_MAX_SLOTS);
+    if (slots < 2) return IZB_ERR_UNSUPPORTED;
+    p.n_slots = slots;
+    const int smem = slots * DT_SLOT_BYTES + DT_SCRATCH_BYTES + 1024;
+    static std::atomic<int> smem_set[IZB_MAX_DEVICES];
+    if (smem_set[ctx->device].load(std::memory_order_relaxed) < smem) {
+        IZB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        smem_set[ctx->device].store(smem, std::memory_order_relaxed);
+    }
+    // the grid barrier needs every CTA resident at once: a cooperative launch checks exactly that
+    IZB_CUDA_TRY(cudaMemsetAsync(p.counter, 0, 256, s));
+    void* args[] = {&p};
+    IZB_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), dim3(ctx->sm_count), dim3(DT_THREADS), args,
+                                             static_cast<size_t>(smem), s));
+    ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    return IZB_OK;
+}
+
+}  // namespace
+}  // namespace izb
+
+using namespace izb;
+
+extern "C" {
+
+size_t izb_qwen3_decode_token_workspace_bytes(izb_ctx* ctx, const izb_qwen3_decode_args* args) {
+    if (!ctx || dt_validate(args) != IZB_OK) return 0;
+    DtParams p;
+    DtLayout lay;
+    dt_plan(ctx, args, &p, &lay);
+    return lay.total;
+}
+
+int32_t izb_qwen3_decode_token(izb_ctx* ctx, izb_stream stream, const izb_qwen3_decode_args* args) {
+    if (!ctx) return IZB_ERR_BAD_ARG;
+    const int rc = dt_validate(args);
+    if (rc != IZB_OK) return rc;
+    if (!args->layers || !args->embed || !args->final_norm || !args->lm_head || !args->token || !args->cos_half || !args->sin_half ||
+        !args->next_token)
+        return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(args->embed, 2) || !izb_aligned(args->lm_head, 16) || !izb_aligned(args->token, 4) || !izb_aligned(args->next_token, 4) ||
+        (args->logits && !izb_aligned(args->logits, 4)))
+        return IZB_ERR_BAD_ARG;
+    DtParams p;
+    std::memset(&p, 0, sizeof(p));
+    DtLayout lay;
+    dt_plan(ctx, args, &p, &lay);
+    if (!args->workspace || !izb_aligned(args->workspace, 256) || args->workspace_bytes < lay.total) return IZB_ERR_BAD_ARG;
+    p.a = *args;
+    uint8_t* ws = static_cast<uint8_t*>(args->workspace);
+    p.part_qkv = reinterpret_cast<float*>(ws + lay.part_qkv);
+    p.part_o = reinterpret_cast<float*>(ws + lay.part_o);
+    p.part_gu = reinterpret_cast<float*>(ws + lay.part_gu);
+    p.part_down = reinterpret_cast<float*>(ws + lay.part_down);
+    p.att_part = reinterpret_cast<float*>(ws + lay.att_part);
+    p.stream_a = reinterpret_cast<float*>(ws + lay.stream_a);
+    p.stream_b = reinterpret_cast<float*>(ws + lay.stream_b);
+    p.best = reinterpret_cast<unsigned long long*>(ws + lay.best);
+    p.counter = reinterpret_cast<unsigned int*>(ws + lay.counter);
+    p.abort_word = reinterpret_cast<int*>(ws + lay.counter + 64);
+    p.status = ctx->d_status + 4;
+    p.status_token = ctx->d_status + 6;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (args->wfmt == IZB_W_Q8_0)
+        return args->lm_head_fmt == IZB_W_Q8_0 ? dt_launch<IZB_W_Q8_0, IZB_W_Q8_0>(ctx, s, p) : dt_launch<IZB_W_Q8_0, IZB_W_Q4_K>(ctx, s, p);
+    return args->lm_head_fmt == IZB_W_Q8_0 ? dt_launch<IZB_W_Q4_K, IZB_W_Q8_0>(ctx, s, p) : dt_launch<IZB_W_Q4_K, IZB_W_Q4_K>(ctx, s, p);
+}
+
+}  // extern "C"

@@ -539,9 +539,18 @@ int32_t izb_ar_allreduce(izb_ar* ar, izb_stream stream, void* buf, int64_t count
     const size_t bytes = static_cast<size_t>(count) * (dtype == IZB_F32 ? 4 : 2);
     if (!buf || !izb_aligned(buf, 4) || bytes % 4 != 0) return IZB_ERR_BAD_ARG;
     if (2 * bytes > ar->slot_bytes) {
-        // two-shot path: whole 16-byte units, operand 16-byte aligned; copy in, exchange, copy out
+        // two-shot path: whole 16-byte units, operand 16-byte aligned; copy in, exchange, copy out.
+        // A ragged end (4, 8 or 12 bytes) goes through the one-shot kernel afterwards.
         if (bytes > ar->big_bytes) return IZB_ERR_UNSUPPORTED;
-        if (bytes % 16 != 0 || !izb_aligned(buf, 16)) return IZB_ERR_UNSUPPORTED;
+        if (!izb_aligned(buf, 16)) return IZB_ERR_UNSUPPORTED;
+        const size_t tail = bytes % 16;
+        if (tail != 0) {
+            const size_t whole = bytes - tail;
+            const int64_t per = dtype == IZB_F32 ? 4 : 2;
+            const int rc = izb_ar_allreduce(ar, stream, buf, static_cast<int64_t>(whole) / per, dtype);
+            if (rc != IZB_OK) return rc;
+            return izb_ar_allreduce(ar, stream, static_cast<unsigned char*>(buf) + whole, static_cast<int64_t>(tail) / per, dtype);
+        }
         const long long n_units = static_cast<long long>(bytes / 16);
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         const int b = ar->next_buf;

@@ -141,3 +141,57 @@ class Qwen3Decoder:
             logits = ops.linear(hidden, self.lm_head, self.lm_head_fmt, n=vocab, k=self.w.hidden, out_dtype=torch.float32)
         nxt = ops.argmax_rows(logits)
         return (nxt, logits) if return_logits else nxt
+
+
+class Qwen3TokenKernel:
+    """The whole decode token of one sequence in one cooperative launch (izb_qwen3_decode_token): the same
+    result as `Qwen3Decoder.step` for batch 1, without the ~200 launches.  Holds the device table of layer
+    pointers and the workspace; `caches` are the `KvCache` objects of a batch of one."""
+
+    def __init__(self, decoder: Qwen3Decoder, caches: list):
+        import ctypes as C
+        from . import _lib as L
+        w = decoder.w
+        dev = decoder.embed.device
+        self.decoder, self.caches = decoder, caches
+        rows = (L.Qwen3LayerPtrs * len(decoder.layers))()
+        for i, (layer, cache) in enumerate(zip(decoder.layers, caches)):
+            lw = layer.w
+            assert cache.k.shape[0] == 1, "one sequence"
+            rows[i] = L.Qwen3LayerPtrs(lw.input_layernorm.data_ptr(), lw.post_attention_layernorm.data_ptr(),
+                                       0 if lw.q_norm is None else lw.q_norm.data_ptr(), 0 if lw.k_norm is None else lw.k_norm.data_ptr(),
+                                       lw.qkv.data_ptr(), lw.o.data_ptr(), lw.gate_up.data_ptr(), lw.down.data_ptr(),
+                                       cache.k.data_ptr(), cache.v.data_ptr())
+        host = torch.frombuffer(bytearray(bytes(rows)), dtype=torch.uint8)
+        self.layer_table = host.to(dev)
+        a = L.Qwen3DecodeArgs()
+        a.wfmt, a.lm_head_fmt = ops.WFMT[w.fmt], ops.WFMT[decoder.lm_head_fmt]
+        a.n_layers, a.hidden, a.heads, a.kv_heads, a.head_dim = len(decoder.layers), w.hidden, w.heads, w.kv_heads, w.head_dim
+        a.intermediate, a.vocab = w.intermediate, decoder.embed.shape[0]
+        a.kv_capacity, a.eps = caches[0].capacity, w.eps
+        a.layers, a.embed, a.final_norm, a.lm_head = (self.layer_table.data_ptr(), decoder.embed.data_ptr(),
+                                                      decoder.final_norm.data_ptr(), decoder.lm_head.data_ptr())
+        self.ctx = ops.Context.get(dev.index)
+        need = L.lib().izb_qwen3_decode_token_workspace_bytes(self.ctx.handle, C.byref(a))
+        if need == 0:
+            raise ValueError("this model is outside what izb_qwen3_decode_token takes")
+        self.workspace = torch.zeros(need, device=dev, dtype=torch.uint8)
+        a.workspace, a.workspace_bytes = self.workspace.data_ptr(), need
+        self.args = a
+        self.next_token = torch.zeros(1, device=dev, dtype=torch.int32)
+        self.logits = torch.empty(a.vocab, device=dev, dtype=torch.float32)
+
+    def step(self, token: torch.Tensor, pos: int, cos_half=None, sin_half=None, return_logits: bool = False):
+        """token: int32 [1] on the device -> next token int32 [1] (a view of this object's buffer)."""
+        import ctypes as C
+        from . import _lib as L
+        assert token.dtype == torch.int32 and token.numel() == 1 and token.is_cuda
+        if cos_half is None:
+            cos_half, sin_half = self.decoder.rope_tables(pos, 1)
+        self.keep = (token, cos_half, sin_half)
+        a = self.args
+        a.pos, a.token, a.cos_half, a.sin_half = pos, token.data_ptr(), cos_half.data_ptr(), sin_half.data_ptr()
+        a.logits = self.logits.data_ptr() if return_logits else None
+        a.next_token = self.next_token.data_ptr()
+        L.check(L.lib().izb_qwen3_decode_token(self.ctx.handle, ops._stream(), C.byref(a)), "izb_qwen3_decode_token")
+        return (self.next_token, self.logits) if return_logits else self.next_token

@@ -1,0 +1,169 @@
+"""The one-launch decode token (izb_qwen3_decode_token) against (a) the oracle's composition of the same
+layer functions, op by op with bf16 between them, and (b) the step composed from the separate entry points
+(izwi_b200/decoder.py) on the same weights and caches.  Gate for the logits of a composed token: max error
+<= 3e-2 of the largest magnitude and cosine >= 0.9995 (per-op gates are 2e-2 / 0.9999; a token is ~12 ops
+per layer deep).  The single launch keeps fp32 where the separate ops round to bf16 only where the
+reference stores a tensor (QKV output, attention output, gate/up output, the residual stream)."""
+import numpy as np
+import pytest
+import torch
+
+import izwi_oracle as o
+from gpu_util import bf16_np, to_np
+
+pytestmark = pytest.mark.gpu
+
+HID, HEADS, KVH, D, INTER, VOCAB, EPS = 512, 4, 2, 128, 1024, 1024, 1e-6
+
+
+def _w(rng, fmt, n, k):
+    if fmt == "q8_0":
+        raw = o.make_q8_0_blocks(rng, n * k // 32, d_scale=4e-4)
+    else:
+        raw = o.make_q4_k_blocks(rng, n * k // 256, d_scale=2e-4, dmin_scale=1.5e-3)
+    return raw, o.dequantize(raw, fmt).reshape(n, k)
+
+
+def _model_np(rng, fmt, lm_fmt, n_layers):
+    qd, kd = HEADS * D, KVH * D
+    layers = [{"ln1": bf16_np(rng.normal(1, 0.1, HID)), "ln2": bf16_np(rng.normal(1, 0.1, HID)),
+               "qn": bf16_np(rng.normal(1, 0.1, D)), "kn": bf16_np(rng.normal(1, 0.1, D)),
+               "qkv": _w(rng, fmt, qd + 2 * kd, HID), "o": _w(rng, fmt, HID, qd), "gu": _w(rng, fmt, 2 * INTER, HID),
+               "down": _w(rng, fmt, HID, INTER)} for _ in range(n_layers)]
+    return {"layers": layers, "embed": bf16_np(rng.normal(0, 1, (VOCAB, HID))), "norm": bf16_np(rng.normal(1, 0.1, HID)),
+            "lm_head": _w(rng, lm_fmt, VOCAB, HID)}
+
+
+def _oracle_token(model, token, kcs, vcs, pos, cos, sin):
+    qd, kd = HEADS * D, KVH * D
+    lin = lambda a, w: o.bf16_round(o.linear(a, w))  # noqa: E731
+    x = model["embed"][token][None, :]
+    for L, kc, vc in zip(model["layers"], kcs, vcs):
+        normed, _ = o.rms_norm(x, L["ln1"], EPS)
+        qkv = lin(normed, L["qkv"][1])
+        q = qkv[:, :qd].reshape(1, HEADS, D)
+        k = qkv[:, qd:qd + kd].reshape(1, KVH, D)
+        v = qkv[:, qd + kd:].reshape(1, KVH, D)
+        q, _ = o.rms_norm(q, L["qn"], EPS)
+        k, _ = o.rms_norm(k, L["kn"], EPS)
+        q, k = o.rope_pair(q, cos, sin), o.rope_pair(k, cos, sin)
+        kc[:, :, pos], vc[:, :, pos] = k, v
+        attn = o.bf16_round(o.decode_gqa_attention(q, kc, vc, pos + 1, D ** -0.5))
+        out = lin(attn.reshape(1, qd), L["o"][1])
+        normed2, x1 = o.rms_norm(out, L["ln2"], EPS, residual=x)
+        gu = lin(normed2, L["gu"][1])
+        act = o.bf16_round(o.silu_mul(gu[:, :INTER], gu[:, INTER:]))
+        x = o.bf16_round(x1 + lin(act, L["down"][1]))
+    hidden, _ = o.rms_norm(x, model["norm"], EPS)
+    return o.linear(hidden, model["lm_head"][1])[0]
+
+
+def _build(cuda, model, fmt, lm_fmt, cap):
+    from izwi_b200 import decoder
+    dev = lambda a: torch.from_numpy(a).to(cuda).to(torch.bfloat16)  # noqa: E731
+    layers = [decoder.Qwen3DecoderLayer(decoder.Qwen3LayerWeights(
+        fmt, HID, HEADS, KVH, D, INTER, dev(L["ln1"]), dev(L["ln2"]), dev(L["qn"]), dev(L["kn"]),
+        torch.from_numpy(L["qkv"][0]).to(cuda), torch.from_numpy(L["o"][0]).to(cuda),
+        torch.from_numpy(L["gu"][0]).to(cuda), torch.from_numpy(L["down"][0]).to(cuda), EPS)) for L in model["layers"]]
+    dec = decoder.Qwen3Decoder(dev(model["embed"]), layers, dev(model["norm"]), torch.from_numpy(model["lm_head"][0]).to(cuda), lm_fmt,
+                               rope_theta=10000.0)
+    caches = lambda: [decoder.KvCache(1, KVH, cap, D, cuda) for _ in layers]  # noqa: E731
+    return dec, caches
+
+
+@pytest.mark.parametrize("fmt,lm_fmt,n_layers", [("q8_0", "q8_0", 3), ("q4_k", "q4_k", 2), ("q4_k", "q8_0", 2)])
+def test_tokens_against_oracle_and_composed_step(cuda, fmt, lm_fmt, n_layers):
+    from izwi_b200 import decoder, ops
+    rng = np.random.default_rng(33)
+    model = _model_np(rng, fmt, lm_fmt, n_layers)
+    cap = 48
+    dec, make_caches = _build(cuda, model, fmt, lm_fmt, cap)
+    caches_one, caches_ref = make_caches(), make_caches()
+    kernel = decoder.Qwen3TokenKernel(dec, caches_one)
+    kcs = [np.zeros((1, KVH, cap, D), dtype=np.float32) for _ in range(n_layers)]
+    vcs = [np.zeros((1, KVH, cap, D), dtype=np.float32) for _ in range(n_layers)]
+    inv = 1.0 / (10000.0 ** (np.arange(0, D, 2) / D))
+    token = 17
+    ctx = ops.Context.get(0)
+    for pos in range(40):  # past 18 positions every split of the cache holds more than one
+        ang = (pos * inv)[None, :]
+        cos, sin = bf16_np(np.cos(ang)), bf16_np(np.sin(ang))
+        cos_d = torch.from_numpy(cos).to(cuda).to(torch.bfloat16)
+        sin_d = torch.from_numpy(sin).to(cuda).to(torch.bfloat16)
+        before = ctx.launch_count
+        nxt, logits = kernel.step(torch.tensor([token], device=cuda, dtype=torch.int32), pos, cos_d, sin_d, return_logits=True)
+        assert ctx.launch_count - before == 1
+        ctx.check()
+        got = to_np(logits)
+        nxt_ref, logits_ref = dec.step(torch.tensor([token], device=cuda), caches_ref, pos, cos_d, sin_d, return_logits=True)
+        ref = to_np(logits_ref)[0]
+        assert np.isfinite(got).all()
+        if pos < 6 or pos % 8 == 0:
+            want = _oracle_token(model, token, kcs, vcs, pos, cos, sin)
+            rel, cosine = o.rel_err_and_cosine(got[None, :], want[None, :])
+            assert rel <= 3e-2 and cosine >= 0.9995, ("oracle", fmt, pos, rel, cosine)
+        else:  # keep the oracle's caches in step without the logits
+            _oracle_token(model, token, kcs, vcs, pos, cos, sin)
+        rel, cosine = o.rel_err_and_cosine(got[None, :], ref[None, :])
+        assert rel <= 3e-2 and cosine >= 0.9995, ("composed", fmt, pos, rel, cosine)
+        assert int(nxt.item()) == int(np.argmax(got))  # the kernel's choice is the arg-max of its own logits
+        assert int(np.argmax(got)) == int(np.argmax(got == got.max()))  # lowest index on ties
+        token = int(nxt_ref.item())
+    for c_one, c_ref, kc in zip(caches_one, caches_ref, kcs):
+        k_one, k_ref = to_np(c_one.k[:, :, :40]), to_np(c_ref.k[:, :, :40])
+        assert np.abs(k_one - kc[:, :, :40]).max() <= 3e-2 * np.abs(kc).max()
+        assert np.abs(k_one - k_ref).max() <= 3e-2 * np.abs(kc).max()
+        assert np.abs(to_np(c_one.v[:, :, :40]) - to_np(c_ref.v[:, :, :40])).max() <= 3e-2 * np.abs(to_np(c_ref.v)).max()
+
+
+def test_chained_tokens_without_host_reads(cuda):
+    """next_token of one launch is the `token` pointer of the next: the chain equals the one fed through the host."""
+    from izwi_b200 import decoder, ops
+    rng = np.random.default_rng(5)
+    model = _model_np(rng, "q8_0", "q8_0", 2)
+    dec, make_caches = _build(cuda, model, "q8_0", "q8_0", 16)
+    a, b = decoder.Qwen3TokenKernel(dec, make_caches()), decoder.Qwen3TokenKernel(dec, make_caches())
+    tok_dev = torch.tensor([3], device=cuda, dtype=torch.int32)
+    tok_host = 3
+    chain, fed = [], []
+    for pos in range(8):
+        tok_dev = a.step(tok_dev, pos).clone()
+        chain.append(tok_dev)
+        tok_host = int(b.step(torch.tensor([tok_host], device=cuda, dtype=torch.int32), pos).item())
+        fed.append(tok_host)
+    ops.Context.get(0).check()
+    assert [int(t.item()) for t in chain] == fed
+
+
+def test_token_outside_the_vocabulary_is_reported(cuda):
+    from izwi_b200 import _lib as L
+    from izwi_b200 import decoder, ops
+    rng = np.random.default_rng(6)
+    model = _model_np(rng, "q8_0", "q8_0", 1)
+    dec, make_caches = _build(cuda, model, "q8_0", "q8_0", 8)
+    k = decoder.Qwen3TokenKernel(dec, make_caches())
+    k.next_token.fill_(-5)
+    k.step(torch.tensor([VOCAB], device=cuda, dtype=torch.int32), 0)
+    with pytest.raises(L.IzbError) as e:
+        ops.Context.get(0).check()
+    assert e.value.status == L.IZB_ERR_BAD_ARG
+    assert int(k.next_token.item()) == -5
+    # the context is usable afterwards
+    k.step(torch.tensor([1], device=cuda, dtype=torch.int32), 0)
+    ops.Context.get(0).check()
+    assert 0 <= int(k.next_token.item()) < VOCAB
+
+
+def test_shapes_outside_the_kernel_are_refused(cuda):
+    import ctypes as C
+    from izwi_b200 import _lib as L
+    from izwi_b200 import ops
+    a = L.Qwen3DecodeArgs()
+    a.wfmt = a.lm_head_fmt = L.IZB_W_Q8_0
+    a.n_layers, a.hidden, a.heads, a.kv_heads, a.head_dim, a.intermediate, a.vocab = 1, 512, 8, 4, 64, 1024, 1024
+    a.kv_capacity = 8
+    ctx = ops.Context.get(0)
+    assert L.lib().izb_qwen3_decode_token_workspace_bytes(ctx.handle, C.byref(a)) == 0  # head_dim 64
+    assert L.lib().izb_qwen3_decode_token(ctx.handle, ops._stream(), C.byref(a)) == L.IZB_ERR_UNSUPPORTED
+    a.head_dim, a.wfmt = 128, L.IZB_W_BF16
+    assert L.lib().izb_qwen3_decode_token(ctx.handle, ops._stream(), C.byref(a)) == L.IZB_ERR_UNSUPPORTED
