@@ -624,6 +624,7 @@ int32_t izb_gguf_upload(const izb_gguf* g, const izb_gguf_tensor* t, void* dev_d
  * izb_decode_gqa_attention.  A cooperative launch of one CTA per SM; every device-side wait is bounded
  * (izb_ctx_check: IZB_ERR_TIMEOUT; a token id outside the vocabulary: IZB_ERR_BAD_ARG, nothing read). */
 typedef struct izb_qwen3_layer_ptrs {
+    /* every pointer 16-byte aligned */
     const void* input_norm; /* bf16 [hidden] */
     const void* post_norm;  /* bf16 [hidden] */
     const void* q_norm;     /* bf16 [head_dim], or NULL */
@@ -644,12 +645,12 @@ typedef struct izb_qwen3_decode_args {
     int64_t kv_capacity;
     float eps;
     int32_t reserved_;
-    const izb_qwen3_layer_ptrs* layers; /* DEVICE array [n_layers] */
+    const izb_qwen3_layer_ptrs* layers; /* HOST array [n_layers <= 48] of device pointers: copied into the launch */
     const void* embed;      /* bf16 [vocab, hidden] */
     const void* final_norm; /* bf16 [hidden] */
     const void* lm_head;    /* raw blocks [vocab, hidden], 16-byte aligned */
     const int32_t* token;   /* device: the token to embed (the previous call's next_token chains without a host read) */
-    const void* cos_half;   /* bf16 [head_dim / 2]: cos / sin of pos * inv_freq */
+    const void* cos_half;   /* bf16 [head_dim / 2]: cos / sin of pos * inv_freq; 8-byte aligned */
     const void* sin_half;
     float* logits;          /* device fp32 [vocab], or NULL */
     int32_t* next_token;    /* device: arg-max of the logits, lowest index on ties */

@@ -24,10 +24,12 @@
 // the workspace's abort word (which every other wait also watches) and a context status word, and
 // the CTA leaves.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "gemv_dot.cuh"
 #include "izb_common.cuh"
+#include "tma.cuh"
 
 namespace izb {
 
@@ -41,18 +43,21 @@ constexpr int DT_MAX_BOXES = 48;    // K <= 12288
 constexpr int DT_MAX_HIDDEN = 4096;
 constexpr int DT_D = 128;           // head_dim
 constexpr int DT_MAX_GQ = 4;        // query heads per kv head
-constexpr int DT_MAX_SPLITS = 32;
+constexpr int DT_MAX_LAYERS = 48;   // layer pointers and tensor maps travel as kernel parameters
+constexpr int DT_MAX_SPLITS = 16;
+constexpr int DT_REC = DT_D + 4;     // floats of one attention partial in global memory: D sums, max, sum of weights, padding to 16 bytes
 
 struct DtParams {
     izb_qwen3_decode_args a;
     int s_qkv, s_o, s_gu, s_down, att_splits;
     int n_slots;
+    int dbg;
     // workspace carve-up
     float* part_qkv;   // [s_qkv][q_dim + 2 kv_dim]
     float* part_o;     // [s_o][hidden]
     float* part_gu;    // [s_gu][2 I]
     float* part_down;  // [s_down][hidden]
-    float* att_part;   // [heads][att_splits][D + 2]
+    float* att_part;   // [heads][att_splits][DT_REC]
     float* stream_a;   // [hidden] the layer's input stream (bf16 values)
     float* stream_b;   // [hidden] the stream behind the attention block
     unsigned long long* best;  // [G] packed (logit, ~index) of every CTA
@@ -60,7 +65,11 @@ struct DtParams {
     int* abort_word;
     int* status;        // context status word of a wait that gave up
     int* status_token;  // context status word of a token id outside the embedding table
+    izb_qwen3_layer_ptrs layers[DT_MAX_LAYERS];
+    // weights viewed as [k box][row][bytes of one 256-k box of a row]: qkv, o, gate_up, down of every layer, then lm_head
+    CUtensorMap maps[4 * DT_MAX_LAYERS + 1];
 };
+static_assert(sizeof(DtParams) <= 32764, "kernel parameter space");
 
 struct DtShared {
     unsigned long long full[DT_MAX_SLOTS];
@@ -102,22 +111,23 @@ __device__ __forceinline__ unsigned long long best_key(float v, int idx) {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, unsigned int target) {
     consumer_sync();  // this CTA's writes of the phase are done
+    if (P.dbg & 4) return true;
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(P.counter, 1u);
+        // release: the CTA's writes of the phase (ordered before this thread by the barrier above) are visible
+        // to whoever reads the count with acquire
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.counter) : "memory");
         const long long t0 = clock64();
         bool ok = true;
         for (;;) {
             unsigned int v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.counter) : "memory");
-            if (v >= target) break;
+            if (v >= target || (P.dbg & 1)) break;
             int ab;
             asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(ab) : "l"(P.abort_word) : "memory");
             if (ab != 0 || clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
                 ok = false;
                 break;
             }
-            __nanosleep(20);
         }
         if (!ok) {
             atomicExch(P.abort_word, 1);
@@ -151,28 +161,17 @@ struct DtRing {
     long long issued;
 };
 
-__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const uint8_t* w, int N, int K,
-                                              int S, int w_row_bytes, int lane) {
+__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const CUtensorMap* map, int N, int K,
+                                              int S, int w_row_bytes) {
     const int boxes = K / 256, tiles = N / DT_TILE_ROWS, units = tiles * S;
-    const size_t row_bytes = static_cast<size_t>(boxes) * w_row_bytes;
     volatile int* abort_flag = &sh.abort_flag;
     for (int u = static_cast<int>(blockIdx.x); u < units; u += static_cast<int>(gridDim.x)) {
         const DtUnit un = dt_unit(u, S, boxes);
         for (int b = un.b0; b < un.b1; ++b) {
-            bool freed = true;
-            if (R.issued >= P.n_slots) freed = mbar_wait_bounded_relaxed(smem_u32(&sh.empty[R.slot]), R.phase ^ 1u, abort_flag);
-            if (!__all_sync(0xFFFFFFFFu, freed)) return false;  // the lanes leave together
+            if (R.issued >= P.n_slots && !mbar_wait_bounded_relaxed(smem_u32(&sh.empty[R.slot]), R.phase ^ 1u, abort_flag)) return false;
             const uint32_t fbar = smem_u32(&sh.full[R.slot]);
-            const uint32_t dst = ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES;
-            if (lane == 0) mbar_expect_tx(fbar, static_cast<uint32_t>(DT_TILE_ROWS * w_row_bytes));
-            __syncwarp();
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int row = lane + 32 * h;
-                bulk_g2s(dst + static_cast<uint32_t>(row * w_row_bytes),
-                         w + (static_cast<size_t>(un.tile) * DT_TILE_ROWS + row) * row_bytes + static_cast<size_t>(b) * w_row_bytes,
-                         static_cast<uint32_t>(w_row_bytes), fbar);
-            }
+            mbar_expect_tx(fbar, static_cast<uint32_t>(DT_TILE_ROWS * w_row_bytes));
+            tma_load_3d(ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES, map, 0, un.tile * DT_TILE_ROWS, b, fbar);
             ++R.issued;
             if (++R.slot == P.n_slots) {
                 R.slot = 0;
@@ -197,6 +196,7 @@ __device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, ui
     float acc[1] = {0.f};
     bool ok = true;
     for (int b = un.b0; b < un.b1; ++b) {
+        if (P.dbg & 2) break;
         if (ok && !mbar_wait_bounded(smem_u32(&sh.full[R.slot]), R.phase, abort_flag)) ok = false;
         if (ok) {
             const uint32_t wrow = ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES + static_cast<uint32_t>(row * w_row_bytes);
@@ -230,22 +230,34 @@ __device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, ui
     return ok;
 }
 
-// Sum of one activation element over the k slices of the projection that produced it (fixed order).
-__device__ __forceinline__ float part_sum(const float* part, int S, int n, int i) {
-    float v = 0.f;
-    for (int s = 0; s < S; ++s) v += __ldcg(part + static_cast<size_t>(s) * n + i);
-    return v;
+// Sums of four consecutive activation elements over the k slices of the projection that produced them,
+// in slice order.  The loads of CH slices are issued before the first add: it is the number of L2 round
+// trips, not of loads, that a phase pays for.
+template <int CH>
+__device__ __forceinline__ float4 part_sum4(const float* part, int S, int n, int i0) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < S; s0 += CH) {
+        float4 t[CH];
+#pragma unroll
+        for (int j = 0; j < CH; ++j)
+            t[j] = s0 + j < S ? __ldcg(reinterpret_cast<const float4*>(part + static_cast<size_t>(s0 + j) * n + i0)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            acc.x += t[j].x; acc.y += t[j].y; acc.z += t[j].z; acc.w += t[j].w;
+        }
+    }
+    return acc;
 }
 
-// xf[0 .. hidden) and 1 / rms over them, by all consumers.
+// xf[0 .. hidden) and 1 / rms over them, by all consumers; `value4(i0)` = elements i0 .. i0 + 3.
 template <typename F>
-__device__ __forceinline__ void stage_stream(DtShared& sh, float* xf, int hidden, float eps, F value) {
+__device__ __forceinline__ void stage_stream(DtShared& sh, float* xf, int hidden, float eps, F value4) {
     const int tid = threadIdx.x;
     float ss = 0.f;
-    for (int i = tid; i < hidden; i += DT_CONSUMERS) {
-        const float v = value(i);
-        xf[i] = v;
-        ss = fmaf(v, v, ss);
+    for (int i0 = tid * 4; i0 < hidden; i0 += DT_CONSUMERS * 4) {
+        const float4 v = value4(i0);
+        *reinterpret_cast<float4*>(xf + i0) = v;
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
@@ -257,6 +269,48 @@ __device__ __forceinline__ void stage_stream(DtShared& sh, float* xf, int hidden
         sh.inv_rms = rsqrtf(t / static_cast<float>(hidden) + eps);
     }
     consumer_sync();
+}
+
+// stream + the k slices of the projection behind it, rounded to bf16 as the reference stores the stream
+__device__ __forceinline__ float4 stream_plus(const float* stream, const float* part, int S, int n, int i0) {
+    const float4 r = __ldcg(reinterpret_cast<const float4*>(stream + i0));
+    const float4 p = part_sum4<8>(part, S, n, i0);
+    return make_float4(bf16r(r.x + p.x), bf16r(r.y + p.y), bf16r(r.z + p.z), bf16r(r.w + p.w));
+}
+
+// The norm weights a warp needs for its boxes of a norm phase (boxes warp, warp + 8: hidden <= 4096), asked for
+// BEFORE the stream is read so that both answers travel together.
+struct DtNormW {
+    uint4 w[2];
+};
+__device__ __forceinline__ DtNormW load_norm_weights(const __nv_bfloat16* nw, int boxes) {
+    DtNormW r;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int b = warp + i * DT_CONSUMER_WARPS;
+        r.w[i] = b < boxes ? __ldg(reinterpret_cast<const uint4*>(nw + b * 256 + lane * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    return r;
+}
+// xq of every box of the normalised stream: x * (1 / rms) * weight
+__device__ __forceinline__ void convert_normed(uint32_t xq0, const float* xf, float inv, const DtNormW& nw, int boxes) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int b = warp + i * DT_CONSUMER_WARPS;
+        if (b >= boxes) break;
+        const int k0 = b * 256 + lane * 8;
+        const float4 x0 = *reinterpret_cast<const float4*>(xf + k0), x1 = *reinterpret_cast<const float4*>(xf + k0 + 4);
+        const uint32_t ww[4] = {nw.w[i].x, nw.w[i].y, nw.w[i].z, nw.w[i].w};
+        float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[2 * j] = v[2 * j] * inv * bf16_lo_to_f32(ww[j]);
+            v[2 * j + 1] = v[2 * j + 1] * inv * bf16_hi_to_f32(ww[j]);
+        }
+        gv_convert_unit_f32(v, xq0 + static_cast<uint32_t>(b * GV_XQ_BYTES), lane);
+    }
 }
 
 // One warp converts one 256-k box: lane = 8 consecutive values.
@@ -293,12 +347,20 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
     // ---- the new token's rows of this kv head: warps 0 .. gq-1 a query head each, warp gq k, warp gq+1 v ----
     if (warp < gq + 2) {
         const int col0 = warp < gq ? (kvh * gq + warp) * DT_D : warp == gq ? q_dim + kvh * DT_D : q_dim + kv_dim + kvh * DT_D;
-        float x[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) x[j] = bf16r(part_sum(P.part_qkv, P.s_qkv, n_qkv, col0 + lane * 4 + j));  // the QKV output as stored
+        // everything this warp's row needs from memory, asked for together
+        const __nv_bfloat16* w = warp <= gq ? static_cast<const __nv_bfloat16*>(warp < gq ? Lp.q_norm : Lp.k_norm) : nullptr;
+        const int jh = (lane & 15) * 4;  // lanes 0..15 hold the first half of the head, 16..31 the second
+        uint2 wv = make_uint2(0u, 0u), cv = make_uint2(0u, 0u), sv = make_uint2(0u, 0u);
+        if (w) wv = __ldg(reinterpret_cast<const uint2*>(w + lane * 4));
         if (warp <= gq) {
-            const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(warp < gq ? Lp.q_norm : Lp.k_norm);
+            cv = __ldg(reinterpret_cast<const uint2*>(cosv + jh));
+            sv = __ldg(reinterpret_cast<const uint2*>(sinv + jh));
+        }
+        const float4 xs = part_sum4<4>(P.part_qkv, P.s_qkv, n_qkv, col0 + lane * 4);
+        float x[4] = {bf16r(xs.x), bf16r(xs.y), bf16r(xs.z), bf16r(xs.w)};  // the QKV output as stored
+        if (warp <= gq) {
             if (w) {
+                const float wf[4] = {bf16_lo_to_f32(wv.x), bf16_hi_to_f32(wv.x), bf16_lo_to_f32(wv.y), bf16_hi_to_f32(wv.y)};
                 float ss = 0.f;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
@@ -306,14 +368,14 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
                 const float scale = rsqrtf(ss / static_cast<float>(DT_D) + A.eps);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) x[j] = x[j] * scale * __bfloat162float(w[lane * 4 + j]);
+                for (int j = 0; j < 4; ++j) x[j] = x[j] * scale * wf[j];
             }
-            const int jh = (lane & 15) * 4;  // lanes 0..15 hold the first half of the head, 16..31 the second
+            const float cf[4] = {bf16_lo_to_f32(cv.x), bf16_hi_to_f32(cv.x), bf16_lo_to_f32(cv.y), bf16_hi_to_f32(cv.y)};
+            const float sf[4] = {bf16_lo_to_f32(sv.x), bf16_hi_to_f32(sv.x), bf16_lo_to_f32(sv.y), bf16_hi_to_f32(sv.y)};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float other = __shfl_xor_sync(0xFFFFFFFFu, x[j], 16);
-                const float c = __bfloat162float(cosv[jh + j]), s = __bfloat162float(sinv[jh + j]);
-                x[j] = lane < 16 ? x[j] * c - other * s : other * s + x[j] * c;
+                x[j] = lane < 16 ? x[j] * cf[j] - other * sf[j] : other * sf[j] + x[j] * cf[j];
             }
         }
         float* dst = warp < gq ? qs + warp * DT_D : warp == gq ? knew : vnew;
@@ -340,33 +402,48 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
         }
     }
     const float scale = rsqrtf(static_cast<float>(DT_D));
-    for (int t = t0 + warp; t < t1; t += DT_CONSUMER_WARPS) {
-        float kv[4], vv[4];
-        if (t == A.pos) {
+    // eight positions per trip to the cache: the loads of a position are a dependent chain otherwise
+    constexpr int PT = 8;
+    for (int tb = t0 + warp; tb < t1; tb += PT * DT_CONSUMER_WARPS) {
+        uint2 kw[PT], vw[PT];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                kv[j] = knew[lane * 4 + j];
-                vv[j] = vnew[lane * 4 + j];
+        for (int u = 0; u < PT; ++u) {
+            const int t = tb + u * DT_CONSUMER_WARPS;
+            kw[u] = vw[u] = make_uint2(0u, 0u);
+            if (t < t1 && t != A.pos) {
+                kw[u] = *reinterpret_cast<const uint2*>(kc + static_cast<size_t>(t) * DT_D + lane * 4);
+                vw[u] = *reinterpret_cast<const uint2*>(vc + static_cast<size_t>(t) * DT_D + lane * 4);
             }
-        } else {
-            const uint2 kw = *reinterpret_cast<const uint2*>(kc + static_cast<size_t>(t) * DT_D + lane * 4);
-            const uint2 vw = *reinterpret_cast<const uint2*>(vc + static_cast<size_t>(t) * DT_D + lane * 4);
-            kv[0] = bf16_lo_to_f32(kw.x); kv[1] = bf16_hi_to_f32(kw.x); kv[2] = bf16_lo_to_f32(kw.y); kv[3] = bf16_hi_to_f32(kw.y);
-            vv[0] = bf16_lo_to_f32(vw.x); vv[1] = bf16_hi_to_f32(vw.x); vv[2] = bf16_lo_to_f32(vw.y); vv[3] = bf16_hi_to_f32(vw.y);
         }
 #pragma unroll
-        for (int g = 0; g < DT_MAX_GQ; ++g) {
-            if (g >= gq) break;
-            float s = q[g][0] * kv[0] + q[g][1] * kv[1] + q[g][2] * kv[2] + q[g][3] * kv[3];
+        for (int u = 0; u < PT; ++u) {
+            const int t = tb + u * DT_CONSUMER_WARPS;
+            if (t >= t1) break;
+            float kv[4], vv[4];
+            if (t == A.pos) {
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-            s *= scale;
-            const float m_new = fmaxf(m[g], s);
-            const float a = __expf(m[g] - m_new), p = __expf(s - m_new);  // first position: exp(-inf) = 0
-            l[g] = l[g] * a + p;
+                for (int j = 0; j < 4; ++j) {
+                    kv[j] = knew[lane * 4 + j];
+                    vv[j] = vnew[lane * 4 + j];
+                }
+            } else {
+                kv[0] = bf16_lo_to_f32(kw[u].x); kv[1] = bf16_hi_to_f32(kw[u].x); kv[2] = bf16_lo_to_f32(kw[u].y); kv[3] = bf16_hi_to_f32(kw[u].y);
+                vv[0] = bf16_lo_to_f32(vw[u].x); vv[1] = bf16_hi_to_f32(vw[u].x); vv[2] = bf16_lo_to_f32(vw[u].y); vv[3] = bf16_hi_to_f32(vw[u].y);
+            }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(p, vv[j], acc[g][j] * a);
-            m[g] = m_new;
+            for (int g = 0; g < DT_MAX_GQ; ++g) {
+                if (g >= gq) break;
+                float sc = q[g][0] * kv[0] + q[g][1] * kv[1] + q[g][2] * kv[2] + q[g][3] * kv[3];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xFFFFFFFFu, sc, o);
+                sc *= scale;
+                const float m_new = fmaxf(m[g], sc);
+                const float a = __expf(m[g] - m_new), p = __expf(sc - m_new);  // first position: exp(-inf) = 0
+                l[g] = l[g] * a + p;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(p, vv[j], acc[g][j] * a);
+                m[g] = m_new;
+            }
         }
     }
     // ---- the eight warps' (max, sum, weighted values) -> one partial per query head and split ----
@@ -395,7 +472,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
             for (int j = 0; j < 4; ++j) num[j] = fmaf(f, wp[lane * 4 + j], num[j]);
             den = fmaf(f, wp[DT_D + 1], den);
         }
-        float* out = P.att_part + (static_cast<size_t>(kvh * gq + g) * P.att_splits + split) * (DT_D + 2);
+        float* out = P.att_part + (static_cast<size_t>(kvh * gq + g) * P.att_splits + split) * DT_REC;
 #pragma unroll
         for (int j = 0; j < 4; ++j) out[lane * 4 + j] = num[j];
         if (lane == 0) {
@@ -437,18 +514,20 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
     DtRing R{0, 0u, 0};
 
     if (warp == DT_CONSUMER_WARPS) {
-        // ---------------- producer: every projection's boxes, in the consumers' order ----------------
+        // ---------------- producer (one lane): every projection's boxes, in the consumers' order ----------------
+        if (lane != 0) return;
         bool ok = true;
+        if (P.dbg & 2) return;
         for (int l = 0; l < A.n_layers && ok; ++l) {
-            const izb_qwen3_layer_ptrs& Lp = A.layers[l];
-            ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.qkv), n_qkv, A.hidden, P.s_qkv, w_row, lane);
-            if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.o), A.hidden, q_dim, P.s_o, w_row, lane);
-            if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.gate_up), 2 * A.intermediate, A.hidden, P.s_gu, w_row, lane);
-            if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(Lp.down), A.hidden, A.intermediate, P.s_down, w_row, lane);
+            const CUtensorMap* m = P.maps + 4 * l;
+            ok = produce_phase(P, sh, ring0, R, m + 0, n_qkv, A.hidden, P.s_qkv, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 1, A.hidden, q_dim, P.s_o, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 2, 2 * A.intermediate, A.hidden, P.s_gu, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 3, A.hidden, A.intermediate, P.s_down, w_row);
         }
-        if (ok) ok = produce_phase(P, sh, ring0, R, static_cast<const uint8_t*>(A.lm_head), A.vocab, A.hidden, 1, lm_row, lane);
+        if (ok) ok = produce_phase(P, sh, ring0, R, P.maps + 4 * A.n_layers, A.vocab, A.hidden, 1, lm_row);
         // the copies still in flight land before the CTA's shared memory goes away
-        if (lane == 0) {
+        {
             const long long first = R.issued > P.n_slots ? R.issued - P.n_slots : 0;
             for (long long f = first; f < R.issued; ++f) {
                 const uint32_t bar = smem_u32(&sh.full[f % P.n_slots]);
@@ -480,20 +559,20 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
     }
 
     for (int l = 0; l < A.n_layers && ok; ++l) {
-        const izb_qwen3_layer_ptrs& Lp = A.layers[l];
+        const izb_qwen3_layer_ptrs& Lp = P.layers[l];
         // ===== QKV: stream = previous stream + down partials (layer 0: the embedding row); input norm =====
         {
-            if (l == 0) stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return __bfloat162float(embed_row[i]); });
-            else stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return bf16r(__ldcg(P.stream_b + i) + part_sum(P.part_down, P.s_down, A.hidden, i)); });
-            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_a[i] = xf[i];
-            const float inv = sh.inv_rms;
-            const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(Lp.input_norm);
-            unsigned long long done = 0;
             const int boxes = A.hidden / 256, units = (n_qkv / DT_TILE_ROWS) * P.s_qkv;
-            convert_boxes(xq0, 0, boxes, done, [&](int k0, float (&v)[8]) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = xf[k0 + j] * inv * __bfloat162float(nw[k0 + j]);
-            });
+            const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(Lp.input_norm), boxes);
+            if (l == 0)
+                stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) {
+                    const uint2 w = *reinterpret_cast<const uint2*>(embed_row + i0);
+                    return make_float4(bf16_lo_to_f32(w.x), bf16_hi_to_f32(w.x), bf16_lo_to_f32(w.y), bf16_hi_to_f32(w.y));
+                });
+            else
+                stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.s_down, A.hidden, i0); });
+            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_a[i] = xf[i];
+            convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
             consumer_sync();
             for (int u = cta; u < units; u += G) {
                 const DtUnit un = dt_unit(u, P.s_qkv, boxes);
@@ -524,20 +603,54 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
             for (int u = cta; u < units; u += G) {
                 const DtUnit un = dt_unit(u, P.s_o, boxes);
                 convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
-                    const int head = k0 / DT_D, d0 = k0 - head * DT_D;
-                    const float* p = P.att_part + static_cast<size_t>(head) * P.att_splits * (DT_D + 2);
-                    float mm = -INFINITY;
-                    for (int s = 0; s < P.att_splits; ++s) mm = fmaxf(mm, __ldcg(p + s * (DT_D + 2) + DT_D));
-                    float num[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, den = 0.f;
-                    for (int s = 0; s < P.att_splits; ++s) {
-                        const float ms = __ldcg(p + s * (DT_D + 2) + DT_D);
-                        const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);  // a split past the end of the cache
-                        den = fmaf(f, __ldcg(p + s * (DT_D + 2) + DT_D + 1), den);
+                    // merge of the splits' (max, sum of weights, weighted values) for this lane's 8 values of one head;
+                    // the records of the first eight splits and all the (max, sum) pairs are asked for in one go
+                    const int head = k0 / DT_D, d0 = k0 - head * DT_D, S = P.att_splits;
+                    const float* p = P.att_part + static_cast<size_t>(head) * S * DT_REC;
+                    float2 ml[DT_MAX_SPLITS];
+                    float4 t0[8], t1[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) num[j] = fmaf(f, __ldcg(p + s * (DT_D + 2) + d0 + j), num[j]);
+                    for (int j = 0; j < DT_MAX_SPLITS; ++j)
+                        ml[j] = j < S ? __ldcg(reinterpret_cast<const float2*>(p + j * DT_REC + DT_D)) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int sj = j < S ? j : 0;
+                        t0[j] = __ldcg(reinterpret_cast<const float4*>(p + sj * DT_REC + d0));
+                        t1[j] = __ldcg(reinterpret_cast<const float4*>(p + sj * DT_REC + d0 + 4));
                     }
+                    float mm = -INFINITY;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = bf16r(num[j] / den);  // the attention output as stored
+                    for (int j = 0; j < DT_MAX_SPLITS; ++j) mm = fmaxf(mm, ml[j].x);
+                    float f[DT_MAX_SPLITS], den = 0.f;
+#pragma unroll
+                    for (int j = 0; j < DT_MAX_SPLITS; ++j) {
+                        f[j] = ml[j].x == -INFINITY ? 0.f : __expf(ml[j].x - mm);  // a split past the end of the cache
+                        den = fmaf(f[j], ml[j].y, den);
+                    }
+                    float num[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int c = 0; c < DT_MAX_SPLITS / 8; ++c) {
+                        if (c > 0) {
+                            if (8 * c >= S) break;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int sj = 8 * c + j < S ? 8 * c + j : 0;
+                                t0[j] = __ldcg(reinterpret_cast<const float4*>(p + sj * DT_REC + d0));
+                                t1[j] = __ldcg(reinterpret_cast<const float4*>(p + sj * DT_REC + d0 + 4));
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float cj = f[8 * c + j];  // 0 beyond the last split
+                            num[0] = fmaf(cj, t0[j].x, num[0]); num[1] = fmaf(cj, t0[j].y, num[1]);
+                            num[2] = fmaf(cj, t0[j].z, num[2]); num[3] = fmaf(cj, t0[j].w, num[3]);
+                            num[4] = fmaf(cj, t1[j].x, num[4]); num[5] = fmaf(cj, t1[j].y, num[5]);
+                            num[6] = fmaf(cj, t1[j].z, num[6]); num[7] = fmaf(cj, t1[j].w, num[7]);
+                        }
+                    }
+                    const float r = 1.0f / den;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = bf16r(num[j] * r);  // the attention output as stored
                 });
                 consumer_sync();
                 float y;
@@ -549,16 +662,11 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         if (!ok) break;
         // ===== gate / up: stream += O partials; post-attention norm =====
         {
-            stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return bf16r(__ldcg(P.stream_a + i) + part_sum(P.part_o, P.s_o, A.hidden, i)); });
-            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_b[i] = xf[i];
-            const float inv = sh.inv_rms;
-            const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(Lp.post_norm);
-            unsigned long long done = 0;
             const int boxes = A.hidden / 256, units = (2 * A.intermediate / DT_TILE_ROWS) * P.s_gu;
-            convert_boxes(xq0, 0, boxes, done, [&](int k0, float (&v)[8]) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = xf[k0 + j] * inv * __bfloat162float(nw[k0 + j]);
-            });
+            const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(Lp.post_norm), boxes);
+            stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_a, P.part_o, P.s_o, A.hidden, i0); });
+            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_b[i] = xf[i];
+            convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
             consumer_sync();
             for (int u = cta; u < units; u += G) {
                 const DtUnit un = dt_unit(u, P.s_gu, boxes);
@@ -577,10 +685,14 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
             for (int u = cta; u < units; u += G) {
                 const DtUnit un = dt_unit(u, P.s_down, boxes);
                 convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
+                    const float4 g0 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, k0), g1 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, k0 + 4);
+                    const float4 u0 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, A.intermediate + k0);
+                    const float4 u1 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, A.intermediate + k0 + 4);
+                    const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                    const float us[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const float g = bf16r(part_sum(P.part_gu, P.s_gu, n_gu, k0 + j));  // gate and up as the projection stores them
-                        const float up = bf16r(part_sum(P.part_gu, P.s_gu, n_gu, A.intermediate + k0 + j));
+                        const float g = bf16r(gs[j]), up = bf16r(us[j]);  // gate and up as the projection stores them
                         v[j] = g * rcp_approx(1.0f + __expf(-g)) * up;
                     }
                 });
@@ -596,15 +708,10 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
     // ===== final norm, lm_head, arg-max =====
     unsigned long long best = 0;
     if (ok) {
-        stage_stream(sh, xf, A.hidden, A.eps, [&](int i) { return bf16r(__ldcg(P.stream_b + i) + part_sum(P.part_down, P.s_down, A.hidden, i)); });
-        const float inv = sh.inv_rms;
-        const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(A.final_norm);
-        unsigned long long done = 0;
         const int boxes = A.hidden / 256, units = A.vocab / DT_TILE_ROWS;
-        convert_boxes(xq0, 0, boxes, done, [&](int k0, float (&v)[8]) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = xf[k0 + j] * inv * __bfloat162float(nw[k0 + j]);
-        });
+        const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(A.final_norm), boxes);
+        stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.s_down, A.hidden, i0); });
+        convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
         consumer_sync();
         for (int u = cta; u < units; u += G) {
             const DtUnit un = dt_unit(u, 1, boxes);
@@ -687,8 +794,20 @@ int dt_validate(const izb_qwen3_decode_args* a) {
     if (a->hidden % 256 != 0 || a->hidden > DT_MAX_HIDDEN || a->intermediate % 256 != 0 || a->intermediate > DT_MAX_BOXES * 256) return IZB_ERR_UNSUPPORTED;
     if (a->heads * DT_D > DT_MAX_BOXES * 256) return IZB_ERR_UNSUPPORTED;
     if (a->hidden % DT_TILE_ROWS != 0 || a->vocab % DT_TILE_ROWS != 0 || (2 * a->intermediate) % DT_TILE_ROWS != 0) return IZB_ERR_UNSUPPORTED;
+    if (a->n_layers > DT_MAX_LAYERS) return IZB_ERR_UNSUPPORTED;
     if (a->pos < 0 || a->pos >= a->kv_capacity) return IZB_ERR_BAD_ARG;
     return IZB_OK;
+}
+
+// Weights [N, K] in GGML blocks as [K / 256 boxes][N rows][words of one box of a row]; one copy = 64 rows of one box.
+int dt_weight_map(CUtensorMap* out, const void* w, int fmt, int N, int K) {
+    const int w_row_bytes = fmt == IZB_W_Q8_0 ? 272 : 144;
+    const uint64_t boxes = static_cast<uint64_t>(K) / 256, row_bytes = boxes * w_row_bytes;
+    const uint32_t words = static_cast<uint32_t>(w_row_bytes / 4);
+    const uint64_t dims[3] = {words, static_cast<uint64_t>(N), boxes};
+    const uint64_t strides[2] = {row_bytes, static_cast<uint64_t>(w_row_bytes)};
+    const uint32_t box[3] = {words, static_cast<uint32_t>(DT_TILE_ROWS), 1};
+    return tma_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 void dt_plan(const izb_ctx* ctx, const izb_qwen3_decode_args* a, DtParams* p, DtLayout* lay) {
@@ -698,14 +817,19 @@ void dt_plan(const izb_ctx* ctx, const izb_qwen3_decode_args* a, DtParams* p, Dt
     p->s_o = pick_slices(a->hidden / DT_TILE_ROWS, q_dim / 256, G);
     p->s_gu = pick_slices(2 * a->intermediate / DT_TILE_ROWS, a->hidden / 256, G);
     p->s_down = pick_slices(a->hidden / DT_TILE_ROWS, a->intermediate / 256, G);
-    p->att_splits = std::max(1, std::min(DT_MAX_SPLITS, G / a->kv_heads));
+    // splits of the cache per KV head: 64 positions each while eight splits cover the context (one trip for the
+    // merge), 256 each beyond; the workspace is laid out for the most there can be
+    const int max_splits = std::max(1, std::min(DT_MAX_SPLITS, G / a->kv_heads));
+    const int ctx_len = a->pos + 1;
+    const int want = ctx_len <= 8 * 64 * 4 ? std::min(8, (ctx_len + 63) / 64) : (ctx_len + 255) / 256;
+    p->att_splits = std::max(1, std::min(max_splits, want));
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t at = off; off += al256(bytes); return at; };
     lay->part_qkv = take(sizeof(float) * p->s_qkv * n_qkv);
     lay->part_o = take(sizeof(float) * p->s_o * a->hidden);
     lay->part_gu = take(sizeof(float) * p->s_gu * 2 * a->intermediate);
     lay->part_down = take(sizeof(float) * p->s_down * a->hidden);
-    lay->att_part = take(sizeof(float) * a->heads * p->att_splits * (DT_D + 2));
+    lay->att_part = take(sizeof(float) * a->heads * max_splits * DT_REC);
     lay->stream_a = take(sizeof(float) * a->hidden);
     lay->stream_b = take(sizeof(float) * a->hidden);
     lay->best = take(sizeof(unsigned long long) * G);
@@ -761,7 +885,8 @@ int32_t izb_qwen3_decode_token(izb_ctx* ctx, izb_stream stream, const izb_qwen3_
     if (!args->layers || !args->embed || !args->final_norm || !args->lm_head || !args->token || !args->cos_half || !args->sin_half ||
         !args->next_token)
         return IZB_ERR_BAD_ARG;
-    if (!izb_aligned(args->embed, 2) || !izb_aligned(args->lm_head, 16) || !izb_aligned(args->token, 4) || !izb_aligned(args->next_token, 4) ||
+    if (!izb_aligned(args->cos_half, 8) || !izb_aligned(args->sin_half, 8) || !izb_aligned(args->final_norm, 16)) return IZB_ERR_BAD_ARG;
+    if (!izb_aligned(args->embed, 8) || !izb_aligned(args->lm_head, 16) || !izb_aligned(args->token, 4) || !izb_aligned(args->next_token, 4) ||
         (args->logits && !izb_aligned(args->logits, 4)))
         return IZB_ERR_BAD_ARG;
     DtParams p;
@@ -770,6 +895,25 @@ int32_t izb_qwen3_decode_token(izb_ctx* ctx, izb_stream stream, const izb_qwen3_
     dt_plan(ctx, args, &p, &lay);
     if (!args->workspace || !izb_aligned(args->workspace, 256) || args->workspace_bytes < lay.total) return IZB_ERR_BAD_ARG;
     p.a = *args;
+    p.a.layers = nullptr;  // the kernel reads its own copy
+    const int q_dim = args->heads * DT_D, n_qkv = q_dim + 2 * args->kv_heads * DT_D;
+    for (int l = 0; l < args->n_layers; ++l) {
+        const izb_qwen3_layer_ptrs& L = args->layers[l];
+        if (!L.input_norm || !L.post_norm || !L.qkv || !L.o || !L.gate_up || !L.down || !L.k_cache || !L.v_cache) return IZB_ERR_BAD_ARG;
+        if (!izb_aligned(L.input_norm, 16) || !izb_aligned(L.post_norm, 16) || (L.q_norm && !izb_aligned(L.q_norm, 16)) ||
+            (L.k_norm && !izb_aligned(L.k_norm, 16)) || !izb_aligned(L.k_cache, 16) || !izb_aligned(L.v_cache, 16))
+            return IZB_ERR_BAD_ARG;
+        p.layers[l] = L;
+        int rc2 = dt_weight_map(&p.maps[4 * l + 0], L.qkv, args->wfmt, n_qkv, args->hidden);
+        if (rc2 == IZB_OK) rc2 = dt_weight_map(&p.maps[4 * l + 1], L.o, args->wfmt, args->hidden, q_dim);
+        if (rc2 == IZB_OK) rc2 = dt_weight_map(&p.maps[4 * l + 2], L.gate_up, args->wfmt, 2 * args->intermediate, args->hidden);
+        if (rc2 == IZB_OK) rc2 = dt_weight_map(&p.maps[4 * l + 3], L.down, args->wfmt, args->hidden, args->intermediate);
+        if (rc2 != IZB_OK) return rc2;
+    }
+    {
+        const int rc2 = dt_weight_map(&p.maps[4 * args->n_layers], args->lm_head, args->lm_head_fmt, args->vocab, args->hidden);
+        if (rc2 != IZB_OK) return rc2;
+    }
     uint8_t* ws = static_cast<uint8_t*>(args->workspace);
     p.part_qkv = reinterpret_cast<float*>(ws + lay.part_qkv);
     p.part_o = reinterpret_cast<float*>(ws + lay.part_o);
@@ -783,6 +927,7 @@ int32_t izb_qwen3_decode_token(izb_ctx* ctx, izb_stream stream, const izb_qwen3_
     p.abort_word = reinterpret_cast<int*>(ws + lay.counter + 64);
     p.status = ctx->d_status + 4;
     p.status_token = ctx->d_status + 6;
+    { const char* e = std::getenv("IZB_DT_DEBUG"); p.dbg = e ? std::atoi(e) : 0; }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (args->wfmt == IZB_W_Q8_0)
         return args->lm_head_fmt == IZB_W_Q8_0 ? dt_launch<IZB_W_Q8_0, IZB_W_Q8_0>(ctx, s, p) : dt_launch<IZB_W_Q8_0, IZB_W_Q4_K>(ctx, s, p);

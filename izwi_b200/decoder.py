@@ -162,14 +162,13 @@ class Qwen3TokenKernel:
                                        0 if lw.q_norm is None else lw.q_norm.data_ptr(), 0 if lw.k_norm is None else lw.k_norm.data_ptr(),
                                        lw.qkv.data_ptr(), lw.o.data_ptr(), lw.gate_up.data_ptr(), lw.down.data_ptr(),
                                        cache.k.data_ptr(), cache.v.data_ptr())
-        host = torch.frombuffer(bytearray(bytes(rows)), dtype=torch.uint8)
-        self.layer_table = host.to(dev)
+        self.layer_table = rows  # host array of device pointers: the library copies it into the launch
         a = L.Qwen3DecodeArgs()
         a.wfmt, a.lm_head_fmt = ops.WFMT[w.fmt], ops.WFMT[decoder.lm_head_fmt]
         a.n_layers, a.hidden, a.heads, a.kv_heads, a.head_dim = len(decoder.layers), w.hidden, w.heads, w.kv_heads, w.head_dim
         a.intermediate, a.vocab = w.intermediate, decoder.embed.shape[0]
         a.kv_capacity, a.eps = caches[0].capacity, w.eps
-        a.layers, a.embed, a.final_norm, a.lm_head = (self.layer_table.data_ptr(), decoder.embed.data_ptr(),
+        a.layers, a.embed, a.final_norm, a.lm_head = (C.cast(self.layer_table, C.c_void_p), decoder.embed.data_ptr(),
                                                       decoder.final_norm.data_ptr(), decoder.lm_head.data_ptr())
         self.ctx = ops.Context.get(dev.index)
         need = L.lib().izb_qwen3_decode_token_workspace_bytes(self.ctx.handle, C.byref(a))

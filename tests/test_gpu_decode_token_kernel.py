@@ -116,6 +116,44 @@ def test_tokens_against_oracle_and_composed_step(cuda, fmt, lm_fmt, n_layers):
         assert np.abs(to_np(c_one.v[:, :, :40]) - to_np(c_ref.v[:, :, :40])).max() <= 3e-2 * np.abs(to_np(c_ref.v)).max()
 
 
+@pytest.mark.parametrize("start", [300, 2100])
+def test_long_context_splits_of_the_cache(cuda, start):
+    """A cache that already holds `start` positions: the attention phase splits it over CTAs (5 splits at
+    300 positions: one trip of the merge; 9 at 2100: two), against the oracle and the composed step."""
+    from izwi_b200 import decoder, ops
+    rng = np.random.default_rng(44)
+    fmt = "q8_0"
+    model = _model_np(rng, fmt, fmt, 2)
+    cap = start + 8
+    dec, make_caches = _build(cuda, model, fmt, fmt, cap)
+    caches_one, caches_ref = make_caches(), make_caches()
+    kcs, vcs = [], []
+    for c1, c2 in zip(caches_one, caches_ref):
+        k0, v0 = bf16_np(rng.normal(0, 1, (1, KVH, cap, D))), bf16_np(rng.normal(0, 1, (1, KVH, cap, D)))
+        k0[:, :, start:], v0[:, :, start:] = 0, 0
+        for c in (c1, c2):
+            c.k.copy_(torch.from_numpy(k0).to(cuda).to(torch.bfloat16))
+            c.v.copy_(torch.from_numpy(v0).to(cuda).to(torch.bfloat16))
+        kcs.append(k0.copy())
+        vcs.append(v0.copy())
+    kernel = decoder.Qwen3TokenKernel(dec, caches_one)
+    inv = 1.0 / (10000.0 ** (np.arange(0, D, 2) / D))
+    token = 5
+    for pos in range(start, start + 3):
+        ang = (pos * inv)[None, :]
+        cos, sin = bf16_np(np.cos(ang)), bf16_np(np.sin(ang))
+        cos_d, sin_d = torch.from_numpy(cos).to(cuda).to(torch.bfloat16), torch.from_numpy(sin).to(cuda).to(torch.bfloat16)
+        nxt, logits = kernel.step(torch.tensor([token], device=cuda, dtype=torch.int32), pos, cos_d, sin_d, return_logits=True)
+        ops.Context.get(0).check()
+        got = to_np(logits)
+        nxt_ref, logits_ref = dec.step(torch.tensor([token], device=cuda), caches_ref, pos, cos_d, sin_d, return_logits=True)
+        want = _oracle_token(model, token, kcs, vcs, pos, cos, sin)
+        for name, other in (("oracle", want), ("composed", to_np(logits_ref)[0])):
+            rel, cosine = o.rel_err_and_cosine(got[None, :], other[None, :])
+            assert rel <= 3e-2 and cosine >= 0.9995, (name, start, pos, rel, cosine)
+        token = int(nxt_ref.item())
+
+
 def test_chained_tokens_without_host_reads(cuda):
     """next_token of one launch is the `token` pointer of the next: the chain equals the one fed through the host."""
     from izwi_b200 import decoder, ops
