@@ -8,10 +8,11 @@
 // Why one launch: at one token a 0.6B model is ~200 launches of 3..8 us each, every one of which reads
 // its few megabytes in well under a microsecond; the token costs launches, not bytes.  Here a
 // cooperative grid of one CTA per SM walks the phases of every layer and meets at a grid-wide barrier
-// between phases (five per layer).  Inside a CTA a producer warp streams this CTA's share of the weight
-// blocks through a shared-memory ring with bulk copies and runs AHEAD of the barriers (weights depend
-// on nobody), so that after a barrier the consumers find their weights already on chip and the time
-// of a phase is the barrier plus reading a few kilobytes of activations from L2.
+// between phases (five per layer).  Inside a CTA a producer lane streams this CTA's share of the weight
+// blocks through a shared-memory ring with tiled TMA copies (one per 64-row, 256-k box; the tensor maps
+// travel as launch parameters) and runs AHEAD of the barriers (weights depend on nobody), so that after a
+// barrier the consumers find their weights already on chip and the time of a phase is the barrier plus
+// reading a few kilobytes of activations from L2, every load of which is asked for before the first is used.
 //
 // Work split of a projection [N, K]: units = (64-row tile, k slice); slices S per phase chosen by the
 // host so that the units cover the SMs; unit u goes to CTA u mod G.  A unit writes 64 fp32 partial sums
@@ -24,7 +25,6 @@
 // the workspace's abort word (which every other wait also watches) and a context status word, and
 // the CTA leaves.
 #include <algorithm>
-#include <cstdlib>
 #include <cstring>
 
 #include "gemv_dot.cuh"
@@ -51,7 +51,6 @@ struct DtParams {
     izb_qwen3_decode_args a;
     int s_qkv, s_o, s_gu, s_down, att_splits;
     int n_slots;
-    int dbg;
     // workspace carve-up
     float* part_qkv;   // [s_qkv][q_dim + 2 kv_dim]
     float* part_o;     // [s_o][hidden]
@@ -111,7 +110,6 @@ __device__ __forceinline__ unsigned long long best_key(float v, int idx) {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, unsigned int target) {
     consumer_sync();  // this CTA's writes of the phase are done
-    if (P.dbg & 4) return true;
     if (threadIdx.x == 0) {
         // release: the CTA's writes of the phase (ordered before this thread by the barrier above) are visible
         // to whoever reads the count with acquire
@@ -121,7 +119,7 @@ __device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, un
         for (;;) {
             unsigned int v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.counter) : "memory");
-            if (v >= target || (P.dbg & 1)) break;
+            if (v >= target) break;
             int ab;
             asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(ab) : "l"(P.abort_word) : "memory");
             if (ab != 0 || clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
@@ -196,7 +194,6 @@ __device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, ui
     float acc[1] = {0.f};
     bool ok = true;
     for (int b = un.b0; b < un.b1; ++b) {
-        if (P.dbg & 2) break;
         if (ok && !mbar_wait_bounded(smem_u32(&sh.full[R.slot]), R.phase, abort_flag)) ok = false;
         if (ok) {
             const uint32_t wrow = ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES + static_cast<uint32_t>(row * w_row_bytes);
@@ -517,7 +514,6 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         // ---------------- producer (one lane): every projection's boxes, in the consumers' order ----------------
         if (lane != 0) return;
         bool ok = true;
-        if (P.dbg & 2) return;
         for (int l = 0; l < A.n_layers && ok; ++l) {
             const CUtensorMap* m = P.maps + 4 * l;
             ok = produce_phase(P, sh, ring0, R, m + 0, n_qkv, A.hidden, P.s_qkv, w_row);
@@ -927,7 +923,6 @@ int32_t izb_qwen3_decode_token(izb_ctx* ctx, izb_stream stream, const izb_qwen3_
     p.abort_word = reinterpret_cast<int*>(ws + lay.counter + 64);
     p.status = ctx->d_status + 4;
     p.status_token = ctx->d_status + 6;
-    { const char* e = std::getenv("IZB_DT_DEBUG"); p.dbg = e ? std::atoi(e) : 0; }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (args->wfmt == IZB_W_Q8_0)
         return args->lm_head_fmt == IZB_W_Q8_0 ? dt_launch<IZB_W_Q8_0, IZB_W_Q8_0>(ctx, s, p) : dt_launch<IZB_W_Q8_0, IZB_W_Q4_K>(ctx, s, p);
