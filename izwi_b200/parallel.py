@@ -149,8 +149,8 @@ class Comm:
         assert t.is_contiguous()
         code = L.IZB_F32 if t.dtype == torch.float32 else L.IZB_BF16
         nbytes = t.numel() * t.element_size()
-        big = nbytes > (1 << 20)          # two-shot path: whole 16-byte units
-        if getattr(self, "ar", None) and nbytes <= self.ar_max and nbytes % (16 if big else 4) == 0 \
+        big = nbytes > (1 << 20)          # two-shot path: 16-byte aligned operand (a ragged end takes the one-shot kernel)
+        if getattr(self, "ar", None) and nbytes <= self.ar_max and nbytes % 4 == 0 \
                 and t.data_ptr() % (16 if big else 4) == 0:
             L.check(L.lib().izb_ar_allreduce(self.ar, _stream(), _ptr(t), t.numel(), code), "izb_ar_allreduce")
         else:
