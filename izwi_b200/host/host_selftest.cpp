@@ -236,7 +236,8 @@ static int chat_main(int argc, char** argv) {
             if (step.finished) break;
         }
         ctx->check_device();
-        std::printf("\npositions: %lld\nchat: ok\n", static_cast<long long>(st.pos));
+        std::printf("\npositions: %lld\nlaunches: %lld\nchat: ok\n", static_cast<long long>(st.pos),
+                    static_cast<long long>(izb_ctx_launch_count(ctx->get())));
         return 0;
     } catch (const std::exception& e) {
         std::printf("FAIL %s\n", e.what());

@@ -14,6 +14,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -48,6 +49,9 @@ class Qwen3Cache {
     }
     std::vector<DeviceBuffer> k, v;
     int64_t capacity;
+    // the one-launch token (izb_qwen3_decode_token): its workspace and the 4 bytes its own arg-max goes to;
+    // created by the first single-token forward of a model that qualifies
+    DeviceBuffer token_workspace, token_choice;
 };
 
 class Qwen3Model {
@@ -93,6 +97,7 @@ class Qwen3Model {
         if (pos < 0 || pos + n > cache.capacity) throw InferenceError("Qwen3 forward exceeds the KV cache capacity");
         if (scratch.bytes() < scratch_bytes(n)) throw InferenceError("Qwen3 forward scratch is too small");
         const Qwen3Config& c = cfg_;
+        if (n == 1 && forward_one_launch(ctx, s, ids, pos, cache, logits)) return;
         const int64_t H = c.hidden_size, QD = c.num_heads * c.head_dim, KD = c.num_kv_heads * c.head_dim, I = c.intermediate_size;
         const int64_t QKV = QD + 2 * KD;
         auto* base = static_cast<uint8_t*>(scratch.get());
@@ -197,6 +202,63 @@ class Qwen3Model {
     }
 
   private:
+    // One token of one sequence as ONE launch when the library takes this model (every projection of the layers in
+    // one of Q8_0 / Q4_K, lm_head in either, head_dim 128, ...: izb_qwen3_decode_token); false = compose the step.
+    // IZWI_B200_TOKEN_KERNEL=0 keeps the composed step.
+    bool forward_one_launch(const Context& ctx, cudaStream_t s, const int32_t* id, int64_t pos, Qwen3Cache& cache, float* logits) const {
+        static const bool enabled = [] {
+            const char* e = std::getenv("IZWI_B200_TOKEN_KERNEL");
+            return !(e && e[0] == '0');
+        }();
+        if (!enabled || token_kernel_refused_) return false;
+        const Qwen3Config& c = cfg_;
+        const int32_t fmt = layers_[0].qkv.wfmt();
+        for (const Qwen3LayerWeights& w : layers_)
+            for (const Qwen3Projection* p : {&w.qkv, &w.o, &w.gate_up, &w.down})
+                if (p->wfmt() != fmt) { token_kernel_refused_ = true; return false; }
+        std::vector<izb_qwen3_layer_ptrs> rows(static_cast<size_t>(c.num_layers));
+        for (int64_t l = 0; l < c.num_layers; ++l) {
+            const Qwen3LayerWeights& w = layers_[l];
+            rows[l] = {w.input_layernorm->get(), w.post_attention_layernorm->get(), w.q_norm ? w.q_norm->get() : nullptr,
+                       w.k_norm ? w.k_norm->get() : nullptr, w.qkv.weight()->get(), w.o.weight()->get(), w.gate_up.weight()->get(),
+                       w.down.weight()->get(), cache.k[l].get(), cache.v[l].get()};
+        }
+        izb_qwen3_decode_args a{};
+        a.wfmt = fmt;
+        a.lm_head_fmt = lm_head_.wfmt();
+        a.n_layers = static_cast<int32_t>(c.num_layers);
+        a.hidden = static_cast<int32_t>(c.hidden_size);
+        a.heads = static_cast<int32_t>(c.num_heads);
+        a.kv_heads = static_cast<int32_t>(c.num_kv_heads);
+        a.head_dim = static_cast<int32_t>(c.head_dim);
+        a.intermediate = static_cast<int32_t>(c.intermediate_size);
+        a.vocab = static_cast<int32_t>(c.vocab_size);
+        a.pos = static_cast<int32_t>(pos);
+        a.kv_capacity = cache.capacity;
+        a.eps = c.rms_norm_eps;
+        a.layers = rows.data();
+        a.embed = embed_->get();
+        a.final_norm = final_norm_->get();
+        a.lm_head = lm_head_.weight()->get();
+        a.token = id;
+        a.cos_half = static_cast<const uint8_t*>(cos_.get()) + static_cast<size_t>(pos) * (c.head_dim / 2) * 2;
+        a.sin_half = static_cast<const uint8_t*>(sin_.get()) + static_cast<size_t>(pos) * (c.head_dim / 2) * 2;
+        a.logits = logits;
+        const size_t need = izb_qwen3_decode_token_workspace_bytes(ctx.get(), &a);
+        if (need == 0) { token_kernel_refused_ = true; return false; }
+        if (cache.token_workspace.bytes() < need) {
+            cache.token_workspace = DeviceBuffer(need);
+            cache.token_choice = DeviceBuffer(4);
+        }
+        a.workspace = cache.token_workspace.get();
+        a.workspace_bytes = cache.token_workspace.bytes();
+        a.next_token = static_cast<int32_t*>(cache.token_choice.get());
+        const int32_t rc = izb_qwen3_decode_token(ctx.get(), s, &a);
+        if (rc == IZB_ERR_UNSUPPORTED) { token_kernel_refused_ = true; return false; }
+        check(rc, "izb_qwen3_decode_token");
+        return true;
+    }
+
     static uint16_t to_bf16(float f) {
         uint32_t u;
         std::memcpy(&u, &f, 4);
@@ -233,6 +295,7 @@ class Qwen3Model {
     Qwen3Projection lm_head_;
     DeviceBuffer cos_, sin_;
     mutable std::shared_ptr<DeviceBuffer> ones_, add_sink_;
+    mutable bool token_kernel_refused_ = false;
 };
 
 // Token ids that end a reply (the tokenizer's im_end / eos / eos_alt, chat.rs:346-349).

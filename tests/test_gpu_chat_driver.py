@@ -16,6 +16,8 @@ gguf = pytest.importorskip("gguf")
 pytestmark = pytest.mark.gpu
 
 HID, HEADS, KVH, D, INTER, LAYERS, VOCAB, EPS, THETA = 256, 4, 2, 64, 512, 2, 512, 1e-6, 1e6
+# the same model with heads of 128: the shape the one-launch token (izb_qwen3_decode_token) takes
+WIDE_HEADS, WIDE_KVH, WIDE_D = 2, 1, 128
 
 
 @pytest.fixture(scope="module")
@@ -30,10 +32,9 @@ def _q8(rng, n, k, scale):
     return raw.reshape(n, -1)
 
 
-@pytest.fixture(scope="module")
-def model(tmp_path_factory):
+def _write_model(tmp_path_factory, HEADS, KVH, D):
     rng = np.random.default_rng(77)
-    path = tmp_path_factory.mktemp("chat") / "tiny-qwen3-q8_0.gguf"
+    path = tmp_path_factory.mktemp("chat") / f"tiny-qwen3-q8_0-d{D}.gguf"
     t = {"token_embd.weight": bf16_np(rng.normal(0, 0.5, (VOCAB, HID))),
          "output_norm.weight": rng.normal(1, 0.1, HID).astype(np.float32),
          "output.weight": _q8(rng, VOCAB, HID, 6e-4)}
@@ -74,7 +75,17 @@ def model(tmp_path_factory):
     return path, t
 
 
-def _python_mirror(t, cuda):
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    return _write_model(tmp_path_factory, HEADS, KVH, D)
+
+
+@pytest.fixture(scope="module")
+def wide_model(tmp_path_factory):
+    return _write_model(tmp_path_factory, WIDE_HEADS, WIDE_KVH, WIDE_D)
+
+
+def _python_mirror(t, cuda, HEADS=HEADS, KVH=KVH, D=D):
     from izwi_b200 import decoder
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)  # noqa: E731
     bf = lambda a: dev(a.astype(np.float32)).to(torch.bfloat16)  # noqa: E731
@@ -91,14 +102,18 @@ def _python_mirror(t, cuda):
                                 rope_theta=THETA)
 
 
-def _run(selftest, path, tmp_path, mode, prompt, max_new):
+def _run(selftest, path, tmp_path, mode, prompt, max_new, env=None, with_launches=False):
+    import os
     out = tmp_path / f"logits_{mode}.bin"
     proc = subprocess.run([str(selftest), "chat", str(path), str(max_new), str(out), mode, *map(str, prompt)],
-                          capture_output=True, text=True, timeout=300)
+                          capture_output=True, text=True, timeout=300, env=None if env is None else {**os.environ, **env})
     assert proc.returncode == 0 and "chat: ok" in proc.stdout, proc.stdout + proc.stderr
     line = [ln for ln in proc.stdout.splitlines() if ln.startswith("generated:")][0]
     tokens = [int(v) for v in line.split()[1:]]
     positions = int([ln for ln in proc.stdout.splitlines() if ln.startswith("positions:")][0].split()[1])
+    if with_launches:
+        launches = int([ln for ln in proc.stdout.splitlines() if ln.startswith("launches:")][0].split()[1])
+        return np.fromfile(out, dtype=np.float32), tokens, positions, launches
     return np.fromfile(out, dtype=np.float32), tokens, positions
 
 
@@ -132,3 +147,36 @@ def test_prefill_then_greedy_decode_follows_the_decode_step_mirror(cuda, selftes
         pos += 1
     if tokens_d and tokens_p:
         assert tokens_d[0] == tokens_p[0] or abs(logits_d[tokens_d[0]] - logits_d[tokens_p[0]]) <= 2e-2 * spread
+
+
+def test_single_tokens_go_through_the_one_launch_kernel(cuda, selftest, wide_model, tmp_path):
+    """A model the one-launch token takes (Q8_0 everywhere, head_dim 128): every single-token forward of the
+    driver is one launch, and logits and greedy tokens agree with the composed step (the same driver with
+    IZWI_B200_TOKEN_KERNEL=0) and with the Python mirror."""
+    from izwi_b200 import decoder, ops
+    path, t = wide_model
+    prompt, max_new = [11, 403, 77, 250, 9], 6
+    on = _run(selftest, path, tmp_path, "decode", prompt, max_new, with_launches=True)
+    off = _run(selftest, path, tmp_path, "decode", prompt, max_new, env={"IZWI_B200_TOKEN_KERNEL": "0"}, with_launches=True)
+    # 4 forced prompt steps + up to 6 generated tokens: one launch each (+ the arg-max per generated token and the
+    # first token's composed... the first prompt token goes through start_decode's forward of one token as well)
+    steps = len(prompt) + len(on[1])
+    assert on[3] <= 2 * steps + 2, on[3]
+    assert off[3] >= 8 * steps, off[3]
+    rel, cos = o.rel_err_and_cosine(on[0][None, :], off[0][None, :])
+    assert rel <= 3e-2 and cos >= 0.9995, (rel, cos)
+    mirror = _python_mirror(t, cuda, WIDE_HEADS, WIDE_KVH, WIDE_D)
+    caches = [decoder.KvCache(1, WIDE_KVH, 256, WIDE_D, cuda) for _ in range(LAYERS)]
+    for pos, tok in enumerate(prompt):
+        _, logits = mirror.step(torch.tensor([tok], device=cuda), caches, pos, return_logits=True)
+    want = logits[0].float().cpu().numpy()
+    ops.Context.get(0).check()
+    rel, cos = o.rel_err_and_cosine(on[0][None, :], want[None, :])
+    assert rel <= 3e-2 and cos >= 0.9995, (rel, cos)
+    spread = float(want.max() - want.min())
+    pos = len(prompt)
+    for tok in on[1]:
+        assert want[tok] >= want.max() - 2e-2 * spread, ("driver token is not a maximum of the mirror's logits", tok)
+        _, logits = mirror.step(torch.tensor([tok], device=cuda), caches, pos, return_logits=True)
+        want = logits[0].float().cpu().numpy()
+        pos += 1
