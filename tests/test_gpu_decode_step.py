@@ -1,8 +1,8 @@
 """Whole decode tokens through two Qwen3 decoder layers assembled from the C-ABI entry points
 (izwi_b200/decoder.py) against the same composition of oracle functions, with a growing KV cache.
 Every op output is bf16 on both sides; the composition is compared after each token.  Gate for the
-composed stream: max error <= 3e-2 of the largest magnitude and cosine >= 0.9995 (the per-op gates
-are 2e-2 / 0.9999; differences of one bf16 step per op accumulate over ~20 ops per token)."""
+composed stream: the per-op gate itself, max error <= 2e-2 of the largest magnitude and cosine >= 0.9999
+(measured over the six variants: 7.8e-3 .. 1.6e-2 and 0.99995 .. 0.999996)."""
 import numpy as np
 import pytest
 import torch
@@ -84,7 +84,7 @@ def test_three_tokens_two_layers(cuda, fmt, fused_qk, fused_linear):
             want = _oracle_layer(L, want, kc, vc, pos, cos, sin)
         rel, cosine = o.rel_err_and_cosine(got, want)
         assert np.isfinite(got).all()
-        assert rel <= 3e-2 and cosine >= 0.9995, (fmt, pos, rel, cosine)
+        assert rel <= 2e-2 and cosine >= 0.9999, (fmt, pos, rel, cosine)
     # the caches hold the same keys on both sides (up to one bf16 step from the fused arithmetic)
     for cache, kc in zip(caches, kcs):
         k_got = to_np(cache.k[:, :, :3])
