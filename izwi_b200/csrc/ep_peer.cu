@@ -86,6 +86,8 @@ __global__ void __launch_bounds__(256)
     ep_counts_kernel(EpPeers peers, EpLayout lay, EpTables* __restrict__ tb, const int* __restrict__ offsets, int world,
                      int rank, int n_experts, int e_local, long long recv_cap, int* status) {
     __shared__ int bad;
+    __shared__ int s_cnt[EP_MAX_WORLD][EP_MAX_EXPERTS];
+    __shared__ int s_pre[EP_MAX_WORLD + 1][EP_MAX_EXPERTS + 1];
     izb::pdl_launch_dependents();
     izb::pdl_wait();  // offsets come from the permutation kernel before this one
     EpHeader* hdr = reinterpret_cast<EpHeader*>(peers.base[rank]);
@@ -103,7 +105,8 @@ __global__ void __launch_bounds__(256)
             ep_st_pair(dst, c, seq);
         }
     }
-    // collect everyone's
+    // collect everyone's into shared memory: every table below is sums over this [world][experts] matrix, and
+    // walking it in global memory made this one-CTA kernel a third of the dispatch
     const long long t0 = clock64();
     bool ok = true;
     for (int i = threadIdx.x; i < world * n_experts && ok; i += blockDim.x) {
@@ -116,7 +119,9 @@ __global__ void __launch_bounds__(256)
             }
             v = ep_ld_pair(src);
         }
-        tb->cnt[i / n_experts][i % n_experts] = ok ? static_cast<int>(v.x) : 0;
+        const int c = ok ? static_cast<int>(v.x) : 0;
+        s_cnt[i / n_experts][i % n_experts] = c;
+        tb->cnt[i / n_experts][i % n_experts] = c;
     }
     if (!ok) bad = 1;
     __syncthreads();
@@ -128,26 +133,58 @@ __global__ void __launch_bounds__(256)
         for (int e = threadIdx.x; e < n_experts; e += blockDim.x) tb->dst_row[e] = -1;
         return;
     }
+    // exclusive prefix sums over the experts, one warp per row: rows 0 .. world-1 = each source's counts,
+    // row `world` = the totals over all sources; s_pre[r][n_experts] = the row's sum
+    {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+        const int chunk = (n_experts + 31) / 32;
+        for (int r = warp; r <= world; r += nwarps) {
+            const int lo = min(lane * chunk, n_experts), hi = min(lo + chunk, n_experts);
+            int sum = 0;
+            for (int e = lo; e < hi; ++e) {
+                int c = 0;
+                if (r < world) c = s_cnt[r][e];
+                else for (int s2 = 0; s2 < world; ++s2) c += s_cnt[s2][e];
+                sum += c;
+            }
+            int incl = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            int at = incl - sum;
+            for (int e = lo; e < hi; ++e) {
+                int c = 0;
+                if (r < world) c = s_cnt[r][e];
+                else for (int s2 = 0; s2 < world; ++s2) c += s_cnt[s2][e];
+                s_pre[r][e] = at;
+                at += c;
+            }
+            if (lane == 31) s_pre[r][n_experts] = incl;
+        }
+    }
+    __syncthreads();
+    const int* tot_pre = s_pre[world];
     // where my rows for expert e start on its owner: all rows of the owner's earlier experts, then the
     // rows of lower ranks for e
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
         const int first = e / e_local * e_local;
-        long long at = 0;
-        for (int e2 = first; e2 < e; ++e2)
-            for (int s = 0; s < world; ++s) at += tb->cnt[s][e2];
-        for (int s = 0; s < rank; ++s) at += tb->cnt[s][e];
+        long long at = tot_pre[e] - tot_pre[first];
+        for (int s2 = 0; s2 < rank; ++s2) at += s_cnt[s2][e];
         tb->dst_row[e] = at + (offsets[e + 1] - offsets[e]) <= recv_cap ? static_cast<int>(at) : -1;
     }
     // rows I receive: [local expert][source] starts, and the GEMM's segment offsets
+    const int mine0 = rank * e_local;
+    for (int i = threadIdx.x; i < e_local * world; i += blockDim.x) {
+        const int el = i / world, s2 = i - el * world;
+        long long at = tot_pre[mine0 + el] - tot_pre[mine0];
+        if (s2 == 0) tb->seg[el] = static_cast<int>(at < recv_cap ? at : recv_cap);
+        for (int s3 = 0; s3 < s2; ++s3) at += s_cnt[s3][mine0 + el];
+        tb->recv_start[i] = static_cast<int>(at < recv_cap ? at : recv_cap);
+    }
     if (threadIdx.x == 0) {
-        long long at = 0;
-        for (int el = 0; el < e_local; ++el) {
-            tb->seg[el] = static_cast<int>(at < recv_cap ? at : recv_cap);
-            for (int s = 0; s < world; ++s) {
-                tb->recv_start[el * world + s] = static_cast<int>(at < recv_cap ? at : recv_cap);
-                at += tb->cnt[s][rank * e_local + el];
-            }
-        }
+        const long long at = tot_pre[mine0 + e_local] - tot_pre[mine0];
         const int total = static_cast<int>(at < recv_cap ? at : recv_cap);
         tb->seg[e_local] = total;
         tb->recv_start[e_local * world] = total;
@@ -155,10 +192,8 @@ __global__ void __launch_bounds__(256)
     }
     // where results go back: source s keeps its rows of expert e at its own offsets[e] = sum of its earlier counts
     for (int i = threadIdx.x; i < world * e_local; i += blockDim.x) {
-        const int s = i / e_local, el = i % e_local, e = rank * e_local + el;
-        int at = 0;
-        for (int e2 = 0; e2 < e; ++e2) at += tb->cnt[s][e2];
-        tb->ret_start[s][el] = at;
+        const int s2 = i / e_local, el = i % e_local;
+        tb->ret_start[s2][el] = s_pre[s2][mine0 + el];
     }
 }
 
