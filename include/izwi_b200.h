@@ -611,6 +611,18 @@ int32_t izb_gguf_meta_str(const izb_gguf* g, const char* key, const char** out, 
 int32_t izb_gguf_upload(const izb_gguf* g, const izb_gguf_tensor* t, void* dev_dst, size_t dst_bytes,
                         izb_stream stream);
 
+/* MLX affine-packed weights -> dense, the load-time expansion of `load_weight` for MLX-exported checkpoints
+ * (models/shared/weights/mlx.rs:140-256): w[r][c] = q * scales[r][g] + biases[r][g] in fp32 (product and sum
+ * rounded separately), q = (word[r][c / pack] >> ((c % pack) * bits)) & (2^bits - 1), pack = in_dim / packed_in,
+ * bits = word_bits / pack (1..8), g = c / (in_dim / groups).  `packed` is [out_dim, packed_in] words of `word_bits`
+ * (32 or 8) bits; `scales` / `biases` are fp32 [out_dim, groups], or [groups, out_dim] with params_transposed != 0
+ * (the reference transposes those back, mlx.rs:66-74); biases may be NULL (zeros).  `out` is [out_dim, in_dim] in
+ * out_dtype (fp32: the reference's vector bit for bit; bf16 / fp16: its `to_dtype` to the model's type).  Shapes the
+ * reference rejects return IZB_ERR_BAD_ARG. */
+int32_t izb_dequantize_mlx_affine(izb_ctx* ctx, izb_stream stream, const void* packed, int32_t word_bits, int64_t packed_in,
+                                  const float* scales, const float* biases, int64_t groups, int32_t params_transposed,
+                                  int64_t out_dim, int64_t in_dim, int32_t out_dtype, void* out);
+
 /* ---- one decode token of a Qwen3 decoder in one launch -----------------------------------------------
  * Qwen3Model::forward for seq_len = 1 and one sequence, plus the greedy choice of the chat decode loop
  * (qwen3/core.rs:2099-2125, 1863-1881, 1624-1732; qwen3/chat.rs:574-601): embedding row, every decoder

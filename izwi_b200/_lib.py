@@ -183,6 +183,8 @@ _SIGNATURES = {
     "izb_depthwise_conv1d_bias_swish": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                     C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                                     C.c_int32]),
+    "izb_dequantize_mlx_affine": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
+                                              C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "izb_qwen3_decode_token_workspace_bytes": (C.c_size_t, [C.c_void_p, C.POINTER(Qwen3DecodeArgs)]),
     "izb_qwen3_decode_token": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(Qwen3DecodeArgs)]),
     "izb_gguf_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),

@@ -66,6 +66,29 @@ def dequantize(raw: torch.Tensor, fmt: str, n_elems: int, dtype: torch.dtype = t
     return out
 
 
+def dequantize_mlx_affine(packed: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor | None, out_dim: int, in_dim: int,
+                          dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """MLX affine-packed weight ([out_dim, packed_in] uint8, or int32 / uint32 words) -> dense [out_dim, in_dim]:
+    `load_weight` of models/shared/weights/mlx.rs on the device.  scales / biases fp32 [out_dim, groups] or
+    [groups, out_dim]."""
+    assert packed.is_cuda and packed.dim() == 2 and packed.is_contiguous() and packed.shape[0] == out_dim
+    word_bits = 8 if packed.dtype == torch.uint8 else 32
+    assert packed.dtype in (torch.uint8, torch.int32, torch.uint32)
+    assert scales.dtype == torch.float32 and scales.dim() == 2 and scales.is_contiguous()
+    transposed = scales.shape[0] != out_dim
+    groups = scales.shape[0] if transposed else scales.shape[1]
+    if transposed and scales.shape[1] != out_dim:
+        raise ValueError("quantization scales shape mismatch")
+    if biases is not None:
+        assert biases.dtype == torch.float32 and biases.shape == scales.shape and biases.is_contiguous()
+    out = torch.empty(out_dim, in_dim, device=packed.device, dtype=dtype)
+    ctx = Context.get(packed.device.index)
+    L.check(L.lib().izb_dequantize_mlx_affine(ctx.handle, _stream(), _ptr(packed), word_bits, packed.shape[1], _ptr(scales),
+                                              None if biases is None else _ptr(biases), groups, 1 if transposed else 0, out_dim, in_dim,
+                                              DTYPE[dtype], _ptr(out)), "izb_dequantize_mlx_affine")
+    return out
+
+
 EPILOGUE = {None: L.IZB_EPI_NONE, "none": L.IZB_EPI_NONE, "gelu": L.IZB_EPI_GELU, "silu": L.IZB_EPI_SILU,
             "swiglu": L.IZB_EPI_SWIGLU, "gelu_tanh": L.IZB_EPI_GELU_TANH, "glu": L.IZB_EPI_GLU}
 PROLOGUE = {None: 0, "none": 0, "rms_norm": 1, "silu_mul": 2}  # izb_prologue

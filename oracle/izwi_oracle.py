@@ -222,6 +222,57 @@ def quantize_q8_0(x: np.ndarray) -> np.ndarray:
     return out.reshape(-1)
 
 
+def dequantize_mlx_affine(packed: np.ndarray, scales: np.ndarray, biases, out_dim: int, in_dim: int) -> np.ndarray:
+    """MLX affine-packed weights -> dense fp32 [out_dim, in_dim] (models/shared/weights/mlx.rs:50-236).
+    `packed` is uint32 or uint8 [out_dim, packed_in]; pack = in_dim / packed_in values sit in one word,
+    bits = word_bits / pack each, value pi of a word at bit pi * bits.  `scales` / `biases` are
+    [out_dim, groups] or [groups, out_dim] (transposed back, mlx.rs:66-74); biases may be None (zeros).
+    value = q * scale + bias in fp32, the product and the sum rounded separately."""
+    packed = np.asarray(packed)
+    if packed.dtype not in (np.uint32, np.uint8) or packed.ndim != 2:
+        raise ValueError("packed weight must be a 2-D uint32 or uint8 array")
+    word_bits = 32 if packed.dtype == np.uint32 else 8
+    if packed.shape[0] != out_dim:
+        raise ValueError(f"quantized weight rows mismatch: expected out_dim={out_dim}, packed_rows={packed.shape[0]}")
+    packed_in = packed.shape[1]
+    if packed_in == 0 or in_dim == 0:
+        raise ValueError("invalid packed shape for quantized weight")
+    if in_dim % packed_in != 0:
+        raise ValueError(f"incompatible input dim: expected_in={in_dim}, packed_in={packed_in}")
+    pack = in_dim // packed_in
+    if word_bits % pack != 0:
+        raise ValueError(f"invalid quant packing factor: word_bits={word_bits}, pack_factor={pack}")
+    bits = word_bits // pack
+    if bits == 0 or bits > 8:
+        raise ValueError(f"unsupported quantization bit-width inferred from packing: {bits}")
+    scales = np.asarray(scales, dtype=np.float32)
+    if scales.ndim != 2 or scales.size == 0:
+        raise ValueError("empty quantization scales")
+    biases = None if biases is None else np.asarray(biases, dtype=np.float32)
+    if scales.shape[0] == out_dim:
+        groups = scales.shape[1]
+    elif scales.shape[1] == out_dim:
+        groups = scales.shape[0]
+        scales = scales.T
+        biases = None if biases is None else biases.T
+    else:
+        raise ValueError(f"quantization scales shape mismatch: expected out_dim={out_dim}, got {scales.shape}")
+    if groups == 0 or in_dim % groups != 0:
+        raise ValueError(f"invalid quantization groups: in_dim={in_dim}, groups={groups}")
+    if biases is None:
+        biases = np.zeros((out_dim, groups), dtype=np.float32)
+    elif biases.shape != (out_dim, groups):
+        raise ValueError(f"quantization biases shape mismatch: expected ({out_dim},{groups})")
+    group_size = in_dim // groups
+    mask = np.uint32((1 << bits) - 1)
+    words = packed.astype(np.uint32)
+    shifts = (np.arange(pack, dtype=np.uint32) * np.uint32(bits))[None, None, :]
+    q = ((words[:, :, None] >> shifts) & mask).reshape(out_dim, in_dim).astype(np.float32)
+    g = np.arange(in_dim) // group_size
+    prod = (q * scales[:, g]).astype(np.float32)
+    return (prod + biases[:, g]).astype(np.float32)
+
+
 def dequantize_q8_0(raw: np.ndarray) -> np.ndarray:
     """Q8_0: 34-byte blocks of (fp16 d, 32 x int8 q); value = d * q in fp32."""
     blocks = np.asarray(raw, dtype=np.uint8).reshape(-1, 34)

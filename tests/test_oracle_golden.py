@@ -197,3 +197,46 @@ def test_rms_norm_known_answer_and_residual():
 def test_argmax_rows_ties_and_nan():
     idx, val = o.argmax_rows(np.array([[1.0, 5.0, 5.0, np.nan], [np.nan, np.nan, np.nan, np.nan]]))
     assert list(idx) == [1, 0] and val[0] == 5.0 and val[1] == -np.inf
+
+
+# The known-answer tests of the reference's MLX-affine loader (models/shared/weights/mlx.rs:420-486), read as text.
+MLX_KNOWN = [
+    (np.array([[0x76543210]], dtype=np.uint32), [[0.1, 0.2]], [[-1.0, 0.5]], 1, 8,
+     [-1.0 + 0.0 * 0.1, -1.0 + 1.0 * 0.1, -1.0 + 2.0 * 0.1, -1.0 + 3.0 * 0.1, 0.5 + 4.0 * 0.2, 0.5 + 5.0 * 0.2, 0.5 + 6.0 * 0.2, 0.5 + 7.0 * 0.2]),
+    (np.array([[1, 2, 3, 4]], dtype=np.uint8), [[0.5, 2.0]], [[0.0, -1.0]], 1, 4, [0.5, 1.0, 5.0, 7.0]),
+    (np.array([[0x76543210]], dtype=np.uint32), [[0.1, 0.2]], None, 1, 8,
+     [0.0 * 0.1, 1.0 * 0.1, 2.0 * 0.1, 3.0 * 0.1, 4.0 * 0.2, 5.0 * 0.2, 6.0 * 0.2, 7.0 * 0.2]),
+    (np.array([[1, 2, 3, 4]], dtype=np.uint8), [[0.5, 2.0]], None, 1, 4, [0.5, 1.0, 6.0, 8.0]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(MLX_KNOWN)))
+def test_mlx_affine_known_answers(case):
+    import izwi_oracle as o
+    packed, scales, biases, out_dim, in_dim, want = MLX_KNOWN[case]
+    got = o.dequantize_mlx_affine(packed, np.array(scales, dtype=np.float32), None if biases is None else np.array(biases, dtype=np.float32),
+                                  out_dim, in_dim)
+    assert got.shape == (out_dim, in_dim) and got.dtype == np.float32
+    assert np.abs(got.reshape(-1) - np.array(want, dtype=np.float64)).max() < 1e-6  # the reference's own tolerance
+
+
+def test_mlx_affine_transposed_params_and_shape_rules():
+    import izwi_oracle as o
+    rng = np.random.default_rng(0)
+    out_dim, in_dim, groups = 6, 128, 4
+    packed = rng.integers(0, 2 ** 32, (out_dim, in_dim // 8), dtype=np.uint32)
+    sc, bi = rng.normal(0, 0.1, (out_dim, groups)).astype(np.float32), rng.normal(0, 1, (out_dim, groups)).astype(np.float32)
+    a = o.dequantize_mlx_affine(packed, sc, bi, out_dim, in_dim)
+    b = o.dequantize_mlx_affine(packed, np.ascontiguousarray(sc.T), np.ascontiguousarray(bi.T), out_dim, in_dim)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # element by element, as the reference's loops compute it
+    for r, c in ((0, 0), (3, 37), (5, 127)):
+        q = (int(packed[r, c // 8]) >> ((c % 8) * 4)) & 15
+        assert a[r, c] == np.float32(np.float32(q) * sc[r, c // 32]) + bi[r, c // 32]
+    for bad in (lambda: o.dequantize_mlx_affine(packed, sc, bi, out_dim + 1, in_dim),                # rows mismatch
+                lambda: o.dequantize_mlx_affine(packed, sc, bi, out_dim, in_dim + 8),                # in_dim % packed_in
+                lambda: o.dequantize_mlx_affine(packed, sc, bi, out_dim, 16 * 3),                    # word_bits % pack
+                lambda: o.dequantize_mlx_affine(packed, sc[:, :3], bi[:, :3], out_dim, in_dim),      # in_dim % groups
+                lambda: o.dequantize_mlx_affine(packed, sc, bi[:, :2], out_dim, in_dim)):            # biases shape
+        with pytest.raises(ValueError):
+            bad()
