@@ -273,7 +273,16 @@ class Qwen3Model {
         size_t need = 0;
         for (const Qwen3LayerWeights& w : layers_)
             for (const Qwen3Projection* p : {&w.qkv, &w.o, &w.gate_up, &w.down})
-                need = std::max(need, izb_linear_workspace_bytes_ex(p->wfmt(), tokens, p->out_dim(), p->in_dim(), IZB_EPI_NONE));
+            {
+                // the query that knows the whole call: the bf16 copy for the GEMM route, or (3..8 tokens over Q8_0)
+                // room for the activations as the integer tensor-core kernel reads them
+                izb_linear_args a{};
+                a.wfmt = p->wfmt();
+                a.M = tokens;
+                a.N = p->out_dim();
+                a.K = p->in_dim();
+                need = std::max(need, izb_linear_workspace_bytes_args(&a));
+            }
         return (need + 255) / 256 * 256;
     }
     // out = a + b over bf16 rows: the residual add after the MLP when no projection carries it.  Done by the
