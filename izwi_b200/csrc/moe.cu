@@ -6,6 +6,8 @@
 #include <cstring>
 
 #include "gemm_tc.cuh"
+#include <cstdlib>
+
 #include "izb_common.cuh"
 
 namespace izb {
@@ -144,6 +146,81 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32)
         if (tok < T)
             topk_row(logits + static_cast<long long>(tok) * E, lane, E, k,
                      idx + static_cast<long long>(tok) * k, wts + static_cast<long long>(tok) * k);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// A handful of tokens (decode): no permutation, no gather, no grouped GEMM.  Every (token, expert) pair
+// streams its expert's rows once with 16-byte loads (a warp per output, fp32 accumulation, one shuffle
+// reduction): two launches behind the router, HBM-bound on the 8 experts' 9.4 MB each instead of
+// launch-bound on six kernels.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float dot8(uint4 a, uint4 b, float acc) {
+    const uint32_t x[4] = {a.x, a.y, a.z, a.w}, y[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        acc = fmaf(izb::bf16_lo_to_f32(x[i]), izb::bf16_lo_to_f32(y[i]), acc);
+        acc = fmaf(izb::bf16_hi_to_f32(x[i]), izb::bf16_hi_to_f32(y[i]), acc);
+    }
+    return acc;
+}
+
+// hidden[p][i] = silu(gate_i . x_t) * (up_i . x_t) for pair p = (t, j), expert idx[p]; grid (outputs / 8, pairs)
+__global__ void __launch_bounds__(256)
+    moe_small_gate_up_kernel(const uint4* __restrict__ x, long long ldx_units, const int* __restrict__ idx,
+                             const uint4* __restrict__ w_gate_up, int h_units, int I, int top_k, __nv_bfloat16* __restrict__ hidden) {
+    extern __shared__ uint4 xs[];  // the token's row
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
+    const int p = blockIdx.y, t = p / top_k, e = idx[p];
+    for (int c = threadIdx.x; c < h_units; c += blockDim.x) xs[c] = x[static_cast<long long>(t) * ldx_units + c];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint4* base = w_gate_up + static_cast<long long>(e) * 2 * I * h_units;
+    for (int i = blockIdx.x * 8 + warp; i < I; i += gridDim.x * 8) {
+        const uint4* g = base + static_cast<long long>(i) * h_units;
+        const uint4* u = base + static_cast<long long>(I + i) * h_units;
+        float ag = 0.f, au = 0.f;
+#pragma unroll 8
+        for (int c = lane; c < h_units; c += 32) {  // sixteen 16-byte loads in flight per lane
+            const uint4 gv = g[c], uv = u[c], xv = xs[c];
+            ag = dot8(gv, xv, ag);
+            au = dot8(uv, xv, au);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ag += __shfl_xor_sync(0xFFFFFFFFu, ag, o);
+            au += __shfl_xor_sync(0xFFFFFFFFu, au, o);
+        }
+        if (lane == 0) hidden[static_cast<long long>(p) * I + i] = __float2bfloat16_rn(ag / (1.0f + __expf(-ag)) * au);
+    }
+}
+
+// y[t][n] = sum_j wts[t][j] * (down_{e_j}[n] . hidden[t][j]); grid (outputs / 8, tokens)
+__global__ void __launch_bounds__(256)
+    moe_small_down_kernel(const uint4* __restrict__ hidden, const int* __restrict__ idx, const float* __restrict__ wts,
+                          const uint4* __restrict__ w_down, int H, int i_units, int top_k, __nv_bfloat16* __restrict__ y) {
+    extern __shared__ uint4 hs[];  // [top_k][i_units]
+    izb::pdl_launch_dependents();
+    izb::pdl_wait();
+    const int t = blockIdx.y;
+    for (int c = threadIdx.x; c < top_k * i_units; c += blockDim.x) hs[c] = hidden[static_cast<long long>(t) * top_k * i_units + c];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int n = blockIdx.x * 8 + warp; n < H; n += gridDim.x * 8) {
+        float out = 0.f;
+#pragma unroll 8
+        for (int j = 0; j < top_k; ++j) {  // the rows of all the token's experts are asked for together
+            const int e = idx[t * top_k + j];
+            const uint4* row = w_down + (static_cast<long long>(e) * H + n) * i_units;
+            float acc = 0.f;
+#pragma unroll 4
+            for (int c = lane; c < i_units; c += 32) acc = dot8(row[c], hs[j * i_units + c], acc);
+            out = fmaf(wts[t * top_k + j], acc, out);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) out += __shfl_xor_sync(0xFFFFFFFFu, out, o);
+        if (lane == 0) y[static_cast<long long>(t) * H + n] = __float2bfloat16_rn(out);
     }
 }
 
@@ -394,6 +471,18 @@ MoeWorkspace moe_layout(int64_t T, int64_t H, int64_t I, int64_t E, int64_t k) {
     w.total = at;
     return w;
 }
+// The pair-streaming path reads an expert's weights once per pair routed to it: right for a few decode tokens
+// (IZB_MOE_SMALL_MAX_PAIRS, default 32 = four tokens at top-8), wrong as soon as experts repeat.
+bool moe_small_path(const izb_ctx* ctx, const izb_moe_args* a, int64_t pairs) {
+    static const int max_pairs = [] {
+        const char* e = std::getenv("IZB_MOE_SMALL_MAX_PAIRS");
+        return e ? std::atoi(e) : 32;
+    }();
+    if (pairs > max_pairs) return false;
+    if (a->H % 8 != 0 || a->I % 8 != 0) return false;
+    if (!izb_aligned(a->x, 16) || !izb_aligned(a->w_gate_up, 16) || !izb_aligned(a->w_down, 16) || !izb_aligned(a->y, 2)) return false;
+    return a->H * 2 <= 48 * 1024 && static_cast<int64_t>(a->top_k) * a->I * 2 <= 48 * 1024 && ctx != nullptr;
+}
 }  // namespace
 
 extern "C" {
@@ -416,6 +505,23 @@ int32_t izb_moe_forward(izb_ctx* ctx, izb_stream stream, const izb_moe_args* a) 
     int rc = izb_moe_route(ctx, stream, a->x, a->H, a->w_router, a->router_bias, a->T, a->H, a->E, a->top_k, ws + L.logits,
                            ws + L.idx, ws + L.wts);
     if (rc != IZB_OK) return rc;
+    if (moe_small_path(ctx, a, pairs)) {
+        // a handful of tokens: every pair streams its expert's rows (two launches behind the router)
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        const int h_units = static_cast<int>(a->H / 8), i_units = static_cast<int>(a->I / 8);
+        const int gx = static_cast<int>((a->I + 7) / 8), dx = static_cast<int>((a->H + 7) / 8);
+        IZB_CUDA_TRY(izb::launch_chained(ctx, moe_small_gate_up_kernel, dim3(gx, static_cast<unsigned>(pairs)), dim3(256),
+                                         static_cast<size_t>(a->H) * 2, s, static_cast<const uint4*>(a->x), static_cast<long long>(h_units),
+                                         reinterpret_cast<const int*>(ws + L.idx), static_cast<const uint4*>(a->w_gate_up), h_units,
+                                         static_cast<int>(a->I), a->top_k, reinterpret_cast<__nv_bfloat16*>(ws + L.hidden)));
+        IZB_CUDA_TRY(izb::launch_chained(ctx, moe_small_down_kernel, dim3(dx, static_cast<unsigned>(a->T)), dim3(256),
+                                         static_cast<size_t>(a->top_k) * a->I * 2, s, reinterpret_cast<const uint4*>(ws + L.hidden),
+                                         reinterpret_cast<const int*>(ws + L.idx), reinterpret_cast<const float*>(ws + L.wts),
+                                         static_cast<const uint4*>(a->w_down), static_cast<int>(a->H), i_units, a->top_k,
+                                         static_cast<__nv_bfloat16*>(a->y)));
+        ctx->launches.fetch_add(2, std::memory_order_relaxed);
+        return IZB_OK;
+    }
     rc = izb_moe_permute(ctx, stream, ws + L.idx, pairs, a->E, ws + L.offsets, ws + L.perm, ws + L.inv);
     if (rc != IZB_OK) return rc;
     rc = izb_moe_gather(ctx, stream, a->x, a->H, ws + L.perm, a->top_k, pairs, a->H, ws + L.x_perm);

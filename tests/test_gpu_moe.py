@@ -93,9 +93,10 @@ def test_grouped_gemm_matches_per_expert_oracle(cuda, rows_per_expert, epilogue)
     assert_matmul_close(got, want, f"grouped {rows_per_expert} {epilogue}")
 
 
-@pytest.mark.parametrize("t", [1, 64, 300])
+@pytest.mark.parametrize("t", [1, 2, 4, 5, 64, 300])
 def test_moe_layer_matches_oracle(cuda, t):
-    """Whole layer at the Qwen3-30B-A3B expert shape with fewer experts (H 2048, I 768, top-8 of 32)."""
+    """Whole layer at the Qwen3-30B-A3B expert shape with fewer experts (H 2048, I 768, top-8 of 32).  Up to four
+    tokens take the pair-streaming path (two launches behind the router), more the permute / grouped-GEMM path."""
     from izwi_b200 import moe, ops
     rng = np.random.default_rng(50 + t)
     h, i, e, k = 2048, 768, 32, 8
