@@ -412,34 +412,70 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
                 vw[u] = *reinterpret_cast<const uint2*>(vc + static_cast<size_t>(t) * DT_D + lane * 4);
             }
         }
+        // the trip's scores first (independent chains), one running-max step for the trip, then the values
+        float sc[DT_MAX_GQ][PT];
 #pragma unroll
         for (int u = 0; u < PT; ++u) {
             const int t = tb + u * DT_CONSUMER_WARPS;
-            if (t >= t1) break;
-            float kv[4], vv[4];
+            float kv[4];
             if (t == A.pos) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    kv[j] = knew[lane * 4 + j];
-                    vv[j] = vnew[lane * 4 + j];
-                }
+                for (int j = 0; j < 4; ++j) kv[j] = knew[lane * 4 + j];
             } else {
                 kv[0] = bf16_lo_to_f32(kw[u].x); kv[1] = bf16_hi_to_f32(kw[u].x); kv[2] = bf16_lo_to_f32(kw[u].y); kv[3] = bf16_hi_to_f32(kw[u].y);
+            }
+#pragma unroll
+            for (int g = 0; g < DT_MAX_GQ; ++g) {
+                float d = 0.f;
+                if (g < gq) d = q[g][0] * kv[0] + q[g][1] * kv[1] + q[g][2] * kv[2] + q[g][3] * kv[3];
+                sc[g][u] = d;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int g = 0; g < DT_MAX_GQ; ++g) {
+                if (g >= gq) break;
+#pragma unroll
+                for (int u = 0; u < PT; ++u) sc[g][u] += __shfl_xor_sync(0xFFFFFFFFu, sc[g][u], o);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < DT_MAX_GQ; ++g) {
+            if (g >= gq) break;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < PT; ++u) {
+                sc[g][u] = tb + u * DT_CONSUMER_WARPS < t1 ? sc[g][u] * scale : -INFINITY;
+                mx = fmaxf(mx, sc[g][u]);
+            }
+            const float m_new = fmaxf(m[g], mx);   // finite: position tb is valid
+            const float a = __expf(m[g] - m_new);  // first trip: exp(-inf) = 0
+            m[g] = m_new;
+            l[g] *= a;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[g][j] *= a;
+#pragma unroll
+            for (int u = 0; u < PT; ++u) {
+                sc[g][u] = __expf(sc[g][u] - m_new);  // past the end: exp(-inf) = 0
+                l[g] += sc[g][u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PT; ++u) {
+            const int t = tb + u * DT_CONSUMER_WARPS;
+            float vv[4];
+            if (t == A.pos) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) vv[j] = vnew[lane * 4 + j];
+            } else {
                 vv[0] = bf16_lo_to_f32(vw[u].x); vv[1] = bf16_hi_to_f32(vw[u].x); vv[2] = bf16_lo_to_f32(vw[u].y); vv[3] = bf16_hi_to_f32(vw[u].y);
             }
 #pragma unroll
             for (int g = 0; g < DT_MAX_GQ; ++g) {
                 if (g >= gq) break;
-                float sc = q[g][0] * kv[0] + q[g][1] * kv[1] + q[g][2] * kv[2] + q[g][3] * kv[3];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xFFFFFFFFu, sc, o);
-                sc *= scale;
-                const float m_new = fmaxf(m[g], sc);
-                const float a = __expf(m[g] - m_new), p = __expf(sc - m_new);  // first position: exp(-inf) = 0
-                l[g] = l[g] * a + p;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(p, vv[j], acc[g][j] * a);
-                m[g] = m_new;
+                for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(sc[g][u], vv[j], acc[g][j]);
             }
         }
     }
