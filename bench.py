@@ -508,7 +508,7 @@ def measure_attention_cases(device):
     return out
 
 
-def measure_decode_token_cases(device):
+def measure_decode_token_cases(device, shape=None, variants=None):
     """A whole greedy decode token of a Qwen3-0.6B-shaped model with Q8_0 projections (embedding, 28
     layers of norm / fused QKV / q,k norm / RoPE / KV append / GQA attention / O / norm / gate-up /
     SiLU-multiply / down, final norm, lm_head over 151,936 tokens, arg-max), captured once in a CUDA
@@ -517,7 +517,11 @@ def measure_decode_token_cases(device):
     from izwi_b200 import decoder, ops
     from izwi_b200 import workloads as wl
     peak_bw, _ = load_peaks()
-    shape = wl.QWEN3_0_6B
+    if shape is None:
+        # the 0.6B shape (launch- and latency-bound: 0.64 GB of weights per token) and, for the one-launch kernel and
+        # the fused chain, the 8B shape (8.7 GB per token: bandwidth starts to matter)
+        return (measure_decode_token_cases(device, wl.QWEN3_0_6B, ((512, "one_launch"), (4096, "one_launch"), (512, True), (4096, True), (512, False)))
+                + measure_decode_token_cases(device, wl.QWEN3_8B, ((512, "one_launch"), (512, True))))
     gen = torch.Generator(device=device).manual_seed(6)
     vocab, hid, qd, kd = 151936, shape.hidden, shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
     ones = lambda n: (1.0 + 0.1 * torch.randn(n, device=device, generator=gen)).to(torch.bfloat16)  # noqa: E731
@@ -532,7 +536,7 @@ def measure_decode_token_cases(device):
     model = decoder.Qwen3Decoder(embed, layers, ones(hid), wl.make_q8_0_weight(vocab, hid, gen), "q8_0")
     weight_bytes = sum(w.numel() for l in layers for w in (l.w.qkv, l.w.o, l.w.gate_up, l.w.down)) + model.lm_head.numel()
     out = []
-    for ctx_len, fused in ((512, "one_launch"), (4096, "one_launch"), (512, True), (4096, True), (512, False)):
+    for ctx_len, fused in variants:
         # fused: norms, SiLU-multiply and residual adds ride inside the one-token projections;
         # "one_launch": the whole token in one cooperative launch (izb_qwen3_decode_token)
         one_launch = fused == "one_launch"
@@ -568,7 +572,7 @@ def measure_decode_token_cases(device):
         ops.Context.get(device.index).check()
         kv_bytes = shape.layers * 2 * shape.kv_heads * (ctx_len + 1) * shape.head_dim * 2
         gbs = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
-        out.append({"workload": f"qwen3-0.6b-q8_0-greedy-token-ctx{ctx_len}", "ms_per_token": round(ms, 4),
+        out.append({"workload": f"{shape.name}-q8_0-greedy-token-ctx{ctx_len}", "ms_per_token": round(ms, 4),
                     "tokens_per_s": round(1e3 / ms, 1), "kernels_per_token": int(launches), "fused_projections": fused,
                     "weight_and_kv_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak_bw, 4),
                     "next_token": int(nxt[0])})
