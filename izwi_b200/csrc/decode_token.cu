@@ -14,9 +14,11 @@
 // barrier the consumers find their weights already on chip and the time of a phase is the barrier plus
 // reading a few kilobytes of activations from L2, every load of which is asked for before the first is used.
 //
-// Work split of a projection [N, K]: units = (64-row tile, k slice); slices S per phase chosen by the
-// host so that the units cover the SMs; unit u goes to CTA u mod G.  A unit writes 64 fp32 partial sums
-// to part[slice][row]; the consumers of the NEXT phase add the S slices (fixed order: results do not
+// Work split of a projection [N, K]: units = (64-row tile, range of 256-k boxes).  A small projection is cut
+// into S k slices per tile so that the units cover the SMs, unit u to CTA u mod G; a large one (four or
+// more boxes per CTA) is dealt as contiguous box ranges, so that every CTA streams the same bytes to within
+// one box (DtSplit).  A unit writes 64 fp32 partial sums
+// to part[slice][row]; the consumers of the NEXT phase add the tile's slices (fixed order: results do not
 // depend on timing), apply what sits between the two projections (residual add and bf16 rounding of the
 // stream, RmsNorm, SiLU-multiply, the merge of the attention splits) and convert to the 16-bit block
 // fixed point that the integer dot products read (gemv_dot.cuh).
@@ -25,6 +27,7 @@
 // the workspace's abort word (which every other wait also watches) and a context status word, and
 // the CTA leaves.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "gemv_dot.cuh"
@@ -47,15 +50,26 @@ constexpr int DT_MAX_LAYERS = 48;   // layer pointers and tensor maps travel as 
 constexpr int DT_MAX_SPLITS = 16;
 constexpr int DT_REC = DT_D + 4;     // floats of one attention partial in global memory: D sums, max, sum of weights, padding to 16 bytes
 
+// How the (64-row tile, 256-k box) units of one projection are dealt to the CTAs.
+//   round robin: S slices per tile of boxes / S boxes each, unit u = (tile, slice) to CTA u mod G: the few units of a
+//   small projection land on different SMs.
+//   contiguous (host picks it once every CTA gets four or more units): CTA c walks units [c U / G, (c + 1) U / G) in
+//   (tile, box) order, so every CTA streams the same number of boxes to within one; a tile cut by a CTA boundary is
+//   written as two or more partial sums (slots), S = the most slots a tile can have.
+struct DtSplit {
+    int tiles, boxes, S, contiguous;
+};
+
 struct DtParams {
     izb_qwen3_decode_args a;
-    int s_qkv, s_o, s_gu, s_down, att_splits;
+    DtSplit sp_qkv, sp_o, sp_gu, sp_down, sp_lm;
+    int att_splits;
     int n_slots;
     // workspace carve-up
-    float* part_qkv;   // [s_qkv][q_dim + 2 kv_dim]
-    float* part_o;     // [s_o][hidden]
-    float* part_gu;    // [s_gu][2 I]
-    float* part_down;  // [s_down][hidden]
+    float* part_qkv;   // [sp_qkv.S][q_dim + 2 kv_dim]
+    float* part_o;     // [sp_o.S][hidden]
+    float* part_gu;    // [sp_gu.S][2 I]
+    float* part_down;  // [sp_down.S][hidden]
     float* att_part;   // [heads][att_splits][DT_REC]
     float* stream_a;   // [hidden] the layer's input stream (bf16 values)
     float* stream_b;   // [hidden] the stream behind the attention block
@@ -137,18 +151,57 @@ __device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, un
     return *reinterpret_cast<volatile int*>(&sh.abort_flag) == 0;
 }
 
-// Units of a projection phase for this CTA: u = cta, cta + G, ...; unit -> (tile, slice) -> boxes [b0, b1).
+// Units of a projection phase for one CTA, in the order both the producer and the consumers walk them.
 struct DtUnit {
-    int tile, slice, b0, b1;
+    int tile, slice, b0, b1;  // rows 64 tile .., boxes [b0, b1); `slice` = which partial sum of the tile this is
 };
-__device__ __forceinline__ DtUnit dt_unit(int u, int S, int boxes) {
-    DtUnit r;
-    r.tile = u / S;
-    r.slice = u - r.tile * S;
-    r.b0 = r.slice * boxes / S;
-    r.b1 = (r.slice + 1) * boxes / S;
-    return r;
+// tiles * boxes * G stays below 2^31 in contiguous mode (the host checks), so this is 32-bit arithmetic.
+__host__ __device__ __forceinline__ int dt_start(const DtSplit& sp, int c, int G) {
+    return static_cast<int>(static_cast<unsigned>(c) * static_cast<unsigned>(sp.tiles * sp.boxes) / static_cast<unsigned>(G));
 }
+// The CTA whose contiguous range holds unit u.
+__host__ __device__ __forceinline__ int dt_cta_of(const DtSplit& sp, int u, int G) {
+    int c = static_cast<int>(static_cast<unsigned>(u) * static_cast<unsigned>(G) / static_cast<unsigned>(sp.tiles * sp.boxes));  // start(c) <= u
+    while (dt_start(sp, c + 1, G) <= u) ++c;
+    return c;
+}
+// Partial sums (slices or slots) the next phase adds up for the rows of `tile`.
+__host__ __device__ __forceinline__ int dt_slots(const DtSplit& sp, int tile, int G) {
+    if (!sp.contiguous) return sp.S;
+    const int u0 = tile * sp.boxes;
+    return dt_cta_of(sp, u0 + sp.boxes - 1, G) - dt_cta_of(sp, u0, G) + 1;
+}
+struct DtWalk {
+    DtSplit sp;
+    int G, cta;
+    int u, end;  // contiguous: next unit and end of the range; round robin: next (tile, slice) index (step G) and their count
+    __device__ __forceinline__ DtWalk(const DtSplit& split, int cta_, int G_) : sp(split), G(G_), cta(cta_) {
+        if (sp.contiguous) {
+            u = dt_start(sp, cta, G);
+            end = dt_start(sp, cta + 1, G);
+        } else {
+            u = cta;
+            end = sp.tiles * sp.S;
+        }
+    }
+    __device__ __forceinline__ bool next(DtUnit& un) {
+        if (u >= end) return false;
+        if (sp.contiguous) {
+            un.tile = u / sp.boxes;
+            un.b0 = u - un.tile * sp.boxes;
+            un.b1 = min(sp.boxes, un.b0 + (end - u));
+            un.slice = cta - dt_cta_of(sp, un.tile * sp.boxes, G);
+            u += un.b1 - un.b0;
+        } else {
+            un.tile = u / sp.S;
+            un.slice = u - un.tile * sp.S;
+            un.b0 = un.slice * sp.boxes / sp.S;
+            un.b1 = (un.slice + 1) * sp.boxes / sp.S;
+            u += G;
+        }
+        return true;
+    }
+};
 
 // ---------------------------------------------------------------------------------------------
 // Producer warp: the weight boxes of this CTA's units of one projection, in unit order.
@@ -159,12 +212,12 @@ struct DtRing {
     long long issued;
 };
 
-__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const CUtensorMap* map, int N, int K,
-                                              int S, int w_row_bytes) {
-    const int boxes = K / 256, tiles = N / DT_TILE_ROWS, units = tiles * S;
+__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const CUtensorMap* map,
+                                              const DtSplit& sp, int w_row_bytes) {
     volatile int* abort_flag = &sh.abort_flag;
-    for (int u = static_cast<int>(blockIdx.x); u < units; u += static_cast<int>(gridDim.x)) {
-        const DtUnit un = dt_unit(u, S, boxes);
+    DtWalk walk(sp, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+    DtUnit un;
+    while (walk.next(un)) {
         for (int b = un.b0; b < un.b1; ++b) {
             if (R.issued >= P.n_slots && !mbar_wait_bounded_relaxed(smem_u32(&sh.empty[R.slot]), R.phase ^ 1u, abort_flag)) return false;
             const uint32_t fbar = smem_u32(&sh.full[R.slot]);
@@ -231,7 +284,8 @@ __device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, ui
 // in slice order.  The loads of CH slices are issued before the first add: it is the number of L2 round
 // trips, not of loads, that a phase pays for.
 template <int CH>
-__device__ __forceinline__ float4 part_sum4(const float* part, int S, int n, int i0) {
+__device__ __forceinline__ float4 part_sum4(const float* part, const DtSplit& sp, int n, int i0) {
+    const int S = dt_slots(sp, i0 / DT_TILE_ROWS, static_cast<int>(gridDim.x));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < S; s0 += CH) {
         float4 t[CH];
@@ -269,9 +323,9 @@ __device__ __forceinline__ void stage_stream(DtShared& sh, float* xf, int hidden
 }
 
 // stream + the k slices of the projection behind it, rounded to bf16 as the reference stores the stream
-__device__ __forceinline__ float4 stream_plus(const float* stream, const float* part, int S, int n, int i0) {
+__device__ __forceinline__ float4 stream_plus(const float* stream, const float* part, const DtSplit& sp, int n, int i0) {
     const float4 r = __ldcg(reinterpret_cast<const float4*>(stream + i0));
-    const float4 p = part_sum4<8>(part, S, n, i0);
+    const float4 p = part_sum4<8>(part, sp, n, i0);
     return make_float4(bf16r(r.x + p.x), bf16r(r.y + p.y), bf16r(r.z + p.z), bf16r(r.w + p.w));
 }
 
@@ -353,7 +407,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
             cv = __ldg(reinterpret_cast<const uint2*>(cosv + jh));
             sv = __ldg(reinterpret_cast<const uint2*>(sinv + jh));
         }
-        const float4 xs = part_sum4<4>(P.part_qkv, P.s_qkv, n_qkv, col0 + lane * 4);
+        const float4 xs = part_sum4<4>(P.part_qkv, P.sp_qkv, n_qkv, col0 + lane * 4);
         float x[4] = {bf16r(xs.x), bf16r(xs.y), bf16r(xs.z), bf16r(xs.w)};  // the QKV output as stored
         if (warp <= gq) {
             if (w) {
@@ -552,12 +606,12 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         bool ok = true;
         for (int l = 0; l < A.n_layers && ok; ++l) {
             const CUtensorMap* m = P.maps + 4 * l;
-            ok = produce_phase(P, sh, ring0, R, m + 0, n_qkv, A.hidden, P.s_qkv, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 1, A.hidden, q_dim, P.s_o, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 2, 2 * A.intermediate, A.hidden, P.s_gu, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 3, A.hidden, A.intermediate, P.s_down, w_row);
+            ok = produce_phase(P, sh, ring0, R, m + 0, P.sp_qkv, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 1, P.sp_o, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 2, P.sp_gu, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 3, P.sp_down, w_row);
         }
-        if (ok) ok = produce_phase(P, sh, ring0, R, P.maps + 4 * A.n_layers, A.vocab, A.hidden, 1, lm_row);
+        if (ok) ok = produce_phase(P, sh, ring0, R, P.maps + 4 * A.n_layers, P.sp_lm, lm_row);
         // the copies still in flight land before the CTA's shared memory goes away
         {
             const long long first = R.issued > P.n_slots ? R.issued - P.n_slots : 0;
@@ -594,7 +648,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         const izb_qwen3_layer_ptrs& Lp = P.layers[l];
         // ===== QKV: stream = previous stream + down partials (layer 0: the embedding row); input norm =====
         {
-            const int boxes = A.hidden / 256, units = (n_qkv / DT_TILE_ROWS) * P.s_qkv;
+            const int boxes = A.hidden / 256;
             const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(Lp.input_norm), boxes);
             if (l == 0)
                 stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) {
@@ -602,12 +656,13 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
                     return make_float4(bf16_lo_to_f32(w.x), bf16_hi_to_f32(w.x), bf16_lo_to_f32(w.y), bf16_hi_to_f32(w.y));
                 });
             else
-                stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.s_down, A.hidden, i0); });
+                stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.sp_down, A.hidden, i0); });
             if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_a[i] = xf[i];
             convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
             consumer_sync();
-            for (int u = cta; u < units; u += G) {
-                const DtUnit un = dt_unit(u, P.s_qkv, boxes);
+            DtWalk walk(P.sp_qkv, cta, G);
+            DtUnit un;
+            while (walk.next(un)) {
                 float y;
                 ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
                 if (tid < 64) P.part_qkv[static_cast<size_t>(un.slice) * n_qkv + un.tile * DT_TILE_ROWS + tid] = y;
@@ -631,9 +686,9 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         // ===== O projection over the merged attention output =====
         {
             unsigned long long done = 0;
-            const int boxes = q_dim / 256, units = (A.hidden / DT_TILE_ROWS) * P.s_o;
-            for (int u = cta; u < units; u += G) {
-                const DtUnit un = dt_unit(u, P.s_o, boxes);
+            DtWalk walk(P.sp_o, cta, G);
+            DtUnit un;
+            while (walk.next(un)) {
                 convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
                     // merge of the splits' (max, sum of weights, weighted values) for this lane's 8 values of one head;
                     // the records of the first eight splits and all the (max, sum) pairs are asked for in one go
@@ -694,14 +749,15 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         if (!ok) break;
         // ===== gate / up: stream += O partials; post-attention norm =====
         {
-            const int boxes = A.hidden / 256, units = (2 * A.intermediate / DT_TILE_ROWS) * P.s_gu;
+            const int boxes = A.hidden / 256;
             const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(Lp.post_norm), boxes);
-            stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_a, P.part_o, P.s_o, A.hidden, i0); });
+            stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_a, P.part_o, P.sp_o, A.hidden, i0); });
             if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_b[i] = xf[i];
             convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
             consumer_sync();
-            for (int u = cta; u < units; u += G) {
-                const DtUnit un = dt_unit(u, P.s_gu, boxes);
+            DtWalk walk(P.sp_gu, cta, G);
+            DtUnit un;
+            while (walk.next(un)) {
                 float y;
                 ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
                 if (tid < 64) P.part_gu[static_cast<size_t>(un.slice) * 2 * A.intermediate + un.tile * DT_TILE_ROWS + tid] = y;
@@ -712,14 +768,14 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         // ===== down over silu(gate) * up =====
         {
             unsigned long long done = 0;
-            const int boxes = A.intermediate / 256, units = (A.hidden / DT_TILE_ROWS) * P.s_down;
             const int n_gu = 2 * A.intermediate;
-            for (int u = cta; u < units; u += G) {
-                const DtUnit un = dt_unit(u, P.s_down, boxes);
+            DtWalk walk(P.sp_down, cta, G);
+            DtUnit un;
+            while (walk.next(un)) {
                 convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
-                    const float4 g0 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, k0), g1 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, k0 + 4);
-                    const float4 u0 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, A.intermediate + k0);
-                    const float4 u1 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, A.intermediate + k0 + 4);
+                    const float4 g0 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, k0), g1 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, k0 + 4);
+                    const float4 u0 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, A.intermediate + k0);
+                    const float4 u1 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, A.intermediate + k0 + 4);
                     const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
                     const float us[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
@@ -740,13 +796,14 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
     // ===== final norm, lm_head, arg-max =====
     unsigned long long best = 0;
     if (ok) {
-        const int boxes = A.hidden / 256, units = A.vocab / DT_TILE_ROWS;
+        const int boxes = A.hidden / 256;
         const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(A.final_norm), boxes);
-        stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.s_down, A.hidden, i0); });
+        stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.sp_down, A.hidden, i0); });
         convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
         consumer_sync();
-        for (int u = cta; u < units; u += G) {
-            const DtUnit un = dt_unit(u, 1, boxes);
+        DtWalk walk(P.sp_lm, cta, G);
+        DtUnit un;
+        while (walk.next(un)) {
             float y;
             ok = consume_unit<LM_FMT>(P, sh, ring0, xq0, R, un, y) && ok;
             if (tid < 64) {
@@ -812,6 +869,23 @@ int pick_slices(int tiles, int boxes, int G) {
     return best_s;
 }
 
+// The dealing of one projection's units: contiguous ranges once every CTA gets `IZB_TOKEN_CONTIGUOUS_MIN` (default 4;
+// 0 = never) or more (tile, box) units, where an uneven count of round-robin units costs more than the extra partial
+// sums of the cut tiles; S = the most partial sums a tile can have (the workspace is laid out for it).
+DtSplit dt_split(int tiles, int boxes, int G) {
+    DtSplit sp{tiles, boxes, 1, 0};
+    const char* e = std::getenv("IZB_TOKEN_CONTIGUOUS_MIN");
+    const int min_units = (e && *e) ? std::atoi(e) : 4;
+    const long long U = static_cast<long long>(tiles) * boxes;
+    if (min_units > 0 && U >= static_cast<long long>(min_units) * G && U * (G + 1) < (1ll << 31)) {
+        sp.contiguous = 1;
+        for (int t = 0; t < tiles; ++t) sp.S = std::max(sp.S, dt_slots(sp, t, G));
+    } else {
+        sp.S = pick_slices(tiles, boxes, G);
+    }
+    return sp;
+}
+
 struct DtLayout {
     size_t part_qkv, part_o, part_gu, part_down, att_part, stream_a, stream_b, best, counter, total;
 };
@@ -845,10 +919,11 @@ int dt_weight_map(CUtensorMap* out, const void* w, int fmt, int N, int K) {
 void dt_plan(const izb_ctx* ctx, const izb_qwen3_decode_args* a, DtParams* p, DtLayout* lay) {
     const int G = ctx->sm_count;
     const int q_dim = a->heads * DT_D, kv_dim = a->kv_heads * DT_D, n_qkv = q_dim + 2 * kv_dim;
-    p->s_qkv = pick_slices(n_qkv / DT_TILE_ROWS, a->hidden / 256, G);
-    p->s_o = pick_slices(a->hidden / DT_TILE_ROWS, q_dim / 256, G);
-    p->s_gu = pick_slices(2 * a->intermediate / DT_TILE_ROWS, a->hidden / 256, G);
-    p->s_down = pick_slices(a->hidden / DT_TILE_ROWS, a->intermediate / 256, G);
+    p->sp_qkv = dt_split(n_qkv / DT_TILE_ROWS, a->hidden / 256, G);
+    p->sp_o = dt_split(a->hidden / DT_TILE_ROWS, q_dim / 256, G);
+    p->sp_gu = dt_split(2 * a->intermediate / DT_TILE_ROWS, a->hidden / 256, G);
+    p->sp_down = dt_split(a->hidden / DT_TILE_ROWS, a->intermediate / 256, G);
+    p->sp_lm = DtSplit{a->vocab / DT_TILE_ROWS, a->hidden / 256, 1, 0};  // a logit is one unit's sum: whole rows, round robin
     // splits of the cache per KV head: 64 positions each while eight splits cover the context (one trip for the
     // merge), 256 each beyond; the workspace is laid out for the most there can be
     const int max_splits = std::max(1, std::min(DT_MAX_SPLITS, G / a->kv_heads));
@@ -857,10 +932,10 @@ void dt_plan(const izb_ctx* ctx, const izb_qwen3_decode_args* a, DtParams* p, Dt
     p->att_splits = std::max(1, std::min(max_splits, want));
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t at = off; off += al256(bytes); return at; };
-    lay->part_qkv = take(sizeof(float) * p->s_qkv * n_qkv);
-    lay->part_o = take(sizeof(float) * p->s_o * a->hidden);
-    lay->part_gu = take(sizeof(float) * p->s_gu * 2 * a->intermediate);
-    lay->part_down = take(sizeof(float) * p->s_down * a->hidden);
+    lay->part_qkv = take(sizeof(float) * p->sp_qkv.S * n_qkv);
+    lay->part_o = take(sizeof(float) * p->sp_o.S * a->hidden);
+    lay->part_gu = take(sizeof(float) * p->sp_gu.S * 2 * a->intermediate);
+    lay->part_down = take(sizeof(float) * p->sp_down.S * a->hidden);
     lay->att_part = take(sizeof(float) * a->heads * max_splits * DT_REC);
     lay->stream_a = take(sizeof(float) * a->hidden);
     lay->stream_b = take(sizeof(float) * a->hidden);
