@@ -14,11 +14,9 @@
 // barrier the consumers find their weights already on chip and the time of a phase is the barrier plus
 // reading a few kilobytes of activations from L2, every load of which is asked for before the first is used.
 //
-// Work split of a projection [N, K]: units = (64-row tile, range of 256-k boxes).  A small projection is cut
-// into S k slices per tile so that the units cover the SMs, unit u to CTA u mod G; a large one (four or
-// more boxes per CTA) is dealt as contiguous box ranges, so that every CTA streams the same bytes to within
-// one box (DtSplit).  A unit writes 64 fp32 partial sums
-// to part[slice][row]; the consumers of the NEXT phase add the tile's slices (fixed order: results do not
+// Work split of a projection [N, K]: units = (64-row tile, k slice); slices S per phase chosen by the
+// host so that the units cover the SMs; unit u goes to CTA u mod G.  A unit writes 64 fp32 partial sums
+// to part[slice][row]; the consumers of the NEXT phase add the S slices (fixed order: results do not
 // depend on timing), apply what sits between the two projections (residual add and bf16 rounding of the
 // stream, RmsNorm, SiLU-multiply, the merge of the attention splits) and convert to the 16-bit block
 // fixed point that the integer dot products read (gemv_dot.cuh).
@@ -27,7 +25,7 @@
 // the workspace's abort word (which every other wait also watches) and a context status word, and
 // the CTA leaves.
 #include <algorithm>
-#include <cstdlib>
+#include <cstddef>
 #include <cstring>
 
 #include "gemv_dot.cuh"
@@ -50,26 +48,15 @@ constexpr int DT_MAX_LAYERS = 48;   // layer pointers and tensor maps travel as 
 constexpr int DT_MAX_SPLITS = 16;
 constexpr int DT_REC = DT_D + 4;     // floats of one attention partial in global memory: D sums, max, sum of weights, padding to 16 bytes
 
-// How the (64-row tile, 256-k box) units of one projection are dealt to the CTAs.
-//   round robin: S slices per tile of boxes / S boxes each, unit u = (tile, slice) to CTA u mod G: the few units of a
-//   small projection land on different SMs.
-//   contiguous (host picks it once every CTA gets four or more units): CTA c walks units [c U / G, (c + 1) U / G) in
-//   (tile, box) order, so every CTA streams the same number of boxes to within one; a tile cut by a CTA boundary is
-//   written as two or more partial sums (slots), S = the most slots a tile can have.
-struct DtSplit {
-    int tiles, boxes, S, contiguous;
-};
-
 struct DtParams {
     izb_qwen3_decode_args a;
-    DtSplit sp_qkv, sp_o, sp_gu, sp_down, sp_lm;
-    int att_splits;
+    int s_qkv, s_o, s_gu, s_down, att_splits;
     int n_slots;
     // workspace carve-up
-    float* part_qkv;   // [sp_qkv.S][q_dim + 2 kv_dim]
-    float* part_o;     // [sp_o.S][hidden]
-    float* part_gu;    // [sp_gu.S][2 I]
-    float* part_down;  // [sp_down.S][hidden]
+    float* part_qkv;   // [s_qkv][q_dim + 2 kv_dim]
+    float* part_o;     // [s_o][hidden]
+    float* part_gu;    // [s_gu][2 I]
+    float* part_down;  // [s_down][hidden]
     float* att_part;   // [heads][att_splits][DT_REC]
     float* stream_a;   // [hidden] the layer's input stream (bf16 values)
     float* stream_b;   // [hidden] the stream behind the attention block
@@ -122,28 +109,29 @@ __device__ __forceinline__ unsigned long long best_key(float v, int idx) {
 // ---------------------------------------------------------------------------------------------
 // Grid barrier: arrival n of the kernel's k-th barrier makes the counter reach k * G.  Consumers only.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, unsigned int target) {
+__device__ __noinline__ bool grid_barrier_call(unsigned int* counter, int* abort_word, int* status, DtShared* shp, unsigned int target) {
+    DtShared& sh = *shp;
     consumer_sync();  // this CTA's writes of the phase are done
     if (threadIdx.x == 0) {
         // release: the CTA's writes of the phase (ordered before this thread by the barrier above) are visible
         // to whoever reads the count with acquire
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.counter) : "memory");
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
         const long long t0 = clock64();
         bool ok = true;
         for (;;) {
             unsigned int v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.counter) : "memory");
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
             if (v >= target) break;
             int ab;
-            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(ab) : "l"(P.abort_word) : "memory");
+            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(ab) : "l"(abort_word) : "memory");
             if (ab != 0 || clock64() - t0 > IZB_WAIT_LIMIT_CLOCKS) {
                 ok = false;
                 break;
             }
         }
         if (!ok) {
-            atomicExch(P.abort_word, 1);
-            atomicExch(P.status, 1);
+            atomicExch(abort_word, 1);
+            atomicExch(status, 1);
             sh.abort_flag = 1;
         }
     }
@@ -151,57 +139,22 @@ __device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, un
     return *reinterpret_cast<volatile int*>(&sh.abort_flag) == 0;
 }
 
-// Units of a projection phase for one CTA, in the order both the producer and the consumers walk them.
+__device__ __forceinline__ bool grid_barrier(const DtParams& P, DtShared& sh, unsigned int target) {
+    return grid_barrier_call(P.counter, P.abort_word, P.status, &sh, target);
+}
+
+// Units of a projection phase for this CTA: u = cta, cta + G, ...; unit -> (tile, slice) -> boxes [b0, b1).
 struct DtUnit {
-    int tile, slice, b0, b1;  // rows 64 tile .., boxes [b0, b1); `slice` = which partial sum of the tile this is
+    int tile, slice, b0, b1;
 };
-// tiles * boxes * G stays below 2^31 in contiguous mode (the host checks), so this is 32-bit arithmetic.
-__host__ __device__ __forceinline__ int dt_start(const DtSplit& sp, int c, int G) {
-    return static_cast<int>(static_cast<unsigned>(c) * static_cast<unsigned>(sp.tiles * sp.boxes) / static_cast<unsigned>(G));
+__device__ __forceinline__ DtUnit dt_unit(int u, int S, int boxes) {
+    DtUnit r;
+    r.tile = u / S;
+    r.slice = u - r.tile * S;
+    r.b0 = r.slice * boxes / S;
+    r.b1 = (r.slice + 1) * boxes / S;
+    return r;
 }
-// The CTA whose contiguous range holds unit u.
-__host__ __device__ __forceinline__ int dt_cta_of(const DtSplit& sp, int u, int G) {
-    int c = static_cast<int>(static_cast<unsigned>(u) * static_cast<unsigned>(G) / static_cast<unsigned>(sp.tiles * sp.boxes));  // start(c) <= u
-    while (dt_start(sp, c + 1, G) <= u) ++c;
-    return c;
-}
-// Partial sums (slices or slots) the next phase adds up for the rows of `tile`.
-__host__ __device__ __forceinline__ int dt_slots(const DtSplit& sp, int tile, int G) {
-    if (!sp.contiguous) return sp.S;
-    const int u0 = tile * sp.boxes;
-    return dt_cta_of(sp, u0 + sp.boxes - 1, G) - dt_cta_of(sp, u0, G) + 1;
-}
-struct DtWalk {
-    DtSplit sp;
-    int G, cta;
-    int u, end;  // contiguous: next unit and end of the range; round robin: next (tile, slice) index (step G) and their count
-    __device__ __forceinline__ DtWalk(const DtSplit& split, int cta_, int G_) : sp(split), G(G_), cta(cta_) {
-        if (sp.contiguous) {
-            u = dt_start(sp, cta, G);
-            end = dt_start(sp, cta + 1, G);
-        } else {
-            u = cta;
-            end = sp.tiles * sp.S;
-        }
-    }
-    __device__ __forceinline__ bool next(DtUnit& un) {
-        if (u >= end) return false;
-        if (sp.contiguous) {
-            un.tile = u / sp.boxes;
-            un.b0 = u - un.tile * sp.boxes;
-            un.b1 = min(sp.boxes, un.b0 + (end - u));
-            un.slice = cta - dt_cta_of(sp, un.tile * sp.boxes, G);
-            u += un.b1 - un.b0;
-        } else {
-            un.tile = u / sp.S;
-            un.slice = u - un.tile * sp.S;
-            un.b0 = un.slice * sp.boxes / sp.S;
-            un.b1 = (un.slice + 1) * sp.boxes / sp.S;
-            u += G;
-        }
-        return true;
-    }
-};
 
 // ---------------------------------------------------------------------------------------------
 // Producer warp: the weight boxes of this CTA's units of one projection, in unit order.
@@ -212,25 +165,43 @@ struct DtRing {
     long long issued;
 };
 
-__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const CUtensorMap* map,
-                                              const DtSplit& sp, int w_row_bytes) {
+struct DtRingResult {
+    DtRing ring;
+    int ok;
+};
+__device__ __noinline__ DtRingResult produce_phase_call(DtShared* shp, uint32_t ring0, DtRing R, int n_slots, const CUtensorMap* map, int N, int K,
+                                                        int S, int w_row_bytes) {
+    DtShared& sh = *shp;
+    const int boxes = K / 256, tiles = N / DT_TILE_ROWS, units = tiles * S;
     volatile int* abort_flag = &sh.abort_flag;
-    DtWalk walk(sp, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
-    DtUnit un;
-    while (walk.next(un)) {
+    const uint32_t full0 = smem_u32(&sh.full[0]), empty0 = smem_u32(&sh.empty[0]);
+    DtRingResult out;
+    out.ok = 1;
+    for (int u = static_cast<int>(blockIdx.x); u < units && out.ok; u += static_cast<int>(gridDim.x)) {
+        const DtUnit un = dt_unit(u, S, boxes);
         for (int b = un.b0; b < un.b1; ++b) {
-            if (R.issued >= P.n_slots && !mbar_wait_bounded_relaxed(smem_u32(&sh.empty[R.slot]), R.phase ^ 1u, abort_flag)) return false;
-            const uint32_t fbar = smem_u32(&sh.full[R.slot]);
+            if (R.issued >= n_slots && !mbar_wait_bounded_relaxed(empty0 + 8u * R.slot, R.phase ^ 1u, abort_flag)) {
+                out.ok = 0;
+                break;
+            }
+            const uint32_t fbar = full0 + 8u * R.slot;
             mbar_expect_tx(fbar, static_cast<uint32_t>(DT_TILE_ROWS * w_row_bytes));
             tma_load_3d(ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES, map, 0, un.tile * DT_TILE_ROWS, b, fbar);
             ++R.issued;
-            if (++R.slot == P.n_slots) {
+            if (++R.slot == n_slots) {
                 R.slot = 0;
                 R.phase ^= 1u;
             }
         }
     }
-    return true;
+    out.ring = R;
+    return out;
+}
+__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const CUtensorMap* map, int N, int K,
+                                              int S, int w_row_bytes) {
+    const DtRingResult r = produce_phase_call(&sh, ring0, R, P.n_slots, map, N, K, S, w_row_bytes);
+    R = r.ring;
+    return r.ok != 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -238,18 +209,30 @@ __device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, u
 // Q8_0: thread = (row, pair of blocks) of every box; Q4_K: thread = (row, half of the super-block, box parity).
 // Returns the row's sum in the threads with tid < 64.
 // ---------------------------------------------------------------------------------------------
+// One copy of this code per weight format serves the five projection phases: it is a call, not inline code, so that
+// the layer loop stays small for the instruction cache.  Ring position in and out by value (registers).
+struct DtUnitResult {
+    float sum;
+    int slot;
+    uint32_t phase;
+    int ok;
+};
 template <int FMT>
-__device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, uint32_t ring0, uint32_t xq0, DtRing& R, const DtUnit& un,
-                                             float& out) {
+__device__ __noinline__ DtUnitResult consume_unit_call(DtShared* sh, uint32_t ring0, uint32_t xq0, int n_slots, int slot, uint32_t phase,
+                                                       int b0, int b1) {
     const int tid = threadIdx.x, row = tid & 63, quarter = tid >> 6;
     const int w_row_bytes = FMT == IZB_W_Q8_0 ? 272 : 144;
-    volatile int* abort_flag = &sh.abort_flag;
+    const uint32_t sh_addr = smem_u32(sh);
+    volatile int* abort_flag = &sh->abort_flag;
+    const uint32_t full0 = sh_addr + static_cast<uint32_t>(offsetof(DtShared, full));
+    const uint32_t empty0 = sh_addr + static_cast<uint32_t>(offsetof(DtShared, empty));
+    const uint32_t red0 = sh_addr + static_cast<uint32_t>(offsetof(DtShared, red));
     float acc[1] = {0.f};
     bool ok = true;
-    for (int b = un.b0; b < un.b1; ++b) {
-        if (ok && !mbar_wait_bounded(smem_u32(&sh.full[R.slot]), R.phase, abort_flag)) ok = false;
+    for (int b = b0; b < b1; ++b) {
+        if (ok && !mbar_wait_bounded(full0 + 8u * slot, phase, abort_flag)) ok = false;
         if (ok) {
-            const uint32_t wrow = ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES + static_cast<uint32_t>(row * w_row_bytes);
+            const uint32_t wrow = ring0 + static_cast<uint32_t>(slot) * DT_SLOT_BYTES + static_cast<uint32_t>(row * w_row_bytes);
             const uint32_t xq = xq0 + static_cast<uint32_t>(b * GV_XQ_BYTES);
             if constexpr (FMT == IZB_W_Q8_0) {
                 switch (quarter) {
@@ -260,32 +243,46 @@ __device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, ui
                 }
             } else {
                 // the two halves of a super-block go to quarters 0 / 1 for even boxes of the unit, 2 / 3 for odd ones
-                if ((quarter >> 1) == ((b - un.b0) & 1)) {
+                if ((quarter >> 1) == ((b - b0) & 1)) {
                     if (quarter & 1) gv_half_q4_k<1, 1>(acc, wrow, xq, GV_XQ_BYTES);
                     else gv_half_q4_k<0, 1>(acc, wrow, xq, GV_XQ_BYTES);
                 }
             }
         }
         __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(smem_u32(&sh.empty[R.slot]));
-        if (++R.slot == P.n_slots) {
-            R.slot = 0;
-            R.phase ^= 1u;
+        if ((tid & 31) == 0) mbar_arrive(empty0 + 8u * slot);
+        if (++slot == n_slots) {
+            slot = 0;
+            phase ^= 1u;
         }
     }
     ok = consumer_all(ok);  // also: the sums of the unit before this one have been read
-    sh.red[quarter][row] = acc[0];
+    sts32f(red0 + 4u * static_cast<uint32_t>(quarter * DT_TILE_ROWS + row), acc[0]);
     consumer_sync();
-    out = tid < 64 ? (sh.red[0][tid] + sh.red[1][tid]) + (sh.red[2][tid] + sh.red[3][tid]) : 0.f;
-    return ok;
+    DtUnitResult r;
+    r.sum = tid < 64 ? (lds32f(red0 + 4u * tid) + lds32f(red0 + 4u * (DT_TILE_ROWS + tid))) +
+                           (lds32f(red0 + 4u * (2 * DT_TILE_ROWS + tid)) + lds32f(red0 + 4u * (3 * DT_TILE_ROWS + tid)))
+                     : 0.f;
+    r.slot = slot;
+    r.phase = phase;
+    r.ok = ok;
+    return r;
+}
+template <int FMT>
+__device__ __forceinline__ bool consume_unit(const DtParams& P, DtShared& sh, uint32_t ring0, uint32_t xq0, DtRing& R, const DtUnit& un,
+                                             float& out) {
+    const DtUnitResult r = consume_unit_call<FMT>(&sh, ring0, xq0, P.n_slots, R.slot, R.phase, un.b0, un.b1);
+    R.slot = r.slot;
+    R.phase = r.phase;
+    out = r.sum;
+    return r.ok != 0;
 }
 
 // Sums of four consecutive activation elements over the k slices of the projection that produced them,
 // in slice order.  The loads of CH slices are issued before the first add: it is the number of L2 round
 // trips, not of loads, that a phase pays for.
 template <int CH>
-__device__ __forceinline__ float4 part_sum4(const float* part, const DtSplit& sp, int n, int i0) {
-    const int S = dt_slots(sp, i0 / DT_TILE_ROWS, static_cast<int>(gridDim.x));
+__device__ __forceinline__ float4 part_sum4(const float* part, int S, int n, int i0) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < S; s0 += CH) {
         float4 t[CH];
@@ -323,9 +320,9 @@ __device__ __forceinline__ void stage_stream(DtShared& sh, float* xf, int hidden
 }
 
 // stream + the k slices of the projection behind it, rounded to bf16 as the reference stores the stream
-__device__ __forceinline__ float4 stream_plus(const float* stream, const float* part, const DtSplit& sp, int n, int i0) {
+__device__ __forceinline__ float4 stream_plus(const float* stream, const float* part, int S, int n, int i0) {
     const float4 r = __ldcg(reinterpret_cast<const float4*>(stream + i0));
-    const float4 p = part_sum4<8>(part, sp, n, i0);
+    const float4 p = part_sum4<8>(part, S, n, i0);
     return make_float4(bf16r(r.x + p.x), bf16r(r.y + p.y), bf16r(r.z + p.z), bf16r(r.w + p.w));
 }
 
@@ -362,6 +359,21 @@ __device__ __forceinline__ void convert_normed(uint32_t xq0, const float* xf, fl
         }
         gv_convert_unit_f32(v, xq0 + static_cast<uint32_t>(b * GV_XQ_BYTES), lane);
     }
+}
+
+// The opening of a phase that reads the residual stream: stream = bf16(stream_in + the slices of the projection
+// behind it), kept by CTA 0 in stream_out (when given); RmsNorm with norm_w; activations of every box converted.
+// A call: three phases share the code.
+__device__ __noinline__ void norm_prologue_call(DtShared* shp, float* xf, uint32_t xq0, const float* stream_in, const float* part, int S,
+                                                int hidden, float eps, const __nv_bfloat16* norm_w, float* stream_out) {
+    DtShared& sh = *shp;
+    const int boxes = hidden / 256;
+    const DtNormW nw = load_norm_weights(norm_w, boxes);
+    stage_stream(sh, xf, hidden, eps, [&](int i0) { return stream_plus(stream_in, part, S, hidden, i0); });
+    if (stream_out)
+        for (int i = threadIdx.x; i < hidden; i += DT_CONSUMERS) stream_out[i] = xf[i];
+    convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
+    consumer_sync();
 }
 
 // One warp converts one 256-k box: lane = 8 consecutive values.
@@ -407,7 +419,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
             cv = __ldg(reinterpret_cast<const uint2*>(cosv + jh));
             sv = __ldg(reinterpret_cast<const uint2*>(sinv + jh));
         }
-        const float4 xs = part_sum4<4>(P.part_qkv, P.sp_qkv, n_qkv, col0 + lane * 4);
+        const float4 xs = part_sum4<4>(P.part_qkv, P.s_qkv, n_qkv, col0 + lane * 4);
         float x[4] = {bf16r(xs.x), bf16r(xs.y), bf16r(xs.z), bf16r(xs.w)};  // the QKV output as stored
         if (warp <= gq) {
             if (w) {
@@ -606,12 +618,12 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         bool ok = true;
         for (int l = 0; l < A.n_layers && ok; ++l) {
             const CUtensorMap* m = P.maps + 4 * l;
-            ok = produce_phase(P, sh, ring0, R, m + 0, P.sp_qkv, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 1, P.sp_o, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 2, P.sp_gu, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 3, P.sp_down, w_row);
+            ok = produce_phase(P, sh, ring0, R, m + 0, n_qkv, A.hidden, P.s_qkv, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 1, A.hidden, q_dim, P.s_o, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 2, 2 * A.intermediate, A.hidden, P.s_gu, w_row);
+            if (ok) ok = produce_phase(P, sh, ring0, R, m + 3, A.hidden, A.intermediate, P.s_down, w_row);
         }
-        if (ok) ok = produce_phase(P, sh, ring0, R, P.maps + 4 * A.n_layers, P.sp_lm, lm_row);
+        if (ok) ok = produce_phase(P, sh, ring0, R, P.maps + 4 * A.n_layers, A.vocab, A.hidden, 1, lm_row);
         // the copies still in flight land before the CTA's shared memory goes away
         {
             const long long first = R.issued > P.n_slots ? R.issued - P.n_slots : 0;
@@ -648,21 +660,22 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         const izb_qwen3_layer_ptrs& Lp = P.layers[l];
         // ===== QKV: stream = previous stream + down partials (layer 0: the embedding row); input norm =====
         {
-            const int boxes = A.hidden / 256;
-            const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(Lp.input_norm), boxes);
-            if (l == 0)
+            const int boxes = A.hidden / 256, units = (n_qkv / DT_TILE_ROWS) * P.s_qkv;
+            if (l == 0) {
+                const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(Lp.input_norm), boxes);
                 stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) {
                     const uint2 w = *reinterpret_cast<const uint2*>(embed_row + i0);
                     return make_float4(bf16_lo_to_f32(w.x), bf16_hi_to_f32(w.x), bf16_lo_to_f32(w.y), bf16_hi_to_f32(w.y));
                 });
-            else
-                stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.sp_down, A.hidden, i0); });
-            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_a[i] = xf[i];
-            convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
-            consumer_sync();
-            DtWalk walk(P.sp_qkv, cta, G);
-            DtUnit un;
-            while (walk.next(un)) {
+                if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_a[i] = xf[i];
+                convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
+                consumer_sync();
+            } else {
+                norm_prologue_call(&sh, xf, xq0, P.stream_b, P.part_down, P.s_down, A.hidden, A.eps,
+                                   static_cast<const __nv_bfloat16*>(Lp.input_norm), cta == 0 ? P.stream_a : nullptr);
+            }
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_qkv, boxes);
                 float y;
                 ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
                 if (tid < 64) P.part_qkv[static_cast<size_t>(un.slice) * n_qkv + un.tile * DT_TILE_ROWS + tid] = y;
@@ -686,9 +699,9 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         // ===== O projection over the merged attention output =====
         {
             unsigned long long done = 0;
-            DtWalk walk(P.sp_o, cta, G);
-            DtUnit un;
-            while (walk.next(un)) {
+            const int boxes = q_dim / 256, units = (A.hidden / DT_TILE_ROWS) * P.s_o;
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_o, boxes);
                 convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
                     // merge of the splits' (max, sum of weights, weighted values) for this lane's 8 values of one head;
                     // the records of the first eight splits and all the (max, sum) pairs are asked for in one go
@@ -749,15 +762,11 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         if (!ok) break;
         // ===== gate / up: stream += O partials; post-attention norm =====
         {
-            const int boxes = A.hidden / 256;
-            const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(Lp.post_norm), boxes);
-            stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_a, P.part_o, P.sp_o, A.hidden, i0); });
-            if (cta == 0) for (int i = tid; i < A.hidden; i += DT_CONSUMERS) P.stream_b[i] = xf[i];
-            convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
-            consumer_sync();
-            DtWalk walk(P.sp_gu, cta, G);
-            DtUnit un;
-            while (walk.next(un)) {
+            const int boxes = A.hidden / 256, units = (2 * A.intermediate / DT_TILE_ROWS) * P.s_gu;
+            norm_prologue_call(&sh, xf, xq0, P.stream_a, P.part_o, P.s_o, A.hidden, A.eps, static_cast<const __nv_bfloat16*>(Lp.post_norm),
+                               cta == 0 ? P.stream_b : nullptr);
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_gu, boxes);
                 float y;
                 ok = consume_unit<FMT>(P, sh, ring0, xq0, R, un, y) && ok;
                 if (tid < 64) P.part_gu[static_cast<size_t>(un.slice) * 2 * A.intermediate + un.tile * DT_TILE_ROWS + tid] = y;
@@ -768,14 +777,14 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
         // ===== down over silu(gate) * up =====
         {
             unsigned long long done = 0;
+            const int boxes = A.intermediate / 256, units = (A.hidden / DT_TILE_ROWS) * P.s_down;
             const int n_gu = 2 * A.intermediate;
-            DtWalk walk(P.sp_down, cta, G);
-            DtUnit un;
-            while (walk.next(un)) {
+            for (int u = cta; u < units; u += G) {
+                const DtUnit un = dt_unit(u, P.s_down, boxes);
                 convert_boxes(xq0, un.b0, un.b1, done, [&](int k0, float (&v)[8]) {
-                    const float4 g0 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, k0), g1 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, k0 + 4);
-                    const float4 u0 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, A.intermediate + k0);
-                    const float4 u1 = part_sum4<4>(P.part_gu, P.sp_gu, n_gu, A.intermediate + k0 + 4);
+                    const float4 g0 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, k0), g1 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, k0 + 4);
+                    const float4 u0 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, A.intermediate + k0);
+                    const float4 u1 = part_sum4<4>(P.part_gu, P.s_gu, n_gu, A.intermediate + k0 + 4);
                     const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
                     const float us[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
@@ -796,14 +805,11 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
     // ===== final norm, lm_head, arg-max =====
     unsigned long long best = 0;
     if (ok) {
-        const int boxes = A.hidden / 256;
-        const DtNormW nw = load_norm_weights(static_cast<const __nv_bfloat16*>(A.final_norm), boxes);
-        stage_stream(sh, xf, A.hidden, A.eps, [&](int i0) { return stream_plus(P.stream_b, P.part_down, P.sp_down, A.hidden, i0); });
-        convert_normed(xq0, xf, sh.inv_rms, nw, boxes);
-        consumer_sync();
-        DtWalk walk(P.sp_lm, cta, G);
-        DtUnit un;
-        while (walk.next(un)) {
+        const int boxes = A.hidden / 256, units = A.vocab / DT_TILE_ROWS;
+        norm_prologue_call(&sh, xf, xq0, P.stream_b, P.part_down, P.s_down, A.hidden, A.eps, static_cast<const __nv_bfloat16*>(A.final_norm),
+                           nullptr);
+        for (int u = cta; u < units; u += G) {
+            const DtUnit un = dt_unit(u, 1, boxes);
             float y;
             ok = consume_unit<LM_FMT>(P, sh, ring0, xq0, R, un, y) && ok;
             if (tid < 64) {
@@ -869,23 +875,6 @@ int pick_slices(int tiles, int boxes, int G) {
     return best_s;
 }
 
-// The dealing of one projection's units: contiguous ranges once every CTA gets `IZB_TOKEN_CONTIGUOUS_MIN` (default 4;
-// 0 = never) or more (tile, box) units, where an uneven count of round-robin units costs more than the extra partial
-// sums of the cut tiles; S = the most partial sums a tile can have (the workspace is laid out for it).
-DtSplit dt_split(int tiles, int boxes, int G) {
-    DtSplit sp{tiles, boxes, 1, 0};
-    const char* e = std::getenv("IZB_TOKEN_CONTIGUOUS_MIN");
-    const int min_units = (e && *e) ? std::atoi(e) : 4;
-    const long long U = static_cast<long long>(tiles) * boxes;
-    if (min_units > 0 && U >= static_cast<long long>(min_units) * G && U * (G + 1) < (1ll << 31)) {
-        sp.contiguous = 1;
-        for (int t = 0; t < tiles; ++t) sp.S = std::max(sp.S, dt_slots(sp, t, G));
-    } else {
-        sp.S = pick_slices(tiles, boxes, G);
-    }
-    return sp;
-}
-
 struct DtLayout {
     size_t part_qkv, part_o, part_gu, part_down, att_part, stream_a, stream_b, best, counter, total;
 };
@@ -919,11 +908,10 @@ int dt_weight_map(CUtensorMap* out, const void* w, int fmt, int N, int K) {
 void dt_plan(const izb_ctx* ctx, const izb_qwen3_decode_args* a, DtParams* p, DtLayout* lay) {
     const int G = ctx->sm_count;
     const int q_dim = a->heads * DT_D, kv_dim = a->kv_heads * DT_D, n_qkv = q_dim + 2 * kv_dim;
-    p->sp_qkv = dt_split(n_qkv / DT_TILE_ROWS, a->hidden / 256, G);
-    p->sp_o = dt_split(a->hidden / DT_TILE_ROWS, q_dim / 256, G);
-    p->sp_gu = dt_split(2 * a->intermediate / DT_TILE_ROWS, a->hidden / 256, G);
-    p->sp_down = dt_split(a->hidden / DT_TILE_ROWS, a->intermediate / 256, G);
-    p->sp_lm = DtSplit{a->vocab / DT_TILE_ROWS, a->hidden / 256, 1, 0};  // a logit is one unit's sum: whole rows, round robin
+    p->s_qkv = pick_slices(n_qkv / DT_TILE_ROWS, a->hidden / 256, G);
+    p->s_o = pick_slices(a->hidden / DT_TILE_ROWS, q_dim / 256, G);
+    p->s_gu = pick_slices(2 * a->intermediate / DT_TILE_ROWS, a->hidden / 256, G);
+    p->s_down = pick_slices(a->hidden / DT_TILE_ROWS, a->intermediate / 256, G);
     // splits of the cache per KV head: 64 positions each while eight splits cover the context (one trip for the
     // merge), 256 each beyond; the workspace is laid out for the most there can be
     const int max_splits = std::max(1, std::min(DT_MAX_SPLITS, G / a->kv_heads));
@@ -932,10 +920,10 @@ void dt_plan(const izb_ctx* ctx, const izb_qwen3_decode_args* a, DtParams* p, Dt
     p->att_splits = std::max(1, std::min(max_splits, want));
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t at = off; off += al256(bytes); return at; };
-    lay->part_qkv = take(sizeof(float) * p->sp_qkv.S * n_qkv);
-    lay->part_o = take(sizeof(float) * p->sp_o.S * a->hidden);
-    lay->part_gu = take(sizeof(float) * p->sp_gu.S * 2 * a->intermediate);
-    lay->part_down = take(sizeof(float) * p->sp_down.S * a->hidden);
+    lay->part_qkv = take(sizeof(float) * p->s_qkv * n_qkv);
+    lay->part_o = take(sizeof(float) * p->s_o * a->hidden);
+    lay->part_gu = take(sizeof(float) * p->s_gu * 2 * a->intermediate);
+    lay->part_down = take(sizeof(float) * p->s_down * a->hidden);
     lay->att_part = take(sizeof(float) * a->heads * max_splits * DT_REC);
     lay->stream_a = take(sizeof(float) * a->hidden);
     lay->stream_b = take(sizeof(float) * a->hidden);
