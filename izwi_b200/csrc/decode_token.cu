@@ -392,9 +392,20 @@ __device__ __forceinline__ void convert_boxes(uint32_t xq0, int b0, int b1, unsi
 // ---------------------------------------------------------------------------------------------
 // Attention phase unit: kv head `kvh`, positions [t0, t1) of the cache (position `pos` = the new token).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, float* scratch, const izb_qwen3_layer_ptrs& Lp, int kvh,
-                                               int split, int t0, int t1) {
-    const izb_qwen3_decode_args& A = P.a;
+// What the unit reads of the launch parameters, by value: the unit is a call (one copy of the code per group size
+// GQ = 1, 2, 4 query heads per kv head, of which a model runs one), and a call cannot name the parameter space.
+struct DtAttArgs {
+    const float* part_qkv;
+    float* att_part;
+    const void *cos_half, *sin_half, *q_norm, *k_norm;
+    void *k_cache, *v_cache;
+    int s_qkv, att_splits, heads, kv_heads, kv_capacity, pos, scratch_offset;
+    float eps;
+};
+template <int GQ>
+__device__ __noinline__ void attention_unit_call(const DtAttArgs A, int kvh, int split, int t0, int t1) {
+    extern __shared__ __align__(1024) uint8_t dyn_smem[];
+    float* scratch = reinterpret_cast<float*>(dyn_smem + A.scratch_offset);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gq = A.heads / A.kv_heads, q_dim = A.heads * DT_D, kv_dim = A.kv_heads * DT_D, n_qkv = q_dim + 2 * kv_dim;
     float* qs = scratch;                  // [gq][D] rotated query heads (bf16 values)
@@ -403,15 +414,15 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
     float* wpart = vnew + DT_D;           // [warps][gq][D + 2]
     const __nv_bfloat16* cosv = static_cast<const __nv_bfloat16*>(A.cos_half);
     const __nv_bfloat16* sinv = static_cast<const __nv_bfloat16*>(A.sin_half);
-    __nv_bfloat16* kc = static_cast<__nv_bfloat16*>(Lp.k_cache) + static_cast<size_t>(kvh) * A.kv_capacity * DT_D;
-    __nv_bfloat16* vc = static_cast<__nv_bfloat16*>(Lp.v_cache) + static_cast<size_t>(kvh) * A.kv_capacity * DT_D;
+    __nv_bfloat16* kc = static_cast<__nv_bfloat16*>(A.k_cache) + static_cast<size_t>(kvh) * A.kv_capacity * DT_D;
+    __nv_bfloat16* vc = static_cast<__nv_bfloat16*>(A.v_cache) + static_cast<size_t>(kvh) * A.kv_capacity * DT_D;
     const bool owns_new = A.pos >= t0 && A.pos < t1;
 
     // ---- the new token's rows of this kv head: warps 0 .. gq-1 a query head each, warp gq k, warp gq+1 v ----
     if (warp < gq + 2) {
         const int col0 = warp < gq ? (kvh * gq + warp) * DT_D : warp == gq ? q_dim + kvh * DT_D : q_dim + kv_dim + kvh * DT_D;
         // everything this warp's row needs from memory, asked for together
-        const __nv_bfloat16* w = warp <= gq ? static_cast<const __nv_bfloat16*>(warp < gq ? Lp.q_norm : Lp.k_norm) : nullptr;
+        const __nv_bfloat16* w = warp <= gq ? static_cast<const __nv_bfloat16*>(warp < gq ? A.q_norm : A.k_norm) : nullptr;
         const int jh = (lane & 15) * 4;  // lanes 0..15 hold the first half of the head, 16..31 the second
         uint2 wv = make_uint2(0u, 0u), cv = make_uint2(0u, 0u), sv = make_uint2(0u, 0u);
         if (w) wv = __ldg(reinterpret_cast<const uint2*>(w + lane * 4));
@@ -419,7 +430,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
             cv = __ldg(reinterpret_cast<const uint2*>(cosv + jh));
             sv = __ldg(reinterpret_cast<const uint2*>(sinv + jh));
         }
-        const float4 xs = part_sum4<4>(P.part_qkv, P.s_qkv, n_qkv, col0 + lane * 4);
+        const float4 xs = part_sum4<4>(A.part_qkv, A.s_qkv, n_qkv, col0 + lane * 4);
         float x[4] = {bf16r(xs.x), bf16r(xs.y), bf16r(xs.z), bf16r(xs.w)};  // the QKV output as stored
         if (warp <= gq) {
             if (w) {
@@ -453,9 +464,9 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
     consumer_sync();
 
     // ---- every warp: positions t0 + warp, + 8, ...; lane owns 4 of the 128 values ----
-    float q[DT_MAX_GQ][4], acc[DT_MAX_GQ][4], m[DT_MAX_GQ], l[DT_MAX_GQ];
+    float q[GQ][4], acc[GQ][4], m[GQ], l[GQ];
 #pragma unroll
-    for (int g = 0; g < DT_MAX_GQ; ++g) {
+    for (int g = 0; g < GQ; ++g) {
         m[g] = -INFINITY;
         l[g] = 0.f;
 #pragma unroll
@@ -479,7 +490,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
             }
         }
         // the trip's scores first (independent chains), one running-max step for the trip, then the values
-        float sc[DT_MAX_GQ][PT];
+        float sc[GQ][PT];
 #pragma unroll
         for (int u = 0; u < PT; ++u) {
             const int t = tb + u * DT_CONSUMER_WARPS;
@@ -491,7 +502,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
                 kv[0] = bf16_lo_to_f32(kw[u].x); kv[1] = bf16_hi_to_f32(kw[u].x); kv[2] = bf16_lo_to_f32(kw[u].y); kv[3] = bf16_hi_to_f32(kw[u].y);
             }
 #pragma unroll
-            for (int g = 0; g < DT_MAX_GQ; ++g) {
+            for (int g = 0; g < GQ; ++g) {
                 float d = 0.f;
                 if (g < gq) d = q[g][0] * kv[0] + q[g][1] * kv[1] + q[g][2] * kv[2] + q[g][3] * kv[3];
                 sc[g][u] = d;
@@ -500,14 +511,14 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
-            for (int g = 0; g < DT_MAX_GQ; ++g) {
+            for (int g = 0; g < GQ; ++g) {
                 if (g >= gq) break;
 #pragma unroll
                 for (int u = 0; u < PT; ++u) sc[g][u] += __shfl_xor_sync(0xFFFFFFFFu, sc[g][u], o);
             }
         }
 #pragma unroll
-        for (int g = 0; g < DT_MAX_GQ; ++g) {
+        for (int g = 0; g < GQ; ++g) {
             if (g >= gq) break;
             float mx = -INFINITY;
 #pragma unroll
@@ -538,7 +549,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
                 vv[0] = bf16_lo_to_f32(vw[u].x); vv[1] = bf16_hi_to_f32(vw[u].x); vv[2] = bf16_lo_to_f32(vw[u].y); vv[3] = bf16_hi_to_f32(vw[u].y);
             }
 #pragma unroll
-            for (int g = 0; g < DT_MAX_GQ; ++g) {
+            for (int g = 0; g < GQ; ++g) {
                 if (g >= gq) break;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(sc[g][u], vv[j], acc[g][j]);
@@ -547,7 +558,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
     }
     // ---- the eight warps' (max, sum, weighted values) -> one partial per query head and split ----
 #pragma unroll
-    for (int g = 0; g < DT_MAX_GQ; ++g) {
+    for (int g = 0; g < GQ; ++g) {
         if (g >= gq) break;
         float* wp = wpart + (warp * DT_MAX_GQ + g) * (DT_D + 2);
 #pragma unroll
@@ -571,7 +582,7 @@ __device__ __forceinline__ void attention_unit(const DtParams& P, DtShared& sh, 
             for (int j = 0; j < 4; ++j) num[j] = fmaf(f, wp[lane * 4 + j], num[j]);
             den = fmaf(f, wp[DT_D + 1], den);
         }
-        float* out = P.att_part + (static_cast<size_t>(kvh * gq + g) * P.att_splits + split) * DT_REC;
+        float* out = A.att_part + (static_cast<size_t>(kvh * gq + g) * A.att_splits + split) * DT_REC;
 #pragma unroll
         for (int j = 0; j < 4; ++j) out[lane * 4 + j] = num[j];
         if (lane == 0) {
@@ -608,7 +619,6 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
     uint8_t* scratch_gen = dyn_smem + static_cast<size_t>(P.n_slots) * DT_SLOT_BYTES;
     const uint32_t xq0 = ring0 + static_cast<uint32_t>(P.n_slots) * DT_SLOT_BYTES;            // [DT_MAX_BOXES][GV_XQ_BYTES]
     float* xf = reinterpret_cast<float*>(scratch_gen + DT_MAX_BOXES * GV_XQ_BYTES);           // [DT_MAX_HIDDEN]
-    float* att_scratch = reinterpret_cast<float*>(scratch_gen);                                // attention phase: over the same bytes
 
     DtRing R{0, 0u, 0};
 
@@ -688,10 +698,22 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
             const int ctx_len = A.pos + 1;
             const int per = (ctx_len + P.att_splits - 1) / P.att_splits;
             const int units = A.kv_heads * P.att_splits;
-            for (int u = cta; u < units; u += G) {
-                const int kvh = u / P.att_splits, split = u - kvh * P.att_splits;
-                const int t0 = min(ctx_len, split * per), t1 = min(ctx_len, t0 + per);
-                attention_unit(P, sh, att_scratch, Lp, kvh, split, t0, t1);
+            if (cta < units) {
+                DtAttArgs aa;
+                aa.part_qkv = P.part_qkv; aa.att_part = P.att_part;
+                aa.cos_half = A.cos_half; aa.sin_half = A.sin_half; aa.q_norm = Lp.q_norm; aa.k_norm = Lp.k_norm;
+                aa.k_cache = Lp.k_cache; aa.v_cache = Lp.v_cache;
+                aa.s_qkv = P.s_qkv; aa.att_splits = P.att_splits; aa.heads = A.heads; aa.kv_heads = A.kv_heads;
+                aa.kv_capacity = A.kv_capacity; aa.pos = A.pos; aa.scratch_offset = P.n_slots * DT_SLOT_BYTES;
+                aa.eps = A.eps;
+                const int gq = A.heads / A.kv_heads;
+                for (int u = cta; u < units; u += G) {
+                    const int kvh = u / P.att_splits, split = u - kvh * P.att_splits;
+                    const int t0 = min(ctx_len, split * per), t1 = min(ctx_len, t0 + per);
+                    if (gq == 1) attention_unit_call<1>(aa, kvh, split, t0, t1);
+                    else if (gq == 2) attention_unit_call<2>(aa, kvh, split, t0, t1);
+                    else attention_unit_call<4>(aa, kvh, split, t0, t1);
+                }
             }
         }
         ok = grid_barrier(P, sh, ++barriers * G) && ok;
