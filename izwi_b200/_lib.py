@@ -96,6 +96,8 @@ _SIGNATURES = {
     "izb_linear_group_plan_bytes": (C.c_size_t, [C.c_int32]),
     "izb_linear_group_plan": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_int32, C.c_void_p, C.c_size_t]),
     "izb_linear_group_launch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "izb_linear_group_launch_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                                 C.c_void_p, C.c_void_p, C.c_size_t]),
     "izb_static_scratch_bytes": (C.c_size_t, []),
     "izb_linear_quantized_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                                 C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),

@@ -581,4 +581,16 @@ int32_t izb_linear_group_launch(izb_ctx* ctx, izb_stream stream, const void* hos
     return skinny_launch(ctx, static_cast<cudaStream_t>(stream), *hdr, dev, nullptr);
 }
 
+int32_t izb_linear_group_launch_host(izb_ctx* ctx, izb_stream stream, const void* host_plan, const void* dev_plan, const void* host_in,
+                                     void* dev_in, size_t in_bytes, const void* dev_out, void* host_out, size_t out_bytes) {
+    if (!ctx || (in_bytes && (!host_in || !dev_in)) || (out_bytes && (!dev_out || !host_out))) return IZB_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (in_bytes) IZB_CUDA_TRY(cudaMemcpyAsync(dev_in, host_in, in_bytes, cudaMemcpyHostToDevice, s));
+    const int32_t st = izb_linear_group_launch(ctx, stream, host_plan, dev_plan);
+    if (st != IZB_OK) return st;
+    if (out_bytes) IZB_CUDA_TRY(cudaMemcpyAsync(host_out, dev_out, out_bytes, cudaMemcpyDeviceToHost, s));
+    IZB_CUDA_TRY(cudaStreamSynchronize(s));
+    return IZB_OK;
+}
+
 }  // extern "C"

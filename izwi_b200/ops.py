@@ -360,3 +360,23 @@ class LinearGroup:
     def launch(self) -> None:
         L.check(L.lib().izb_linear_group_launch(self.ctx.handle, _stream(), C.c_void_p(self.host_plan.data_ptr()),
                                                 C.c_void_p(self.dev_plan.data_ptr())), "izb_linear_group_launch")
+
+    def launch_host(self, host_in: torch.Tensor, dev_in: torch.Tensor, dev_out: torch.Tensor | None = None,
+                    host_out: torch.Tensor | None = None) -> None:
+        """One step for a caller with host tensors (izb_linear_group_launch_host): `host_in` -> `dev_in` (the buffer
+        the problems' x pointers lie in), the launch, `dev_out` -> `host_out`; returns when the results are in host
+        memory.  Without `dev_out` / `host_out` nothing is copied back: for a group whose y pointers already lie in
+        page-locked host memory."""
+        assert not host_in.is_cuda and dev_in.is_cuda and host_in.is_contiguous() and dev_in.is_contiguous()
+        in_bytes = host_in.numel() * host_in.element_size()
+        assert in_bytes <= dev_in.numel() * dev_in.element_size()
+        out_bytes, p_dev_out, p_host_out = 0, None, None
+        if host_out is not None:
+            assert dev_out is not None and dev_out.is_cuda and not host_out.is_cuda and dev_out.is_contiguous() and host_out.is_contiguous()
+            out_bytes = host_out.numel() * host_out.element_size()
+            assert out_bytes <= dev_out.numel() * dev_out.element_size()
+            p_dev_out, p_host_out = C.c_void_p(dev_out.data_ptr()), C.c_void_p(host_out.data_ptr())
+        L.check(L.lib().izb_linear_group_launch_host(self.ctx.handle, _stream(), C.c_void_p(self.host_plan.data_ptr()),
+                                                     C.c_void_p(self.dev_plan.data_ptr()), C.c_void_p(host_in.data_ptr()),
+                                                     C.c_void_p(dev_in.data_ptr()), in_bytes, p_dev_out, p_host_out, out_bytes),
+                "izb_linear_group_launch_host")

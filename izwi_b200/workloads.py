@@ -155,18 +155,24 @@ def make_linear_stack(shape: DecoderShape, fmt: str, m: int, device: torch.devic
     return LinearStack(shape, fmt, m, weights, acts, outs, acts_buf, outs_buf)
 
 
-def stack_group(stack: LinearStack):
-    """All projections of the stack as one grouped persistent launch."""
+def stack_group(stack: LinearStack, host_outs: torch.Tensor | None = None):
+    """All projections of the stack as one grouped persistent launch.  `host_outs`: a page-locked host tensor shaped
+    like `stack.outs_buf`; the launch then stores every result straight into it (no copy back afterwards)."""
     from . import ops
     import ctypes as C
     from . import _lib as L
     probs, scratch = [], []
+    if host_outs is not None:
+        assert host_outs.is_pinned() and host_outs.shape == stack.outs_buf.shape and host_outs.dtype == stack.outs_buf.dtype
     for wl, al, ol in zip(stack.weights, stack.acts, stack.outs):
         for (_, n, k), w, x, y in zip(stack.shape.projections, wl, al, ol):
+            if host_outs is not None:
+                at = (y.data_ptr() - stack.outs_buf.data_ptr()) // y.element_size()
+                y = host_outs[at:at + y.numel()].view(y.shape)
             a = ops.linear_args(x, w, stack.fmt, n, k, y)
             need = L.lib().izb_linear_workspace_bytes_args(C.byref(a))
             if need:  # 3..16 tokens over block formats: room for the activations as the integer kernel reads them
                 scratch.append(torch.empty(need, device=x.device, dtype=torch.uint8))
                 a = ops.linear_args(x, w, stack.fmt, n, k, y, workspace=scratch[-1])
             probs.append(a)
-    return ops.LinearGroup(probs, stack.acts_buf.device, keepalive=(stack, scratch))
+    return ops.LinearGroup(probs, stack.acts_buf.device, keepalive=(stack, scratch, host_outs))

@@ -54,3 +54,53 @@ def test_group_plan_rejects_mixed_formats_and_large_m(cuda):
     with pytest.raises(IzbError) as e:
         ops.LinearGroup([ops.linear_args(xl, w, "bf16", 8, 256, yl)], cuda)
     assert e.value.status == -2
+
+
+def test_group_step_with_host_buffers(cuda):
+    """izb_linear_group_launch_host: activations from page-locked host memory, results back in host memory when the
+    call returns; every step sees that step's inputs."""
+    from izwi_b200 import ops
+    rng = np.random.default_rng(61)
+    shapes = [(1024, 512), (512, 1024), (768, 512)]
+    acts = torch.zeros(sum(k for _, k in shapes), device=cuda, dtype=torch.bfloat16)
+    outs = torch.zeros(sum(n for n, _ in shapes), device=cuda, dtype=torch.bfloat16)
+    probs, keep, weights = [], [], []
+    xo = yo = 0
+    for n, k in shapes:
+        raw, wf = make_weight_np("q8_0", n, k, rng)
+        wd = upload_weight("q8_0", raw, cuda)
+        probs.append(ops.linear_args(acts[xo:xo + k].view(1, k), wd, "q8_0", n, k, outs[yo:yo + n].view(1, n)))
+        keep.append(wd)
+        weights.append(wf)
+        xo, yo = xo + k, yo + n
+    group = ops.LinearGroup(probs, cuda, keepalive=keep)
+    h_in = torch.empty(acts.shape, dtype=torch.bfloat16).pin_memory()
+    h_out = torch.empty(outs.shape, dtype=torch.bfloat16).pin_memory()
+    for step in range(3):
+        x = bf16_np(rng.normal(0, 1, acts.shape[0]))
+        h_in.copy_(torch.from_numpy(x).to(torch.bfloat16))
+        h_out.fill_(float("nan"))
+        group.launch_host(h_in, acts, outs, h_out)  # no synchronisation here: the call returns with the results
+        got = h_out.float().numpy()
+        xo = yo = 0
+        for (n, k), wf in zip(shapes, weights):
+            assert_matmul_close(torch.from_numpy(got[yo:yo + n][None, :]), o.linear(x[None, xo:xo + k], wf), f"host step {step} N={n}")
+            xo, yo = xo + k, yo + n
+    group.ctx.check()
+    # the same problems with their y pointers in page-locked host memory: the kernel stores there, nothing is copied back
+    direct = torch.empty(outs.shape, dtype=torch.bfloat16).pin_memory()
+    probs2, yo = [], 0
+    for (n, k), p_dev in zip(shapes, probs):
+        a2 = ops.linear_args(acts[:k].view(1, k), keep[0], "q8_0", n, k, direct[yo:yo + n].view(1, n))
+        a2.x, a2.w = p_dev.x, p_dev.w
+        probs2.append(a2)
+        yo += n
+    group2 = ops.LinearGroup(probs2, cuda, keepalive=keep)
+    direct.fill_(float("nan"))
+    group2.launch_host(h_in, acts)
+    assert torch.equal(direct, h_out)
+    import ctypes as C
+    from izwi_b200 import _lib as L
+    st = L.lib().izb_linear_group_launch_host(group.ctx.handle, None, C.c_void_p(group.host_plan.data_ptr()), C.c_void_p(group.dev_plan.data_ptr()),
+                                              None, C.c_void_p(acts.data_ptr()), 16, C.c_void_p(outs.data_ptr()), C.c_void_p(h_out.data_ptr()), 16)
+    assert st == L.IZB_ERR_BAD_ARG
