@@ -508,8 +508,8 @@ def measure_attention_cases(device):
     return out
 
 
-def measure_decode_token_cases(device, shape=None, variants=None):
-    """A whole greedy decode token of a Qwen3-0.6B-shaped model with Q8_0 projections (embedding, 28
+def measure_decode_token_cases(device, shape=None, variants=None, fmt="q8_0"):
+    """A whole greedy decode token of a Qwen3-0.6B-shaped model with Q8_0 (or Q4_K) projections (embedding, 28
     layers of norm / fused QKV / q,k norm / RoPE / KV append / GQA attention / O / norm / gate-up /
     SiLU-multiply / down, final norm, lm_head over 151,936 tokens, arg-max), captured once in a CUDA
     graph at a fixed context length and replayed: what the linear stack of the headline sits in."""
@@ -521,19 +521,21 @@ def measure_decode_token_cases(device, shape=None, variants=None):
         # the 0.6B shape (launch- and latency-bound: 0.64 GB of weights per token) and, for the one-launch kernel and
         # the fused chain, the 8B shape (8.7 GB per token: bandwidth starts to matter)
         return (measure_decode_token_cases(device, wl.QWEN3_0_6B, ((512, "one_launch"), (4096, "one_launch"), (512, True), (4096, True), (512, False)))
+                + measure_decode_token_cases(device, wl.QWEN3_0_6B, ((512, "one_launch"), (512, True)), fmt="q4_k")
                 + measure_decode_token_cases(device, wl.QWEN3_8B, ((512, "one_launch"), (512, True))))
     gen = torch.Generator(device=device).manual_seed(6)
     vocab, hid, qd, kd = 151936, shape.hidden, shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
     ones = lambda n: (1.0 + 0.1 * torch.randn(n, device=device, generator=gen)).to(torch.bfloat16)  # noqa: E731
     layers = []
+    make_w = wl.make_q8_0_weight if fmt == "q8_0" else wl.make_q4_k_weight
     for _ in range(shape.layers):
         layers.append(decoder.Qwen3DecoderLayer(decoder.Qwen3LayerWeights(
-            "q8_0", hid, shape.q_heads, shape.kv_heads, shape.head_dim, shape.intermediate, ones(hid), ones(hid),
-            ones(shape.head_dim), ones(shape.head_dim), wl.make_q8_0_weight(qd + 2 * kd, hid, gen),
-            wl.make_q8_0_weight(hid, qd, gen), wl.make_q8_0_weight(2 * shape.intermediate, hid, gen),
-            wl.make_q8_0_weight(hid, shape.intermediate, gen))))
+            fmt, hid, shape.q_heads, shape.kv_heads, shape.head_dim, shape.intermediate, ones(hid), ones(hid),
+            ones(shape.head_dim), ones(shape.head_dim), make_w(qd + 2 * kd, hid, gen),
+            make_w(hid, qd, gen), make_w(2 * shape.intermediate, hid, gen),
+            make_w(hid, shape.intermediate, gen))))
     embed = (torch.randn(vocab, hid, device=device, generator=gen) * 0.5).to(torch.bfloat16)
-    model = decoder.Qwen3Decoder(embed, layers, ones(hid), wl.make_q8_0_weight(vocab, hid, gen), "q8_0")
+    model = decoder.Qwen3Decoder(embed, layers, ones(hid), make_w(vocab, hid, gen), fmt)
     weight_bytes = sum(w.numel() for l in layers for w in (l.w.qkv, l.w.o, l.w.gate_up, l.w.down)) + model.lm_head.numel()
     out = []
     for ctx_len, fused in variants:
@@ -542,7 +544,7 @@ def measure_decode_token_cases(device, shape=None, variants=None):
         one_launch = fused == "one_launch"
         for l in layers:
             l.fused_linear = fused
-            l.fusion_max_tokens = ops.linear_fusion_max_tokens("q8_0") if fused else 0
+            l.fusion_max_tokens = ops.linear_fusion_max_tokens(fmt) if fused else 0
         # the cache contents depend on the context length only, so the fused and unfused builds of one
         # length see the same model state and must pick the same token
         cgen = torch.Generator(device=device).manual_seed(7000 + ctx_len)
@@ -572,7 +574,7 @@ def measure_decode_token_cases(device, shape=None, variants=None):
         ops.Context.get(device.index).check()
         kv_bytes = shape.layers * 2 * shape.kv_heads * (ctx_len + 1) * shape.head_dim * 2
         gbs = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
-        out.append({"workload": f"{shape.name}-q8_0-greedy-token-ctx{ctx_len}", "ms_per_token": round(ms, 4),
+        out.append({"workload": f"{shape.name}-{fmt}-greedy-token-ctx{ctx_len}", "ms_per_token": round(ms, 4),
                     "tokens_per_s": round(1e3 / ms, 1), "kernels_per_token": int(launches), "fused_projections": fused,
                     "weight_and_kv_gbs": round(gbs, 1), "hbm_frac_of_measured": round(gbs / peak_bw, 4),
                     "next_token": int(nxt[0])})
