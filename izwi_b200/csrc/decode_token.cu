@@ -26,6 +26,7 @@
 // the CTA leaves.
 #include <algorithm>
 #include <cstddef>
+#include <cstdlib>
 #include <cstring>
 
 #include "gemv_dot.cuh"
@@ -169,39 +170,89 @@ struct DtRingResult {
     DtRing ring;
     int ok;
 };
-__device__ __noinline__ DtRingResult produce_phase_call(DtShared* shp, uint32_t ring0, DtRing R, int n_slots, const CUtensorMap* map, int N, int K,
-                                                        int S, int w_row_bytes) {
+// Shapes of the five kinds of projection phase, by value (a call cannot name the parameter space).
+struct DtPhases {
+    int tiles[5], boxes[5], S[5];  // qkv, o, gate/up, down of a layer; lm_head
+    int n_layers;
+};
+// A position in this CTA's walk over every weight box of the token: layer, projection, unit, box.
+struct DtCursor {
+    int l, j, u, tile, b, b1;
+    bool done;
+};
+__device__ __forceinline__ void dt_phase_dims(const DtPhases& ph, int j, int& tiles, int& boxes, int& S) {
+    switch (j) {
+        case 0: tiles = ph.tiles[0]; boxes = ph.boxes[0]; S = ph.S[0]; break;
+        case 1: tiles = ph.tiles[1]; boxes = ph.boxes[1]; S = ph.S[1]; break;
+        case 2: tiles = ph.tiles[2]; boxes = ph.boxes[2]; S = ph.S[2]; break;
+        case 3: tiles = ph.tiles[3]; boxes = ph.boxes[3]; S = ph.S[3]; break;
+        default: tiles = ph.tiles[4]; boxes = ph.boxes[4]; S = ph.S[4]; break;
+    }
+}
+// Makes the cursor point at a box: skips phases in which this CTA has no unit (left).
+__device__ __forceinline__ void dt_cursor_settle(const DtPhases& ph, DtCursor& c) {
+    while (!c.done) {
+        int tiles, boxes, S;
+        dt_phase_dims(ph, c.j, tiles, boxes, S);
+        if (c.u < tiles * S) {
+            const DtUnit un = dt_unit(c.u, S, boxes);
+            c.tile = un.tile;
+            c.b = un.b0;
+            c.b1 = un.b1;
+            if (c.b < c.b1) return;
+            c.u += static_cast<int>(gridDim.x);  // an empty slice (more slices than boxes): next unit
+            continue;
+        }
+        // next phase: lm_head (j = 4) follows the last layer's down projection
+        if (c.j == 4) {
+            c.done = true;
+        } else if (c.j == 3) {
+            ++c.l;
+            c.j = c.l == ph.n_layers ? 4 : 0;
+        } else {
+            ++c.j;
+        }
+        c.u = static_cast<int>(blockIdx.x);
+    }
+}
+__device__ __forceinline__ void dt_cursor_next(const DtPhases& ph, DtCursor& c) {
+    if (++c.b < c.b1) return;
+    c.u += static_cast<int>(gridDim.x);
+    dt_cursor_settle(ph, c);
+}
+__device__ __forceinline__ const CUtensorMap* dt_cursor_map(const CUtensorMap* maps, const DtCursor& c) {
+    return maps + (c.j == 4 ? 4 * c.l : 4 * c.l + c.j);  // at lm_head l == n_layers
+}
+// The producer lane's whole job: every box of this CTA, in the consumers' order, into the ring.  (Asking boxes
+// into L2 ahead of the ring with cp.async.bulk.prefetch.tensor, so that HBM streams on while the ring is full,
+// was measured and is not here: 12 boxes ahead changed nothing, 24 and more cost 4 % at the 0.6B shape and 22 % at 8B.)
+__device__ __noinline__ DtRingResult produce_all_call(DtShared* shp, uint32_t ring0, int n_slots, const CUtensorMap* maps,
+                                                      const DtPhases ph, int w_row_bytes, int lm_row_bytes) {
     DtShared& sh = *shp;
-    const int boxes = K / 256, tiles = N / DT_TILE_ROWS, units = tiles * S;
     volatile int* abort_flag = &sh.abort_flag;
     const uint32_t full0 = smem_u32(&sh.full[0]), empty0 = smem_u32(&sh.empty[0]);
     DtRingResult out;
     out.ok = 1;
-    for (int u = static_cast<int>(blockIdx.x); u < units && out.ok; u += static_cast<int>(gridDim.x)) {
-        const DtUnit un = dt_unit(u, S, boxes);
-        for (int b = un.b0; b < un.b1; ++b) {
-            if (R.issued >= n_slots && !mbar_wait_bounded_relaxed(empty0 + 8u * R.slot, R.phase ^ 1u, abort_flag)) {
-                out.ok = 0;
-                break;
-            }
-            const uint32_t fbar = full0 + 8u * R.slot;
-            mbar_expect_tx(fbar, static_cast<uint32_t>(DT_TILE_ROWS * w_row_bytes));
-            tma_load_3d(ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES, map, 0, un.tile * DT_TILE_ROWS, b, fbar);
-            ++R.issued;
-            if (++R.slot == n_slots) {
-                R.slot = 0;
-                R.phase ^= 1u;
-            }
+    DtRing R{0, 0u, 0};
+    DtCursor cur{0, 0, static_cast<int>(blockIdx.x), 0, 0, 0, false};
+    dt_cursor_settle(ph, cur);
+    while (!cur.done) {
+        if (R.issued >= n_slots && !mbar_wait_bounded_relaxed(empty0 + 8u * R.slot, R.phase ^ 1u, abort_flag)) {
+            out.ok = 0;
+            break;
+        }
+        const uint32_t fbar = full0 + 8u * R.slot;
+        mbar_expect_tx(fbar, static_cast<uint32_t>(DT_TILE_ROWS * (cur.j == 4 ? lm_row_bytes : w_row_bytes)));
+        tma_load_3d(ring0 + static_cast<uint32_t>(R.slot) * DT_SLOT_BYTES, dt_cursor_map(maps, cur), 0, cur.tile * DT_TILE_ROWS, cur.b, fbar);
+        dt_cursor_next(ph, cur);
+        ++R.issued;
+        if (++R.slot == n_slots) {
+            R.slot = 0;
+            R.phase ^= 1u;
         }
     }
     out.ring = R;
     return out;
-}
-__device__ __forceinline__ bool produce_phase(const DtParams& P, DtShared& sh, uint32_t ring0, DtRing& R, const CUtensorMap* map, int N, int K,
-                                              int S, int w_row_bytes) {
-    const DtRingResult r = produce_phase_call(&sh, ring0, R, P.n_slots, map, N, K, S, w_row_bytes);
-    R = r.ring;
-    return r.ok != 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -625,15 +676,16 @@ __global__ void __launch_bounds__(DT_THREADS, 1) qwen3_decode_token_kernel(const
     if (warp == DT_CONSUMER_WARPS) {
         // ---------------- producer (one lane): every projection's boxes, in the consumers' order ----------------
         if (lane != 0) return;
-        bool ok = true;
-        for (int l = 0; l < A.n_layers && ok; ++l) {
-            const CUtensorMap* m = P.maps + 4 * l;
-            ok = produce_phase(P, sh, ring0, R, m + 0, n_qkv, A.hidden, P.s_qkv, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 1, A.hidden, q_dim, P.s_o, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 2, 2 * A.intermediate, A.hidden, P.s_gu, w_row);
-            if (ok) ok = produce_phase(P, sh, ring0, R, m + 3, A.hidden, A.intermediate, P.s_down, w_row);
-        }
-        if (ok) ok = produce_phase(P, sh, ring0, R, P.maps + 4 * A.n_layers, A.vocab, A.hidden, 1, lm_row);
+        DtPhases ph;
+        ph.tiles[0] = n_qkv / DT_TILE_ROWS; ph.boxes[0] = A.hidden / 256; ph.S[0] = P.s_qkv;
+        ph.tiles[1] = A.hidden / DT_TILE_ROWS; ph.boxes[1] = q_dim / 256; ph.S[1] = P.s_o;
+        ph.tiles[2] = 2 * A.intermediate / DT_TILE_ROWS; ph.boxes[2] = A.hidden / 256; ph.S[2] = P.s_gu;
+        ph.tiles[3] = A.hidden / DT_TILE_ROWS; ph.boxes[3] = A.intermediate / 256; ph.S[3] = P.s_down;
+        ph.tiles[4] = A.vocab / DT_TILE_ROWS; ph.boxes[4] = A.hidden / 256; ph.S[4] = 1;
+        ph.n_layers = A.n_layers;
+        const DtRingResult pr = produce_all_call(&sh, ring0, P.n_slots, P.maps, ph, w_row, lm_row);
+        R = pr.ring;
+        const bool ok = pr.ok != 0;
         // the copies still in flight land before the CTA's shared memory goes away
         {
             const long long first = R.issued > P.n_slots ? R.issued - P.n_slots : 0;
@@ -965,6 +1017,7 @@ int dt_launch(izb_ctx* ctx, cudaStream_t s, DtParams& p) {
     slots = std::min(slots, DT_MAX_SLOTS);
     if (slots < 2) return IZB_ERR_UNSUPPORTED;
     p.n_slots = slots;
+
     const int smem = slots * DT_SLOT_BYTES + DT_SCRATCH_BYTES + 1024;
     static std::atomic<int> smem_set[IZB_MAX_DEVICES];
     if (smem_set[ctx->device].load(std::memory_order_relaxed) < smem) {
