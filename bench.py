@@ -664,7 +664,14 @@ def measure_moe_cases(device):
         step()
         per_layer = ctx.launch_count - l0
         state["i"] = 0
-        ms = _time_call(step, 30)
+        ms_eager = _time_call(step, 30)
+        # a decode loop replays its launches from a CUDA graph: the three layers in one graph, time per layer
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for lay in layers:
+                lay.forward(x)
+        ms = _time_call(graph.replay, 30) / len(layers)
+        del graph
         lay = layers[0]
         y, logits, idx, wts = lay.forward(x)
         touched = int(torch.unique(idx).numel())
@@ -673,7 +680,7 @@ def measure_moe_cases(device):
         out.append({"workload": f"qwen3-30b-a3b-moe-layer-T{t}", "ms": round(ms, 4), "experts_touched": touched,
                     "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "tensor_frac": round(flops / (ms * 1e-3) / 1e12 / peak_tf, 4),
                     "weight_gbs": round(wbytes / (ms * 1e-3) / 1e9, 1), "hbm_frac_of_measured": round(wbytes / (ms * 1e-3) / 1e9 / peak_bw, 4),
-                    "kernels_per_layer": int(per_layer),
+                    "kernels_per_layer": int(per_layer), "launch": "CUDA-graph replay of three layers", "ms_eager_launches": round(ms_eager, 4),
                     "parity": moe_parity(x, y, idx, wts, lambda: logits, lay.w_router, lay.router_bias, lay.w_gate_up,
                                          lay.w_down, k)})
     ctx.check()

@@ -165,7 +165,33 @@ __device__ __forceinline__ float dot8(uint4 a, uint4 b, float acc) {
     return acc;
 }
 
-// hidden[p][i] = silu(gate_i . x_t) * (up_i . x_t) for pair p = (t, j), expert idx[p]; grid (outputs / 8, pairs)
+// hidden[p][i] = silu(gate_i . x_t) * (up_i . x_t) for pair p = (t, j), expert idx[p]; grid (outputs / 8, pairs).
+// A warp owns output i: its gate row and its up row, sixteen 16-byte loads per lane and pass of 2048 values of H,
+// all issued before the first product.  The loads of the first pass go out before the token's row is staged in
+// shared memory, so that the two trips to memory overlap.
+constexpr int MOE_SMALL_HB = 8;  // 16-byte units per lane, row and pass
+struct MoeSmallRows {
+    uint4 g[MOE_SMALL_HB], u[MOE_SMALL_HB];
+};
+__device__ __forceinline__ void moe_small_load(MoeSmallRows& r, const uint4* g, const uint4* u, int c0, int h_units, int lane) {
+#pragma unroll
+    for (int m = 0; m < MOE_SMALL_HB; ++m) {
+        const int c = c0 + 32 * m + lane;
+        r.g[m] = c < h_units ? g[c] : make_uint4(0u, 0u, 0u, 0u);
+        r.u[m] = c < h_units ? u[c] : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+__device__ __forceinline__ void moe_small_dot(const MoeSmallRows& r, const uint4* xs, int c0, int h_units, int lane, float& ag, float& au) {
+#pragma unroll
+    for (int m = 0; m < MOE_SMALL_HB; ++m) {
+        const int c = c0 + 32 * m + lane;
+        if (c < h_units) {
+            const uint4 xv = xs[c];
+            ag = dot8(r.g[m], xv, ag);
+            au = dot8(r.u[m], xv, au);
+        }
+    }
+}
 __global__ void __launch_bounds__(256)
     moe_small_gate_up_kernel(const uint4* __restrict__ x, long long ldx_units, const int* __restrict__ idx,
                              const uint4* __restrict__ w_gate_up, int h_units, int I, int top_k, __nv_bfloat16* __restrict__ hidden) {
@@ -173,19 +199,25 @@ __global__ void __launch_bounds__(256)
     izb::pdl_launch_dependents();
     izb::pdl_wait();
     const int p = blockIdx.y, t = p / top_k, e = idx[p];
-    for (int c = threadIdx.x; c < h_units; c += blockDim.x) xs[c] = x[static_cast<long long>(t) * ldx_units + c];
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint4* base = w_gate_up + static_cast<long long>(e) * 2 * I * h_units;
-    for (int i = blockIdx.x * 8 + warp; i < I; i += gridDim.x * 8) {
+    int i = blockIdx.x * 8 + warp;
+    MoeSmallRows r;
+    bool loaded = false;  // the first pass of the first row is in flight while the token's row is staged
+    if (i < I) {
+        moe_small_load(r, base + static_cast<long long>(i) * h_units, base + static_cast<long long>(I + i) * h_units, 0, h_units, lane);
+        loaded = true;
+    }
+    for (int c = threadIdx.x; c < h_units; c += blockDim.x) xs[c] = x[static_cast<long long>(t) * ldx_units + c];
+    __syncthreads();
+    for (; i < I; i += gridDim.x * 8) {
         const uint4* g = base + static_cast<long long>(i) * h_units;
         const uint4* u = base + static_cast<long long>(I + i) * h_units;
         float ag = 0.f, au = 0.f;
-#pragma unroll 8
-        for (int c = lane; c < h_units; c += 32) {  // sixteen 16-byte loads in flight per lane
-            const uint4 gv = g[c], uv = u[c], xv = xs[c];
-            ag = dot8(gv, xv, ag);
-            au = dot8(uv, xv, au);
+        for (int c0 = 0; c0 < h_units; c0 += 32 * MOE_SMALL_HB) {
+            if (!loaded) moe_small_load(r, g, u, c0, h_units, lane);
+            loaded = false;
+            moe_small_dot(r, xs, c0, h_units, lane, ag, au);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -196,27 +228,58 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-// y[t][n] = sum_j wts[t][j] * (down_{e_j}[n] . hidden[t][j]); grid (outputs / 8, tokens)
+// y[t][n] = sum_j wts[t][j] * (down_{e_j}[n] . hidden[t][j]); grid (outputs / 8, tokens).
+// A warp owns one output row n.  Its weights are top_k short rows (I values each) in top_k different matrices: the
+// loads of four experts' rows (up to sixteen 16-byte loads per lane) are issued together, before the first product,
+// so that a row costs two trips to memory instead of one per expert; the expert ids and routing weights are asked
+// for before the token's hidden rows are staged, so that those trips overlap too.
+constexpr int MOE_SMALL_JB = 4;  // experts per batch of loads
+constexpr int MOE_SMALL_CB = 4;  // 16-byte units per lane and expert in a batch (128 units = 1024 values of I per pass)
 __global__ void __launch_bounds__(256)
     moe_small_down_kernel(const uint4* __restrict__ hidden, const int* __restrict__ idx, const float* __restrict__ wts,
                           const uint4* __restrict__ w_down, int H, int i_units, int top_k, __nv_bfloat16* __restrict__ y) {
     extern __shared__ uint4 hs[];  // [top_k][i_units]
+    __shared__ int s_e[32];
+    __shared__ float s_w[32];
     izb::pdl_launch_dependents();
     izb::pdl_wait();
     const int t = blockIdx.y;
+    if (threadIdx.x < top_k && threadIdx.x < 32) {
+        s_e[threadIdx.x] = idx[t * top_k + threadIdx.x];
+        s_w[threadIdx.x] = wts[t * top_k + threadIdx.x];
+    }
     for (int c = threadIdx.x; c < top_k * i_units; c += blockDim.x) hs[c] = hidden[static_cast<long long>(t) * top_k * i_units + c];
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int n = blockIdx.x * 8 + warp; n < H; n += gridDim.x * 8) {
         float out = 0.f;
-#pragma unroll 8
-        for (int j = 0; j < top_k; ++j) {  // the rows of all the token's experts are asked for together
-            const int e = idx[t * top_k + j];
-            const uint4* row = w_down + (static_cast<long long>(e) * H + n) * i_units;
-            float acc = 0.f;
-#pragma unroll 4
-            for (int c = lane; c < i_units; c += 32) acc = dot8(row[c], hs[j * i_units + c], acc);
-            out = fmaf(wts[t * top_k + j], acc, out);
+        for (int j0 = 0; j0 < top_k; j0 += MOE_SMALL_JB) {
+            float acc[MOE_SMALL_JB] = {0.f, 0.f, 0.f, 0.f};
+            for (int c0 = 0; c0 < i_units; c0 += 32 * MOE_SMALL_CB) {
+                uint4 wv[MOE_SMALL_JB][MOE_SMALL_CB];
+#pragma unroll
+                for (int jj = 0; jj < MOE_SMALL_JB; ++jj) {
+                    const int j = min(j0 + jj, top_k - 1);  // past the last expert: its row again, weight 0 below
+                    const uint4* row = w_down + (static_cast<long long>(s_e[j]) * H + n) * i_units;
+#pragma unroll
+                    for (int m = 0; m < MOE_SMALL_CB; ++m) {
+                        const int c = c0 + 32 * m + lane;
+                        wv[jj][m] = c < i_units ? row[c] : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < MOE_SMALL_JB; ++jj) {
+                    const int j = min(j0 + jj, top_k - 1);
+#pragma unroll
+                    for (int m = 0; m < MOE_SMALL_CB; ++m) {
+                        const int c = c0 + 32 * m + lane;
+                        if (c < i_units) acc[jj] = dot8(wv[jj][m], hs[j * i_units + c], acc[jj]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < MOE_SMALL_JB; ++jj)
+                if (j0 + jj < top_k) out = fmaf(s_w[j0 + jj], acc[jj], out);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) out += __shfl_xor_sync(0xFFFFFFFFu, out, o);
@@ -479,7 +542,7 @@ bool moe_small_path(const izb_ctx* ctx, const izb_moe_args* a, int64_t pairs) {
         return e ? std::atoi(e) : 32;
     }();
     if (pairs > max_pairs) return false;
-    if (a->H % 8 != 0 || a->I % 8 != 0) return false;
+    if (a->H % 8 != 0 || a->I % 8 != 0 || a->top_k > 32) return false;
     if (!izb_aligned(a->x, 16) || !izb_aligned(a->w_gate_up, 16) || !izb_aligned(a->w_down, 16) || !izb_aligned(a->y, 2)) return false;
     return a->H * 2 <= 48 * 1024 && static_cast<int64_t>(a->top_k) * a->I * 2 <= 48 * 1024 && ctx != nullptr;
 }
