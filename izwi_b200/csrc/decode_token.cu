@@ -21,6 +21,11 @@
 // stream, RmsNorm, SiLU-multiply, the merge of the attention splits) and convert to the 16-bit block
 // fixed point that the integer dot products read (gemv_dot.cuh).
 //
+// Code size: the layer loop is straight-line code that every CTA fetches once per layer.  What several phases share
+// (the per-unit consumer, the producer's walk, the norm prologue, the grid barrier, the attention unit) is a call
+// (__noinline__, state passed by value) rather than an inline copy per phase: measured 4 % faster, and `no
+// instruction` stalls halved.
+//
 // Every wait is bounded: ring barriers and the grid barrier give up after IZB_WAIT_LIMIT_CLOCKS, raise
 // the workspace's abort word (which every other wait also watches) and a context status word, and
 // the CTA leaves.
