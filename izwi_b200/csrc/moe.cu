@@ -81,6 +81,9 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int T, int E, 
 // CTA of a token tile to finish (a counter per tile, left at zero again) picks the experts of its 16
 // tokens, one warp per token.  NG x KS = 8 warps: (4, 2) in general, (1, 8) for a single token tile,
 // where E / 8 CTAs each stream eight rows of the weight instead of E / 32 CTAs thirty-two.
+// (A single token tile as one cluster of eight CTAs, the logits meeting in CTA 0's shared memory instead of the
+// counter and the last CTA's trip to L2, was measured: 0.0336 ms per one-token layer against 0.0307, since eight
+// CTAs halve the loads in flight per expert row.)
 constexpr int ROUTE_TOKENS = 16;
 constexpr int ROUTE_WARPS = 8;
 constexpr int ROUTE_MAX_TILES = 1024;

@@ -216,3 +216,27 @@ def test_fused_router_ties_go_to_the_lowest_expert(cuda):
     got = idx.cpu().numpy()
     assert (got[0::2] == np.arange(40, 44)).all() and (got[1::2] == np.arange(0, 4)).all()
     assert np.allclose(wts.cpu().numpy(), 0.25)
+
+
+@pytest.mark.parametrize("t,e,h,k", [(1, 128, 2048, 8), (16, 128, 2048, 8), (9, 40, 512, 4), (2, 8, 256, 8)])
+def test_single_token_tile_router(cuda, t, e, h, k):
+    """A decode step's router (one token tile: E / 8 CTAs, the last one to finish picks the experts): logits within
+    the gates, choice bit-exact against the top-k of the logits written, ties to the lowest expert, and nothing
+    left behind that a second launch trips over (the tile counter returns to zero)."""
+    from izwi_b200 import moe, ops
+    rng = np.random.default_rng(2000 + t + e)
+    x = bf16_np(rng.normal(0, 1, (t, h)))
+    wr = bf16_np(rng.normal(0, 1.0 / np.sqrt(h), (e, h)))
+    wr[3] = wr[1]  # two identical experts: equal logits, the lower id first
+    br = bf16_np(rng.normal(0, 0.5, e))
+    br[3] = br[1]
+    up = lambda a: torch.from_numpy(a).to(cuda).to(torch.bfloat16)  # noqa: E731
+    for _ in range(2):
+        logits, idx, wts = moe.route(up(x), up(wr), up(br), k)
+        ops.Context.get(0).check()
+        assert_matmul_close(logits, o.moe_router_logits(x, wr, br), f"router logits T={t} E={e}")
+        got_logits = logits.cpu().numpy()
+        assert np.array_equal(got_logits[:, 1], got_logits[:, 3])
+        want_idx, want_w = o.moe_topk(got_logits, k)
+        assert np.array_equal(idx.cpu().numpy(), want_idx)
+        assert np.abs(wts.cpu().numpy() - want_w).max() < 1e-6
