@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32)
         const uint4* xb = reinterpret_cast<const uint4*>(x + r_hi * ldx) + t4;
         const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(min(n0 + g, E - 1)) * H) + t4;
         const int n_blk = H / 32;
-#pragma unroll 4
+#pragma unroll(KS == 8 ? 8 : 4)  // a single token tile: the eight steps of H = 2048 in one batch of loads
         for (int b = ks; b < n_blk; b += KS) {
             const uint4 a_lo = xa[b * 4], a_hi = xb[b * 4], bw = wr[b * 4];
             mma_bf16_16816(acc, a_lo.x, a_hi.x, a_lo.y, a_hi.y, bw.x, bw.y);
@@ -257,7 +257,9 @@ __global__ void __launch_bounds__(256)
     for (int n = blockIdx.x * 8 + warp; n < H; n += gridDim.x * 8) {
         float out = 0.f;
         for (int j0 = 0; j0 < top_k; j0 += MOE_SMALL_JB) {
-            float acc[MOE_SMALL_JB] = {0.f, 0.f, 0.f, 0.f};
+            float acc[MOE_SMALL_JB];
+#pragma unroll
+            for (int jj = 0; jj < MOE_SMALL_JB; ++jj) acc[jj] = 0.f;
             for (int c0 = 0; c0 < i_units; c0 += 32 * MOE_SMALL_CB) {
                 uint4 wv[MOE_SMALL_JB][MOE_SMALL_CB];
 #pragma unroll
