@@ -101,6 +101,16 @@ def test_group_step_with_host_buffers(cuda):
     assert torch.equal(direct, h_out)
     import ctypes as C
     from izwi_b200 import _lib as L
+    # the whole step in the C call, as a C or Rust caller makes it: copy in, launch, copy out, wait
+    acts.zero_()
+    copied = torch.empty(outs.shape, dtype=torch.bfloat16).pin_memory()
+    copied.fill_(float("nan"))
+    st = L.lib().izb_linear_group_launch_host(group.ctx.handle, C.c_void_p(torch.cuda.current_stream().cuda_stream),
+                                              C.c_void_p(group.host_plan.data_ptr()), C.c_void_p(group.dev_plan.data_ptr()),
+                                              C.c_void_p(h_in.data_ptr()), C.c_void_p(acts.data_ptr()), h_in.numel() * 2,
+                                              C.c_void_p(outs.data_ptr()), C.c_void_p(copied.data_ptr()), copied.numel() * 2)
+    assert st == 0
+    assert torch.equal(copied, h_out)
     st = L.lib().izb_linear_group_launch_host(group.ctx.handle, None, C.c_void_p(group.host_plan.data_ptr()), C.c_void_p(group.dev_plan.data_ptr()),
                                               None, C.c_void_p(acts.data_ptr()), 16, C.c_void_p(outs.data_ptr()), C.c_void_p(h_out.data_ptr()), 16)
     assert st == L.IZB_ERR_BAD_ARG
