@@ -89,6 +89,10 @@ __device__ __forceinline__ float silu(float x) {
     return fmaf(0.5f * x, t, 0.5f * x);
 }
 
+// EPI: the epilogue, a compile-time choice: the epilogue loop of an instantiation holds its own activation only
+// (the erf / tanh / sigmoid bodies are 32-fold unrolled; all of them behind run-time branches in one loop made
+// the epilogue warps wait for instruction fetch).
+template <int EPI>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ GemmParams p, int n_stages, int* status) {
     extern __shared__ __align__(1024) uint8_t dyn_smem[];
@@ -97,8 +101,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bn = p.bn;
     // gated epilogues: the tile's accumulator holds the matching columns of both row halves of W side by side
-    const bool swiglu = p.epilogue == GEMM_EPI_SWIGLU || p.epilogue == GEMM_EPI_GLU;
-    const bool glu = p.epilogue == GEMM_EPI_GLU;
+    constexpr bool swiglu = EPI == GEMM_EPI_SWIGLU || EPI == GEMM_EPI_GLU;
+    constexpr bool glu = EPI == GEMM_EPI_GLU;
     const int out_cols = swiglu ? bn / 2 : bn;  // output columns one tile produces
     const uint32_t a_bytes = GT_BM * GT_BK * 2, b_bytes = static_cast<uint32_t>(bn) * GT_BK * 2;
     const uint32_t stage_bytes = a_bytes + b_bytes;
@@ -267,7 +271,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                 const int col0 = col_base + cc;
                 // The mode tests sit outside the element loops on purpose: inside, the compiler turns
                 // them into selects and evaluates erf and exp for every element of every mode.
-                if (swiglu) {
+                if constexpr (swiglu) {
                     float u[32];
                     tc_ld_32x32(t_row + static_cast<uint32_t>(bn / 2 + cc), u);
                     if (bias) {
@@ -279,7 +283,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                             }
                         }
                     }
-                    if (glu) {
+                    if constexpr (glu) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = v[i] * sigmoid_fast(u[i]);
                     } else {
@@ -292,13 +296,13 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                         for (int i = 0; i < 32; ++i)
                             if (col0 + i < p.n_out) v[i] += __bfloat162float(bias[col0 + i]);
                     }
-                    if (p.epilogue == GEMM_EPI_GELU) {
+                    if constexpr (EPI == GEMM_EPI_GELU) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
-                    } else if (p.epilogue == GEMM_EPI_SILU) {
+                    } else if constexpr (EPI == GEMM_EPI_SILU) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = silu(v[i]);
-                    } else if (p.epilogue == GEMM_EPI_GELU_TANH) {
+                    } else if constexpr (EPI == GEMM_EPI_GELU_TANH) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
                     }
@@ -482,15 +486,25 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     if (n_stages < 2) return IZB_ERR_UNSUPPORTED;
     static_assert(sizeof(GemmShared) <= 2048, "static shared memory budget");
     const int smem_bytes = n_stages * stage_bytes + staging;
-    static std::atomic<int> smem_set[IZB_MAX_DEVICES];  // the attribute is per device: one record each
     const int slot = ctx->device;
-    if (smem_set[slot].load(std::memory_order_relaxed) < smem_bytes) {
-        IZB_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-        smem_set[slot].store(smem_bytes, std::memory_order_relaxed);
+    void (*kernel)(GemmParams, int, int*) = nullptr;
+    switch (epilogue) {
+        case GEMM_EPI_NONE: kernel = gemm_tc_kernel<GEMM_EPI_NONE>; break;
+        case GEMM_EPI_GELU: kernel = gemm_tc_kernel<GEMM_EPI_GELU>; break;
+        case GEMM_EPI_SILU: kernel = gemm_tc_kernel<GEMM_EPI_SILU>; break;
+        case GEMM_EPI_SWIGLU: kernel = gemm_tc_kernel<GEMM_EPI_SWIGLU>; break;
+        case GEMM_EPI_GELU_TANH: kernel = gemm_tc_kernel<GEMM_EPI_GELU_TANH>; break;
+        default: kernel = gemm_tc_kernel<GEMM_EPI_GLU>; break;
+    }
+    // the attribute is per kernel and per device: one record for each pair
+    static std::atomic<int> smem_set[IZB_MAX_DEVICES][GEMM_EPI_GLU + 1];
+    if (smem_set[slot][epilogue].load(std::memory_order_relaxed) < smem_bytes) {
+        IZB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        smem_set[slot][epilogue].store(smem_bytes, std::memory_order_relaxed);
     }
     const long long tiles_bound = m_tiles * ((n_out + out_cols - 1) / out_cols);
     const int grid = static_cast<int>(std::min<long long>(tiles_bound, ctx->sm_count));
-    IZB_CUDA_TRY(launch_chained(ctx, gemm_tc_kernel, dim3(grid), dim3(GT_THREADS), smem_bytes, stream, p, n_stages, ctx->d_status + 1));
+    IZB_CUDA_TRY(launch_chained(ctx, kernel, dim3(grid), dim3(GT_THREADS), smem_bytes, stream, p, n_stages, ctx->d_status + 1));
     ctx->launches.fetch_add(1, std::memory_order_relaxed);
     return IZB_OK;
 }
