@@ -89,6 +89,31 @@ __device__ __forceinline__ float silu(float x) {
     return fmaf(0.5f * x, t, 0.5f * x);
 }
 
+// d (16 bytes of one output row: kind 0 = eight bf16, 1 = eight fp16, 2 = four fp32) plus the bf16 residual values
+// behind rs, of which `valid` exist.  A call, not inline code: it sits in the eight-fold unrolled flush loop of the
+// epilogue, which should stay small.
+__device__ __noinline__ uint4 gt_add_residual(uint4 d, const __nv_bfloat16* rs, int valid, int kind) {
+    uint32_t w[4] = {d.x, d.y, d.z, d.w};
+    if (kind == 2) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (e < valid) w[e] = __float_as_uint(__uint_as_float(w[e]) + __bfloat162float(rs[e]));
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float r_lo = 2 * e < valid ? __bfloat162float(rs[2 * e]) : 0.f;
+            const float r_hi = 2 * e + 1 < valid ? __bfloat162float(rs[2 * e + 1]) : 0.f;
+            if (kind == 1) {
+                const __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
+                w[e] = pack_f16x2(__low2float(h) + r_lo, __high2float(h) + r_hi);
+            } else {
+                w[e] = pack_bf16x2(bf16_lo_to_f32(w[e]) + r_lo, bf16_hi_to_f32(w[e]) + r_hi);
+            }
+        }
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // EPI: the epilogue, a compile-time choice: the epilogue loop of an instantiation holds its own activation only
 // (the erf / tanh / sigmoid bodies are 32-fold unrolled; all of them behind run-time branches in one loop made
 // the epilogue warps wait for instruction fetch).
@@ -342,29 +367,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                     const int col = flush_col0 + ch * vec;
                     if (grow < c.rows_end && ch * vec < valid_cols && col < p.n_out) {
                         uint4 d = lds128(stg + static_cast<uint32_t>(r * 128 + ((ch ^ (r & 7)) << 4)));
-                        if (p.residual) {
-                            // the residual rides in here, where a lane holds 16 contiguous bytes of one output row
-                            const __nv_bfloat16* rs = p.residual + grow * p.ld_res + col;
-                            uint32_t w[4] = {d.x, d.y, d.z, d.w};
-                            if (f32_out) {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (col + e < p.n_out) w[e] = __float_as_uint(__uint_as_float(w[e]) + __bfloat162float(rs[e]));
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float r_lo = col + 2 * e < p.n_out ? __bfloat162float(rs[2 * e]) : 0.f;
-                                    const float r_hi = col + 2 * e + 1 < p.n_out ? __bfloat162float(rs[2 * e + 1]) : 0.f;
-                                    if (f16_out) {
-                                        const __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
-                                        w[e] = pack_f16x2(__low2float(h) + r_lo, __high2float(h) + r_hi);
-                                    } else {
-                                        w[e] = pack_bf16x2(bf16_lo_to_f32(w[e]) + r_lo, bf16_hi_to_f32(w[e]) + r_hi);
-                                    }
-                                }
-                            }
-                            d = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+                        if (p.residual)  // the residual rides in here, where a lane holds 16 contiguous bytes of one output row
+                            d = gt_add_residual(d, p.residual + grow * p.ld_res + col, p.n_out - col, f32_out ? 2 : (f16_out ? 1 : 0));
                         if (f32_out) {
                             float* dst = static_cast<float*>(p.y) + grow * p.ldy + col;
                             if (vec_ok && col + 4 <= p.n_out) {
