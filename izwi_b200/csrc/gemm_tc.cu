@@ -114,10 +114,10 @@ __device__ __noinline__ uint4 gt_add_residual(uint4 d, const __nv_bfloat16* rs, 
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// EPI: the epilogue, a compile-time choice: the epilogue loop of an instantiation holds its own activation only
+// EPI, OUT: the epilogue and the output type, compile-time choices: the epilogue loop of an instantiation holds its own activation only
 // (the erf / tanh / sigmoid bodies are 32-fold unrolled; all of them behind run-time branches in one loop made
 // the epilogue warps wait for instruction fetch).
-template <int EPI>
+template <int EPI, int OUT>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ GemmParams p, int n_stages, int* status) {
     extern __shared__ __align__(1024) uint8_t dyn_smem[];
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     const uint32_t smem0 = smem_u32(dyn_smem);
     const int n_kb = (p.K + GT_BK - 1) / GT_BK;
     volatile int* abort_flag = &sh.abort_flag;
-    const bool f32_out = p.y_dtype == IZB_F32, f16_out = p.y_dtype == IZB_F16;
+    constexpr bool f32_out = OUT == IZB_F32, f16_out = OUT == IZB_F16;  // the output type, compile-time like the epilogue
     const uint32_t stage_out = smem0 + static_cast<uint32_t>(n_stages) * stage_bytes;  // output staging after the ring
     // 16-byte global stores need an aligned base and row stride
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (p.ldy * (f32_out ? 4 : 2)) % 16 == 0;
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                 }
                 // park this thread's 32 values in its staging row
                 const uint32_t my_row = stg + static_cast<uint32_t>(lane) * 128;
-                if (f32_out) {
+                if constexpr (f32_out) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q)
                         sts128(my_row + static_cast<uint32_t>((q ^ (lane & 7)) << 4), __float_as_uint(v[4 * q]),
@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint32_t dst = my_row + static_cast<uint32_t>(((half * 4 + q) ^ (lane & 7)) << 4);
-                        if (f16_out)
+                        if constexpr (f16_out)
                             sts128(dst, pack_f16x2(v[8 * q], v[8 * q + 1]), pack_f16x2(v[8 * q + 2], v[8 * q + 3]),
                                    pack_f16x2(v[8 * q + 4], v[8 * q + 5]), pack_f16x2(v[8 * q + 6], v[8 * q + 7]));
                         else
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                         uint4 d = lds128(stg + static_cast<uint32_t>(r * 128 + ((ch ^ (r & 7)) << 4)));
                         if (p.residual)  // the residual rides in here, where a lane holds 16 contiguous bytes of one output row
                             d = gt_add_residual(d, p.residual + grow * p.ld_res + col, p.n_out - col, f32_out ? 2 : (f16_out ? 1 : 0));
-                        if (f32_out) {
+                        if constexpr (f32_out) {
                             float* dst = static_cast<float*>(p.y) + grow * p.ldy + col;
                             if (vec_ok && col + 4 <= p.n_out) {
                                 *reinterpret_cast<uint4*>(dst) = d;
@@ -492,19 +492,28 @@ int gemm_tc_launch(izb_ctx* ctx, cudaStream_t stream, const void* x, long long l
     const int smem_bytes = n_stages * stage_bytes + staging;
     const int slot = ctx->device;
     void (*kernel)(GemmParams, int, int*) = nullptr;
+#define IZB_GT_PICK(E)                                                                               \
+    case E:                                                                                          \
+        kernel = y_dtype == IZB_F32   ? gemm_tc_kernel<E, IZB_F32>                                   \
+                 : y_dtype == IZB_F16 ? gemm_tc_kernel<E, IZB_F16>                                   \
+                                      : gemm_tc_kernel<E, IZB_BF16>;                                 \
+        break;
     switch (epilogue) {
-        case GEMM_EPI_NONE: kernel = gemm_tc_kernel<GEMM_EPI_NONE>; break;
-        case GEMM_EPI_GELU: kernel = gemm_tc_kernel<GEMM_EPI_GELU>; break;
-        case GEMM_EPI_SILU: kernel = gemm_tc_kernel<GEMM_EPI_SILU>; break;
-        case GEMM_EPI_SWIGLU: kernel = gemm_tc_kernel<GEMM_EPI_SWIGLU>; break;
-        case GEMM_EPI_GELU_TANH: kernel = gemm_tc_kernel<GEMM_EPI_GELU_TANH>; break;
-        default: kernel = gemm_tc_kernel<GEMM_EPI_GLU>; break;
+        IZB_GT_PICK(GEMM_EPI_NONE)
+        IZB_GT_PICK(GEMM_EPI_GELU)
+        IZB_GT_PICK(GEMM_EPI_SILU)
+        IZB_GT_PICK(GEMM_EPI_SWIGLU)
+        IZB_GT_PICK(GEMM_EPI_GELU_TANH)
+        default:
+        IZB_GT_PICK(GEMM_EPI_GLU)
     }
+#undef IZB_GT_PICK
     // the attribute is per kernel and per device: one record for each pair
-    static std::atomic<int> smem_set[IZB_MAX_DEVICES][GEMM_EPI_GLU + 1];
-    if (smem_set[slot][epilogue].load(std::memory_order_relaxed) < smem_bytes) {
+    static std::atomic<int> smem_set[IZB_MAX_DEVICES][(GEMM_EPI_GLU + 1) * 3];
+    const int which = epilogue * 3 + y_dtype;
+    if (smem_set[slot][which].load(std::memory_order_relaxed) < smem_bytes) {
         IZB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-        smem_set[slot][epilogue].store(smem_bytes, std::memory_order_relaxed);
+        smem_set[slot][which].store(smem_bytes, std::memory_order_relaxed);
     }
     const long long tiles_bound = m_tiles * ((n_out + out_cols - 1) / out_cols);
     const int grid = static_cast<int>(std::min<long long>(tiles_bound, ctx->sm_count));
